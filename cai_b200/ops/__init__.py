@@ -1,0 +1,163 @@
+"""Tensor-level wrappers over the sm_100a kernel library.
+
+Each function takes CUDA ``torch.Tensor`` arguments, launches on the current stream and returns
+its output tensor(s). There is no PyTorch fallback: these are the only implementation.
+"""
+from __future__ import annotations
+
+import torch
+
+from ._lib import KernelError, check, device_status, lib
+
+EPI_BF16, EPI_F32, EPI_F32_ACCUM, EPI_BF16_RESIDUAL = 0, 1, 2, 3
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t):
+    return t.data_ptr() if t is not None else None
+
+
+def gemm(a, b, *, trans_a=False, trans_b=False, out=None, out_dtype=torch.bfloat16, accumulate=False,
+         residual=None, alpha=1.0, sm_limit=0):
+    """``C[M,N] = alpha * op(A) @ op(B)^T`` on the tcgen05 tensor cores.
+
+    ``a`` is ``[M,K]`` (or ``[K,M]`` with ``trans_a``); ``b`` is ``[N,K]`` (or ``[K,N]`` with
+    ``trans_b``). With ``out_dtype=torch.float32`` and ``accumulate`` the product is added to
+    ``out``; ``residual`` (bf16 ``[M,N]``) is added in the epilogue.
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
+    assert a.stride(1) == 1 and b.stride(1) == 1
+    if trans_a:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if trans_b:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"K mismatch {K} vs {Kb}"
+    if out is None:
+        assert not accumulate
+        out = torch.empty((M, N), device=a.device, dtype=out_dtype)
+    assert out.shape == (M, N) and out.stride(1) == 1
+    if out.dtype == torch.bfloat16:
+        epi = EPI_BF16_RESIDUAL if residual is not None else EPI_BF16
+        assert not accumulate
+    else:
+        assert out.dtype == torch.float32 and residual is None
+        epi = EPI_F32_ACCUM if accumulate else EPI_F32
+    ldr = residual.stride(0) if residual is not None else 0
+    check(lib().cai_gemm_bf16(_p(a), _p(b), _p(out), _p(residual), M, N, K, a.stride(0), b.stride(0),
+                              out.stride(0), ldr, int(trans_a), int(trans_b), epi, float(alpha),
+                              int(sm_limit), _stream()), "gemm")
+    return out
+
+
+def rmsnorm_fwd(x, g, eps=1e-6):
+    rows, H = x.shape
+    y = torch.empty_like(x)
+    rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
+    check(lib().cai_rmsnorm_fwd(_p(x), _p(g), _p(y), _p(rstd), rows, H, float(eps), _stream()), "rmsnorm_fwd")
+    return y, rstd
+
+
+def rmsnorm_bwd(x, g, rstd, dy, dx=None, dg=None, dx_accumulate=False, dg_accumulate=False, scratch=None):
+    rows, H = x.shape
+    if dx is None:
+        assert not dx_accumulate
+        dx = torch.empty_like(x)
+    if dg is None:
+        assert not dg_accumulate
+        dg = torch.empty(H, device=x.device, dtype=torch.float32)
+    parts = lib().cai_rmsnorm_bwd_parts(rows)
+    if scratch is None:
+        scratch = torch.empty(parts * H, device=x.device, dtype=torch.float32)
+    assert scratch.numel() >= parts * H
+    check(lib().cai_rmsnorm_bwd(_p(x), _p(g), _p(rstd), _p(dy), _p(dx), _p(dg), _p(scratch), rows, H,
+                                int(dx_accumulate), int(dg_accumulate), _stream()), "rmsnorm_bwd")
+    return dx, dg
+
+
+def rope_table(seq, hd, theta=10000.0, device="cuda"):
+    t = torch.empty((seq, hd // 2, 2), device=device, dtype=torch.float32)
+    check(lib().cai_rope_table(_p(t), seq, hd, float(theta), _stream()), "rope_table")
+    return t
+
+
+def rope_apply_(qkv, table, seq, nh, nkv, hd, inverse=False):
+    T = qkv.shape[0]
+    check(lib().cai_rope_apply(_p(qkv), _p(table), T, seq, nh, nkv, hd, qkv.stride(0), int(inverse), _stream()),
+          "rope_apply")
+    return qkv
+
+
+def swiglu_fwd(gu):
+    T, F2 = gu.shape
+    act = torch.empty((T, F2 // 2), device=gu.device, dtype=gu.dtype)
+    check(lib().cai_swiglu_fwd(_p(gu), _p(act), T, F2 // 2, _stream()), "swiglu_fwd")
+    return act
+
+
+def swiglu_bwd(gu, dact):
+    T, F2 = gu.shape
+    dgu = torch.empty_like(gu)
+    check(lib().cai_swiglu_bwd(_p(gu), _p(dact), _p(dgu), T, F2 // 2, _stream()), "swiglu_bwd")
+    return dgu
+
+
+def embed_fwd(tokens, E, vocab_lo=0, vocab_hi=None):
+    T = tokens.numel()
+    H = E.shape[1]
+    hi = vocab_lo + E.shape[0] if vocab_hi is None else vocab_hi
+    out = torch.empty((T, H), device=E.device, dtype=E.dtype)
+    check(lib().cai_embed_fwd(_p(tokens), _p(E), _p(out), T, H, vocab_lo, hi, _stream()), "embed_fwd")
+    return out
+
+
+def embed_bwd_(tokens, dout, dE, vocab_lo=0, vocab_hi=None):
+    T = tokens.numel()
+    H = dE.shape[1]
+    hi = vocab_lo + dE.shape[0] if vocab_hi is None else vocab_hi
+    check(lib().cai_embed_bwd(_p(tokens), _p(dout), _p(dE), T, H, vocab_lo, hi, _stream()), "embed_bwd")
+    return dE
+
+
+def cross_entropy_(logits, targets, loss_sum, grad_scale=1.0, loss_scale=1.0, row_lse=None):
+    """In place: logits become dlogits; ``loss_sum`` (f32[1]) accumulates the scaled row losses."""
+    rows, V = logits.shape
+    check(lib().cai_cross_entropy(_p(logits), _p(targets), _p(loss_sum), _p(row_lse), rows, V, logits.stride(0),
+                                  float(grad_scale), float(loss_scale), _stream()), "cross_entropy")
+    return logits
+
+
+def adamw_(master, m, v, grad, param, step, lr, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.01, grad_scale=1.0):
+    n = master.numel()
+    check(lib().cai_adamw(_p(master), _p(m), _p(v), _p(grad), _p(param), n, float(lr), float(beta1), float(beta2),
+                          float(eps), float(wd), float(grad_scale), int(step), _stream()), "adamw")
+
+
+def flash_attn_fwd(qkv, B, S, nh, nkv, hd, scale=None):
+    assert qkv.dtype == torch.bfloat16 and qkv.is_contiguous()
+    scale = hd ** -0.5 if scale is None else scale
+    out = torch.empty((B * S, nh * hd), device=qkv.device, dtype=torch.bfloat16)
+    lse = torch.empty((B, nh, S), device=qkv.device, dtype=torch.float32)
+    check(lib().cai_flash_attn_fwd(_p(qkv), _p(out), _p(lse), B, S, nh, nkv, hd, float(scale), _stream()),
+          "flash_attn_fwd")
+    return out, lse
+
+
+def flash_attn_bwd(qkv, out, dout, lse, B, S, nh, nkv, hd, scale=None, dqkv=None, delta=None):
+    scale = hd ** -0.5 if scale is None else scale
+    if dqkv is None:
+        dqkv = torch.empty_like(qkv)
+    if delta is None:
+        delta = torch.empty((B, nh, S), device=qkv.device, dtype=torch.float32)
+    check(lib().cai_flash_attn_bwd(_p(qkv), _p(out), _p(dout), _p(lse), _p(delta), _p(dqkv), B, S, nh, nkv, hd,
+                                   float(scale), _stream()), "flash_attn_bwd")
+    return dqkv
+
+
+__all__ = [n for n in dir() if not n.startswith("_")]

@@ -1,0 +1,99 @@
+/* cai_kernels.h - C ABI of the sm_100a kernel library (libcai_kernels.so).
+ *
+ * Every launcher takes raw device pointers and a CUDA stream handle, enqueues work and returns
+ * immediately: 0 on success, a negative code on a host-side failure (cai_last_error() has the
+ * text). Device-side waits are bounded; a kernel that gives up records a code in the device's
+ * status word, which cai_status_read() returns.
+ *
+ * Matrices are row-major. bf16 tensors are 2-byte brain floats; "f32" are IEEE floats. */
+#ifndef CAI_KERNELS_H
+#define CAI_KERNELS_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+#define CAI_API extern "C" __attribute__((visibility("default")))
+#else
+#define CAI_API
+#endif
+
+/* GEMM epilogues */
+enum {
+    CAI_EPI_BF16 = 0,          /* C(bf16) = alpha*acc */
+    CAI_EPI_F32 = 1,           /* C(f32)  = alpha*acc */
+    CAI_EPI_F32_ACCUM = 2,     /* C(f32) += alpha*acc */
+    CAI_EPI_BF16_RESIDUAL = 3  /* C(bf16) = alpha*acc + R(bf16); R may alias C */
+};
+
+CAI_API int cai_status_read(int clear);
+CAI_API const char* cai_last_error(void);
+CAI_API int cai_sm_count(void);
+
+/* C[M,N] = alpha * sum_k A(m,k) B(n,k).
+ * a_mn_major = 0: A is stored [M,K] (pitch lda); 1: A is stored [K,M].
+ * b_mn_major = 0: B is stored [N,K] (pitch ldb); 1: B is stored [K,N].
+ * sm_limit > 0 caps the number of CTAs (to leave SMs to a concurrent stream). */
+CAI_API int cai_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                          long long lda, long long ldb, long long ldc, long long ldr, int a_mn_major,
+                          int b_mn_major, int epi, float alpha, int sm_limit, void* stream);
+
+/* ---- normalisation (reference: src/cuda/cai_kernels.cu:37-77, src/refmodel.c:47-77) */
+/* y = x * rsqrt(mean(x^2)+eps) * g ; rstd[row] saved for backward. */
+CAI_API int cai_rmsnorm_fwd(const void* x, const void* g, void* y, float* rstd, int rows, int H, float eps,
+                            void* stream);
+/* dx (+)= rmsnorm backward ; dg_partial is scratch [cai_rmsnorm_bwd_parts(rows), H] f32 ;
+ * dg(f32)[H] (+)= sum over rows. */
+CAI_API int cai_rmsnorm_bwd_parts(int rows);
+CAI_API int cai_rmsnorm_bwd(const void* x, const void* g, const float* rstd, const void* dy, void* dx,
+                            float* dg, float* dg_partial, int rows, int H, int dx_accumulate,
+                            int dg_accumulate, void* stream);
+
+/* ---- rotary embedding, in place on the q and k heads of a packed [T, (nh+2*nkv)*hd] buffer.
+ * table is float2 [seq, hd/2] (cos, sin); position of row t is t % seq. inverse=1 applies the
+ * transpose rotation (backward). */
+CAI_API int cai_rope_table(float* table, int seq, int hd, float theta, void* stream);
+CAI_API int cai_rope_apply(void* qkv, const float* table, int T, int seq, int nh, int nkv, int hd,
+                           long long ld, int inverse, void* stream);
+
+/* ---- SwiGLU on a packed [T, 2F] gate|up buffer (reference: src/cuda/cai_kernels.cu:146-160) */
+CAI_API int cai_swiglu_fwd(const void* gu, void* act, int T, int F, void* stream);
+CAI_API int cai_swiglu_bwd(const void* gu, const void* dact, void* dgu, int T, int F, void* stream);
+
+/* ---- embedding (reference: src/cuda/cai_kernels.cu:19-34). vocab_lo/vocab_hi give the slice of
+ * the vocabulary this rank owns; tokens outside produce zeros / are skipped. */
+CAI_API int cai_embed_fwd(const int* tokens, const void* E, void* out, int T, int H, int vocab_lo, int vocab_hi,
+                          void* stream);
+CAI_API int cai_embed_bwd(const int* tokens, const void* dout, float* dE, int T, int H, int vocab_lo,
+                          int vocab_hi, void* stream);
+
+/* ---- fused softmax cross-entropy over bf16 logits [rows, V] (pitch ld).
+ * In place: logits are overwritten by dlogits = (softmax - onehot) * grad_scale.
+ * loss_sum (f32[1]) += sum of row losses * loss_scale. targets < 0 are ignored.
+ * (reference: src/cuda/cai_kernels.cu:165-184) */
+CAI_API int cai_cross_entropy(void* logits, const int* targets, float* loss_sum, float* row_lse, int rows, int V,
+                              long long ld, float grad_scale, float loss_scale, void* stream);
+
+/* ---- AdamW on an fp32 master copy with bf16 write-back
+ * (reference: src/refmodel.c:481-492, src/cuda/cai_kernels.cu:185-194).
+ * p -= lr * (mhat / (sqrt(vhat) + eps) + wd * p); grad is multiplied by grad_scale first. */
+CAI_API int cai_adamw(float* master, float* m, float* v, const float* grad, void* param_bf16, long long n,
+                      float lr, float beta1, float beta2, float eps, float wd, float grad_scale, int step,
+                      void* stream);
+
+/* ---- small utilities */
+CAI_API int cai_cast_f32_to_bf16(const float* src, void* dst, long long n, void* stream);
+CAI_API int cai_cast_bf16_to_f32(const void* src, float* dst, long long n, void* stream);
+CAI_API int cai_fill_f32(float* dst, float v, long long n, void* stream);
+CAI_API int cai_add_bf16(const void* a, const void* b, void* out, long long n, void* stream);
+CAI_API int cai_l2_flush(void* scratch, long long bytes, void* stream);
+
+/* ---- causal GQA flash attention (reference: src/cuda/cai_kernels.cu:80-143)
+ * qkv is packed [B*S, (nh+2*nkv)*hd] bf16, head_dim 128. out is [B*S, nh*hd] bf16,
+ * lse is f32 [B, nh, S]. */
+CAI_API int cai_flash_attn_fwd(const void* qkv, void* out, float* lse, int B, int S, int nh, int nkv, int hd,
+                               float scale, void* stream);
+/* dqkv packed like qkv. delta is scratch f32 [B, nh, S]. */
+CAI_API int cai_flash_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
+                               void* dqkv, int B, int S, int nh, int nkv, int hd, float scale, void* stream);
+
+#endif /* CAI_KERNELS_H */
