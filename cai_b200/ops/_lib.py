@@ -51,11 +51,9 @@ def _declare(L):
     L.cai_fill_f32.argtypes = [P, F, LL, P]
     L.cai_add_bf16.argtypes = [P, P, P, LL, P]
     L.cai_l2_flush.argtypes = [P, LL, P]
-    for name in ("cai_flash_attn_fwd", "cai_flash_attn_bwd"):
-        if hasattr(L, name):
-            getattr(L, name).restype = I
     if hasattr(L, "cai_flash_attn_fwd"):
         L.cai_flash_attn_fwd.argtypes = [P, P, P, I, I, I, I, I, F, P]
+    if hasattr(L, "cai_flash_attn_bwd"):
         L.cai_flash_attn_bwd.argtypes = [P, P, P, P, P, P, I, I, I, I, I, F, P]
 
 

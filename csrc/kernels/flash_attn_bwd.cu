@@ -1,0 +1,447 @@
+// flash_attn_bwd.cu - causal grouped-query flash attention backward for sm_100a, head_dim 128.
+//
+// Three launches, all deterministic (no atomics):
+//   1. attn_delta_kernel   delta[b,h,s] = sum_d dO * O                      (bandwidth bound)
+//   2. attn_dkdv_kernel    one CTA per (kv tile, kv head, batch). It sweeps the query tiles at or
+//                          below the diagonal of every query head of the group and accumulates
+//                          dK and dV in tensor memory. Scores are computed transposed
+//                          (S^T = K Q^T, dP^T = V dO^T) so that TMEM lanes are kv rows; the bf16
+//                          P^T and dS^T are written back over S^T / dP^T and feed
+//                          dV += P^T dO and dK += dS^T Q as A operands straight from TMEM.
+//   3. attn_dq_kernel      one CTA per (q tile, head, batch): S = Q K^T, dP = dO V^T,
+//                          dS -> TMEM, dQ += dS K.
+// Q, K, V and dO tiles arrive by TMA from the packed activation; each shared-memory tile serves
+// both as a K-major operand (for the score products) and as an MN-major operand (for the
+// gradient products) through different UMMA descriptors, so nothing is transposed in memory.
+//
+// Replaces the reference's one-thread-per-query backward, which recomputes dp twice, scatters
+// dK/dV with atomicAdd and never zeroes dq/dk/dv (src/cuda/cai_kernels.cu:110-143).
+#include <math.h>
+
+#include "attn_common.cuh"
+#include "cai_kernels.h"
+#include "host_common.h"
+#include "sm100.cuh"
+
+namespace cai {
+
+constexpr int kAttnBwdThreads = 256;  // warp 0 TMA, warp 1 MMA, warps 4-7 compute
+
+struct AttnBwdParams {
+    int B, S, nh, nkv;
+    float scale, scale_log2;
+    const float* lse;
+    const float* delta;
+    __nv_bfloat16* dqkv;
+    int* status;
+};
+
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
+                                  float* __restrict__ delta, int B, int S, int nh) {
+    const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const long long total = static_cast<long long>(B) * S * nh;
+    if (w >= total) return;
+    const int h = w % nh;
+    const long long row = w / nh;  // b*S + s
+    const long long off = row * (static_cast<long long>(nh) * kAttnHD) + h * kAttnHD + lane * 4;
+    const uint2 a = *reinterpret_cast<const uint2*>(out + off);
+    const uint2 d = *reinterpret_cast<const uint2*>(dout + off);
+    float s = bf16_lo(a.x) * bf16_lo(d.x) + bf16_hi(a.x) * bf16_hi(d.x) + bf16_lo(a.y) * bf16_lo(d.y) +
+              bf16_hi(a.y) * bf16_hi(d.y);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) {
+        const int b = row / S, sidx = row % S;
+        delta[(static_cast<long long>(b) * nh + h) * S + sidx] = s;
+    }
+}
+
+__device__ __forceinline__ void bar_sync_compute() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Store one finished 128x128 fp32 accumulator (TMEM) as bf16 rows of the packed gradient buffer.
+__device__ __forceinline__ void store_acc_bf16(uint32_t tacc, __nv_bfloat16* dst_row) {
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tacc + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(v[j4 * 8 + 0]), __uint_as_float(v[j4 * 8 + 1]));
+            o.y = pack_bf16(__uint_as_float(v[j4 * 8 + 2]), __uint_as_float(v[j4 * 8 + 3]));
+            o.z = pack_bf16(__uint_as_float(v[j4 * 8 + 4]), __uint_as_float(v[j4 * 8 + 5]));
+            o.w = pack_bf16(__uint_as_float(v[j4 * 8 + 6]), __uint_as_float(v[j4 * 8 + 7]));
+            *reinterpret_cast<uint4*>(dst_row + c * 32 + j4 * 8) = o;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------- dK / dV
+__global__ void __launch_bounds__(kAttnBwdThreads, 1)
+attn_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
+                 const AttnBwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sK = smem;
+    uint8_t* sV = smem + kAttnTileBytes;
+    uint8_t* sQ = smem + 2 * kAttnTileBytes;   // 2 stages
+    uint8_t* sdO = smem + 4 * kAttnTileBytes;  // 2 stages
+    float* sL = reinterpret_cast<float*>(smem + 6 * kAttnTileBytes);  // [2][128] lse * log2e
+    float* sD = sL + 256;                                              // [2][128] delta
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sD + 256);
+    uint64_t* kv_full = bars;
+    uint64_t* qdo_full = bars + 1;
+    uint64_t* qdo_empty = bars + 3;
+    uint64_t* sdp_full = bars + 5;
+    uint64_t* pds_ready = bars + 6;
+    uint64_t* final_bar = bars + 7;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j = blockIdx.x;  // kv tile
+    const int g = blockIdx.y, b = blockIdx.z;
+    const int rep = p.nh / p.nkv;
+    const int nq = p.S / kAttnTile;
+    const int per_head = nq - j;          // query tiles at or below the diagonal
+    const int iters = rep * per_head;
+    const int row_base = b * p.S;
+    const int col_k = (p.nh + g) * kAttnHD, col_v = (p.nh + p.nkv + g) * kAttnHD;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tm_qkv);
+        tma_prefetch_desc(&tm_do);
+        mbar_init(kv_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&qdo_full[i], 1);
+            mbar_init(&qdo_empty[i], 1);
+        }
+        mbar_init(sdp_full, 1);
+        mbar_init(pds_ready, 128);
+        mbar_init(final_bar, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 384;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int kv_row = row_base + j * kAttnTile;
+            mbar_expect_tx(kv_full, 2 * kAttnTileBytes);
+            tma_load_2d(sK, &tm_qkv, kv_full, col_k, kv_row);
+            tma_load_2d(sK + kAttnSub, &tm_qkv, kv_full, col_k + 64, kv_row);
+            tma_load_2d(sV, &tm_qkv, kv_full, col_v, kv_row);
+            tma_load_2d(sV + kAttnSub, &tm_qkv, kv_full, col_v + 64, kv_row);
+            bool ok = true;
+            for (int it = 0; it < iters && ok; ++it) {
+                const int slot = it & 1;
+                const uint32_t ph = (it >> 1) & 1;
+                const int h = g * rep + it / per_head;
+                const int q_row = row_base + (j + it % per_head) * kAttnTile;
+                if (!mbar_wait(&qdo_empty[slot], ph ^ 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+                mbar_expect_tx(&qdo_full[slot], 2 * kAttnTileBytes);
+                uint8_t* q = sQ + slot * kAttnTileBytes;
+                uint8_t* d = sdO + slot * kAttnTileBytes;
+                tma_load_2d(q, &tm_qkv, &qdo_full[slot], h * kAttnHD, q_row);
+                tma_load_2d(q + kAttnSub, &tm_qkv, &qdo_full[slot], h * kAttnHD + 64, q_row);
+                tma_load_2d(d, &tm_do, &qdo_full[slot], h * kAttnHD, q_row);
+                tma_load_2d(d + kAttnSub, &tm_do, &qdo_full[slot], h * kAttnHD + 64, q_row);
+            }
+            if (!ok)
+                for (int i = 0; i < 32; ++i) __nanosleep(50000);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_kk = umma_idesc_bf16(128, 128, 0, 0);
+            const uint32_t idesc_mn = umma_idesc_bf16(128, 128, 0, 1);
+            const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aD = smem_u32(sdO);
+            bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN);
+            for (int it = 0; it < iters && ok; ++it) {
+                const int slot = it & 1;
+                const uint32_t ph = (it >> 1) & 1;
+                if (!mbar_wait(&qdo_full[slot], ph, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+                tc_fence_after();
+                issue_qk(tS, aK, aQ + slot * kAttnTileBytes, idesc_kk);    // S^T  = K Q^T
+                issue_qk(tdP, aV, aD + slot * kAttnTileBytes, idesc_kk);   // dP^T = V dO^T
+                umma_commit(sdp_full);
+                if (!mbar_wait(pds_ready, it & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+                tc_fence_after();
+                issue_pv(tdV, tS, aD + slot * kAttnTileBytes, idesc_mn, it > 0);   // dV += P^T dO
+                issue_pv(tdK, tdP, aQ + slot * kAttnTileBytes, idesc_mn, it > 0);  // dK += dS^T Q
+                umma_commit(&qdo_empty[slot]);
+            }
+            if (ok) umma_commit(final_bar);
+        }
+    } else if (warp >= 4) {
+        const int r = (warp & 3) * 32 + lane;  // kv row inside the tile == TMEM lane
+        const uint32_t lane_bits = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        bool ok = true;
+        for (int it = 0; it < iters; ++it) {
+            const int h = g * rep + it / per_head;
+            const int i = j + it % per_head;
+            const int buf = it & 1;
+            const long long vec = (static_cast<long long>(b) * p.nh + h) * p.S + i * kAttnTile + r;
+            sL[buf * 128 + r] = p.lse[vec] * 1.4426950408889634f;
+            sD[buf * 128 + r] = p.delta[vec];
+            bar_sync_compute();
+            if (!mbar_wait(sdp_full, it & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+            tc_fence_after();
+            const bool diag = (i == j);
+            const float* L = sL + buf * 128;
+            const float* D = sD + buf * 128;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t s[32], dp[32];
+                tmem_ld_32x32(tS + lane_bits + c * 32, s);
+                tmem_ld_32x32(tdP + lane_bits + c * 32, dp);
+                tmem_ld_wait();
+                uint32_t pk[16], dk[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    const int q0 = c * 32 + e;
+                    float p0 = fast_exp2(__uint_as_float(s[e]) * p.scale_log2 - L[q0]);
+                    float p1 = fast_exp2(__uint_as_float(s[e + 1]) * p.scale_log2 - L[q0 + 1]);
+                    if (diag) {  // key (row r) may not lie after the query (column)
+                        if (r > q0) p0 = 0.f;
+                        if (r > q0 + 1) p1 = 0.f;
+                    }
+                    const float d0 = p0 * (__uint_as_float(dp[e]) - D[q0]) * p.scale;
+                    const float d1 = p1 * (__uint_as_float(dp[e + 1]) - D[q0 + 1]) * p.scale;
+                    pk[e >> 1] = pack_bf16(p0, p1);
+                    dk[e >> 1] = pack_bf16(d0, d1);
+                }
+                tmem_st_32x16(tS + lane_bits + c * 16, pk);
+                tmem_st_32x16(tdP + lane_bits + c * 16, dk);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(pds_ready);
+        }
+        if (ok && mbar_wait(final_bar, 0, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) {
+            tc_fence_after();
+            const long long grow = static_cast<long long>(row_base) + j * kAttnTile + r;
+            const long long ld = static_cast<long long>(p.nh + 2 * p.nkv) * kAttnHD;
+            if (iters > 0) {
+                store_acc_bf16(tdK + lane_bits, p.dqkv + grow * ld + col_k);
+                store_acc_bf16(tdV + lane_bits, p.dqkv + grow * ld + col_v);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---------------------------------------------------------------------------- dQ
+__global__ void __launch_bounds__(kAttnBwdThreads, 1)
+attn_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
+               const AttnBwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sQ = smem;
+    uint8_t* sdO = smem + kAttnTileBytes;
+    uint8_t* sK = smem + 2 * kAttnTileBytes;  // 2 stages
+    uint8_t* sV = smem + 4 * kAttnTileBytes;  // 2 stages
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kAttnTileBytes);
+    uint64_t* q_full = bars;
+    uint64_t* kv_full = bars + 1;
+    uint64_t* kv_empty = bars + 3;
+    uint64_t* sdp_full = bars + 5;
+    uint64_t* ds_ready = bars + 6;
+    uint64_t* final_bar = bars + 7;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int i = gridDim.x - 1 - blockIdx.x;  // q tile, heaviest first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int g = h / (p.nh / p.nkv);
+    const int n = i + 1;
+    const int row_base = b * p.S;
+    const int col_q = h * kAttnHD, col_k = (p.nh + g) * kAttnHD, col_v = (p.nh + p.nkv + g) * kAttnHD;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tm_qkv);
+        tma_prefetch_desc(&tm_do);
+        mbar_init(q_full, 1);
+        for (int k = 0; k < 2; ++k) {
+            mbar_init(&kv_full[k], 1);
+            mbar_init(&kv_empty[k], 1);
+        }
+        mbar_init(sdp_full, 1);
+        mbar_init(ds_ready, 128);
+        mbar_init(final_bar, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdQ = tmem_base + 256;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int q_row = row_base + i * kAttnTile;
+            mbar_expect_tx(q_full, 2 * kAttnTileBytes);
+            tma_load_2d(sQ, &tm_qkv, q_full, col_q, q_row);
+            tma_load_2d(sQ + kAttnSub, &tm_qkv, q_full, col_q + 64, q_row);
+            tma_load_2d(sdO, &tm_do, q_full, col_q, q_row);
+            tma_load_2d(sdO + kAttnSub, &tm_do, q_full, col_q + 64, q_row);
+            bool ok = true;
+            for (int j = 0; j < n && ok; ++j) {
+                const int slot = j & 1;
+                const uint32_t ph = (j >> 1) & 1;
+                const int kv_row = row_base + j * kAttnTile;
+                if (!mbar_wait(&kv_empty[slot], ph ^ 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+                mbar_expect_tx(&kv_full[slot], 2 * kAttnTileBytes);
+                uint8_t* k = sK + slot * kAttnTileBytes;
+                uint8_t* v = sV + slot * kAttnTileBytes;
+                tma_load_2d(k, &tm_qkv, &kv_full[slot], col_k, kv_row);
+                tma_load_2d(k + kAttnSub, &tm_qkv, &kv_full[slot], col_k + 64, kv_row);
+                tma_load_2d(v, &tm_qkv, &kv_full[slot], col_v, kv_row);
+                tma_load_2d(v + kAttnSub, &tm_qkv, &kv_full[slot], col_v + 64, kv_row);
+            }
+            if (!ok)
+                for (int k = 0; k < 32; ++k) __nanosleep(50000);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_kk = umma_idesc_bf16(128, 128, 0, 0);
+            const uint32_t idesc_mn = umma_idesc_bf16(128, 128, 0, 1);
+            const uint32_t aQ = smem_u32(sQ), aD = smem_u32(sdO), aK = smem_u32(sK), aV = smem_u32(sV);
+            bool ok = mbar_wait(q_full, 0, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN);
+            for (int j = 0; j < n && ok; ++j) {
+                const int slot = j & 1;
+                const uint32_t ph = (j >> 1) & 1;
+                if (!mbar_wait(&kv_full[slot], ph, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+                tc_fence_after();
+                issue_qk(tS, aQ, aK + slot * kAttnTileBytes, idesc_kk);    // S  = Q K^T
+                issue_qk(tdP, aD, aV + slot * kAttnTileBytes, idesc_kk);   // dP = dO V^T
+                umma_commit(sdp_full);
+                if (!mbar_wait(ds_ready, j & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+                tc_fence_after();
+                issue_pv(tdQ, tdP, aK + slot * kAttnTileBytes, idesc_mn, j > 0);  // dQ += dS K
+                umma_commit(&kv_empty[slot]);
+            }
+            if (ok) umma_commit(final_bar);
+        }
+    } else if (warp >= 4) {
+        const int r = (warp & 3) * 32 + lane;  // q row inside the tile
+        const uint32_t lane_bits = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const long long vec = (static_cast<long long>(b) * p.nh + h) * p.S + i * kAttnTile + r;
+        const float lse2 = p.lse[vec] * 1.4426950408889634f;
+        const float dl = p.delta[vec];
+        bool ok = true;
+        for (int j = 0; j < n; ++j) {
+            if (!mbar_wait(sdp_full, j & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+            tc_fence_after();
+            const bool diag = (j == i);
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t s[32], dp[32];
+                tmem_ld_32x32(tS + lane_bits + c * 32, s);
+                tmem_ld_32x32(tdP + lane_bits + c * 32, dp);
+                tmem_ld_wait();
+                uint32_t dk[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    const int k0 = c * 32 + e;
+                    float p0 = fast_exp2(__uint_as_float(s[e]) * p.scale_log2 - lse2);
+                    float p1 = fast_exp2(__uint_as_float(s[e + 1]) * p.scale_log2 - lse2);
+                    if (diag) {
+                        if (k0 > r) p0 = 0.f;
+                        if (k0 + 1 > r) p1 = 0.f;
+                    }
+                    dk[e >> 1] = pack_bf16(p0 * (__uint_as_float(dp[e]) - dl) * p.scale,
+                                           p1 * (__uint_as_float(dp[e + 1]) - dl) * p.scale);
+                }
+                tmem_st_32x16(tdP + lane_bits + c * 16, dk);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(ds_ready);
+        }
+        if (ok && mbar_wait(final_bar, 0, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) {
+            tc_fence_after();
+            const long long grow = static_cast<long long>(row_base) + i * kAttnTile + r;
+            const long long ld = static_cast<long long>(p.nh + 2 * p.nkv) * kAttnHD;
+            store_acc_bf16(tdQ + lane_bits, p.dqkv + grow * ld + col_q);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+}  // namespace cai
+
+using namespace cai;
+
+CAI_API int cai_flash_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
+                               void* dqkv, int B, int S, int nh, int nkv, int hd, float scale, void* stream) {
+    if (hd != kAttnHD || S % kAttnTile || nkv <= 0 || nh % nkv) {
+        set_last_error("flash_attn_bwd: needs head_dim 128, seq %% 128 == 0, heads %% kv_heads == 0");
+        return CAI_K_BAD_ARG;
+    }
+    if (B <= 0 || S <= 0) return CAI_K_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long long ld = static_cast<long long>(nh + 2 * nkv) * hd;
+    const long long ldo = static_cast<long long>(nh) * hd;
+    CUtensorMap tm_qkv, tm_do;
+    if (!encode_tmap_2d(&tm_qkv, qkv, static_cast<uint64_t>(B) * S, ld, ld, 64, kAttnTile, 2)) return CAI_K_BAD_ARG;
+    if (!encode_tmap_2d(&tm_do, dout, static_cast<uint64_t>(B) * S, ldo, ldo, 64, kAttnTile, 2)) return CAI_K_BAD_ARG;
+    constexpr int smem_bytes = 6 * kAttnTileBytes + 2048 + 1024 + 256;
+    static bool configured[64] = {};
+    const int dev = current_device();
+    if (!configured[dev & 63]) {
+        if (cudaFuncSetAttribute(attn_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
+            set_last_error("cudaFuncSetAttribute(attn_bwd) failed");
+            return CAI_K_CUDA;
+        }
+        configured[dev & 63] = true;
+    }
+    const long long warps = static_cast<long long>(B) * S * nh;
+    attn_delta_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(dout), delta, B, S, nh);
+    AttnBwdParams p;
+    p.B = B; p.S = S; p.nh = nh; p.nkv = nkv;
+    p.scale = scale;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.lse = lse;
+    p.delta = delta;
+    p.dqkv = static_cast<__nv_bfloat16*>(dqkv);
+    p.status = status_words(dev);
+    const int nq = S / kAttnTile;
+    attn_dkdv_kernel<<<dim3(nq, nkv, B), kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_do, p);
+    attn_dq_kernel<<<dim3(nq, nh, B), kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_do, p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_last_error("attn_bwd launch failed: %s", cudaGetErrorString(e));
+        return CAI_K_CUDA;
+    }
+    return CAI_K_OK;
+}
