@@ -1,0 +1,351 @@
+"""Device engine: one rank's compiled plan, its arena and the native executor.
+
+``Engine`` is the public training API: build it from a config (or from plan files the offline
+compiler wrote), feed it pinned host batches with :meth:`Engine.step`, read the loss back. All
+device work — kernels, NCCL calls, fused compute+collective kernels — is issued by the C++
+executor in ``libcai_kernels.so``; Python only owns the arena allocation (one ``torch`` buffer),
+parameter initialisation, batches and checkpoints.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+import tempfile
+from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_ulonglong, c_void_p
+from pathlib import Path
+
+import torch
+
+from .. import plan as planlib
+from ..ops import _lib as klib
+
+_TORCH_DTYPE = {0: torch.float32, 1: torch.bfloat16, 2: torch.float16, 3: torch.uint8, 4: torch.uint8,
+                5: torch.int32, 6: torch.uint8}
+
+
+class TraceRec(ctypes.Structure):
+    _fields_ = [("op_index", ctypes.c_uint32), ("kind", ctypes.c_uint16), ("stream", ctypes.c_uint16),
+                ("start_s", ctypes.c_double), ("end_s", ctypes.c_double), ("bytes", ctypes.c_uint64),
+                ("flops", ctypes.c_uint64)]
+
+
+def _declare_runtime(L):
+    if getattr(L, "_cai_rt_declared", False):
+        return
+    P, I = c_void_p, c_int
+    L.cai_exec_create.argtypes = [ctypes.POINTER(P), P, c_size_t, P]
+    L.cai_exec_destroy.argtypes = [P]
+    L.cai_exec_destroy.restype = None
+    L.cai_nccl_unique_id.argtypes = [c_char_p, P]
+    L.cai_exec_init_comm.argtypes = [P, c_char_p, I, P, P, I, I]
+    L.cai_exec_stream.argtypes = [P, I]
+    L.cai_exec_stream.restype = P
+    L.cai_exec_tensor_ptr.argtypes = [P, I]
+    L.cai_exec_tensor_ptr.restype = P
+    L.cai_exec_launches.argtypes = [P]
+    L.cai_exec_launches.restype = c_ulonglong
+    L.cai_exec_step.argtypes = [P, I, c_float]
+    L.cai_exec_sync.argtypes = [P]
+    L.cai_exec_use_graph.argtypes = [P, I]
+    L.cai_exec_trace_enable.argtypes = [P, I]
+    L.cai_exec_trace_read.argtypes = [P, ctypes.POINTER(TraceRec), I]
+    L.cai_exec_set_sm_limit.argtypes = [P, I]
+    L.cai_exec_set_sm_limit.restype = None
+    if hasattr(L, "cai_fused_attach"):
+        L.cai_fused_attach.argtypes = [P, I, I, I, ctypes.POINTER(P), ctypes.POINTER(P), P, c_longlong, c_longlong]
+    L._cai_rt_declared = True
+
+
+def nccl_library_path() -> str:
+    """The NCCL that torch itself loaded (so the executor's communicators share one library)."""
+    try:
+        import nvidia.nccl
+        cand = Path(list(nvidia.nccl.__path__)[0]) / "lib" / "libnccl.so.2"
+        if cand.exists():
+            return str(cand)
+    except Exception:
+        pass
+    return "libnccl.so.2"
+
+
+def synthetic_batch(vocab, seq, rows, step, seed, rank_offset=0, out_tokens=None, out_targets=None):
+    """Uniform-random token rows and their next-token targets (pinned int32 ``[rows, seq]``)."""
+    g = torch.Generator(device="cpu")
+    g.manual_seed((int(seed) * 1000003 + int(step)) * 4099 + int(rank_offset))
+    s = torch.randint(0, vocab, (rows, seq + 1), generator=g, dtype=torch.int32)
+    if out_tokens is None:
+        out_tokens = torch.empty((rows, seq), dtype=torch.int32).pin_memory()
+        out_targets = torch.empty((rows, seq), dtype=torch.int32).pin_memory()
+    out_tokens.copy_(s[:, :-1])
+    out_targets.copy_(s[:, 1:])
+    return out_tokens, out_targets
+
+
+class Engine:
+    """Executes one rank's plan. See the module docstring."""
+
+    def __init__(self, config=None, *, config_text=None, plan_path=None, topology_path=None, rank=None, world=None,
+                 local_rank=None, graph=False, init_params=True, comm=None):
+        self.rank = int(os.environ.get("RANK", 0)) if rank is None else rank
+        self.world = int(os.environ.get("WORLD_SIZE", 1)) if world is None else world
+        self.local_rank = int(os.environ.get("LOCAL_RANK", self.rank)) if local_rank is None else local_rank
+        if not torch.cuda.is_available():
+            raise RuntimeError("Engine needs a CUDA device; use cai_b200.plan.Simulator for GPU-free replay")
+        torch.cuda.set_device(self.local_rank)
+        self.device = torch.device("cuda", self.local_rank)
+        self._tmp = None
+        if plan_path is None:
+            if config_text is None:
+                config_text = Path(config).read_text()
+            if comm is not None:
+                config_text += f"\ncomm = {comm}\n"
+            self.config_text = config_text
+            self._tmp = tempfile.TemporaryDirectory(prefix="cai_plan_")
+            planlib.compile_plans(config_text, self._tmp.name, ranks=(self.rank, self.rank + 1), version=2, text=True)
+            plan_path = Path(self._tmp.name) / f"plan.rank{self.rank:06d}.bin"
+            topology_path = Path(self._tmp.name) / "topology.bin"
+        else:
+            self.config_text = config_text
+        self.plan = planlib.PlanFile(plan_path)
+        if self.plan.hdr.version != 2:
+            raise planlib.PlanError(f"{plan_path} is a cost-only (version 1) plan; compile with --exec")
+        self.topology = planlib.read_topology(topology_path)
+        th = planlib.fnv1a(bytes(self.topology))
+        if th != self.plan.hdr.topology_hash:
+            raise planlib.PlanError("plan was compiled for a different topology (hash mismatch)")
+        if self.plan.hdr.world_size != self.world:
+            raise planlib.PlanError(f"plan world_size {self.plan.hdr.world_size} != launched world {self.world}")
+        self.hdr, self.model, self.train = self.plan.hdr, self.plan.model, self.plan.train
+        self.named = self.plan.named_dict()
+
+        L = klib.lib()
+        _declare_runtime(L)
+        self.L = L
+        # the whole arena is ONE allocation; every tensor of the plan is an offset into it
+        self.arena = torch.empty(int(self.hdr.arena_bytes) + 1024, dtype=torch.uint8, device=self.device)
+        base = (self.arena.data_ptr() + 1023) & ~1023
+        self._arena_shift = base - self.arena.data_ptr()
+        self.arena.zero_()
+        self.ex = c_void_p()
+        klib.check(L.cai_exec_create(ctypes.byref(self.ex), self.plan.raw, len(self.plan.raw), c_void_p(base)),
+                   "exec_create")
+        self.stream = torch.cuda.ExternalStream(L.cai_exec_stream(self.ex, 0), device=self.device)
+        self.step_count = 0
+        self.lr = float(self.train.lr)
+        self._init_comms()
+        ga, T = self.hdr.num_microbatches, self.model.microbatch * self.model.seq_len
+        self.tokens_dev = self.view("@tokens")
+        self.targets_dev = self.view("@targets")
+        self.loss_dev = self.view("@loss")
+        self.loss_host = torch.zeros(8, dtype=torch.float32).pin_memory()
+        self.batch_rows, self.batch_cols = ga, T
+        with torch.cuda.stream(self.stream):
+            klib.check(L.cai_rope_table(c_void_p(self.view("@rope_table").data_ptr()), self.model.seq_len,
+                                        self.model.head_dim, float(self.train.rope_theta),
+                                        c_void_p(self.stream.cuda_stream)), "rope_table")
+        if init_params:
+            self.init_parameters()
+        if graph:
+            self.use_graph(True)
+        torch.cuda.synchronize(self.device)
+
+    # ------------------------------------------------------------------ arena views
+    def tensor_view(self, tid: int) -> torch.Tensor:
+        t = self.plan.tensors[tid]
+        rows, cols, ld = self.plan.shape(tid)
+        dt = _TORCH_DTYPE[t.dtype]
+        off = self._arena_shift + t.offset
+        flat = self.arena[off:off + t.nbytes].view(dt)
+        if ld == 0 or rows * ld != flat.numel():
+            return flat
+        return flat.view(rows, ld)[:, :cols]
+
+    def view(self, name: str) -> torch.Tensor:
+        return self.tensor_view(self.named[name].tensor)
+
+    def param(self, name: str) -> torch.Tensor:
+        return self.view(name)
+
+    def grad(self, name: str) -> torch.Tensor:
+        return self.tensor_view(self.named[name].grad)
+
+    def parameter_names(self):
+        return [k for k, v in self.named.items() if v.init_std >= 0]
+
+    # ------------------------------------------------------------------ communicators
+    def _init_comms(self):
+        self.dist = None
+        groups = [g for g in self.plan.groups if g.size > 1]
+        if not groups:
+            return
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            dist.init_process_group(backend="cpu:gloo,cuda:nccl", rank=self.rank, world_size=self.world,
+                                    device_id=self.device)
+        self.dist = dist
+        store = dist.distributed_c10d._get_default_store()
+        libpath = nccl_library_path().encode()
+        for g in groups:
+            members = planlib.group_members(self.config_text, g.kind, self.rank)
+            me = members.index(self.rank)
+            n_ids = 2 if g.kind == planlib.GROUP_PP else 1
+            key = f"cai/nccl/{self.hdr.plan_hash:x}/{g.kind}/{g.color}"
+            if me == 0:
+                blob = b""
+                for _ in range(n_ids):
+                    buf = ctypes.create_string_buffer(128)
+                    klib.check(self.L.cai_nccl_unique_id(libpath, buf), "nccl_unique_id")
+                    blob += buf.raw
+                store.set(key, blob)
+            else:
+                blob = store.get(key)
+            id1 = ctypes.create_string_buffer(blob[:128], 128)
+            id2 = ctypes.create_string_buffer(blob[128:256], 128) if n_ids == 2 else None
+            klib.check(self.L.cai_exec_init_comm(self.ex, libpath, g.kind, id1, id2, len(members), me), "init_comm")
+        self._attach_fused(groups)
+
+    def _attach_fused(self, groups):
+        """Give the fused compute+collective kernels their symmetric buffers (see parallel.symm)."""
+        if not self.train.comm_mode or not hasattr(self.L, "cai_fused_attach"):
+            return
+        from ..parallel import symm
+        self.symm = symm.attach(self, groups)
+
+    # ------------------------------------------------------------------ parameters
+    def _global_shape_and_slice(self, name, rows, cols):
+        """Global shape of a parameter and the index expression of this rank's shard."""
+        m, tp = self.model, self.hdr.tp
+        tp_id = self.rank % tp
+        H, hd = m.hidden_size, m.head_dim
+        base = name.split(".")[-1]
+        if base in ("embed", "lm_head"):
+            return (m.vocab_size, H), (slice(tp_id * rows, (tp_id + 1) * rows), slice(None))
+        if base == "wqkv":
+            nh_l, nkv_l = m.num_heads // tp, m.num_kv_heads // tp
+            q0, k0, v0 = 0, m.num_heads * hd, (m.num_heads + m.num_kv_heads) * hd
+            idx = torch.cat([torch.arange(q0 + tp_id * nh_l * hd, q0 + (tp_id + 1) * nh_l * hd),
+                             torch.arange(k0 + tp_id * nkv_l * hd, k0 + (tp_id + 1) * nkv_l * hd),
+                             torch.arange(v0 + tp_id * nkv_l * hd, v0 + (tp_id + 1) * nkv_l * hd)])
+            return ((m.num_heads + 2 * m.num_kv_heads) * hd, H), (idx, slice(None))
+        if base == "wo":
+            return (H, m.num_heads * hd), (slice(None), slice(tp_id * cols, (tp_id + 1) * cols))
+        if base == "wgu":
+            F, F_l = m.ffn_hidden, m.ffn_hidden // tp
+            idx = torch.cat([torch.arange(tp_id * F_l, (tp_id + 1) * F_l), torch.arange(F + tp_id * F_l, F + (tp_id + 1) * F_l)])
+            return (2 * F, H), (idx, slice(None))
+        if base == "wd":
+            return (H, m.ffn_hidden), (slice(None), slice(tp_id * cols, (tp_id + 1) * cols))
+        return (rows, cols), (slice(None), slice(None))
+
+    def init_parameters(self):
+        """N(0, init_std) for matrices, ones for norm gains. Every rank draws the full tensor from a
+        seed derived from the parameter's name and keeps its shard, so the model is the same for
+        every parallel layout."""
+        n_flat = int(self.plan.xhdr.param_elems)
+        n_opt = int(self.plan.xhdr.opt_elems)
+        master = self.view("@flat_master")
+        dp, dp_id = self.hdr.dp, self.rank // (self.hdr.tp * self.hdr.num_stages * self.hdr.cp)
+        shard_lo = dp_id * n_opt if dp > 1 else 0
+        shard_hi = min(shard_lo + n_opt, n_flat) if dp > 1 else n_flat
+        with torch.cuda.stream(self.stream):
+            self.view("@flat_m").zero_()
+            self.view("@flat_v").zero_()
+            master.zero_()
+            for name, nt in self.named.items():
+                if nt.init_std < 0:
+                    continue
+                w = self.tensor_view(nt.tensor)
+                if nt.init_std == 0:
+                    full = torch.ones((nt.rows, nt.cols), device=self.device, dtype=torch.float32)
+                else:
+                    gshape, idx = self._global_shape_and_slice(name, nt.rows, nt.cols)
+                    g = torch.Generator(device=self.device)
+                    g.manual_seed(planlib.fnv1a(name.encode(), int(self.train.seed) + 1) & 0x7FFFFFFFFFFFFFFF)
+                    glob = torch.randn(gshape, generator=g, device=self.device, dtype=torch.float32) * nt.init_std
+                    r, c = idx
+                    if isinstance(r, torch.Tensor):
+                        full = glob[r.to(self.device)][:, c]
+                    else:
+                        full = glob[r, c]
+                    del glob
+                w.copy_(full.to(torch.bfloat16))
+                # fp32 master copy of the part of this tensor that falls into this rank's optimizer shard
+                lo = nt.flat_off512 * 512
+                hi = lo + nt.rows * nt.cols
+                a, b = max(lo, shard_lo), min(hi, shard_hi)
+                if a < b:
+                    master[a - shard_lo:b - shard_lo].copy_(full.reshape(-1)[a - lo:b - lo])
+        torch.cuda.synchronize(self.device)
+
+    # ------------------------------------------------------------------ stepping
+    def use_graph(self, on=True):
+        klib.check(self.L.cai_exec_use_graph(self.ex, int(on)), "use_graph")
+
+    def load_batch(self, tokens: torch.Tensor, targets: torch.Tensor):
+        """Async host->device copy of one step's inputs (pinned int32 ``[grad_accum, microbatch*seq]``)."""
+        with torch.cuda.stream(self.stream):
+            self.tokens_dev.copy_(tokens.view(self.batch_rows, self.batch_cols), non_blocking=True)
+            self.targets_dev.copy_(targets.view(self.batch_rows, self.batch_cols), non_blocking=True)
+        return tokens.numel() * 4 + targets.numel() * 4
+
+    def run_step(self, lr=None):
+        """Enqueue one optimizer step on the batch already on the device."""
+        self.step_count += 1
+        klib.check(self.L.cai_exec_step(self.ex, self.step_count, float(self.lr if lr is None else lr)), "exec_step")
+
+    def read_loss(self) -> float:
+        """Device->host read of the step's mean loss (synchronises the step)."""
+        with torch.cuda.stream(self.stream):
+            self.loss_host.copy_(self.loss_dev.view(-1)[:8], non_blocking=True)
+        klib.check(self.L.cai_exec_sync(self.ex), "exec_sync")
+        st = klib.device_status(clear=True)
+        if st != 0:
+            raise RuntimeError(f"a kernel gave up on a bounded wait (device status {st})")
+        return float(self.loss_host[0])
+
+    def step(self, tokens, targets, lr=None) -> float:
+        self.load_batch(tokens, targets)
+        self.run_step(lr)
+        return self.read_loss()
+
+    def synchronize(self):
+        klib.check(self.L.cai_exec_sync(self.ex), "exec_sync")
+
+    @property
+    def launches_per_step(self) -> int:
+        return int(self.L.cai_exec_launches(self.ex))
+
+    # ------------------------------------------------------------------ trace
+    def trace_step(self, tokens, targets):
+        """Run one step with per-op CUDA events; returns a list of TraceRec with measured times."""
+        self.L.cai_exec_use_graph(self.ex, 0)
+        self.L.cai_exec_trace_enable(self.ex, 1)
+        self.step(tokens, targets)
+        buf = (TraceRec * len(self.plan.ops))()
+        n = self.L.cai_exec_trace_read(self.ex, buf, len(buf))
+        self.L.cai_exec_trace_enable(self.ex, 0)
+        return [buf[i] for i in range(n)]
+
+    # ------------------------------------------------------------------ metrics
+    def tokens_per_step(self) -> int:
+        return int(self.hdr.global_tokens_per_step)
+
+    def mfu(self, step_time_s: float, peak_flops: float = None) -> float:
+        peak = peak_flops or self.topology.gpu_flops_bf16
+        useful = self.hdr.global_tokens_per_step * self.hdr.flops_per_token_useful / self.hdr.world_size
+        return useful / (peak * step_time_s) if step_time_s > 0 else 0.0
+
+    def close(self):
+        if getattr(self, "ex", None):
+            self.L.cai_exec_destroy(self.ex)
+            self.ex = None
+        if self._tmp is not None:
+            self._tmp.cleanup()
+            self._tmp = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,712 @@
+// exec_plan.cc - the version-2 plan: an executable schedule for one rank.
+//
+// Where the reference's op table only carries costs (src/model.c:441-539), this builder lays out
+// every tensor of the rank in the static arena and emits, in 1F1B order over the six streams, one
+// record per kernel launch with its operands. It also closes the gaps the reference schedule
+// has for real execution: norm / SwiGLU / embedding backward ops exist, dependent pointwise ops run
+// on the stream of their producer instead of racing on compute_lo, and every cross-stream edge
+// has a record/wait pair (verify_hazards proves it).
+//
+// Parallel layout of a dense decoder under tensor parallelism (Megatron with sequence
+// parallelism): the residual stream is sharded by rows ([T/tp, H] per rank); QKV and gate/up are
+// column-parallel (all-gather of the normalised rows feeds the GEMM), the attention output and
+// down projections are row-parallel (GEMM feeds a reduce-scatter that also adds the residual).
+// In comm mode "fused" those pairs are single kernels (OP_AG_GEMM / OP_GEMM_RS); in mode
+// "baseline" they are NCCL collectives next to plain GEMMs.
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstring>
+
+#include "plan.h"
+
+namespace cai {
+
+int fill_plan_header(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph, uint64_t th, uint32_t version,
+                     Topology* topo_out, PlanHeader* h, std::string* err);
+
+namespace {
+
+constexpr uint64_t kTensorAlign = 1024;
+constexpr uint32_t kFlatAlignElems = 512;  // parameters start on multiples of this many elements
+
+int failf(std::string* err, int code, const char* fmt, ...) {
+    if (err) {
+        char buf[256];
+        va_list ap;
+        va_start(ap, fmt);
+        std::vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        *err = buf;
+    }
+    return code;
+}
+
+ExecOp xop(uint16_t kernel, uint16_t flags = 0) {
+    ExecOp x{};
+    x.kernel = kernel;
+    x.flags = flags;
+    for (int& t : x.t) t = -1;
+    return x;
+}
+
+struct Param {
+    int w = -1, g = -1;      // bf16 weight, fp32 gradient
+    uint32_t rows = 0, cols = 0;
+};
+
+struct LayerParams { Param g1, wqkv, wo, g2, wgu, wd; };
+
+// Saved activations of one layer for one in-flight microbatch.
+struct LayerActs { int x, rstd1, xn1, qkv, ao, lse, hmid, rstd2, xn2, gu, act; };
+
+struct Builder {
+    const Config& cfg;
+    const Decomp& d;
+    Plan* p;
+    uint32_t rank, stage, tp_id;
+    bool first_stage, last_stage, fused, tied;
+    uint64_t cursor[TC_COUNT] = {0, 0, 0, 0, 0, 0};
+    uint64_t flat_elems = 0;       // elements in the flat parameter space so far
+    uint32_t next_event = 0;
+    int flat_param = -1, flat_grad = -1, flat_master = -1, flat_m = -1, flat_v = -1;
+
+    // local dimensions
+    uint32_t H, hd, nh_l, nkv_l, Hq_l, Cqkv, F_l, V_l, T, Tl, seq, mbsz, tp, layers;
+
+    Builder(const Config& c, const Decomp& dd, Plan* pl, uint32_t r) : cfg(c), d(dd), p(pl), rank(r) {}
+
+    // ---- tensors
+    int tensor_at(uint16_t tclass, uint16_t dtype, uint64_t offset, uint32_t rows, uint32_t cols, uint32_t ld) {
+        TensorDesc t{};
+        t.offset = offset;
+        t.nbytes = static_cast<uint64_t>(rows) * ld * dtype_size(dtype);
+        t.shape_id = static_cast<uint32_t>(p->tensors.size());
+        t.dtype = dtype;
+        t.tclass = tclass;
+        p->tensors.push_back(t);
+        p->shapes.insert(p->shapes.end(), {rows, cols, ld, 1u});
+        return static_cast<int>(p->tensors.size()) - 1;
+    }
+    int tensor(uint16_t tclass, uint16_t dtype, uint32_t rows, uint32_t cols) {
+        cursor[tclass] = align_up(cursor[tclass], kTensorAlign);
+        const int id = tensor_at(tclass, dtype, cursor[tclass], rows, cols, cols);
+        cursor[tclass] += p->tensors[id].nbytes;
+        return id;
+    }
+    // rows [row0, row0+rows) of an existing tensor
+    int view(int parent, uint32_t row0, uint32_t rows) {
+        const TensorDesc& pt = p->tensors[parent];
+        const uint32_t cols = p->shapes[parent * 4 + 1], ld = p->shapes[parent * 4 + 2];
+        return tensor_at(pt.tclass, pt.dtype, pt.offset + static_cast<uint64_t>(row0) * ld * dtype_size(pt.dtype), rows,
+                         cols, ld);
+    }
+    uint32_t rows_of(int t) const { return p->shapes[t * 4]; }
+    uint32_t cols_of(int t) const { return p->shapes[t * 4 + 1]; }
+
+    // A parameter occupies the same element range in the bf16 weight, fp32 gradient, master,
+    // m and v buffers, so a single AdamW launch covers the whole flat space.
+    Param param(const char* name, uint32_t rows, uint32_t cols, float init_std) {
+        flat_elems = align_up(flat_elems, kFlatAlignElems);
+        Param q;
+        q.rows = rows;
+        q.cols = cols;
+        q.w = tensor_at(TC_PARAM, DT_BF16, flat_elems * 2, rows, cols, cols);
+        q.g = tensor_at(TC_GRAD, DT_FP32, flat_elems * 4, rows, cols, cols);
+        NamedTensor nt{};
+        std::snprintf(nt.name, sizeof nt.name, "%s", name);
+        nt.tensor = q.w;
+        nt.grad = q.g;
+        nt.master = static_cast<int32_t>(flat_elems >> 9);  // flat offset in units of kFlatAlignElems
+        nt.rows = rows;
+        nt.cols = cols;
+        nt.init_std = init_std;
+        p->named.push_back(nt);
+        flat_elems += static_cast<uint64_t>(rows) * cols;
+        return q;
+    }
+
+    // ---- ops
+    void push(uint16_t kind, uint16_t stream, double flops, double bytes, uint32_t aux0, uint16_t mb, const ExecOp* x) {
+        Op o{};
+        o.kind = kind;
+        o.stream_id = stream;
+        o.flops = static_cast<uint64_t>(flops < 0 ? 0 : flops);
+        o.bytes = static_cast<uint64_t>(bytes < 0 ? 0 : bytes);
+        o.aux0 = aux0;
+        o.aux1 = mb;
+        if (x) {
+            p->exec.push_back(*x);
+            o.exec = static_cast<uint32_t>(p->exec.size());
+        }
+        p->ops.push_back(o);
+    }
+    uint32_t record(uint16_t stream, uint16_t mb) {
+        push(OP_EVENT_RECORD, stream, 0, 0, next_event, mb, nullptr);
+        return next_event++;
+    }
+    void wait(uint16_t stream, uint32_t ev, uint16_t mb) { push(OP_EVENT_WAIT, stream, 0, 0, ev, mb, nullptr); }
+    void sync(uint16_t from, uint16_t to, uint16_t mb) {
+        if (from == to) return;
+        wait(to, record(from, mb), mb);
+    }
+
+    // C[M,N] = A * B^T style product; trans flags as in the kernel library.
+    void gemm(uint16_t stream, int A, int B, int C, int R, uint32_t M, uint32_t N, uint32_t K, bool ta, bool tb, int epi,
+              uint16_t mb) {
+        ExecOp x = xop(K_GEMM, static_cast<uint16_t>((ta ? 1 : 0) | (tb ? 2 : 0) | (epi << 4)));
+        x.t[0] = A; x.t[1] = B; x.t[2] = C; x.t[3] = R;
+        x.i[0] = M; x.i[1] = N; x.i[2] = K;
+        x.f[0] = 1.0f;
+        push(OP_GEMM, stream, 2.0 * M * N * K, 0, 0, mb, &x);
+    }
+    void rmsnorm_fwd(int x, int g, int y, int rstd, uint32_t rows, uint16_t mb) {
+        ExecOp e = xop(K_RMSNORM_FWD);
+        e.t[0] = x; e.t[1] = g; e.t[2] = y; e.t[3] = rstd;
+        e.i[0] = rows; e.i[1] = H;
+        e.f[0] = cfg.train.norm_eps;
+        push(OP_RMSNORM, ST_COMPUTE_HI, 5.0 * rows * H, 0, 0, mb, &e);
+    }
+    void rmsnorm_bwd(int x, int g, int rstd, int dy, int dx, int dg, int scratch, uint32_t rows, bool dx_acc, bool dg_acc,
+                     uint16_t mb) {
+        ExecOp e = xop(K_RMSNORM_BWD);
+        e.t[0] = x; e.t[1] = g; e.t[2] = rstd; e.t[3] = dy; e.t[4] = dx; e.t[5] = dg; e.t[6] = scratch;
+        e.i[0] = rows; e.i[1] = H; e.i[2] = dx_acc; e.i[3] = dg_acc;
+        push(OP_RMSNORM, ST_COMPUTE_HI, 10.0 * rows * H, 0, 0, mb, &e);
+    }
+    void nccl(uint16_t kernel, uint16_t opkind, uint16_t stream, int src, int dst, uint64_t count, uint16_t dtype,
+              uint16_t group, int peer, uint16_t mb) {
+        ExecOp e = xop(kernel);
+        e.t[0] = src; e.t[1] = dst;
+        e.i[0] = static_cast<int32_t>(count & 0xFFFFFFFFu);
+        e.i[1] = static_cast<int32_t>(count >> 32);
+        e.i[2] = dtype; e.i[3] = group; e.i[4] = peer;
+        push(opkind, stream, 0, static_cast<double>(count) * dtype_size(dtype), group, mb, &e);
+    }
+
+    // y[T, N] = gather_rows(x_local[Tl, K]) * W[N, K]^T  (column-parallel linear, forward), or
+    // with tb: y[T, N] = gather_rows(x_local) * W[K, N] (input gradient of a row-parallel linear).
+    // x_full receives the gathered rows (kept for the weight gradient).
+    void col_parallel(int x_local, int x_full, int W, int y, uint32_t N, uint32_t K, bool tb, uint16_t mb) {
+        if (tp == 1) {
+            gemm(ST_COMPUTE_HI, x_local, W, y, -1, T, N, K, false, tb, 0, mb);
+            return;
+        }
+        if (fused) {
+            ExecOp e = xop(K_AG_GEMM, static_cast<uint16_t>(tb ? 2 : 0));
+            e.t[0] = x_local; e.t[1] = W; e.t[2] = y; e.t[3] = x_full;
+            e.i[0] = T; e.i[1] = N; e.i[2] = K; e.i[3] = GROUP_TP;
+            e.f[0] = 1.0f;
+            push(OP_AG_GEMM, ST_COMPUTE_HI, 2.0 * T * N * K, static_cast<double>(T) * K * 2, GROUP_TP, mb, &e);
+            return;
+        }
+        sync(ST_COMPUTE_HI, ST_COMM_TP, mb);
+        nccl(K_NCCL_ALL_GATHER, OP_ALL_GATHER, ST_COMM_TP, x_local, x_full, static_cast<uint64_t>(Tl) * K, DT_BF16,
+             GROUP_TP, -1, mb);
+        sync(ST_COMM_TP, ST_COMPUTE_HI, mb);
+        gemm(ST_COMPUTE_HI, x_full, W, y, -1, T, N, K, false, tb, 0, mb);
+    }
+    // out_local[Tl, N] = residual + reduce_scatter_rows(a[T, K] * W[N, K]^T) (row-parallel linear,
+    // forward), or with tb the input gradient of a column-parallel linear (residual may be -1).
+    void row_parallel(int a, int W, int residual, int out_local, int partial, int rs_tmp, uint32_t N, uint32_t K, bool tb,
+                      uint16_t mb) {
+        if (tp == 1) {
+            gemm(ST_COMPUTE_HI, a, W, out_local, residual, T, N, K, false, tb, residual >= 0 ? 3 : 0, mb);
+            return;
+        }
+        if (fused) {
+            ExecOp e = xop(K_GEMM_RS, static_cast<uint16_t>(tb ? 2 : 0));
+            e.t[0] = a; e.t[1] = W; e.t[2] = out_local; e.t[3] = residual; e.t[4] = partial;
+            e.i[0] = T; e.i[1] = N; e.i[2] = K; e.i[3] = GROUP_TP;
+            e.f[0] = 1.0f;
+            push(OP_GEMM_RS, ST_COMPUTE_HI, 2.0 * T * N * K, static_cast<double>(T) * N * 2, GROUP_TP, mb, &e);
+            return;
+        }
+        gemm(ST_COMPUTE_HI, a, W, partial, -1, T, N, K, false, tb, 0, mb);
+        sync(ST_COMPUTE_HI, ST_COMM_TP, mb);
+        nccl(K_NCCL_REDUCE_SCATTER, OP_REDUCE_SCATTER, ST_COMM_TP, partial, residual >= 0 ? rs_tmp : out_local,
+             static_cast<uint64_t>(Tl) * N, DT_BF16, GROUP_TP, -1, mb);
+        sync(ST_COMM_TP, ST_COMPUTE_HI, mb);
+        if (residual >= 0) {
+            ExecOp e = xop(K_ADD);
+            e.t[0] = residual; e.t[1] = rs_tmp; e.t[2] = out_local;
+            e.i[0] = static_cast<int32_t>(static_cast<uint64_t>(Tl) * N);
+            push(OP_ELEMENTWISE, ST_COMPUTE_HI, static_cast<double>(Tl) * N, 0, 0, mb, &e);
+        }
+    }
+};
+
+}  // namespace
+
+void exec_operands(const ExecOp& x, std::vector<int>* reads, std::vector<int>* writes) {
+    reads->clear();
+    writes->clear();
+    auto R = [&](int i) { if (x.t[i] >= 0) reads->push_back(x.t[i]); };
+    auto W = [&](int i) { if (x.t[i] >= 0) writes->push_back(x.t[i]); };
+    switch (x.kernel) {
+        case K_EMBED_FWD: R(0); R(1); W(2); break;
+        case K_EMBED_BWD: R(0); R(1); R(2); W(2); break;
+        case K_RMSNORM_FWD: R(0); R(1); W(2); W(3); break;
+        case K_RMSNORM_BWD: R(0); R(1); R(2); R(3); if (x.i[2]) R(4); W(4); if (x.i[3]) R(5); W(5); W(6); break;
+        case K_GEMM: {
+            const int epi = x.flags >> 4;
+            R(0); R(1); if (epi == 2) R(2); R(3); W(2);
+            break;
+        }
+        case K_ROPE: R(0); R(1); W(0); break;
+        case K_ATTN_FWD: R(0); W(1); W(2); break;
+        case K_ATTN_BWD: R(0); R(1); R(2); R(3); W(4); W(5); break;
+        case K_SWIGLU_FWD: R(0); W(1); break;
+        case K_SWIGLU_BWD: R(0); R(1); W(2); break;
+        case K_CROSS_ENTROPY: R(0); R(1); R(2); W(0); W(2); break;
+        case K_ADAMW: R(0); R(1); R(2); R(3); W(0); W(1); W(2); W(4); break;
+        case K_ZERO: W(0); break;
+        case K_ADD: R(0); R(1); W(2); break;
+        case K_NCCL_ALL_REDUCE: R(0); W(1); break;
+        case K_NCCL_REDUCE_SCATTER: case K_NCCL_ALL_GATHER: case K_NCCL_ALL_TO_ALL: R(0); W(1); break;
+        case K_NCCL_SEND: R(0); break;
+        case K_NCCL_RECV: W(1); break;
+        case K_AG_GEMM: R(0); R(1); W(2); W(3); break;
+        case K_GEMM_RS: R(0); R(1); R(3); W(2); W(4); break;
+        case K_RS_ADAMW: R(0); R(1); R(2); R(3); W(0); W(1); W(2); W(4); break;
+        default:
+            for (int i = 0; i < 8; ++i) { R(i); }
+            break;
+    }
+}
+
+int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph, uint64_t th, Plan* out,
+                  std::string* err) {
+    const ModelSpec& m = cfg.model;
+    *out = Plan{};
+    Topology topo;
+    if (int rc = fill_plan_header(cfg, d, rank, ph, th, 2, &topo, &out->hdr, err); rc != OK) return rc;
+    PlanHeader& h = out->hdr;
+    out->groups = rank_groups(d, topo, m.is_moe != 0, rank);
+    out->train = cfg.train;
+    out->model = m;
+
+    if (m.is_moe) return failf(err, ERR_INVALID, "executable plans for MoE models are built by the MoE planner");
+    if (d.cp != 1) return failf(err, ERR_INVALID, "context parallelism (cp>1) has no executable schedule");
+    if (m.head_dim != 128) return failf(err, ERR_INVALID, "executable plans need head_dim = 128 (got %u)", m.head_dim);
+    if (m.num_heads % d.tp || m.num_kv_heads % d.tp || m.ffn_hidden % d.tp || m.vocab_size % d.tp)
+        return failf(err, ERR_INVALID, "tp=%u must divide heads, kv heads, ffn and vocab", d.tp);
+    if ((m.microbatch * m.seq_len) % d.tp || m.seq_len % 128)
+        return failf(err, ERR_INVALID, "tokens per microbatch must divide by tp and seq_len by 128");
+    if ((m.vocab_size / d.tp) % 8 || m.hidden_size % 8 || (m.ffn_hidden / d.tp) % 8)
+        return failf(err, ERR_INVALID, "local hidden / ffn / vocab sizes must be multiples of 8");
+
+    Builder b(cfg, d, out, rank);
+    b.stage = h.pipeline_stage;
+    b.tp_id = rank % d.tp;
+    b.first_stage = b.stage == 0;
+    b.last_stage = b.stage == d.pp - 1;
+    b.fused = cfg.train.comm_mode != 0;
+    b.tied = cfg.train.tie_embeddings && d.pp == 1;
+    b.tp = d.tp;
+    b.H = m.hidden_size; b.hd = m.head_dim;
+    b.nh_l = m.num_heads / d.tp; b.nkv_l = m.num_kv_heads / d.tp;
+    b.Hq_l = b.nh_l * b.hd;
+    b.Cqkv = (b.nh_l + 2 * b.nkv_l) * b.hd;
+    b.F_l = m.ffn_hidden / d.tp;
+    b.V_l = m.vocab_size / d.tp;
+    b.seq = m.seq_len; b.mbsz = m.microbatch;
+    b.T = m.microbatch * m.seq_len;
+    b.Tl = b.T / d.tp;
+    b.layers = h.layers_in_stage;
+    const uint32_t H = b.H, T = b.T, Tl = b.Tl, tp = b.tp, ga = d.num_microbatches;
+    const float istd = cfg.train.init_std;
+
+    // ---------------- parameters (flat space)
+    Param embed, head, gf;
+    if (b.first_stage || (b.last_stage && b.tied)) embed = b.param("embed", b.V_l, H, istd);
+    std::vector<LayerParams> L(b.layers);
+    const uint32_t base_layer = [&] {
+        uint32_t base = m.num_layers / d.pp, rem = m.num_layers % d.pp, s = b.stage;
+        return s * base + std::min(s, rem);
+    }();
+    for (uint32_t l = 0; l < b.layers; ++l) {
+        char nm[40];
+        auto name = [&](const char* suffix) {
+            std::snprintf(nm, sizeof nm, "L%u.%s", base_layer + l, suffix);
+            return nm;
+        };
+        L[l].g1 = b.param(name("g1"), 1, H, 0.f);
+        L[l].wqkv = b.param(name("wqkv"), b.Cqkv, H, istd);
+        L[l].wo = b.param(name("wo"), H, b.Hq_l, istd);
+        L[l].g2 = b.param(name("g2"), 1, H, 0.f);
+        L[l].wgu = b.param(name("wgu"), 2 * b.F_l, H, istd);
+        L[l].wd = b.param(name("wd"), H, b.F_l, istd);
+    }
+    if (b.last_stage) {
+        gf = b.param("gf", 1, H, 0.f);
+        if (!b.tied) head = b.param("lm_head", b.V_l, H, istd);
+        else head = embed;
+    }
+    const uint64_t n_flat = align_up(b.flat_elems, kFlatAlignElems);
+    if (n_flat > 0x7FFFFFFFFFFFull) return failf(err, ERR_INVALID, "parameter space too large");
+    b.flat_param = b.tensor_at(TC_PARAM, DT_BF16, 0, 1, static_cast<uint32_t>(std::min<uint64_t>(n_flat, 0xFFFFFFFFu)), 0);
+    b.flat_grad = b.tensor_at(TC_GRAD, DT_FP32, 0, 1, static_cast<uint32_t>(std::min<uint64_t>(n_flat, 0xFFFFFFFFu)), 0);
+    out->tensors[b.flat_param].nbytes = n_flat * 2;
+    out->tensors[b.flat_grad].nbytes = n_flat * 4;
+    b.cursor[TC_PARAM] = n_flat * 2;
+    b.cursor[TC_GRAD] = n_flat * 4;
+    // optimizer state: master | m | v, each n_flat fp32 (sharded 1/dp when the optimizer is sharded)
+    const uint64_t n_opt = d.dp > 1 ? align_up((n_flat + d.dp - 1) / d.dp, kFlatAlignElems) : n_flat;
+    b.flat_master = b.tensor_at(TC_OPTSTATE, DT_FP32, 0, 1, 0, 0);
+    b.flat_m = b.tensor_at(TC_OPTSTATE, DT_FP32, n_opt * 4, 1, 0, 0);
+    b.flat_v = b.tensor_at(TC_OPTSTATE, DT_FP32, n_opt * 8, 1, 0, 0);
+    for (int t : {b.flat_master, b.flat_m, b.flat_v}) out->tensors[t].nbytes = n_opt * 4;
+    b.cursor[TC_OPTSTATE] = n_opt * 12;
+    out->xhdr.param_elems = n_flat;
+    out->xhdr.reserved = n_opt;
+
+    // ---------------- inputs, workspace
+    const int tokens = b.tensor(TC_COMM, DT_INT32, ga, T);
+    const int targets = b.tensor(TC_COMM, DT_INT32, ga, T);
+    const int loss_acc = b.tensor(TC_WORKSPACE, DT_FP32, 1, 8);
+    const int rope_tab = b.tensor(TC_WORKSPACE, DT_FP32, b.seq, b.hd);  // [seq, hd/2] float2
+    const uint32_t norm_parts = std::min<uint32_t>(std::max(Tl, 1u), 4 * 160);
+    const int norm_scratch = b.tensor(TC_WORKSPACE, DT_FP32, norm_parts, H);
+    const int dstream = b.tensor(TC_WORKSPACE, DT_BF16, Tl, H);     // gradient of the residual stream
+    const int dxn = b.tensor(TC_WORKSPACE, DT_BF16, Tl, H);         // gradient of a norm output (local rows)
+    const int dfull = tp > 1 ? b.tensor(TC_WORKSPACE, DT_BF16, T, H) : -1;  // gathered gradient rows
+    const int dqkv = b.tensor(TC_WORKSPACE, DT_BF16, T, b.Cqkv);
+    const int dao = b.tensor(TC_WORKSPACE, DT_BF16, T, b.Hq_l);
+    const int dgu = b.tensor(TC_WORKSPACE, DT_BF16, T, 2 * b.F_l);
+    const int dact = b.tensor(TC_WORKSPACE, DT_BF16, T, b.F_l);
+    const int delta = b.tensor(TC_WORKSPACE, DT_FP32, b.nh_l, T);
+    const int partial = tp > 1 ? b.tensor(TC_COMM, DT_BF16, T, H) : -1;     // row-parallel partial sums / staging
+    const int rs_tmp = tp > 1 ? b.tensor(TC_WORKSPACE, DT_BF16, Tl, H) : -1;
+    const int xn_local = tp > 1 ? b.tensor(TC_COMM, DT_BF16, Tl, H) : -1;   // norm output peers gather from
+    const uint32_t chunk = std::min<uint32_t>(cfg.train.ce_chunk ? cfg.train.ce_chunk : 1024, T);
+    int logits = -1, hf = -1, hf_full = -1, rstdf = -1, xf = -1, dhf_full = -1;
+    if (b.last_stage) logits = b.tensor(TC_WORKSPACE, DT_BF16, chunk, b.V_l);
+    if (b.last_stage && tp > 1) dhf_full = dfull;
+
+    // ---------------- activations: one set per in-flight microbatch
+    const uint32_t slots = std::max<uint32_t>(1, std::min<uint32_t>(d.pp - b.stage, ga));
+    out->xhdr.act_slots = slots;
+    std::vector<std::vector<LayerActs>> A(slots, std::vector<LayerActs>(b.layers));
+    std::vector<int> x_out(slots), hf_s(slots), hff_s(slots), rstdf_s(slots);
+    for (uint32_t s = 0; s < slots; ++s) {
+        for (uint32_t l = 0; l < b.layers; ++l) {
+            LayerActs& a = A[s][l];
+            a.x = b.tensor(TC_ACTIVATION, DT_BF16, Tl, H);
+            a.rstd1 = b.tensor(TC_ACTIVATION, DT_FP32, 1, Tl);
+            a.xn1 = b.tensor(TC_ACTIVATION, DT_BF16, T, H);       // gathered rows (== local when tp = 1)
+            a.qkv = b.tensor(TC_ACTIVATION, DT_BF16, T, b.Cqkv);
+            a.ao = b.tensor(TC_ACTIVATION, DT_BF16, T, b.Hq_l);
+            a.lse = b.tensor(TC_ACTIVATION, DT_FP32, b.nh_l, T);
+            a.hmid = b.tensor(TC_ACTIVATION, DT_BF16, Tl, H);
+            a.rstd2 = b.tensor(TC_ACTIVATION, DT_FP32, 1, Tl);
+            a.xn2 = b.tensor(TC_ACTIVATION, DT_BF16, T, H);
+            a.gu = b.tensor(TC_ACTIVATION, DT_BF16, T, 2 * b.F_l);
+            a.act = b.tensor(TC_ACTIVATION, DT_BF16, T, b.F_l);
+        }
+        x_out[s] = b.tensor(TC_ACTIVATION, DT_BF16, Tl, H);       // output of the stage's last layer
+        if (b.last_stage) {
+            rstdf_s[s] = b.tensor(TC_ACTIVATION, DT_FP32, 1, Tl);
+            hf_s[s] = tp > 1 ? b.tensor(TC_ACTIVATION, DT_BF16, Tl, H) : -1;
+            hff_s[s] = b.tensor(TC_ACTIVATION, DT_BF16, T, H);    // normalised final hidden, all rows
+        }
+    }
+    (void)hf; (void)hf_full; (void)rstdf; (void)xf;
+
+    // pipeline hand-off buffers
+    const int pipe_in = !b.first_stage ? b.tensor(TC_COMM, DT_BF16, Tl, H) : -1;
+    const int pipe_gin = !b.last_stage ? b.tensor(TC_COMM, DT_BF16, Tl, H) : -1;
+    const uint32_t pp_prev = b.stage > 0 ? b.stage - 1 : 0, pp_next = b.stage + 1;
+
+    const double grad_scale = 1.0 / (static_cast<double>(T) * ga);
+    std::vector<int> send_done(slots, -1);  // event recorded after a slot's activation send
+
+    // ================================================================ forward of one microbatch
+    auto forward = [&](uint16_t mb) {
+        const uint32_t s = mb % slots;
+        const int tok_mb = b.view(tokens, mb, 1);
+        int x = A[s].empty() ? x_out[s] : A[s][0].x;
+        if (b.first_stage) {
+            if (tp == 1) {
+                ExecOp e = xop(K_EMBED_FWD);
+                e.t[0] = tok_mb; e.t[1] = embed.w; e.t[2] = x;
+                e.i[0] = T; e.i[1] = H; e.i[2] = 0; e.i[3] = b.V_l;
+                b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 0, 2.0 * T * H, 0, mb, &e);
+            } else {
+                // vocabulary-parallel gather: every rank fills the rows whose token it owns, the
+                // reduce-scatter sums the slices and leaves each rank its rows of the sequence
+                ExecOp e = xop(K_EMBED_FWD);
+                e.t[0] = tok_mb; e.t[1] = embed.w; e.t[2] = partial;
+                e.i[0] = T; e.i[1] = H; e.i[2] = b.tp_id * b.V_l; e.i[3] = (b.tp_id + 1) * b.V_l;
+                b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 0, 2.0 * T * H, 0, mb, &e);
+                b.sync(ST_COMPUTE_HI, ST_COMM_TP, mb);
+                b.nccl(K_NCCL_REDUCE_SCATTER, OP_REDUCE_SCATTER, ST_COMM_TP, partial, x, static_cast<uint64_t>(Tl) * H,
+                       DT_BF16, GROUP_TP, -1, mb);
+                b.sync(ST_COMM_TP, ST_COMPUTE_HI, mb);
+            }
+        } else {
+            // the slot's previous microbatch must be done with this buffer before it is refilled
+            b.sync(ST_COMPUTE_HI, ST_COMM_PP, mb);
+            b.nccl(K_NCCL_RECV, OP_PIPE_RECV, ST_COMM_PP, -1, x, static_cast<uint64_t>(Tl) * H, DT_BF16, GROUP_PP,
+                   static_cast<int>(pp_prev), mb);
+            b.sync(ST_COMM_PP, ST_COMPUTE_HI, mb);
+        }
+        if (send_done[s] >= 0) {
+            // the activation this slot handed to the next stage must have left before it is rewritten
+            b.wait(ST_COMPUTE_HI, static_cast<uint32_t>(send_done[s]), mb);
+            send_done[s] = -1;
+        }
+        for (uint32_t l = 0; l < b.layers; ++l) {
+            const LayerActs& a = A[s][l];
+            const LayerParams& w = L[l];
+            const int x_next = l + 1 < b.layers ? A[s][l + 1].x : x_out[s];
+            // attention block
+            b.rmsnorm_fwd(a.x, w.g1.w, tp > 1 ? xn_local : a.xn1, a.rstd1, Tl, mb);
+            b.col_parallel(tp > 1 ? xn_local : a.xn1, a.xn1, w.wqkv.w, a.qkv, b.Cqkv, H, false, mb);
+            {
+                ExecOp e = xop(K_ROPE);
+                e.t[0] = a.qkv; e.t[1] = rope_tab;
+                e.i[0] = T; e.i[1] = b.seq; e.i[2] = b.nh_l; e.i[3] = b.nkv_l; e.i[4] = b.hd;
+                b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 6.0 * T * (b.nh_l + b.nkv_l) * b.hd, 0, 0, mb, &e);
+            }
+            {
+                ExecOp e = xop(K_ATTN_FWD);
+                e.t[0] = a.qkv; e.t[1] = a.ao; e.t[2] = a.lse;
+                e.i[0] = b.mbsz; e.i[1] = b.seq; e.i[2] = b.nh_l; e.i[3] = b.nkv_l; e.i[4] = b.hd;
+                e.f[0] = 1.0f / std::sqrt(static_cast<float>(b.hd));
+                b.push(OP_ATTENTION_FWD, ST_COMPUTE_HI, 2.0 * T * b.Hq_l * b.seq, 0, 0, mb, &e);
+            }
+            b.row_parallel(a.ao, w.wo.w, a.x, a.hmid, partial, rs_tmp, H, b.Hq_l, false, mb);
+            // MLP block
+            b.rmsnorm_fwd(a.hmid, w.g2.w, tp > 1 ? xn_local : a.xn2, a.rstd2, Tl, mb);
+            b.col_parallel(tp > 1 ? xn_local : a.xn2, a.xn2, w.wgu.w, a.gu, 2 * b.F_l, H, false, mb);
+            {
+                ExecOp e = xop(K_SWIGLU_FWD);
+                e.t[0] = a.gu; e.t[1] = a.act;
+                e.i[0] = T; e.i[1] = b.F_l;
+                b.push(OP_SWIGLU, ST_COMPUTE_HI, 4.0 * T * b.F_l, 0, 0, mb, &e);
+            }
+            b.row_parallel(a.act, w.wd.w, a.hmid, x_next, partial, rs_tmp, H, b.F_l, false, mb);
+        }
+        if (!b.last_stage) {
+            b.sync(ST_COMPUTE_HI, ST_COMM_PP, mb);
+            b.nccl(K_NCCL_SEND, OP_PIPE_SEND, ST_COMM_PP, x_out[s], -1, static_cast<uint64_t>(Tl) * H, DT_BF16, GROUP_PP,
+                   static_cast<int>(pp_next), mb);
+            send_done[s] = static_cast<int>(b.record(ST_COMM_PP, mb));
+        } else {
+            // final norm; the loss itself is computed chunk by chunk at the start of backward so
+            // that the logits never exist for more than `chunk` rows
+            b.rmsnorm_fwd(x_out[s], gf.w, tp > 1 ? hf_s[s] : hff_s[s], rstdf_s[s], Tl, mb);
+            if (tp > 1) {
+                b.sync(ST_COMPUTE_HI, ST_COMM_TP, mb);
+                b.nccl(K_NCCL_ALL_GATHER, OP_ALL_GATHER, ST_COMM_TP, hf_s[s], hff_s[s], static_cast<uint64_t>(Tl) * H,
+                       DT_BF16, GROUP_TP, -1, mb);
+                b.sync(ST_COMM_TP, ST_COMPUTE_HI, mb);
+            }
+        }
+    };
+
+    // ================================================================ backward of one microbatch
+    auto backward = [&](uint16_t mb) {
+        const uint32_t s = mb % slots;
+        const bool first_mb = mb == 0;                 // first gradient contribution overwrites
+        const int wg_epi = first_mb ? 1 : 2;           // CAI_EPI_F32 / CAI_EPI_F32_ACCUM
+        const int tok_mb = b.view(tokens, mb, 1);
+        if (b.last_stage) {
+            // LM head + cross-entropy, `chunk` rows at a time: logits -> dlogits in place ->
+            // d(hidden) rows and the head's weight gradient.
+            const int dh_rows = tp > 1 ? dhf_full : dstream;   // gradient wrt the normalised hidden, all T rows
+            for (uint32_t r0 = 0; r0 < T; r0 += chunk) {
+                const uint32_t rows = std::min(chunk, T - r0);
+                const int hf_c = b.view(hff_s[s], r0, rows);
+                const int lg = rows == chunk ? logits : b.view(logits, 0, rows);
+                b.gemm(ST_COMPUTE_HI, hf_c, head.w, lg, -1, rows, b.V_l, H, false, false, 0, mb);
+                ExecOp e = xop(tp > 1 ? K_CROSS_ENTROPY_TP : K_CROSS_ENTROPY);
+                const int tg = b.tensor_at(TC_COMM, DT_INT32,
+                                           out->tensors[targets].offset + (static_cast<uint64_t>(mb) * T + r0) * 4, 1,
+                                           rows, rows);
+                e.t[0] = lg; e.t[1] = tg; e.t[2] = loss_acc;
+                e.i[0] = rows; e.i[1] = b.V_l; e.i[2] = b.tp_id * b.V_l; e.i[3] = GROUP_TP;
+                e.f[0] = static_cast<float>(grad_scale);
+                e.f[1] = static_cast<float>(grad_scale);
+                b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 5.0 * rows * b.V_l, 0, 0, mb, &e);
+                const int dh_c = b.view(dh_rows, r0, rows);
+                b.gemm(ST_COMPUTE_HI, lg, head.w, dh_c, -1, rows, H, b.V_l, false, true, 0, mb);
+                b.gemm(ST_COMPUTE_HI, lg, hf_c, head.g, -1, b.V_l, H, rows, true, true,
+                       (first_mb && r0 == 0) ? 1 : 2, mb);
+            }
+            if (tp > 1) {
+                // partial sums over vocabulary shards -> rows of this rank
+                b.sync(ST_COMPUTE_HI, ST_COMM_TP, mb);
+                b.nccl(K_NCCL_REDUCE_SCATTER, OP_REDUCE_SCATTER, ST_COMM_TP, dhf_full, dxn, static_cast<uint64_t>(Tl) * H,
+                       DT_BF16, GROUP_TP, -1, mb);
+                b.sync(ST_COMM_TP, ST_COMPUTE_HI, mb);
+            }
+            b.rmsnorm_bwd(x_out[s], gf.w, rstdf_s[s], tp > 1 ? dxn : dstream, dstream, gf.g, norm_scratch, Tl, false,
+                          !first_mb, mb);
+        } else {
+            // Gradients travel up the pipeline on their own stream (and communicator): with a
+            // single in-order p2p stream per rank, the warm-up sends of one stage and the first
+            // gradient send of the next would wait for each other.
+            b.sync(ST_COMPUTE_HI, ST_IO, mb);
+            b.nccl(K_NCCL_RECV, OP_PIPE_RECV, ST_IO, -1, dstream, static_cast<uint64_t>(Tl) * H, DT_BF16, GROUP_PP,
+                   static_cast<int>(pp_next), mb);
+            b.sync(ST_IO, ST_COMPUTE_HI, mb);
+        }
+        for (int l = static_cast<int>(b.layers) - 1; l >= 0; --l) {
+            const LayerActs& a = A[s][l];
+            const LayerParams& w = L[l];
+            const int g_rows = tp > 1 ? dfull : dstream;  // all T rows of the incoming gradient
+            // ---- MLP block: x_next = hmid + act * Wd^T
+            b.col_parallel(dstream, dfull, w.wd.w, dact, b.F_l, H, true, mb);                     // dact = gather(dx) * Wd
+            b.gemm(ST_COMPUTE_HI, g_rows, a.act, w.wd.g, -1, H, b.F_l, T, true, true, wg_epi, mb);  // dWd = dx^T act
+            {
+                ExecOp e = xop(K_SWIGLU_BWD);
+                e.t[0] = a.gu; e.t[1] = dact; e.t[2] = dgu;
+                e.i[0] = T; e.i[1] = b.F_l;
+                b.push(OP_SWIGLU, ST_COMPUTE_HI, 8.0 * T * b.F_l, 0, 0, mb, &e);
+            }
+            b.row_parallel(dgu, w.wgu.w, -1, dxn, partial, rs_tmp, H, 2 * b.F_l, true, mb);        // dxn2 = RS(dgu * Wgu)
+            b.gemm(ST_COMPUTE_HI, dgu, a.xn2, w.wgu.g, -1, 2 * b.F_l, H, T, true, true, wg_epi, mb);
+            b.rmsnorm_bwd(a.hmid, w.g2.w, a.rstd2, dxn, dstream, w.g2.g, norm_scratch, Tl, true, !first_mb, mb);
+            // ---- attention block: hmid = x + ao * Wo^T
+            b.col_parallel(dstream, dfull, w.wo.w, dao, b.Hq_l, H, true, mb);                     // dao = gather(dh) * Wo
+            b.gemm(ST_COMPUTE_HI, g_rows, a.ao, w.wo.g, -1, H, b.Hq_l, T, true, true, wg_epi, mb);
+            {
+                ExecOp e = xop(K_ATTN_BWD);
+                e.t[0] = a.qkv; e.t[1] = a.ao; e.t[2] = dao; e.t[3] = a.lse; e.t[4] = delta; e.t[5] = dqkv;
+                e.i[0] = b.mbsz; e.i[1] = b.seq; e.i[2] = b.nh_l; e.i[3] = b.nkv_l; e.i[4] = b.hd;
+                e.f[0] = 1.0f / std::sqrt(static_cast<float>(b.hd));
+                b.push(OP_ATTENTION_BWD, ST_COMPUTE_HI, 4.0 * T * b.Hq_l * b.seq, 0, 0, mb, &e);
+            }
+            {
+                ExecOp e = xop(K_ROPE, 1);
+                e.t[0] = dqkv; e.t[1] = rope_tab;
+                e.i[0] = T; e.i[1] = b.seq; e.i[2] = b.nh_l; e.i[3] = b.nkv_l; e.i[4] = b.hd;
+                b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 6.0 * T * (b.nh_l + b.nkv_l) * b.hd, 0, 0, mb, &e);
+            }
+            b.row_parallel(dqkv, w.wqkv.w, -1, dxn, partial, rs_tmp, H, b.Cqkv, true, mb);
+            b.gemm(ST_COMPUTE_HI, dqkv, a.xn1, w.wqkv.g, -1, b.Cqkv, H, T, true, true, wg_epi, mb);
+            b.rmsnorm_bwd(a.x, w.g1.w, a.rstd1, dxn, dstream, w.g1.g, norm_scratch, Tl, true, !first_mb, mb);
+        }
+        if (b.first_stage) {
+            int drows = dstream;
+            if (tp > 1) {
+                b.sync(ST_COMPUTE_HI, ST_COMM_TP, mb);
+                b.nccl(K_NCCL_ALL_GATHER, OP_ALL_GATHER, ST_COMM_TP, dstream, dfull, static_cast<uint64_t>(Tl) * H, DT_BF16,
+                       GROUP_TP, -1, mb);
+                b.sync(ST_COMM_TP, ST_COMPUTE_HI, mb);
+                drows = dfull;
+            }
+            if (first_mb && !(b.last_stage && b.tied)) {
+                ExecOp z = xop(K_ZERO);
+                z.t[0] = embed.g;
+                b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 0, 4.0 * b.V_l * H, 0, mb, &z);
+            }
+            ExecOp e = xop(K_EMBED_BWD);
+            e.t[0] = tok_mb; e.t[1] = drows; e.t[2] = embed.g;
+            e.i[0] = T; e.i[1] = H; e.i[2] = b.tp_id * b.V_l; e.i[3] = (b.tp_id + 1) * b.V_l;
+            b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 0, 6.0 * T * H, 0, mb, &e);
+        } else {
+            b.sync(ST_COMPUTE_HI, ST_IO, mb);
+            b.nccl(K_NCCL_SEND, OP_PIPE_SEND, ST_IO, dstream, -1, static_cast<uint64_t>(Tl) * H, DT_BF16, GROUP_PP,
+                   static_cast<int>(pp_prev), mb);
+            // dstream is overwritten by the next backward: the send must finish first
+            b.sync(ST_IO, ST_COMPUTE_HI, mb);
+        }
+    };
+    (void)pipe_in; (void)pipe_gin;
+
+    // ================================================================ the step
+    {
+        ExecOp z = xop(K_ZERO);
+        z.t[0] = loss_acc;
+        b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 0, 32, 0, 0, &z);
+    }
+    for (const Tick& t : schedule_1f1b(b.stage, d.pp, ga)) {
+        if (t.kind == 0) forward(t.microbatch);
+        else backward(t.microbatch);
+    }
+    // Gains of the norms are replicated over the TP group but each rank saw only its rows.
+    if (tp > 1) {
+        b.sync(ST_COMPUTE_HI, ST_COMM_TP, 0);
+        for (const NamedTensor& nt : out->named) {
+            if (nt.init_std != 0.f) continue;
+            b.nccl(K_NCCL_ALL_REDUCE, OP_ALL_REDUCE, ST_COMM_TP, nt.grad, nt.grad, static_cast<uint64_t>(nt.rows) * nt.cols,
+                   DT_FP32, GROUP_TP, -1, 0);
+        }
+        b.sync(ST_COMM_TP, ST_COMPUTE_HI, 0);
+    }
+    // optimizer
+    if (d.dp > 1) {
+        if (b.fused) {
+            ExecOp e = xop(K_RS_ADAMW);
+            e.t[0] = b.flat_master; e.t[1] = b.flat_m; e.t[2] = b.flat_v; e.t[3] = b.flat_grad; e.t[4] = b.flat_param;
+            e.i[0] = static_cast<int32_t>(n_flat & 0xFFFFFFFFu); e.i[1] = static_cast<int32_t>(n_flat >> 32);
+            e.i[2] = static_cast<int32_t>(n_opt & 0xFFFFFFFFu); e.i[3] = GROUP_DP;
+            e.f[0] = 1.0f / d.dp;
+            b.sync(ST_COMPUTE_HI, ST_COMM_DP, 0);
+            b.push(OP_RS_ADAMW, ST_COMM_DP, 18.0 * n_opt, 4.0 * n_flat, GROUP_DP, 0, &e);
+            b.sync(ST_COMM_DP, ST_COMPUTE_HI, 0);
+        } else {
+            // baseline: all-reduce the gradients, every rank updates everything
+            b.sync(ST_COMPUTE_HI, ST_COMM_DP, 0);
+            b.nccl(K_NCCL_ALL_REDUCE, OP_ALL_REDUCE, ST_COMM_DP, b.flat_grad, b.flat_grad, n_flat, DT_FP32, GROUP_DP, -1, 0);
+            b.sync(ST_COMM_DP, ST_COMPUTE_LO, 0);
+            ExecOp e = xop(K_ADAMW);
+            e.t[0] = b.flat_master; e.t[1] = b.flat_m; e.t[2] = b.flat_v; e.t[3] = b.flat_grad; e.t[4] = b.flat_param;
+            e.i[0] = static_cast<int32_t>(n_flat & 0xFFFFFFFFu); e.i[1] = static_cast<int32_t>(n_flat >> 32);
+            e.f[0] = 1.0f / d.dp;
+            b.push(OP_OPTIMIZER, ST_COMPUTE_LO, 18.0 * n_flat, 0, 0, 0, &e);
+            b.sync(ST_COMPUTE_LO, ST_COMPUTE_HI, 0);
+        }
+    } else {
+        ExecOp e = xop(K_ADAMW);
+        e.t[0] = b.flat_master; e.t[1] = b.flat_m; e.t[2] = b.flat_v; e.t[3] = b.flat_grad; e.t[4] = b.flat_param;
+        e.i[0] = static_cast<int32_t>(n_flat & 0xFFFFFFFFu); e.i[1] = static_cast<int32_t>(n_flat >> 32);
+        e.f[0] = 1.0f;
+        b.push(OP_OPTIMIZER, ST_COMPUTE_HI, 18.0 * n_flat, 0, 0, 0, &e);
+    }
+
+    // ---------------- arena
+    uint64_t want[TC_COUNT];
+    for (int c = 0; c < TC_COUNT; ++c) want[c] = align_up(b.cursor[c], kTensorAlign);
+    Arena arena;
+    arena_layout(&arena, want);
+    arena_relocate(arena, out->tensors.data(), static_cast<uint32_t>(out->tensors.size()));
+    // named tensors keep the flat offset (units of 512 elements) in `master`
+    h.num_tensors = static_cast<uint32_t>(out->tensors.size());
+    h.num_groups = static_cast<uint32_t>(out->groups.size());
+    h.num_ops = static_cast<uint32_t>(out->ops.size());
+    h.num_events = b.next_event;
+    h.arena_bytes = arena.total;
+    // well-known tensors for the runtime
+    out->xhdr.num_exec = static_cast<uint32_t>(out->exec.size());
+    out->xhdr.num_named = static_cast<uint32_t>(out->named.size());
+    NamedTensor wk{};
+    auto well_known = [&](const char* name, int id) {
+        NamedTensor nt{};
+        std::snprintf(nt.name, sizeof nt.name, "%s", name);
+        nt.tensor = id;
+        nt.grad = -1;
+        nt.master = -1;
+        nt.rows = id >= 0 ? b.rows_of(id) : 0;
+        nt.cols = id >= 0 ? b.cols_of(id) : 0;
+        nt.init_std = -1.f;  // marks a runtime buffer, not a parameter
+        out->named.push_back(nt);
+    };
+    (void)wk;
+    well_known("@tokens", tokens);
+    well_known("@targets", targets);
+    well_known("@loss", loss_acc);
+    well_known("@rope_table", rope_tab);
+    well_known("@flat_param", b.flat_param);
+    well_known("@flat_grad", b.flat_grad);
+    well_known("@flat_master", b.flat_master);
+    well_known("@flat_m", b.flat_m);
+    well_known("@flat_v", b.flat_v);
+    out->xhdr.num_named = static_cast<uint32_t>(out->named.size());
+    return OK;
+}
+
+}  // namespace cai

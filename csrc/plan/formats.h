@@ -190,6 +190,8 @@ enum KernelId : uint16_t {
     K_NCCL_ALL_REDUCE, K_NCCL_REDUCE_SCATTER, K_NCCL_ALL_GATHER, K_NCCL_ALL_TO_ALL, K_NCCL_SEND, K_NCCL_RECV,
     K_GEMM_RS, K_AG_GEMM, K_RS_ADAMW, K_FSDP_AG_GEMM, K_MOE_ROUTE, K_MOE_DISPATCH_GEMM, K_MOE_GEMM_COMBINE,
     K_LOAD_TOKENS,
+    K_ADD,
+    K_CROSS_ENTROPY_TP,
     K_COUNT
 };
 

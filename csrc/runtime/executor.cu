@@ -1,0 +1,498 @@
+// executor.cu - the device runtime: replays a version-2 plan on six CUDA streams.
+//
+// This is the real-GPU counterpart of the reference's replay loop (src/runtime.c:145-181) and of
+// the backend its src/backend_cuda.c:13-30 only sketches: every non-event op becomes a kernel
+// launch (or an NCCL call) on the CUDA stream of its logical stream, EVENT_RECORD / EVENT_WAIT
+// become cudaEventRecord / cudaStreamWaitEvent on a pre-created pool, and all operands are
+// offsets into ONE arena allocation. The host never allocates or synchronises inside a step. A
+// whole step can be captured once into a CUDA graph and relaunched, with the per-step scalars
+// (learning rate, Adam bias corrections) read from a small device buffer that is refreshed
+// before each launch.
+//
+// NCCL is reached through dlopen so the library has no link-time dependency on it; communicators
+// are built from unique ids the launcher distributes (the reference exchanges them through files
+// in /tmp, src/cuda/cai_nccl.cu:35-52).
+#include <cuda_bf16.h>
+#include <dlfcn.h>
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "../kernels/cai_kernels.h"
+#include "../kernels/host_common.h"
+#include "../plan/formats.h"
+#include "cai_runtime.h"
+
+namespace cai {
+
+// ------------------------------------------------------------------ NCCL through dlopen
+struct NcclApi {
+    void* handle = nullptr;
+    int (*GetUniqueId)(void*) = nullptr;
+    int (*CommInitRank)(void**, int, NcclId, int) = nullptr;
+    int (*CommDestroy)(void*) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*ReduceScatter)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+    int (*Send)(const void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*Recv)(void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*GroupStart)() = nullptr;
+    int (*GroupEnd)() = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+};
+static NcclApi g_nccl;
+
+static bool nccl_load(const char* path) {
+    if (g_nccl.handle) return true;
+    void* h = dlopen(path && *path ? path : "libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) {
+        set_last_error("dlopen(%s) failed: %s", path ? path : "libnccl.so.2", dlerror());
+        return false;
+    }
+#define LOADSYM(field, name)                                             \
+    *reinterpret_cast<void**>(&g_nccl.field) = dlsym(h, name);           \
+    if (!g_nccl.field) {                                                 \
+        set_last_error("NCCL symbol %s missing", name);                 \
+        return false;                                                    \
+    }
+    LOADSYM(GetUniqueId, "ncclGetUniqueId")
+    LOADSYM(CommInitRank, "ncclCommInitRank")
+    LOADSYM(CommDestroy, "ncclCommDestroy")
+    LOADSYM(AllReduce, "ncclAllReduce")
+    LOADSYM(ReduceScatter, "ncclReduceScatter")
+    LOADSYM(AllGather, "ncclAllGather")
+    LOADSYM(Send, "ncclSend")
+    LOADSYM(Recv, "ncclRecv")
+    LOADSYM(GroupStart, "ncclGroupStart")
+    LOADSYM(GroupEnd, "ncclGroupEnd")
+    LOADSYM(GetErrorString, "ncclGetErrorString")
+#undef LOADSYM
+    g_nccl.handle = h;
+    return true;
+}
+
+static int nccl_dtype(int dt) {
+    switch (dt) {
+        case DT_FP32: return 7;
+        case DT_BF16: return 9;
+        case DT_FP16: return 6;
+        case DT_INT32: return 2;
+        default: return 1;  // bytes
+    }
+}
+
+__global__ void adamw_dev_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+                                 const float* __restrict__ grad, __nv_bfloat16* __restrict__ param, long long n,
+                                 const float* __restrict__ hyper, float gscale) {
+    // hyper: lr, beta1, beta2, eps, wd, 1-beta1^t, 1-beta2^t
+    const float lr = hyper[0], b1 = hyper[1], b2 = hyper[2], eps = hyper[3], wd = hyper[4], bc1 = hyper[5], bc2 = hyper[6];
+    const long long i4 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+    if (i4 >= n) return;
+    const float4 p4 = *reinterpret_cast<const float4*>(master + i4);
+    const float4 m4 = *reinterpret_cast<const float4*>(m + i4);
+    const float4 v4 = *reinterpret_cast<const float4*>(v + i4);
+    const float4 g4 = *reinterpret_cast<const float4*>(grad + i4);
+    float p[4] = {p4.x, p4.y, p4.z, p4.w}, mm[4] = {m4.x, m4.y, m4.z, m4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+    const float g[4] = {g4.x * gscale, g4.y * gscale, g4.z * gscale, g4.w * gscale};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        mm[e] = b1 * mm[e] + (1.f - b1) * g[e];
+        vv[e] = b2 * vv[e] + (1.f - b2) * g[e] * g[e];
+        p[e] -= lr * ((mm[e] / bc1) / (sqrtf(vv[e] / bc2) + eps) + wd * p[e]);
+    }
+    *reinterpret_cast<float4*>(master + i4) = make_float4(p[0], p[1], p[2], p[3]);
+    *reinterpret_cast<float4*>(m + i4) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    *reinterpret_cast<float4*>(v + i4) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    __nv_bfloat162 lo = __floats2bfloat162_rn(p[0], p[1]), hi = __floats2bfloat162_rn(p[2], p[3]);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo);
+    o.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(param + i4) = o;
+}
+
+struct Comm {
+    void* comm = nullptr;   // forward / only communicator
+    void* comm2 = nullptr;  // second communicator of the pipeline group (gradient direction)
+    int rank = 0, size = 1;
+};
+
+struct TraceRec { uint32_t op; cudaEvent_t start, stop; };
+
+}  // namespace cai
+
+using namespace cai;
+
+struct cai_exec {
+    PlanHeader hdr{};
+    ExecHeader xhdr{};
+    TrainSpec train{};
+    ModelSpec model{};
+    std::vector<TensorDesc> tensors;
+    std::vector<CommGroup> groups;
+    std::vector<Op> ops;
+    std::vector<ExecOp> exec;
+    std::vector<NamedTensor> named;
+    std::vector<uint32_t> shapes;
+    uint8_t* arena = nullptr;
+    int device = 0;
+    cudaStream_t streams[ST_COUNT] = {};
+    std::vector<cudaEvent_t> events;
+    cudaEvent_t fork_ev = nullptr, join_ev[ST_COUNT] = {};
+    Comm comms[GROUP_COUNT];
+    float* hyper_dev = nullptr;   // 8 floats
+    float* hyper_host = nullptr;  // pinned
+    cudaGraphExec_t graph = nullptr;
+    bool use_graph = false;
+    bool trace_on = false;
+    std::vector<TraceRec> trace;
+    cai_fused_hook_t fused_hook = nullptr;
+    void* fused_ctx = nullptr;
+    int sm_limit_hi = 0;
+    uint64_t launches = 0;  // kernels / collectives enqueued by the last replay
+
+    void* ptr(int t) const { return t >= 0 ? arena + tensors[t].offset : nullptr; }
+    long long ld(int t) const { return shapes[static_cast<size_t>(t) * 4 + 2]; }
+};
+
+namespace {
+
+int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
+    auto P = [&](int i) { return ex->ptr(x.t[i]); };
+    switch (x.kernel) {
+        case K_EMBED_FWD:
+            return cai_embed_fwd((const int*)P(0), P(1), P(2), x.i[0], x.i[1], x.i[2], x.i[3], st);
+        case K_EMBED_BWD:
+            return cai_embed_bwd((const int*)P(0), P(1), (float*)P(2), x.i[0], x.i[1], x.i[2], x.i[3], st);
+        case K_RMSNORM_FWD:
+            return cai_rmsnorm_fwd(P(0), P(1), P(2), (float*)P(3), x.i[0], x.i[1], x.f[0], st);
+        case K_RMSNORM_BWD:
+            return cai_rmsnorm_bwd(P(0), P(1), (const float*)P(2), P(3), P(4), (float*)P(5), (float*)P(6), x.i[0], x.i[1],
+                                   x.i[2], x.i[3], st);
+        case K_GEMM: {
+            const int ta = x.flags & 1, tb = (x.flags >> 1) & 1, epi = x.flags >> 4;
+            return cai_gemm_bf16(P(0), P(1), P(2), P(3), x.i[0], x.i[1], x.i[2], ex->ld(x.t[0]), ex->ld(x.t[1]),
+                                 ex->ld(x.t[2]), x.t[3] >= 0 ? ex->ld(x.t[3]) : 0, ta, tb, epi, x.f[0], ex->sm_limit_hi, st);
+        }
+        case K_ROPE:
+            return cai_rope_apply(P(0), (const float*)P(1), x.i[0], x.i[1], x.i[2], x.i[3], x.i[4], ex->ld(x.t[0]),
+                                  x.flags & 1, st);
+        case K_ATTN_FWD:
+            return cai_flash_attn_fwd(P(0), P(1), (float*)P(2), x.i[0], x.i[1], x.i[2], x.i[3], x.i[4], x.f[0], st);
+        case K_ATTN_BWD:
+            return cai_flash_attn_bwd(P(0), P(1), P(2), (const float*)P(3), (float*)P(4), P(5), x.i[0], x.i[1], x.i[2],
+                                      x.i[3], x.i[4], x.f[0], st);
+        case K_SWIGLU_FWD: return cai_swiglu_fwd(P(0), P(1), x.i[0], x.i[1], st);
+        case K_SWIGLU_BWD: return cai_swiglu_bwd(P(0), P(1), P(2), x.i[0], x.i[1], st);
+        case K_CROSS_ENTROPY:
+            return cai_cross_entropy(P(0), (const int*)P(1), (float*)P(2), nullptr, x.i[0], x.i[1], ex->ld(x.t[0]), x.f[0],
+                                     x.f[1], st);
+        case K_ADAMW: {
+            const long long n = (static_cast<long long>(static_cast<uint32_t>(x.i[1])) << 32) | static_cast<uint32_t>(x.i[0]);
+            const unsigned blocks = static_cast<unsigned>(((n + 3) / 4 + 255) / 256);
+            adamw_dev_kernel<<<blocks, 256, 0, st>>>((float*)P(0), (float*)P(1), (float*)P(2), (const float*)P(3),
+                                                     (__nv_bfloat16*)P(4), n, ex->hyper_dev, x.f[0]);
+            return cudaGetLastError() == cudaSuccess ? 0 : CAI_K_CUDA;
+        }
+        case K_ZERO:
+            return cudaMemsetAsync(P(0), 0, ex->tensors[x.t[0]].nbytes, st) == cudaSuccess ? 0 : CAI_K_CUDA;
+        case K_ADD:
+            return cai_add_bf16(P(0), P(1), P(2), x.i[0], st);
+        case K_NCCL_ALL_REDUCE: case K_NCCL_REDUCE_SCATTER: case K_NCCL_ALL_GATHER: case K_NCCL_SEND: case K_NCCL_RECV: {
+            const int group = x.i[3];
+            if (group < 0 || group >= GROUP_COUNT || !ex->comms[group].comm) {
+                set_last_error("op needs communicator %d which was not initialised", group);
+                return CAI_K_BAD_ARG;
+            }
+            const Comm& c = ex->comms[group];
+            const size_t count = (static_cast<size_t>(static_cast<uint32_t>(x.i[1])) << 32) | static_cast<uint32_t>(x.i[0]);
+            const int dt = nccl_dtype(x.i[2]);
+            int rc = 0;
+            if (x.kernel == K_NCCL_ALL_REDUCE) rc = g_nccl.AllReduce(P(0), P(1), count, dt, 0, c.comm, st);
+            else if (x.kernel == K_NCCL_REDUCE_SCATTER) rc = g_nccl.ReduceScatter(P(0), P(1), count, dt, 0, c.comm, st);
+            else if (x.kernel == K_NCCL_ALL_GATHER) rc = g_nccl.AllGather(P(0), P(1), count, dt, c.comm, st);
+            else {
+                // pipeline hand-off: activations use the first communicator, gradients the second
+                void* comm = (op.stream_id == ST_IO && c.comm2) ? c.comm2 : c.comm;
+                if (x.kernel == K_NCCL_SEND) rc = g_nccl.Send(P(0), count, dt, x.i[4], comm, st);
+                else rc = g_nccl.Recv(P(1), count, dt, x.i[4], comm, st);
+            }
+            if (rc != 0) {
+                set_last_error("NCCL call failed: %s", g_nccl.GetErrorString(rc));
+                return CAI_K_CUDA;
+            }
+            return 0;
+        }
+        default:
+            if (ex->fused_hook) return ex->fused_hook(ex->fused_ctx, ex, &x, static_cast<int>(op.stream_id), st);
+            set_last_error("no launcher for kernel id %d", (int)x.kernel);
+            return CAI_K_BAD_ARG;
+    }
+}
+
+int replay(cai_exec* ex) {
+    cudaStream_t hi = ex->streams[ST_COMPUTE_HI];
+    // fork: every stream starts after everything already queued on compute_hi
+    cudaEventRecord(ex->fork_ev, hi);
+    for (int s = 1; s < ST_COUNT; ++s) cudaStreamWaitEvent(ex->streams[s], ex->fork_ev, 0);
+    ex->launches = 0;
+    for (size_t i = 0; i < ex->ops.size(); ++i) {
+        const Op& op = ex->ops[i];
+        cudaStream_t st = ex->streams[op.stream_id];
+        if (op.kind == OP_EVENT_RECORD) {
+            if (cudaEventRecord(ex->events[op.aux0], st) != cudaSuccess) return CAI_K_CUDA;
+            continue;
+        }
+        if (op.kind == OP_EVENT_WAIT) {
+            if (cudaStreamWaitEvent(st, ex->events[op.aux0], 0) != cudaSuccess) return CAI_K_CUDA;
+            continue;
+        }
+        if (!op.exec) continue;
+        TraceRec* tr = nullptr;
+        if (ex->trace_on && !ex->use_graph) {
+            TraceRec r;
+            r.op = static_cast<uint32_t>(i);
+            cudaEventCreate(&r.start);
+            cudaEventCreate(&r.stop);
+            ex->trace.push_back(r);
+            tr = &ex->trace.back();
+            cudaEventRecord(tr->start, st);
+        }
+        const int rc = run_op(ex, op, ex->exec[op.exec - 1], st);
+        if (rc != 0) return rc;
+        ++ex->launches;
+        if (tr) cudaEventRecord(tr->stop, st);
+    }
+    // join: compute_hi waits for every other stream
+    for (int s = 1; s < ST_COUNT; ++s) {
+        cudaEventRecord(ex->join_ev[s], ex->streams[s]);
+        cudaStreamWaitEvent(hi, ex->join_ev[s], 0);
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : CAI_K_CUDA;
+}
+
+}  // namespace
+
+CAI_API int cai_exec_create(cai_exec** out, const void* plan_bytes, size_t nbytes, void* arena_base) {
+    auto ex = new cai_exec();
+    const uint8_t* p = static_cast<const uint8_t*>(plan_bytes);
+    const uint8_t* end = p + nbytes;
+    auto take = [&](void* dst, size_t n) {
+        if (p + n > end) return false;
+        memcpy(dst, p, n);
+        p += n;
+        return true;
+    };
+    bool ok = take(&ex->hdr, sizeof ex->hdr) && ex->hdr.magic == kPlanMagic && ex->hdr.version == 2;
+    if (ok) {
+        ex->tensors.resize(ex->hdr.num_tensors);
+        ex->groups.resize(ex->hdr.num_groups);
+        ex->ops.resize(ex->hdr.num_ops);
+        ok = take(ex->tensors.data(), ex->tensors.size() * sizeof(TensorDesc)) &&
+             take(ex->groups.data(), ex->groups.size() * sizeof(CommGroup)) &&
+             take(ex->ops.data(), ex->ops.size() * sizeof(Op)) && take(&ex->xhdr, sizeof ex->xhdr) &&
+             ex->xhdr.magic == kExecMagic && take(&ex->train, sizeof ex->train) && take(&ex->model, sizeof ex->model);
+    }
+    if (ok) {
+        ex->exec.resize(ex->xhdr.num_exec);
+        ex->named.resize(ex->xhdr.num_named);
+        ex->shapes.resize(static_cast<size_t>(ex->hdr.num_tensors) * 4);
+        ok = take(ex->exec.data(), ex->exec.size() * sizeof(ExecOp)) &&
+             take(ex->named.data(), ex->named.size() * sizeof(NamedTensor)) &&
+             take(ex->shapes.data(), ex->shapes.size() * sizeof(uint32_t));
+    }
+    if (!ok) {
+        set_last_error("not a version-2 plan (or truncated)");
+        delete ex;
+        return CAI_K_BAD_ARG;
+    }
+    for (const TensorDesc& t : ex->tensors)
+        if (t.offset + t.nbytes > ex->hdr.arena_bytes) {
+            set_last_error("tensor outside the arena");
+            delete ex;
+            return CAI_K_BAD_ARG;
+        }
+    for (const Op& o : ex->ops)
+        if (o.stream_id >= ST_COUNT || ((o.kind == OP_EVENT_RECORD || o.kind == OP_EVENT_WAIT) && o.aux0 >= ex->hdr.num_events) ||
+            o.exec > ex->exec.size()) {
+            set_last_error("malformed op table");
+            delete ex;
+            return CAI_K_BAD_ARG;
+        }
+    ex->arena = static_cast<uint8_t*>(arena_base);
+    ex->device = current_device();
+    int lo_prio = 0, hi_prio = 0;
+    cudaDeviceGetStreamPriorityRange(&lo_prio, &hi_prio);
+    for (int s = 0; s < ST_COUNT; ++s) {
+        const int prio = (s == ST_COMPUTE_HI || s == ST_COMM_TP) ? hi_prio : lo_prio;
+        if (cudaStreamCreateWithPriority(&ex->streams[s], cudaStreamNonBlocking, prio) != cudaSuccess) {
+            set_last_error("stream creation failed");
+            delete ex;
+            return CAI_K_CUDA;
+        }
+        cudaEventCreateWithFlags(&ex->join_ev[s], cudaEventDisableTiming);
+    }
+    cudaEventCreateWithFlags(&ex->fork_ev, cudaEventDisableTiming);
+    ex->events.resize(ex->hdr.num_events);
+    for (cudaEvent_t& e : ex->events) cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
+    cudaMalloc(&ex->hyper_dev, 8 * sizeof(float));
+    cudaMallocHost(&ex->hyper_host, 8 * sizeof(float));
+    *out = ex;
+    return 0;
+}
+
+CAI_API void cai_exec_destroy(cai_exec* ex) {
+    if (!ex) return;
+    cudaDeviceSynchronize();
+    if (ex->graph) cudaGraphExecDestroy(ex->graph);
+    for (TraceRec& r : ex->trace) { cudaEventDestroy(r.start); cudaEventDestroy(r.stop); }
+    for (cudaEvent_t e : ex->events) cudaEventDestroy(e);
+    for (int s = 0; s < ST_COUNT; ++s) {
+        if (ex->join_ev[s]) cudaEventDestroy(ex->join_ev[s]);
+        if (ex->streams[s]) cudaStreamDestroy(ex->streams[s]);
+    }
+    if (ex->fork_ev) cudaEventDestroy(ex->fork_ev);
+    for (Comm& c : ex->comms) {
+        if (c.comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c.comm);
+        if (c.comm2 && g_nccl.CommDestroy) g_nccl.CommDestroy(c.comm2);
+    }
+    cudaFree(ex->hyper_dev);
+    cudaFreeHost(ex->hyper_host);
+    delete ex;
+}
+
+CAI_API int cai_nccl_unique_id(const char* libpath, void* id128) {
+    if (!nccl_load(libpath)) return CAI_K_CUDA;
+    const int rc = g_nccl.GetUniqueId(id128);
+    if (rc != 0) {
+        set_last_error("ncclGetUniqueId: %s", g_nccl.GetErrorString(rc));
+        return CAI_K_CUDA;
+    }
+    return 0;
+}
+
+CAI_API int cai_exec_init_comm(cai_exec* ex, const char* libpath, int group_kind, const void* id128, const void* id128_second,
+                               int nranks, int rank) {
+    if (group_kind < 0 || group_kind >= GROUP_COUNT) return CAI_K_BAD_ARG;
+    if (!nccl_load(libpath)) return CAI_K_CUDA;
+    Comm& c = ex->comms[group_kind];
+    c.rank = rank;
+    c.size = nranks;
+    NcclId id;
+    memcpy(&id, id128, sizeof id);
+    int rc = g_nccl.CommInitRank(&c.comm, nranks, id, rank);
+    if (rc == 0 && id128_second) {
+        memcpy(&id, id128_second, sizeof id);
+        rc = g_nccl.CommInitRank(&c.comm2, nranks, id, rank);
+    }
+    if (rc != 0) {
+        set_last_error("ncclCommInitRank: %s", g_nccl.GetErrorString(rc));
+        return CAI_K_CUDA;
+    }
+    return 0;
+}
+
+CAI_API void* cai_exec_stream(cai_exec* ex, int stream_id) {
+    return stream_id >= 0 && stream_id < ST_COUNT ? ex->streams[stream_id] : nullptr;
+}
+CAI_API void* cai_exec_tensor_ptr(cai_exec* ex, int tensor) {
+    return tensor >= 0 && static_cast<size_t>(tensor) < ex->tensors.size() ? ex->ptr(tensor) : nullptr;
+}
+CAI_API long long cai_exec_tensor_ld(cai_exec* ex, int tensor) { return ex->ld(tensor); }
+CAI_API unsigned long long cai_exec_tensor_bytes(cai_exec* ex, int tensor) { return ex->tensors[tensor].nbytes; }
+CAI_API int cai_exec_group_rank(cai_exec* ex, int kind) { return ex->comms[kind].rank; }
+CAI_API int cai_exec_group_size(cai_exec* ex, int kind) { return ex->comms[kind].size; }
+CAI_API unsigned long long cai_exec_launches(cai_exec* ex) { return ex->launches; }
+CAI_API void cai_exec_set_fused_hook(cai_exec* ex, cai_fused_hook_t hook, void* ctx) {
+    ex->fused_hook = hook;
+    ex->fused_ctx = ctx;
+}
+CAI_API void cai_exec_set_sm_limit(cai_exec* ex, int sms) { ex->sm_limit_hi = sms; }
+CAI_API float* cai_exec_hyper(cai_exec* ex) { return ex->hyper_dev; }
+
+// Enqueue one optimizer step (all microbatches, forward + backward + update). `step` is the
+// 1-based AdamW step count. Returns after enqueueing; the caller synchronises when it wants
+// the loss.
+CAI_API int cai_exec_step(cai_exec* ex, int step, float lr) {
+    cudaStream_t hi = ex->streams[ST_COMPUTE_HI];
+    float* h = ex->hyper_host;
+    const TrainSpec& t = ex->train;
+    h[0] = lr; h[1] = t.beta1; h[2] = t.beta2; h[3] = t.adam_eps; h[4] = t.weight_decay;
+    h[5] = 1.f - powf(t.beta1, static_cast<float>(step));
+    h[6] = 1.f - powf(t.beta2, static_cast<float>(step));
+    h[7] = 0.f;
+    if (cudaMemcpyAsync(ex->hyper_dev, h, 8 * sizeof(float), cudaMemcpyHostToDevice, hi) != cudaSuccess) return CAI_K_CUDA;
+    if (ex->use_graph) {
+        if (!ex->graph) {
+            cudaGraph_t g = nullptr;
+            if (cudaStreamBeginCapture(hi, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+                set_last_error("cudaStreamBeginCapture failed");
+                return CAI_K_CUDA;
+            }
+            const int rc = replay(ex);
+            const cudaError_t ce = cudaStreamEndCapture(hi, &g);
+            if (rc != 0 || ce != cudaSuccess || !g) {
+                if (rc == 0) set_last_error("graph capture failed: %s", cudaGetErrorString(ce));
+                if (g) cudaGraphDestroy(g);
+                return rc ? rc : CAI_K_CUDA;
+            }
+            const cudaError_t ie = cudaGraphInstantiate(&ex->graph, g, 0);
+            cudaGraphDestroy(g);
+            if (ie != cudaSuccess) {
+                set_last_error("cudaGraphInstantiate failed: %s", cudaGetErrorString(ie));
+                return CAI_K_CUDA;
+            }
+        }
+        return cudaGraphLaunch(ex->graph, hi) == cudaSuccess ? 0 : CAI_K_CUDA;
+    }
+    if (ex->trace_on) {
+        for (TraceRec& r : ex->trace) { cudaEventDestroy(r.start); cudaEventDestroy(r.stop); }
+        ex->trace.clear();
+        ex->trace.reserve(ex->ops.size());
+    }
+    return replay(ex);
+}
+
+CAI_API int cai_exec_sync(cai_exec* ex) {
+    return cudaStreamSynchronize(ex->streams[ST_COMPUTE_HI]) == cudaSuccess ? 0 : CAI_K_CUDA;
+}
+
+CAI_API int cai_exec_use_graph(cai_exec* ex, int on) {
+    ex->use_graph = on != 0;
+    if (!on && ex->graph) {
+        cudaGraphExecDestroy(ex->graph);
+        ex->graph = nullptr;
+    }
+    return 0;
+}
+
+CAI_API int cai_exec_trace_enable(cai_exec* ex, int on) {
+    ex->trace_on = on != 0;
+    return 0;
+}
+
+// Measured timeline of the last traced step: one record per op with start / end in seconds
+// relative to the first op. Returns the number of records written.
+CAI_API int cai_exec_trace_read(cai_exec* ex, cai_exec_trace_rec* out, int cap) {
+    if (ex->trace.empty()) return 0;
+    cudaDeviceSynchronize();
+    int n = 0;
+    for (const TraceRec& r : ex->trace) {
+        if (n >= cap) break;
+        float a = 0.f, b = 0.f;
+        cudaEventElapsedTime(&a, ex->trace[0].start, r.start);
+        cudaEventElapsedTime(&b, ex->trace[0].start, r.stop);
+        const Op& op = ex->ops[r.op];
+        out[n].op_index = r.op;
+        out[n].kind = op.kind;
+        out[n].stream = op.stream_id;
+        out[n].start_s = a * 1e-3;
+        out[n].end_s = b * 1e-3;
+        out[n].bytes = op.bytes;
+        out[n].flops = op.flops;
+        ++n;
+    }
+    return n;
+}

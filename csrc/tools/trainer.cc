@@ -1,0 +1,76 @@
+// trainer <plan.bin> <topology.bin> [--steps N] [--ckpt PATH] [--ckpt-every K] [--trace CSV]
+//
+// Replays a compiled plan with the analytic backend (no GPU): per-step critical path, pipeline
+// bubble, MFU and tokens/s, per-stream occupancy, optional op timeline as CSV, periodic and
+// emergency checkpoints. Same command line and table as the reference (tools/trainer.c). The
+// device trainer that runs the same plan on GPUs is `python -m cai_b200.trainer`.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "cai.h"
+
+int main(int argc, char** argv) {
+    if (argc < 3) {
+        std::fprintf(stderr, "usage: %s <plan.bin> <topology.bin> [--steps N] [--ckpt PATH] [--ckpt-every K] [--trace CSV]\n", argv[0]);
+        return 2;
+    }
+    cai_init_desc_t desc;
+    std::memset(&desc, 0, sizeof desc);
+    desc.plan_path = argv[1];
+    desc.topology_path = argv[2];
+    desc.max_steps = 10;
+    const char* trace = nullptr;
+    if (const char* r = std::getenv("RANK")) desc.global_rank = std::strtoul(r, nullptr, 10);
+    for (int i = 3; i < argc; ++i) {
+        if (!std::strcmp(argv[i], "--steps") && i + 1 < argc) desc.max_steps = std::strtoul(argv[++i], nullptr, 10);
+        else if (!std::strcmp(argv[i], "--ckpt") && i + 1 < argc) { desc.checkpoint_path = argv[++i]; if (!desc.checkpoint_every) desc.checkpoint_every = 5; }
+        else if (!std::strcmp(argv[i], "--ckpt-every") && i + 1 < argc) desc.checkpoint_every = std::strtoul(argv[++i], nullptr, 10);
+        else if (!std::strcmp(argv[i], "--trace") && i + 1 < argc) trace = argv[++i];
+        else { std::fprintf(stderr, "unknown arg: %s\n", argv[i]); return 2; }
+    }
+    cai_context_t* ctx = nullptr;
+    int rc = cai_init(&ctx, &desc);
+    if (rc != 0) { std::fprintf(stderr, "init failed: %s\n", cai_status_str(rc)); return 1; }
+    if (desc.checkpoint_path && (rc = cai_load_checkpoint(ctx, desc.checkpoint_path)) != 0) {
+        std::fprintf(stderr, "checkpoint rejected: %s\n", cai_status_str(rc));
+        cai_finalize(ctx);
+        return 1;
+    }
+    if (trace) cai_trace_enable(ctx, 1);
+    std::printf("step | step_time | bubble |   MFU  | tokens/s    | tok/s/gpu\n");
+    std::printf("-----+-----------+--------+--------+-------------+----------\n");
+    double sum_mfu = 0, sum_tps = 0;
+    unsigned n = 0;
+    cai_step_stats_t st;
+    for (;;) {
+        cai_batch_t batch;
+        if (cai_next_batch(ctx, &batch) != 0) break;
+        rc = cai_train_step(ctx, &batch);
+        if (rc != 0) {
+            std::fprintf(stderr, "step %u failed: %s\n", batch.step, cai_status_str(rc));
+            cai_save_checkpoint(ctx, "emergency");
+            cai_finalize(ctx);
+            return 1;
+        }
+        cai_last_step_stats(ctx, &st);
+        std::printf("%4u | %7.2f ms| %5.1f%% | %5.1f%% | %9.2e | %8.1f\n", batch.step, st.step_time_s * 1e3,
+                    st.bubble_ratio * 100.0, st.mfu * 100.0, st.tokens_per_s, st.tokens_per_s_per_gpu);
+        sum_mfu += st.mfu;
+        sum_tps += st.tokens_per_s;
+        ++n;
+        if (cai_should_checkpoint(ctx) && cai_save_checkpoint(ctx, "periodic") != 0)
+            std::fprintf(stderr, "warning: checkpoint write failed at step %u\n", batch.step);
+    }
+    if (n) {
+        std::printf("\nsummary: %u steps | avg MFU %.1f%% | avg %.3e tokens/s | arena %.2f GiB/gpu\n", n, sum_mfu / n * 100.0,
+                    sum_tps / n, st.arena_bytes / (1024.0 * 1024.0 * 1024.0));
+        static const char* names[] = {"compute_hi", "compute_lo", "comm_tp", "comm_pp", "comm_dp", "io"};
+        std::printf("per-stream occupancy (ms): ");
+        for (int s = 0; s < 6; ++s) std::printf("%s=%.1f ", names[s], st.stream_busy[s] * 1e3);
+        std::printf("\n");
+    }
+    if (trace && cai_trace_dump_csv(ctx, trace) == 0) std::printf("wrote op timeline to %s\n", trace);
+    cai_finalize(ctx);
+    return 0;
+}
