@@ -23,7 +23,9 @@ LIBDIR = ROOT / "cai_b200" / "lib"
 BINDIR = ROOT / "bin"
 
 NVCC = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-CXX = os.environ.get("CXX") or shutil.which("g++") or "g++"
+# The system g++ links libstdc++ dynamically; a toolchain that links it statically (some images set
+# CXX to one) puts a second copy of the C++ runtime next to the one PyTorch loads, which crashes.
+CXX = os.environ.get("CAI_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else shutil.which("g++") or "g++")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -1,0 +1,61 @@
+"""A plain PyTorch restatement of the dense decoder the plans execute (RMSNorm, RoPE, causal GQA
+attention, SwiGLU, tied LM head, mean next-token cross-entropy).
+
+It is the fp32 reference that GPU tests compare the engine against: it reads the engine's own
+parameters, so both sides start from identical weights. It is never on a hot path.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+
+def rope(x, seq, theta):
+    """x: [B, S, heads, hd]; rotate-half convention with position = index inside the sequence."""
+    hd = x.shape[-1]
+    half = hd // 2
+    pos = torch.arange(seq, device=x.device, dtype=torch.float32)
+    inv = theta ** (-torch.arange(half, device=x.device, dtype=torch.float32) / half)
+    ang = pos[:, None] * inv[None, :]
+    c, s = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
+    x1, x2 = x[..., :half], x[..., half:]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1)
+
+
+def forward_loss(params: dict, tokens, targets, *, layers, heads, kv_heads, head_dim, seq, eps, theta,
+                 dtype=torch.float32):
+    """params: name -> tensor (``embed``, ``L{i}.g1/wqkv/wo/g2/wgu/wd``, ``gf``, optional ``lm_head``).
+    tokens / targets: int64 [B, S]. Returns the mean cross-entropy."""
+    B, S = tokens.shape
+    p = {k: v.to(dtype) for k, v in params.items()}
+    x = p["embed"][tokens]                                     # B S H
+
+    def norm(h, g):
+        return h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps) * g.view(-1)
+
+    rep = heads // kv_heads
+    for l in range(layers):
+        pre = f"L{l}."
+        h = norm(x, p[pre + "g1"])
+        qkv = h @ p[pre + "wqkv"].t()
+        q, k, v = qkv.split([heads * head_dim, kv_heads * head_dim, kv_heads * head_dim], -1)
+        q = rope(q.view(B, S, heads, head_dim), seq, theta)
+        k = rope(k.view(B, S, kv_heads, head_dim), seq, theta)
+        v = v.view(B, S, kv_heads, head_dim)
+        q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+        k = k.repeat_interleave(rep, 1)
+        v = v.repeat_interleave(rep, 1)
+        s = (q @ k.transpose(-1, -2)) * head_dim ** -0.5
+        mask = torch.ones(S, S, device=x.device, dtype=torch.bool).tril()
+        s = s.masked_fill(~mask, float("-inf"))
+        a = torch.softmax(s, -1) @ v
+        a = a.transpose(1, 2).reshape(B, S, heads * head_dim)
+        x = x + a @ p[pre + "wo"].t()
+        h = norm(x, p[pre + "g2"])
+        gu = h @ p[pre + "wgu"].t()
+        g, u = gu.chunk(2, -1)
+        x = x + (F.silu(g) * u) @ p[pre + "wd"].t()
+    h = norm(x, p["gf"])
+    head = p.get("lm_head", p["embed"])
+    logits = h @ head.t()
+    return F.cross_entropy(logits.view(B * S, -1).float(), targets.reshape(-1))

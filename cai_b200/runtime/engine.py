@@ -34,7 +34,7 @@ def _declare_runtime(L):
     if getattr(L, "_cai_rt_declared", False):
         return
     P, I = c_void_p, c_int
-    L.cai_exec_create.argtypes = [ctypes.POINTER(P), P, c_size_t, P]
+    L.cai_exec_create.argtypes = [ctypes.POINTER(P), P, c_size_t, P, ctypes.POINTER(P)]
     L.cai_exec_destroy.argtypes = [P]
     L.cai_exec_destroy.restype = None
     L.cai_nccl_unique_id.argtypes = [c_char_p, P]
@@ -128,9 +128,13 @@ class Engine:
         self._arena_shift = base - self.arena.data_ptr()
         self.arena.zero_()
         self.ex = c_void_p()
-        klib.check(L.cai_exec_create(ctypes.byref(self.ex), self.plan.raw, len(self.plan.raw), c_void_p(base)),
+        # The six streams come from torch's pool: tensors touched on them stay valid for torch's
+        # caching allocators after the executor is gone. compute_hi and comm_tp get high priority.
+        self.streams = [torch.cuda.Stream(device=self.device, priority=-1 if s in (0, 2) else 0) for s in range(6)]
+        handles = (c_void_p * 6)(*[c_void_p(s.cuda_stream) for s in self.streams])
+        klib.check(L.cai_exec_create(ctypes.byref(self.ex), self.plan.raw, len(self.plan.raw), c_void_p(base), handles),
                    "exec_create")
-        self.stream = torch.cuda.ExternalStream(L.cai_exec_stream(self.ex, 0), device=self.device)
+        self.stream = self.streams[0]
         self.step_count = 0
         self.lr = float(self.train.lr)
         self._init_comms()

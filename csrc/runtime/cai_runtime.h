@@ -32,7 +32,9 @@ typedef struct {
     uint64_t flops;
 } cai_exec_trace_rec;
 
-CAI_API int cai_exec_create(cai_exec** out, const void* plan_bytes, size_t nbytes, void* arena_base);
+/* caller_streams: NULL, or six CUDA stream handles (NULL entries are created and owned by the executor). */
+CAI_API int cai_exec_create(cai_exec** out, const void* plan_bytes, size_t nbytes, void* arena_base,
+                            void* const* caller_streams);
 CAI_API void cai_exec_destroy(cai_exec* ex);
 CAI_API int cai_nccl_unique_id(const char* libpath, void* id128);
 CAI_API int cai_exec_init_comm(cai_exec* ex, const char* libpath, int group_kind, const void* id128,

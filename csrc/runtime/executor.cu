@@ -139,6 +139,7 @@ struct cai_exec {
     uint8_t* arena = nullptr;
     int device = 0;
     cudaStream_t streams[ST_COUNT] = {};
+    bool owns_stream[ST_COUNT] = {};
     std::vector<cudaEvent_t> events;
     cudaEvent_t fork_ev = nullptr, join_ev[ST_COUNT] = {};
     Comm comms[GROUP_COUNT];
@@ -262,7 +263,11 @@ int replay(cai_exec* ex) {
         }
         const int rc = run_op(ex, op, ex->exec[op.exec - 1], st);
         if (rc != 0) return rc;
-        ++ex->launches;
+        {
+            // kernels of this library behind the op (memsets and NCCL calls are not ours)
+            const uint16_t k = ex->exec[op.exec - 1].kernel;
+            ex->launches += k == K_ATTN_BWD ? 3 : k == K_RMSNORM_BWD ? 2 : (k == K_ZERO || (k >= K_NCCL_ALL_REDUCE && k <= K_NCCL_RECV)) ? 0 : 1;
+        }
         if (tr) cudaEventRecord(tr->stop, st);
     }
     // join: compute_hi waits for every other stream
@@ -275,7 +280,8 @@ int replay(cai_exec* ex) {
 
 }  // namespace
 
-CAI_API int cai_exec_create(cai_exec** out, const void* plan_bytes, size_t nbytes, void* arena_base) {
+CAI_API int cai_exec_create(cai_exec** out, const void* plan_bytes, size_t nbytes, void* arena_base,
+                            void* const* caller_streams) {
     auto ex = new cai_exec();
     const uint8_t* p = static_cast<const uint8_t*>(plan_bytes);
     const uint8_t* end = p + nbytes;
@@ -327,7 +333,12 @@ CAI_API int cai_exec_create(cai_exec** out, const void* plan_bytes, size_t nbyte
     cudaDeviceGetStreamPriorityRange(&lo_prio, &hi_prio);
     for (int s = 0; s < ST_COUNT; ++s) {
         const int prio = (s == ST_COMPUTE_HI || s == ST_COMM_TP) ? hi_prio : lo_prio;
-        if (cudaStreamCreateWithPriority(&ex->streams[s], cudaStreamNonBlocking, prio) != cudaSuccess) {
+        if (caller_streams && caller_streams[s]) {
+            // streams owned by the caller (e.g. a framework's stream pool) are used, never destroyed
+            ex->streams[s] = static_cast<cudaStream_t>(caller_streams[s]);
+        } else if (cudaStreamCreateWithPriority(&ex->streams[s], cudaStreamNonBlocking, prio) == cudaSuccess) {
+            ex->owns_stream[s] = true;
+        } else {
             set_last_error("stream creation failed");
             delete ex;
             return CAI_K_CUDA;
@@ -351,7 +362,7 @@ CAI_API void cai_exec_destroy(cai_exec* ex) {
     for (cudaEvent_t e : ex->events) cudaEventDestroy(e);
     for (int s = 0; s < ST_COUNT; ++s) {
         if (ex->join_ev[s]) cudaEventDestroy(ex->join_ev[s]);
-        if (ex->streams[s]) cudaStreamDestroy(ex->streams[s]);
+        if (ex->streams[s] && ex->owns_stream[s]) cudaStreamDestroy(ex->streams[s]);
     }
     if (ex->fork_ev) cudaEventDestroy(ex->fork_ev);
     for (Comm& c : ex->comms) {

@@ -1,0 +1,350 @@
+// cai_selftest - unit tests of the GPU-free library, one binary, exit code = number of failures.
+//
+// Covers what the reference's tests/cai_test.c covers (topology math, arena packing, 1F1B schedule,
+// decomposition, plan round trip, cost model, expert-parallel memory, group tiling, spare ranks)
+// plus the executable-plan checks that are new here (event order, hazard analysis, pipeline
+// pairing, checkpoint files, golden hashes of the bundled configs).
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <set>
+
+#include "cai.h"
+#include "plan.h"
+
+using namespace cai;
+
+static int g_fail = 0, g_checks = 0;
+#define CHECK(cond, ...)                                   \
+    do {                                                   \
+        ++g_checks;                                        \
+        if (!(cond)) {                                     \
+            ++g_fail;                                      \
+            std::printf("FAIL %s:%d: ", __FILE__, __LINE__); \
+            std::printf(__VA_ARGS__);                      \
+            std::printf("\n");                             \
+        }                                                  \
+    } while (0)
+
+static Config small_cfg() {
+    Config c;
+    config_defaults(&c);
+    ModelSpec& m = c.model;
+    m.hidden_size = 4096; m.ffn_hidden = 14336; m.num_layers = 24; m.num_heads = 32; m.num_kv_heads = 8;
+    m.head_dim = 128; m.vocab_size = 128000; m.seq_len = 4096;
+    m.tp = 4; m.pp = 3; m.grad_accum = 12; m.microbatch = 1; m.recompute = 1;
+    c.topo.gpus_per_rack = 72; c.topo.num_racks = 1;
+    return c;
+}
+
+static void test_topology() {
+    Topology t;
+    topology_default(&t);
+    t.num_racks = 3056;
+    std::string err;
+    CHECK(topology_finalize(&t, &err) == OK, "finalize: %s", err.c_str());
+    CHECK(t.world_size == 220032, "world %u", t.world_size);
+    for (uint32_t r : {0u, 1u, 71u, 72u, 73u, 100000u, 220031u}) {
+        const PhysId p = phys_of_rank(t, r);
+        CHECK(rank_of(t, p.rack_id, p.tray_id, p.gpu_in_tray) == r, "round trip of rank %u", r);
+        CHECK(p.gpu_in_rack == r % 72 && p.rack_id == r / 72, "coords of rank %u", r);
+    }
+    CHECK(same_rack(t, 0, 71) && !same_rack(t, 71, 72), "same_rack");
+    Topology bad = t;
+    bad.trays_per_rack = 5;
+    CHECK(topology_finalize(&bad, &err) == ERR_TOPOLOGY, "inconsistent trays accepted");
+    CHECK(topology_hash(t) != topology_hash(bad), "hash ignores fields");
+}
+
+static void test_arena() {
+    const uint64_t want[TC_COUNT] = {1000, 513, 0, 7, 4096, 1};
+    Arena a;
+    arena_layout(&a, want);
+    uint64_t prev_end = 0;
+    for (int c = 0; c < TC_COUNT; ++c) {
+        CHECK(a.seg_off[c] % 512 == 0, "segment %d not aligned", c);
+        CHECK(a.seg_off[c] >= prev_end, "segment %d overlaps", c);
+        CHECK(a.seg_len[c] == want[c], "segment %d length", c);
+        prev_end = a.seg_off[c] + a.seg_len[c];
+    }
+    CHECK(a.total % 512 == 0 && a.total >= prev_end, "total");
+    TensorDesc t{};
+    t.tclass = TC_COMM;
+    t.offset = 16;
+    arena_relocate(a, &t, 1);
+    CHECK(t.offset == a.seg_off[TC_COMM] + 16, "relocate");
+}
+
+static void test_pipeline() {
+    CHECK(std::fabs(pipeline_bubble(16, 128) - 15.0 / 143.0) < 1e-12, "bubble 16/128");
+    CHECK(pipeline_bubble(1, 8) == 0.0 && pipeline_bubble(4, 0) == 0.0, "degenerate bubble");
+    CHECK(pipeline_bubble_interleaved(3, 12, 2) < pipeline_bubble_interleaved(3, 12, 1), "vpp lowers bubble");
+    CHECK(std::fabs(pipeline_bubble_interleaved(3, 12, 2) - 2.0 / 26.0) < 1e-12, "vpp=2 value");
+    const uint32_t pp = 4, m = 8;
+    for (uint32_t s = 0; s < pp; ++s) {
+        const std::vector<Tick> t = schedule_1f1b(s, pp, m);
+        CHECK(t.size() == 2 * m, "stage %u has %zu ticks", s, t.size());
+        std::vector<int> f(m, -1), b(m, -1);
+        for (size_t i = 0; i < t.size(); ++i) (t[i].kind == 0 ? f : b)[t[i].microbatch] = static_cast<int>(i);
+        int in_flight = 0, max_in_flight = 0;
+        for (const Tick& k : t) {
+            in_flight += k.kind == 0 ? 1 : -1;
+            max_in_flight = std::max(max_in_flight, in_flight);
+        }
+        CHECK(max_in_flight == static_cast<int>(pp - s), "stage %u keeps %d microbatches in flight", s, max_in_flight);
+        for (uint32_t k = 0; k < m; ++k) CHECK(f[k] >= 0 && b[k] > f[k], "stage %u mb %u order", s, k);
+    }
+}
+
+static void test_decompose() {
+    Config c = small_cfg();
+    Decomp d;
+    std::string err;
+    CHECK(decompose(c, &d, &err) == OK, "%s", err.c_str());
+    CHECK(d.model_replica_gpus == 12 && d.dp == 6 && d.global_batch == 72, "replica %u dp %u gb %llu",
+          d.model_replica_gpus, d.dp, (unsigned long long)d.global_batch);
+    CHECK(d.total_params > 5700000000ull && d.total_params < 5800000000ull, "params %llu", (unsigned long long)d.total_params);
+    Config bad = c;
+    bad.model.tp = 5;
+    CHECK(decompose(bad, &d, &err) == ERR_INVALID, "tp=5 accepted");
+    bad = c;
+    bad.model.vpp = 5;
+    CHECK(decompose(bad, &d, &err) == ERR_INVALID, "vpp=5 accepted");
+    bad = c;
+    bad.model.vpp = 2;
+    Decomp d2;
+    CHECK(decompose(bad, &d2, &err) == OK && d2.bubble_ratio < pipeline_bubble(3, 12), "vpp=2");
+    bad = c;
+    bad.model.pp = 100;
+    CHECK(decompose(bad, &d, &err) == ERR_INVALID, "pp > layers accepted");
+}
+
+static void test_plan_roundtrip() {
+    Config c = small_cfg();
+    std::string err;
+    topology_finalize(&c.topo, &err);
+    Decomp d;
+    decompose(c, &d, &err);
+    const uint64_t ph = plan_hash(c, d), th = topology_hash(c.topo);
+    CHECK(ph == 0x61eec02c9563ad48ull, "small.cfg plan_hash %016llx", (unsigned long long)ph);
+    CHECK(th == 0xa6628b5f000e9efaull, "small.cfg topology_hash %016llx", (unsigned long long)th);
+    Plan p, q;
+    CHECK(build_plan_v1(c, d, 4, ph, th, &p, &err) == OK, "%s", err.c_str());
+    CHECK(p.hdr.pipeline_stage == 1 && p.ops.size() == 3327 && p.hdr.num_events == 721, "stage %u ops %zu events %u",
+          p.hdr.pipeline_stage, p.ops.size(), p.hdr.num_events);
+    CHECK(p.hdr.arena_bytes == 1959259136ull, "arena %llu", (unsigned long long)p.hdr.arena_bytes);
+    const std::string path = "/tmp/cai_selftest_plan.bin";
+    CHECK(plan_write(path, p) == OK, "write");
+    CHECK(plan_read(path, &q) == OK, "read");
+    CHECK(std::memcmp(&p.hdr, &q.hdr, sizeof p.hdr) == 0, "header differs");
+    CHECK(p.ops.size() == q.ops.size() && std::memcmp(p.ops.data(), q.ops.data(), p.ops.size() * sizeof(Op)) == 0, "ops differ");
+    CHECK(std::memcmp(p.groups.data(), q.groups.data(), p.groups.size() * sizeof(CommGroup)) == 0, "groups differ");
+    uint64_t by_class[TC_COUNT];
+    plan_arena_breakdown(q, by_class);
+    uint64_t sum = 0;
+    for (uint64_t b : by_class) sum += b;
+    CHECK(sum <= q.hdr.arena_bytes, "breakdown exceeds arena");
+    Config c2 = c;
+    c2.topo.num_racks = 2;
+    topology_finalize(&c2.topo, &err);
+    CHECK(topology_hash(c2.topo) != th, "topology hash insensitive");
+    std::remove(path.c_str());
+}
+
+static void test_costmodel() {
+    // replay single-op plans through the public runtime API
+    Config c = small_cfg();
+    std::string err;
+    c.topo.num_racks = 20;
+    c.model.tp = 8; c.model.pp = 1;
+    topology_finalize(&c.topo, &err);
+    Decomp d;
+    CHECK(decompose(c, &d, &err) == OK, "%s", err.c_str());
+    const uint64_t ph = plan_hash(c, d), th = topology_hash(c.topo);
+    topology_write("/tmp/cai_selftest_topo.bin", c.topo);
+    auto time_of = [&](Op op, CommGroup g) {
+        Plan p;
+        build_plan_v1(c, d, 0, ph, th, &p, &err);
+        p.ops.assign(1, op);
+        p.groups.assign(1, g);
+        p.hdr.num_ops = 1; p.hdr.num_groups = 1; p.hdr.num_events = 0;
+        p.hdr.num_stages = 1;
+        plan_write("/tmp/cai_selftest_one.bin", p);
+        cai_init_desc_t desc{};
+        desc.plan_path = "/tmp/cai_selftest_one.bin";
+        desc.topology_path = "/tmp/cai_selftest_topo.bin";
+        cai_context_t* ctx = nullptr;
+        log_set_level(LOG_ERROR);
+        if (cai_init(&ctx, &desc) != 0) return -1.0;
+        cai_batch_t b;
+        cai_next_batch(ctx, &b);
+        cai_train_step(ctx, &b);
+        cai_step_stats_t st;
+        cai_last_step_stats(ctx, &st);
+        cai_finalize(ctx);
+        return st.step_time_s;
+    };
+    Op ar{};
+    ar.kind = OP_ALL_REDUCE; ar.stream_id = ST_COMM_TP; ar.bytes = 1 << 26;
+    CommGroup g{0, GROUP_TP, 1, 8, 0};
+    const double intra = time_of(ar, g);
+    g.intra_rack = 0;
+    const double inter = time_of(ar, g);
+    g.size = 1024;
+    const double big = time_of(ar, g);
+    CHECK(intra > 0 && intra < inter, "intra %g inter %g", intra, inter);
+    CHECK(big > inter, "1024-rank all-reduce not slower");
+    Op gm{};
+    gm.kind = OP_GEMM; gm.stream_id = ST_COMPUTE_HI; gm.flops = static_cast<uint64_t>(c.topo.gpu_flops_bf16);
+    CHECK(std::fabs(time_of(gm, g) - 1.0) < 1e-6, "peak-flops GEMM should take 1 s");
+}
+
+static void test_ep_memory() {
+    Config c;
+    config_load("configs/full220k_moe.cfg", &c, nullptr);
+    std::string err;
+    Decomp a, b;
+    c.model.ep = 191;
+    const int ra = decompose(c, &a, &err);
+    c.model.ep = 9;
+    const int rb = decompose(c, &b, &err);
+    CHECK(ra == OK && rb == OK, "moe decompose: %s", err.c_str());
+    if (ra == OK && rb == OK) CHECK(a.mem_param < b.mem_param, "larger ep should shrink param memory");
+}
+
+static void test_grouptiling_and_spare() {
+    Config c = small_cfg();
+    std::string err;
+    topology_finalize(&c.topo, &err);
+    Decomp d;
+    decompose(c, &d, &err);
+    VerifyReport rep;
+    verify_tiling(d, c.topo, false, GROUP_TP, "TP", &rep);
+    verify_tiling(d, c.topo, false, GROUP_DP, "DP", &rep);
+    verify_tiling(d, c.topo, false, GROUP_PP, "PP", &rep);
+    CHECK(rep.problems == 0, "tiling problems: %d", rep.problems);
+    // members lists are consistent with the coordinates
+    const std::vector<uint32_t> tpm = group_members(d, false, GROUP_TP, 5), ppm = group_members(d, false, GROUP_PP, 5),
+                                dpm = group_members(d, false, GROUP_DP, 5);
+    CHECK(tpm == (std::vector<uint32_t>{4, 5, 6, 7}), "tp members");
+    CHECK(ppm == (std::vector<uint32_t>{1, 5, 9}), "pp members");
+    CHECK(dpm.size() == 6 && dpm[0] == 5 && dpm[1] == 17, "dp members");
+
+    Topology t = c.topo;
+    t.num_racks = 2;
+    t.spare_gpus = 4;
+    topology_finalize(&t, &err);
+    uint32_t spare = 0;
+    CHECK(spare_rank(t, 100, &spare) == OK && spare >= t.world_size, "spare pick");
+    CHECK(spare_rank(t, 3, &spare) == OK && spare / 72 != 0, "spare %u should sit in another rack", spare);
+    t.spare_gpus = 0;
+    topology_finalize(&t, &err);
+    CHECK(spare_rank(t, 3, &spare) != OK, "no spares but got one");
+}
+
+static void test_config_parser() {
+    Config c;
+    std::string err;
+    CHECK(config_parse("hidden_size = 1024 # comment\n\n gpu_mem_bytes=288e9\nparam_dtype = fp8e4m3\n", &c, &err) == OK, "%s", err.c_str());
+    CHECK(c.model.hidden_size == 1024 && c.topo.gpu_mem_bytes == 288000000000ull && c.model.param_dtype == DT_FP8_E4M3, "values");
+    CHECK(config_parse("bogus_key = 3\n", &c, &err) == ERR_INVALID && err.find("line 1") != std::string::npos, "unknown key: %s", err.c_str());
+    CHECK(config_parse("tp = 2\nthis line has no equals\n", &c, &err) == ERR_INVALID && err.find("line 2") != std::string::npos, "%s", err.c_str());
+    CHECK(config_parse("lr = 3e-4\ncomm = baseline\nseed = 7\n", &c, &err) == OK && c.train.comm_mode == 0 && c.train.seed == 7, "train keys");
+    CHECK(sizeof(ModelSpec) == 96, "ModelSpec size");
+}
+
+static void test_exec_plans() {
+    for (const char* path : {"configs/tiny.cfg", "configs/b200_tp8.cfg", "configs/b200_pp2tp4.cfg"}) {
+        for (const char* mode : {"fused", "baseline"}) {
+            Config c;
+            std::string err;
+            if (config_load(path, &c, &err) != OK) { CHECK(false, "%s: %s", path, err.c_str()); continue; }
+            c.train.comm_mode = std::strcmp(mode, "fused") == 0;
+            topology_finalize(&c.topo, &err);
+            Decomp d;
+            CHECK(decompose(c, &d, &err) == OK, "%s", err.c_str());
+            const uint64_t ph = plan_hash(c, d), th = topology_hash(c.topo);
+            std::vector<Plan> stages;
+            for (uint32_t s = 0; s < d.pp; ++s) {
+                Plan p;
+                CHECK(build_plan_v2(c, d, s * d.tp * d.cp, ph, th, &p, &err) == OK, "%s: %s", path, err.c_str());
+                VerifyReport rep;
+                verify_event_order(p, &rep);
+                verify_hazards(p, &rep);
+                CHECK(rep.problems == 0, "%s (%s) stage %u: %d problems: %s", path, mode, s, rep.problems,
+                      rep.lines.empty() ? "" : rep.lines.back().c_str());
+                for (const TensorDesc& t : p.tensors) CHECK(t.offset + t.nbytes <= p.hdr.arena_bytes, "tensor outside arena");
+                // file round trip keeps the execution section
+                CHECK(plan_write("/tmp/cai_selftest_x.bin", p) == OK, "write v2");
+                Plan q;
+                CHECK(plan_read("/tmp/cai_selftest_x.bin", &q) == OK && q.exec.size() == p.exec.size() &&
+                          q.named.size() == p.named.size() && q.shapes == p.shapes,
+                      "v2 round trip");
+                stages.push_back(std::move(p));
+            }
+            VerifyReport rep;
+            verify_pipeline_pairing(stages, &rep);
+            CHECK(rep.problems == 0, "%s: pipeline pairing", path);
+        }
+    }
+    // a deliberately broken schedule must be caught: drop every wait of the tp8 baseline plan
+    Config c;
+    std::string err;
+    config_load("configs/b200_tp8.cfg", &c, &err);
+    c.train.comm_mode = 0;
+    topology_finalize(&c.topo, &err);
+    Decomp d;
+    decompose(c, &d, &err);
+    Plan p;
+    build_plan_v2(c, d, 0, plan_hash(c, d), topology_hash(c.topo), &p, &err);
+    std::vector<Op> kept;
+    for (const Op& o : p.ops)
+        if (o.kind != OP_EVENT_WAIT) kept.push_back(o);
+    p.ops = kept;
+    VerifyReport rep;
+    verify_hazards(p, &rep);
+    CHECK(rep.problems > 0, "hazard checker missed a schedule without waits");
+}
+
+static void test_checkpoint_files() {
+    const char* base = "/tmp/cai_selftest_ckpt";
+    const float w[4] = {1, 2, 3, 4};
+    const double v[2] = {5, 6};
+    const char* names[2] = {"weights", "moments"};
+    const void* data[2] = {w, v};
+    const uint64_t nbytes[2] = {sizeof w, sizeof v};
+    CHECK(cai_ckpt_write(base, "periodic", 3, 17, 0xabcdefull, 2, names, data, nbytes) == 0, "write");
+    uint32_t step = 0, nsec = 0;
+    uint64_t ph = 0;
+    char file[512];
+    CHECK(cai_ckpt_probe(base, 3, &step, &ph, &nsec, file, sizeof file) == 0 && step == 17 && ph == 0xabcdefull && nsec == 2, "probe");
+    CHECK(std::strstr(file, ".latest.rank000003") != nullptr, "latest pointer: %s", file);
+    char name[16];
+    uint64_t n = 0;
+    double back[2] = {0, 0};
+    CHECK(cai_ckpt_section(file, 1, name, &n, back, sizeof back) == 0 && n == sizeof v && back[1] == 6 && !std::strcmp(name, "moments"), "section");
+    CHECK(cai_ckpt_probe("/tmp/cai_selftest_nothing_here", 0, &step, &ph, &nsec, file, sizeof file) == 1, "missing checkpoint");
+    // the first 12 bytes keep the reference's layout: u32 step, u64 plan_hash
+    FILE* f = std::fopen(file, "rb");
+    uint32_t s2 = 0;
+    uint64_t h2 = 0;
+    CHECK(f && std::fread(&s2, 4, 1, f) == 1 && std::fread(&h2, 8, 1, f) == 1 && s2 == 17 && h2 == 0xabcdefull, "prefix");
+    if (f) std::fclose(f);
+}
+
+int main() {
+    log_set_level(LOG_ERROR);
+    test_topology();
+    test_arena();
+    test_pipeline();
+    test_decompose();
+    test_plan_roundtrip();
+    test_costmodel();
+    test_ep_memory();
+    test_grouptiling_and_spare();
+    test_config_parser();
+    test_exec_plans();
+    test_checkpoint_files();
+    std::printf("%d checks, %d failures\n", g_checks, g_fail);
+    return g_fail ? 1 : 0;
+}

@@ -1,0 +1,158 @@
+"""GPU-free tests of the offline compiler, verifier, analytic runtime and tools."""
+import ctypes
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+BIN = ROOT / "bin"
+
+
+@pytest.fixture(scope="session", autouse=True)
+def _built():
+    from cai_b200 import _build
+    _build.build_host()
+
+
+def run(*cmd, ok=True):
+    r = subprocess.run([str(c) for c in cmd], capture_output=True, text=True, cwd=ROOT)
+    if ok:
+        assert r.returncode == 0, r.stdout + r.stderr
+    return r
+
+
+def test_native_selftest():
+    r = run(BIN / "cai_selftest")
+    assert "0 failures" in r.stdout
+
+
+GOLDEN = {  # config -> (plan_hash, topology_hash, ops of rank 0, ops of the last-stage sample rank)
+    "small": ("61eec02c9563ad48", "a6628b5f000e9efa", 3243, 3303),
+    "full220k": ("6435c0f31b2cde67", "03ef8972bac28218", 34563, 30979),
+    "full220k_moe": ("5f02c7d3a752a1b4", "03ef8972bac28218", 40707, 36355),
+}
+
+
+@pytest.mark.parametrize("name", list(GOLDEN))
+def test_reference_format_golden_values(name, tmp_path):
+    """Same configs as the reference ship, same hashes, op counts and file sizes as its compiler."""
+    from cai_b200 import plan
+    ph, th, ops0, ops_last = GOLDEN[name]
+    r = run(BIN / "plan_compiler", ROOT / "configs" / f"{name}.cfg", tmp_path, "--quiet")
+    assert f"topology_hash={th}, plan_hash={ph}" in r.stdout
+    assert (tmp_path / "topology.bin").stat().st_size == 68
+    files = sorted(tmp_path.glob("plan.rank*.bin"))
+    p0 = plan.PlanFile(files[0])
+    assert p0.hdr.version == 1 and p0.hdr.num_ops == ops0
+    assert files[0].stat().st_size == 128 + 24 * p0.hdr.num_tensors + 16 * p0.hdr.num_groups + 32 * ops0
+    assert plan.PlanFile(files[1]).hdr.num_ops == ops_last
+    assert f"{p0.hdr.plan_hash:016x}" == ph
+
+
+def test_small_plan_file_is_byte_identical_to_reference_output(tmp_path):
+    import hashlib
+    run(BIN / "plan_compiler", ROOT / "configs" / "small.cfg", tmp_path, "--quiet", "--rank", "0")
+    digest = hashlib.sha256((tmp_path / "plan.rank000000.bin").read_bytes()).hexdigest()
+    assert digest == "100247a2a5cbd88bd4d49f4a343269761e23dd48792e5911ef707a7bbc46efc2"
+    tdig = hashlib.sha256((tmp_path / "topology.bin").read_bytes()).hexdigest()
+    assert tdig == "ca06c2d94267e216a20d448df206c0f30967df9b1f21159f8374d604b7178a9e"
+
+
+def test_simulated_step_matches_reference_numbers(tmp_path):
+    from cai_b200 import plan
+    run(BIN / "plan_compiler", ROOT / "configs" / "small.cfg", tmp_path, "--quiet")
+    sim = plan.Simulator(tmp_path / "plan.rank000000.bin", tmp_path / "topology.bin", max_steps=3)
+    s = sim.step()
+    assert abs(s.step_time_s * 1e3 - 98.13) < 0.05 and abs(s.mfu - 0.617) < 0.002
+    assert abs(s.bubble_ratio - 2 / 14) < 1e-9
+    assert s.stream_busy[5] == 0.0
+    sim.close()
+    r = run(BIN / "trainer", tmp_path / "plan.rank000000.bin", tmp_path / "topology.bin", "--steps", "2",
+            "--trace", tmp_path / "t.csv")
+    assert "avg MFU 61.7%" in r.stdout
+    lines = (tmp_path / "t.csv").read_text().splitlines()
+    assert lines[0] == "op_index,kind,stream,start_us,end_us,dur_us,bytes,flops" and len(lines) > 1000
+
+
+def test_topology_mismatch_is_refused(tmp_path):
+    from cai_b200 import plan
+    a, b = tmp_path / "a", tmp_path / "b"
+    run(BIN / "plan_compiler", ROOT / "configs" / "small.cfg", a, "--quiet", "--rank", "0")
+    run(BIN / "plan_compiler", ROOT / "configs" / "full220k.cfg", b, "--quiet", "--rank", "0")
+    with pytest.raises(plan.PlanError, match="topology"):
+        plan.Simulator(a / "plan.rank000000.bin", b / "topology.bin")
+    r = run(BIN / "trainer", a / "plan.rank000000.bin", b / "topology.bin", ok=False)
+    assert r.returncode == 1
+
+
+def test_linter_verify_recover_tools(tmp_path):
+    r = run(BIN / "topology_linter", ROOT / "configs" / "small.cfg")
+    assert "RESULT: all checks passed" in r.stdout
+    r = run(BIN / "plan_verify", ROOT / "configs" / "full220k.cfg")
+    assert "tile all 220032 ranks" in r.stdout and "RESULT: all checks passed" in r.stdout
+    r = run(BIN / "plan_verify", ROOT / "configs" / "b200_pp2tp4.cfg", "--exec")
+    assert "no unordered RAW/WAW/WAR pair" in r.stdout and "pair up in issue order" in r.stdout
+    # spare-rank recovery needs spares
+    r = run(BIN / "plan_recover", ROOT / "configs" / "small.cfg", 3, tmp_path, ok=False)
+    assert r.returncode == 1 and "no spare GPUs" in r.stderr
+    cfg = tmp_path / "spare.cfg"
+    cfg.write_text((ROOT / "configs" / "small.cfg").read_text().replace("num_racks     = 1", "num_racks = 2")
+                   .replace("spare_gpus    = 0", "spare_gpus = 12"))
+    r = run(BIN / "plan_recover", cfg, 3, tmp_path)
+    assert "different rack" in r.stdout and (tmp_path / "plan.recover.rank000003.bin").exists()
+    # the recovery plan is the plan of the failed rank, byte for byte
+    run(BIN / "plan_compiler", cfg, tmp_path / "all", "--quiet", "--rank", "3")
+    assert (tmp_path / "plan.recover.rank000003.bin").read_bytes() == (tmp_path / "all" / "plan.rank000003.bin").read_bytes()
+    # --dir mode checks files on disk
+    r = run(BIN / "plan_verify", cfg, "--dir", tmp_path / "all")
+    assert "carry the expected hashes" in r.stdout
+
+
+def test_checkpoint_resume_and_plan_hash_guard(tmp_path):
+    from cai_b200 import plan
+    run(BIN / "plan_compiler", ROOT / "configs" / "small.cfg", tmp_path, "--quiet", "--rank", "0")
+    pl, tp = tmp_path / "plan.rank000000.bin", tmp_path / "topology.bin"
+    ck = tmp_path / "ck"
+    run(BIN / "trainer", pl, tp, "--steps", "7", "--ckpt", ck)
+    assert (tmp_path / "ck.periodic.rank000000").exists() and (tmp_path / "ck.latest.rank000000").exists()
+    raw = (tmp_path / "ck.latest.rank000000").read_bytes()
+    assert int.from_bytes(raw[:4], "little") == 5 and raw[4:12] == bytes.fromhex("61eec02c9563ad48")[::-1]
+    r = run(BIN / "trainer", pl, tp, "--steps", "7", "--ckpt", ck)
+    assert "   5 |" in r.stdout and "   0 |" not in r.stdout   # resumed at step 5
+    # a checkpoint of another plan is refused
+    other = tmp_path / "o"
+    run(BIN / "plan_compiler", ROOT / "configs" / "b200_tp8.cfg", other, "--quiet", "--rank", "0")
+    sim = plan.Simulator(other / "plan.rank000000.bin", other / "topology.bin", checkpoint_path=ck)
+    assert sim.load_checkpoint(ck) != 0
+    sim.close()
+
+
+def test_describe_and_group_members():
+    from cai_b200 import plan
+    text = (ROOT / "configs" / "b200_pp2tp4.cfg").read_text()
+    d = plan.describe(text)
+    assert d["tp"] == 4 and d["pp"] == 2 and d["dp"] == 1 and d["world_size"] == 8
+    assert abs(d["bubble_ratio"] - 1 / 17) < 1e-6
+    assert plan.group_members(text, plan.GROUP_TP, 5) == [4, 5, 6, 7]
+    assert plan.group_members(text, plan.GROUP_PP, 5) == [1, 5]
+    with pytest.raises(plan.PlanError):
+        plan.describe("tp = 5\n")
+
+
+def test_executable_plan_structure(tmp_path):
+    from cai_b200 import plan
+    plan.compile_plans(ROOT / "configs" / "tiny.cfg", tmp_path, version=2)
+    p = plan.PlanFile(tmp_path / "plan.rank000000.bin")
+    assert p.hdr.version == 2 and p.xhdr.num_exec > 50
+    names = p.named_dict()
+    for n in ("embed", "L0.wqkv", "L1.wd", "gf", "@tokens", "@loss", "@flat_param"):
+        assert n in names
+    # every parameter sits at the same element offset in the weight and gradient buffers
+    for n, nt in names.items():
+        if nt.init_std < 0:
+            continue
+        w, g = p.tensors[nt.tensor], p.tensors[nt.grad]
+        base_w, base_g = p.tensors[names["@flat_param"].tensor].offset, p.tensors[names["@flat_grad"].tensor].offset
+        assert (w.offset - base_w) // 2 == (g.offset - base_g) // 4 == nt.flat_off512 * 512
+    assert all(t.offset + t.nbytes <= p.hdr.arena_bytes for t in p.tensors)
