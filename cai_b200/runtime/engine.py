@@ -193,7 +193,7 @@ class Engine:
         for g in groups:
             members = planlib.group_members(self.config_text, g.kind, self.rank)
             me = members.index(self.rank)
-            n_ids = 2 if g.kind == planlib.GROUP_PP else 1
+            n_ids = 2 if g.kind in (planlib.GROUP_PP, planlib.GROUP_TP) else 1
             key = f"cai/nccl/{self.hdr.plan_hash:x}/{g.kind}/{g.color}"
             if me == 0:
                 blob = b""

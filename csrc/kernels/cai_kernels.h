@@ -73,6 +73,17 @@ CAI_API int cai_embed_bwd(const int* tokens, const void* dout, float* dE, int T,
 CAI_API int cai_cross_entropy(void* logits, const int* targets, float* loss_sum, float* row_lse, int rows, int V,
                               long long ld, float grad_scale, float loss_scale, void* stream);
 
+/* Vocabulary-parallel cross-entropy in three steps; the caller max-reduces rowmax and sum-reduces
+ * rowsum over the tensor-parallel group in between. vocab_lo is the first vocabulary id of this
+ * rank's V columns; add_lse is 1 on exactly one rank of the group so that the summed losses are
+ * lse - logit[target]. */
+CAI_API int cai_ce_rowmax(const void* logits, float* rowmax, int rows, int V, long long ld, void* stream);
+CAI_API int cai_ce_rowsum(const void* logits, const float* rowmax, float* rowsum, int rows, int V, long long ld,
+                          void* stream);
+CAI_API int cai_ce_grad_tp(void* logits, const int* targets, const float* rowmax, const float* rowsum, float* loss_sum,
+                           int rows, int V, long long ld, int vocab_lo, int add_lse, float grad_scale, float loss_scale,
+                           void* stream);
+
 /* ---- AdamW on an fp32 master copy with bf16 write-back
  * (reference: src/refmodel.c:481-492, src/cuda/cai_kernels.cu:185-194).
  * p -= lr * (mhat / (sqrt(vhat) + eps) + wd * p); grad is multiplied by grad_scale first. */

@@ -351,6 +351,71 @@ cross_entropy_kernel(__nv_bfloat16* logits, const int* __restrict__ targets, flo
     }
 }
 
+// Vocabulary-parallel variant: every rank holds V_local columns of the logits. Row maxima and
+// exp-sums are reduced over the tensor-parallel group between the three kernels.
+__global__ void __launch_bounds__(kCeThreads)
+ce_rowmax_kernel(const __nv_bfloat16* __restrict__ logits, float* __restrict__ rowmax, int V, long long ld) {
+    __shared__ float red[33];
+    const long long row = blockIdx.x;
+    const uint4* l4 = reinterpret_cast<const uint4*>(logits + row * ld);
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < (V >> 3); i += kCeThreads) {
+        float f[8];
+        unpack8(l4[i], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) mx = fmaxf(mx, f[e]);
+    }
+    mx = block_max(mx, red);
+    if (threadIdx.x == 0) rowmax[row] = mx;
+}
+__global__ void __launch_bounds__(kCeThreads)
+ce_rowsum_kernel(const __nv_bfloat16* __restrict__ logits, const float* __restrict__ rowmax,
+                 float* __restrict__ rowsum, int V, long long ld) {
+    __shared__ float red[33];
+    const long long row = blockIdx.x;
+    const uint4* l4 = reinterpret_cast<const uint4*>(logits + row * ld);
+    const float mx = rowmax[row];
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < (V >> 3); i += kCeThreads) {
+        float f[8];
+        unpack8(l4[i], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum += __expf(f[e] - mx);
+    }
+    sum = block_sum(sum, red);
+    if (threadIdx.x == 0) rowsum[row] = sum;
+}
+__global__ void __launch_bounds__(kCeThreads)
+ce_grad_tp_kernel(__nv_bfloat16* logits, const int* __restrict__ targets, const float* __restrict__ rowmax,
+                  const float* __restrict__ rowsum, float* loss_sum, int V, long long ld, int vocab_lo,
+                  int add_lse, float grad_scale, float loss_scale) {
+    const long long row = blockIdx.x;
+    __nv_bfloat16* lr = logits + row * ld;
+    uint4* l4 = reinterpret_cast<uint4*>(lr);
+    const int tgt_global = targets[row];
+    const int tgt = tgt_global - vocab_lo;  // local column, may be out of range
+    const float lse = rowmax[row] + logf(rowsum[row]);
+    if (threadIdx.x == 0 && loss_sum && tgt_global >= 0) {
+        float contrib = add_lse ? lse : 0.f;
+        if (tgt >= 0 && tgt < V) contrib -= __bfloat162float(lr[tgt]);
+        atomicAdd(loss_sum, contrib * loss_scale);
+    }
+    __syncthreads();
+    const float gs = tgt_global >= 0 ? grad_scale : 0.f;
+    for (int i = threadIdx.x; i < (V >> 3); i += kCeThreads) {
+        float f[8];
+        unpack8(l4[i], f);
+        const int c0 = i * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float p = __expf(f[e] - lse);
+            if (c0 + e == tgt) p -= 1.f;
+            f[e] = p * gs;
+        }
+        l4[i] = pack8(f);
+    }
+}
+
 // ------------------------------------------------------------------ AdamW
 __global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
                              const float* __restrict__ grad, __nv_bfloat16* __restrict__ param, long long n,
@@ -546,6 +611,30 @@ CAI_API int cai_cross_entropy(void* logits, const int* targets, float* loss_sum,
     cross_entropy_kernel<<<rows, kCeThreads, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)logits, targets, loss_sum,
                                                                         row_lse, V, ld, grad_scale, loss_scale);
     CAI_LAUNCH_CHECK("cross_entropy");
+    return CAI_K_OK;
+}
+
+CAI_API int cai_ce_rowmax(const void* logits, float* rowmax, int rows, int V, long long ld, void* stream) {
+    if (rows <= 0) return CAI_K_OK;
+    ce_rowmax_kernel<<<rows, kCeThreads, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, rowmax, V, ld);
+    CAI_LAUNCH_CHECK("ce_rowmax");
+    return CAI_K_OK;
+}
+CAI_API int cai_ce_rowsum(const void* logits, const float* rowmax, float* rowsum, int rows, int V, long long ld,
+                          void* stream) {
+    if (rows <= 0) return CAI_K_OK;
+    ce_rowsum_kernel<<<rows, kCeThreads, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, rowmax, rowsum, V, ld);
+    CAI_LAUNCH_CHECK("ce_rowsum");
+    return CAI_K_OK;
+}
+CAI_API int cai_ce_grad_tp(void* logits, const int* targets, const float* rowmax, const float* rowsum, float* loss_sum,
+                           int rows, int V, long long ld, int vocab_lo, int add_lse, float grad_scale, float loss_scale,
+                           void* stream) {
+    if (rows <= 0) return CAI_K_OK;
+    ce_grad_tp_kernel<<<rows, kCeThreads, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)logits, targets, rowmax, rowsum,
+                                                                     loss_sum, V, ld, vocab_lo, add_lse, grad_scale,
+                                                                     loss_scale);
+    CAI_LAUNCH_CHECK("ce_grad_tp");
     return CAI_K_OK;
 }
 

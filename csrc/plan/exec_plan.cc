@@ -258,7 +258,7 @@ void exec_operands(const ExecOp& x, std::vector<int>* reads, std::vector<int>* w
         case K_ATTN_BWD: R(0); R(1); R(2); R(3); W(4); W(5); break;
         case K_SWIGLU_FWD: R(0); W(1); break;
         case K_SWIGLU_BWD: R(0); R(1); W(2); break;
-        case K_CROSS_ENTROPY: R(0); R(1); R(2); W(0); W(2); break;
+        case K_CROSS_ENTROPY: case K_CROSS_ENTROPY_TP: R(0); R(1); R(2); W(0); W(2); W(3); break;
         case K_ADAMW: R(0); R(1); R(2); R(3); W(0); W(1); W(2); W(4); break;
         case K_ZERO: W(0); break;
         case K_ADD: R(0); R(1); W(2); break;
@@ -382,6 +382,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     const uint32_t chunk = std::min<uint32_t>(cfg.train.ce_chunk ? cfg.train.ce_chunk : 1024, T);
     int logits = -1, hf = -1, hf_full = -1, rstdf = -1, xf = -1, dhf_full = -1;
     if (b.last_stage) logits = b.tensor(TC_WORKSPACE, DT_BF16, chunk, b.V_l);
+    const int ce_scratch = (b.last_stage && tp > 1) ? b.tensor(TC_WORKSPACE, DT_FP32, 2, chunk) : -1;
     if (b.last_stage && tp > 1) dhf_full = dfull;
 
     // ---------------- activations: one set per in-flight microbatch
@@ -525,10 +526,10 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
                 const int tg = b.tensor_at(TC_COMM, DT_INT32,
                                            out->tensors[targets].offset + (static_cast<uint64_t>(mb) * T + r0) * 4, 1,
                                            rows, rows);
-                e.t[0] = lg; e.t[1] = tg; e.t[2] = loss_acc;
-                e.i[0] = rows; e.i[1] = b.V_l; e.i[2] = b.tp_id * b.V_l; e.i[3] = GROUP_TP;
+                e.t[0] = lg; e.t[1] = tg; e.t[2] = loss_acc; e.t[3] = ce_scratch;
+                e.i[0] = rows; e.i[1] = b.V_l; e.i[2] = b.tp_id * b.V_l; e.i[3] = GROUP_TP; e.i[4] = b.tp_id == 0;
                 e.f[0] = static_cast<float>(grad_scale);
-                e.f[1] = static_cast<float>(grad_scale);
+                e.f[1] = static_cast<float>(grad_scale / d.dp);  // reported loss is the mean over the global batch
                 b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 5.0 * rows * b.V_l, 0, 0, mb, &e);
                 const int dh_c = b.view(dh_rows, r0, rows);
                 b.gemm(ST_COMPUTE_HI, lg, head.w, dh_c, -1, rows, H, b.V_l, false, true, 0, mb);
@@ -635,9 +636,16 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             b.nccl(K_NCCL_ALL_REDUCE, OP_ALL_REDUCE, ST_COMM_TP, nt.grad, nt.grad, static_cast<uint64_t>(nt.rows) * nt.cols,
                    DT_FP32, GROUP_TP, -1, 0);
         }
+        // each rank accumulated the loss terms of its vocabulary slice
+        if (b.last_stage) b.nccl(K_NCCL_ALL_REDUCE, OP_ALL_REDUCE, ST_COMM_TP, loss_acc, loss_acc, 8, DT_FP32, GROUP_TP, -1, 0);
         b.sync(ST_COMM_TP, ST_COMPUTE_HI, 0);
     }
     // optimizer
+    if (d.dp > 1 && b.last_stage) {
+        b.sync(ST_COMPUTE_HI, ST_COMM_DP, 0);
+        b.nccl(K_NCCL_ALL_REDUCE, OP_ALL_REDUCE, ST_COMM_DP, loss_acc, loss_acc, 8, DT_FP32, GROUP_DP, -1, 0);
+        b.sync(ST_COMM_DP, ST_COMPUTE_HI, 0);
+    }
     if (d.dp > 1) {
         if (b.fused) {
             ExecOp e = xop(K_RS_ADAMW);

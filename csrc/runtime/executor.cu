@@ -190,6 +190,27 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
         case K_CROSS_ENTROPY:
             return cai_cross_entropy(P(0), (const int*)P(1), (float*)P(2), nullptr, x.i[0], x.i[1], ex->ld(x.t[0]), x.f[0],
                                      x.f[1], st);
+        case K_CROSS_ENTROPY_TP: {
+            // vocabulary-parallel: row max and exp-sum are reduced over the TP group in stream order,
+            // on the group's second communicator (the first one belongs to the comm_tp stream)
+            const Comm& c = ex->comms[GROUP_TP];
+            void* comm = c.comm2 ? c.comm2 : c.comm;
+            if (!comm) {
+                set_last_error("vocabulary-parallel cross-entropy needs the TP communicator");
+                return CAI_K_BAD_ARG;
+            }
+            float* rowmax = (float*)P(3);
+            float* rowsum = rowmax + ex->shapes[static_cast<size_t>(x.t[3]) * 4 + 2];
+            const int rows = x.i[0], V = x.i[1];
+            int rc = cai_ce_rowmax(P(0), rowmax, rows, V, ex->ld(x.t[0]), st);
+            if (rc) return rc;
+            if (g_nccl.AllReduce(rowmax, rowmax, rows, 7, 2 /* max */, comm, st) != 0) return CAI_K_CUDA;
+            rc = cai_ce_rowsum(P(0), rowmax, rowsum, rows, V, ex->ld(x.t[0]), st);
+            if (rc) return rc;
+            if (g_nccl.AllReduce(rowsum, rowsum, rows, 7, 0 /* sum */, comm, st) != 0) return CAI_K_CUDA;
+            return cai_ce_grad_tp(P(0), (const int*)P(1), rowmax, rowsum, (float*)P(2), rows, V, ex->ld(x.t[0]), x.i[2],
+                                  x.i[4], x.f[0], x.f[1], st);
+        }
         case K_ADAMW: {
             const long long n = (static_cast<long long>(static_cast<uint32_t>(x.i[1])) << 32) | static_cast<uint32_t>(x.i[0]);
             const unsigned blocks = static_cast<unsigned>(((n + 3) / 4 + 255) / 256);
@@ -266,7 +287,7 @@ int replay(cai_exec* ex) {
         {
             // kernels of this library behind the op (memsets and NCCL calls are not ours)
             const uint16_t k = ex->exec[op.exec - 1].kernel;
-            ex->launches += k == K_ATTN_BWD ? 3 : k == K_RMSNORM_BWD ? 2 : (k == K_ZERO || (k >= K_NCCL_ALL_REDUCE && k <= K_NCCL_RECV)) ? 0 : 1;
+            ex->launches += (k == K_ATTN_BWD || k == K_CROSS_ENTROPY_TP) ? 3 : k == K_RMSNORM_BWD ? 2 : (k == K_ZERO || (k >= K_NCCL_ALL_REDUCE && k <= K_NCCL_RECV)) ? 0 : 1;
         }
         if (tr) cudaEventRecord(tr->stop, st);
     }

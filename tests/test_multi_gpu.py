@@ -1,0 +1,84 @@
+"""Multi-GPU tests: the same tiny model trained under different parallel layouts must give the same
+loss curve. Each case runs as child processes under torch.distributed.run; cases that need more
+GPUs than the box has are skipped."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+_port = [29610]
+
+
+def _gpus():
+    import torch
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def run_case(tmp_path, nproc, **kw):
+    out = tmp_path / f"loss_{'_'.join(f'{k}{v}' for k, v in kw.items())}_n{nproc}.json"
+    _port[0] += 1
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_port[0]), str(ROOT / "tests" / "mp_train_worker.py"),
+           "--out", str(out)]
+    for k, v in kw.items():
+        cmd += [f"--{k}", str(v)]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert r.returncode == 0, (r.stdout[-3000:], r.stderr[-3000:])
+    return json.loads(out.read_text())
+
+
+def close(a, b, tol=0.02):
+    assert len(a) == len(b)
+    for x, y in zip(a, b):
+        assert abs(x - y) <= tol * max(1.0, abs(y)), (a, b)
+
+
+@pytest.fixture(scope="module")
+def single(tmp_path_factory):
+    return run_case(tmp_path_factory.mktemp("single"), 1)
+
+
+@pytest.mark.parametrize("comm", ["baseline", "fused"])
+def test_tensor_parallel_2_matches_single_gpu(tmp_path, single, comm):
+    if _gpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    r = run_case(tmp_path, 2, tp=2, comm=comm)
+    close(r["losses"], single["losses"])
+    assert r["losses"][-1] < r["losses"][0]
+
+
+def test_data_parallel_2_baseline_and_fused_agree(tmp_path):
+    if _gpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    a = run_case(tmp_path, 2, comm="baseline")
+    b = run_case(tmp_path, 2, comm="fused")
+    close(a["losses"], b["losses"], tol=0.01)
+    assert a["dp"] == 2 and a["losses"][-1] < a["losses"][0]
+
+
+def test_pipeline_parallel_2_matches_single_gpu(tmp_path, single):
+    if _gpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    r = run_case(tmp_path, 2, pp=2)
+    close(r["losses"], single["losses"])
+
+
+@pytest.mark.parametrize("comm", ["baseline", "fused"])
+def test_tensor_parallel_4(tmp_path, single, comm):
+    if _gpus() < 4:
+        pytest.skip("needs 4 GPUs")
+    r = run_case(tmp_path, 4, tp=4, comm=comm)
+    close(r["losses"], single["losses"])
+
+
+def test_tp2_pp2_cuda_graph(tmp_path, single):
+    if _gpus() < 4:
+        pytest.skip("needs 4 GPUs")
+    r = run_case(tmp_path, 4, tp=2, pp=2, comm="baseline", graph=1)
+    close(r["losses"], single["losses"])
