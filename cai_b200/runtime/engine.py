@@ -52,8 +52,6 @@ def _declare_runtime(L):
     L.cai_exec_trace_read.argtypes = [P, ctypes.POINTER(TraceRec), I]
     L.cai_exec_set_sm_limit.argtypes = [P, I]
     L.cai_exec_set_sm_limit.restype = None
-    if hasattr(L, "cai_fused_attach"):
-        L.cai_fused_attach.argtypes = [P, I, I, I, ctypes.POINTER(P), ctypes.POINTER(P), P, c_longlong, c_longlong]
     L._cai_rt_declared = True
 
 
@@ -126,6 +124,7 @@ class Engine:
         self.arena = torch.empty(int(self.hdr.arena_bytes) + 1024, dtype=torch.uint8, device=self.device)
         base = (self.arena.data_ptr() + 1023) & ~1023
         self._arena_shift = base - self.arena.data_ptr()
+        self.arena_base = base
         self.arena.zero_()
         self.ex = c_void_p()
         # The six streams come from torch's pool: tensors touched on them stay valid for torch's
@@ -207,14 +206,13 @@ class Engine:
             id1 = ctypes.create_string_buffer(blob[:128], 128)
             id2 = ctypes.create_string_buffer(blob[128:256], 128) if n_ids == 2 else None
             klib.check(self.L.cai_exec_init_comm(self.ex, libpath, g.kind, id1, id2, len(members), me), "init_comm")
-        self._attach_fused(groups)
-
-    def _attach_fused(self, groups):
-        """Give the fused compute+collective kernels their symmetric buffers (see parallel.symm)."""
-        if not self.train.comm_mode or not hasattr(self.L, "cai_fused_attach"):
-            return
-        from ..parallel import symm
-        self.symm = symm.attach(self, groups)
+        self.peers = None
+        if self.train.comm_mode:
+            # fused compute+collective kernels address the other members' arenas directly
+            from ..parallel import peers
+            self.peers = peers.attach(self, groups, store)
+            torch.cuda.synchronize(self.device)
+            dist.barrier(device_ids=[self.local_rank])
 
     # ------------------------------------------------------------------ parameters
     def _global_shape_and_slice(self, name, rows, cols):
@@ -250,8 +248,9 @@ class Engine:
         n_opt = int(self.plan.xhdr.opt_elems)
         master = self.view("@flat_master")
         dp, dp_id = self.hdr.dp, self.rank // (self.hdr.tp * self.hdr.num_stages * self.hdr.cp)
-        shard_lo = dp_id * n_opt if dp > 1 else 0
-        shard_hi = min(shard_lo + n_opt, n_flat) if dp > 1 else n_flat
+        sharded = dp > 1 and n_opt < n_flat   # optimizer state split over the data-parallel group
+        shard_lo = dp_id * n_opt if sharded else 0
+        shard_hi = min(shard_lo + n_opt, n_flat) if sharded else n_flat
         with torch.cuda.stream(self.stream):
             self.view("@flat_m").zero_()
             self.view("@flat_v").zero_()
@@ -331,6 +330,104 @@ class Engine:
         self.L.cai_exec_trace_enable(self.ex, 0)
         return [buf[i] for i in range(n)]
 
+    # ------------------------------------------------------------------ checkpoint / resume
+    # File layout (per rank): "<path>.<tag>.rank%06u" plus a rolling "<path>.latest.rank%06u". The
+    # first 12 bytes are the reference's (u32 step, u64 plan_hash; src/runtime.c:244-262); a section
+    # table follows with this rank's resident state: bf16 parameters, fp32 master / m / v shard,
+    # step counter. The snapshot is copied device->host on the io stream into pinned buffers and the
+    # file is written (temporary name + rename) by a background thread, so saving overlaps training.
+    def save_checkpoint(self, path, tag="periodic", wait=False):
+        import threading
+        sections = {"param": self.view("@flat_param"), "master": self.view("@flat_master"),
+                    "m": self.view("@flat_m"), "v": self.view("@flat_v")}
+        io = self.streams[5]
+        io.wait_stream(self.stream)
+        host = {}
+        with torch.cuda.stream(io):
+            for k, t in sections.items():
+                buf = self._ckpt_pinned.get(k) if hasattr(self, "_ckpt_pinned") else None
+                if buf is None or buf.numel() != t.numel() or buf.dtype != t.dtype:
+                    buf = torch.empty(t.shape, dtype=t.dtype).pin_memory()
+                buf.copy_(t, non_blocking=True)
+                host[k] = buf
+        self._ckpt_pinned = host
+        done = torch.cuda.Event()
+        done.record(io)
+        self.stream.wait_event(done)  # the next optimizer update must not overtake the snapshot
+        step, ph, rank = self.step_count, int(self.hdr.plan_hash), self.rank
+        prev = getattr(self, "_ckpt_thread", None)
+        if prev is not None:
+            prev.join()
+
+        def write():
+            done.synchronize()
+            import numpy as np
+            meta = np.array([step], dtype=np.int64)
+            names = list(host) + ["meta"]
+            arrs = [host[k].view(torch.uint8).numpy() if host[k].dtype != torch.bfloat16
+                    else host[k].view(torch.int16).numpy().view(np.uint8) for k in host] + [meta.view(np.uint8)]
+            n = len(names)
+            c_names = (ctypes.c_char_p * n)(*[x.encode() for x in names])
+            c_data = (c_void_p * n)(*[c_void_p(a.ctypes.data) for a in arrs])
+            c_len = (ctypes.c_uint64 * n)(*[a.nbytes for a in arrs])
+            rc = planlib.lib().cai_ckpt_write(str(path).encode(), tag.encode(), rank, step, ph, n, c_names, c_data, c_len)
+            self._ckpt_rc = rc
+
+        self._ckpt_rc = 0
+        th = threading.Thread(target=write, daemon=True)
+        th.start()
+        self._ckpt_thread = th
+        if wait:
+            th.join()
+            if self._ckpt_rc != 0:
+                raise IOError(f"checkpoint write failed ({self._ckpt_rc}) for {path}")
+
+    def wait_checkpoint(self):
+        th = getattr(self, "_ckpt_thread", None)
+        if th is not None:
+            th.join()
+            self._ckpt_thread = None
+        return getattr(self, "_ckpt_rc", 0)
+
+    def load_checkpoint(self, path) -> bool:
+        """Resume from "<path>.latest.rank..." (or the literal path). Returns False when there is
+        nothing to resume from; raises when the checkpoint belongs to another plan."""
+        import numpy as np
+        L = planlib.lib()
+        step, ph, nsec = ctypes.c_uint32(0), ctypes.c_uint64(0), ctypes.c_uint32(0)
+        resolved = ctypes.create_string_buffer(1024)
+        rc = L.cai_ckpt_probe(str(path).encode(), self.rank, ctypes.byref(step), ctypes.byref(ph), ctypes.byref(nsec),
+                              resolved, len(resolved))
+        if rc == 1:
+            return False
+        if rc != 0:
+            raise IOError(f"cannot read checkpoint {path}")
+        if ph.value != self.hdr.plan_hash:
+            raise planlib.PlanError(f"checkpoint {resolved.value.decode()} belongs to plan {ph.value:016x}, "
+                                    f"this plan is {int(self.hdr.plan_hash):016x}")
+        targets = {"param": self.view("@flat_param"), "master": self.view("@flat_master"), "m": self.view("@flat_m"),
+                   "v": self.view("@flat_v")}
+        for i in range(nsec.value):
+            name = ctypes.create_string_buffer(16)
+            nbytes = ctypes.c_uint64(0)
+            L.cai_ckpt_section(resolved.value, i, name, ctypes.byref(nbytes), None, 0)
+            buf = np.empty(nbytes.value, dtype=np.uint8)
+            rc = L.cai_ckpt_section(resolved.value, i, name, ctypes.byref(nbytes), c_void_p(buf.ctypes.data), buf.nbytes)
+            if rc != 0:
+                raise IOError(f"checkpoint section {i} unreadable")
+            key = name.value.decode()
+            if key == "meta":
+                self.step_count = int(buf.view(np.int64)[0])
+            elif key in targets:
+                t = targets[key]
+                src = torch.from_numpy(buf)
+                if src.numel() != t.numel() * t.element_size():
+                    raise planlib.PlanError(f"checkpoint section {key} has the wrong size")
+                with torch.cuda.stream(self.stream):
+                    t.view(torch.uint8).view(-1).copy_(src.to(self.device))
+        self.synchronize()
+        return True
+
     # ------------------------------------------------------------------ metrics
     def tokens_per_step(self) -> int:
         return int(self.hdr.global_tokens_per_step)
@@ -341,9 +438,20 @@ class Engine:
         return useful / (peak * step_time_s) if step_time_s > 0 else 0.0
 
     def close(self):
+        self.wait_checkpoint()
+        if getattr(self, "ex", None) and getattr(self, "peers", None) and self.dist is not None and self.dist.is_initialized():
+            # nobody may unmap or free an arena while a peer's kernel can still touch it
+            torch.cuda.synchronize(self.device)
+            try:
+                self.dist.barrier(device_ids=[self.local_rank])
+            except Exception:
+                pass
         if getattr(self, "ex", None):
             self.L.cai_exec_destroy(self.ex)
             self.ex = None
+        if getattr(self, "peers", None):
+            self.peers.close()
+            self.peers = None
         if self._tmp is not None:
             self._tmp.cleanup()
             self._tmp = None

@@ -1,0 +1,26 @@
+// fused.h - host-side launchers of the fused compute+collective kernels (internal to
+// libcai_kernels.so; the executor calls them when it meets the fused op kinds of a plan).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace cai {
+struct PeerTable;
+}
+
+// Gradient reduce-scatter + scale + sharded AdamW + parameter all-gather, one kernel (rs_adamw.cu).
+int cai_fused_rs_adamw(const cai::PeerTable& pt, unsigned long long grad_off, unsigned long long param_off, float* master,
+                       float* m, float* v, long long n_flat, long long n_shard, const float* hyper, float gscale,
+                       uint32_t seq, unsigned int* done_counter, cudaStream_t st);
+
+// All-gather of a row-sharded activation fused into the GEMM that consumes it (gemm_tcgen05.cu).
+int cai_fused_ag_gemm(const cai::PeerTable& pt, int group_kind, unsigned long long src_off, long long ld_src, void* a_full,
+                      const void* B, void* C, int T, int N, int K, long long ldb, long long ldc, int b_mn,
+                      int rows_per_rank, const uint32_t* epoch_base, uint32_t seq, int n_copy, cudaStream_t st);
+
+// GEMM whose epilogue reduce-scatters the product over the group and adds a residual (gemm_tcgen05.cu).
+int cai_fused_gemm_rs(const cai::PeerTable& pt, int group_kind, const void* A, const void* B, unsigned long long stage_off,
+                      void* out_local, const void* residual, int T, int N, int K, long long lda, long long ldb,
+                      long long ldo, long long ldr, int b_mn, int rows_per_rank, const uint32_t* epoch_base, uint32_t seq,
+                      cudaStream_t st);

@@ -15,6 +15,9 @@
 // Replaces the one-thread-per-output fp32 GEMMs of the reference
 // (src/cuda/cai_gpu_train.cu:40-74) and folds its add_k / zero_k passes
 // (src/cuda/cai_kernels.cu:161-164, cai_gpu_train.cu:75-78) into the epilogue.
+#include "../comm/fused.h"
+#include "../comm/peer.cuh"
+#include "../plan/formats.h"
 #include "cai_kernels.h"
 #include "host_common.h"
 #include "sm100.cuh"
@@ -37,7 +40,22 @@ struct GemmParams {
     long long ldc, ldr;
     int tiles_m, tiles_n, group_m;
     int* status;
+    // ---- fused collective modes (see the block comment above gemm_bf16_kernel)
+    int mode;                        // kGemmPlain / kGemmAllGatherA / kGemmReduceScatter
+    int group_kind;                  // communicator kind whose signal region is used
+    int n_copy;                      // all-gather: leading CTAs that only move rows
+    int rows_per_rank;               // rows of the sharded dimension each member owns
+    int m_rot;                       // tile rows are walked starting from this block
+    const uint32_t* epoch_base;      // device word refreshed by the host every step
+    uint32_t seq;                    // per-op sequence number (fixed in the plan)
+    unsigned long long src_off;      // all-gather: arena offset of the local rows on every member
+    unsigned long long stage_off;    // reduce-scatter: arena offset of the staging buffer on every member
+    __nv_bfloat16* a_full;           // all-gather: local buffer that receives every member's rows
+    long long ld_src;
+    PeerTable pt;
 };
+
+constexpr int kGemmPlain = 0, kGemmAllGatherA = 1, kGemmReduceScatter = 2;
 
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
     const int per_group = p.group_m * p.tiles_n;
@@ -47,6 +65,57 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
     const int in = tile - g * per_group;
     tm = first_m + in % gsz;
     tn = in / gsz;
+    if (p.m_rot) {
+        tm += p.m_rot;
+        if (tm >= p.tiles_m) tm -= p.tiles_m;
+    }
+}
+
+__device__ __forceinline__ void bar_sync_epilogue() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+
+// All-gather staging, run by the leading CTAs of the grid: pull every member's rows (peer loads
+// over NVLink, 128 rows at a time) into the local gathered buffer and publish one local flag per
+// 128-row block, which the TMA producers of the compute CTAs wait on.
+__device__ __forceinline__ void allgather_copy_role(const GemmParams& p, uint32_t epoch) {
+    __shared__ int ok_s;
+    const int blocks_per_rank = p.rows_per_rank / kBM;
+    const int units = p.pt.size * blocks_per_rank;
+    const size_t row_bytes = static_cast<size_t>(p.K) * 2;
+    for (int u = blockIdx.x; u < units; u += p.n_copy) {
+        // own rows first, then the peers in ring order, so early tiles never wait on NVLink
+        const int s = (p.pt.rank + u / blocks_per_rank) % p.pt.size;
+        const int j = u % blocks_per_rank;
+        if (threadIdx.x == 0)
+            ok_s = wait_flag_ge(sig_word(p.pt, p.pt.rank, p.group_kind, kSigEntry + s), epoch, p.status) ? 1 : 0;
+        __syncthreads();
+        if (!ok_s) return;
+        const uint8_t* src = p.pt.base[s] + p.src_off + static_cast<size_t>(j) * kBM * p.ld_src * 2;
+        uint8_t* dst = reinterpret_cast<uint8_t*>(p.a_full) + (static_cast<size_t>(s) * p.rows_per_rank + j * kBM) * row_bytes;
+        const int vec_per_row = static_cast<int>(row_bytes >> 4);
+        const int total = kBM * vec_per_row;
+        for (int v0 = threadIdx.x; v0 < total; v0 += kGemmThreads * 8) {
+            uint4 tmp[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int v = v0 + e * kGemmThreads;
+                if (v < total) {
+                    const int r = v / vec_per_row, c = v - r * vec_per_row;
+                    tmp[e] = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * p.ld_src * 2 + c * 16);
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int v = v0 + e * kGemmThreads;
+                if (v < total) *reinterpret_cast<uint4*>(dst + static_cast<size_t>(v) * 16) = tmp[e];
+            }
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t* flag = sig_word(p.pt, p.pt.rank, p.group_kind, kSigLocal + s * blocks_per_rank + j);
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+        }
+    }
 }
 
 template <int BN, int STAGES>
@@ -71,6 +140,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+
+    // Fused modes. kGemmAllGatherA: A is the row-wise concatenation of every member's local rows;
+    // the first n_copy CTAs pull them into a_full and the TMA producers wait per 128-row block.
+    // kGemmReduceScatter: the epilogue pushes each bf16 tile into the staging buffer of the member
+    // that owns those rows (peer stores) and raises a per-tile flag there; when a CTA has no GEMM
+    // tiles left it sums, for output tiles of its own rows, the partials of all members (+ residual).
+    uint32_t epoch = 0;
+    if (p.mode != kGemmPlain) {
+        epoch = *p.epoch_base + 2 * p.seq;
+        if (p.mode == kGemmAllGatherA) {
+            if (blockIdx.x == 0 && threadIdx.x == 0) signal_all(p.pt, p.group_kind, kSigEntry + p.pt.rank, epoch);
+            if (static_cast<int>(blockIdx.x) < p.n_copy) {
+                allgather_copy_role(p, epoch);
+                return;
+            }
+        }
+    }
+    const int cta = static_cast<int>(blockIdx.x) - p.n_copy;
+    const int ncta = static_cast<int>(gridDim.x) - p.n_copy;
 
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmA);
@@ -104,10 +192,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
                 int tm, tn;
                 tile_coords(p, tile, tm, tn);
                 const int m0 = tm * kBM, n0 = tn * BN;
+                if (p.mode == kGemmAllGatherA) {
+                    // rows of this tile must have been staged by a copy CTA; they were written through
+                    // the generic proxy, the TMA engine reads through the async proxy
+                    const uint32_t* flag = sig_word(p.pt, p.pt.rank, p.group_kind, kSigLocal + tm);
+                    bool seen = false;
+                    for (uint32_t it = 0; it < kSpinLimit && !seen; ++it) {
+                        uint32_t v;
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+                        seen = static_cast<int32_t>(v - epoch) >= 0;
+                        if (!seen && it > 32) __nanosleep(100);
+                    }
+                    if (!seen) {
+                        *abort_flag = 1;
+                        atomicCAS(p.status, 0, CAI_DEV_TIMEOUT_PEER_FLAG);
+                        ok = false;
+                        break;
+                    }
+                    fence_proxy_async_all();
+                }
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, CAI_DEV_TIMEOUT_TMA_EMPTY)) {
                         ok = false;
@@ -150,7 +257,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             uint32_t ph = 0;
             bool ok = true;
             int t = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+            for (int tile = cta; tile < num_tiles && ok; tile += ncta, ++t) {
                 const int acc = t & 1;
                 const uint32_t acc_ph = (t >> 1) & 1;
                 if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag, p.status, CAI_DEV_TIMEOUT_TMEM_EMPTY)) {
@@ -191,7 +298,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         int t = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+        for (int tile = cta; tile < num_tiles && ok; tile += ncta, ++t) {
             int tm, tn;
             tile_coords(p, tile, tm, tn);
             const int acc = t & 1;
@@ -212,7 +319,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const int col0 = tn * BN + c * 32;
                 if (!row_ok || col0 >= p.N) continue;
                 const float alpha = p.alpha;
-                if (p.epi == CAI_EPI_BF16 || p.epi == CAI_EPI_BF16_RESIDUAL) {
+                if (p.mode == kGemmReduceScatter) {
+                    const int owner = static_cast<int>(row / p.rows_per_rank);
+                    const long long lrow = row - static_cast<long long>(owner) * p.rows_per_rank;
+                    __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.pt.base[owner] + p.stage_off) +
+                                          (static_cast<long long>(p.pt.rank) * p.rows_per_rank + lrow) * p.N + col0;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (col0 + j * 8 >= p.N) break;
+                        uint4 o;
+                        o.x = pack_bf16(__uint_as_float(r[j * 8 + 0]) * alpha, __uint_as_float(r[j * 8 + 1]) * alpha);
+                        o.y = pack_bf16(__uint_as_float(r[j * 8 + 2]) * alpha, __uint_as_float(r[j * 8 + 3]) * alpha);
+                        o.z = pack_bf16(__uint_as_float(r[j * 8 + 4]) * alpha, __uint_as_float(r[j * 8 + 5]) * alpha);
+                        o.w = pack_bf16(__uint_as_float(r[j * 8 + 6]) * alpha, __uint_as_float(r[j * 8 + 7]) * alpha);
+                        *reinterpret_cast<uint4*>(drow + j * 8) = o;
+                    }
+                } else if (p.epi == CAI_EPI_BF16 || p.epi == CAI_EPI_BF16_RESIDUAL) {
                     __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
                     const __nv_bfloat16* rrow =
                         p.epi == CAI_EPI_BF16_RESIDUAL
@@ -260,6 +382,62 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+            if (p.mode == kGemmReduceScatter) {
+                // every row of the tile is on its way to the owner: order the peer stores of all
+                // four epilogue warps before the flag that announces the tile
+                __threadfence_system();
+                bar_sync_epilogue();
+                if (warp == 2 && lane == 0) {
+                    const int blocks_per_rank = p.rows_per_rank / kBM;
+                    const int owner = tm / blocks_per_rank;
+                    const uint32_t slot = static_cast<uint32_t>((tm - owner * blocks_per_rank) * p.tiles_n + tn);
+                    st_release_sys(sig_word(p.pt, owner, p.group_kind, kSigTile + p.pt.rank * kSigTileSlots + slot), epoch);
+                }
+            }
+        }
+    }
+
+    if (p.mode == kGemmReduceScatter) {
+        // ---------------- reduce phase: sum the partials of all members for tiles of my rows
+        __shared__ int red_ok;
+        __syncthreads();
+        const int blocks_per_rank = p.rows_per_rank / kBM;
+        const int items = blocks_per_rank * p.tiles_n;
+        const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.pt.base[p.pt.rank] + p.stage_off);
+        for (int item = cta; item < items; item += ncta) {
+            if (threadIdx.x == 0) {
+                int good = 1;
+                for (int src = 0; src < p.pt.size && good; ++src)
+                    good = wait_flag_ge(sig_word(p.pt, p.pt.rank, p.group_kind, kSigTile + src * kSigTileSlots + item), epoch,
+                                        p.status) ? 1 : 0;
+                red_ok = good;
+            }
+            __syncthreads();
+            if (!red_ok) break;
+            const int mb = item / p.tiles_n, tn = item - mb * p.tiles_n;
+            const int vec_cols = BN / 8;
+            for (int u = threadIdx.x; u < kBM * vec_cols; u += kGemmThreads) {
+                const int rr = u / vec_cols, cc = (u - rr * vec_cols) * 8;
+                const long long lrow = static_cast<long long>(mb) * kBM + rr;
+                const int col = tn * BN + cc;
+                if (lrow >= p.rows_per_rank || col >= p.N) continue;
+                float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (int src = 0; src < p.pt.size; ++src) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage + (static_cast<long long>(src) * p.rows_per_rank + lrow) * p.N + col);
+                    acc8[0] += bf16_lo(v.x); acc8[1] += bf16_hi(v.x); acc8[2] += bf16_lo(v.y); acc8[3] += bf16_hi(v.y);
+                    acc8[4] += bf16_lo(v.z); acc8[5] += bf16_hi(v.z); acc8[6] += bf16_lo(v.w); acc8[7] += bf16_hi(v.w);
+                }
+                if (p.R) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.R) + lrow * p.ldr + col);
+                    acc8[0] += bf16_lo(v.x); acc8[1] += bf16_hi(v.x); acc8[2] += bf16_lo(v.y); acc8[3] += bf16_hi(v.y);
+                    acc8[4] += bf16_lo(v.z); acc8[5] += bf16_hi(v.z); acc8[6] += bf16_lo(v.w); acc8[7] += bf16_hi(v.w);
+                }
+                uint4 o;
+                o.x = pack_bf16(acc8[0], acc8[1]); o.y = pack_bf16(acc8[2], acc8[3]);
+                o.z = pack_bf16(acc8[4], acc8[5]); o.w = pack_bf16(acc8[6], acc8[7]);
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + lrow * p.ldc + col) = o;
+            }
+            __syncthreads();
         }
     }
 
@@ -289,7 +467,13 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
     p.tiles_n = (p.N + BN - 1) / BN;
     p.group_m = 8;
     const int tiles = p.tiles_m * p.tiles_n;
-    const int grid = tiles < sms ? tiles : sms;
+    int grid = tiles < sms - p.n_copy ? tiles : sms - p.n_copy;
+    if (grid < 1) grid = 1;
+    grid += p.n_copy;
+    if (p.mode == kGemmReduceScatter && (p.rows_per_rank / kBM) * p.tiles_n > static_cast<int>(kSigTileSlots)) {
+        set_last_error("gemm_rs: too many tiles per member for the signal block");
+        return CAI_K_BAD_ARG;
+    }
     gemm_bf16_kernel<BN, STAGES><<<grid, kGemmThreads, smem_bytes, stream>>>(tmA, tmB, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
@@ -297,6 +481,44 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
         return CAI_K_CUDA;
     }
     return CAI_K_OK;
+}
+
+// Picks the tile width, encodes the tensor maps and launches. `p` carries everything but the
+// tile bookkeeping.
+static int gemm_dispatch(const void* A, const void* B, long long lda, long long ldb, GemmParams& p, int sm_limit,
+                         cudaStream_t st) {
+    const int M = p.M, N = p.N, K = p.K;
+    const int dev = current_device();
+    int sms = sm_count(dev);
+    if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
+    const int usable = sms - p.n_copy > 0 ? sms - p.n_copy : 1;
+    // Tile width: fewer, wider tiles amortise the A operand better; narrower tiles quantise
+    // into waves better when the output is small.
+    auto cost = [&](int bn) {
+        const long long tiles = (long long)((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
+        const long long waves = (tiles + usable - 1) / usable;
+        return (double)waves * bn * (bn == 128 ? 1.06 : 1.0);
+    };
+    const int BN = cost(256) <= cost(128) ? 256 : 128;
+    CUtensorMap tmA, tmB;
+    bool ok;
+    if (!p.a_mn) ok = encode_tmap_2d(&tmA, A, M, K, lda, kBK, kBM, 2);
+    else ok = encode_tmap_2d(&tmA, A, K, M, lda, 64, kBK, 2);
+    if (!ok) return CAI_K_BAD_ARG;
+    if (!p.b_mn) ok = encode_tmap_2d(&tmB, B, N, K, ldb, kBK, BN, 2);
+    else ok = encode_tmap_2d(&tmB, B, K, N, ldb, 64, kBK, 2);
+    if (!ok) return CAI_K_BAD_ARG;
+    p.status = status_words(dev);
+    if (BN == 256) return launch_gemm<256, 4>(tmA, tmB, p, sms, st);
+    return launch_gemm<128, 6>(tmA, tmB, p, sms, st);
+}
+
+static void plain_params(GemmParams& p) {
+    p.mode = kGemmPlain;
+    p.group_kind = 0; p.n_copy = 0; p.rows_per_rank = 0; p.m_rot = 0;
+    p.epoch_base = nullptr; p.seq = 0; p.src_off = 0; p.stage_off = 0; p.a_full = nullptr; p.ld_src = 0;
+    p.pt = PeerTable{};
+    p.R = nullptr; p.ldr = 0; p.alpha = 1.f; p.epi = CAI_EPI_BF16; p.a_mn = 0;
 }
 
 }  // namespace cai
@@ -320,29 +542,8 @@ CAI_API int cai_gemm_bf16(const void* A, const void* B, void* C, const void* R, 
         set_last_error("gemm: residual epilogue needs R with ldr %% 8 == 0");
         return CAI_K_BAD_ARG;
     }
-    const int dev = current_device();
-    int sms = sm_count(dev);
-    if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
-
-    // Tile width: fewer, wider tiles amortise the A operand better; narrower tiles quantise
-    // into waves better when the output is small.
-    auto cost = [&](int bn) {
-        const long long tiles = (long long)((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
-        const long long waves = (tiles + sms - 1) / sms;
-        return (double)waves * bn * (bn == 128 ? 1.06 : 1.0);
-    };
-    const int BN = cost(256) <= cost(128) ? 256 : 128;
-
-    CUtensorMap tmA, tmB;
-    bool ok;
-    if (!a_mn_major) ok = encode_tmap_2d(&tmA, A, M, K, lda, kBK, kBM, 2);
-    else ok = encode_tmap_2d(&tmA, A, K, M, lda, 64, kBK, 2);
-    if (!ok) return CAI_K_BAD_ARG;
-    if (!b_mn_major) ok = encode_tmap_2d(&tmB, B, N, K, ldb, kBK, BN, 2);
-    else ok = encode_tmap_2d(&tmB, B, K, N, ldb, 64, kBK, 2);
-    if (!ok) return CAI_K_BAD_ARG;
-
     GemmParams p;
+    plain_params(p);
     p.M = M; p.N = N; p.K = K;
     p.a_mn = a_mn_major ? 1 : 0;
     p.b_mn = b_mn_major ? 1 : 0;
@@ -350,8 +551,57 @@ CAI_API int cai_gemm_bf16(const void* A, const void* B, void* C, const void* R, 
     p.alpha = alpha;
     p.C = C; p.R = R;
     p.ldc = ldc; p.ldr = ldr;
-    p.status = status_words(dev);
-    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if (BN == 256) return launch_gemm<256, 4>(tmA, tmB, p, sms, st);
-    return launch_gemm<128, 6>(tmA, tmB, p, sms, st);
+    return gemm_dispatch(A, B, lda, ldb, p, sm_limit, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// y[T,N] = concat_rows(x_local of every member)[T,K] * op(B); also leaves the gathered rows in a_full.
+int cai_fused_ag_gemm(const PeerTable& pt, int group_kind, unsigned long long src_off, long long ld_src, void* a_full,
+                      const void* B, void* C, int T, int N, int K, long long ldb, long long ldc, int b_mn,
+                      int rows_per_rank, const uint32_t* epoch_base, uint32_t seq, int n_copy, cudaStream_t st) {
+    if (rows_per_rank % kBM || rows_per_rank * pt.size != T || (N & 7) || (K & 7) || (ldb & 7) || (ldc & 7) ||
+        T / kBM > static_cast<int>(kSigLocalSlots)) {
+        set_last_error("ag_gemm: rows per member must be a multiple of 128 (T=%d rows_per_rank=%d)", T, rows_per_rank);
+        return CAI_K_BAD_ARG;
+    }
+    GemmParams p;
+    plain_params(p);
+    p.M = T; p.N = N; p.K = K;
+    p.b_mn = b_mn ? 1 : 0;
+    p.C = C; p.ldc = ldc;
+    p.mode = kGemmAllGatherA;
+    p.group_kind = group_kind;
+    p.n_copy = n_copy;
+    p.rows_per_rank = rows_per_rank;
+    p.m_rot = pt.rank * (rows_per_rank / kBM);  // own rows first
+    p.epoch_base = epoch_base; p.seq = seq;
+    p.src_off = src_off; p.ld_src = ld_src;
+    p.a_full = static_cast<__nv_bfloat16*>(a_full);
+    p.pt = pt;
+    return gemm_dispatch(a_full, B, K, ldb, p, 0, st);
+}
+
+// out_local[T/size, N] = residual + sum over members of (A_member[T,K] * op(B_member))[my rows].
+int cai_fused_gemm_rs(const PeerTable& pt, int group_kind, const void* A, const void* B, unsigned long long stage_off,
+                      void* out_local, const void* residual, int T, int N, int K, long long lda, long long ldb,
+                      long long ldo, long long ldr, int b_mn, int rows_per_rank, const uint32_t* epoch_base, uint32_t seq,
+                      cudaStream_t st) {
+    if (rows_per_rank % kBM || rows_per_rank * pt.size != T || (N & 7) || (lda & 7) || (ldb & 7) || (ldo & 7) ||
+        (residual && (ldr & 7))) {
+        set_last_error("gemm_rs: rows per member must be a multiple of 128 (T=%d rows_per_rank=%d)", T, rows_per_rank);
+        return CAI_K_BAD_ARG;
+    }
+    GemmParams p;
+    plain_params(p);
+    p.M = T; p.N = N; p.K = K;
+    p.b_mn = b_mn ? 1 : 0;
+    p.C = out_local; p.ldc = ldo;
+    p.R = residual; p.ldr = ldr;
+    p.mode = kGemmReduceScatter;
+    p.group_kind = group_kind;
+    p.rows_per_rank = rows_per_rank;
+    p.m_rot = ((pt.rank + 1) % pt.size) * (rows_per_rank / kBM);  // push to the other members first
+    p.epoch_base = epoch_base; p.seq = seq;
+    p.stage_off = stage_off;
+    p.pt = pt;
+    return gemm_dispatch(A, B, lda, ldb, p, 0, st);
 }

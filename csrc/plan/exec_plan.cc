@@ -18,6 +18,7 @@
 #include <cstdarg>
 #include <cstring>
 
+#include "../comm/signals.h"
 #include "plan.h"
 
 namespace cai {
@@ -69,6 +70,7 @@ struct Builder {
     uint64_t cursor[TC_COUNT] = {0, 0, 0, 0, 0, 0};
     uint64_t flat_elems = 0;       // elements in the flat parameter space so far
     uint32_t next_event = 0;
+    uint32_t next_seq = 0;         // sequence number of the next fused compute+collective op
     int flat_param = -1, flat_grad = -1, flat_master = -1, flat_m = -1, flat_v = -1;
 
     // local dimensions
@@ -195,7 +197,7 @@ struct Builder {
         if (fused) {
             ExecOp e = xop(K_AG_GEMM, static_cast<uint16_t>(tb ? 2 : 0));
             e.t[0] = x_local; e.t[1] = W; e.t[2] = y; e.t[3] = x_full;
-            e.i[0] = T; e.i[1] = N; e.i[2] = K; e.i[3] = GROUP_TP;
+            e.i[0] = T; e.i[1] = N; e.i[2] = K; e.i[3] = GROUP_TP; e.i[4] = static_cast<int32_t>(next_seq++);
             e.f[0] = 1.0f;
             push(OP_AG_GEMM, ST_COMPUTE_HI, 2.0 * T * N * K, static_cast<double>(T) * K * 2, GROUP_TP, mb, &e);
             return;
@@ -217,7 +219,7 @@ struct Builder {
         if (fused) {
             ExecOp e = xop(K_GEMM_RS, static_cast<uint16_t>(tb ? 2 : 0));
             e.t[0] = a; e.t[1] = W; e.t[2] = out_local; e.t[3] = residual; e.t[4] = partial;
-            e.i[0] = T; e.i[1] = N; e.i[2] = K; e.i[3] = GROUP_TP;
+            e.i[0] = T; e.i[1] = N; e.i[2] = K; e.i[3] = GROUP_TP; e.i[4] = static_cast<int32_t>(next_seq++);
             e.f[0] = 1.0f;
             push(OP_GEMM_RS, ST_COMPUTE_HI, 2.0 * T * N * K, static_cast<double>(T) * N * 2, GROUP_TP, mb, &e);
             return;
@@ -352,7 +354,9 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     b.cursor[TC_PARAM] = n_flat * 2;
     b.cursor[TC_GRAD] = n_flat * 4;
     // optimizer state: master | m | v, each n_flat fp32 (sharded 1/dp when the optimizer is sharded)
-    const uint64_t n_opt = d.dp > 1 ? align_up((n_flat + d.dp - 1) / d.dp, kFlatAlignElems) : n_flat;
+    // sharded 1/dp only when the fused reduce-scatter + AdamW kernel owns the update; the NCCL baseline
+    // all-reduces the gradients and every replica updates everything
+    const uint64_t n_opt = (d.dp > 1 && b.fused) ? align_up((n_flat + d.dp - 1) / d.dp, kFlatAlignElems) : n_flat;
     b.flat_master = b.tensor_at(TC_OPTSTATE, DT_FP32, 0, 1, 0, 0);
     b.flat_m = b.tensor_at(TC_OPTSTATE, DT_FP32, n_opt * 4, 1, 0, 0);
     b.flat_v = b.tensor_at(TC_OPTSTATE, DT_FP32, n_opt * 8, 1, 0, 0);
@@ -365,6 +369,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     const int tokens = b.tensor(TC_COMM, DT_INT32, ga, T);
     const int targets = b.tensor(TC_COMM, DT_INT32, ga, T);
     const int loss_acc = b.tensor(TC_WORKSPACE, DT_FP32, 1, 8);
+    const int signals = b.tensor(TC_COMM, DT_UINT8, 1, kSigBytes);  // epoch counters of the fused kernels
     const int rope_tab = b.tensor(TC_WORKSPACE, DT_FP32, b.seq, b.hd);  // [seq, hd/2] float2
     const uint32_t norm_parts = std::min<uint32_t>(std::max(Tl, 1u), 4 * 160);
     const int norm_scratch = b.tensor(TC_WORKSPACE, DT_FP32, norm_parts, H);
@@ -651,7 +656,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             ExecOp e = xop(K_RS_ADAMW);
             e.t[0] = b.flat_master; e.t[1] = b.flat_m; e.t[2] = b.flat_v; e.t[3] = b.flat_grad; e.t[4] = b.flat_param;
             e.i[0] = static_cast<int32_t>(n_flat & 0xFFFFFFFFu); e.i[1] = static_cast<int32_t>(n_flat >> 32);
-            e.i[2] = static_cast<int32_t>(n_opt & 0xFFFFFFFFu); e.i[3] = GROUP_DP;
+            e.i[2] = static_cast<int32_t>(n_opt & 0xFFFFFFFFu); e.i[3] = GROUP_DP; e.i[4] = static_cast<int32_t>(b.next_seq++);
             e.f[0] = 1.0f / d.dp;
             b.sync(ST_COMPUTE_HI, ST_COMM_DP, 0);
             b.push(OP_RS_ADAMW, ST_COMM_DP, 18.0 * n_opt, 4.0 * n_flat, GROUP_DP, 0, &e);
@@ -707,6 +712,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     well_known("@tokens", tokens);
     well_known("@targets", targets);
     well_known("@loss", loss_acc);
+    well_known("@signals", signals);
     well_known("@rope_table", rope_tab);
     well_known("@flat_param", b.flat_param);
     well_known("@flat_grad", b.flat_grad);

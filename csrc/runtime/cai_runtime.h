@@ -39,6 +39,11 @@ CAI_API void cai_exec_destroy(cai_exec* ex);
 CAI_API int cai_nccl_unique_id(const char* libpath, void* id128);
 CAI_API int cai_exec_init_comm(cai_exec* ex, const char* libpath, int group_kind, const void* id128,
                                const void* id128_second, int nranks, int rank);
+CAI_API int cai_exec_set_peers(cai_exec* ex, int group_kind, int n, void* const* bases, int rank);
+CAI_API void cai_exec_set_ag_copy_ctas(cai_exec* ex, int n);
+CAI_API int cai_ipc_export(void* ptr, void* handle64, unsigned long long* offset);
+CAI_API int cai_ipc_open(const void* handle64, unsigned long long offset, void** out);
+CAI_API int cai_ipc_close(void* mapped, unsigned long long offset);
 CAI_API void* cai_exec_stream(cai_exec* ex, int stream_id);
 CAI_API void* cai_exec_tensor_ptr(cai_exec* ex, int tensor);
 CAI_API long long cai_exec_tensor_ld(cai_exec* ex, int tensor);

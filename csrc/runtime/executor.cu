@@ -21,6 +21,8 @@
 #include <string>
 #include <vector>
 
+#include "../comm/fused.h"
+#include "../comm/peer.cuh"
 #include "../kernels/cai_kernels.h"
 #include "../kernels/host_common.h"
 #include "../plan/formats.h"
@@ -143,6 +145,11 @@ struct cai_exec {
     std::vector<cudaEvent_t> events;
     cudaEvent_t fork_ev = nullptr, join_ev[ST_COUNT] = {};
     Comm comms[GROUP_COUNT];
+    PeerTable peers[GROUP_COUNT] = {};
+    bool has_peers[GROUP_COUNT] = {};
+    unsigned int* counters_dev = nullptr;  // scratch words for grid-completion tickets
+    uint32_t epochs_per_step = 2;
+    int ag_copy_ctas = 16;
     float* hyper_dev = nullptr;   // 8 floats
     float* hyper_host = nullptr;  // pinned
     cudaGraphExec_t graph = nullptr;
@@ -246,6 +253,32 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
                 return CAI_K_CUDA;
             }
             return 0;
+        }
+        case K_AG_GEMM: case K_GEMM_RS: case K_RS_ADAMW: {
+            const int group = x.i[3];
+            if (group < 0 || group >= GROUP_COUNT || !ex->has_peers[group]) {
+                set_last_error("fused op needs the peer table of communicator %d (arenas not exchanged)", group);
+                return CAI_K_BAD_ARG;
+            }
+            const PeerTable& pt = ex->peers[group];
+            const uint32_t* epoch_base = reinterpret_cast<const uint32_t*>(ex->hyper_dev) + 7;
+            const uint32_t seq = static_cast<uint32_t>(x.i[4]);
+            if (x.kernel == K_AG_GEMM) {
+                const int T = x.i[0], N = x.i[1], K = x.i[2];
+                return cai_fused_ag_gemm(pt, group, ex->tensors[x.t[0]].offset, ex->ld(x.t[0]), P(3), P(1), P(2), T, N, K,
+                                         ex->ld(x.t[1]), ex->ld(x.t[2]), (x.flags >> 1) & 1, T / pt.size, epoch_base, seq,
+                                         ex->ag_copy_ctas, st);
+            }
+            if (x.kernel == K_GEMM_RS) {
+                const int T = x.i[0], N = x.i[1], K = x.i[2];
+                return cai_fused_gemm_rs(pt, group, P(0), P(1), ex->tensors[x.t[4]].offset, P(2), P(3), T, N, K, ex->ld(x.t[0]),
+                                         ex->ld(x.t[1]), ex->ld(x.t[2]), x.t[3] >= 0 ? ex->ld(x.t[3]) : 0, (x.flags >> 1) & 1,
+                                         T / pt.size, epoch_base, seq, st);
+            }
+            const long long n_flat = (static_cast<long long>(static_cast<uint32_t>(x.i[1])) << 32) | static_cast<uint32_t>(x.i[0]);
+            const long long n_shard = static_cast<uint32_t>(x.i[2]);
+            return cai_fused_rs_adamw(pt, ex->tensors[x.t[3]].offset, ex->tensors[x.t[4]].offset, (float*)P(0), (float*)P(1),
+                                      (float*)P(2), n_flat, n_shard, ex->hyper_dev, x.f[0], seq, ex->counters_dev, st);
         }
         default:
             if (ex->fused_hook) return ex->fused_hook(ex->fused_ctx, ex, &x, static_cast<int>(op.stream_id), st);
@@ -370,6 +403,14 @@ CAI_API int cai_exec_create(cai_exec** out, const void* plan_bytes, size_t nbyte
     ex->events.resize(ex->hdr.num_events);
     for (cudaEvent_t& e : ex->events) cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
     cudaMalloc(&ex->hyper_dev, 8 * sizeof(float));
+    cudaMalloc(&ex->counters_dev, 256 * sizeof(unsigned int));
+    cudaMemset(ex->counters_dev, 0, 256 * sizeof(unsigned int));
+    {
+        uint32_t fused = 0;
+        for (const ExecOp& x : ex->exec)
+            if (x.kernel == K_AG_GEMM || x.kernel == K_GEMM_RS || x.kernel == K_RS_ADAMW) ++fused;
+        ex->epochs_per_step = 2 * fused + 2;
+    }
     cudaMallocHost(&ex->hyper_host, 8 * sizeof(float));
     *out = ex;
     return 0;
@@ -391,6 +432,7 @@ CAI_API void cai_exec_destroy(cai_exec* ex) {
         if (c.comm2 && g_nccl.CommDestroy) g_nccl.CommDestroy(c.comm2);
     }
     cudaFree(ex->hyper_dev);
+    cudaFree(ex->counters_dev);
     cudaFreeHost(ex->hyper_host);
     delete ex;
 }
@@ -426,6 +468,27 @@ CAI_API int cai_exec_init_comm(cai_exec* ex, const char* libpath, int group_kind
     return 0;
 }
 
+// Arena bases of the members of a communicator as mapped in this process (bases[rank] is the local
+// arena). Enables the fused compute+collective kernels of that communicator.
+CAI_API int cai_exec_set_peers(cai_exec* ex, int group_kind, int n, void* const* bases, int rank) {
+    if (group_kind < 0 || group_kind >= GROUP_COUNT || n < 1 || n > kMaxPeers || rank < 0 || rank >= n) return CAI_K_BAD_ARG;
+    int sig = -1;
+    for (const NamedTensor& nt : ex->named)
+        if (!strcmp(nt.name, "@signals")) sig = nt.tensor;
+    if (sig < 0 || ex->tensors[sig].nbytes < kSigBytes) {
+        set_last_error("plan has no signal block");
+        return CAI_K_BAD_ARG;
+    }
+    PeerTable& pt = ex->peers[group_kind];
+    for (int i = 0; i < n; ++i) pt.base[i] = static_cast<uint8_t*>(bases[i]);
+    pt.rank = rank;
+    pt.size = n;
+    pt.sig_off = ex->tensors[sig].offset;
+    ex->has_peers[group_kind] = true;
+    return 0;
+}
+CAI_API void cai_exec_set_ag_copy_ctas(cai_exec* ex, int n) { ex->ag_copy_ctas = n; }
+
 CAI_API void* cai_exec_stream(cai_exec* ex, int stream_id) {
     return stream_id >= 0 && stream_id < ST_COUNT ? ex->streams[stream_id] : nullptr;
 }
@@ -454,7 +517,8 @@ CAI_API int cai_exec_step(cai_exec* ex, int step, float lr) {
     h[0] = lr; h[1] = t.beta1; h[2] = t.beta2; h[3] = t.adam_eps; h[4] = t.weight_decay;
     h[5] = 1.f - powf(t.beta1, static_cast<float>(step));
     h[6] = 1.f - powf(t.beta2, static_cast<float>(step));
-    h[7] = 0.f;
+    // epoch base of this step's fused kernels: grows by a fixed stride per step, never resets
+    reinterpret_cast<uint32_t*>(h)[7] = static_cast<uint32_t>(step) * ex->epochs_per_step;
     if (cudaMemcpyAsync(ex->hyper_dev, h, 8 * sizeof(float), cudaMemcpyHostToDevice, hi) != cudaSuccess) return CAI_K_CUDA;
     if (ex->use_graph) {
         if (!ex->graph) {

@@ -6,6 +6,7 @@
 // report text follow the reference tool (tools/plan_compiler.c); `--exec` writes version-2
 // (executable) plans instead of cost-only version-1 plans.
 #include <cstdio>
+#include <fstream>
 #include <cstdlib>
 #include <cstring>
 #include <set>
@@ -66,6 +67,12 @@ int main(int argc, char** argv) {
     if (topology_write(tpath, cfg.topo) != OK) { std::fprintf(stderr, "cannot write %s\n", tpath.c_str()); return 1; }
     std::printf("wrote %s (topology_hash=%016llx, plan_hash=%016llx)\n", tpath.c_str(), (unsigned long long)th,
                 (unsigned long long)ph);
+    {
+        // keep the config next to the plans: the device trainer derives communicator membership from it
+        std::ifstream in(cfgpath, std::ios::binary);
+        std::ofstream out(outdir + "/config.cfg", std::ios::binary);
+        out << in.rdbuf();
+    }
 
     const uint32_t ws = cfg.topo.world_size;
     std::vector<uint32_t> ranks;

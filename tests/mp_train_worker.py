@@ -33,7 +33,7 @@ def main():
     losses = []
     for step in range(a.steps):
         # the global batch is dp * rows sequences; each data-parallel replica takes its slice
-        tok, tgt = synthetic_batch(m.vocab_size, m.seq_len, rows * dp, step=step, seed=11)
+        tok, tgt = synthetic_batch(m.vocab_size, m.seq_len, rows * dp, step=step % 2, seed=11)
         tok, tgt = tok[dp_id * rows:(dp_id + 1) * rows].contiguous().pin_memory(), tgt[dp_id * rows:(dp_id + 1) * rows].contiguous().pin_memory()
         if a.graph and step == 2:
             eng.use_graph(True)

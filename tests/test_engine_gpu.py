@@ -114,3 +114,59 @@ def test_trace_has_measured_times():
     assert all(r.end_s >= r.start_s for r in recs)
     assert sum(r.end_s - r.start_s for r in recs) > 0
     eng.close()
+
+
+def test_loss_curve_matches_fp64_oracle():
+    """Device (bf16) training against the fp64 CPU oracle started from the same weights."""
+    from cai_b200.models.oracle import Oracle, load_engine_weights
+    from cai_b200.runtime.engine import synthetic_batch
+    eng = _engine()
+    m, t = eng.model, eng.train
+    rows = eng.hdr.num_microbatches * m.microbatch
+    ora = Oracle(vocab=m.vocab_size, seq=m.seq_len, hidden=m.hidden_size, layers=m.num_layers, n_heads=m.num_heads,
+                 n_kv_heads=m.num_kv_heads, head_dim=m.head_dim, ffn=m.ffn_hidden, eps=t.norm_eps, rope=True,
+                 rope_theta=t.rope_theta, tied=True, init_std=0.02, seed=1)
+    load_engine_weights(ora, eng)
+    tok, tgt = synthetic_batch(m.vocab_size, m.seq_len, rows, step=0, seed=5)
+    dev, ref = [], []
+    for _ in range(5):
+        dev.append(eng.step(tok, tgt))
+        ref.append(ora.forward(tok.numpy(), tgt.numpy()))
+        ora.backward(tok.numpy(), tgt.numpy())
+        ora.adamw(t.lr, t.beta1, t.beta2, t.adam_eps, t.weight_decay)
+    assert ref[-1] < ref[0] - 0.2
+    for a, b in zip(dev, ref):
+        assert abs(a - b) < 0.03 * max(1.0, b), (dev, ref)
+    eng.close()
+
+
+def test_checkpoint_resume_reproduces_the_curve(tmp_path):
+    from cai_b200 import plan as planlib
+    from cai_b200.runtime.engine import synthetic_batch
+    eng = _engine()
+    m = eng.model
+    rows = eng.hdr.num_microbatches * m.microbatch
+    batches = [synthetic_batch(m.vocab_size, m.seq_len, rows, step=s % 2, seed=9) for s in range(6)]
+    for s in range(3):
+        eng.step(*batches[s])
+    eng.save_checkpoint(tmp_path / "ck", "periodic")
+    tail = [eng.step(*batches[s]) for s in range(3, 6)]
+    assert eng.wait_checkpoint() == 0
+    eng.close()
+    raw = (tmp_path / "ck.latest.rank000000").read_bytes()
+    assert int.from_bytes(raw[:4], "little") == 3 and (tmp_path / "ck.periodic.rank000000").exists()
+
+    eng2 = _engine()
+    assert eng2.load_checkpoint(tmp_path / "ck") and eng2.step_count == 3
+    tail2 = [eng2.step(*batches[s]) for s in range(3, 6)]
+    assert all(abs(a - b) < 2e-3 for a, b in zip(tail, tail2)), (tail, tail2)
+    assert not eng2.load_checkpoint(tmp_path / "nothing")
+    eng2.close()
+
+    # a checkpoint of a different plan is refused
+    from cai_b200.runtime.engine import Engine
+    other = Engine(config_text=(ROOT / "configs" / "tiny.cfg").read_text() + "\nffn_hidden = 1024\n", rank=0, world=1,
+                   local_rank=0)
+    with pytest.raises(planlib.PlanError):
+        other.load_checkpoint(tmp_path / "ck")
+    other.close()
