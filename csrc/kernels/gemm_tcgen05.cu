@@ -73,48 +73,57 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
 
 __device__ __forceinline__ void bar_sync_epilogue() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 
-// All-gather staging, run by the leading CTAs of the grid: pull every member's rows (peer loads
-// over NVLink, 128 rows at a time) into the local gathered buffer and publish one local flag per
-// 128-row block, which the TMA producers of the compute CTAs wait on.
-__device__ __forceinline__ void allgather_copy_role(const GemmParams& p, uint32_t epoch) {
-    __shared__ int ok_s;
+// All-gather staging, run by the leading CTAs of the grid: one thread per copy CTA drives the TMA
+// engine, pulling every member's rows (bulk loads over NVLink, 128 rows per unit) through a ring of
+// shared-memory slots into the local gathered buffer, and publishes one local flag per 128-row
+// block that the TMA producers of the compute CTAs wait on. Several pieces are in flight per CTA,
+// which is what it takes to fill an NVLink.
+constexpr int kAgSlots = 6;
+constexpr uint32_t kAgPiece = 32768;
+
+__device__ __forceinline__ void allgather_copy_role(const GemmParams& p, uint32_t epoch, uint8_t* ring, uint64_t* bars) {
+    if (threadIdx.x != 0) return;
+    volatile int no_abort = 0;
+    for (int i = 0; i < kAgSlots; ++i) mbar_init(&bars[i], 1);
+    mbar_fence_init();
     const int blocks_per_rank = p.rows_per_rank / kBM;
     const int units = p.pt.size * blocks_per_rank;
     const size_t row_bytes = static_cast<size_t>(p.K) * 2;
+    const bool contiguous = p.ld_src == p.K;
+    // a piece is a contiguous byte range: 32 KiB of a contiguous block, or one row otherwise
+    const uint32_t piece = contiguous ? kAgPiece : static_cast<uint32_t>(row_bytes);
+    const uint32_t pieces = static_cast<uint32_t>(contiguous ? (kBM * row_bytes) / kAgPiece : kBM);
+    uint32_t n = 0;  // pieces issued by this CTA so far (slot = n % kAgSlots, phase = (n / kAgSlots) & 1)
     for (int u = blockIdx.x; u < units; u += p.n_copy) {
         // own rows first, then the peers in ring order, so early tiles never wait on NVLink
         const int s = (p.pt.rank + u / blocks_per_rank) % p.pt.size;
         const int j = u % blocks_per_rank;
-        if (threadIdx.x == 0)
-            ok_s = wait_flag_ge(sig_word(p.pt, p.pt.rank, p.group_kind, kSigEntry + s), epoch, p.status) ? 1 : 0;
-        __syncthreads();
-        if (!ok_s) return;
+        if (!wait_flag_ge(sig_word(p.pt, p.pt.rank, p.group_kind, kSigEntry + s), epoch, p.status)) return;
         const uint8_t* src = p.pt.base[s] + p.src_off + static_cast<size_t>(j) * kBM * p.ld_src * 2;
         uint8_t* dst = reinterpret_cast<uint8_t*>(p.a_full) + (static_cast<size_t>(s) * p.rows_per_rank + j * kBM) * row_bytes;
-        const int vec_per_row = static_cast<int>(row_bytes >> 4);
-        const int total = kBM * vec_per_row;
-        for (int v0 = threadIdx.x; v0 < total; v0 += kGemmThreads * 8) {
-            uint4 tmp[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const int v = v0 + e * kGemmThreads;
-                if (v < total) {
-                    const int r = v / vec_per_row, c = v - r * vec_per_row;
-                    tmp[e] = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * p.ld_src * 2 + c * 16);
-                }
+        const size_t src_step = contiguous ? piece : static_cast<size_t>(p.ld_src) * 2;
+        constexpr uint32_t kLag = kAgSlots - 2;  // loads in flight ahead of the store
+        for (uint32_t i = 0; i < pieces + kLag; ++i) {
+            if (i < pieces) {
+                const uint32_t slot = n % kAgSlots;
+                if (n >= kAgSlots) bulk_wait_read1();  // the store that last used this slot has read it
+                mbar_expect_tx(&bars[slot], piece);
+                bulk_load(ring + slot * kAgPiece, src + i * src_step, piece, &bars[slot]);
+                ++n;
             }
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const int v = v0 + e * kGemmThreads;
-                if (v < total) *reinterpret_cast<uint4*>(dst + static_cast<size_t>(v) * 16) = tmp[e];
+            if (i >= kLag) {
+                const uint32_t m = n - (i < pieces ? kLag + 1 : pieces + kLag - i);  // global index of the piece to store
+                const uint32_t slot = m % kAgSlots;
+                if (!mbar_wait(&bars[slot], (m / kAgSlots) & 1, &no_abort, p.status, CAI_DEV_TIMEOUT_TMA_FULL)) return;
+                bulk_store(dst + static_cast<size_t>(i - kLag) * piece, ring + slot * kAgPiece, piece);
+                tma_store_commit();
             }
         }
+        tma_store_wait0();
+        fence_proxy_async_all();
         __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            uint32_t* flag = sig_word(p.pt, p.pt.rank, p.group_kind, kSigLocal + s * blocks_per_rank + j);
-            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
-        }
+        uint32_t* flag = sig_word(p.pt, p.pt.rank, p.group_kind, kSigLocal + s * blocks_per_rank + j);
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
     }
 }
 
@@ -152,7 +161,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (p.mode == kGemmAllGatherA) {
             if (blockIdx.x == 0 && threadIdx.x == 0) signal_all(p.pt, p.group_kind, kSigEntry + p.pt.rank, epoch);
             if (static_cast<int>(blockIdx.x) < p.n_copy) {
-                allgather_copy_role(p, epoch);
+                allgather_copy_role(p, epoch, smem, bars);
                 return;
             }
         }
@@ -205,7 +214,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         uint32_t v;
                         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
                         seen = static_cast<int32_t>(v - epoch) >= 0;
-                        if (!seen && it > 32) __nanosleep(100);
+                        if (!seen && it > 32) {
+                            __nanosleep(100);
+                            if ((it & 1023u) == 0 && *reinterpret_cast<volatile int*>(p.status) != 0) break;
+                        }
                     }
                     if (!seen) {
                         *abort_flag = 1;

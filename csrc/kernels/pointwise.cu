@@ -79,101 +79,167 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 }
 
 // ------------------------------------------------------------------ RMSNorm
-__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
-                                                          const __nv_bfloat16* __restrict__ g,
-                                                          __nv_bfloat16* __restrict__ y,
-                                                          float* __restrict__ rstd, int H, float eps) {
-    __shared__ float red[33];
-    const long long row = blockIdx.x;
-    const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+// A row is handled by R = ceil(H / 2048) warps, each lane keeping 64 elements of x (and dy) in
+// registers, so every tensor is read exactly once and no block-wide barrier sits between the
+// reduction and the second sweep when R = 1. A CTA of 8 warps works on 8 / R rows at a time.
+constexpr int kNormThreads = 256;
+constexpr int kNormWarpCols = 2048;  // columns one warp covers: 32 lanes x 8 chunks x 8 elements
+
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g,
+                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, int H, float eps, int R) {
+    __shared__ float part[8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int groups = 8 / R;
+    const int grp = warp / R, sub = warp - grp * R;
+    const bool active = grp < groups;
+    const int col0 = sub * kNormWarpCols;
     const uint4* gr = reinterpret_cast<const uint4*>(g);
-    uint4* yr = reinterpret_cast<uint4*>(y + row * H);
-    const int nv = H >> 3;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-        float f[8];
-        unpack8(xr[i], f);
+    for (long long base = static_cast<long long>(blockIdx.x) * groups; base < rows; base += static_cast<long long>(gridDim.x) * groups) {
+        const long long row = base + grp;
+        const bool live = active && row < rows;
+        uint4 xv[8];
+        float ss = 0.f;
+        if (live) {
+            const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
-    }
-    ss = block_sum(ss, red);
-    const float rr = rsqrtf(ss / H + eps);
-    if (threadIdx.x == 0 && rstd) rstd[row] = rr;
-    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-        float f[8], gg[8];
-        unpack8(xr[i], f);
-        unpack8(gr[i], gg);
+            for (int c = 0; c < 8; ++c) {
+                const int col = col0 + (c * 32 + lane) * 8;
+                if (col < H) {
+                    xv[c] = xr[col >> 3];
+                    float f[8];
+                    unpack8(xv[c], f);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = f[e] * rr * gg[e];
-        yr[i] = pack8(f);
+                    for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
+                }
+            }
+        }
+        ss = warp_sum(ss);
+        if (R > 1) {
+            if (lane == 0) part[warp] = ss;
+            __syncthreads();
+            if (active) {
+                ss = 0.f;
+                for (int k = 0; k < R; ++k) ss += part[grp * R + k];
+            }
+            __syncthreads();
+        }
+        if (live) {
+            const float rr = rsqrtf(ss / H + eps);
+            if (sub == 0 && lane == 0 && rstd) rstd[row] = rr;
+            uint4* yr = reinterpret_cast<uint4*>(y + row * H);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int col = col0 + (c * 32 + lane) * 8;
+                if (col < H) {
+                    float f[8], gg[8];
+                    unpack8(xv[c], f);
+                    unpack8(gr[col >> 3], gg);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) f[e] = f[e] * rr * gg[e];
+                    yr[col >> 3] = pack8(f);
+                }
+            }
+        }
     }
 }
 
-constexpr int kNormBwdThreads = 256;
-constexpr int kNormBwdChunks = 8;  // H <= 8 * 256 * 8 = 16384
-
-__global__ void __launch_bounds__(kNormBwdThreads)
+__global__ void __launch_bounds__(kNormThreads)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g,
                    const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dy,
                    __nv_bfloat16* __restrict__ dx, float* __restrict__ dg_partial, int rows, int H,
-                   int dx_acc) {
-    __shared__ float red[33];
-    float dg[kNormBwdChunks][8];
+                   int dx_acc, int R) {
+    extern __shared__ float dg_s[];  // [H] gain-gradient partial of this CTA
+    __shared__ float part[8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int groups = 8 / R;
+    const int grp = warp / R, sub = warp - grp * R;
+    const bool active = grp < groups;
+    const int col0 = sub * kNormWarpCols;
+    for (int i = threadIdx.x; i < H; i += kNormThreads) dg_s[i] = 0.f;
+    float dg[8][8];
 #pragma unroll
-    for (int c = 0; c < kNormBwdChunks; ++c)
+    for (int c = 0; c < 8; ++c)
 #pragma unroll
         for (int e = 0; e < 8; ++e) dg[c][e] = 0.f;
-    const int nv = H >> 3;
     const uint4* gr = reinterpret_cast<const uint4*>(g);
-    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
-        const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
-        const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * H);
-        uint4* dxr = reinterpret_cast<uint4*>(dx + row * H);
-        const float rr = rstd[row];
+    __syncthreads();
+    for (long long base = static_cast<long long>(blockIdx.x) * groups; base < rows; base += static_cast<long long>(gridDim.x) * groups) {
+        const long long row = base + grp;
+        const bool live = active && row < rows;
+        uint4 xv[8], dv[8];
         float S = 0.f;
+        if (live) {
+            const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+            const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * H);
 #pragma unroll
-        for (int c = 0; c < kNormBwdChunks; ++c) {
-            const int i = c * kNormBwdThreads + threadIdx.x;
-            if (i < nv) {
-                float xf[8], df[8], gf[8];
-                unpack8(xr[i], xf);
-                unpack8(dyr[i], df);
-                unpack8(gr[i], gf);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) S += df[e] * gf[e] * xf[e];
-            }
-        }
-        S = block_sum(S, red);
-        const float k = rr * rr * rr * S / H;
-#pragma unroll
-        for (int c = 0; c < kNormBwdChunks; ++c) {
-            const int i = c * kNormBwdThreads + threadIdx.x;
-            if (i < nv) {
-                float xf[8], df[8], gf[8], o[8];
-                unpack8(xr[i], xf);
-                unpack8(dyr[i], df);
-                unpack8(gr[i], gf);
-                if (dx_acc) unpack8(dxr[i], o);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float v = rr * df[e] * gf[e] - k * xf[e];
-                    o[e] = dx_acc ? o[e] + v : v;
-                    dg[c][e] += df[e] * xf[e] * rr;
+            for (int c = 0; c < 8; ++c) {
+                const int col = col0 + (c * 32 + lane) * 8;
+                if (col < H) {
+                    xv[c] = xr[col >> 3];
+                    dv[c] = dyr[col >> 3];
                 }
-                dxr[i] = pack8(o);
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int col = col0 + (c * 32 + lane) * 8;
+                if (col < H) {
+                    float xf[8], df[8], gf[8];
+                    unpack8(xv[c], xf);
+                    unpack8(dv[c], df);
+                    unpack8(gr[col >> 3], gf);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) S += df[e] * gf[e] * xf[e];
+                }
+            }
+        }
+        S = warp_sum(S);
+        if (R > 1) {
+            if (lane == 0) part[warp] = S;
+            __syncthreads();
+            if (active) {
+                S = 0.f;
+                for (int k = 0; k < R; ++k) S += part[grp * R + k];
+            }
+            __syncthreads();
+        }
+        if (live) {
+            const float rr = rstd[row];
+            const float k3 = rr * rr * rr * S / H;
+            uint4* dxr = reinterpret_cast<uint4*>(dx + row * H);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int col = col0 + (c * 32 + lane) * 8;
+                if (col < H) {
+                    float xf[8], df[8], gf[8], o[8];
+                    unpack8(xv[c], xf);
+                    unpack8(dv[c], df);
+                    unpack8(gr[col >> 3], gf);
+                    if (dx_acc) unpack8(dxr[col >> 3], o);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float v = rr * df[e] * gf[e] - k3 * xf[e];
+                        o[e] = dx_acc ? o[e] + v : v;
+                        dg[c][e] += df[e] * xf[e] * rr;
+                    }
+                    dxr[col >> 3] = pack8(o);
+                }
             }
         }
     }
-    float* out = dg_partial + (long long)blockIdx.x * H;
+    if (active) {
 #pragma unroll
-    for (int c = 0; c < kNormBwdChunks; ++c) {
-        const int i = c * kNormBwdThreads + threadIdx.x;
-        if (i < nv) {
-            float4* o4 = reinterpret_cast<float4*>(out + i * 8);
-            o4[0] = make_float4(dg[c][0], dg[c][1], dg[c][2], dg[c][3]);
-            o4[1] = make_float4(dg[c][4], dg[c][5], dg[c][6], dg[c][7]);
+        for (int c = 0; c < 8; ++c) {
+            const int col = col0 + (c * 32 + lane) * 8;
+            if (col < H) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) atomicAdd(&dg_s[col + e], dg[c][e]);
+            }
         }
     }
+    __syncthreads();
+    float* out = dg_partial + static_cast<long long>(blockIdx.x) * H;
+    for (int i = threadIdx.x; i < H; i += kNormThreads) out[i] = dg_s[i];
 }
 
 __global__ void reduce_parts_kernel(const float* __restrict__ parts, float* __restrict__ out, int nparts,
@@ -494,23 +560,31 @@ static inline unsigned blocks_for(long long n, int threads) {
 
 using namespace cai;
 
+static int norm_row_warps(int H) { return (H + kNormWarpCols - 1) / kNormWarpCols; }
+
 CAI_API int cai_rmsnorm_fwd(const void* x, const void* g, void* y, float* rstd, int rows, int H, float eps,
                             void* stream) {
     if (rows <= 0) return CAI_K_OK;
-    if (H & 7) {
-        set_last_error("rmsnorm: H must be a multiple of 8");
+    const int R = norm_row_warps(H);
+    if ((H & 7) || R > 8) {
+        set_last_error("rmsnorm: H must be a multiple of 8 and <= 16384");
         return CAI_K_BAD_ARG;
     }
-    rmsnorm_fwd_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)g,
-                                                               (__nv_bfloat16*)y, rstd, H, eps);
+    const int groups = 8 / R;
+    const long long want = (static_cast<long long>(rows) + groups - 1) / groups;
+    const int cap = cai_rmsnorm_bwd_parts(rows) * 4;
+    const int grid = static_cast<int>(want < cap ? want : cap);
+    rmsnorm_fwd_kernel<<<grid, kNormThreads, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)g,
+                                                                       (__nv_bfloat16*)y, rstd, rows, H, eps, R);
     CAI_LAUNCH_CHECK("rmsnorm_fwd");
     return CAI_K_OK;
 }
 
+// Number of [H]-float partial rows cai_rmsnorm_bwd writes into its scratch buffer.
 CAI_API int cai_rmsnorm_bwd_parts(int rows) {
     int sms = sm_count(current_device());
     if (sms <= 0) sms = 148;
-    const int cap = sms * 4;
+    const int cap = sms * 2;
     return rows < cap ? rows : cap;
 }
 
@@ -518,14 +592,15 @@ CAI_API int cai_rmsnorm_bwd(const void* x, const void* g, const float* rstd, con
                             float* dg_partial, int rows, int H, int dx_accumulate, int dg_accumulate,
                             void* stream) {
     if (rows <= 0) return CAI_K_OK;
-    if ((H & 7) || H > kNormBwdChunks * kNormBwdThreads * 8) {
-        set_last_error("rmsnorm_bwd: H must be a multiple of 8 and <= %d", kNormBwdChunks * kNormBwdThreads * 8);
+    const int R = norm_row_warps(H);
+    if ((H & 7) || R > 8 || H * 4 > 48 * 1024) {
+        set_last_error("rmsnorm_bwd: H must be a multiple of 8 and <= 12288");
         return CAI_K_BAD_ARG;
     }
     const int parts = cai_rmsnorm_bwd_parts(rows);
-    rmsnorm_bwd_kernel<<<parts, kNormBwdThreads, 0, (cudaStream_t)stream>>>(
+    rmsnorm_bwd_kernel<<<parts, kNormThreads, H * sizeof(float), (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)g, rstd, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx,
-        dg_partial, rows, H, dx_accumulate);
+        dg_partial, rows, H, dx_accumulate, R);
     CAI_LAUNCH_CHECK("rmsnorm_bwd");
     reduce_parts_kernel<<<blocks_for(H, 256), 256, 0, (cudaStream_t)stream>>>(dg_partial, dg, parts, H,
                                                                              dg_accumulate);

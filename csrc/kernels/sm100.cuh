@@ -127,6 +127,23 @@ __device__ __forceinline__ void tma_store_wait_read0() {
 __device__ __forceinline__ void tma_store_wait0() {
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
+// Untiled bulk copies (the TMA engine moving a contiguous byte range). Addresses and size must be
+// multiples of 16 bytes. The load may read another GPU's memory (no multicast is ever used).
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_wait_read1() {
+    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
+
 // Make generic-proxy writes to shared memory visible to the async proxy (TMA / tcgen05).
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -280,7 +297,12 @@ __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target, int* status) {
     for (uint32_t it = 0; it < kSpinLimit; ++it) {
         if (static_cast<int32_t>(ld_acquire_sys(p) - target) >= 0) return true;
-        if (it > 64) __nanosleep(200);
+        if (it > 64) {
+            __nanosleep(200);
+            // once any kernel on this device has given up, later waits fail fast instead of each
+            // running out its own limit (a dead peer would otherwise cost seconds per launch)
+            if ((it & 1023u) == 0 && status && *reinterpret_cast<volatile int*>(status) != 0) return false;
+        }
     }
     if (status) atomicCAS(status, 0, CAI_DEV_TIMEOUT_PEER_FLAG);
     return false;

@@ -12,7 +12,7 @@
 
 int main(int argc, char** argv) {
     if (argc < 3) {
-        std::fprintf(stderr, "usage: %s <plan.bin> <topology.bin> [--steps N] [--ckpt PATH] [--ckpt-every K] [--trace CSV]\n", argv[0]);
+        std::fprintf(stderr, "usage: %s <plan.bin> <topology.bin> [--steps N] [--ckpt PATH] [--ckpt-every K] [--trace CSV] [--fail-at STEP]\n", argv[0]);
         return 2;
     }
     cai_init_desc_t desc;
@@ -21,12 +21,14 @@ int main(int argc, char** argv) {
     desc.topology_path = argv[2];
     desc.max_steps = 10;
     const char* trace = nullptr;
+    long fail_at = -1;  // host-side fault injection: report a backend error at this step
     if (const char* r = std::getenv("RANK")) desc.global_rank = std::strtoul(r, nullptr, 10);
     for (int i = 3; i < argc; ++i) {
         if (!std::strcmp(argv[i], "--steps") && i + 1 < argc) desc.max_steps = std::strtoul(argv[++i], nullptr, 10);
         else if (!std::strcmp(argv[i], "--ckpt") && i + 1 < argc) { desc.checkpoint_path = argv[++i]; if (!desc.checkpoint_every) desc.checkpoint_every = 5; }
         else if (!std::strcmp(argv[i], "--ckpt-every") && i + 1 < argc) desc.checkpoint_every = std::strtoul(argv[++i], nullptr, 10);
         else if (!std::strcmp(argv[i], "--trace") && i + 1 < argc) trace = argv[++i];
+        else if (!std::strcmp(argv[i], "--fail-at") && i + 1 < argc) fail_at = std::strtol(argv[++i], nullptr, 10);
         else { std::fprintf(stderr, "unknown arg: %s\n", argv[i]); return 2; }
     }
     cai_context_t* ctx = nullptr;
@@ -46,7 +48,7 @@ int main(int argc, char** argv) {
     for (;;) {
         cai_batch_t batch;
         if (cai_next_batch(ctx, &batch) != 0) break;
-        rc = cai_train_step(ctx, &batch);
+        rc = (static_cast<long>(batch.step) == fail_at) ? -6 : cai_train_step(ctx, &batch);
         if (rc != 0) {
             std::fprintf(stderr, "step %u failed: %s\n", batch.step, cai_status_str(rc));
             cai_save_checkpoint(ctx, "emergency");

@@ -1,0 +1,105 @@
+"""Failure detection and recovery, all on the host: no GPU is faulted, trapped or hung."""
+import multiprocessing as mp
+import subprocess
+import time
+from datetime import timedelta
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+BIN = ROOT / "bin"
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _built():
+    from cai_b200 import _build
+    _build.build_host()
+
+
+def _rank_main(rank, world, port, die_after, q):
+    from torch.distributed import TCPStore
+    from cai_b200.utils.health import Heartbeat, RankFailure
+    store = TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=timedelta(seconds=20))
+    hb = Heartbeat(store, rank, world)
+    try:
+        for step in range(1, 6):
+            if rank == 1 and step > die_after:
+                q.put((rank, "exited", step))
+                return                      # leaves between steps, nothing in flight
+            hb.beat(step)
+            hb.check(step, timeout=1.5)
+        q.put((rank, "done", 5))
+        time.sleep(0.5)
+    except RankFailure as e:
+        q.put((rank, "failure", e.missing, e.step))
+        time.sleep(0.5)
+
+
+def test_heartbeat_names_the_rank_that_left():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29871
+    procs = [ctx.Process(target=_rank_main, args=(r, 3, port, 2, q)) for r in range(3)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=60)
+    got = [q.get(timeout=5) for _ in range(3)]
+    by_rank = {g[0]: g for g in got}
+    assert by_rank[1][1] == "exited"
+    for r in (0, 2):
+        assert by_rank[r][1] == "failure" and by_rank[r][2] == [1] and by_rank[r][3] == 3
+
+
+def test_watchdog_fires_on_an_overrunning_step_only():
+    from cai_b200.utils.health import Watchdog
+    hits = []
+    wd = Watchdog(0.1, lambda: hits.append(time.monotonic()))
+    wd.arm()
+    time.sleep(0.03)
+    wd.disarm()
+    time.sleep(0.2)
+    assert not hits
+    wd.arm()
+    time.sleep(0.3)
+    assert len(hits) == 1 and wd.fired
+    wd.close()
+
+
+def test_injected_step_failure_writes_emergency_checkpoint_and_recovers(tmp_path):
+    cfg = tmp_path / "spare.cfg"
+    cfg.write_text((ROOT / "configs" / "small.cfg").read_text().replace("num_racks     = 1", "num_racks = 2")
+                   .replace("spare_gpus    = 0", "spare_gpus = 12"))
+    plans = tmp_path / "plans"
+    subprocess.run([BIN / "plan_compiler", cfg, plans, "--quiet", "--rank", "7"], check=True, capture_output=True)
+    pl, tp, ck = plans / "plan.rank000007.bin", plans / "topology.bin", tmp_path / "ck"
+    env = {"RANK": "7", "PATH": "/usr/bin:/bin"}
+    r = subprocess.run([BIN / "trainer", pl, tp, "--steps", "10", "--ckpt", ck, "--fail-at", "7"], capture_output=True,
+                       text=True, env=env)
+    assert r.returncode == 1 and "step 7 failed: backend error" in r.stderr
+    em = tmp_path / "ck.emergency.rank000007"
+    assert em.exists() and int.from_bytes(em.read_bytes()[:4], "little") == 7
+    # the failed rank moves to a spare GPU: identical plan, resume from the rolling checkpoint
+    r = subprocess.run([BIN / "plan_recover", cfg, "7", tmp_path / "rec"], capture_output=True, text=True)
+    assert r.returncode == 0 and "different rack" in r.stdout
+    rec = tmp_path / "rec" / "plan.recover.rank000007.bin"
+    assert rec.read_bytes() == pl.read_bytes()
+    r = subprocess.run([BIN / "trainer", rec, tp, "--steps", "10", "--ckpt", ck], capture_output=True, text=True, env=env)
+    assert r.returncode == 0 and "   7 |" in r.stdout and "   6 |" not in r.stdout and "   9 |" in r.stdout
+
+
+def test_corrupted_plan_and_missing_files_are_refused(tmp_path):
+    from cai_b200 import plan
+    subprocess.run([BIN / "plan_compiler", ROOT / "configs" / "small.cfg", tmp_path, "--quiet", "--rank", "0"], check=True,
+                   capture_output=True)
+    raw = bytearray((tmp_path / "plan.rank000000.bin").read_bytes())
+    raw[16] ^= 0xFF                       # flip a byte of topology_hash
+    (tmp_path / "bad.bin").write_bytes(raw)
+    with pytest.raises(plan.PlanError):
+        plan.Simulator(tmp_path / "bad.bin", tmp_path / "topology.bin")
+    (tmp_path / "trunc.bin").write_bytes(raw[:1000])
+    with pytest.raises(plan.PlanError):
+        plan.Simulator(tmp_path / "trunc.bin", tmp_path / "topology.bin")
+    with pytest.raises(plan.PlanError):
+        plan.Simulator(tmp_path / "plan.rank000000.bin", tmp_path / "no_such_topology.bin")
