@@ -1,0 +1,196 @@
+// norm_kernels.cuh - device code of RMSNorm backward, shared by the two translation units that
+// launch it (pointwise.cu and rmsnorm_bwd_static.cu), plus the small vector / reduction helpers the
+// bandwidth-bound kernels use. Kernels are `static` so that each including file owns its copy.
+#pragma once
+
+#include <math.h>
+
+#include "sm100.cuh"
+
+namespace cai {
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x);
+    f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+    f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z);
+    f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint4 o;
+    o.x = pack_bf16(f[0], f[1]);
+    o.y = pack_bf16(f[2], f[3]);
+    o.z = pack_bf16(f[4], f[5]);
+    o.w = pack_bf16(f[6], f[7]);
+    return o;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Sum over the block; every thread gets the result. `red` is >= 33 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    if (w == 0) {
+        float t = lane < nw ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    if (w == 0) {
+        float t = lane < nw ? red[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+constexpr int kNormThreads = 256;
+constexpr int kNormWarpCols = 2048;  // columns one warp covers: 32 lanes x 8 chunks x 8 elements
+
+static __global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g,
+                   const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dy,
+                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dg_partial, int rows, int H,
+                   int dx_acc, int R) {
+    extern __shared__ float dg_s[];  // [H] gain-gradient partial of this CTA
+    __shared__ float part[8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int groups = 8 / R;
+    const int grp = warp / R, sub = warp - grp * R;
+    const bool active = grp < groups;
+    const int col0 = sub * kNormWarpCols;
+    for (int i = threadIdx.x; i < H; i += kNormThreads) dg_s[i] = 0.f;
+    float dg[8][8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dg[c][e] = 0.f;
+    const uint4* gr = reinterpret_cast<const uint4*>(g);
+    __syncthreads();
+    for (long long base = static_cast<long long>(blockIdx.x) * groups; base < rows; base += static_cast<long long>(gridDim.x) * groups) {
+        const long long row = base + grp;
+        const bool live = active && row < rows;
+        uint4 xv[8], dv[8];
+        float S = 0.f;
+        if (live) {
+            const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+            const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * H);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int col = col0 + (c * 32 + lane) * 8;
+                if (col < H) {
+                    xv[c] = xr[col >> 3];
+                    dv[c] = dyr[col >> 3];
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int col = col0 + (c * 32 + lane) * 8;
+                if (col < H) {
+                    float xf[8], df[8], gf[8];
+                    unpack8(xv[c], xf);
+                    unpack8(dv[c], df);
+                    unpack8(gr[col >> 3], gf);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) S += df[e] * gf[e] * xf[e];
+                }
+            }
+        }
+        S = warp_sum(S);
+        if (R > 1) {
+            if (lane == 0) part[warp] = S;
+            __syncthreads();
+            if (active) {
+                S = 0.f;
+                for (int k = 0; k < R; ++k) S += part[grp * R + k];
+            }
+            __syncthreads();
+        }
+        if (live) {
+            const float rr = rstd[row];
+            const float k3 = rr * rr * rr * S / H;
+            uint4* dxr = reinterpret_cast<uint4*>(dx + row * H);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int col = col0 + (c * 32 + lane) * 8;
+                if (col < H) {
+                    float xf[8], df[8], gf[8], o[8];
+                    unpack8(xv[c], xf);
+                    unpack8(dv[c], df);
+                    unpack8(gr[col >> 3], gf);
+                    if (dx_acc) unpack8(dxr[col >> 3], o);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float v = rr * df[e] * gf[e] - k3 * xf[e];
+                        o[e] = dx_acc ? o[e] + v : v;
+                        dg[c][e] += df[e] * xf[e] * rr;
+                    }
+                    dxr[col >> 3] = pack8(o);
+                }
+            }
+        }
+    }
+    if (active) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const int col = col0 + (c * 32 + lane) * 8;
+            if (col < H) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) atomicAdd(&dg_s[col + e], dg[c][e]);
+            }
+        }
+    }
+    __syncthreads();
+    float* out = dg_partial + static_cast<long long>(blockIdx.x) * H;
+    for (int i = threadIdx.x; i < H; i += kNormThreads) out[i] = dg_s[i];
+}
+
+// out[col] (+)= sum over parts of parts[p][col]. A block covers 32 columns; its 8 warps split the
+// partial rows, so a column's loads are spread over 8 independent chains instead of one long one.
+static __global__ void __launch_bounds__(256)
+reduce_parts_kernel(const float* __restrict__ parts, float* __restrict__ out, int nparts, int H, int accumulate) {
+    __shared__ float acc[8][32];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int col = blockIdx.x * 32 + lane;
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    if (col < H) {
+        int p = w;
+        for (; p + 24 < nparts; p += 32) {
+            s0 += parts[static_cast<long long>(p) * H + col];
+            s1 += parts[static_cast<long long>(p + 8) * H + col];
+            s2 += parts[static_cast<long long>(p + 16) * H + col];
+            s3 += parts[static_cast<long long>(p + 24) * H + col];
+        }
+        for (; p < nparts; p += 8) s0 += parts[static_cast<long long>(p) * H + col];
+    }
+    acc[w][lane] = (s0 + s1) + (s2 + s3);
+    __syncthreads();
+    if (w == 0 && col < H) {
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s += acc[k][lane];
+        out[col] = accumulate ? out[col] + s : s;
+    }
+}
+
+}  // namespace cai
