@@ -25,7 +25,7 @@
 
 namespace cai {
 
-constexpr int kAttnBwdThreads = 256;  // warp 0 TMA, warp 1 MMA, warps 4-7 compute
+constexpr int kAttnBwdThreads = 384;  // warp 0 TMA, warp 1 MMA, warps 4-11 compute (two groups split the columns)
 
 struct AttnBwdParams {
     int B, S, nh, nkv;
@@ -57,12 +57,12 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out, const _
     }
 }
 
-__device__ __forceinline__ void bar_sync_compute() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void bar_sync_compute() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // Store one finished 128x128 fp32 accumulator (TMEM) as bf16 rows of the packed gradient buffer.
-__device__ __forceinline__ void store_acc_bf16(uint32_t tacc, __nv_bfloat16* dst_row) {
+__device__ __forceinline__ void store_acc_bf16(uint32_t tacc, __nv_bfloat16* dst_row, int c_lo = 0, int c_hi = 4) {
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int c = c_lo; c < c_hi; ++c) {
         uint32_t v[32];
         tmem_ld_32x32(tacc + c * 32, v);
         tmem_ld_wait();
@@ -119,7 +119,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
             mbar_init(&qdo_empty[i], 1);
         }
         mbar_init(sdp_full, 1);
-        mbar_init(pds_ready, 128);
+        mbar_init(pds_ready, 256);
         mbar_init(final_bar, 1);
         *abort_flag = 0;
         mbar_fence_init();
@@ -184,6 +184,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
         }
     } else if (warp >= 4) {
         const int r = (warp & 3) * 32 + lane;  // kv row inside the tile == TMEM lane
+        const int half = warp >= 8 ? 1 : 0;    // which 64 query columns this warp group handles
         const uint32_t lane_bits = static_cast<uint32_t>((warp & 3) * 32) << 16;
         bool ok = true;
         for (int it = 0; it < iters; ++it) {
@@ -191,21 +192,25 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
             const int i = j + it % per_head;
             const int buf = it & 1;
             const long long vec = (static_cast<long long>(b) * p.nh + h) * p.S + i * kAttnTile + r;
-            sL[buf * 128 + r] = p.lse[vec] * 1.4426950408889634f;
-            sD[buf * 128 + r] = p.delta[vec];
+            if (half == 0) sL[buf * 128 + r] = p.lse[vec] * 1.4426950408889634f;
+            else sD[buf * 128 + r] = p.delta[vec];
             bar_sync_compute();
             if (!mbar_wait(sdp_full, it & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
             tc_fence_after();
             const bool diag = (i == j);
             const float* L = sL + buf * 128;
             const float* D = sD + buf * 128;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            // Both warp groups read their score columns first and keep the bf16 results in registers;
+            // only after every thread has finished reading are P^T / dS^T written back over S^T / dP^T
+            // (the packed output of the upper columns lands where the lower columns were read from).
+            uint32_t pk[2][16], dk[2][16];
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                const int c = half * 2 + cc;
                 uint32_t s[32], dp[32];
                 tmem_ld_32x32(tS + lane_bits + c * 32, s);
                 tmem_ld_32x32(tdP + lane_bits + c * 32, dp);
                 tmem_ld_wait();
-                uint32_t pk[16], dk[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
                     const int q0 = c * 32 + e;
@@ -217,11 +222,18 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
                     }
                     const float d0 = p0 * (__uint_as_float(dp[e]) - D[q0]) * p.scale;
                     const float d1 = p1 * (__uint_as_float(dp[e + 1]) - D[q0 + 1]) * p.scale;
-                    pk[e >> 1] = pack_bf16(p0, p1);
-                    dk[e >> 1] = pack_bf16(d0, d1);
+                    pk[cc][e >> 1] = pack_bf16(p0, p1);
+                    dk[cc][e >> 1] = pack_bf16(d0, d1);
                 }
-                tmem_st_32x16(tS + lane_bits + c * 16, pk);
-                tmem_st_32x16(tdP + lane_bits + c * 16, dk);
+            }
+            tc_fence_before();
+            bar_sync_compute();
+            tc_fence_after();
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                const int c = half * 2 + cc;
+                tmem_st_32x16(tS + lane_bits + c * 16, pk[cc]);
+                tmem_st_32x16(tdP + lane_bits + c * 16, dk[cc]);
             }
             tmem_st_wait();
             tc_fence_before();
@@ -231,10 +243,8 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
             tc_fence_after();
             const long long grow = static_cast<long long>(row_base) + j * kAttnTile + r;
             const long long ld = static_cast<long long>(p.nh + 2 * p.nkv) * kAttnHD;
-            if (iters > 0) {
-                store_acc_bf16(tdK + lane_bits, p.dqkv + grow * ld + col_k);
-                store_acc_bf16(tdV + lane_bits, p.dqkv + grow * ld + col_v);
-            }
+            if (half == 0) store_acc_bf16(tdK + lane_bits, p.dqkv + grow * ld + col_k);
+            else store_acc_bf16(tdV + lane_bits, p.dqkv + grow * ld + col_v);
         }
     }
 
@@ -283,7 +293,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
             mbar_init(&kv_empty[k], 1);
         }
         mbar_init(sdp_full, 1);
-        mbar_init(ds_ready, 128);
+        mbar_init(ds_ready, 256);
         mbar_init(final_bar, 1);
         *abort_flag = 0;
         mbar_fence_init();
@@ -346,6 +356,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
         }
     } else if (warp >= 4) {
         const int r = (warp & 3) * 32 + lane;  // q row inside the tile
+        const int half = warp >= 8 ? 1 : 0;    // which 64 key columns this warp group handles
         const uint32_t lane_bits = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const long long vec = (static_cast<long long>(b) * p.nh + h) * p.S + i * kAttnTile + r;
         const float lse2 = p.lse[vec] * 1.4426950408889634f;
@@ -355,13 +366,14 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
             if (!mbar_wait(sdp_full, j & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
             tc_fence_after();
             const bool diag = (j == i);
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            uint32_t dk[2][16];
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                const int c = half * 2 + cc;
                 uint32_t s[32], dp[32];
                 tmem_ld_32x32(tS + lane_bits + c * 32, s);
                 tmem_ld_32x32(tdP + lane_bits + c * 32, dp);
                 tmem_ld_wait();
-                uint32_t dk[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
                     const int k0 = c * 32 + e;
@@ -371,11 +383,16 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
                         if (k0 > r) p0 = 0.f;
                         if (k0 + 1 > r) p1 = 0.f;
                     }
-                    dk[e >> 1] = pack_bf16(p0 * (__uint_as_float(dp[e]) - dl) * p.scale,
-                                           p1 * (__uint_as_float(dp[e + 1]) - dl) * p.scale);
+                    dk[cc][e >> 1] = pack_bf16(p0 * (__uint_as_float(dp[e]) - dl) * p.scale,
+                                               p1 * (__uint_as_float(dp[e + 1]) - dl) * p.scale);
                 }
-                tmem_st_32x16(tdP + lane_bits + c * 16, dk);
             }
+            // dS is written back over dP only after both warp groups have read their dP columns
+            tc_fence_before();
+            bar_sync_compute();
+            tc_fence_after();
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) tmem_st_32x16(tdP + lane_bits + (half * 2 + cc) * 16, dk[cc]);
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(ds_ready);
@@ -384,7 +401,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
             tc_fence_after();
             const long long grow = static_cast<long long>(row_base) + i * kAttnTile + r;
             const long long ld = static_cast<long long>(p.nh + 2 * p.nkv) * kAttnHD;
-            store_acc_bf16(tdQ + lane_bits, p.dqkv + grow * ld + col_q);
+            store_acc_bf16(tdQ + lane_bits, p.dqkv + grow * ld + col_q, half * 2, half * 2 + 2);
         }
     }
 

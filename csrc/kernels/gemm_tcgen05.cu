@@ -127,7 +127,7 @@ __device__ __forceinline__ void allgather_copy_role(const GemmParams& p, uint32_
     }
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool RS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmParams p) {
@@ -310,6 +310,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         int t = 0;
         bool ok = true;
+        int rs_prev_owner = -1;
+        uint32_t rs_prev_slot = 0;
+        (void)rs_prev_owner; (void)rs_prev_slot;
         for (int tile = cta; tile < num_tiles && ok; tile += ncta, ++t) {
             int tm, tn;
             tile_coords(p, tile, tm, tn);
@@ -320,6 +323,59 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 break;
             }
             tc_fence_after();
+            if constexpr (RS) {
+                // Reduce-scatter epilogue: the warp's 32 rows x BN bf16 are staged in shared memory
+                // and every lane hands its row (one contiguous run in the owner's staging buffer) to
+                // the TMA engine as a bulk store over NVLink. The tile's arrival flag is raised one
+                // tile late, once the stores of that tile have completed, so that the wait for remote
+                // completion overlaps the next tile.
+                constexpr int kPitch = BN * 2 + 16;  // padded row pitch: conflict-free 16-byte lanes
+                uint8_t* stg = smem + STAGES * kStageBytes + 256 + q * 32 * kPitch;
+                const long long row = (long long)tm * kBM + q * 32 + lane;
+                const int blocks_per_rank = p.rows_per_rank / kBM;
+                const int owner = tm / blocks_per_rank;
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staging free again
+                __syncwarp();
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32;
+                    tmem_ld_32x32(taddr, r);
+                    tmem_ld_wait();
+                    const float alpha = p.alpha;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint4 o;
+                        o.x = pack_bf16(__uint_as_float(r[j * 8 + 0]) * alpha, __uint_as_float(r[j * 8 + 1]) * alpha);
+                        o.y = pack_bf16(__uint_as_float(r[j * 8 + 2]) * alpha, __uint_as_float(r[j * 8 + 3]) * alpha);
+                        o.z = pack_bf16(__uint_as_float(r[j * 8 + 4]) * alpha, __uint_as_float(r[j * 8 + 5]) * alpha);
+                        o.w = pack_bf16(__uint_as_float(r[j * 8 + 6]) * alpha, __uint_as_float(r[j * 8 + 7]) * alpha);
+                        *reinterpret_cast<uint4*>(stg + lane * kPitch + c * 64 + j * 16) = o;
+                    }
+                }
+                tc_fence_before();
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+                {
+                    const int col0 = tn * BN;
+                    const int cols = p.N - col0 < BN ? p.N - col0 : BN;
+                    const long long lrow = row - static_cast<long long>(owner) * p.rows_per_rank;
+                    __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.pt.base[owner] + p.stage_off) +
+                                          (static_cast<long long>(p.pt.rank) * p.rows_per_rank + lrow) * p.N + col0;
+                    if (cols > 0) bulk_store(drow, stg + lane * kPitch, static_cast<uint32_t>(cols) * 2);
+                    tma_store_commit();
+                }
+                // announce the previous tile: its stores (all but the newest group) have completed
+                asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
+                fence_proxy_async_all();
+                __threadfence_system();
+                bar_sync_epilogue();
+                if (warp == 2 && lane == 0 && rs_prev_owner >= 0)
+                    st_release_sys(sig_word(p.pt, rs_prev_owner, p.group_kind, kSigTile + p.pt.rank * kSigTileSlots + rs_prev_slot), epoch);
+                rs_prev_owner = owner;
+                rs_prev_slot = static_cast<uint32_t>((tm - owner * blocks_per_rank) * p.tiles_n + tn);
+            } else {
             const long long row = (long long)tm * kBM + q * 32 + lane;
             const bool row_ok = row < p.M;
 #pragma unroll 1
@@ -331,22 +387,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const int col0 = tn * BN + c * 32;
                 if (!row_ok || col0 >= p.N) continue;
                 const float alpha = p.alpha;
-                if (p.mode == kGemmReduceScatter) {
-                    const int owner = static_cast<int>(row / p.rows_per_rank);
-                    const long long lrow = row - static_cast<long long>(owner) * p.rows_per_rank;
-                    __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.pt.base[owner] + p.stage_off) +
-                                          (static_cast<long long>(p.pt.rank) * p.rows_per_rank + lrow) * p.N + col0;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (col0 + j * 8 >= p.N) break;
-                        uint4 o;
-                        o.x = pack_bf16(__uint_as_float(r[j * 8 + 0]) * alpha, __uint_as_float(r[j * 8 + 1]) * alpha);
-                        o.y = pack_bf16(__uint_as_float(r[j * 8 + 2]) * alpha, __uint_as_float(r[j * 8 + 3]) * alpha);
-                        o.z = pack_bf16(__uint_as_float(r[j * 8 + 4]) * alpha, __uint_as_float(r[j * 8 + 5]) * alpha);
-                        o.w = pack_bf16(__uint_as_float(r[j * 8 + 6]) * alpha, __uint_as_float(r[j * 8 + 7]) * alpha);
-                        *reinterpret_cast<uint4*>(drow + j * 8) = o;
-                    }
-                } else if (p.epi == CAI_EPI_BF16 || p.epi == CAI_EPI_BF16_RESIDUAL) {
+                if (p.epi == CAI_EPI_BF16 || p.epi == CAI_EPI_BF16_RESIDUAL) {
                     __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
                     const __nv_bfloat16* rrow =
                         p.epi == CAI_EPI_BF16_RESIDUAL
@@ -394,22 +435,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-            if (p.mode == kGemmReduceScatter) {
-                // every row of the tile is on its way to the owner: order the peer stores of all
-                // four epilogue warps before the flag that announces the tile
-                __threadfence_system();
-                bar_sync_epilogue();
-                if (warp == 2 && lane == 0) {
-                    const int blocks_per_rank = p.rows_per_rank / kBM;
-                    const int owner = tm / blocks_per_rank;
-                    const uint32_t slot = static_cast<uint32_t>((tm - owner * blocks_per_rank) * p.tiles_n + tn);
-                    st_release_sys(sig_word(p.pt, owner, p.group_kind, kSigTile + p.pt.rank * kSigTileSlots + slot), epoch);
-                }
             }
+        }
+        if constexpr (RS) {
+            // the last tile's stores: wait for completion, then announce it
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            fence_proxy_async_all();
+            __threadfence_system();
+            bar_sync_epilogue();
+            if (warp == 2 && lane == 0 && rs_prev_owner >= 0)
+                st_release_sys(sig_word(p.pt, rs_prev_owner, p.group_kind, kSigTile + p.pt.rank * kSigTileSlots + rs_prev_slot), epoch);
         }
     }
 
-    if (p.mode == kGemmReduceScatter) {
+    if constexpr (RS) {
         // ---------------- reduce phase: sum the partials of all members for tiles of my rows
         __shared__ int red_ok;
         __syncthreads();
@@ -427,27 +466,52 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             __syncthreads();
             if (!red_ok) break;
             const int mb = item / p.tiles_n, tn = item - mb * p.tiles_n;
-            const int vec_cols = BN / 8;
-            for (int u = threadIdx.x; u < kBM * vec_cols; u += kGemmThreads) {
-                const int rr = u / vec_cols, cc = (u - rr * vec_cols) * 8;
-                const long long lrow = static_cast<long long>(mb) * kBM + rr;
-                const int col = tn * BN + cc;
-                if (lrow >= p.rows_per_rank || col >= p.N) continue;
-                float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                for (int src = 0; src < p.pt.size; ++src) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(stage + (static_cast<long long>(src) * p.rows_per_rank + lrow) * p.N + col);
-                    acc8[0] += bf16_lo(v.x); acc8[1] += bf16_hi(v.x); acc8[2] += bf16_lo(v.y); acc8[3] += bf16_hi(v.y);
-                    acc8[4] += bf16_lo(v.z); acc8[5] += bf16_hi(v.z); acc8[6] += bf16_lo(v.w); acc8[7] += bf16_hi(v.w);
+            constexpr int vec_cols = BN / 8;
+            constexpr int kUnits = kBM * vec_cols;
+            // four independent units per thread and iteration keep enough loads in flight
+            for (int u0 = threadIdx.x; u0 < kUnits; u0 += kGemmThreads * 4) {
+                uint4 part[4][kMaxPeers];
+                uint4 res[4];
+                bool live[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int u = u0 + k * kGemmThreads;
+                    const int rr = u / vec_cols, cc = (u - rr * vec_cols) * 8;
+                    const long long lrow = static_cast<long long>(mb) * kBM + rr;
+                    const int col = tn * BN + cc;
+                    live[k] = u < kUnits && lrow < p.rows_per_rank && col < p.N;
+                    if (!live[k]) continue;
+#pragma unroll
+                    for (int src = 0; src < kMaxPeers; ++src)
+                        if (src < p.pt.size)
+                            part[k][src] = *reinterpret_cast<const uint4*>(stage + (static_cast<long long>(src) * p.rows_per_rank + lrow) * p.N + col);
+                    if (p.R) res[k] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.R) + lrow * p.ldr + col);
                 }
-                if (p.R) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.R) + lrow * p.ldr + col);
-                    acc8[0] += bf16_lo(v.x); acc8[1] += bf16_hi(v.x); acc8[2] += bf16_lo(v.y); acc8[3] += bf16_hi(v.y);
-                    acc8[4] += bf16_lo(v.z); acc8[5] += bf16_hi(v.z); acc8[6] += bf16_lo(v.w); acc8[7] += bf16_hi(v.w);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (!live[k]) continue;
+                    const int u = u0 + k * kGemmThreads;
+                    const int rr = u / vec_cols, cc = (u - rr * vec_cols) * 8;
+                    const long long lrow = static_cast<long long>(mb) * kBM + rr;
+                    const int col = tn * BN + cc;
+                    float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int src = 0; src < kMaxPeers; ++src)
+                        if (src < p.pt.size) {
+                            const uint4 v = part[k][src];
+                            acc8[0] += bf16_lo(v.x); acc8[1] += bf16_hi(v.x); acc8[2] += bf16_lo(v.y); acc8[3] += bf16_hi(v.y);
+                            acc8[4] += bf16_lo(v.z); acc8[5] += bf16_hi(v.z); acc8[6] += bf16_lo(v.w); acc8[7] += bf16_hi(v.w);
+                        }
+                    if (p.R) {
+                        const uint4 v = res[k];
+                        acc8[0] += bf16_lo(v.x); acc8[1] += bf16_hi(v.x); acc8[2] += bf16_lo(v.y); acc8[3] += bf16_hi(v.y);
+                        acc8[4] += bf16_lo(v.z); acc8[5] += bf16_hi(v.z); acc8[6] += bf16_lo(v.w); acc8[7] += bf16_hi(v.w);
+                    }
+                    uint4 o;
+                    o.x = pack_bf16(acc8[0], acc8[1]); o.y = pack_bf16(acc8[2], acc8[3]);
+                    o.z = pack_bf16(acc8[4], acc8[5]); o.w = pack_bf16(acc8[6], acc8[7]);
+                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + lrow * p.ldc + col) = o;
                 }
-                uint4 o;
-                o.x = pack_bf16(acc8[0], acc8[1]); o.y = pack_bf16(acc8[2], acc8[3]);
-                o.z = pack_bf16(acc8[4], acc8[5]); o.w = pack_bf16(acc8[6], acc8[7]);
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + lrow * p.ldc + col) = o;
             }
             __syncthreads();
         }
@@ -461,14 +525,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool RS>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int sms,
                        cudaStream_t stream) {
-    constexpr int smem_bytes = STAGES * (kAStageBytes + BN * kBK * 2) + 1024 + 256;
+    constexpr int smem_bytes = STAGES * (kAStageBytes + BN * kBK * 2) + 1024 + 256 + (RS ? 4 * 32 * (BN * 2 + 16) : 0);
     static bool configured[64] = {};
     const int dev = current_device();
     if (!configured[dev & 63]) {
-        if (cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES, RS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  smem_bytes) != cudaSuccess) {
             set_last_error("cudaFuncSetAttribute(gemm) failed: %s", cudaGetErrorString(cudaGetLastError()));
             return CAI_K_CUDA;
@@ -486,7 +550,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
         set_last_error("gemm_rs: too many tiles per member for the signal block");
         return CAI_K_BAD_ARG;
     }
-    gemm_bf16_kernel<BN, STAGES><<<grid, kGemmThreads, smem_bytes, stream>>>(tmA, tmB, p);
+    gemm_bf16_kernel<BN, STAGES, RS><<<grid, kGemmThreads, smem_bytes, stream>>>(tmA, tmB, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         set_last_error("gemm launch failed: %s", cudaGetErrorString(e));
@@ -521,8 +585,12 @@ static int gemm_dispatch(const void* A, const void* B, long long lda, long long 
     else ok = encode_tmap_2d(&tmB, B, K, N, ldb, 64, kBK, 2);
     if (!ok) return CAI_K_BAD_ARG;
     p.status = status_words(dev);
-    if (BN == 256) return launch_gemm<256, 4>(tmA, tmB, p, sms, st);
-    return launch_gemm<128, 6>(tmA, tmB, p, sms, st);
+    if (p.mode == kGemmReduceScatter) {
+        if (BN == 256) return launch_gemm<256, 3, true>(tmA, tmB, p, sms, st);
+        return launch_gemm<128, 5, true>(tmA, tmB, p, sms, st);
+    }
+    if (BN == 256) return launch_gemm<256, 4, false>(tmA, tmB, p, sms, st);
+    return launch_gemm<128, 6, false>(tmA, tmB, p, sms, st);
 }
 
 static void plain_params(GemmParams& p) {

@@ -67,26 +67,20 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 constexpr int kNormThreads = 256;
 constexpr int kNormWarpCols = 2048;  // columns one warp covers: 32 lanes x 8 chunks x 8 elements
 
+// Backward, input gradient: dx (+)= rr * dy * g - rr^3 * x * sum(dy * g * x) / H. A row is handled
+// by R = ceil(H / 2048) warps that keep their slice of x and dy in registers (each tensor is read
+// once); a CTA of 8 warps works on 8 / R rows at a time.
 static __global__ void __launch_bounds__(kNormThreads)
-rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g,
-                   const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dy,
-                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dg_partial, int rows, int H,
-                   int dx_acc, int R) {
-    extern __shared__ float dg_s[];  // [H] gain-gradient partial of this CTA
+rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g,
+                      const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dy,
+                      __nv_bfloat16* __restrict__ dx, int rows, int H, int dx_acc, int R) {
     __shared__ float part[8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int groups = 8 / R;
     const int grp = warp / R, sub = warp - grp * R;
     const bool active = grp < groups;
     const int col0 = sub * kNormWarpCols;
-    for (int i = threadIdx.x; i < H; i += kNormThreads) dg_s[i] = 0.f;
-    float dg[8][8];
-#pragma unroll
-    for (int c = 0; c < 8; ++c)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) dg[c][e] = 0.f;
     const uint4* gr = reinterpret_cast<const uint4*>(g);
-    __syncthreads();
     for (long long base = static_cast<long long>(blockIdx.x) * groups; base < rows; base += static_cast<long long>(gridDim.x) * groups) {
         const long long row = base + grp;
         const bool live = active && row < rows;
@@ -143,26 +137,38 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                     for (int e = 0; e < 8; ++e) {
                         const float v = rr * df[e] * gf[e] - k3 * xf[e];
                         o[e] = dx_acc ? o[e] + v : v;
-                        dg[c][e] += df[e] * xf[e] * rr;
                     }
                     dxr[col >> 3] = pack8(o);
                 }
             }
         }
     }
-    if (active) {
+}
+
+// Backward, gain gradient: partial[part][col] = sum over the part's rows of dy * x * rstd. Threads
+// own columns (coalesced 16-byte loads), CTAs own row ranges; x and dy were just streamed by the dx
+// kernel, so this second sweep is mostly served from L2.
+static __global__ void __launch_bounds__(256)
+rmsnorm_bwd_dg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ rstd,
+                      const __nv_bfloat16* __restrict__ dy, float* __restrict__ dg_partial, int rows, int H,
+                      int rows_per_part) {
+    const long long r0 = static_cast<long long>(blockIdx.x) * rows_per_part;
+    const long long r1 = r0 + rows_per_part < rows ? r0 + rows_per_part : rows;
+    for (int c = threadIdx.x; c < (H >> 3); c += 256) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (long long r = r0; r < r1; ++r) {
+            float xf[8], df[8];
+            unpack8(reinterpret_cast<const uint4*>(x + r * H)[c], xf);
+            unpack8(reinterpret_cast<const uint4*>(dy + r * H)[c], df);
+            const float rr = rstd[r];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            const int col = col0 + (c * 32 + lane) * 8;
-            if (col < H) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) atomicAdd(&dg_s[col + e], dg[c][e]);
-            }
+            for (int e = 0; e < 8; ++e) acc[e] += df[e] * xf[e] * rr;
         }
+        float4* o = reinterpret_cast<float4*>(dg_partial + static_cast<long long>(blockIdx.x) * H + c * 8);
+        o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
-    __syncthreads();
-    float* out = dg_partial + static_cast<long long>(blockIdx.x) * H;
-    for (int i = threadIdx.x; i < H; i += kNormThreads) out[i] = dg_s[i];
 }
 
 // out[col] (+)= sum over parts of parts[p][col]. A block covers 32 columns; its 8 warps split the
@@ -191,6 +197,27 @@ reduce_parts_kernel(const float* __restrict__ parts, float* __restrict__ out, in
         for (int k = 0; k < 8; ++k) s += acc[k][lane];
         out[col] = accumulate ? out[col] + s : s;
     }
+}
+
+// Host side of RMSNorm backward, shared by the entry points: `scratch` holds at most `parts_cap`
+// rows of H floats. Returns a cudaError_t-style 0 / non-zero.
+static inline int launch_rmsnorm_bwd(const void* x, const void* g, const float* rstd, const void* dy, void* dx, float* dg,
+                                     float* scratch, int parts_cap, int sms, int rows, int H, int dx_accumulate,
+                                     int dg_accumulate, cudaStream_t st) {
+    const int R = (H + kNormWarpCols - 1) / kNormWarpCols;
+    const int groups = 8 / R;
+    const long long want = (static_cast<long long>(rows) + groups - 1) / groups;
+    const int grid = static_cast<int>(want < sms * 8LL ? want : sms * 8LL);
+    rmsnorm_bwd_dx_kernel<<<grid, kNormThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(g),
+                                                        rstd, static_cast<const __nv_bfloat16*>(dy),
+                                                        static_cast<__nv_bfloat16*>(dx), rows, H, dx_accumulate, R);
+    int parts = rows < parts_cap ? rows : parts_cap;
+    const int rows_per_part = (rows + parts - 1) / parts;
+    parts = (rows + rows_per_part - 1) / rows_per_part;
+    rmsnorm_bwd_dg_kernel<<<parts, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rstd, static_cast<const __nv_bfloat16*>(dy),
+                                                 scratch, rows, H, rows_per_part);
+    reduce_parts_kernel<<<(H + 31) / 32, 256, 0, st>>>(scratch, dg, parts, H, dg_accumulate);
+    return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 
 }  // namespace cai

@@ -429,18 +429,15 @@ CAI_API int cai_rmsnorm_bwd(const void* x, const void* g, const float* rstd, con
                             void* stream) {
     if (rows <= 0) return CAI_K_OK;
     const int R = norm_row_warps(H);
-    if ((H & 7) || R > 8 || H * 4 > 48 * 1024) {
-        set_last_error("rmsnorm_bwd: H must be a multiple of 8 and <= 12288");
+    if ((H & 7) || R > 8) {
+        set_last_error("rmsnorm_bwd: H must be a multiple of 8 and <= 16384");
         return CAI_K_BAD_ARG;
     }
-    const int parts = cai_rmsnorm_bwd_parts(rows);
-    rmsnorm_bwd_kernel<<<parts, kNormThreads, H * sizeof(float), (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)g, rstd, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx,
-        dg_partial, rows, H, dx_accumulate, R);
-    CAI_LAUNCH_CHECK("rmsnorm_bwd");
-    reduce_parts_kernel<<<(H + 31) / 32, 256, 0, (cudaStream_t)stream>>>(dg_partial, dg, parts, H,
-                                                                             dg_accumulate);
-    CAI_LAUNCH_CHECK("rmsnorm_bwd_reduce");
+    if (launch_rmsnorm_bwd(x, g, rstd, dy, dx, dg, dg_partial, cai_rmsnorm_bwd_parts(rows), sm_count(current_device()), rows,
+                           H, dx_accumulate, dg_accumulate, (cudaStream_t)stream) != 0) {
+        set_last_error("rmsnorm_bwd launch failed");
+        return CAI_K_CUDA;
+    }
     return CAI_K_OK;
 }
 

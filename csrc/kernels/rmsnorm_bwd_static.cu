@@ -44,20 +44,10 @@ CAI_API int cai_rmsnorm_bwd_static(const void* x, const void* g, const float* rs
         g_scratch_addr[dev] = p;
     }
     float* scratch = g_scratch_addr[dev];
-    const int R = (H + kNormWarpCols - 1) / kNormWarpCols;
-    const int parts = rows < CAI_RMSNORM_STATIC_PARTS ? rows : CAI_RMSNORM_STATIC_PARTS;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // every CTA writes its whole row of the scratch before the reduction reads rows [0, parts)
-    rmsnorm_bwd_kernel<<<parts, kNormThreads, H * sizeof(float), st>>>(
-        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(g), rstd,
-        static_cast<const __nv_bfloat16*>(dy), static_cast<__nv_bfloat16*>(dx), scratch, rows, H, dx_accumulate, R);
-    if (cudaGetLastError() != cudaSuccess) {
+    // the gain-gradient kernel writes rows [0, parts) of the scratch in full before the reduction reads them
+    if (launch_rmsnorm_bwd(x, g, rstd, dy, dx, dg, scratch, CAI_RMSNORM_STATIC_PARTS, sm_count(dev), rows, H, dx_accumulate,
+                           dg_accumulate, static_cast<cudaStream_t>(stream)) != 0) {
         set_last_error("rmsnorm_bwd_static: launch failed");
-        return CAI_K_CUDA;
-    }
-    reduce_parts_kernel<<<(H + 31) / 32, 256, 0, st>>>(scratch, dg, parts, H, dg_accumulate);
-    if (cudaGetLastError() != cudaSuccess) {
-        set_last_error("rmsnorm_bwd_static: reduction launch failed");
         return CAI_K_CUDA;
     }
     return CAI_K_OK;

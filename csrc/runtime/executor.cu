@@ -267,7 +267,7 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
                 const int T = x.i[0], N = x.i[1], K = x.i[2];
                 return cai_fused_ag_gemm(pt, group, ex->tensors[x.t[0]].offset, ex->ld(x.t[0]), P(3), P(1), P(2), T, N, K,
                                          ex->ld(x.t[1]), ex->ld(x.t[2]), (x.flags >> 1) & 1, T / pt.size, epoch_base, seq,
-                                         ex->ag_copy_ctas, st);
+                                         ex->ag_copy_ctas < 4 * pt.size ? ex->ag_copy_ctas : 4 * pt.size, st);
             }
             if (x.kernel == K_GEMM_RS) {
                 const int T = x.i[0], N = x.i[1], K = x.i[2];
@@ -320,7 +320,7 @@ int replay(cai_exec* ex) {
         {
             // kernels of this library behind the op (memsets and NCCL calls are not ours)
             const uint16_t k = ex->exec[op.exec - 1].kernel;
-            ex->launches += (k == K_ATTN_BWD || k == K_CROSS_ENTROPY_TP) ? 3 : k == K_RMSNORM_BWD ? 2 : (k == K_ZERO || (k >= K_NCCL_ALL_REDUCE && k <= K_NCCL_RECV)) ? 0 : 1;
+            ex->launches += (k == K_ATTN_BWD || k == K_CROSS_ENTROPY_TP || k == K_RMSNORM_BWD) ? 3 : (k == K_ZERO || (k >= K_NCCL_ALL_REDUCE && k <= K_NCCL_RECV)) ? 0 : 1;
         }
         if (tr) cudaEventRecord(tr->stop, st);
     }
