@@ -1,5 +1,6 @@
-"""A plain PyTorch restatement of the dense decoder the plans execute (RMSNorm, RoPE, causal GQA
-attention, SwiGLU, tied LM head, mean next-token cross-entropy).
+"""A plain PyTorch restatement of the decoder the plans execute (RMSNorm, RoPE, causal GQA
+attention, SwiGLU or a softmax top-k mixture of SwiGLU experts, tied LM head, mean next-token
+cross-entropy).
 
 It is the fp32 reference that GPU tests compare the engine against: it reads the engine's own
 parameters, so both sides start from identical weights. It is never on a hot path.
@@ -22,8 +23,30 @@ def rope(x, seq, theta):
     return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1)
 
 
+def moe_ffn(h, wr, wgu, wd, top_k):
+    """Mixture of experts without capacity drops. h [..., H]; wr [E, H]; wgu [E*2F, H] (per expert:
+    gate rows then up rows); wd [E*H, F]. Weights are the softmax probabilities of the chosen
+    experts renormalised over the chosen k."""
+    E, H = wr.shape
+    F_ = wd.shape[1]
+    flat = h.reshape(-1, H)
+    prob = torch.softmax(flat @ wr.t(), -1)
+    top_p, top_e = prob.topk(top_k, -1)
+    top_w = top_p / top_p.sum(-1, keepdim=True)
+    out = torch.zeros_like(flat)
+    wgu, wd = wgu.view(E, 2 * F_, H), wd.view(E, H, F_)
+    for e in range(E):
+        tok, slot = (top_e == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        g, u = (flat[tok] @ wgu[e].t()).chunk(2, -1)
+        y = (F.silu(g) * u) @ wd[e].t()
+        out = out.index_add(0, tok, y * top_w[tok, slot, None])
+    return out.view_as(h)
+
+
 def forward_loss(params: dict, tokens, targets, *, layers, heads, kv_heads, head_dim, seq, eps, theta,
-                 dtype=torch.float32):
+                 dtype=torch.float32, top_k=0):
     """params: name -> tensor (``embed``, ``L{i}.g1/wqkv/wo/g2/wgu/wd``, ``gf``, optional ``lm_head``).
     tokens / targets: int64 [B, S]. Returns the mean cross-entropy."""
     B, S = tokens.shape
@@ -52,6 +75,9 @@ def forward_loss(params: dict, tokens, targets, *, layers, heads, kv_heads, head
         a = a.transpose(1, 2).reshape(B, S, heads * head_dim)
         x = x + a @ p[pre + "wo"].t()
         h = norm(x, p[pre + "g2"])
+        if pre + "wr" in p:
+            x = x + moe_ffn(h, p[pre + "wr"], p[pre + "experts.wgu"], p[pre + "experts.wd"], top_k)
+            continue
         gu = h @ p[pre + "wgu"].t()
         g, u = gu.chunk(2, -1)
         x = x + (F.silu(g) * u) @ p[pre + "wd"].t()

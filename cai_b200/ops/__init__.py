@@ -21,12 +21,16 @@ def _p(t):
 
 
 def gemm(a, b, *, trans_a=False, trans_b=False, out=None, out_dtype=torch.bfloat16, accumulate=False,
-         residual=None, alpha=1.0, sm_limit=0):
+         residual=None, alpha=1.0, sm_limit=0, seg_counts=None, seg_rows=0, seg_mode=0):
     """``C[M,N] = alpha * op(A) @ op(B)^T`` on the tcgen05 tensor cores.
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` with ``trans_a``); ``b`` is ``[N,K]`` (or ``[K,N]`` with
     ``trans_b``). With ``out_dtype=torch.float32`` and ``accumulate`` the product is added to
     ``out``; ``residual`` (bf16 ``[M,N]``) is added in the epilogue.
+
+    Ragged form (expert slabs): ``seg_counts`` (int32, one entry per ``seg_rows`` rows) gives the
+    live rows of each sub-slab of M (``seg_mode=1``: tiles past the count are neither computed nor
+    written) or of K (``seg_mode=2``: k-blocks past the count are skipped).
     """
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
     assert a.stride(1) == 1 and b.stride(1) == 1
@@ -50,9 +54,37 @@ def gemm(a, b, *, trans_a=False, trans_b=False, out=None, out_dtype=torch.bfloat
         assert out.dtype == torch.float32 and residual is None
         epi = EPI_F32_ACCUM if accumulate else EPI_F32
     ldr = residual.stride(0) if residual is not None else 0
+    if seg_counts is not None:
+        assert seg_counts.dtype == torch.int32 and seg_mode in (1, 2) and seg_rows > 0
+        check(lib().cai_gemm_bf16_seg(_p(a), _p(b), _p(out), _p(residual), M, N, K, a.stride(0), b.stride(0),
+                                      out.stride(0), ldr, int(trans_a), int(trans_b), epi, float(alpha),
+                                      _p(seg_counts), int(seg_rows), int(seg_mode), int(sm_limit), _stream()), "gemm_seg")
+        return out
     check(lib().cai_gemm_bf16(_p(a), _p(b), _p(out), _p(residual), M, N, K, a.stride(0), b.stride(0),
                               out.stride(0), ldr, int(trans_a), int(trans_b), epi, float(alpha),
                               int(sm_limit), _stream()), "gemm")
+    return out
+
+
+def moe_route_fwd(logits, k, cap):
+    """Softmax top-k router. logits f32 ``[T,E]``. Returns ``idx`` int32 ``[T,k]``, ``w`` f32 ``[T,k]``
+    (renormalised over the chosen k), ``pos`` int32 ``[T,k]`` (slot in the expert's slab, -1 when
+    the expert already holds ``cap`` tokens) and ``counts`` int32 ``[E]``."""
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    idx = torch.empty(T, k, device=logits.device, dtype=torch.int32)
+    pos = torch.empty_like(idx)
+    w = torch.empty(T, k, device=logits.device, dtype=torch.float32)
+    counts = torch.empty(E, device=logits.device, dtype=torch.int32)
+    check(lib().cai_moe_route_fwd(_p(logits), _p(idx), _p(w), _p(pos), _p(counts), T, E, k, int(cap), _stream()), "moe_route_fwd")
+    return idx, w, pos, counts
+
+
+def moe_route_bwd(logits, idx, dw, pos):
+    """Gradient of the router logits (bf16 ``[T,E]``) from the gradient of the combine weights."""
+    T, E = logits.shape
+    out = torch.empty(T, E, device=logits.device, dtype=torch.bfloat16)
+    check(lib().cai_moe_route_bwd(_p(logits), _p(idx), _p(dw), _p(pos), _p(out), T, E, idx.shape[1], _stream()), "moe_route_bwd")
     return out
 
 

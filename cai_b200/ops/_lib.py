@@ -35,6 +35,14 @@ def _declare(L):
     L.cai_status_read.argtypes = [I]
     L.cai_sm_count.argtypes = []
     L.cai_gemm_bf16.argtypes = [P, P, P, P, I, I, I, LL, LL, LL, LL, I, I, I, F, I, P]
+    L.cai_gemm_bf16_seg.argtypes = [P, P, P, P, I, I, I, LL, LL, LL, LL, I, I, I, F, P, I, I, I, P]
+    L.cai_moe_route_fwd.argtypes = [P, P, P, P, P, I, I, I, I, P]
+    L.cai_moe_route_bwd.argtypes = [P, P, P, P, P, I, I, I, P]
+    ULL = ctypes.c_ulonglong
+    L.cai_signal_block_bytes.restype = ULL
+    L.cai_signal_block_bytes.argtypes = []
+    L.cai_moe_dispatch_c.argtypes = [P, I, I, ULL, P, P, P, P, P, ULL, ULL, I, I, I, I, I, P, ctypes.c_uint32, P, P]
+    L.cai_moe_combine_c.argtypes = [P, I, I, ULL, P, P, P, P, P, ULL, P, P, I, I, I, I, I, I, P, ctypes.c_uint32, P]
     L.cai_rmsnorm_fwd.argtypes = [P, P, P, P, I, I, F, P]
     L.cai_rmsnorm_bwd_parts.argtypes = [I]
     L.cai_rmsnorm_bwd.argtypes = [P, P, P, P, P, P, P, I, I, I, I, P]

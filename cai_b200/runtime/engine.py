@@ -221,6 +221,11 @@ class Engine:
         tp_id = self.rank % tp
         H, hd = m.hidden_size, m.head_dim
         base = name.split(".")[-1]
+        if ".experts." in name:
+            # local experts are a contiguous block of rows of the all-experts tensor
+            ep = max(1, self.hdr.ep)
+            ep_id = (self.rank // (self.hdr.tp * self.hdr.num_stages * self.hdr.cp)) % ep
+            return (rows * ep, cols), (slice(ep_id * rows, (ep_id + 1) * rows), slice(None))
         if base in ("embed", "lm_head"):
             return (m.vocab_size, H), (slice(tp_id * rows, (tp_id + 1) * rows), slice(None))
         if base == "wqkv":
@@ -248,9 +253,15 @@ class Engine:
         n_opt = int(self.plan.xhdr.opt_elems)
         master = self.view("@flat_master")
         dp, dp_id = self.hdr.dp, self.rank // (self.hdr.tp * self.hdr.num_stages * self.hdr.cp)
-        sharded = dp > 1 and n_opt < n_flat   # optimizer state split over the data-parallel group
-        shard_lo = dp_id * n_opt if sharded else 0
-        shard_hi = min(shard_lo + n_opt, n_flat) if sharded else n_flat
+        # [0, n_rep) of the flat space is replicated over the data-parallel group (optimizer state
+        # possibly sharded, n_shard elements per rank); [n_rep, n_flat) holds this rank's own experts,
+        # whose state follows the shard in the optimizer buffers.
+        split = self.named.get("@flat_split")
+        n_rep = int(split.flat_off512) * 512 if split is not None else n_flat
+        n_shard = int(split.rows) * 512 if split is not None else n_opt
+        sharded = dp > 1 and n_shard < n_rep   # optimizer state split over the data-parallel group
+        shard_lo = dp_id * n_shard if sharded else 0
+        shard_hi = min(shard_lo + n_shard, n_rep) if sharded else n_rep
         with torch.cuda.stream(self.stream):
             self.view("@flat_m").zero_()
             self.view("@flat_v").zero_()
@@ -276,6 +287,9 @@ class Engine:
                 # fp32 master copy of the part of this tensor that falls into this rank's optimizer shard
                 lo = nt.flat_off512 * 512
                 hi = lo + nt.rows * nt.cols
+                if lo >= n_rep:
+                    master[n_shard + lo - n_rep:n_shard + hi - n_rep].copy_(full.reshape(-1))
+                    continue
                 a, b = max(lo, shard_lo), min(hi, shard_hi)
                 if a < b:
                     master[a - shard_lo:b - shard_lo].copy_(full.reshape(-1)[a - lo:b - lo])

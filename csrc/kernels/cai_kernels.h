@@ -37,6 +37,17 @@ CAI_API int cai_gemm_bf16(const void* A, const void* B, void* C, const void* R, 
                           long long lda, long long ldb, long long ldc, long long ldr, int a_mn_major,
                           int b_mn_major, int epi, float alpha, int sm_limit, void* stream);
 
+/* Same product over ragged slabs (expert buffers of a mixture-of-experts layer). The segmented
+ * dimension is cut into slabs of seg_rows rows (a multiple of 128); only the first
+ * seg_counts[slab] rows of a slab hold data (device array). seg_mode 1: M is segmented, output
+ * tiles past a slab's count are neither computed nor written. seg_mode 2: K is segmented (weight
+ * gradient), k-blocks past a slab's count are skipped; rows between the count and the next multiple
+ * of 64 must be zero in A and B. */
+CAI_API int cai_gemm_bf16_seg(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                              long long lda, long long ldb, long long ldc, long long ldr, int a_mn_major,
+                              int b_mn_major, int epi, float alpha, const int* seg_counts, int seg_rows, int seg_mode,
+                              int sm_limit, void* stream);
+
 /* ---- normalisation (reference: src/cuda/cai_kernels.cu:37-77, src/refmodel.c:47-77) */
 /* y = x * rsqrt(mean(x^2)+eps) * g ; rstd[row] saved for backward. */
 CAI_API int cai_rmsnorm_fwd(const void* x, const void* g, void* y, float* rstd, int rows, int H, float eps,

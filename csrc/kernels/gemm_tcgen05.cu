@@ -53,7 +53,19 @@ struct GemmParams {
     __nv_bfloat16* a_full;           // all-gather: local buffer that receives every member's rows
     long long ld_src;
     PeerTable pt;
+    // ---- ragged segments (expert slabs of a mixture-of-experts layer): the segmented dimension is
+    // cut into slabs of seg_rows rows of which only the first seg_counts[slab] hold data.
+    // seg_mode 1: the M dimension is segmented, output tiles that start past a slab's count are skipped.
+    // seg_mode 2: the K dimension is segmented (weight gradient), k-blocks past a slab's count are skipped.
+    const int* seg_counts;
+    int seg_rows;
+    int seg_mode;
 };
+
+__device__ __forceinline__ bool seg_live(const GemmParams& p, int row0) {
+    const int slab = row0 / p.seg_rows;
+    return row0 - slab * p.seg_rows < p.seg_counts[slab];
+}
 
 constexpr int kGemmPlain = 0, kGemmAllGatherA = 1, kGemmReduceScatter = 2;
 
@@ -205,6 +217,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 int tm, tn;
                 tile_coords(p, tile, tm, tn);
                 const int m0 = tm * kBM, n0 = tn * BN;
+                if (p.seg_mode == 1 && !seg_live(p, m0)) continue;
                 if (p.mode == kGemmAllGatherA) {
                     // rows of this tile must have been staged by a copy CTA; they were written through
                     // the generic proxy, the TMA engine reads through the async proxy
@@ -228,6 +241,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     fence_proxy_async_all();
                 }
                 for (int kb = 0; kb < num_kb; ++kb) {
+                    if (p.seg_mode == 2 && !seg_live(p, kb * kBK)) continue;
                     if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, CAI_DEV_TIMEOUT_TMA_EMPTY)) {
                         ok = false;
                         break;
@@ -269,16 +283,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             uint32_t ph = 0;
             bool ok = true;
             int t = 0;
-            for (int tile = cta; tile < num_tiles && ok; tile += ncta, ++t) {
+            for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
+                if (p.seg_mode == 1) {
+                    int tm, tn;
+                    tile_coords(p, tile, tm, tn);
+                    if (!seg_live(p, tm * kBM)) continue;
+                }
                 const int acc = t & 1;
                 const uint32_t acc_ph = (t >> 1) & 1;
+                ++t;
                 if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag, p.status, CAI_DEV_TIMEOUT_TMEM_EMPTY)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
+                uint32_t started = 0;  // becomes 1 after the first MMA of the tile (which overwrites the accumulator)
                 for (int kb = 0; kb < num_kb; ++kb) {
+                    if (p.seg_mode == 2 && !seg_live(p, kb * kBK)) continue;
                     if (!mbar_wait(&full[s], ph, abort_flag, p.status, CAI_DEV_TIMEOUT_TMA_FULL)) {
                         ok = false;
                         break;
@@ -294,7 +316,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         const uint64_t bdesc =
                             p.b_mn ? umma_smem_desc_sw128(b_base + k * (kUmmaK * 128), kBK * 128, 1024)
                                    : umma_smem_desc_sw128(b_base + k * (kUmmaK * 2), 0, 1024);
-                        umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_f16_ss(d_tmem, adesc, bdesc, idesc, started);
+                        started = 1;
                     }
                     umma_commit(&empty[s]);
                     if (++s == STAGES) {
@@ -313,11 +336,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int rs_prev_owner = -1;
         uint32_t rs_prev_slot = 0;
         (void)rs_prev_owner; (void)rs_prev_slot;
-        for (int tile = cta; tile < num_tiles && ok; tile += ncta, ++t) {
+        for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
             int tm, tn;
             tile_coords(p, tile, tm, tn);
+            if (p.seg_mode == 1 && !seg_live(p, tm * kBM)) continue;
             const int acc = t & 1;
             const uint32_t acc_ph = (t >> 1) & 1;
+            ++t;
+            // a weight-gradient tile whose every k-block was skipped has an undefined accumulator: it counts as zero
+            bool acc_valid = true;
+            if (p.seg_mode == 2) {
+                acc_valid = false;
+                for (int kb = 0; kb < num_kb && !acc_valid; ++kb) acc_valid = seg_live(p, kb * kBK);
+            }
             if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag, p.status, CAI_DEV_TIMEOUT_TMEM_FULL)) {
                 ok = false;
                 break;
@@ -384,6 +415,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32;
                 tmem_ld_32x32(taddr, r);
                 tmem_ld_wait();
+                if (!acc_valid) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) r[e] = 0u;
+                }
                 const int col0 = tn * BN + c * 32;
                 if (!row_ok || col0 >= p.N) continue;
                 const float alpha = p.alpha;
@@ -598,6 +633,7 @@ static void plain_params(GemmParams& p) {
     p.group_kind = 0; p.n_copy = 0; p.rows_per_rank = 0; p.m_rot = 0;
     p.epoch_base = nullptr; p.seq = 0; p.src_off = 0; p.stage_off = 0; p.a_full = nullptr; p.ld_src = 0;
     p.pt = PeerTable{};
+    p.seg_counts = nullptr; p.seg_rows = 0; p.seg_mode = 0;
     p.R = nullptr; p.ldr = 0; p.alpha = 1.f; p.epi = CAI_EPI_BF16; p.a_mn = 0;
 }
 
@@ -608,7 +644,19 @@ using namespace cai;
 CAI_API int cai_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
                           long long lda, long long ldb, long long ldc, long long ldr, int a_mn_major,
                           int b_mn_major, int epi, float alpha, int sm_limit, void* stream) {
+    return cai_gemm_bf16_seg(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, a_mn_major, b_mn_major, epi, alpha, nullptr, 0, 0,
+                             sm_limit, stream);
+}
+
+CAI_API int cai_gemm_bf16_seg(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                              long long lda, long long ldb, long long ldc, long long ldr, int a_mn_major,
+                              int b_mn_major, int epi, float alpha, const int* seg_counts, int seg_rows, int seg_mode,
+                              int sm_limit, void* stream) {
     if (M <= 0 || N <= 0 || K <= 0) return CAI_K_OK;
+    if (seg_mode && (!seg_counts || seg_rows <= 0 || seg_rows % 128 || seg_mode > 2)) {
+        set_last_error("gemm: segmented form needs counts and a slab size that is a multiple of 128");
+        return CAI_K_BAD_ARG;
+    }
     if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 3) || epi < 0 || epi > CAI_EPI_BF16_RESIDUAL) {
         set_last_error("gemm: N, lda, ldb must be multiples of 8 (N=%d lda=%lld ldb=%lld ldc=%lld epi=%d)", N,
                        lda, ldb, ldc, epi);
@@ -631,6 +679,7 @@ CAI_API int cai_gemm_bf16(const void* A, const void* B, void* C, const void* R, 
     p.alpha = alpha;
     p.C = C; p.R = R;
     p.ldc = ldc; p.ldr = ldr;
+    p.seg_counts = seg_counts; p.seg_rows = seg_rows; p.seg_mode = seg_mode;
     return gemm_dispatch(A, B, lda, ldb, p, sm_limit, reinterpret_cast<cudaStream_t>(stream));
 }
 

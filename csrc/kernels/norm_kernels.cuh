@@ -208,15 +208,16 @@ static inline int launch_rmsnorm_bwd(const void* x, const void* g, const float* 
     const int groups = 8 / R;
     const long long want = (static_cast<long long>(rows) + groups - 1) / groups;
     const int grid = static_cast<int>(want < sms * 8LL ? want : sms * 8LL);
-    rmsnorm_bwd_dx_kernel<<<grid, kNormThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(g),
-                                                        rstd, static_cast<const __nv_bfloat16*>(dy),
-                                                        static_cast<__nv_bfloat16*>(dx), rows, H, dx_accumulate, R);
     int parts = rows < parts_cap ? rows : parts_cap;
     const int rows_per_part = (rows + parts - 1) / parts;
     parts = (rows + rows_per_part - 1) / rows_per_part;
     rmsnorm_bwd_dg_kernel<<<parts, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rstd, static_cast<const __nv_bfloat16*>(dy),
                                                  scratch, rows, H, rows_per_part);
     reduce_parts_kernel<<<(H + 31) / 32, 256, 0, st>>>(scratch, dg, parts, H, dg_accumulate);
+    // dx last: callers may pass dx == dy (in place), and the gain gradient needs the unmodified dy
+    rmsnorm_bwd_dx_kernel<<<grid, kNormThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(g),
+                                                        rstd, static_cast<const __nv_bfloat16*>(dy),
+                                                        static_cast<__nv_bfloat16*>(dx), rows, H, dx_accumulate, R);
     return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 

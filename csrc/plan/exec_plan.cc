@@ -56,10 +56,14 @@ struct Param {
     uint32_t rows = 0, cols = 0;
 };
 
-struct LayerParams { Param g1, wqkv, wo, g2, wgu, wd; };
+struct LayerParams { Param g1, wqkv, wo, g2, wgu, wd, wr; };  // MoE: wgu / wd stack the local experts, wr is the router
 
 // Saved activations of one layer for one in-flight microbatch.
-struct LayerActs { int x, rstd1, xn1, qkv, ao, lse, hmid, rstd2, xn2, gu, act; };
+struct LayerActs {
+    int x, rstd1, xn1, qkv, ao, lse, hmid, rstd2, xn2, gu, act;
+    // mixture-of-experts layers: router state and the expert slabs (gu / act above are slabs too)
+    int logits = -1, ridx = -1, rw = -1, rpos = -1, counts = -1, cnt_recv = -1, xs = -1, ys = -1;
+};
 
 struct Builder {
     const Config& cfg;
@@ -162,6 +166,16 @@ struct Builder {
         x.f[0] = 1.0f;
         push(OP_GEMM, stream, 2.0 * M * N * K, 0, 0, mb, &x);
     }
+    // GEMM over a ragged expert slab: `counts` holds the live rows of each `seg_rows`-row sub-slab.
+    // seg_mode 1 segments M (forward / input gradient), 2 segments K (weight gradient).
+    void gemm_seg(int A, int B, int C, uint32_t M, uint32_t N, uint32_t K, bool ta, bool tb, int epi, int counts,
+                  uint32_t seg_rows, int seg_mode, uint16_t mb) {
+        ExecOp x = xop(K_GEMM, static_cast<uint16_t>((ta ? 1 : 0) | (tb ? 2 : 0) | (epi << 4)));
+        x.t[0] = A; x.t[1] = B; x.t[2] = C; x.t[4] = counts;
+        x.i[0] = M; x.i[1] = N; x.i[2] = K; x.i[3] = seg_rows; x.i[4] = seg_mode;
+        x.f[0] = 1.0f;
+        push(OP_GEMM, ST_COMPUTE_HI, 2.0 * M * N * K, 0, 0, mb, &x);
+    }
     void rmsnorm_fwd(int x, int g, int y, int rstd, uint32_t rows, uint16_t mb) {
         ExecOp e = xop(K_RMSNORM_FWD);
         e.t[0] = x; e.t[1] = g; e.t[2] = y; e.t[3] = rstd;
@@ -252,7 +266,7 @@ void exec_operands(const ExecOp& x, std::vector<int>* reads, std::vector<int>* w
         case K_RMSNORM_BWD: R(0); R(1); R(2); R(3); if (x.i[2]) R(4); W(4); if (x.i[3]) R(5); W(5); W(6); break;
         case K_GEMM: {
             const int epi = x.flags >> 4;
-            R(0); R(1); if (epi == 2) R(2); R(3); W(2);
+            R(0); R(1); if (epi == 2) R(2); R(3); R(4); W(2);
             break;
         }
         case K_ROPE: R(0); R(1); W(0); break;
@@ -271,6 +285,11 @@ void exec_operands(const ExecOp& x, std::vector<int>* reads, std::vector<int>* w
         case K_AG_GEMM: R(0); R(1); W(2); W(3); break;
         case K_GEMM_RS: R(0); R(1); R(3); W(2); W(4); break;
         case K_RS_ADAMW: R(0); R(1); R(2); R(3); W(0); W(1); W(2); W(4); break;
+        case K_MOE_ROUTE:
+            if (x.flags & 1) { R(0); R(1); R(2); R(3); W(4); } else { R(0); W(1); W(2); W(3); W(4); }
+            break;
+        case K_MOE_DISPATCH_GEMM: R(0); R(1); R(2); R(3); R(4); W(5); W(6); break;
+        case K_MOE_GEMM_COMBINE: R(0); R(2); R(3); R(4); R(5); R(6); W(1); W(7); break;
         default:
             for (int i = 0; i < 8; ++i) { R(i); }
             break;
@@ -288,7 +307,14 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     out->train = cfg.train;
     out->model = m;
 
-    if (m.is_moe) return failf(err, ERR_INVALID, "executable plans for MoE models are built by the MoE planner");
+    const bool moe = m.is_moe != 0;
+    if (moe) {
+        if (d.tp != 1 || d.pp != 1) return failf(err, ERR_INVALID, "MoE plans need tp = 1 and pp = 1 (got tp=%u pp=%u)", d.tp, d.pp);
+        if (d.ep != 1 && d.ep != d.dp) return failf(err, ERR_INVALID, "MoE plans need ep = 1 or ep = dp (got ep=%u dp=%u)", d.ep, d.dp);
+        if (m.num_experts % 32 || m.num_experts > 256 || m.moe_top_k < 1 || m.moe_top_k > 8 || m.num_experts % d.ep)
+            return failf(err, ERR_INVALID, "MoE plans need experts %% 32 == 0 (<= 256), top_k <= 8, experts %% ep == 0");
+        if (!cfg.train.comm_mode) return failf(err, ERR_INVALID, "MoE plans exist only for comm = fused (in-kernel dispatch/combine)");
+    }
     if (d.cp != 1) return failf(err, ERR_INVALID, "context parallelism (cp>1) has no executable schedule");
     if (m.head_dim != 128) return failf(err, ERR_INVALID, "executable plans need head_dim = 128 (got %u)", m.head_dim);
     if (m.num_heads % d.tp || m.num_kv_heads % d.tp || m.ffn_hidden % d.tp || m.vocab_size % d.tp)
@@ -337,14 +363,30 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         L[l].wqkv = b.param(name("wqkv"), b.Cqkv, H, istd);
         L[l].wo = b.param(name("wo"), H, b.Hq_l, istd);
         L[l].g2 = b.param(name("g2"), 1, H, 0.f);
-        L[l].wgu = b.param(name("wgu"), 2 * b.F_l, H, istd);
-        L[l].wd = b.param(name("wd"), H, b.F_l, istd);
+        if (moe) {
+            L[l].wr = b.param(name("wr"), m.num_experts, H, istd);
+        } else {
+            L[l].wgu = b.param(name("wgu"), 2 * b.F_l, H, istd);
+            L[l].wd = b.param(name("wd"), H, b.F_l, istd);
+        }
     }
     if (b.last_stage) {
         gf = b.param("gf", 1, H, 0.f);
         if (!b.tied) head = b.param("lm_head", b.V_l, H, istd);
         else head = embed;
     }
+    // Expert weights come last in the flat space: everything before them is replicated over the
+    // data-parallel group (gradients are reduced), the experts of an expert-parallel group are not.
+    const uint32_t E_l = moe ? m.num_experts / d.ep : 0;
+    const uint64_t n_replicated = moe && d.ep > 1 ? align_up(b.flat_elems, kFlatAlignElems) : 0;
+    if (moe)
+        for (uint32_t l = 0; l < b.layers; ++l) {
+            char nm[40];
+            std::snprintf(nm, sizeof nm, "L%u.experts.wgu", base_layer + l);
+            L[l].wgu = b.param(nm, E_l * 2 * m.ffn_hidden, H, istd);
+            std::snprintf(nm, sizeof nm, "L%u.experts.wd", base_layer + l);
+            L[l].wd = b.param(nm, E_l * H, m.ffn_hidden, istd);
+        }
     const uint64_t n_flat = align_up(b.flat_elems, kFlatAlignElems);
     if (n_flat > 0x7FFFFFFFFFFFull) return failf(err, ERR_INVALID, "parameter space too large");
     b.flat_param = b.tensor_at(TC_PARAM, DT_BF16, 0, 1, static_cast<uint32_t>(std::min<uint64_t>(n_flat, 0xFFFFFFFFu)), 0);
@@ -356,7 +398,12 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     // optimizer state: master | m | v, each n_flat fp32 (sharded 1/dp when the optimizer is sharded)
     // sharded 1/dp only when the fused reduce-scatter + AdamW kernel owns the update; the NCCL baseline
     // all-reduces the gradients and every replica updates everything
-    const uint64_t n_opt = (d.dp > 1 && b.fused) ? align_up((n_flat + d.dp - 1) / d.dp, kFlatAlignElems) : n_flat;
+    // Expert weights of an expert-parallel group are not replicated: their optimizer state is local and
+    // sits behind the (possibly sharded) state of the replicated parameters.
+    const uint64_t n_rep = n_replicated ? n_replicated : n_flat;
+    const uint64_t n_exp = n_flat - n_rep;
+    const uint64_t n_shard = (d.dp > 1 && b.fused) ? align_up((n_rep + d.dp - 1) / d.dp, kFlatAlignElems) : n_rep;
+    const uint64_t n_opt = n_shard + n_exp;
     b.flat_master = b.tensor_at(TC_OPTSTATE, DT_FP32, 0, 1, 0, 0);
     b.flat_m = b.tensor_at(TC_OPTSTATE, DT_FP32, n_opt * 4, 1, 0, 0);
     b.flat_v = b.tensor_at(TC_OPTSTATE, DT_FP32, n_opt * 8, 1, 0, 0);
@@ -364,6 +411,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     b.cursor[TC_OPTSTATE] = n_opt * 12;
     out->xhdr.param_elems = n_flat;
     out->xhdr.reserved = n_opt;
+    const uint64_t hdr_n_rep = n_rep, hdr_n_shard = n_shard;
 
     // ---------------- inputs, workspace
     const int tokens = b.tensor(TC_COMM, DT_INT32, ga, T);
@@ -390,6 +438,41 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     const int ce_scratch = (b.last_stage && tp > 1) ? b.tensor(TC_WORKSPACE, DT_FP32, 2, chunk) : -1;
     if (b.last_stage && tp > 1) dhf_full = dfull;
 
+    // Mixture of experts: every member keeps, per local expert and per source member, a slab of
+    // `moe_cap` rows (capacity factor x the even share); tokens beyond a slab's capacity skip that expert.
+    const uint32_t moe_cap = moe ? static_cast<uint32_t>(align_up(
+        static_cast<uint64_t>(std::max(1.0, cfg.train.moe_capacity_factor_x100 / 100.0) * T * m.moe_top_k / m.num_experts + 0.999), 128)) : 0;
+    const uint32_t moe_rows = moe ? E_l * d.ep * moe_cap : 0;
+    int dy_s = -1, dact_s = -1, dgu_s = -1, dx_s = -1, dw_r = -1, dlogits = -1;
+    if (moe) {
+        dy_s = b.tensor(TC_COMM, DT_BF16, moe_rows, H);        // gradient rows pushed by the token owners
+        dx_s = b.tensor(TC_COMM, DT_BF16, moe_rows, H);        // input gradients pulled back by the token owners
+        dact_s = b.tensor(TC_WORKSPACE, DT_BF16, moe_rows, m.ffn_hidden);
+        dgu_s = b.tensor(TC_WORKSPACE, DT_BF16, moe_rows, 2 * m.ffn_hidden);
+        dw_r = b.tensor(TC_WORKSPACE, DT_FP32, T, m.moe_top_k);
+        dlogits = b.tensor(TC_WORKSPACE, DT_BF16, T, m.num_experts);
+    }
+    auto moe_dispatch = [&](int rows, int scale, const LayerActs& a, int slab, uint16_t mb) {
+        ExecOp e = xop(K_MOE_DISPATCH_GEMM);
+        e.t[0] = rows; e.t[1] = a.ridx; e.t[2] = a.rpos; e.t[3] = scale; e.t[4] = a.counts; e.t[5] = slab; e.t[6] = a.cnt_recv;
+        e.i[0] = m.moe_top_k; e.i[1] = m.num_experts; e.i[2] = moe_cap; e.i[3] = GROUP_EP; e.i[4] = static_cast<int32_t>(b.next_seq++);
+        b.push(OP_MOE_DISPATCH_GEMM, ST_COMPUTE_HI, 0, 2.0 * T * m.moe_top_k * H, GROUP_EP, mb, &e);
+    };
+    // mode 0: out = base + sum_s w_s * slab row ; mode 1: plain sum ; mode 2: dw[t, s] = <dot_with[t], slab row>
+    auto moe_combine = [&](int base, int outt, int weights, const LayerActs& a, int slab, int dot_with, int dw, bool announce,
+                           uint16_t mb) {
+        ExecOp e = xop(K_MOE_GEMM_COMBINE, announce ? 1 : 0);
+        e.t[0] = base; e.t[1] = outt; e.t[2] = a.ridx; e.t[3] = a.rpos; e.t[4] = weights; e.t[5] = slab; e.t[6] = dot_with; e.t[7] = dw;
+        e.i[0] = m.moe_top_k; e.i[1] = m.num_experts; e.i[2] = moe_cap; e.i[3] = GROUP_EP; e.i[4] = static_cast<int32_t>(b.next_seq++);
+        b.push(OP_MOE_GEMM_COMBINE, ST_COMPUTE_HI, 2.0 * T * m.moe_top_k * H, 2.0 * T * m.moe_top_k * H, GROUP_EP, mb, &e);
+    };
+    // per local expert: rows [e * ep * cap, (e+1) * ep * cap) of a slab, counts [e * ep, (e+1) * ep)
+    auto expert_rows = [&](int slab, uint32_t e) { return b.view(slab, e * d.ep * moe_cap, d.ep * moe_cap); };
+    auto expert_cnt = [&](const LayerActs& a, uint32_t e) {
+        const TensorDesc& ct = out->tensors[a.cnt_recv];
+        return b.tensor_at(TC_COMM, DT_INT32, ct.offset + static_cast<uint64_t>(e) * d.ep * 4, 1, d.ep, d.ep);
+    };
+
     // ---------------- activations: one set per in-flight microbatch
     const uint32_t slots = std::max<uint32_t>(1, std::min<uint32_t>(d.pp - b.stage, ga));
     out->xhdr.act_slots = slots;
@@ -407,8 +490,21 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             a.hmid = b.tensor(TC_ACTIVATION, DT_BF16, Tl, H);
             a.rstd2 = b.tensor(TC_ACTIVATION, DT_FP32, 1, Tl);
             a.xn2 = b.tensor(TC_ACTIVATION, DT_BF16, T, H);
-            a.gu = b.tensor(TC_ACTIVATION, DT_BF16, T, 2 * b.F_l);
-            a.act = b.tensor(TC_ACTIVATION, DT_BF16, T, b.F_l);
+            if (!moe) {
+                a.gu = b.tensor(TC_ACTIVATION, DT_BF16, T, 2 * b.F_l);
+                a.act = b.tensor(TC_ACTIVATION, DT_BF16, T, b.F_l);
+            } else {
+                a.logits = b.tensor(TC_ACTIVATION, DT_FP32, T, m.num_experts);
+                a.ridx = b.tensor(TC_ACTIVATION, DT_INT32, T, m.moe_top_k);
+                a.rw = b.tensor(TC_ACTIVATION, DT_FP32, T, m.moe_top_k);
+                a.rpos = b.tensor(TC_ACTIVATION, DT_INT32, T, m.moe_top_k);
+                a.counts = b.tensor(TC_ACTIVATION, DT_INT32, 1, m.num_experts);
+                a.cnt_recv = b.tensor(TC_COMM, DT_INT32, 1, E_l * d.ep);     // written by the sending members
+                a.xs = b.tensor(TC_COMM, DT_BF16, moe_rows, H);              // expert inputs, written by the senders
+                a.gu = b.tensor(TC_ACTIVATION, DT_BF16, moe_rows, 2 * m.ffn_hidden);
+                a.act = b.tensor(TC_ACTIVATION, DT_BF16, moe_rows, m.ffn_hidden);
+                a.ys = b.tensor(TC_COMM, DT_BF16, moe_rows, H);              // expert outputs, read by the token owners
+            }
         }
         x_out[s] = b.tensor(TC_ACTIVATION, DT_BF16, Tl, H);       // output of the stage's last layer
         if (b.last_stage) {
@@ -483,6 +579,33 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
                 b.push(OP_ATTENTION_FWD, ST_COMPUTE_HI, 2.0 * T * b.Hq_l * b.seq, 0, 0, mb, &e);
             }
             b.row_parallel(a.ao, w.wo.w, a.x, a.hmid, partial, rs_tmp, H, b.Hq_l, false, mb);
+            if (moe) {
+                // router -> dispatch (permute + peer stores) -> expert FFN over the slabs -> combine (peer loads)
+                const uint32_t F = m.ffn_hidden, seg_m = d.ep * moe_cap;
+                b.rmsnorm_fwd(a.hmid, w.g2.w, a.xn2, a.rstd2, T, mb);
+                b.gemm(ST_COMPUTE_HI, a.xn2, w.wr.w, a.logits, -1, T, m.num_experts, H, false, false, 1, mb);
+                {
+                    ExecOp e = xop(K_MOE_ROUTE);
+                    e.t[0] = a.logits; e.t[1] = a.ridx; e.t[2] = a.rw; e.t[3] = a.rpos; e.t[4] = a.counts;
+                    e.i[0] = T; e.i[1] = m.num_experts; e.i[2] = m.moe_top_k; e.i[3] = moe_cap;
+                    b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 10.0 * T * m.num_experts, 0, 0, mb, &e);
+                }
+                moe_dispatch(a.xn2, -1, a, a.xs, mb);
+                for (uint32_t e = 0; e < E_l; ++e)
+                    b.gemm_seg(expert_rows(a.xs, e), b.view(w.wgu.w, e * 2 * F, 2 * F), expert_rows(a.gu, e), seg_m, 2 * F, H, false,
+                               false, 0, expert_cnt(a, e), moe_cap, 1, mb);
+                {
+                    ExecOp e = xop(K_SWIGLU_FWD);
+                    e.t[0] = a.gu; e.t[1] = a.act;
+                    e.i[0] = moe_rows; e.i[1] = F;
+                    b.push(OP_SWIGLU, ST_COMPUTE_HI, 4.0 * moe_rows * F, 0, 0, mb, &e);
+                }
+                for (uint32_t e = 0; e < E_l; ++e)
+                    b.gemm_seg(expert_rows(a.act, e), b.view(w.wd.w, e * H, H), expert_rows(a.ys, e), seg_m, H, F, false, false, 0,
+                               expert_cnt(a, e), moe_cap, 1, mb);
+                moe_combine(a.hmid, x_next, a.rw, a, a.ys, -1, -1, true, mb);
+                continue;
+            }
             // MLP block
             b.rmsnorm_fwd(a.hmid, w.g2.w, tp > 1 ? xn_local : a.xn2, a.rstd2, Tl, mb);
             b.col_parallel(tp > 1 ? xn_local : a.xn2, a.xn2, w.wgu.w, a.gu, 2 * b.F_l, H, false, mb);
@@ -563,6 +686,41 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             const LayerActs& a = A[s][l];
             const LayerParams& w = L[l];
             const int g_rows = tp > 1 ? dfull : dstream;  // all T rows of the incoming gradient
+            if (moe) {
+                const uint32_t F = m.ffn_hidden, seg_m = d.ep * moe_cap;
+                moe_combine(-1, -1, -1, a, a.ys, dstream, dw_r, false, mb);           // dw[t,s] = <dx_next[t], y(t,s)>
+                moe_dispatch(dstream, a.rw, a, dy_s, mb);                              // dy rows = w[t,s] * dx_next[t]
+                for (uint32_t e = 0; e < E_l; ++e) {
+                    const int cnt = expert_cnt(a, e);
+                    b.gemm_seg(expert_rows(dy_s, e), b.view(w.wd.w, e * H, H), expert_rows(dact_s, e), seg_m, F, H, false, true, 0,
+                               cnt, moe_cap, 1, mb);
+                    b.gemm_seg(expert_rows(dy_s, e), expert_rows(a.act, e), b.view(w.wd.g, e * H, H), H, F, seg_m, true, true, wg_epi,
+                               cnt, moe_cap, 2, mb);
+                }
+                {
+                    ExecOp e = xop(K_SWIGLU_BWD);
+                    e.t[0] = a.gu; e.t[1] = dact_s; e.t[2] = dgu_s;
+                    e.i[0] = moe_rows; e.i[1] = F;
+                    b.push(OP_SWIGLU, ST_COMPUTE_HI, 8.0 * moe_rows * F, 0, 0, mb, &e);
+                }
+                for (uint32_t e = 0; e < E_l; ++e) {
+                    const int cnt = expert_cnt(a, e);
+                    b.gemm_seg(expert_rows(dgu_s, e), b.view(w.wgu.w, e * 2 * F, 2 * F), expert_rows(dx_s, e), seg_m, H, 2 * F, false,
+                               true, 0, cnt, moe_cap, 1, mb);
+                    b.gemm_seg(expert_rows(dgu_s, e), expert_rows(a.xs, e), b.view(w.wgu.g, e * 2 * F, 2 * F), 2 * F, H, seg_m, true,
+                               true, wg_epi, cnt, moe_cap, 2, mb);
+                }
+                moe_combine(-1, dxn, -1, a, dx_s, -1, -1, true, mb);                  // dxn2[t] = sum_s dx(t,s)
+                {
+                    ExecOp e = xop(K_MOE_ROUTE, 1);
+                    e.t[0] = a.logits; e.t[1] = a.ridx; e.t[2] = dw_r; e.t[3] = a.rpos; e.t[4] = dlogits;
+                    e.i[0] = T; e.i[1] = m.num_experts; e.i[2] = m.moe_top_k;
+                    b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 20.0 * T * m.num_experts, 0, 0, mb, &e);
+                }
+                b.gemm(ST_COMPUTE_HI, dlogits, w.wr.w, dxn, dxn, T, H, m.num_experts, false, true, 3, mb);   // dxn2 += dlogits * Wr
+                b.gemm(ST_COMPUTE_HI, dlogits, a.xn2, w.wr.g, -1, m.num_experts, H, T, true, true, wg_epi, mb);
+                b.rmsnorm_bwd(a.hmid, w.g2.w, a.rstd2, dxn, dstream, w.g2.g, norm_scratch, T, true, !first_mb, mb);
+            } else {
             // ---- MLP block: x_next = hmid + act * Wd^T
             b.col_parallel(dstream, dfull, w.wd.w, dact, b.F_l, H, true, mb);                     // dact = gather(dx) * Wd
             b.gemm(ST_COMPUTE_HI, g_rows, a.act, w.wd.g, -1, H, b.F_l, T, true, true, wg_epi, mb);  // dWd = dx^T act
@@ -575,6 +733,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             b.row_parallel(dgu, w.wgu.w, -1, dxn, partial, rs_tmp, H, 2 * b.F_l, true, mb);        // dxn2 = RS(dgu * Wgu)
             b.gemm(ST_COMPUTE_HI, dgu, a.xn2, w.wgu.g, -1, 2 * b.F_l, H, T, true, true, wg_epi, mb);
             b.rmsnorm_bwd(a.hmid, w.g2.w, a.rstd2, dxn, dstream, w.g2.g, norm_scratch, Tl, true, !first_mb, mb);
+            }
             // ---- attention block: hmid = x + ao * Wo^T
             b.col_parallel(dstream, dfull, w.wo.w, dao, b.Hq_l, H, true, mb);                     // dao = gather(dh) * Wo
             b.gemm(ST_COMPUTE_HI, g_rows, a.ao, w.wo.g, -1, H, b.Hq_l, T, true, true, wg_epi, mb);
@@ -655,12 +814,30 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         if (b.fused) {
             ExecOp e = xop(K_RS_ADAMW);
             e.t[0] = b.flat_master; e.t[1] = b.flat_m; e.t[2] = b.flat_v; e.t[3] = b.flat_grad; e.t[4] = b.flat_param;
-            e.i[0] = static_cast<int32_t>(n_flat & 0xFFFFFFFFu); e.i[1] = static_cast<int32_t>(n_flat >> 32);
-            e.i[2] = static_cast<int32_t>(n_opt & 0xFFFFFFFFu); e.i[3] = GROUP_DP; e.i[4] = static_cast<int32_t>(b.next_seq++);
+            e.i[0] = static_cast<int32_t>(n_rep & 0xFFFFFFFFu); e.i[1] = static_cast<int32_t>(n_rep >> 32);
+            e.i[2] = static_cast<int32_t>(n_shard & 0xFFFFFFFFu); e.i[3] = GROUP_DP; e.i[4] = static_cast<int32_t>(b.next_seq++);
             e.f[0] = 1.0f / d.dp;
             b.sync(ST_COMPUTE_HI, ST_COMM_DP, 0);
-            b.push(OP_RS_ADAMW, ST_COMM_DP, 18.0 * n_opt, 4.0 * n_flat, GROUP_DP, 0, &e);
+            b.push(OP_RS_ADAMW, ST_COMM_DP, 18.0 * n_shard, 4.0 * n_rep, GROUP_DP, 0, &e);
             b.sync(ST_COMM_DP, ST_COMPUTE_HI, 0);
+            if (n_exp) {
+                // the experts this rank owns: plain AdamW on the tail of the flat space
+                auto tail = [&](int flat, uint16_t tclass, uint16_t dt, uint64_t elem_off) {
+                    const TensorDesc& ft = out->tensors[flat];
+                    const int id = b.tensor_at(tclass, dt, ft.offset + elem_off * dtype_size(dt), 1, 0, 0);
+                    out->tensors[id].nbytes = n_exp * dtype_size(dt);
+                    return id;
+                };
+                ExecOp x = xop(K_ADAMW);
+                x.t[0] = tail(b.flat_master, TC_OPTSTATE, DT_FP32, n_shard);
+                x.t[1] = tail(b.flat_m, TC_OPTSTATE, DT_FP32, n_shard);
+                x.t[2] = tail(b.flat_v, TC_OPTSTATE, DT_FP32, n_shard);
+                x.t[3] = tail(b.flat_grad, TC_GRAD, DT_FP32, n_rep);
+                x.t[4] = tail(b.flat_param, TC_PARAM, DT_BF16, n_rep);
+                x.i[0] = static_cast<int32_t>(n_exp & 0xFFFFFFFFu); x.i[1] = static_cast<int32_t>(n_exp >> 32);
+                x.f[0] = 1.0f / d.dp;  // every expert sees tokens of all replicas, each scaled for its local mean
+                b.push(OP_OPTIMIZER, ST_COMPUTE_HI, 18.0 * n_exp, 0, 0, 0, &x);
+            }
         } else {
             // baseline: all-reduce the gradients, every rank updates everything
             b.sync(ST_COMPUTE_HI, ST_COMM_DP, 0);
@@ -719,6 +896,17 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     well_known("@flat_master", b.flat_master);
     well_known("@flat_m", b.flat_m);
     well_known("@flat_v", b.flat_v);
+    {
+        // split of the flat space: [0, n_rep) replicated over dp (optimizer shard n_shard), rest local experts
+        NamedTensor nt{};
+        std::snprintf(nt.name, sizeof nt.name, "@flat_split");
+        nt.tensor = -1; nt.grad = -1;
+        nt.master = static_cast<int32_t>(hdr_n_rep >> 9);
+        nt.rows = static_cast<uint32_t>(hdr_n_shard >> 9);
+        nt.cols = 0;
+        nt.init_std = -1.f;
+        out->named.push_back(nt);
+    }
     out->xhdr.num_named = static_cast<uint32_t>(out->named.size());
     return OK;
 }

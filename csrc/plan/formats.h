@@ -218,7 +218,7 @@ struct NamedTensor {         // 64 bytes: lets the runtime initialise / checkpoi
     char name[40];
     int32_t tensor;          // tensor id of the bf16 parameter
     int32_t grad;            // tensor id of the fp32 gradient
-    int32_t master;          // tensor id of the fp32 master copy (m and v follow at +1, +2)
+    int32_t master;          // offset of the parameter in the flat space, in units of 512 elements
     uint32_t rows, cols;
     float init_std;          // 0 = initialise to ones (norm gains)
 };

@@ -22,6 +22,7 @@
 #include <vector>
 
 #include "../comm/fused.h"
+#include "../comm/moe.h"
 #include "../comm/peer.cuh"
 #include "../kernels/cai_kernels.h"
 #include "../kernels/host_common.h"
@@ -181,6 +182,10 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
                                    x.i[2], x.i[3], st);
         case K_GEMM: {
             const int ta = x.flags & 1, tb = (x.flags >> 1) & 1, epi = x.flags >> 4;
+            if (x.t[4] >= 0)  // ragged expert slab: live rows per sub-slab come from a device table
+                return cai_gemm_bf16_seg(P(0), P(1), P(2), P(3), x.i[0], x.i[1], x.i[2], ex->ld(x.t[0]), ex->ld(x.t[1]),
+                                         ex->ld(x.t[2]), x.t[3] >= 0 ? ex->ld(x.t[3]) : 0, ta, tb, epi, x.f[0],
+                                         (const int*)P(4), x.i[3], x.i[4], ex->sm_limit_hi, st);
             return cai_gemm_bf16(P(0), P(1), P(2), P(3), x.i[0], x.i[1], x.i[2], ex->ld(x.t[0]), ex->ld(x.t[1]),
                                  ex->ld(x.t[2]), x.t[3] >= 0 ? ex->ld(x.t[3]) : 0, ta, tb, epi, x.f[0], ex->sm_limit_hi, st);
         }
@@ -253,6 +258,51 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
                 return CAI_K_CUDA;
             }
             return 0;
+        }
+        case K_MOE_ROUTE:
+            if (x.flags & 1)
+                return cai_moe_route_bwd((const float*)P(0), (const int*)P(1), (const float*)P(2), (const int*)P(3), P(4), x.i[0],
+                                         x.i[1], x.i[2], st);
+            return cai_moe_route_fwd((const float*)P(0), (int*)P(1), (float*)P(2), (int*)P(3), (int*)P(4), x.i[0], x.i[1], x.i[2],
+                                     x.i[3], st);
+        case K_MOE_DISPATCH_GEMM: case K_MOE_GEMM_COMBINE: {
+            // The expert group has the members of the data-parallel group (ep == dp) or is this rank alone.
+            PeerTable self{};
+            const PeerTable* pt = nullptr;
+            if (ex->has_peers[GROUP_EP]) pt = &ex->peers[GROUP_EP];
+            else if (ex->hdr.ep > 1 && ex->has_peers[GROUP_DP] && ex->peers[GROUP_DP].size == static_cast<int>(ex->hdr.ep))
+                pt = &ex->peers[GROUP_DP];
+            else if (ex->hdr.ep <= 1) {
+                int sig = -1;
+                for (const NamedTensor& nt : ex->named)
+                    if (!strcmp(nt.name, "@signals")) sig = nt.tensor;
+                if (sig < 0) {
+                    set_last_error("plan has no signal block");
+                    return CAI_K_BAD_ARG;
+                }
+                self.base[0] = ex->arena;
+                self.rank = 0;
+                self.size = 1;
+                self.sig_off = ex->tensors[sig].offset;
+                pt = &self;
+            } else {
+                set_last_error("expert-parallel op needs the members' arenas (not exchanged)");
+                return CAI_K_BAD_ARG;
+            }
+            const uint32_t* epoch_base = reinterpret_cast<const uint32_t*>(ex->hyper_dev) + 7;
+            const uint32_t seq = static_cast<uint32_t>(x.i[4]);
+            const int k = x.i[0], E = x.i[1], cap = x.i[2];
+            if (x.kernel == K_MOE_DISPATCH_GEMM) {
+                const int T = static_cast<int>(ex->shapes[static_cast<size_t>(x.t[0]) * 4]);
+                const int H = static_cast<int>(ex->shapes[static_cast<size_t>(x.t[0]) * 4 + 1]);
+                return cai_moe_dispatch(*pt, P(0), (const int*)P(1), (const int*)P(2), (const float*)P(3), (const int*)P(4),
+                                        ex->tensors[x.t[5]].offset, ex->tensors[x.t[6]].offset, T, H, k, E, cap, epoch_base, seq,
+                                        ex->counters_dev + 8, st);
+            }
+            const int T = static_cast<int>(ex->shapes[static_cast<size_t>(x.t[2]) * 4]);
+            const int H = static_cast<int>(ex->shapes[static_cast<size_t>(x.t[5]) * 4 + 1]);
+            return cai_moe_combine(*pt, P(0), P(1), (const int*)P(2), (const int*)P(3), (const float*)P(4),
+                                   ex->tensors[x.t[5]].offset, P(6), (float*)P(7), T, H, k, E, cap, x.flags & 1, epoch_base, seq, st);
         }
         case K_AG_GEMM: case K_GEMM_RS: case K_RS_ADAMW: {
             const int group = x.i[3];
@@ -408,7 +458,9 @@ CAI_API int cai_exec_create(cai_exec** out, const void* plan_bytes, size_t nbyte
     {
         uint32_t fused = 0;
         for (const ExecOp& x : ex->exec)
-            if (x.kernel == K_AG_GEMM || x.kernel == K_GEMM_RS || x.kernel == K_RS_ADAMW) ++fused;
+            if (x.kernel == K_AG_GEMM || x.kernel == K_GEMM_RS || x.kernel == K_RS_ADAMW || x.kernel == K_MOE_DISPATCH_GEMM ||
+                x.kernel == K_MOE_GEMM_COMBINE)
+                ++fused;
         ex->epochs_per_step = 2 * fused + 2;
     }
     cudaMallocHost(&ex->hyper_host, 8 * sizeof(float));

@@ -1,4 +1,4 @@
-"""Worker for multi-GPU tests: trains configs/tiny_mp.cfg for a few steps under a given parallel
+"""Worker for multi-GPU tests: trains a tiny config (configs/tiny_mp.cfg by default) for a few steps under a given parallel
 layout and writes the loss curve (rank 0). Launched with torch.distributed.run."""
 import argparse
 import json
@@ -14,6 +14,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--pp", type=int, default=1)
+    ap.add_argument("--ep", type=int, default=1)
+    ap.add_argument("--config", default="tiny_mp")
     ap.add_argument("--comm", default="baseline")
     ap.add_argument("--steps", type=int, default=6)
     ap.add_argument("--graph", type=int, default=0)
@@ -23,8 +25,8 @@ def main():
     from cai_b200.runtime.engine import Engine, synthetic_batch
     world = int(os.environ.get("WORLD_SIZE", 1))
     rank = int(os.environ.get("RANK", 0))
-    text = (ROOT / "configs" / "tiny_mp.cfg").read_text()
-    text += f"\ngpus_per_rack = {world}\ngpus_per_tray = {world}\ntp = {a.tp}\npp = {a.pp}\ncomm = {a.comm}\n"
+    text = (ROOT / "configs" / f"{a.config}.cfg").read_text()
+    text += f"\ngpus_per_rack = {world}\ngpus_per_tray = {world}\ntp = {a.tp}\npp = {a.pp}\nep = {a.ep}\ncomm = {a.comm}\n"
     eng = Engine(config_text=text, rank=rank, world=world, local_rank=int(os.environ.get("LOCAL_RANK", rank)))
     m = eng.model
     dp = eng.hdr.dp

@@ -61,6 +61,17 @@ def test_data_parallel_2_baseline_and_fused_agree(tmp_path):
     assert a["dp"] == 2
 
 
+def test_expert_parallel_2_matches_replicated_experts(tmp_path):
+    """Same MoE model and global batch on 2 GPUs: experts replicated (ep = 1, gradients reduced over dp)
+    against experts sharded (ep = 2, tokens exchanged by the dispatch / combine kernels)."""
+    if _gpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    a = run_case(tmp_path, 2, config="tiny_moe", comm="fused", ep=1)
+    b = run_case(tmp_path, 2, config="tiny_moe", comm="fused", ep=2)
+    close(a["losses"], b["losses"])
+    assert b["losses"][-1] < b["losses"][0]
+
+
 def test_pipeline_parallel_2_matches_single_gpu(tmp_path, single):
     if _gpus() < 2:
         pytest.skip("needs 2 GPUs")
