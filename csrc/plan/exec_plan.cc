@@ -478,33 +478,47 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     out->xhdr.act_slots = slots;
     std::vector<std::vector<LayerActs>> A(slots, std::vector<LayerActs>(b.layers));
     std::vector<int> x_out(slots), hf_s(slots), hff_s(slots), rstdf_s(slots);
+    // Full activation recompute keeps, per in-flight microbatch and layer, only the layer's input;
+    // everything else lives once per stage and is rebuilt by re-running the layer's forward right
+    // before its backward (all of it on the one compute stream, so the shared set is never contended).
+    const bool recompute = m.recompute != 0;
+    auto alloc_layer_rest = [&](LayerActs& a) {
+        a.rstd1 = b.tensor(TC_ACTIVATION, DT_FP32, 1, Tl);
+        a.xn1 = b.tensor(TC_ACTIVATION, DT_BF16, T, H);       // gathered rows (== local when tp = 1)
+        a.qkv = b.tensor(TC_ACTIVATION, DT_BF16, T, b.Cqkv);
+        a.ao = b.tensor(TC_ACTIVATION, DT_BF16, T, b.Hq_l);
+        a.lse = b.tensor(TC_ACTIVATION, DT_FP32, b.nh_l, T);
+        a.hmid = b.tensor(TC_ACTIVATION, DT_BF16, Tl, H);
+        a.rstd2 = b.tensor(TC_ACTIVATION, DT_FP32, 1, Tl);
+        a.xn2 = b.tensor(TC_ACTIVATION, DT_BF16, T, H);
+        if (!moe) {
+            a.gu = b.tensor(TC_ACTIVATION, DT_BF16, T, 2 * b.F_l);
+            a.act = b.tensor(TC_ACTIVATION, DT_BF16, T, b.F_l);
+        } else {
+            a.logits = b.tensor(TC_ACTIVATION, DT_FP32, T, m.num_experts);
+            a.ridx = b.tensor(TC_ACTIVATION, DT_INT32, T, m.moe_top_k);
+            a.rw = b.tensor(TC_ACTIVATION, DT_FP32, T, m.moe_top_k);
+            a.rpos = b.tensor(TC_ACTIVATION, DT_INT32, T, m.moe_top_k);
+            a.counts = b.tensor(TC_ACTIVATION, DT_INT32, 1, m.num_experts);
+            a.cnt_recv = b.tensor(TC_COMM, DT_INT32, 1, E_l * d.ep);     // written by the sending members
+            a.xs = b.tensor(TC_COMM, DT_BF16, moe_rows, H);              // expert inputs, written by the senders
+            a.gu = b.tensor(TC_ACTIVATION, DT_BF16, moe_rows, 2 * m.ffn_hidden);
+            a.act = b.tensor(TC_ACTIVATION, DT_BF16, moe_rows, m.ffn_hidden);
+            a.ys = b.tensor(TC_COMM, DT_BF16, moe_rows, H);              // expert outputs, read by the token owners
+        }
+    };
+    LayerActs shared_acts;
+    int x_scratch = -1;
+    if (recompute) {
+        alloc_layer_rest(shared_acts);
+        x_scratch = b.tensor(TC_ACTIVATION, DT_BF16, Tl, H);   // output of a re-run layer (already consumed downstream)
+    }
     for (uint32_t s = 0; s < slots; ++s) {
         for (uint32_t l = 0; l < b.layers; ++l) {
             LayerActs& a = A[s][l];
+            if (recompute) a = shared_acts;
             a.x = b.tensor(TC_ACTIVATION, DT_BF16, Tl, H);
-            a.rstd1 = b.tensor(TC_ACTIVATION, DT_FP32, 1, Tl);
-            a.xn1 = b.tensor(TC_ACTIVATION, DT_BF16, T, H);       // gathered rows (== local when tp = 1)
-            a.qkv = b.tensor(TC_ACTIVATION, DT_BF16, T, b.Cqkv);
-            a.ao = b.tensor(TC_ACTIVATION, DT_BF16, T, b.Hq_l);
-            a.lse = b.tensor(TC_ACTIVATION, DT_FP32, b.nh_l, T);
-            a.hmid = b.tensor(TC_ACTIVATION, DT_BF16, Tl, H);
-            a.rstd2 = b.tensor(TC_ACTIVATION, DT_FP32, 1, Tl);
-            a.xn2 = b.tensor(TC_ACTIVATION, DT_BF16, T, H);
-            if (!moe) {
-                a.gu = b.tensor(TC_ACTIVATION, DT_BF16, T, 2 * b.F_l);
-                a.act = b.tensor(TC_ACTIVATION, DT_BF16, T, b.F_l);
-            } else {
-                a.logits = b.tensor(TC_ACTIVATION, DT_FP32, T, m.num_experts);
-                a.ridx = b.tensor(TC_ACTIVATION, DT_INT32, T, m.moe_top_k);
-                a.rw = b.tensor(TC_ACTIVATION, DT_FP32, T, m.moe_top_k);
-                a.rpos = b.tensor(TC_ACTIVATION, DT_INT32, T, m.moe_top_k);
-                a.counts = b.tensor(TC_ACTIVATION, DT_INT32, 1, m.num_experts);
-                a.cnt_recv = b.tensor(TC_COMM, DT_INT32, 1, E_l * d.ep);     // written by the sending members
-                a.xs = b.tensor(TC_COMM, DT_BF16, moe_rows, H);              // expert inputs, written by the senders
-                a.gu = b.tensor(TC_ACTIVATION, DT_BF16, moe_rows, 2 * m.ffn_hidden);
-                a.act = b.tensor(TC_ACTIVATION, DT_BF16, moe_rows, m.ffn_hidden);
-                a.ys = b.tensor(TC_COMM, DT_BF16, moe_rows, H);              // expert outputs, read by the token owners
-            }
+            if (!recompute) alloc_layer_rest(a);
         }
         x_out[s] = b.tensor(TC_ACTIVATION, DT_BF16, Tl, H);       // output of the stage's last layer
         if (b.last_stage) {
@@ -522,6 +536,64 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
 
     const double grad_scale = 1.0 / (static_cast<double>(T) * ga);
     std::vector<int> send_done(slots, -1);  // event recorded after a slot's activation send
+
+    // ================================================================ forward of one layer
+    auto layer_forward = [&](uint16_t mb, const LayerActs& a, const LayerParams& w, int x_next) {
+        // attention block
+        b.rmsnorm_fwd(a.x, w.g1.w, tp > 1 ? xn_local : a.xn1, a.rstd1, Tl, mb);
+        b.col_parallel(tp > 1 ? xn_local : a.xn1, a.xn1, w.wqkv.w, a.qkv, b.Cqkv, H, false, mb);
+        {
+            ExecOp e = xop(K_ROPE);
+            e.t[0] = a.qkv; e.t[1] = rope_tab;
+            e.i[0] = T; e.i[1] = b.seq; e.i[2] = b.nh_l; e.i[3] = b.nkv_l; e.i[4] = b.hd;
+            b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 6.0 * T * (b.nh_l + b.nkv_l) * b.hd, 0, 0, mb, &e);
+        }
+        {
+            ExecOp e = xop(K_ATTN_FWD);
+            e.t[0] = a.qkv; e.t[1] = a.ao; e.t[2] = a.lse;
+            e.i[0] = b.mbsz; e.i[1] = b.seq; e.i[2] = b.nh_l; e.i[3] = b.nkv_l; e.i[4] = b.hd;
+            e.f[0] = 1.0f / std::sqrt(static_cast<float>(b.hd));
+            b.push(OP_ATTENTION_FWD, ST_COMPUTE_HI, 2.0 * T * b.Hq_l * b.seq, 0, 0, mb, &e);
+        }
+        b.row_parallel(a.ao, w.wo.w, a.x, a.hmid, partial, rs_tmp, H, b.Hq_l, false, mb);
+        if (moe) {
+            // router -> dispatch (permute + peer stores) -> expert FFN over the slabs -> combine (peer loads)
+            const uint32_t F = m.ffn_hidden, seg_m = d.ep * moe_cap;
+            b.rmsnorm_fwd(a.hmid, w.g2.w, a.xn2, a.rstd2, T, mb);
+            b.gemm(ST_COMPUTE_HI, a.xn2, w.wr.w, a.logits, -1, T, m.num_experts, H, false, false, 1, mb);
+            {
+                ExecOp e = xop(K_MOE_ROUTE);
+                e.t[0] = a.logits; e.t[1] = a.ridx; e.t[2] = a.rw; e.t[3] = a.rpos; e.t[4] = a.counts;
+                e.i[0] = T; e.i[1] = m.num_experts; e.i[2] = m.moe_top_k; e.i[3] = moe_cap;
+                b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 10.0 * T * m.num_experts, 0, 0, mb, &e);
+            }
+            moe_dispatch(a.xn2, -1, a, a.xs, mb);
+            for (uint32_t e = 0; e < E_l; ++e)
+                b.gemm_seg(expert_rows(a.xs, e), b.view(w.wgu.w, e * 2 * F, 2 * F), expert_rows(a.gu, e), seg_m, 2 * F, H, false,
+                           false, 0, expert_cnt(a, e), moe_cap, 1, mb);
+            {
+                ExecOp e = xop(K_SWIGLU_FWD);
+                e.t[0] = a.gu; e.t[1] = a.act;
+                e.i[0] = moe_rows; e.i[1] = F;
+                b.push(OP_SWIGLU, ST_COMPUTE_HI, 4.0 * moe_rows * F, 0, 0, mb, &e);
+            }
+            for (uint32_t e = 0; e < E_l; ++e)
+                b.gemm_seg(expert_rows(a.act, e), b.view(w.wd.w, e * H, H), expert_rows(a.ys, e), seg_m, H, F, false, false, 0,
+                           expert_cnt(a, e), moe_cap, 1, mb);
+            moe_combine(a.hmid, x_next, a.rw, a, a.ys, -1, -1, true, mb);
+            return;
+        }
+        // MLP block
+        b.rmsnorm_fwd(a.hmid, w.g2.w, tp > 1 ? xn_local : a.xn2, a.rstd2, Tl, mb);
+        b.col_parallel(tp > 1 ? xn_local : a.xn2, a.xn2, w.wgu.w, a.gu, 2 * b.F_l, H, false, mb);
+        {
+            ExecOp e = xop(K_SWIGLU_FWD);
+            e.t[0] = a.gu; e.t[1] = a.act;
+            e.i[0] = T; e.i[1] = b.F_l;
+            b.push(OP_SWIGLU, ST_COMPUTE_HI, 4.0 * T * b.F_l, 0, 0, mb, &e);
+        }
+        b.row_parallel(a.act, w.wd.w, a.hmid, x_next, partial, rs_tmp, H, b.F_l, false, mb);
+    };
 
     // ================================================================ forward of one microbatch
     auto forward = [&](uint16_t mb) {
@@ -558,65 +630,8 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             b.wait(ST_COMPUTE_HI, static_cast<uint32_t>(send_done[s]), mb);
             send_done[s] = -1;
         }
-        for (uint32_t l = 0; l < b.layers; ++l) {
-            const LayerActs& a = A[s][l];
-            const LayerParams& w = L[l];
-            const int x_next = l + 1 < b.layers ? A[s][l + 1].x : x_out[s];
-            // attention block
-            b.rmsnorm_fwd(a.x, w.g1.w, tp > 1 ? xn_local : a.xn1, a.rstd1, Tl, mb);
-            b.col_parallel(tp > 1 ? xn_local : a.xn1, a.xn1, w.wqkv.w, a.qkv, b.Cqkv, H, false, mb);
-            {
-                ExecOp e = xop(K_ROPE);
-                e.t[0] = a.qkv; e.t[1] = rope_tab;
-                e.i[0] = T; e.i[1] = b.seq; e.i[2] = b.nh_l; e.i[3] = b.nkv_l; e.i[4] = b.hd;
-                b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 6.0 * T * (b.nh_l + b.nkv_l) * b.hd, 0, 0, mb, &e);
-            }
-            {
-                ExecOp e = xop(K_ATTN_FWD);
-                e.t[0] = a.qkv; e.t[1] = a.ao; e.t[2] = a.lse;
-                e.i[0] = b.mbsz; e.i[1] = b.seq; e.i[2] = b.nh_l; e.i[3] = b.nkv_l; e.i[4] = b.hd;
-                e.f[0] = 1.0f / std::sqrt(static_cast<float>(b.hd));
-                b.push(OP_ATTENTION_FWD, ST_COMPUTE_HI, 2.0 * T * b.Hq_l * b.seq, 0, 0, mb, &e);
-            }
-            b.row_parallel(a.ao, w.wo.w, a.x, a.hmid, partial, rs_tmp, H, b.Hq_l, false, mb);
-            if (moe) {
-                // router -> dispatch (permute + peer stores) -> expert FFN over the slabs -> combine (peer loads)
-                const uint32_t F = m.ffn_hidden, seg_m = d.ep * moe_cap;
-                b.rmsnorm_fwd(a.hmid, w.g2.w, a.xn2, a.rstd2, T, mb);
-                b.gemm(ST_COMPUTE_HI, a.xn2, w.wr.w, a.logits, -1, T, m.num_experts, H, false, false, 1, mb);
-                {
-                    ExecOp e = xop(K_MOE_ROUTE);
-                    e.t[0] = a.logits; e.t[1] = a.ridx; e.t[2] = a.rw; e.t[3] = a.rpos; e.t[4] = a.counts;
-                    e.i[0] = T; e.i[1] = m.num_experts; e.i[2] = m.moe_top_k; e.i[3] = moe_cap;
-                    b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 10.0 * T * m.num_experts, 0, 0, mb, &e);
-                }
-                moe_dispatch(a.xn2, -1, a, a.xs, mb);
-                for (uint32_t e = 0; e < E_l; ++e)
-                    b.gemm_seg(expert_rows(a.xs, e), b.view(w.wgu.w, e * 2 * F, 2 * F), expert_rows(a.gu, e), seg_m, 2 * F, H, false,
-                               false, 0, expert_cnt(a, e), moe_cap, 1, mb);
-                {
-                    ExecOp e = xop(K_SWIGLU_FWD);
-                    e.t[0] = a.gu; e.t[1] = a.act;
-                    e.i[0] = moe_rows; e.i[1] = F;
-                    b.push(OP_SWIGLU, ST_COMPUTE_HI, 4.0 * moe_rows * F, 0, 0, mb, &e);
-                }
-                for (uint32_t e = 0; e < E_l; ++e)
-                    b.gemm_seg(expert_rows(a.act, e), b.view(w.wd.w, e * H, H), expert_rows(a.ys, e), seg_m, H, F, false, false, 0,
-                               expert_cnt(a, e), moe_cap, 1, mb);
-                moe_combine(a.hmid, x_next, a.rw, a, a.ys, -1, -1, true, mb);
-                continue;
-            }
-            // MLP block
-            b.rmsnorm_fwd(a.hmid, w.g2.w, tp > 1 ? xn_local : a.xn2, a.rstd2, Tl, mb);
-            b.col_parallel(tp > 1 ? xn_local : a.xn2, a.xn2, w.wgu.w, a.gu, 2 * b.F_l, H, false, mb);
-            {
-                ExecOp e = xop(K_SWIGLU_FWD);
-                e.t[0] = a.gu; e.t[1] = a.act;
-                e.i[0] = T; e.i[1] = b.F_l;
-                b.push(OP_SWIGLU, ST_COMPUTE_HI, 4.0 * T * b.F_l, 0, 0, mb, &e);
-            }
-            b.row_parallel(a.act, w.wd.w, a.hmid, x_next, partial, rs_tmp, H, b.F_l, false, mb);
-        }
+        for (uint32_t l = 0; l < b.layers; ++l)
+            layer_forward(mb, A[s][l], L[l], l + 1 < b.layers ? A[s][l + 1].x : x_out[s]);
         if (!b.last_stage) {
             b.sync(ST_COMPUTE_HI, ST_COMM_PP, mb);
             b.nccl(K_NCCL_SEND, OP_PIPE_SEND, ST_COMM_PP, x_out[s], -1, static_cast<uint64_t>(Tl) * H, DT_BF16, GROUP_PP,
@@ -686,6 +701,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             const LayerActs& a = A[s][l];
             const LayerParams& w = L[l];
             const int g_rows = tp > 1 ? dfull : dstream;  // all T rows of the incoming gradient
+            if (recompute) layer_forward(mb, a, w, x_scratch);
             if (moe) {
                 const uint32_t F = m.ffn_hidden, seg_m = d.ep * moe_cap;
                 moe_combine(-1, -1, -1, a, a.ys, dstream, dw_r, false, mb);           // dw[t,s] = <dx_next[t], y(t,s)>

@@ -254,12 +254,21 @@ static void test_config_parser() {
 }
 
 static void test_exec_plans() {
-    for (const char* path : {"configs/tiny.cfg", "configs/b200_tp8.cfg", "configs/b200_pp2tp4.cfg"}) {
+    for (const char* path : {"configs/tiny.cfg", "configs/b200_tp8.cfg", "configs/b200_pp2tp4.cfg", "configs/tiny_moe.cfg",
+                             "configs/b200_moe_ep8.cfg"}) {
         for (const char* mode : {"fused", "baseline"}) {
             Config c;
             std::string err;
             if (config_load(path, &c, &err) != OK) { CHECK(false, "%s: %s", path, err.c_str()); continue; }
             c.train.comm_mode = std::strcmp(mode, "fused") == 0;
+            if (c.model.is_moe && !c.train.comm_mode) {
+                // expert exchange exists only as in-kernel dispatch / combine: a baseline plan must be refused
+                topology_finalize(&c.topo, &err);
+                Decomp dm;
+                Plan pm;
+                CHECK(decompose(c, &dm, &err) == OK && build_plan_v2(c, dm, 0, 0, 0, &pm, &err) == ERR_INVALID, "%s: baseline MoE", path);
+                continue;
+            }
             topology_finalize(&c.topo, &err);
             Decomp d;
             CHECK(decompose(c, &d, &err) == OK, "%s", err.c_str());

@@ -170,3 +170,29 @@ def test_checkpoint_resume_reproduces_the_curve(tmp_path):
     with pytest.raises(planlib.PlanError):
         other.load_checkpoint(tmp_path / "ck")
     other.close()
+
+
+def test_activation_recompute_gives_the_same_training_run():
+    """recompute = 1 keeps only each layer's input and re-runs the layer forward inside backward:
+    same losses, same gradients, smaller activation arena."""
+    from cai_b200.runtime.engine import Engine, synthetic_batch
+    text = (ROOT / "configs" / "tiny.cfg").read_text()
+    runs = []
+    for rc in (0, 1):
+        eng = Engine(config_text=text.replace("recompute     = 0", f"recompute     = {rc}"), rank=0, world=1, local_rank=0)
+        m = eng.model
+        assert m.recompute == rc
+        rows = eng.hdr.num_microbatches * m.microbatch
+        tok, tgt = synthetic_batch(m.vocab_size, m.seq_len, rows, step=0, seed=5)
+        first = eng.step(tok, tgt, lr=0.0)
+        grads = {n: eng.grad(n).float().clone() for n in eng.parameter_names()}
+        losses = [first] + [eng.step(tok, tgt) for _ in range(4)]
+        runs.append((losses, grads, int(eng.hdr.arena_bytes)))
+        eng.close()
+    (l0, g0, a0), (l1, g1, a1) = runs
+    assert a1 < a0
+    for x, y in zip(l0, l1):
+        assert abs(x - y) < 1e-3 * max(1.0, abs(x)), (l0, l1)
+    for n in g0:
+        rel = ((g0[n] - g1[n]).norm() / (g0[n].norm() + 1e-12)).item()
+        assert rel < 1e-3, (n, rel)
