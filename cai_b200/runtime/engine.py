@@ -168,6 +168,9 @@ class Engine:
         return self.tensor_view(self.named[name].tensor)
 
     def param(self, name: str) -> torch.Tensor:
+        if getattr(self, "zero3", False):
+            raise RuntimeError("parameters are sharded (zero_stage = 3): a named tensor is only a place in a staging "
+                               "buffer that holds it while its layer runs")
         return self.view(name)
 
     def grad(self, name: str) -> torch.Tensor:
@@ -262,6 +265,8 @@ class Engine:
         sharded = dp > 1 and n_shard < n_rep   # optimizer state split over the data-parallel group
         shard_lo = dp_id * n_shard if sharded else 0
         shard_hi = min(shard_lo + n_shard, n_rep) if sharded else n_rep
+        pshard = self.view("@flat_param")
+        self.zero3 = sharded and pshard.numel() < n_flat   # bf16 parameters sharded like the optimizer state
         with torch.cuda.stream(self.stream):
             self.view("@flat_m").zero_()
             self.view("@flat_v").zero_()
@@ -283,7 +288,8 @@ class Engine:
                     else:
                         full = glob[r, c]
                     del glob
-                w.copy_(full.to(torch.bfloat16))
+                if not self.zero3:
+                    w.copy_(full.to(torch.bfloat16))
                 # fp32 master copy of the part of this tensor that falls into this rank's optimizer shard
                 lo = nt.flat_off512 * 512
                 hi = lo + nt.rows * nt.cols
@@ -293,7 +299,17 @@ class Engine:
                 a, b = max(lo, shard_lo), min(hi, shard_hi)
                 if a < b:
                     master[a - shard_lo:b - shard_lo].copy_(full.reshape(-1)[a - lo:b - lo])
+                    if self.zero3:
+                        pshard[a - shard_lo:b - shard_lo].copy_(full.reshape(-1)[a - lo:b - lo].to(torch.bfloat16))
         torch.cuda.synchronize(self.device)
+        self._peer_barrier()
+
+    def _peer_barrier(self):
+        """Members read each other's parameter shards from the first kernel of a step (zero_stage = 3):
+        nobody starts before every member has written its shard."""
+        if getattr(self, "zero3", False) and self.dist is not None and self.dist.is_initialized():
+            torch.cuda.synchronize(self.device)
+            self.dist.barrier(device_ids=[self.local_rank])
 
     # ------------------------------------------------------------------ stepping
     def use_graph(self, on=True):
@@ -440,6 +456,7 @@ class Engine:
                 with torch.cuda.stream(self.stream):
                     t.view(torch.uint8).view(-1).copy_(src.to(self.device))
         self.synchronize()
+        self._peer_barrier()
         return True
 
     # ------------------------------------------------------------------ metrics

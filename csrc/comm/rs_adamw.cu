@@ -32,6 +32,7 @@ struct RsAdamwParams {
     float gscale;
     uint32_t seq;
     unsigned int* done_counter;
+    int local_params;  // bf16 parameters sharded like the optimizer state: write my shard only
     int* status;
 };
 
@@ -77,9 +78,13 @@ __global__ void __launch_bounds__(256) rs_adamw_kernel(const PeerTable pt, const
             uint2 o;
             o.x = pack_bf16(w[0], w[1]);
             o.y = pack_bf16(w[2], w[3]);
+            if (p.local_params) {
+                *reinterpret_cast<uint2*>(pt.base[pt.rank] + p.param_off + j * 2) = o;
+            } else {
 #pragma unroll
-            for (int mbr = 0; mbr < kMaxPeers; ++mbr)
-                if (mbr < pt.size) *reinterpret_cast<uint2*>(pt.base[mbr] + p.param_off + i * 2) = o;
+                for (int mbr = 0; mbr < kMaxPeers; ++mbr)
+                    if (mbr < pt.size) *reinterpret_cast<uint2*>(pt.base[mbr] + p.param_off + i * 2) = o;
+            }
         }
     }
     // Exit handshake by the last CTA of the grid: peers may reuse their gradient buffers and may
@@ -105,7 +110,7 @@ using namespace cai;
 
 int cai_fused_rs_adamw(const PeerTable& pt, unsigned long long grad_off, unsigned long long param_off, float* master,
                        float* m, float* v, long long n_flat, long long n_shard, const float* hyper, float gscale,
-                       uint32_t seq, unsigned int* done_counter, cudaStream_t st) {
+                       uint32_t seq, unsigned int* done_counter, int local_params, cudaStream_t st) {
     if ((n_shard & 3) || (n_flat & 3)) {
         set_last_error("rs_adamw: element counts must be multiples of 4");
         return CAI_K_BAD_ARG;
@@ -116,6 +121,7 @@ int cai_fused_rs_adamw(const PeerTable& pt, unsigned long long grad_off, unsigne
     p.n_flat = n_flat; p.n_shard = n_shard;
     p.hyper = hyper; p.gscale = gscale; p.seq = seq;
     p.done_counter = done_counter;
+    p.local_params = local_params;
     const int dev = current_device();
     p.status = status_words(dev);
     const int grid = sm_count(dev) * 4;

@@ -101,8 +101,11 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int j = blockIdx.x;  // kv tile
-    const int g = blockIdx.y, b = blockIdx.z;
+    // linear dispatch order -> (kv tile slowest, heaviest first; heads and batch fastest)
+    const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    const int heads_all = gridDim.y * gridDim.z;
+    const int j = lin / heads_all;  // kv tile
+    const int g = (lin % heads_all) % gridDim.y, b = (lin % heads_all) / gridDim.y;
     const int rep = p.nh / p.nkv;
     const int nq = p.S / kAttnTile;
     const int per_head = nq - j;          // query tiles at or below the diagonal
@@ -277,8 +280,10 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int i = gridDim.x - 1 - blockIdx.x;  // q tile, heaviest first
-    const int h = blockIdx.y, b = blockIdx.z;
+    const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    const int heads_all = gridDim.y * gridDim.z;
+    const int i = gridDim.x - 1 - lin / heads_all;  // q tile, heaviest first across all heads
+    const int h = (lin % heads_all) % gridDim.y, b = (lin % heads_all) / gridDim.y;
     const int g = h / (p.nh / p.nkv);
     const int n = i + 1;
     const int row_base = b * p.S;

@@ -53,8 +53,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int pair = gridDim.x - 1 - blockIdx.x;  // heaviest (latest) query tiles first
-    const int h = blockIdx.y, b = blockIdx.z;
+    // CTAs are dispatched in linear block order; walk the query tiles slowest so that the heaviest
+    // (latest) tiles of every head start first and the light ones fill the tail of the grid
+    const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    const int heads_all = gridDim.y * gridDim.z;
+    const int pair = gridDim.x - 1 - lin / heads_all;
+    const int h = (lin % heads_all) % gridDim.y, b = (lin % heads_all) / gridDim.y;
     const int g = h / (p.nh / p.nkv);
     const int qA = pair * 2 * kAttnTile, qB = qA + kAttnTile;
     const int nA = qA / kAttnTile + 1;

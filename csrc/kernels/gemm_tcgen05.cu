@@ -16,6 +16,7 @@
 // (src/cuda/cai_gpu_train.cu:40-74) and folds its add_k / zero_k passes
 // (src/cuda/cai_kernels.cu:161-164, cai_gpu_train.cu:75-78) into the epilogue.
 #include "../comm/fused.h"
+#include "../comm/gather.cuh"
 #include "../comm/peer.cuh"
 #include "../plan/formats.h"
 #include "cai_kernels.h"
@@ -60,6 +61,11 @@ struct GemmParams {
     const int* seg_counts;
     int seg_rows;
     int seg_mode;
+    // ---- kGemmGatherB: B lives in a staging buffer that the leading n_copy CTAs fill from the sharded
+    // parameter space (gather.cuh); b_elem_off is the element offset of B inside the staged range.
+    GatherJob gat;
+    long long b_elem_off;
+    long long ldb;
 };
 
 __device__ __forceinline__ bool seg_live(const GemmParams& p, int row0) {
@@ -67,7 +73,7 @@ __device__ __forceinline__ bool seg_live(const GemmParams& p, int row0) {
     return row0 - slab * p.seg_rows < p.seg_counts[slab];
 }
 
-constexpr int kGemmPlain = 0, kGemmAllGatherA = 1, kGemmReduceScatter = 2;
+constexpr int kGemmPlain = 0, kGemmAllGatherA = 1, kGemmReduceScatter = 2, kGemmGatherB = 3;
 
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
     const int per_group = p.group_m * p.tiles_n;
@@ -177,6 +183,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 return;
             }
         }
+        if (p.mode == kGemmGatherB && static_cast<int>(blockIdx.x) < p.n_copy) {
+            // parameter shards are stable for the whole forward / backward pass: no entry handshake
+            if (threadIdx.x == 0) gather_copy_role(p.pt, p.gat, static_cast<int>(blockIdx.x), epoch, smem, bars, p.status);
+            return;
+        }
     }
     const int cta = static_cast<int>(blockIdx.x) - p.n_copy;
     const int ncta = static_cast<int>(gridDim.x) - p.n_copy;
@@ -239,6 +250,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         break;
                     }
                     fence_proxy_async_all();
+                }
+                if (p.mode == kGemmGatherB) {
+                    // the rows of B this tile reads must have been staged by a copy CTA
+                    long long x = p.b_elem_off, y;
+                    if (!p.b_mn) {
+                        const int n1 = n0 + BN < p.N ? n0 + BN : p.N;
+                        y = x + static_cast<long long>(n1) * p.ldb;
+                        x += static_cast<long long>(n0) * p.ldb;
+                    } else {
+                        y = x + static_cast<long long>(p.K) * p.ldb;
+                    }
+                    if (!gather_wait_range(p.pt, p.gat, x, y, epoch, p.status)) {
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
                 }
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (p.seg_mode == 2 && !seg_live(p, kb * kBK)) continue;
@@ -634,6 +661,7 @@ static void plain_params(GemmParams& p) {
     p.epoch_base = nullptr; p.seq = 0; p.src_off = 0; p.stage_off = 0; p.a_full = nullptr; p.ld_src = 0;
     p.pt = PeerTable{};
     p.seg_counts = nullptr; p.seg_rows = 0; p.seg_mode = 0;
+    p.gat = GatherJob{}; p.b_elem_off = 0; p.ldb = 0;
     p.R = nullptr; p.ldr = 0; p.alpha = 1.f; p.epi = CAI_EPI_BF16; p.a_mn = 0;
 }
 
@@ -732,5 +760,36 @@ int cai_fused_gemm_rs(const PeerTable& pt, int group_kind, const void* A, const 
     p.epoch_base = epoch_base; p.seq = seq;
     p.stage_off = stage_off;
     p.pt = pt;
+    return gemm_dispatch(A, B, lda, ldb, p, 0, st);
+}
+
+// C = op(A) * op(B) (+ residual) where B is a parameter inside the staged range [lo, hi) of the sharded
+// flat parameter space: the leading copy CTAs stage the whole range (every later GEMM of the layer
+// reads the staged copy), the compute CTAs start as soon as the slots under their B tile are there.
+int cai_fused_gather_gemm(const PeerTable& pt, const cai::GatherJob& job_in, const void* A, const void* B, void* C, const void* R,
+                          int M, int N, int K, long long lda, long long ldb, long long ldc, long long ldr, int a_mn, int b_mn,
+                          int epi, float alpha, const uint32_t* epoch_base, uint32_t seq, cudaStream_t st) {
+    GatherJob job = job_in;
+    gather_job_finish(job);
+    const long long b_off = static_cast<const __nv_bfloat16*>(B) - job.dst;
+    if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 3) || b_off < 0 || b_off >= job.hi - job.lo || job.nslots < 1 ||
+        job.nslots > static_cast<int>(kSigLocalSlots) || job.n_copy < 1) {
+        set_last_error("gather_gemm: B must lie inside the staged range (offset %lld of %lld)", b_off, job.hi - job.lo);
+        return CAI_K_BAD_ARG;
+    }
+    GemmParams p;
+    plain_params(p);
+    p.M = M; p.N = N; p.K = K;
+    p.a_mn = a_mn ? 1 : 0; p.b_mn = b_mn ? 1 : 0;
+    p.epi = epi; p.alpha = alpha;
+    p.C = C; p.ldc = ldc; p.R = R; p.ldr = ldr;
+    p.mode = kGemmGatherB;
+    p.group_kind = job.group_kind;
+    p.n_copy = job.n_copy;
+    p.epoch_base = epoch_base; p.seq = seq;
+    p.pt = pt;
+    p.gat = job;
+    p.b_elem_off = b_off;
+    p.ldb = ldb;
     return gemm_dispatch(A, B, lda, ldb, p, 0, st);
 }

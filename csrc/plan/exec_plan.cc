@@ -285,6 +285,7 @@ void exec_operands(const ExecOp& x, std::vector<int>* reads, std::vector<int>* w
         case K_AG_GEMM: R(0); R(1); W(2); W(3); break;
         case K_GEMM_RS: R(0); R(1); R(3); W(2); W(4); break;
         case K_RS_ADAMW: R(0); R(1); R(2); R(3); W(0); W(1); W(2); W(4); break;
+        case K_FSDP_AG_GEMM: R(0); W(1); break;
         case K_MOE_ROUTE:
             if (x.flags & 1) { R(0); R(1); R(2); R(3); W(4); } else { R(0); W(1); W(2); W(3); W(4); }
             break;
@@ -315,6 +316,11 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             return failf(err, ERR_INVALID, "MoE plans need experts %% 32 == 0 (<= 256), top_k <= 8, experts %% ep == 0");
         if (!cfg.train.comm_mode) return failf(err, ERR_INVALID, "MoE plans exist only for comm = fused (in-kernel dispatch/combine)");
     }
+    // ZeRO-3: the bf16 parameters are sharded over the data-parallel group like the optimizer state and
+    // gathered layer by layer (the gather is fused into the first GEMM that reads the layer's weights).
+    const bool zero3 = cfg.train.zero_stage >= 3 && d.dp > 1 && cfg.train.comm_mode != 0 && !moe && d.tp == 1 && d.pp == 1;
+    if (cfg.train.zero_stage >= 3 && d.dp > 1 && !zero3)
+        return failf(err, ERR_INVALID, "zero_stage = 3 needs comm = fused, tp = 1, pp = 1 and a dense model");
     if (d.cp != 1) return failf(err, ERR_INVALID, "context parallelism (cp>1) has no executable schedule");
     if (m.head_dim != 128) return failf(err, ERR_INVALID, "executable plans need head_dim = 128 (got %u)", m.head_dim);
     if (m.num_heads % d.tp || m.num_kv_heads % d.tp || m.ffn_hidden % d.tp || m.vocab_size % d.tp)
@@ -353,27 +359,55 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         uint32_t base = m.num_layers / d.pp, rem = m.num_layers % d.pp, s = b.stage;
         return s * base + std::min(s, rem);
     }();
-    for (uint32_t l = 0; l < b.layers; ++l) {
+    // Under ZeRO-3 the small vectors (norm gains) and the embedding form one group that is gathered once
+    // per step; every layer's matrices form a group of their own, contiguous in the flat space.
+    uint64_t misc_hi = 0;
+    std::vector<std::pair<uint64_t, uint64_t>> layer_range(b.layers);
+    auto lname = [&](char* nm, uint32_t l, const char* suffix) {
+        std::snprintf(nm, 40, "L%u.%s", base_layer + l, suffix);
+        return nm;
+    };
+    if (zero3) {
         char nm[40];
-        auto name = [&](const char* suffix) {
-            std::snprintf(nm, sizeof nm, "L%u.%s", base_layer + l, suffix);
-            return nm;
-        };
-        L[l].g1 = b.param(name("g1"), 1, H, 0.f);
-        L[l].wqkv = b.param(name("wqkv"), b.Cqkv, H, istd);
-        L[l].wo = b.param(name("wo"), H, b.Hq_l, istd);
-        L[l].g2 = b.param(name("g2"), 1, H, 0.f);
-        if (moe) {
-            L[l].wr = b.param(name("wr"), m.num_experts, H, istd);
-        } else {
-            L[l].wgu = b.param(name("wgu"), 2 * b.F_l, H, istd);
-            L[l].wd = b.param(name("wd"), H, b.F_l, istd);
+        for (uint32_t l = 0; l < b.layers; ++l) {
+            L[l].g1 = b.param(lname(nm, l, "g1"), 1, H, 0.f);
+            L[l].g2 = b.param(lname(nm, l, "g2"), 1, H, 0.f);
         }
-    }
-    if (b.last_stage) {
         gf = b.param("gf", 1, H, 0.f);
         if (!b.tied) head = b.param("lm_head", b.V_l, H, istd);
         else head = embed;
+        misc_hi = align_up(b.flat_elems, kFlatAlignElems);
+        for (uint32_t l = 0; l < b.layers; ++l) {
+            layer_range[l].first = align_up(b.flat_elems, kFlatAlignElems);
+            L[l].wqkv = b.param(lname(nm, l, "wqkv"), b.Cqkv, H, istd);
+            L[l].wo = b.param(lname(nm, l, "wo"), H, b.Hq_l, istd);
+            L[l].wgu = b.param(lname(nm, l, "wgu"), 2 * b.F_l, H, istd);
+            L[l].wd = b.param(lname(nm, l, "wd"), H, b.F_l, istd);
+            layer_range[l].second = align_up(b.flat_elems, kFlatAlignElems);
+        }
+    } else {
+        for (uint32_t l = 0; l < b.layers; ++l) {
+            char nm[40];
+            auto name = [&](const char* suffix) {
+                std::snprintf(nm, sizeof nm, "L%u.%s", base_layer + l, suffix);
+                return nm;
+            };
+            L[l].g1 = b.param(name("g1"), 1, H, 0.f);
+            L[l].wqkv = b.param(name("wqkv"), b.Cqkv, H, istd);
+            L[l].wo = b.param(name("wo"), H, b.Hq_l, istd);
+            L[l].g2 = b.param(name("g2"), 1, H, 0.f);
+            if (moe) {
+                L[l].wr = b.param(name("wr"), m.num_experts, H, istd);
+            } else {
+                L[l].wgu = b.param(name("wgu"), 2 * b.F_l, H, istd);
+                L[l].wd = b.param(name("wd"), H, b.F_l, istd);
+            }
+        }
+        if (b.last_stage) {
+            gf = b.param("gf", 1, H, 0.f);
+            if (!b.tied) head = b.param("lm_head", b.V_l, H, istd);
+            else head = embed;
+        }
     }
     // Expert weights come last in the flat space: everything before them is replicated over the
     // data-parallel group (gradients are reduced), the experts of an expert-parallel group are not.
@@ -412,6 +446,60 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     out->xhdr.param_elems = n_flat;
     out->xhdr.reserved = n_opt;
     const uint64_t hdr_n_rep = n_rep, hdr_n_shard = n_shard;
+    int stage_misc = -1, stage_layer[2] = {-1, -1};
+    if (zero3) {
+        // the parameter class holds this rank's shard, the resident group and two layer-sized staging buffers
+        out->tensors[b.flat_param].nbytes = n_shard * 2;
+        b.cursor[TC_PARAM] = n_shard * 2;
+        uint64_t max_layer = 0;
+        for (const auto& r : layer_range) max_layer = std::max(max_layer, r.second - r.first);
+        auto stage = [&](uint64_t elems) {
+            b.cursor[TC_PARAM] = align_up(b.cursor[TC_PARAM], kTensorAlign);
+            const int id = b.tensor_at(TC_PARAM, DT_BF16, b.cursor[TC_PARAM], 1, static_cast<uint32_t>(std::min<uint64_t>(elems, 0xFFFFFFFFu)), 0);
+            out->tensors[id].nbytes = elems * 2;
+            b.cursor[TC_PARAM] += elems * 2;
+            return id;
+        };
+        stage_misc = stage(misc_hi);
+        stage_layer[0] = stage(max_layer);
+        stage_layer[1] = b.layers > 1 ? stage(max_layer) : stage_layer[0];
+        // every parameter tensor now names its place in a staging buffer instead of the flat space
+        auto relocate = [&](const Param& q) {
+            if (q.w < 0) return;
+            const uint64_t flat_off = out->tensors[q.w].offset / 2;
+            uint64_t base = out->tensors[stage_misc].offset, lo = 0;
+            if (flat_off >= misc_hi)
+                for (uint32_t l = 0; l < b.layers; ++l)
+                    if (flat_off >= layer_range[l].first && flat_off < layer_range[l].second) {
+                        base = out->tensors[stage_layer[l & 1]].offset;
+                        lo = layer_range[l].first;
+                    }
+            out->tensors[q.w].offset = base + (flat_off - lo) * 2;
+        };
+        relocate(embed);
+        if (!b.tied) relocate(head); else head = embed;
+        relocate(gf);
+        for (LayerParams& w : L) for (const Param* q : {&w.g1, &w.wqkv, &w.wo, &w.g2, &w.wgu, &w.wd}) relocate(*q);
+    }
+    // Emits the gather of one parameter group. `fuse` marks a record that the runtime merges into the
+    // GEMM that follows it (the gather runs in that kernel's copy CTAs); otherwise it is a kernel of its own.
+    int resident[2] = {-1, -1};
+    auto gather_group = [&](int layer, bool reverse, bool fuse, uint16_t mb) {
+        if (!zero3) return;
+        uint64_t lo = 0, hi = misc_hi;
+        int dst = stage_misc;
+        if (layer >= 0) {
+            if (resident[layer & 1] == layer) return;   // still there from the forward pass
+            resident[layer & 1] = layer;
+            lo = layer_range[layer].first; hi = layer_range[layer].second;
+            dst = stage_layer[layer & 1];
+        }
+        ExecOp e = xop(K_FSDP_AG_GEMM, static_cast<uint16_t>((fuse ? 1 : 0) | (reverse ? 2 : 0)));
+        e.t[0] = b.flat_param; e.t[1] = dst;
+        e.i[0] = static_cast<int32_t>(lo >> 9); e.i[1] = static_cast<int32_t>(hi >> 9); e.i[2] = 0;
+        e.i[3] = GROUP_DP; e.i[4] = static_cast<int32_t>(b.next_seq++);
+        b.push(OP_ALL_GATHER, ST_COMPUTE_HI, 0, static_cast<double>(hi - lo) * 2 * (d.dp - 1) / d.dp, GROUP_DP, mb, &e);
+    };
 
     // ---------------- inputs, workspace
     const int tokens = b.tensor(TC_COMM, DT_INT32, ga, T);
@@ -738,6 +826,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
                 b.rmsnorm_bwd(a.hmid, w.g2.w, a.rstd2, dxn, dstream, w.g2.g, norm_scratch, T, true, !first_mb, mb);
             } else {
             // ---- MLP block: x_next = hmid + act * Wd^T
+            gather_group(l, true, true, mb);                                                      // ZeRO-3 re-gather, top of the range first
             b.col_parallel(dstream, dfull, w.wd.w, dact, b.F_l, H, true, mb);                     // dact = gather(dx) * Wd
             b.gemm(ST_COMPUTE_HI, g_rows, a.act, w.wd.g, -1, H, b.F_l, T, true, true, wg_epi, mb);  // dWd = dx^T act
             {
@@ -804,6 +893,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         z.t[0] = loss_acc;
         b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 0, 32, 0, 0, &z);
     }
+    gather_group(-1, false, false, 0);   // ZeRO-3: embedding and gains, once per step
     for (const Tick& t : schedule_1f1b(b.stage, d.pp, ga)) {
         if (t.kind == 0) forward(t.microbatch);
         else backward(t.microbatch);
@@ -828,7 +918,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     }
     if (d.dp > 1) {
         if (b.fused) {
-            ExecOp e = xop(K_RS_ADAMW);
+            ExecOp e = xop(K_RS_ADAMW, zero3 ? 1 : 0);   // flag 1: bf16 parameters are sharded too, write my shard only
             e.t[0] = b.flat_master; e.t[1] = b.flat_m; e.t[2] = b.flat_v; e.t[3] = b.flat_grad; e.t[4] = b.flat_param;
             e.i[0] = static_cast<int32_t>(n_rep & 0xFFFFFFFFu); e.i[1] = static_cast<int32_t>(n_rep >> 32);
             e.i[2] = static_cast<int32_t>(n_shard & 0xFFFFFFFFu); e.i[3] = GROUP_DP; e.i[4] = static_cast<int32_t>(b.next_seq++);

@@ -22,6 +22,7 @@
 #include <vector>
 
 #include "../comm/fused.h"
+#include "../comm/gather.cuh"
 #include "../comm/moe.h"
 #include "../comm/peer.cuh"
 #include "../kernels/cai_kernels.h"
@@ -161,6 +162,11 @@ struct cai_exec {
     void* fused_ctx = nullptr;
     int sm_limit_hi = 0;
     uint64_t launches = 0;  // kernels / collectives enqueued by the last replay
+    // ZeRO-3: a parameter gather waiting to be merged into the GEMM that follows it in the op table
+    GatherJob pending_gather{};
+    uint32_t pending_seq = 0;
+    bool has_pending_gather = false;
+    long long n_shard = 0;  // elements of the flat parameter space each data-parallel member owns
 
     void* ptr(int t) const { return t >= 0 ? arena + tensors[t].offset : nullptr; }
     long long ld(int t) const { return shapes[static_cast<size_t>(t) * 4 + 2]; }
@@ -182,6 +188,13 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
                                    x.i[2], x.i[3], st);
         case K_GEMM: {
             const int ta = x.flags & 1, tb = (x.flags >> 1) & 1, epi = x.flags >> 4;
+            if (ex->has_pending_gather) {
+                // the layer's weights are staged by the copy CTAs of this GEMM (B lies in the staged range)
+                ex->has_pending_gather = false;
+                return cai_fused_gather_gemm(ex->peers[GROUP_DP], ex->pending_gather, P(0), P(1), P(2), P(3), x.i[0], x.i[1], x.i[2],
+                                             ex->ld(x.t[0]), ex->ld(x.t[1]), ex->ld(x.t[2]), x.t[3] >= 0 ? ex->ld(x.t[3]) : 0, ta, tb, epi,
+                                             x.f[0], reinterpret_cast<const uint32_t*>(ex->hyper_dev) + 7, ex->pending_seq, st);
+            }
             if (x.t[4] >= 0)  // ragged expert slab: live rows per sub-slab come from a device table
                 return cai_gemm_bf16_seg(P(0), P(1), P(2), P(3), x.i[0], x.i[1], x.i[2], ex->ld(x.t[0]), ex->ld(x.t[1]),
                                          ex->ld(x.t[2]), x.t[3] >= 0 ? ex->ld(x.t[3]) : 0, ta, tb, epi, x.f[0],
@@ -259,6 +272,30 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
             }
             return 0;
         }
+        case K_FSDP_AG_GEMM: {
+            if (!ex->has_peers[GROUP_DP] || ex->n_shard <= 0) {
+                set_last_error("parameter gather needs the data-parallel peer table and a sharded plan");
+                return CAI_K_BAD_ARG;
+            }
+            GatherJob job{};
+            job.shard_off = ex->tensors[x.t[0]].offset;
+            job.n_shard = ex->n_shard;
+            job.lo = static_cast<long long>(static_cast<uint32_t>(x.i[0])) << 9;
+            job.hi = static_cast<long long>(static_cast<uint32_t>(x.i[1])) << 9;
+            job.dst = static_cast<__nv_bfloat16*>(P(1));
+            job.reverse = (x.flags >> 1) & 1;
+            job.group_kind = GROUP_DP;
+            if (x.flags & 1) {
+                job.n_copy = x.i[2] > 0 ? x.i[2] : ex->ag_copy_ctas;
+                ex->pending_gather = job;
+                ex->pending_seq = static_cast<uint32_t>(x.i[4]);
+                ex->has_pending_gather = true;   // launched together with the next GEMM
+                return 0;
+            }
+            job.n_copy = x.i[2] > 0 ? x.i[2] : 32;
+            return cai_fsdp_gather(ex->peers[GROUP_DP], job, reinterpret_cast<const uint32_t*>(ex->hyper_dev) + 7,
+                                   static_cast<uint32_t>(x.i[4]), st);
+        }
         case K_MOE_ROUTE:
             if (x.flags & 1)
                 return cai_moe_route_bwd((const float*)P(0), (const int*)P(1), (const float*)P(2), (const int*)P(3), P(4), x.i[0],
@@ -328,7 +365,7 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
             const long long n_flat = (static_cast<long long>(static_cast<uint32_t>(x.i[1])) << 32) | static_cast<uint32_t>(x.i[0]);
             const long long n_shard = static_cast<uint32_t>(x.i[2]);
             return cai_fused_rs_adamw(pt, ex->tensors[x.t[3]].offset, ex->tensors[x.t[4]].offset, (float*)P(0), (float*)P(1),
-                                      (float*)P(2), n_flat, n_shard, ex->hyper_dev, x.f[0], seq, ex->counters_dev, st);
+                                      (float*)P(2), n_flat, n_shard, ex->hyper_dev, x.f[0], seq, ex->counters_dev, x.flags & 1, st);
         }
         default:
             if (ex->fused_hook) return ex->fused_hook(ex->fused_ctx, ex, &x, static_cast<int>(op.stream_id), st);
@@ -370,7 +407,7 @@ int replay(cai_exec* ex) {
         {
             // kernels of this library behind the op (memsets and NCCL calls are not ours)
             const uint16_t k = ex->exec[op.exec - 1].kernel;
-            ex->launches += (k == K_ATTN_BWD || k == K_CROSS_ENTROPY_TP || k == K_RMSNORM_BWD) ? 3 : (k == K_ZERO || (k >= K_NCCL_ALL_REDUCE && k <= K_NCCL_RECV)) ? 0 : 1;
+            ex->launches += (k == K_ATTN_BWD || k == K_CROSS_ENTROPY_TP || k == K_RMSNORM_BWD) ? 3 : (k == K_ZERO || (k >= K_NCCL_ALL_REDUCE && k <= K_NCCL_RECV) || (k == K_FSDP_AG_GEMM && (ex->exec[op.exec - 1].flags & 1))) ? 0 : 1;
         }
         if (tr) cudaEventRecord(tr->stop, st);
     }
@@ -459,8 +496,10 @@ CAI_API int cai_exec_create(cai_exec** out, const void* plan_bytes, size_t nbyte
         uint32_t fused = 0;
         for (const ExecOp& x : ex->exec)
             if (x.kernel == K_AG_GEMM || x.kernel == K_GEMM_RS || x.kernel == K_RS_ADAMW || x.kernel == K_MOE_DISPATCH_GEMM ||
-                x.kernel == K_MOE_GEMM_COMBINE)
+                x.kernel == K_MOE_GEMM_COMBINE || x.kernel == K_FSDP_AG_GEMM)
                 ++fused;
+        for (const NamedTensor& nt : ex->named)
+            if (!strcmp(nt.name, "@flat_split")) ex->n_shard = static_cast<long long>(nt.rows) << 9;
         ex->epochs_per_step = 2 * fused + 2;
     }
     cudaMallocHost(&ex->hyper_host, 8 * sizeof(float));

@@ -16,6 +16,7 @@ def main():
     ap.add_argument("--pp", type=int, default=1)
     ap.add_argument("--ep", type=int, default=1)
     ap.add_argument("--config", default="tiny_mp")
+    ap.add_argument("--zero", type=int, default=1)
     ap.add_argument("--comm", default="baseline")
     ap.add_argument("--steps", type=int, default=6)
     ap.add_argument("--graph", type=int, default=0)
@@ -26,7 +27,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", 1))
     rank = int(os.environ.get("RANK", 0))
     text = (ROOT / "configs" / f"{a.config}.cfg").read_text()
-    text += f"\ngpus_per_rack = {world}\ngpus_per_tray = {world}\ntp = {a.tp}\npp = {a.pp}\nep = {a.ep}\ncomm = {a.comm}\n"
+    text += f"\ngpus_per_rack = {world}\ngpus_per_tray = {world}\ntp = {a.tp}\npp = {a.pp}\nep = {a.ep}\ncomm = {a.comm}\nzero_stage = {a.zero}\n"
     eng = Engine(config_text=text, rank=rank, world=world, local_rank=int(os.environ.get("LOCAL_RANK", rank)))
     m = eng.model
     dp = eng.hdr.dp

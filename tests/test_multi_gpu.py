@@ -61,6 +61,17 @@ def test_data_parallel_2_baseline_and_fused_agree(tmp_path):
     assert a["dp"] == 2
 
 
+def test_zero3_parameter_sharding_matches_replicated_parameters(tmp_path):
+    """zero_stage = 3 (bf16 parameters sharded, gathered layer by layer inside the first consuming GEMM)
+    against zero_stage = 1 (parameters replicated) on the same data."""
+    if _gpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    a = run_case(tmp_path, 2, comm="fused", zero=1)
+    b = run_case(tmp_path, 2, comm="fused", zero=3)
+    close(a["losses"], b["losses"], tol=0.01)
+    assert b["losses"][-1] < b["losses"][0]
+
+
 def test_expert_parallel_2_matches_replicated_experts(tmp_path):
     """Same MoE model and global batch on 2 GPUs: experts replicated (ep = 1, gradients reduced over dp)
     against experts sharded (ep = 2, tokens exchanged by the dispatch / combine kernels)."""
