@@ -193,3 +193,47 @@ def flash_attn_bwd(qkv, out, dout, lse, B, S, nh, nkv, hd, scale=None, dqkv=None
 
 
 __all__ = [n for n in dir() if not n.startswith("_")]
+
+
+# ---------------------------------------------------------------------------- fp8 (e4m3) block-scaled GEMM
+def quant_rows_1x128(x):
+    """bf16 ``[rows, cols]`` -> (e4m3 ``[rows, cols]``, fp32 scales ``[rows, cols/128]``): one scale
+    per row and 128 columns (``amax / 448``), the activation side of the block-scaled GEMM."""
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1 and x.shape[1] % 128 == 0
+    rows, cols = x.shape
+    q = torch.empty(rows, cols, device=x.device, dtype=torch.float8_e4m3fn)
+    s = torch.empty(rows, cols // 128, device=x.device, dtype=torch.float32)
+    check(lib().cai_quant_rows_1x128(_p(x), x.stride(0), _p(q), cols, _p(s), rows, cols, _stream()), "quant_rows")
+    return q, s
+
+
+def quant_blocks_128x128(w, transposed=False):
+    """bf16 ``[rows, cols]`` -> (e4m3 copy, fp32 scales ``[ceil(rows/128), ceil(cols/128)]``), one scale
+    per 128x128 block (the weight side). With ``transposed`` also returns the e4m3 transpose
+    ``[cols, rows]`` and its scale table, which the input-gradient GEMM consumes."""
+    assert w.dtype == torch.bfloat16 and w.dim() == 2 and w.stride(1) == 1
+    rows, cols = w.shape
+    nbr, nbc = (rows + 127) // 128, (cols + 127) // 128
+    q = torch.empty(rows, cols, device=w.device, dtype=torch.float8_e4m3fn)
+    s = torch.empty(nbr, nbc, device=w.device, dtype=torch.float32)
+    qt = torch.empty(cols, rows, device=w.device, dtype=torch.float8_e4m3fn) if transposed else None
+    st = torch.empty(nbc, nbr, device=w.device, dtype=torch.float32) if transposed else None
+    check(lib().cai_quant_blocks_128x128(_p(w), w.stride(0), _p(q), cols, _p(qt), rows, _p(s), _p(st), rows, cols, _stream()),
+          "quant_blocks")
+    return (q, s, qt, st) if transposed else (q, s)
+
+
+def gemm_fp8(aq, sa, bq, sb, *, out=None, out_dtype=torch.bfloat16, residual=None):
+    """``C[M,N] = sum_kb sa[:,kb,None] * sb[n//128,kb] * (aq[:,kb] @ bq[:,kb]^T)`` on the tcgen05 tensor
+    cores (kind::f8f6f4) with the per-block scale-and-add in the epilogue warps. ``aq`` ``[M,K]``,
+    ``bq`` ``[N,K]`` e4m3; ``sa`` ``[M,K/128]``, ``sb`` ``[ceil(N/128),K/128]`` fp32."""
+    M, K = aq.shape
+    N, Kb = bq.shape
+    assert K == Kb and K % 128 == 0 and aq.stride(1) == 1 and bq.stride(1) == 1
+    assert sa.shape == (M, K // 128) and sb.shape == ((N + 127) // 128, K // 128) and sa.is_contiguous() and sb.is_contiguous()
+    if out is None:
+        out = torch.empty(M, N, device=aq.device, dtype=out_dtype)
+    epi = EPI_F32 if out.dtype == torch.float32 else (EPI_BF16_RESIDUAL if residual is not None else EPI_BF16)
+    check(lib().cai_gemm_fp8_blockscaled(_p(aq), _p(sa), _p(bq), _p(sb), _p(out), _p(residual), M, N, K, aq.stride(0), bq.stride(0),
+                                         out.stride(0), residual.stride(0) if residual is not None else 0, epi, _stream()), "gemm_fp8")
+    return out

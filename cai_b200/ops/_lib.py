@@ -36,6 +36,10 @@ def _declare(L):
     L.cai_sm_count.argtypes = []
     L.cai_gemm_bf16.argtypes = [P, P, P, P, I, I, I, LL, LL, LL, LL, I, I, I, F, I, P]
     L.cai_gemm_bf16_seg.argtypes = [P, P, P, P, I, I, I, LL, LL, LL, LL, I, I, I, F, P, I, I, I, P]
+    if hasattr(L, "cai_gemm_fp8_blockscaled"):
+        L.cai_gemm_fp8_blockscaled.argtypes = [P, P, P, P, P, P, I, I, I, LL, LL, LL, LL, I, P]
+        L.cai_quant_rows_1x128.argtypes = [P, LL, P, LL, P, I, I, P]
+        L.cai_quant_blocks_128x128.argtypes = [P, LL, P, LL, P, LL, P, P, I, I, P]
     L.cai_moe_route_fwd.argtypes = [P, P, P, P, P, I, I, I, I, P]
     L.cai_moe_route_bwd.argtypes = [P, P, P, P, P, I, I, I, P]
     ULL = ctypes.c_ulonglong

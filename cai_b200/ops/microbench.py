@@ -6,6 +6,7 @@ iterations). Also the small fixed-size workloads that profiler captures are take
     python -m cai_b200.ops.microbench attn_bwd --batch 1 --seq 4096 --heads 16 --kv-heads 8
     python -m cai_b200.ops.microbench rmsnorm_bwd --rows 4096 --hidden 2048
     python -m cai_b200.ops.microbench swiglu --rows 4096 --ffn 8192
+    python -m cai_b200.ops.microbench gemm_fp8 --m 8192 --n 8192 --k 8192
 
 Prints one JSON line per run: milliseconds (median of ``--iters`` after ``--warmup``), achieved
 TFLOP/s or GB/s, and the fraction of the measured peaks in ``MEASURED_PEAKS.json`` when present.
@@ -51,7 +52,7 @@ def timeit(fn, iters, warmup, flush):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm_bwd", "swiglu"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "attn_fwd", "attn_bwd", "rmsnorm_bwd", "swiglu"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -82,6 +83,14 @@ def main(argv=None):
         tf = 2.0 * a.m * a.n * a.k / ms / 1e9
         out.update(m=a.m, n=a.n, k=a.k, ta=a.ta, tb=a.tb, f32_accumulate=a.f32, ms=ms, tflops=tf,
                    frac_of_peak=tf / tf_peak, peak_source=src)
+    elif a.kernel == "gemm_fp8":
+        from . import gemm_fp8, quant_blocks_128x128, quant_rows_1x128
+        xq, sx = quant_rows_1x128(torch.randn(a.m, a.k, device=dev).to(bf))
+        wq, sw = quant_blocks_128x128(torch.randn(a.n, a.k, device=dev).to(bf))
+        C = torch.empty(a.m, a.n, device=dev, dtype=bf)
+        ms = timeit(lambda: gemm_fp8(xq, sx, wq, sw, out=C), a.iters, a.warmup, flush)
+        tf = 2.0 * a.m * a.n * a.k / ms / 1e9
+        out.update(m=a.m, n=a.n, k=a.k, ms=ms, tflops=tf, frac_of_bf16_peak=tf / tf_peak, peak_source=src)
     elif a.kernel in ("attn_fwd", "attn_bwd"):
         hd = 128
         qkv = torch.randn(a.batch * a.seq, (a.heads + 2 * a.kv_heads) * hd, device=dev).to(bf)

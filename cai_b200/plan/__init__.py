@@ -26,6 +26,13 @@ TCLASSES = ["param", "grad", "optstate", "activation", "comm", "workspace"]
 DTYPES = ["fp32", "bf16", "fp16", "fp8e4m3", "fp8e5m2", "int32", "uint8"]
 DTYPE_SIZE = [4, 2, 2, 1, 1, 4, 1]
 GROUP_TP, GROUP_DP, GROUP_PP, GROUP_EP = 0, 1, 2, 3
+# kernel ids of the execution section (csrc/plan/formats.h, enum KernelId)
+KERNEL_NAMES = ["none", "embed_fwd", "embed_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "gemm", "rope", "attn_fwd", "attn_bwd",
+                "swiglu_fwd", "swiglu_bwd", "cross_entropy", "adamw", "zero", "nccl_all_reduce", "nccl_reduce_scatter",
+                "nccl_all_gather", "nccl_all_to_all", "nccl_send", "nccl_recv", "gemm_rs", "ag_gemm", "rs_adamw",
+                "fsdp_ag_gemm", "moe_route", "moe_dispatch_gemm", "moe_gemm_combine", "load_tokens", "add",
+                "cross_entropy_tp", "quant_fp8", "gemm_fp8"]
+K_GEMM, K_FSDP_AG_GEMM, K_QUANT_FP8, K_GEMM_FP8 = 5, 23, 30, 31
 OP_EVENT_RECORD, OP_EVENT_WAIT = 13, 14
 
 

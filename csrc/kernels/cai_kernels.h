@@ -48,6 +48,20 @@ CAI_API int cai_gemm_bf16_seg(const void* A, const void* B, void* C, const void*
                               int b_mn_major, int epi, float alpha, const int* seg_counts, int seg_rows, int seg_mode,
                               int sm_limit, void* stream);
 
+/* ---- fp8 (e4m3) GEMM with block scales: C[M,N] = sum_kb sa[m,kb] * sb[n/128,kb] * (Aq[m,kb] . Bq[n,kb]).
+ * Aq [M,K], Bq [N,K] e4m3 K-major (K % 128 == 0); sa [M,K/128], sb [ceil(N/128),K/128] fp32.
+ * epi: CAI_EPI_BF16, CAI_EPI_F32 or CAI_EPI_BF16_RESIDUAL. No counterpart in the reference. */
+CAI_API int cai_gemm_fp8_blockscaled(const void* Aq, const float* sa, const void* Bq, const float* sb, void* C, const void* R,
+                                     int M, int N, int K, long long lda, long long ldb, long long ldc, long long ldr, int epi,
+                                     void* stream);
+/* bf16 [rows,cols] -> e4m3 with one scale per row and 128 columns (scale [rows, cols/128], amax/448). */
+CAI_API int cai_quant_rows_1x128(const void* x, long long ldx, void* q, long long ldq, float* scale, int rows, int cols,
+                                 void* stream);
+/* bf16 [rows,cols] -> e4m3 with one scale per 128x128 block (scale [ceil(rows/128), ceil(cols/128)]); qt / scale_t
+ * (optional) receive the transposed tensor [cols,rows] and its scale table. */
+CAI_API int cai_quant_blocks_128x128(const void* w, long long ldw, void* q, long long ldq, void* qt, long long ldqt, float* scale,
+                                     float* scale_t, int rows, int cols, void* stream);
+
 /* ---- normalisation (reference: src/cuda/cai_kernels.cu:37-77, src/refmodel.c:47-77) */
 /* y = x * rsqrt(mean(x^2)+eps) * g ; rstd[row] saved for backward. */
 CAI_API int cai_rmsnorm_fwd(const void* x, const void* g, void* y, float* rstd, int rows, int H, float eps,

@@ -110,7 +110,7 @@ const char* kernel_name(uint16_t k) {
                                      "zero", "nccl_all_reduce", "nccl_reduce_scatter", "nccl_all_gather",
                                      "nccl_all_to_all", "nccl_send", "nccl_recv", "gemm_rs", "ag_gemm", "rs_adamw",
                                      "fsdp_ag_gemm", "moe_route", "moe_dispatch_gemm", "moe_gemm_combine",
-                                     "load_tokens", "add", "cross_entropy_tp"};
+                                     "load_tokens", "add", "cross_entropy_tp", "quant_fp8", "gemm_fp8"};
     return k < K_COUNT ? n[k] : "?";
 }
 bool op_is_comm(uint16_t k) {

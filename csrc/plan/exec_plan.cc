@@ -14,9 +14,11 @@
 // In comm mode "fused" those pairs are single kernels (OP_AG_GEMM / OP_GEMM_RS); in mode
 // "baseline" they are NCCL collectives next to plain GEMMs.
 #include <algorithm>
+#include <array>
 #include <cmath>
 #include <cstdarg>
 #include <cstring>
+#include <map>
 
 #include "../comm/signals.h"
 #include "plan.h"
@@ -76,6 +78,12 @@ struct Builder {
     uint32_t next_event = 0;
     uint32_t next_seq = 0;         // sequence number of the next fused compute+collective op
     int flat_param = -1, flat_grad = -1, flat_master = -1, flat_m = -1, flat_v = -1;
+    // fp8 (param_dtype = fp8e4m3, tp = 1): e4m3 copies of the linear weights (plain and transposed, one fp32
+    // scale per 128x128 block) and a scratch for the 1x128-quantised activation that feeds a GEMM
+    struct Fp8Weight { int q = -1, s = -1, qt = -1, st = -1; };
+    bool fp8 = false;
+    std::map<int, Fp8Weight> fp8w;   // keyed by the bf16 weight tensor
+    int fp8_xq = -1, fp8_sx = -1;
 
     // local dimensions
     uint32_t H, hd, nh_l, nkv_l, Hq_l, Cqkv, F_l, V_l, T, Tl, seq, mbsz, tp, layers;
@@ -166,6 +174,34 @@ struct Builder {
         x.f[0] = 1.0f;
         push(OP_GEMM, stream, 2.0 * M * N * K, 0, 0, mb, &x);
     }
+    // Linear layer product with tp = 1: C[T,N] = a[T,K] * W[N,K]^T (tb: a[T,K] * W[K,N]) (+ residual R).
+    // With fp8 weights the activation is quantised per row and 128 columns and the e4m3 tensor-core GEMM runs.
+    void linear(int a, int W, int C, int R, uint32_t N, uint32_t K, bool tb, uint16_t mb) {
+        auto it = fp8w.find(W);
+        if (!fp8 || it == fp8w.end() || K % 128) {
+            gemm(ST_COMPUTE_HI, a, W, C, R, T, N, K, false, tb, R >= 0 ? 3 : 0, mb);
+            return;
+        }
+        const Fp8Weight& w = it->second;
+        const int xq = tensor_at(TC_WORKSPACE, DT_FP8_E4M3, p->tensors[fp8_xq].offset, T, K, K);
+        const int sx = tensor_at(TC_WORKSPACE, DT_FP32, p->tensors[fp8_sx].offset, T, K / 128, K / 128);
+        ExecOp qx = xop(K_QUANT_FP8, 0);
+        qx.t[0] = a; qx.t[1] = xq; qx.t[2] = sx;
+        qx.i[0] = T; qx.i[1] = K;
+        push(OP_ELEMENTWISE, ST_COMPUTE_HI, 2.0 * T * K, 3.0 * T * K, 0, mb, &qx);
+        ExecOp x = xop(K_GEMM_FP8, static_cast<uint16_t>((R >= 0 ? 3 : 0) << 4));
+        x.t[0] = xq; x.t[1] = tb ? w.qt : w.q; x.t[2] = C; x.t[3] = R; x.t[4] = sx; x.t[5] = tb ? w.st : w.s;
+        x.i[0] = T; x.i[1] = N; x.i[2] = K;
+        push(OP_GEMM, ST_COMPUTE_HI, 2.0 * T * N * K, 0, 0, mb, &x);
+    }
+    // e4m3 copies of a weight [rows, cols]: blocks of 128x128 share a scale; the transposed copy serves the input gradient
+    void quant_weight(int W, uint16_t mb) {
+        const Fp8Weight& w = fp8w.at(W);
+        ExecOp e = xop(K_QUANT_FP8, 1);
+        e.t[0] = W; e.t[1] = w.q; e.t[2] = w.s; e.t[3] = w.qt; e.t[4] = w.st;
+        e.i[0] = rows_of(W); e.i[1] = cols_of(W);
+        push(OP_ELEMENTWISE, ST_COMPUTE_HI, 0, 4.0 * rows_of(W) * cols_of(W), 0, mb, &e);
+    }
     // GEMM over a ragged expert slab: `counts` holds the live rows of each `seg_rows`-row sub-slab.
     // seg_mode 1 segments M (forward / input gradient), 2 segments K (weight gradient).
     void gemm_seg(int A, int B, int C, uint32_t M, uint32_t N, uint32_t K, bool ta, bool tb, int epi, int counts,
@@ -205,7 +241,7 @@ struct Builder {
     // x_full receives the gathered rows (kept for the weight gradient).
     void col_parallel(int x_local, int x_full, int W, int y, uint32_t N, uint32_t K, bool tb, uint16_t mb) {
         if (tp == 1) {
-            gemm(ST_COMPUTE_HI, x_local, W, y, -1, T, N, K, false, tb, 0, mb);
+            linear(x_local, W, y, -1, N, K, tb, mb);
             return;
         }
         if (fused) {
@@ -227,7 +263,7 @@ struct Builder {
     void row_parallel(int a, int W, int residual, int out_local, int partial, int rs_tmp, uint32_t N, uint32_t K, bool tb,
                       uint16_t mb) {
         if (tp == 1) {
-            gemm(ST_COMPUTE_HI, a, W, out_local, residual, T, N, K, false, tb, residual >= 0 ? 3 : 0, mb);
+            linear(a, W, out_local, residual, N, K, tb, mb);
             return;
         }
         if (fused) {
@@ -286,6 +322,8 @@ void exec_operands(const ExecOp& x, std::vector<int>* reads, std::vector<int>* w
         case K_GEMM_RS: R(0); R(1); R(3); W(2); W(4); break;
         case K_RS_ADAMW: R(0); R(1); R(2); R(3); W(0); W(1); W(2); W(4); break;
         case K_FSDP_AG_GEMM: R(0); W(1); break;
+        case K_QUANT_FP8: R(0); W(1); W(2); W(3); W(4); break;
+        case K_GEMM_FP8: R(0); R(1); R(3); R(4); R(5); W(2); break;
         case K_MOE_ROUTE:
             if (x.flags & 1) { R(0); R(1); R(2); R(3); W(4); } else { R(0); W(1); W(2); W(3); W(4); }
             break;
@@ -321,6 +359,9 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     const bool zero3 = cfg.train.zero_stage >= 3 && d.dp > 1 && cfg.train.comm_mode != 0 && !moe && d.tp == 1 && d.pp == 1;
     if (cfg.train.zero_stage >= 3 && d.dp > 1 && !zero3)
         return failf(err, ERR_INVALID, "zero_stage = 3 needs comm = fused, tp = 1, pp = 1 and a dense model");
+    // fp8 parameters: forward and input-gradient GEMMs of the linear layers run in e4m3 with block scales
+    // (tp = 1, dense); weight gradients, attention, the LM head and everything else stay bf16.
+    const bool fp8 = m.param_dtype == DT_FP8_E4M3 && d.tp == 1 && !moe;
     if (d.cp != 1) return failf(err, ERR_INVALID, "context parallelism (cp>1) has no executable schedule");
     if (m.head_dim != 128) return failf(err, ERR_INVALID, "executable plans need head_dim = 128 (got %u)", m.head_dim);
     if (m.num_heads % d.tp || m.num_kv_heads % d.tp || m.ffn_hidden % d.tp || m.vocab_size % d.tp)
@@ -500,6 +541,43 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         e.i[3] = GROUP_DP; e.i[4] = static_cast<int32_t>(b.next_seq++);
         b.push(OP_ALL_GATHER, ST_COMPUTE_HI, 0, static_cast<double>(hi - lo) * 2 * (d.dp - 1) / d.dp, GROUP_DP, mb, &e);
     };
+    // fp8 copies of the linear weights: one set per layer, or a single set under ZeRO-3 (quantised right after
+    // the layer's gather, which then is a kernel of its own instead of riding in the first GEMM)
+    b.fp8 = fp8;
+    int fp8_resident = -1;
+    if (fp8) {
+        const uint32_t max_k = std::max({H, b.Hq_l, b.F_l, b.Cqkv, 2 * b.F_l});
+        b.fp8_xq = b.tensor(TC_WORKSPACE, DT_FP8_E4M3, T, max_k);
+        b.fp8_sx = b.tensor(TC_WORKSPACE, DT_FP32, T, (max_k + 127) / 128);
+        const uint32_t sets = zero3 ? 1 : b.layers;
+        std::vector<std::array<Builder::Fp8Weight, 4>> set(sets);
+        for (uint32_t i = 0; i < sets; ++i) {
+            const Param* ws[4] = {&L[i].wqkv, &L[i].wo, &L[i].wgu, &L[i].wd};
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t r = ws[k]->rows, c = ws[k]->cols;
+                Builder::Fp8Weight& f = set[i][k];
+                f.q = b.tensor(TC_PARAM, DT_FP8_E4M3, r, c);
+                f.qt = b.tensor(TC_PARAM, DT_FP8_E4M3, c, r);
+                f.s = b.tensor(TC_PARAM, DT_FP32, (r + 127) / 128, (c + 127) / 128);
+                f.st = b.tensor(TC_PARAM, DT_FP32, (c + 127) / 128, (r + 127) / 128);
+            }
+        }
+        for (uint32_t l = 0; l < b.layers; ++l) {
+            const Param* ws[4] = {&L[l].wqkv, &L[l].wo, &L[l].wgu, &L[l].wd};
+            for (int k = 0; k < 4; ++k) b.fp8w[ws[k]->w] = set[zero3 ? 0 : l][k];
+        }
+    }
+    auto quant_layer = [&](uint32_t l, uint16_t mb) {
+        for (const Param* q : {&L[l].wqkv, &L[l].wo, &L[l].wgu, &L[l].wd}) b.quant_weight(q->w, mb);
+    };
+    // makes layer l's weights usable: ZeRO-3 gather (fused into the next GEMM unless fp8 needs them quantised first)
+    auto prepare_layer = [&](int l, bool reverse, uint16_t mb) {
+        gather_group(l, reverse, !fp8, mb);
+        if (fp8 && zero3 && fp8_resident != l) {
+            quant_layer(static_cast<uint32_t>(l), mb);
+            fp8_resident = l;
+        }
+    };
 
     // ---------------- inputs, workspace
     const int tokens = b.tensor(TC_COMM, DT_INT32, ga, T);
@@ -629,6 +707,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     auto layer_forward = [&](uint16_t mb, const LayerActs& a, const LayerParams& w, int x_next) {
         // attention block
         b.rmsnorm_fwd(a.x, w.g1.w, tp > 1 ? xn_local : a.xn1, a.rstd1, Tl, mb);
+        prepare_layer(static_cast<int>(&w - L.data()), false, mb);   // ZeRO-3: this layer's weights, inside the QKV GEMM
         b.col_parallel(tp > 1 ? xn_local : a.xn1, a.xn1, w.wqkv.w, a.qkv, b.Cqkv, H, false, mb);
         {
             ExecOp e = xop(K_ROPE);
@@ -826,7 +905,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
                 b.rmsnorm_bwd(a.hmid, w.g2.w, a.rstd2, dxn, dstream, w.g2.g, norm_scratch, T, true, !first_mb, mb);
             } else {
             // ---- MLP block: x_next = hmid + act * Wd^T
-            gather_group(l, true, true, mb);                                                      // ZeRO-3 re-gather, top of the range first
+            prepare_layer(l, true, mb);                                                           // ZeRO-3 re-gather, top of the range first
             b.col_parallel(dstream, dfull, w.wd.w, dact, b.F_l, H, true, mb);                     // dact = gather(dx) * Wd
             b.gemm(ST_COMPUTE_HI, g_rows, a.act, w.wd.g, -1, H, b.F_l, T, true, true, wg_epi, mb);  // dWd = dx^T act
             {
@@ -894,6 +973,8 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 0, 32, 0, 0, &z);
     }
     gather_group(-1, false, false, 0);   // ZeRO-3: embedding and gains, once per step
+    if (fp8 && !zero3)
+        for (uint32_t l = 0; l < b.layers; ++l) quant_layer(l, 0);   // weights changed in the last optimizer step
     for (const Tick& t : schedule_1f1b(b.stage, d.pp, ga)) {
         if (t.kind == 0) forward(t.microbatch);
         else backward(t.microbatch);

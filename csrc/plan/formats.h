@@ -192,6 +192,8 @@ enum KernelId : uint16_t {
     K_LOAD_TOKENS,
     K_ADD,
     K_CROSS_ENTROPY_TP,
+    K_QUANT_FP8,             // flags 0: rows 1x128 (activations), 1: blocks 128x128 (+ transposed copy) (weights)
+    K_GEMM_FP8,              // e4m3 block-scaled GEMM
     K_COUNT
 };
 

@@ -272,6 +272,15 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
             }
             return 0;
         }
+        case K_QUANT_FP8:
+            if (x.flags & 1)
+                return cai_quant_blocks_128x128(P(0), ex->ld(x.t[0]), P(1), ex->ld(x.t[1]), P(3), x.t[3] >= 0 ? ex->ld(x.t[3]) : 0,
+                                                (float*)P(2), (float*)P(4), x.i[0], x.i[1], st);
+            return cai_quant_rows_1x128(P(0), ex->ld(x.t[0]), P(1), ex->ld(x.t[1]), (float*)P(2), x.i[0], x.i[1], st);
+        case K_GEMM_FP8:
+            return cai_gemm_fp8_blockscaled(P(0), (const float*)P(4), P(1), (const float*)P(5), P(2), P(3), x.i[0], x.i[1], x.i[2],
+                                            ex->ld(x.t[0]), ex->ld(x.t[1]), ex->ld(x.t[2]), x.t[3] >= 0 ? ex->ld(x.t[3]) : 0,
+                                            x.flags >> 4, st);
         case K_FSDP_AG_GEMM: {
             if (!ex->has_peers[GROUP_DP] || ex->n_shard <= 0) {
                 set_last_error("parameter gather needs the data-parallel peer table and a sharded plan");
