@@ -34,9 +34,27 @@ sys.path.insert(0, str(ROOT))
 SIM_BASELINE_TOKENS_PER_S_TP8 = 7.55e5  # reference simulator's prediction for this config at tp=8
 
 
-def config_text(n_gpus: int, comm: str) -> str:
-    base = (ROOT / "configs" / "b200_tp8.cfg").read_text()
-    return base + f"\ngpus_per_rack = {n_gpus}\ntrays_per_rack = 1\ngpus_per_tray = {n_gpus}\ntp = {n_gpus}\ncomm = {comm}\n"
+# The named configs of the benchmark set and how each spreads over N GPUs of one box.
+CONFIGS = {
+    "tp8": ("b200_tp8.cfg", "dense 24L h2048 ffn8192 16h/8kv hd128 V32000 (configs/b200_tp8.cfg)", "tp"),
+    "fsdp8b": ("b200_fsdp8b.cfg", "dense 8B 32L h4096 ffn14336 32h/8kv V128256 seq8192, ZeRO-3 + fp8 linear layers "
+               "(configs/b200_fsdp8b.cfg)", "dp"),
+    "moe_ep8": ("b200_moe_ep8.cfg", "MoE 16L h4096 64 experts ffn1536 top-8 (configs/b200_moe_ep8.cfg)", "ep"),
+    "pp2tp4": ("b200_pp2tp4.cfg", "dense 48L h6144 ffn24576 48h/8kv, 1F1B, full recompute (configs/b200_pp2tp4.cfg)", "pp2"),
+}
+
+
+def config_text(n_gpus: int, comm: str, name: str = "tp8") -> str:
+    fname, _, how = CONFIGS[name]
+    base = (ROOT / "configs" / fname).read_text()
+    text = base + f"\ngpus_per_rack = {n_gpus}\ntrays_per_rack = 1\ngpus_per_tray = {n_gpus}\ncomm = {comm}\n"
+    if how == "tp":
+        text += f"tp = {n_gpus}\n"
+    elif how == "ep":
+        text += f"ep = {n_gpus}\n"          # data parallel over all GPUs, experts sharded over the same group
+    elif how == "pp2":
+        text += f"pp = {2 if n_gpus > 1 else 1}\ntp = {max(1, n_gpus // 2)}\n"
+    return text
 
 
 class ClockSampler:
@@ -97,7 +115,7 @@ def run_ours(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29533")
-    eng = Engine(config_text=config_text(world, args.comm), rank=rank, world=world, local_rank=local)
+    eng = Engine(config_text=config_text(world, args.comm, args.config), rank=rank, world=world, local_rank=local)
     m = eng.model
     rows = eng.hdr.num_microbatches * m.microbatch
     K, W = args.steps, max(args.warmup, 3)
@@ -107,7 +125,8 @@ def run_ours(args):
             dist.barrier(device_ids=[local])
         torch.cuda.synchronize()
 
-    batches = [synthetic_batch(m.vocab_size, m.seq_len, rows, step=s, seed=7) for s in range(2)]
+    dp_id = rank // max(1, int(eng.hdr.tp) * int(eng.hdr.num_stages))   # every data-parallel replica draws its own rows
+    batches = [synthetic_batch(m.vocab_size, m.seq_len, rows, step=s, seed=7, rank_offset=dp_id) for s in range(2)]
     loss0 = None
     for s in range(W):
         l = eng.step(*batches[s % 2])
@@ -165,14 +184,14 @@ def run_ours(args):
             "metric": "tokens/s (whole job), device-timed training step",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": (value / SIM_BASELINE_TOKENS_PER_S_TP8) if world == 8 else None,
+            "vs_baseline": (value / SIM_BASELINE_TOKENS_PER_S_TP8) if (world == 8 and args.config == "tp8") else None,
             "baseline_note": "reference publishes no measured number; ratio is against its analytic simulator's "
                              "prediction for tp=8 (7.55e5 tokens/s), given only at N=8",
-            "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init N(0,0.02) weights",
+            "dtype": "bf16" if m.param_dtype != 3 else "fp8e4m3 linear layers, bf16 elsewhere", "data": "synthetic uniform-random tokens, random-init N(0,0.02) weights",
             "impl": "cai_b200",
-            "config": {"model": "dense 24L h2048 ffn8192 16h/8kv hd128 V32000 (configs/b200_tp8.cfg)",
-                       "global_batch": int(eng.hdr.grad_accum * m.microbatch), "seq_len": int(m.seq_len),
-                       "parallelism": f"tp{world}", "microbatch": int(m.microbatch), "grad_accum": int(eng.hdr.grad_accum),
+            "config": {"model": CONFIGS[args.config][1],
+                       "global_batch": int(eng.hdr.grad_accum * m.microbatch * eng.hdr.dp), "seq_len": int(m.seq_len),
+                       "parallelism": f"tp{eng.hdr.tp} pp{eng.hdr.num_stages} dp{eng.hdr.dp} ep{eng.hdr.ep}", "microbatch": int(m.microbatch), "grad_accum": int(eng.hdr.grad_accum),
                        "comm": args.comm, "cuda_graph": bool(args.graph),
                        "l2": "working set (>10 GB per step) exceeds the 126 MB L2; no explicit flush"},
             "mfu_vs_2.25PF": eng.mfu(dev_ms * 1e-3, 2.25e15),
@@ -207,6 +226,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--comm", default="fused", choices=["fused", "baseline"])
     ap.add_argument("--graph", type=int, default=0)
+    ap.add_argument("--config", default="tp8", choices=sorted(CONFIGS), help="which named config (default: the headline one)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

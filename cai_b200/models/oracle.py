@@ -1,6 +1,7 @@
 """ctypes face of the fp64 oracle (``csrc/ref/refmodel.cc``): the CPU double-precision decoder that
 device results are checked against. Supports what the reference's oracle supports (MHA, learned
-positions, tied head) plus GQA, RoPE and N(0, std) initialisation."""
+positions, tied head) plus GQA, RoPE, N(0, std) initialisation and a mixture-of-experts MLP (softmax
+router, top-k, renormalised weights)."""
 from __future__ import annotations
 
 import ctypes
@@ -16,6 +17,8 @@ def _lib():
     if not getattr(L, "_cai_ref_declared", False):
         L.cai_ref_create.argtypes = [c_int] * 8 + [c_double, c_int, c_double, c_int, c_double, c_uint64]
         L.cai_ref_create.restype = c_void_p
+        L.cai_ref_create_moe.argtypes = [c_int] * 8 + [c_double, c_int, c_double, c_int, c_double, c_int, c_int, c_uint64]
+        L.cai_ref_create_moe.restype = c_void_p
         L.cai_ref_free.argtypes = [c_void_p]
         L.cai_ref_free.restype = None
         L.cai_ref_param_count.argtypes = [c_void_p]
@@ -41,11 +44,15 @@ def _lib():
 
 class Oracle:
     def __init__(self, vocab=64, seq=32, hidden=64, layers=2, n_heads=4, n_kv_heads=None, head_dim=16, ffn=128,
-                 eps=1e-6, rope=False, rope_theta=10000.0, tied=True, init_std=0.0, seed=1):
+                 eps=1e-6, rope=False, rope_theta=10000.0, tied=True, init_std=0.0, seed=1, experts=0, top_k=2):
         self.L = _lib()
         self.seq, self.vocab = seq, vocab
-        self.h = self.L.cai_ref_create(vocab, seq, hidden, layers, n_heads, n_kv_heads or n_heads, head_dim, ffn, eps,
-                                       int(rope), rope_theta, int(tied), init_std, seed)
+        if experts:
+            self.h = self.L.cai_ref_create_moe(vocab, seq, hidden, layers, n_heads, n_kv_heads or n_heads, head_dim, ffn,
+                                               eps, int(rope), rope_theta, int(tied), init_std, experts, top_k, seed)
+        else:
+            self.h = self.L.cai_ref_create(vocab, seq, hidden, layers, n_heads, n_kv_heads or n_heads, head_dim, ffn, eps,
+                                           int(rope), rope_theta, int(tied), init_std, seed)
         if not self.h:
             raise ValueError("invalid oracle spec")
         n = self.L.cai_ref_param_count(self.h)

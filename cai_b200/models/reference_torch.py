@@ -15,8 +15,8 @@ def rope(x, seq, theta):
     """x: [B, S, heads, hd]; rotate-half convention with position = index inside the sequence."""
     hd = x.shape[-1]
     half = hd // 2
-    pos = torch.arange(seq, device=x.device, dtype=torch.float32)
-    inv = theta ** (-torch.arange(half, device=x.device, dtype=torch.float32) / half)
+    pos = torch.arange(seq, device=x.device, dtype=x.dtype)
+    inv = theta ** (-torch.arange(half, device=x.device, dtype=x.dtype) / half)
     ang = pos[:, None] * inv[None, :]
     c, s = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
     x1, x2 = x[..., :half], x[..., half:]
@@ -84,4 +84,4 @@ def forward_loss(params: dict, tokens, targets, *, layers, heads, kv_heads, head
     h = norm(x, p["gf"])
     head = p.get("lm_head", p["embed"])
     logits = h @ head.t()
-    return F.cross_entropy(logits.view(B * S, -1).float(), targets.reshape(-1))
+    return F.cross_entropy(logits.view(B * S, -1), targets.reshape(-1))

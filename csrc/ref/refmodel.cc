@@ -99,9 +99,11 @@ RefModel::RefModel(const RefSpec& spec, uint64_t seed) : s_(spec) {
         l.Wv = take((size_t)H * Hkv_);
         l.Wo = take((size_t)Hq_ * H);
         l.g2 = take(H);
-        l.Wg = take((size_t)H * F);
-        l.Wu = take((size_t)H * F);
-        l.Wd = take((size_t)F * H);
+        const size_t ne = s_.experts > 0 ? s_.experts : 1;
+        l.Wg = take(ne * H * F);
+        l.Wu = take(ne * H * F);
+        l.Wd = take(ne * F * H);
+        l.Wr = take(s_.experts > 0 ? (size_t)H * s_.experts : 0);
     }
     ohead_ = s_.tied ? oE_ : take((size_t)V * H);
     p_.assign(o, 0.0);
@@ -137,11 +139,16 @@ RefModel::RefModel(const RefSpec& spec, uint64_t seed) : s_(spec) {
             }
         }
         for (size_t i = 0; i < (size_t)Hq_ * H; ++i) p_[l.Wo + i] = so * rng.normal();
-        for (size_t i = 0; i < (size_t)H * F; ++i) {
-            p_[l.Wg + i] = sq * rng.normal();
-            p_[l.Wu + i] = sq * rng.normal();
+        const size_t ne = s_.experts > 0 ? s_.experts : 1;
+        for (size_t e = 0; e < ne; ++e) {
+            for (size_t i = 0; i < (size_t)H * F; ++i) {
+                p_[l.Wg + e * H * F + i] = sq * rng.normal();
+                p_[l.Wu + e * H * F + i] = sq * rng.normal();
+            }
+            for (size_t i = 0; i < (size_t)F * H; ++i) p_[l.Wd + e * F * H + i] = sd * rng.normal();
         }
-        for (size_t i = 0; i < (size_t)F * H; ++i) p_[l.Wd + i] = sd * rng.normal();
+        if (s_.experts > 0)
+            for (size_t i = 0; i < (size_t)H * s_.experts; ++i) p_[l.Wr + i] = sq * rng.normal();
     }
     if (!s_.tied)
         for (size_t i = 0; i < (size_t)V * H; ++i) p_[ohead_ + i] = se * rng.normal();
@@ -167,9 +174,10 @@ size_t RefModel::offset(const char* name, size_t* count) const {
             else if (f == "Wv") { at = L.Wv; n = (size_t)H * Hkv_; }
             else if (f == "Wo") { at = L.Wo; n = (size_t)Hq_ * H; }
             else if (f == "g2") { at = L.g2; n = H; }
-            else if (f == "Wg") { at = L.Wg; n = (size_t)H * F; }
-            else if (f == "Wu") { at = L.Wu; n = (size_t)H * F; }
-            else if (f == "Wd") { at = L.Wd; n = (size_t)F * H; }
+            else if (f == "Wg") { at = L.Wg; n = (size_t)H * F * (s_.experts > 0 ? s_.experts : 1); }
+            else if (f == "Wu") { at = L.Wu; n = (size_t)H * F * (s_.experts > 0 ? s_.experts : 1); }
+            else if (f == "Wd") { at = L.Wd; n = (size_t)F * H * (s_.experts > 0 ? s_.experts : 1); }
+            else if (f == "Wr" && s_.experts > 0) { at = L.Wr; n = (size_t)H * s_.experts; }
         }
     }
     if (count) *count = n;
@@ -255,6 +263,51 @@ double RefModel::forward(int B, const int* tokens, const int* targets) {
         for (size_t i = 0; i < a.hmid.size(); ++i) a.hmid[i] += a.x[i];
         a.r2.assign(BT, 0); a.x2.assign((size_t)BT * H, 0);
         rms_fwd(a.hmid.data(), &p_[o.g2], a.x2.data(), a.r2.data(), BT, H, s_.eps);
+        if (s_.experts > 0) {
+            // mixture of experts: softmax router, top-k (ties to the lower index), weights renormalised over the k
+            const int E = s_.experts, k = s_.top_k;
+            a.rprob.assign((size_t)BT * E, 0);
+            mm(a.x2.data(), &p_[o.Wr], a.rprob.data(), BT, H, E, false);
+            a.ridx.assign((size_t)BT * k, 0); a.rw.assign((size_t)BT * k, 0);
+            a.gate.assign((size_t)BT * k * F, 0); a.up.assign((size_t)BT * k * F, 0); a.act.assign((size_t)BT * k * F, 0);
+            a.yexp.assign((size_t)BT * k * H, 0);
+            for (int i = 0; i < BT; ++i) {
+                double* pr = &a.rprob[(size_t)i * E];
+                double mx = pr[0], sum = 0;
+                for (int e = 1; e < E; ++e) mx = std::max(mx, pr[e]);
+                for (int e = 0; e < E; ++e) { pr[e] = std::exp(pr[e] - mx); sum += pr[e]; }
+                for (int e = 0; e < E; ++e) pr[e] /= sum;
+                double S = 0;
+                for (int s2 = 0; s2 < k; ++s2) {
+                    int best = -1;
+                    for (int e = 0; e < E; ++e) {
+                        bool taken = false;
+                        for (int q = 0; q < s2; ++q) taken = taken || a.ridx[(size_t)i * k + q] == e;
+                        if (!taken && (best < 0 || pr[e] > pr[best])) best = e;
+                    }
+                    a.ridx[(size_t)i * k + s2] = best;
+                    S += pr[best];
+                }
+                for (int s2 = 0; s2 < k; ++s2) {
+                    const int e = a.ridx[(size_t)i * k + s2];
+                    const size_t r = (size_t)i * k + s2;
+                    a.rw[r] = pr[e] / S;
+                    mm(&a.x2[(size_t)i * H], &p_[o.Wg + (size_t)e * H * F], &a.gate[r * F], 1, H, F, false);
+                    mm(&a.x2[(size_t)i * H], &p_[o.Wu + (size_t)e * H * F], &a.up[r * F], 1, H, F, false);
+                    for (int j = 0; j < F; ++j) {
+                        const double g = a.gate[r * F + j];
+                        a.act[r * F + j] = g / (1.0 + std::exp(-g)) * a.up[r * F + j];
+                    }
+                    mm(&a.act[r * F], &p_[o.Wd + (size_t)e * F * H], &a.yexp[r * H], 1, F, H, false);
+                }
+                for (int j = 0; j < H; ++j) {
+                    double y = a.hmid[(size_t)i * H + j];
+                    for (int s2 = 0; s2 < k; ++s2) y += a.rw[(size_t)i * k + s2] * a.yexp[((size_t)i * k + s2) * H + j];
+                    x[(size_t)i * H + j] = y;
+                }
+            }
+            continue;
+        }
         a.gate.assign((size_t)BT * F, 0); a.up.assign((size_t)BT * F, 0); a.act.assign((size_t)BT * F, 0);
         mm(a.x2.data(), &p_[o.Wg], a.gate.data(), BT, H, F, false);
         mm(a.x2.data(), &p_[o.Wu], a.up.data(), BT, H, F, false);
@@ -297,6 +350,47 @@ void RefModel::backward(int B, const int* tokens, const int* targets) {
     for (int l = L - 1; l >= 0; --l) {
         const LayerAct& a = acts_[l];
         const LayerOff& o = lo_[l];
+        if (s_.experts > 0) {
+            const int E = s_.experts, k = s_.top_k;
+            dx2.assign((size_t)BT * H, 0);
+            std::vector<double> dy(H), da(F), dg(F), du(F), dwv(k), dprob(E), dlogit(E);
+            for (int i = 0; i < BT; ++i) {
+                const double* ds = &dstream[(size_t)i * H];
+                const double* pr = &a.rprob[(size_t)i * E];
+                double S = 0;
+                for (int s2 = 0; s2 < k; ++s2) S += pr[a.ridx[(size_t)i * k + s2]];
+                for (int s2 = 0; s2 < k; ++s2) {
+                    const size_t r = (size_t)i * k + s2;
+                    const int e = a.ridx[r];
+                    double dot = 0;
+                    for (int j = 0; j < H; ++j) { dot += ds[j] * a.yexp[r * H + j]; dy[j] = a.rw[r] * ds[j]; }
+                    dwv[s2] = dot;
+                    // expert e: y = act Wd, act = silu(gate) up, gate = x2 Wg, up = x2 Wu
+                    mm_nt(dy.data(), &p_[o.Wd + (size_t)e * F * H], da.data(), 1, H, F, false);
+                    mm_tn(&a.act[r * F], dy.data(), &g_[o.Wd + (size_t)e * F * H], 1, F, H, true);
+                    for (int j = 0; j < F; ++j) {
+                        const double g = a.gate[r * F + j], sg = 1.0 / (1.0 + std::exp(-g));
+                        du[j] = da[j] * g * sg;
+                        dg[j] = da[j] * a.up[r * F + j] * sg * (1.0 + g * (1.0 - sg));
+                    }
+                    mm_nt(dg.data(), &p_[o.Wg + (size_t)e * H * F], &dx2[(size_t)i * H], 1, F, H, true);
+                    mm_nt(du.data(), &p_[o.Wu + (size_t)e * H * F], &dx2[(size_t)i * H], 1, F, H, true);
+                    mm_tn(&a.x2[(size_t)i * H], dg.data(), &g_[o.Wg + (size_t)e * H * F], 1, H, F, true);
+                    mm_tn(&a.x2[(size_t)i * H], du.data(), &g_[o.Wu + (size_t)e * H * F], 1, H, F, true);
+                }
+                // weights w_s = p_s / S over the chosen experts, then the softmax
+                double gw = 0;
+                for (int s2 = 0; s2 < k; ++s2) gw += dwv[s2] * a.rw[(size_t)i * k + s2];
+                std::fill(dprob.begin(), dprob.end(), 0.0);
+                for (int s2 = 0; s2 < k; ++s2) dprob[a.ridx[(size_t)i * k + s2]] = (dwv[s2] - gw) / S;
+                double gp = 0;
+                for (int e = 0; e < E; ++e) gp += dprob[e] * pr[e];
+                for (int e = 0; e < E; ++e) dlogit[e] = pr[e] * (dprob[e] - gp);
+                mm_nt(dlogit.data(), &p_[o.Wr], &dx2[(size_t)i * H], 1, E, H, true);
+                mm_tn(&a.x2[(size_t)i * H], dlogit.data(), &g_[o.Wr], 1, H, E, true);
+            }
+            rms_bwd(a.hmid.data(), &p_[o.g2], a.r2.data(), dx2.data(), dstream.data(), &g_[o.g2], BT, H, true);
+        } else {
         // MLP: x_next = hmid + act Wd
         dact.assign((size_t)BT * F, 0);
         mm_nt(dstream.data(), &p_[o.Wd], dact.data(), BT, H, F, false);
@@ -313,6 +407,7 @@ void RefModel::backward(int B, const int* tokens, const int* targets) {
         mm_tn(a.x2.data(), dgate.data(), &g_[o.Wg], BT, H, F, true);
         mm_tn(a.x2.data(), dup.data(), &g_[o.Wu], BT, H, F, true);
         rms_bwd(a.hmid.data(), &p_[o.g2], a.r2.data(), dx2.data(), dstream.data(), &g_[o.g2], BT, H, true);
+        }
         // attention: hmid = x + ctx Wo
         dctx.assign((size_t)BT * Hq_, 0);
         mm_nt(dstream.data(), &p_[o.Wo], dctx.data(), BT, H, Hq_, false);
@@ -437,6 +532,17 @@ void* cai_ref_create(int vocab, int seq, int hidden, int layers, int n_heads, in
     s.head_dim = head_dim; s.ffn = ffn; s.eps = eps; s.rope = rope; s.rope_theta = rope_theta; s.tied = tied;
     s.init_std = init_std;
     if (s.n_heads % s.n_kv_heads || (rope && head_dim % 2)) return nullptr;
+    return new RefModel(s, seed);
+}
+void* cai_ref_create_moe(int vocab, int seq, int hidden, int layers, int n_heads, int n_kv_heads, int head_dim, int ffn,
+                         double eps, int rope, double rope_theta, int tied, double init_std, int experts, int top_k,
+                         uint64_t seed) {
+    RefSpec s;
+    s.vocab = vocab; s.seq = seq; s.hidden = hidden; s.layers = layers; s.n_heads = n_heads;
+    s.n_kv_heads = n_kv_heads > 0 ? n_kv_heads : n_heads;
+    s.head_dim = head_dim; s.ffn = ffn; s.eps = eps; s.rope = rope; s.rope_theta = rope_theta; s.tied = tied;
+    s.init_std = init_std; s.experts = experts; s.top_k = top_k;
+    if (s.n_heads % s.n_kv_heads || (rope && head_dim % 2) || experts < 1 || top_k < 1 || top_k > experts) return nullptr;
     return new RefModel(s, seed);
 }
 void cai_ref_free(void* m) { delete static_cast<RefModel*>(m); }

@@ -5,7 +5,9 @@
 // It covers the reference's oracle (src/refmodel.c: multi-head attention, learned absolute
 // positions, tied embedding, RMSNorm with gain, SwiGLU, no biases) and the features the GPU configs
 // need that the reference's oracle lacks: grouped-query attention, rotary position embedding, an
-// untied LM head, and a choice of initialisation (1/sqrt(fan_in) like the reference, or N(0, std)).
+// untied LM head, a choice of initialisation (1/sqrt(fan_in) like the reference, or N(0, std)), and a
+// mixture-of-experts MLP (softmax router, top-k, weights renormalised over the chosen experts, no
+// capacity limit).
 #pragma once
 
 #include <cstddef>
@@ -21,6 +23,8 @@ struct RefSpec {
     double rope_theta = 10000.0;
     int tied = 1;             // LM head shares the embedding matrix
     double init_std = 0.0;    // 0: reference init (E, P ~ 0.02 N; W ~ N / sqrt(fan_in)); > 0: every matrix ~ std * N
+    int experts = 0;          // > 0: every layer's MLP is a mixture of this many SwiGLU experts of width ffn
+    int top_k = 2;            // experts per token
 };
 
 class RefModel {
@@ -36,12 +40,17 @@ public:
     std::vector<double>& params() { return p_; }
     std::vector<double>& grads() { return g_; }
     const RefSpec& spec() const { return s_; }
-    // offset of a named tensor in the flat vectors: "E", "P", "gf", "head", "L<i>.g1|Wq|Wk|Wv|Wo|g2|Wg|Wu|Wd"
+    // offset of a named tensor in the flat vectors: "E", "P", "gf", "head", "L<i>.g1|Wq|Wk|Wv|Wo|g2|Wg|Wu|Wd|Wr"
+    // (mixture of experts: Wg / Wu / Wd hold the experts back to back, Wr [hidden, experts] is the router)
     size_t offset(const char* name, size_t* count = nullptr) const;
 
 private:
-    struct LayerOff { size_t g1, Wq, Wk, Wv, Wo, g2, Wg, Wu, Wd; };
-    struct LayerAct { std::vector<double> x, r1, x1, Q, K, V, probs, ctx, hmid, r2, x2, gate, up, act; };
+    struct LayerOff { size_t g1, Wq, Wk, Wv, Wo, g2, Wg, Wu, Wd, Wr; };
+    struct LayerAct {
+        std::vector<double> x, r1, x1, Q, K, V, probs, ctx, hmid, r2, x2, gate, up, act;
+        std::vector<double> rprob, rw, yexp;   // mixture of experts: router softmax [BT,E], weights [BT,k], expert outputs [BT*k,H]
+        std::vector<int> ridx;                 // chosen experts [BT,k]; gate / up / act are then [BT*k, F]
+    };
     RefSpec s_;
     int Hq_, Hkv_;
     size_t oE_, oP_, ogf_, ohead_;
@@ -70,4 +79,8 @@ void cai_ref_backward(void* m, int B, const int* tokens, const int* targets);
 void cai_ref_adamw(void* m, double lr, double b1, double b2, double eps, double wd);
 double cai_ref_accuracy(void* m, int B, const int* targets);
 double cai_ref_grad_check(void* m, int B, const int* tokens, const int* targets, int n_probe, double h);
+// call before any forward; rebuilds the model with a mixture-of-experts MLP (same seed)
+void* cai_ref_create_moe(int vocab, int seq, int hidden, int layers, int n_heads, int n_kv_heads, int head_dim, int ffn,
+                         double eps, int rope, double rope_theta, int tied, double init_std, int experts, int top_k,
+                         uint64_t seed);
 }
