@@ -1,0 +1,222 @@
+"""Stand-alone check and micro-benchmark of the fused compute+collective GEMMs on 1..8 GPUs.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        cai_b200/parallel/fused_bench.py --op gemm_rs --tokens 4096 --out-features 2048 --in-features 2048
+
+(run as ``python cai_b200/parallel/fused_bench.py ...`` for a single process and a group of one).
+Every rank owns one buffer (signal block, inputs, staging) that the others map over CUDA IPC, as the
+engine does with its arena. For the chosen op the script
+  * checks the fused kernel against the same product computed with a plain GEMM and an NCCL
+    collective (``torch.distributed``),
+  * times both (CUDA events, L2 flushed, max over ranks), and
+  * prints one JSON line (rank 0) with the roofline: the slower of FLOPs at the measured GEMM peak and
+    the bytes that must cross NVLink at the measured per-direction peer bandwidth (770 GB/s).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+from ctypes import c_int, c_longlong, c_uint32, c_ulonglong, c_void_p
+from pathlib import Path
+
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))   # launched as a script by torch.distributed.run
+
+from cai_b200.ops import _lib as klib  # noqa: E402
+from cai_b200.ops import gemm  # noqa: E402
+GROUP_TP = 0
+NVLINK_GBS = 770.0   # measured peer copy bandwidth per direction per GPU on this pool
+
+
+class PeerBuffer:
+    """One device buffer per rank, mapped by every other rank; offset 0 holds the signal block."""
+
+    def __init__(self, nbytes: int, rank: int, world: int, device):
+        self.L = klib.lib()
+        L = self.L
+        L.cai_ipc_export.argtypes = [c_void_p, c_void_p, ctypes.POINTER(c_ulonglong)]
+        L.cai_ipc_open.argtypes = [c_void_p, c_ulonglong, ctypes.POINTER(c_void_p)]
+        L.cai_ipc_close.argtypes = [c_void_p, c_ulonglong]
+        P, I, LL, ULL = c_void_p, c_int, c_longlong, c_ulonglong
+        L.cai_fused_ag_gemm_c.argtypes = [P, I, I, ULL, I, ULL, LL, P, P, P, I, I, I, LL, LL, I, P, c_uint32, I, P]
+        L.cai_fused_gemm_rs_c.argtypes = [P, I, I, ULL, I, P, P, ULL, P, P, I, I, I, LL, LL, LL, LL, I, P, c_uint32, P]
+        self.rank, self.world = rank, world
+        self.sig_bytes = int(L.cai_signal_block_bytes())
+        self.buf = torch.zeros(self.sig_bytes + nbytes + 4096, dtype=torch.uint8, device=device)
+        self.cursor = self.sig_bytes
+        handle = ctypes.create_string_buffer(64)
+        off = c_ulonglong(0)
+        klib.check(L.cai_ipc_export(c_void_p(self.buf.data_ptr()), handle, ctypes.byref(off)), "ipc_export")
+        blobs = [None] * world
+        dist.all_gather_object(blobs, handle.raw + off.value.to_bytes(8, "little"))
+        self.opened = []
+        bases = []
+        for r, blob in enumerate(blobs):
+            if r == rank:
+                bases.append(self.buf.data_ptr())
+                continue
+            out = c_void_p()
+            o = int.from_bytes(blob[64:72], "little")
+            klib.check(L.cai_ipc_open(ctypes.create_string_buffer(blob[:64], 64), c_ulonglong(o), ctypes.byref(out)), "ipc_open")
+            self.opened.append((out.value, o))
+            bases.append(out.value)
+        self.bases = (c_void_p * world)(*[c_void_p(b) for b in bases])
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.seq = 0
+
+    def alloc(self, shape, dtype):
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        self.cursor = (self.cursor + 1023) & ~1023
+        off = self.cursor
+        self.cursor += nbytes
+        assert self.cursor <= self.buf.numel()
+        return self.buf[off:off + nbytes].view(dtype).view(*shape), off
+
+    def next_seq(self):
+        self.seq += 1
+        return self.seq
+
+    def close(self):
+        torch.cuda.synchronize()
+        dist.barrier()
+        for base, off in self.opened:
+            self.L.cai_ipc_close(c_void_p(base), c_ulonglong(off))
+        self.opened = []
+
+
+def _time(fn, iters, warmup, flush):
+    for _ in range(warmup):
+        fn()
+        torch.cuda.synchronize()
+        dist.barrier()   # back-to-back calls of one fused op have no collective in between to order buffer reuse
+    out = []
+    for _ in range(iters):
+        flush.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        out.append(s.elapsed_time(e))
+    t = torch.tensor([statistics.median(out)], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", choices=["ag_gemm", "gemm_rs"], required=True)
+    # (names chosen so that none is a prefix of an option of torch.distributed.run)
+    ap.add_argument("--tokens", type=int, default=4096, help="rows T of the full (gathered) activation")
+    ap.add_argument("--out-features", type=int, default=2048, help="N")
+    ap.add_argument("--in-features", type=int, default=2048, help="K")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--copy-ctas", type=int, default=0, help="0: chosen by the library")
+    a = ap.parse_args(argv)
+    # without a launcher: one process, a group of one (the kernels then move the local rows only)
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29591")
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if not dist.is_initialized():
+        dist.init_process_group(backend="cpu:gloo,cuda:nccl", rank=rank, world_size=world, device_id=dev)
+    L = klib.lib()
+    bf = torch.bfloat16
+    T, N, K = a.tokens, a.out_features, a.in_features
+    Tl = T // world
+    pb = PeerBuffer(2 * T * K * 2 + 2 * T * N * 2 + (64 << 20), rank, world, dev)
+    st = torch.cuda.current_stream().cuda_stream
+    torch.manual_seed(1234 + rank)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    gemm_peak = peaks.get("bf16_tflops", 1590.0)
+    res = {"op": a.op, "world": world, "T": T, "N": N, "K": K}
+    if a.op == "ag_gemm":
+        # C[T,N] = gather(x_local[Tl,K]) @ W[N,K]^T
+        x_local, x_off = pb.alloc((Tl, K), bf)
+        a_full, _ = pb.alloc((T, K), bf)
+        x_local.copy_(torch.randn(Tl, K, device=dev))
+        W = (torch.randn(N, K, device=dev) * 0.05).to(bf)
+        C = torch.empty(T, N, device=dev, dtype=bf)
+        dist.barrier()
+
+        def fused():
+            klib.check(L.cai_fused_ag_gemm_c(pb.bases, rank, world, 0, GROUP_TP, x_off, K, a_full.data_ptr(), W.data_ptr(),
+                                             C.data_ptr(), T, N, K, K, N, 0, pb.epoch.data_ptr(), pb.next_seq(), a.copy_ctas, st),
+                       "ag_gemm")
+
+        gathered = torch.empty(T, K, device=dev, dtype=bf)
+        Cb = torch.empty(T, N, device=dev, dtype=bf)
+
+        def baseline():
+            dist.all_gather_into_tensor(gathered, x_local)
+            gemm(gathered, W, out=Cb)
+
+        fused(); baseline()
+        torch.cuda.synchronize()
+        err = (C.float() - Cb.float()).abs().max().item()
+        res["max_abs_diff_vs_nccl_path"] = err
+        assert err <= 2e-2 * Cb.float().abs().max().item() + 1e-3, err
+        link_bytes = (world - 1) * Tl * K * 2          # rows pulled from the other members
+    else:
+        # out_local[Tl,N] = residual + reduce_scatter_rows(A[T,K] @ W[N,K]^T)
+        A = torch.randn(T, K, device=dev).to(bf)
+        W = (torch.randn(N, K, device=dev) * 0.05).to(bf)
+        _, stage_off = pb.alloc((world, Tl, N), bf)
+        resid = torch.randn(Tl, N, device=dev).to(bf)
+        out = torch.empty(Tl, N, device=dev, dtype=bf)
+        dist.barrier()
+
+        def fused():
+            klib.check(L.cai_fused_gemm_rs_c(pb.bases, rank, world, 0, GROUP_TP, A.data_ptr(), W.data_ptr(), stage_off,
+                                             out.data_ptr(), resid.data_ptr(), T, N, K, K, K, N, N, 0, pb.epoch.data_ptr(),
+                                             pb.next_seq(), st), "gemm_rs")
+
+        partial = torch.empty(T, N, device=dev, dtype=bf)
+        outb = torch.empty(Tl, N, device=dev, dtype=bf)
+
+        def baseline():
+            gemm(A, W, out=partial)
+            dist.reduce_scatter_tensor(outb, partial)
+            outb.add_(resid)
+
+        fused(); baseline()
+        torch.cuda.synchronize()
+        err = (out.float() - outb.float()).abs().max().item()
+        res["max_abs_diff_vs_nccl_path"] = err
+        assert err <= 3e-2 * outb.float().abs().max().item() + 1e-2, err
+        link_bytes = (world - 1) * Tl * N * 2          # partial tiles pushed to the other members
+    ms_f = _time(fused, a.iters, a.warmup, flush)
+    ms_b = _time(baseline, a.iters, a.warmup, flush)
+    flops = 2.0 * T * N * K
+    t_compute = flops / (gemm_peak * 1e12)
+    t_link = link_bytes / (NVLINK_GBS * 1e9)
+    roof = max(t_compute, t_link)
+    res.update(fused_us=ms_f * 1e3, nccl_path_us=ms_b * 1e3, speedup_vs_nccl_path=ms_b / ms_f,
+               roofline_us=roof * 1e6, roofline_bound="compute" if t_compute >= t_link else "nvlink",
+               frac_of_roofline=roof / (ms_f * 1e-3), link_bytes=link_bytes, status=klib.device_status(clear=True))
+    if rank == 0:
+        print(json.dumps(res), flush=True)
+    pb.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -48,6 +48,22 @@ CAI_API int cai_gemm_bf16_seg(const void* A, const void* B, void* C, const void*
                               int b_mn_major, int epi, float alpha, const int* seg_counts, int seg_rows, int seg_mode,
                               int sm_limit, void* stream);
 
+/* ---- fused compute + collective GEMMs over peer memory, C forms with explicit member arena bases
+ * (bases[rank] is the local one; sig_off: arena offset of the signal block, see cai_signal_block_bytes;
+ * epoch_base: device word, epoch of the call = *epoch_base + 2 * seq and must grow from call to call).
+ * ag_gemm: C[T,N] = gather_rows(every member's [T/size, K] block at arena offset src_off) * op(B);
+ *          a_full [T,K] local receives the gathered rows.
+ * gemm_rs: out_local[T/size, N] = residual + sum over members of (A[T,K] * op(B))[my rows]; stage_off is the
+ *          arena offset of a [size, T/size, N] bf16 staging buffer on every member. */
+CAI_API int cai_fused_ag_gemm_c(void* const* bases, int rank, int size, unsigned long long sig_off, int group_kind,
+                                unsigned long long src_off, long long ld_src, void* a_full, const void* B, void* C, int T, int N,
+                                int K, long long ldb, long long ldc, int b_mn, const unsigned int* epoch_base, unsigned int seq,
+                                int n_copy, void* stream);
+CAI_API int cai_fused_gemm_rs_c(void* const* bases, int rank, int size, unsigned long long sig_off, int group_kind, const void* A,
+                                const void* B, unsigned long long stage_off, void* out_local, const void* residual, int T, int N,
+                                int K, long long lda, long long ldb, long long ldo, long long ldr, int b_mn,
+                                const unsigned int* epoch_base, unsigned int seq, void* stream);
+
 /* ---- fp8 (e4m3) GEMM with block scales: C[M,N] = sum_kb sa[m,kb] * sb[n/128,kb] * (Aq[m,kb] . Bq[n,kb]).
  * Aq [M,K], Bq [N,K] e4m3 K-major (K % 128 == 0); sa [M,K/128], sb [ceil(N/128),K/128] fp32.
  * epi: CAI_EPI_BF16, CAI_EPI_F32 or CAI_EPI_BF16_RESIDUAL. No counterpart in the reference. */

@@ -54,7 +54,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // CTAs are dispatched in linear block order; walk the query tiles slowest so that the heaviest
-    // (latest) tiles of every head start first and the light ones fill the tail of the grid
+    // (latest) tiles of every head start first and the light ones fill the tail of the grid. (Pairing
+    // tile i with tile last - i balances the CTAs but was slower: a step with one live tile costs as
+    // much as a step with two.)
     const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
     const int heads_all = gridDim.y * gridDim.z;
     const int pair = gridDim.x - 1 - lin / heads_all;
@@ -181,17 +183,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
                 if (!mbar_wait(&s_full[X], j & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
                 tc_fence_after();
                 const bool diag = (j == nx - 1);
+                // the whole score row (128 fp32) comes into registers with one wait and is used for both the
+                // row maximum and the exponentials
+                uint32_t sc[4][32];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + c * 32, sc[c]);
+                tmem_ld_wait();
                 float mx = -INFINITY;
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(tS + c * 32, v);
-                    tmem_ld_wait();
+                if (!diag) {
+                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
                     for (int e = 0; e < 32; ++e) {
-                        const float s = __uint_as_float(v[e]);
-                        if (!diag || c * 32 + e <= r) mx = fmaxf(mx, s);
+                        m0 = fmaxf(m0, __uint_as_float(sc[0][e]));
+                        m1 = fmaxf(m1, __uint_as_float(sc[1][e]));
+                        m2 = fmaxf(m2, __uint_as_float(sc[2][e]));
+                        m3 = fmaxf(m3, __uint_as_float(sc[3][e]));
                     }
+                    mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int e = 0; e < 32; ++e)
+                            if (c * 32 + e <= r) mx = fmaxf(mx, __uint_as_float(sc[c][e]));
                 }
                 const float m_new = fmaxf(m_used, mx * p.scale_log2);
                 if (__any_sync(0xffffffffu, m_new > m_used + 8.f)) {
@@ -211,23 +225,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
                     }
                     m_used = m_new;
                 }
-#pragma unroll 1
+#pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(tS + c * 32, v);
-                    tmem_ld_wait();
                     uint32_t pk[16];
+                    float l0 = 0.f, l1 = 0.f;
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
-                        float p0 = fast_exp2(__uint_as_float(v[e]) * p.scale_log2 - m_used);
-                        float p1 = fast_exp2(__uint_as_float(v[e + 1]) * p.scale_log2 - m_used);
+                        float p0 = fast_exp2(fmaf(__uint_as_float(sc[c][e]), p.scale_log2, -m_used));
+                        float p1 = fast_exp2(fmaf(__uint_as_float(sc[c][e + 1]), p.scale_log2, -m_used));
                         if (diag) {
                             if (c * 32 + e > r) p0 = 0.f;
                             if (c * 32 + e + 1 > r) p1 = 0.f;
                         }
-                        l += p0 + p1;
+                        l0 += p0;
+                        l1 += p1;
                         pk[e >> 1] = pack_bf16(p0, p1);
                     }
+                    l += l0 + l1;
                     tmem_st_32x16(tS + c * 16, pk);
                 }
                 tmem_st_wait();

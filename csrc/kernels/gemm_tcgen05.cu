@@ -727,6 +727,16 @@ int cai_fused_ag_gemm(const PeerTable& pt, int group_kind, unsigned long long sr
     p.C = C; p.ldc = ldc;
     p.mode = kGemmAllGatherA;
     p.group_kind = group_kind;
+    if (n_copy <= 0) {
+        // As many copy CTAs as the GEMM leaves idle, within [16, 48]: one CTA keeps about 128 KB in flight,
+        // and it takes a few MB in flight to fill an NVLink.
+        const int sms = sm_count(current_device());
+        const int tiles = ((T + kBM - 1) / kBM) * ((N + 255) / 256);
+        n_copy = sms - tiles;
+        n_copy = n_copy < 16 ? 16 : n_copy > 48 ? 48 : n_copy;
+        const int units = T / kBM;
+        if (n_copy > units) n_copy = units;
+    }
     p.n_copy = n_copy;
     p.rows_per_rank = rows_per_rank;
     p.m_rot = pt.rank * (rows_per_rank / kBM);  // own rows first
@@ -792,4 +802,33 @@ int cai_fused_gather_gemm(const PeerTable& pt, const cai::GatherJob& job_in, con
     p.b_elem_off = b_off;
     p.ldb = ldb;
     return gemm_dispatch(A, B, lda, ldb, p, 0, st);
+}
+
+// ---- C forms of the fused GEMMs with explicit member bases (tests, micro-benchmarks, other runtimes).
+// bases[rank] is the local arena; sig_off is the arena offset of the signal block; epoch_base a device word.
+static PeerTable peer_table_of(void* const* bases, int rank, int size, unsigned long long sig_off) {
+    PeerTable pt{};
+    for (int i = 0; i < size && i < kMaxPeers; ++i) pt.base[i] = static_cast<uint8_t*>(bases[i]);
+    pt.rank = rank;
+    pt.size = size;
+    pt.sig_off = sig_off;
+    return pt;
+}
+
+CAI_API int cai_fused_ag_gemm_c(void* const* bases, int rank, int size, unsigned long long sig_off, int group_kind,
+                                unsigned long long src_off, long long ld_src, void* a_full, const void* B, void* C, int T, int N,
+                                int K, long long ldb, long long ldc, int b_mn, const uint32_t* epoch_base, uint32_t seq, int n_copy,
+                                void* stream) {
+    if (size < 1 || size > kMaxPeers || T % size) return CAI_K_BAD_ARG;
+    return cai_fused_ag_gemm(peer_table_of(bases, rank, size, sig_off), group_kind, src_off, ld_src, a_full, B, C, T, N, K, ldb, ldc,
+                             b_mn, T / size, epoch_base, seq, n_copy, static_cast<cudaStream_t>(stream));
+}
+
+CAI_API int cai_fused_gemm_rs_c(void* const* bases, int rank, int size, unsigned long long sig_off, int group_kind, const void* A,
+                                const void* B, unsigned long long stage_off, void* out_local, const void* residual, int T, int N,
+                                int K, long long lda, long long ldb, long long ldo, long long ldr, int b_mn,
+                                const uint32_t* epoch_base, uint32_t seq, void* stream) {
+    if (size < 1 || size > kMaxPeers || T % size) return CAI_K_BAD_ARG;
+    return cai_fused_gemm_rs(peer_table_of(bases, rank, size, sig_off), group_kind, A, B, stage_off, out_local, residual, T, N, K, lda,
+                             ldb, ldo, ldr, b_mn, T / size, epoch_base, seq, static_cast<cudaStream_t>(stream));
 }

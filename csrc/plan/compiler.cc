@@ -50,7 +50,7 @@ const Key kKeys[] = {
     XKEY("lr", lr, F_F32), XKEY("adam_beta1", beta1, F_F32), XKEY("adam_beta2", beta2, F_F32),
     XKEY("adam_eps", adam_eps, F_F32), XKEY("weight_decay", weight_decay, F_F32),
     XKEY("rope_theta", rope_theta, F_F32), XKEY("norm_eps", norm_eps, F_F32), XKEY("init_std", init_std, F_F32),
-    XKEY("seed", seed, F_U32), XKEY("tie_embeddings", tie_embeddings, F_U32), XKEY("zero_stage", zero_stage, F_U32),
+    XKEY("seed", seed, F_U32), XKEY("tie_embeddings", tie_embeddings, F_U32), XKEY("zero_stage", zero_stage, F_U32), XKEY("wgrad_overlap", wgrad_overlap, F_U32),
     XKEY("fp8_block", fp8_block, F_U32), XKEY("comm", comm_mode, F_COMM), XKEY("ce_chunk", ce_chunk, F_U32),
     XKEY("moe_capacity_factor", moe_capacity_factor_x100, F_F32),
 };

@@ -590,6 +590,11 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     const int dstream = b.tensor(TC_WORKSPACE, DT_BF16, Tl, H);     // gradient of the residual stream
     const int dxn = b.tensor(TC_WORKSPACE, DT_BF16, Tl, H);         // gradient of a norm output (local rows)
     const int dfull = tp > 1 ? b.tensor(TC_WORKSPACE, DT_BF16, T, H) : -1;  // gathered gradient rows
+    // With tensor parallelism the kernels of the backward's critical path are small or wait on peers, so the
+    // weight-gradient GEMMs (nothing downstream in the layer needs them) go to compute_lo and fill idle SMs,
+    // most of all under the attention backward. The attention half of a layer then gathers into its own buffer.
+    const bool overlap_wgrad = tp > 1 && !moe && cfg.train.wgrad_overlap != 0;
+    const int dfull_attn = overlap_wgrad ? b.tensor(TC_WORKSPACE, DT_BF16, T, H) : dfull;
     const int dqkv = b.tensor(TC_WORKSPACE, DT_BF16, T, b.Cqkv);
     const int dao = b.tensor(TC_WORKSPACE, DT_BF16, T, b.Hq_l);
     const int dgu = b.tensor(TC_WORKSPACE, DT_BF16, T, 2 * b.F_l);
@@ -822,6 +827,22 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         const uint32_t s = mb % slots;
         const bool first_mb = mb == 0;                 // first gradient contribution overwrites
         const int wg_epi = first_mb ? 1 : 2;           // CAI_EPI_F32 / CAI_EPI_F32_ACCUM
+        bool lo_pending = false;
+        // G[M,N] (+)= A[K,M]^T * B[K,N]: a weight gradient; its operands are complete on compute_hi
+        auto wgrad = [&](int A, int B, int G, uint32_t M, uint32_t N, uint32_t K) {
+            if (!overlap_wgrad) {
+                b.gemm(ST_COMPUTE_HI, A, B, G, -1, M, N, K, true, true, wg_epi, mb);
+                return;
+            }
+            b.sync(ST_COMPUTE_HI, ST_COMPUTE_LO, mb);
+            b.gemm(ST_COMPUTE_LO, A, B, G, -1, M, N, K, true, true, wg_epi, mb);
+            lo_pending = true;
+        };
+        // compute_hi may overwrite what the deferred weight gradients read only after they have run
+        auto join_lo = [&]() {
+            if (lo_pending) b.sync(ST_COMPUTE_LO, ST_COMPUTE_HI, mb);
+            lo_pending = false;
+        };
         const int tok_mb = b.view(tokens, mb, 1);
         if (b.last_stage) {
             // LM head + cross-entropy, `chunk` rows at a time: logits -> dlogits in place ->
@@ -868,6 +889,8 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             const LayerActs& a = A[s][l];
             const LayerParams& w = L[l];
             const int g_rows = tp > 1 ? dfull : dstream;  // all T rows of the incoming gradient
+            const int g_rows_attn = tp > 1 ? dfull_attn : dstream;
+            join_lo();
             if (recompute) layer_forward(mb, a, w, x_scratch);
             if (moe) {
                 const uint32_t F = m.ffn_hidden, seg_m = d.ep * moe_cap;
@@ -907,20 +930,20 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             // ---- MLP block: x_next = hmid + act * Wd^T
             prepare_layer(l, true, mb);                                                           // ZeRO-3 re-gather, top of the range first
             b.col_parallel(dstream, dfull, w.wd.w, dact, b.F_l, H, true, mb);                     // dact = gather(dx) * Wd
-            b.gemm(ST_COMPUTE_HI, g_rows, a.act, w.wd.g, -1, H, b.F_l, T, true, true, wg_epi, mb);  // dWd = dx^T act
+            wgrad(g_rows, a.act, w.wd.g, H, b.F_l, T);                                            // dWd = dx^T act
             {
                 ExecOp e = xop(K_SWIGLU_BWD);
                 e.t[0] = a.gu; e.t[1] = dact; e.t[2] = dgu;
                 e.i[0] = T; e.i[1] = b.F_l;
                 b.push(OP_SWIGLU, ST_COMPUTE_HI, 8.0 * T * b.F_l, 0, 0, mb, &e);
             }
+            wgrad(dgu, a.xn2, w.wgu.g, 2 * b.F_l, H, T);
             b.row_parallel(dgu, w.wgu.w, -1, dxn, partial, rs_tmp, H, 2 * b.F_l, true, mb);        // dxn2 = RS(dgu * Wgu)
-            b.gemm(ST_COMPUTE_HI, dgu, a.xn2, w.wgu.g, -1, 2 * b.F_l, H, T, true, true, wg_epi, mb);
             b.rmsnorm_bwd(a.hmid, w.g2.w, a.rstd2, dxn, dstream, w.g2.g, norm_scratch, Tl, true, !first_mb, mb);
             }
             // ---- attention block: hmid = x + ao * Wo^T
-            b.col_parallel(dstream, dfull, w.wo.w, dao, b.Hq_l, H, true, mb);                     // dao = gather(dh) * Wo
-            b.gemm(ST_COMPUTE_HI, g_rows, a.ao, w.wo.g, -1, H, b.Hq_l, T, true, true, wg_epi, mb);
+            b.col_parallel(dstream, dfull_attn, w.wo.w, dao, b.Hq_l, H, true, mb);                // dao = gather(dh) * Wo
+            wgrad(g_rows_attn, a.ao, w.wo.g, H, b.Hq_l, T);
             {
                 ExecOp e = xop(K_ATTN_BWD);
                 e.t[0] = a.qkv; e.t[1] = a.ao; e.t[2] = dao; e.t[3] = a.lse; e.t[4] = delta; e.t[5] = dqkv;
@@ -934,10 +957,11 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
                 e.i[0] = T; e.i[1] = b.seq; e.i[2] = b.nh_l; e.i[3] = b.nkv_l; e.i[4] = b.hd;
                 b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 6.0 * T * (b.nh_l + b.nkv_l) * b.hd, 0, 0, mb, &e);
             }
+            wgrad(dqkv, a.xn1, w.wqkv.g, b.Cqkv, H, T);
             b.row_parallel(dqkv, w.wqkv.w, -1, dxn, partial, rs_tmp, H, b.Cqkv, true, mb);
-            b.gemm(ST_COMPUTE_HI, dqkv, a.xn1, w.wqkv.g, -1, b.Cqkv, H, T, true, true, wg_epi, mb);
             b.rmsnorm_bwd(a.x, w.g1.w, a.rstd1, dxn, dstream, w.g1.g, norm_scratch, Tl, true, !first_mb, mb);
         }
+        join_lo();
         if (b.first_stage) {
             int drows = dstream;
             if (tp > 1) {

@@ -165,7 +165,7 @@ struct TrainSpec {
     uint32_t comm_mode = 1;       // 0 = NCCL-only baseline ops, 1 = fused compute+collective kernels
     uint32_t ce_chunk = 1024;     // rows of logits materialised at a time
     uint32_t moe_capacity_factor_x100 = 200;
-    uint32_t reserved = 0;
+    uint32_t wgrad_overlap = 1;   // tp > 1: weight-gradient GEMMs run on compute_lo next to the backward's critical path
 };
 static_assert(sizeof(TrainSpec) == 64, "TrainSpec layout");
 

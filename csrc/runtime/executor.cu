@@ -151,7 +151,7 @@ struct cai_exec {
     bool has_peers[GROUP_COUNT] = {};
     unsigned int* counters_dev = nullptr;  // scratch words for grid-completion tickets
     uint32_t epochs_per_step = 2;
-    int ag_copy_ctas = 16;
+    int ag_copy_ctas = 0;   // 0: chosen per launch from the GEMM's tile count
     float* hyper_dev = nullptr;   // 8 floats
     float* hyper_host = nullptr;  // pinned
     cudaGraphExec_t graph = nullptr;
@@ -295,7 +295,7 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
             job.reverse = (x.flags >> 1) & 1;
             job.group_kind = GROUP_DP;
             if (x.flags & 1) {
-                job.n_copy = x.i[2] > 0 ? x.i[2] : ex->ag_copy_ctas;
+                job.n_copy = x.i[2] > 0 ? x.i[2] : (ex->ag_copy_ctas > 0 ? ex->ag_copy_ctas : 16);
                 ex->pending_gather = job;
                 ex->pending_seq = static_cast<uint32_t>(x.i[4]);
                 ex->has_pending_gather = true;   // launched together with the next GEMM
@@ -363,7 +363,7 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
                 const int T = x.i[0], N = x.i[1], K = x.i[2];
                 return cai_fused_ag_gemm(pt, group, ex->tensors[x.t[0]].offset, ex->ld(x.t[0]), P(3), P(1), P(2), T, N, K,
                                          ex->ld(x.t[1]), ex->ld(x.t[2]), (x.flags >> 1) & 1, T / pt.size, epoch_base, seq,
-                                         ex->ag_copy_ctas < 4 * pt.size ? ex->ag_copy_ctas : 4 * pt.size, st);
+                                         ex->ag_copy_ctas, st);
             }
             if (x.kernel == K_GEMM_RS) {
                 const int T = x.i[0], N = x.i[1], K = x.i[2];
