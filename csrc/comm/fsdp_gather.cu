@@ -53,3 +53,38 @@ int cai_fsdp_gather(const PeerTable& pt, GatherJob job, const uint32_t* epoch_ba
     fsdp_gather_kernel<<<job.n_copy, 32, smem_bytes, st>>>(pt, job, epoch_base, seq, status_words(dev));
     return cudaGetLastError() == cudaSuccess ? 0 : CAI_K_CUDA;
 }
+
+// C forms with explicit member bases (tests, micro-benchmarks): the stand-alone gather and the GEMM whose copy
+// CTAs gather the range that holds its B operand (B = dst + b_elem_off).
+static PeerTable fsdp_table_of(void* const* bases, int rank, int size, unsigned long long sig_off) {
+    PeerTable pt{};
+    for (int i = 0; i < size && i < kMaxPeers; ++i) pt.base[i] = static_cast<uint8_t*>(bases[i]);
+    pt.rank = rank;
+    pt.size = size;
+    pt.sig_off = sig_off;
+    return pt;
+}
+static GatherJob fsdp_job_of(unsigned long long shard_off, long long n_shard, long long lo, long long hi, void* dst, int reverse,
+                             int n_copy) {
+    GatherJob job{};
+    job.shard_off = shard_off; job.n_shard = n_shard; job.lo = lo; job.hi = hi;
+    job.dst = static_cast<__nv_bfloat16*>(dst);
+    job.reverse = reverse; job.n_copy = n_copy; job.group_kind = GROUP_DP;
+    return job;
+}
+extern "C" __attribute__((visibility("default"))) int cai_fsdp_gather_c(
+    void* const* bases, int rank, int size, unsigned long long sig_off, unsigned long long shard_off, long long n_shard,
+    long long lo, long long hi, void* dst, int reverse, int n_copy, const unsigned int* epoch_base, unsigned int seq, void* stream) {
+    if (size < 1 || size > kMaxPeers) return CAI_K_BAD_ARG;
+    return cai_fsdp_gather(fsdp_table_of(bases, rank, size, sig_off), fsdp_job_of(shard_off, n_shard, lo, hi, dst, reverse, n_copy),
+                           epoch_base, seq, static_cast<cudaStream_t>(stream));
+}
+extern "C" __attribute__((visibility("default"))) int cai_fused_gather_gemm_c(
+    void* const* bases, int rank, int size, unsigned long long sig_off, unsigned long long shard_off, long long n_shard,
+    long long lo, long long hi, void* dst, int reverse, int n_copy, const void* A, long long b_elem_off, void* C, int M, int N,
+    int K, long long lda, long long ldb, long long ldc, int b_mn, const unsigned int* epoch_base, unsigned int seq, void* stream) {
+    if (size < 1 || size > kMaxPeers) return CAI_K_BAD_ARG;
+    const GatherJob job = fsdp_job_of(shard_off, n_shard, lo, hi, dst, reverse, n_copy);
+    return cai_fused_gather_gemm(fsdp_table_of(bases, rank, size, sig_off), job, A, job.dst + b_elem_off, C, nullptr, M, N, K, lda,
+                                 ldb, ldc, 0, 0, b_mn, CAI_EPI_BF16, 1.0f, epoch_base, seq, static_cast<cudaStream_t>(stream));
+}

@@ -132,3 +132,19 @@ int cai_fused_rs_adamw(const PeerTable& pt, unsigned long long grad_off, unsigne
     }
     return 0;
 }
+
+// C form with explicit member bases (tests, micro-benchmarks). hyper: 8 device floats (lr, beta1, beta2, eps,
+// weight decay, bias corrections 1 and 2, and the epoch base as uint32 bits); scratch: a zeroed device uint32.
+extern "C" __attribute__((visibility("default"))) int cai_fused_rs_adamw_c(
+    void* const* bases, int rank, int size, unsigned long long sig_off, unsigned long long grad_off, unsigned long long param_off,
+    float* master, float* m, float* v, long long n_flat, long long n_shard, const float* hyper, float gscale, unsigned int seq,
+    unsigned int* scratch, int local_params, void* stream) {
+    if (size < 1 || size > kMaxPeers) return CAI_K_BAD_ARG;
+    PeerTable pt{};
+    for (int i = 0; i < size; ++i) pt.base[i] = static_cast<uint8_t*>(bases[i]);
+    pt.rank = rank;
+    pt.size = size;
+    pt.sig_off = sig_off;
+    return cai_fused_rs_adamw(pt, grad_off, param_off, master, m, v, n_flat, n_shard, hyper, gscale, seq, scratch, local_params,
+                              static_cast<cudaStream_t>(stream));
+}

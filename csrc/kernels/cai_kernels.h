@@ -147,5 +147,9 @@ CAI_API int cai_flash_attn_fwd(const void* qkv, void* out, float* lse, int B, in
 /* dqkv packed like qkv. delta is scratch f32 [B, nh, S]. */
 CAI_API int cai_flash_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
                                void* dqkv, int B, int S, int nh, int nkv, int hd, float scale, void* stream);
+/* The same in separately launchable parts (bit 0: delta = rowsum(dO * O), bit 1: dK / dV, bit 2: dQ; the last two
+ * both need delta and write disjoint columns of dqkv, so they may run on different streams). */
+CAI_API int cai_flash_attn_bwd_parts(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
+                                     void* dqkv, int B, int S, int nh, int nkv, int hd, float scale, int parts, void* stream);
 
 #endif /* CAI_KERNELS_H */

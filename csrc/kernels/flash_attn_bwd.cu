@@ -424,6 +424,11 @@ using namespace cai;
 
 CAI_API int cai_flash_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
                                void* dqkv, int B, int S, int nh, int nkv, int hd, float scale, void* stream) {
+    return cai_flash_attn_bwd_parts(qkv, out, dout, lse, delta, dqkv, B, S, nh, nkv, hd, scale, 7, stream);
+}
+
+CAI_API int cai_flash_attn_bwd_parts(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
+                                     void* dqkv, int B, int S, int nh, int nkv, int hd, float scale, int parts, void* stream) {
     if (hd != kAttnHD || S % kAttnTile || nkv <= 0 || nh % nkv) {
         set_last_error("flash_attn_bwd: needs head_dim 128, seq %% 128 == 0, heads %% kv_heads == 0");
         return CAI_K_BAD_ARG;
@@ -447,7 +452,8 @@ CAI_API int cai_flash_attn_bwd(const void* qkv, const void* out, const void* dou
         configured[dev & 63] = true;
     }
     const long long warps = static_cast<long long>(B) * S * nh;
-    attn_delta_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, st>>>(
+    if (parts & 1)
+        attn_delta_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, st>>>(
         static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(dout), delta, B, S, nh);
     AttnBwdParams p;
     p.B = B; p.S = S; p.nh = nh; p.nkv = nkv;
@@ -458,8 +464,8 @@ CAI_API int cai_flash_attn_bwd(const void* qkv, const void* out, const void* dou
     p.dqkv = static_cast<__nv_bfloat16*>(dqkv);
     p.status = status_words(dev);
     const int nq = S / kAttnTile;
-    attn_dkdv_kernel<<<dim3(nq, nkv, B), kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_do, p);
-    attn_dq_kernel<<<dim3(nq, nh, B), kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_do, p);
+    if (parts & 2) attn_dkdv_kernel<<<dim3(nq, nkv, B), kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_do, p);
+    if (parts & 4) attn_dq_kernel<<<dim3(nq, nh, B), kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_do, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         set_last_error("attn_bwd launch failed: %s", cudaGetErrorString(e));

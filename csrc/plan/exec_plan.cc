@@ -115,6 +115,15 @@ struct Builder {
         return tensor_at(pt.tclass, pt.dtype, pt.offset + static_cast<uint64_t>(row0) * ld * dtype_size(pt.dtype), rows,
                          cols, ld);
     }
+    // columns [col0, col0+cols) of every row of an existing tensor
+    int colview(int parent, uint32_t col0, uint32_t cols) {
+        const TensorDesc& pt = p->tensors[parent];
+        const uint32_t rows = p->shapes[parent * 4], ld = p->shapes[parent * 4 + 2];
+        const uint64_t es = dtype_size(pt.dtype);
+        const int id = tensor_at(pt.tclass, pt.dtype, pt.offset + col0 * es, rows, cols, ld);
+        p->tensors[id].nbytes = (static_cast<uint64_t>(rows - 1) * ld + cols) * es;
+        return id;
+    }
     uint32_t rows_of(int t) const { return p->shapes[t * 4]; }
     uint32_t cols_of(int t) const { return p->shapes[t * 4 + 1]; }
 
@@ -307,7 +316,12 @@ void exec_operands(const ExecOp& x, std::vector<int>* reads, std::vector<int>* w
         }
         case K_ROPE: R(0); R(1); W(0); break;
         case K_ATTN_FWD: R(0); W(1); W(2); break;
-        case K_ATTN_BWD: R(0); R(1); R(2); R(3); W(4); W(5); break;
+        case K_ATTN_BWD:
+            R(0); R(1); R(2); R(3);
+            if (x.flags == 0 || (x.flags & 1)) W(4); else R(4);
+            if (x.flags == 0) W(5);
+            else if (x.flags & 6) W(6);
+            break;
         case K_SWIGLU_FWD: R(0); W(1); break;
         case K_SWIGLU_BWD: R(0); R(1); W(2); break;
         case K_CROSS_ENTROPY: case K_CROSS_ENTROPY_TP: R(0); R(1); R(2); W(0); W(2); W(3); break;
@@ -945,11 +959,28 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             b.col_parallel(dstream, dfull_attn, w.wo.w, dao, b.Hq_l, H, true, mb);                // dao = gather(dh) * Wo
             wgrad(g_rows_attn, a.ao, w.wo.g, H, b.Hq_l, T);
             {
-                ExecOp e = xop(K_ATTN_BWD);
-                e.t[0] = a.qkv; e.t[1] = a.ao; e.t[2] = dao; e.t[3] = a.lse; e.t[4] = delta; e.t[5] = dqkv;
-                e.i[0] = b.mbsz; e.i[1] = b.seq; e.i[2] = b.nh_l; e.i[3] = b.nkv_l; e.i[4] = b.hd;
-                e.f[0] = 1.0f / std::sqrt(static_cast<float>(b.hd));
-                b.push(OP_ATTENTION_BWD, ST_COMPUTE_HI, 4.0 * T * b.Hq_l * b.seq, 0, 0, mb, &e);
+                auto attn_bwd = [&](uint16_t parts, uint16_t stream, double flops) {
+                    ExecOp e = xop(K_ATTN_BWD, parts);
+                    e.t[0] = a.qkv; e.t[1] = a.ao; e.t[2] = dao; e.t[3] = a.lse; e.t[4] = delta; e.t[5] = dqkv;
+                    // a part writes only its own columns of dqkv: t[6] names them for the hazard analysis
+                    if (parts == 4) e.t[6] = b.colview(dqkv, 0, b.Hq_l);
+                    if (parts == 2) e.t[6] = b.colview(dqkv, b.Hq_l, b.Cqkv - b.Hq_l);
+                    e.i[0] = b.mbsz; e.i[1] = b.seq; e.i[2] = b.nh_l; e.i[3] = b.nkv_l; e.i[4] = b.hd;
+                    e.f[0] = 1.0f / std::sqrt(static_cast<float>(b.hd));
+                    b.push(OP_ATTENTION_BWD, stream, flops, 0, 0, mb, &e);
+                };
+                const double flops = 4.0 * T * b.Hq_l * b.seq;
+                if (!overlap_wgrad) {
+                    attn_bwd(0, ST_COMPUTE_HI, flops);
+                } else {
+                    // few heads per GPU leave most SMs idle: dQ (on comm_dp's stream, idle during backward) runs
+                    // next to dK/dV; both need delta and write disjoint columns of dqkv
+                    attn_bwd(1, ST_COMPUTE_HI, 0);
+                    b.sync(ST_COMPUTE_HI, ST_COMM_DP, mb);
+                    attn_bwd(4, ST_COMM_DP, 0.4 * flops);
+                    attn_bwd(2, ST_COMPUTE_HI, 0.6 * flops);
+                    b.sync(ST_COMM_DP, ST_COMPUTE_HI, mb);
+                }
             }
             {
                 ExecOp e = xop(K_ROPE, 1);

@@ -111,6 +111,20 @@ void verify_event_order(const Plan& p, VerifyReport* rep) {
     if (!bad) add(rep, true, "rank %u: every wait follows its record (%u events)", p.hdr.global_rank, p.hdr.num_events);
 }
 
+// Two strided views of the same row grid (equal row pitch) that cover disjoint column intervals share
+// no byte although their byte ranges interleave (e.g. the Q columns and the K/V columns of a [T, q|k|v] buffer).
+static bool disjoint_columns(const Plan& p, uint32_t a, uint32_t b) {
+    if (p.shapes.size() < (static_cast<size_t>(std::max(a, b)) + 1) * 4) return false;
+    const TensorDesc& ta = p.tensors[a];
+    const TensorDesc& tb = p.tensors[b];
+    const uint64_t ea = dtype_size(ta.dtype), eb = dtype_size(tb.dtype);
+    const uint64_t pitch_a = p.shapes[a * 4 + 2] * ea, pitch_b = p.shapes[b * 4 + 2] * eb;
+    const uint64_t wa = p.shapes[a * 4 + 1] * ea, wb = p.shapes[b * 4 + 1] * eb;
+    if (!pitch_a || pitch_a != pitch_b || wa >= pitch_a || wb >= pitch_b) return false;
+    const uint64_t d = (tb.offset % pitch_a + pitch_a - ta.offset % pitch_a) % pitch_a;  // start of b relative to a, inside a row
+    return d >= wa && d + wb <= pitch_a;
+}
+
 void verify_hazards(const Plan& p, VerifyReport* rep) {
     if (p.hdr.version < 2 || p.exec.empty()) {
         add(rep, true, "rank %u: cost-only plan, no operands to check", p.hdr.global_rank);
@@ -129,6 +143,7 @@ void verify_hazards(const Plan& p, VerifyReport* rep) {
             const TensorDesc& tb = p.tensors[order[b]];
             if (tb.offset >= ta.offset + ta.nbytes) break;
             if (!tb.nbytes) continue;
+            if (disjoint_columns(p, order[a], order[b])) continue;
             overlaps[order[a]].push_back(order[b]);
             overlaps[order[b]].push_back(order[a]);
         }

@@ -208,8 +208,9 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
         case K_ATTN_FWD:
             return cai_flash_attn_fwd(P(0), P(1), (float*)P(2), x.i[0], x.i[1], x.i[2], x.i[3], x.i[4], x.f[0], st);
         case K_ATTN_BWD:
-            return cai_flash_attn_bwd(P(0), P(1), P(2), (const float*)P(3), (float*)P(4), P(5), x.i[0], x.i[1], x.i[2],
-                                      x.i[3], x.i[4], x.f[0], st);
+            // flags: 0 = the whole backward, otherwise a mask of its parts (1 delta, 2 dK/dV, 4 dQ)
+            return cai_flash_attn_bwd_parts(P(0), P(1), P(2), (const float*)P(3), (float*)P(4), P(5), x.i[0], x.i[1], x.i[2],
+                                            x.i[3], x.i[4], x.f[0], x.flags ? x.flags : 7, st);
         case K_SWIGLU_FWD: return cai_swiglu_fwd(P(0), P(1), x.i[0], x.i[1], st);
         case K_SWIGLU_BWD: return cai_swiglu_bwd(P(0), P(1), P(2), x.i[0], x.i[1], st);
         case K_CROSS_ENTROPY:
@@ -416,7 +417,7 @@ int replay(cai_exec* ex) {
         {
             // kernels of this library behind the op (memsets and NCCL calls are not ours)
             const uint16_t k = ex->exec[op.exec - 1].kernel;
-            ex->launches += (k == K_ATTN_BWD || k == K_CROSS_ENTROPY_TP || k == K_RMSNORM_BWD) ? 3 : (k == K_ZERO || (k >= K_NCCL_ALL_REDUCE && k <= K_NCCL_RECV) || (k == K_FSDP_AG_GEMM && (ex->exec[op.exec - 1].flags & 1))) ? 0 : 1;
+            ex->launches += (k == K_ATTN_BWD && ex->exec[op.exec - 1].flags) ? __builtin_popcount(ex->exec[op.exec - 1].flags) : (k == K_ATTN_BWD || k == K_CROSS_ENTROPY_TP || k == K_RMSNORM_BWD) ? 3 : (k == K_ZERO || (k >= K_NCCL_ALL_REDUCE && k <= K_NCCL_RECV) || (k == K_FSDP_AG_GEMM && (ex->exec[op.exec - 1].flags & 1))) ? 0 : 1;
         }
         if (tr) cudaEventRecord(tr->stop, st);
     }
