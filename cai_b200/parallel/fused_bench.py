@@ -231,7 +231,7 @@ def main(argv=None):
         dist.barrier()
 
         def fused():
-            klib.check(L.cai_fused_gather_gemm_c(pb.bases, rank, world, 0, s_off, ns, 0, n, stage.data_ptr(), 0, max(a.copy_ctas, 16),
+            klib.check(L.cai_fused_gather_gemm_c(pb.bases, rank, world, 0, s_off, ns, 0, n, stage.data_ptr(), 0, a.copy_ctas or 24,
                                                  X.data_ptr(), 0, C.data_ptr(), T, N, K, K, K, N, 0, pb.epoch.data_ptr(),
                                                  pb.next_seq(), st), "gather_gemm")
 

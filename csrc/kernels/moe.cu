@@ -205,16 +205,24 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const PeerTable pt, c
         uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(pt.base[dst] + p.slab_off) +
                                               (static_cast<long long>(el * pt.size + pt.rank) * p.cap + ps) * p.H);
         const float sc = p.scale ? p.scale[i] : 1.f;
-        for (int c = lane; c < hv; c += 32) {
-            uint4 v = src[c];
-            if (p.scale) {
-                float f[8];
-                unpack8(v, f);
+        // four independent 16-byte loads in flight per lane before the first store
+        for (int c0 = lane; c0 < hv; c0 += 128) {
+            uint4 v[4];
 #pragma unroll
-                for (int q = 0; q < 8; ++q) f[q] *= sc;
-                v = pack8(f);
+            for (int u = 0; u < 4; ++u)
+                if (c0 + 32 * u < hv) v[u] = src[c0 + 32 * u];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (c0 + 32 * u >= hv) break;
+                if (p.scale) {
+                    float f[8];
+                    unpack8(v[u], f);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) f[q] *= sc;
+                    v[u] = pack8(f);
+                }
+                out[c0 + 32 * u] = v[u];
             }
-            out[c] = v;
         }
     }
     // (3) handshake by the last CTA: everything this member sends has been issued and fenced; when

@@ -296,7 +296,7 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
             job.reverse = (x.flags >> 1) & 1;
             job.group_kind = GROUP_DP;
             if (x.flags & 1) {
-                job.n_copy = x.i[2] > 0 ? x.i[2] : (ex->ag_copy_ctas > 0 ? ex->ag_copy_ctas : 16);
+                job.n_copy = x.i[2] > 0 ? x.i[2] : (ex->ag_copy_ctas > 0 ? ex->ag_copy_ctas : 24);
                 ex->pending_gather = job;
                 ex->pending_seq = static_cast<uint32_t>(x.i[4]);
                 ex->has_pending_gather = true;   // launched together with the next GEMM

@@ -156,3 +156,48 @@ def test_executable_plan_structure(tmp_path):
         base_w, base_g = p.tensors[names["@flat_param"].tensor].offset, p.tensors[names["@flat_grad"].tensor].offset
         assert (w.offset - base_w) // 2 == (g.offset - base_g) // 4 == nt.flat_off512 * 512
     assert all(t.offset + t.nbytes <= p.hdr.arena_bytes for t in p.tensors)
+
+
+def _variant(tmp_path, name, extra, world=1):
+    """tiny_mp.cfg on `world` GPUs with extra keys: compile every rank, run the whole-cluster verifier
+    (tiling, event order, arena hazards, pipeline pairing) and return rank 0's plan."""
+    from cai_b200 import plan
+    text = (ROOT / "configs" / "tiny_mp.cfg").read_text()
+    text += f"\ngpus_per_rack = {world}\ngpus_per_tray = {world}\n" + extra
+    cfg = tmp_path / f"{name}.cfg"
+    cfg.write_text(text)
+    plan.compile_plans(cfg, tmp_path / name, version=2)
+    problems, report = plan.verify(cfg)
+    assert problems == 0, report[-2000:]
+    return plan.PlanFile(tmp_path / name / "plan.rank000000.bin")
+
+
+def test_plan_variants_compile_and_verify(tmp_path):
+    from cai_b200 import plan
+    kernels = lambda p: {int(x.kernel) for x in p.exec}
+    base = _variant(tmp_path, "base", "")
+    # activation recompute: more ops (each layer's forward runs twice), smaller arena
+    rc = _variant(tmp_path, "recompute", "recompute = 1\n")
+    assert len(rc.exec) > len(base.exec) and rc.hdr.arena_bytes < base.hdr.arena_bytes
+    # fp8 linear layers: quantisers and the block-scaled GEMM appear, the bf16 GEMM stays for weight gradients
+    f8 = _variant(tmp_path, "fp8", "param_dtype = fp8e4m3\n")
+    assert {plan.K_QUANT_FP8, plan.K_GEMM_FP8, plan.K_GEMM} <= kernels(f8)
+    # ZeRO-3 over two GPUs: the parameter class holds a shard plus staging buffers, gathers precede the GEMMs
+    z1 = _variant(tmp_path, "zero1", "comm = fused\n", world=2)
+    z3 = _variant(tmp_path, "zero3", "comm = fused\nzero_stage = 3\n", world=2)
+    assert plan.K_FSDP_AG_GEMM in kernels(z3) and plan.K_FSDP_AG_GEMM not in kernels(z1)
+    n1, n3 = z1.named_dict(), z3.named_dict()
+    assert z3.tensors[n3["@flat_param"].tensor].nbytes * 2 <= z1.tensors[n1["@flat_param"].tensor].nbytes + 2048
+    fused = [i for i, x in enumerate(z3.exec) if int(x.kernel) == plan.K_FSDP_AG_GEMM and (x.flags & 1)]
+    assert fused and all(int(z3.exec[i + 1].kernel) == plan.K_GEMM for i in fused)   # merged into the GEMM that follows
+    # tensor parallel: weight gradients leave the critical path (compute_lo), dQ runs beside dK/dV
+    tp = _variant(tmp_path, "tp2", "tp = 2\ncomm = fused\n", world=2)
+    lo_gemms = [op for op in tp.ops if op.exec and int(tp.exec[op.exec - 1].kernel) == plan.K_GEMM and op.stream_id == 1]
+    assert len(lo_gemms) >= 4 * 4 * 4   # 4 layers x 4 microbatches x 4 weight gradients
+    off = _variant(tmp_path, "tp2_serial", "tp = 2\ncomm = fused\nwgrad_overlap = 0\n", world=2)
+    assert not [op for op in off.ops if op.exec and int(off.exec[op.exec - 1].kernel) == plan.K_GEMM and op.stream_id == 1]
+    # refused combinations
+    for bad in ("zero_stage = 3\ncomm = baseline\n", "zero_stage = 3\ncomm = fused\ntp = 2\n"):
+        with pytest.raises(plan.PlanError):   # 4 GPUs: dp = 4, or tp = 2 x dp = 2
+            plan.compile_plans((ROOT / "configs" / "tiny_mp.cfg").read_text() + "\ngpus_per_rack = 4\ngpus_per_tray = 4\n" + bad,
+                               tmp_path / "bad", version=2, text=True)
