@@ -119,6 +119,19 @@ def build_host(verbose=False) -> Path:
     return lib
 
 
+def build_sanitized_selftest(verbose=False) -> Path:
+    """The GPU-free C++ code (plan compiler, verifier, analytic runtime, oracle) and its self-test compiled as
+    one executable under AddressSanitizer + UndefinedBehaviorSanitizer."""
+    out = BUILD / "asan" / "cai_selftest_asan"
+    out.parent.mkdir(parents=True, exist_ok=True)
+    srcs = host_lib_sources() + [CSRC / "tools" / "cai_selftest.cc"]
+    headers = list((CSRC / "plan").glob("*.h")) + list((CSRC / "ref").glob("*.h"))
+    if _newer(out, srcs + headers):
+        _run([CXX, "-std=c++17", "-O1", "-g", "-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-fno-sanitize-recover=undefined",
+              "-I", CSRC, "-I", CSRC / "plan"] + srcs + ["-o", out, "-lm", "-lpthread"], verbose)
+    return out
+
+
 def build_all(verbose=False):
     host = build_host(verbose)
     kern = build_kernels(verbose)

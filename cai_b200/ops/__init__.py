@@ -66,6 +66,19 @@ def gemm(a, b, *, trans_a=False, trans_b=False, out=None, out_dtype=torch.bfloat
     return out
 
 
+def gemm_grouped(a, b, out, M, N, K, *, groups, trans_a=False, trans_b=False, accumulate=False, seg_counts=None, seg_rows=0,
+                 seg_mode=0):
+    """``groups`` products ``C_g[M,N] = op(A_g) @ op(B_g)^T`` in one launch; ``a``, ``b``, ``out`` hold the groups stacked
+    along their row dimension (rows of ``[M,K]`` / ``[N,K]``, or of ``[K,M]`` / ``[K,N]`` when transposed)."""
+    epi = (EPI_F32_ACCUM if accumulate else EPI_F32) if out.dtype == torch.float32 else EPI_BF16
+    ga, gb = (K if trans_a else M), (K if trans_b else N)
+    grp_seg = ((K if seg_mode == 2 else M) // seg_rows) if seg_mode else 0
+    check(lib().cai_gemm_bf16_grouped(_p(a), _p(b), _p(out), M, N, K, a.stride(0), b.stride(0), out.stride(0), int(trans_a),
+                                      int(trans_b), epi, _p(seg_counts), int(seg_rows), int(seg_mode), groups, ga, gb, M, grp_seg,
+                                      _stream()), "gemm_grouped")
+    return out
+
+
 def moe_route_fwd(logits, k, cap):
     """Softmax top-k router. logits f32 ``[T,E]``. Returns ``idx`` int32 ``[T,k]``, ``w`` f32 ``[T,k]``
     (renormalised over the chosen k), ``pos`` int32 ``[T,k]`` (slot in the expert's slab, -1 when

@@ -40,6 +40,8 @@ def _declare(L):
         L.cai_gemm_fp8_blockscaled.argtypes = [P, P, P, P, P, P, I, I, I, LL, LL, LL, LL, I, P]
         L.cai_quant_rows_1x128.argtypes = [P, LL, P, LL, P, I, I, P]
         L.cai_quant_blocks_128x128.argtypes = [P, LL, P, LL, P, LL, P, P, I, I, P]
+    if hasattr(L, "cai_gemm_bf16_grouped"):
+        L.cai_gemm_bf16_grouped.argtypes = [P, P, P, I, I, I, LL, LL, LL, I, I, I, P, I, I, I, LL, LL, LL, I, P]
     L.cai_moe_route_fwd.argtypes = [P, P, P, P, P, I, I, I, I, P]
     L.cai_moe_route_bwd.argtypes = [P, P, P, P, P, I, I, I, P]
     ULL = ctypes.c_ulonglong

@@ -49,6 +49,7 @@ def _declare_runtime(L):
     L.cai_exec_sync.argtypes = [P]
     L.cai_exec_use_graph.argtypes = [P, I]
     L.cai_exec_trace_enable.argtypes = [P, I]
+    L.cai_exec_nvtx_enable.argtypes = [P, I]
     L.cai_exec_trace_read.argtypes = [P, ctypes.POINTER(TraceRec), I]
     L.cai_exec_set_sm_limit.argtypes = [P, I]
     L.cai_exec_set_sm_limit.restype = None
@@ -120,12 +121,16 @@ class Engine:
         L = klib.lib()
         _declare_runtime(L)
         self.L = L
-        # the whole arena is ONE allocation; every tensor of the plan is an offset into it
-        self.arena = torch.empty(int(self.hdr.arena_bytes) + 1024, dtype=torch.uint8, device=self.device)
-        base = (self.arena.data_ptr() + 1023) & ~1023
+        # the whole arena is ONE allocation; every tensor of the plan is an offset into it. A guard region
+        # filled with a known pattern sits on either side (check_canaries()).
+        G = self._GUARD
+        self.arena = torch.empty(int(self.hdr.arena_bytes) + 1024 + 2 * G, dtype=torch.uint8, device=self.device)
+        base = (self.arena.data_ptr() + G + 1023) & ~1023
         self._arena_shift = base - self.arena.data_ptr()
         self.arena_base = base
         self.arena.zero_()
+        self.arena[:self._arena_shift].fill_(0xA5)
+        self.arena[self._arena_shift + int(self.hdr.arena_bytes):].fill_(0xA5)
         self.ex = c_void_p()
         # The six streams come from torch's pool: tensors touched on them stay valid for torch's
         # caching allocators after the executor is gone. compute_hi and comm_tp get high priority.
@@ -152,6 +157,19 @@ class Engine:
         if graph:
             self.use_graph(True)
         torch.cuda.synchronize(self.device)
+
+    _GUARD = 4096
+
+    def check_canaries(self):
+        """Debug aid: the guard bytes on both sides of the arena must still hold their pattern, i.e. no kernel
+        wrote below the first or past the last tensor of the plan. Synchronises the device."""
+        torch.cuda.synchronize(self.device)
+        head = self.arena[:self._arena_shift]
+        tail = self.arena[self._arena_shift + int(self.hdr.arena_bytes):]
+        bad = int((head != 0xA5).sum().item()) + int((tail != 0xA5).sum().item())
+        if bad:
+            raise RuntimeError(f"{bad} guard bytes around the arena were overwritten")
+        return True
 
     # ------------------------------------------------------------------ arena views
     def tensor_view(self, tid: int) -> torch.Tensor:
@@ -350,6 +368,10 @@ class Engine:
         return int(self.L.cai_exec_launches(self.ex))
 
     # ------------------------------------------------------------------ trace
+    def nvtx(self, on=True):
+        """One NVTX range per op of a replay, named by kernel, for timeline tools."""
+        self.L.cai_exec_nvtx_enable(self.ex, int(on))
+
     def trace_step(self, tokens, targets):
         """Run one step with per-op CUDA events; returns a list of TraceRec with measured times."""
         self.L.cai_exec_use_graph(self.ex, 0)

@@ -1,7 +1,7 @@
 """Device trainer: one process == one GPU rank.
 
     python -m cai_b200.trainer <plan.bin> <topology.bin> [--steps N] [--ckpt PATH] [--ckpt-every K]
-                               [--trace CSV] [--graph] [--jsonl FILE]
+                               [--trace CSV] [--graph] [--nvtx] [--jsonl FILE]
     python -m cai_b200.trainer --config configs/x.cfg [...]        (compiles this rank's plan first)
 
 Same command line, table and checkpoint naming as the reference's ``trainer`` (tools/trainer.c),
@@ -35,6 +35,7 @@ def main(argv=None):
     ap.add_argument("--ckpt-every", type=int, default=0)
     ap.add_argument("--trace")
     ap.add_argument("--graph", action="store_true")
+    ap.add_argument("--nvtx", action="store_true", help="NVTX range per op, named by kernel (for timeline tools)")
     ap.add_argument("--jsonl")
     ap.add_argument("--comm", choices=["fused", "baseline"])
     a = ap.parse_args(argv)
@@ -76,6 +77,8 @@ def main(argv=None):
     n = 0
     start_ev, stop_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     first = eng.step_count
+    if a.nvtx:
+        eng.nvtx(True)
     try:
         for step in range(first, a.steps):
             tok, tgt = synthetic_batch(m.vocab_size, m.seq_len, rows * h.dp, step=step, seed=eng.train.seed)

@@ -48,6 +48,14 @@ CAI_API int cai_gemm_bf16_seg(const void* A, const void* B, void* C, const void*
                               int b_mn_major, int epi, float alpha, const int* seg_counts, int seg_rows, int seg_mode,
                               int sm_limit, void* stream);
 
+/* `groups` independent products of one shape in ONE launch (the local experts of a mixture-of-experts layer):
+ * group g reads A and B at row coordinate + g * grp_a / grp_b (rows of the [M,K] or, MN-major, [K,M] tensor),
+ * writes C at row + g * grp_c and owns grp_seg entries of seg_counts. MN-major grouped operands need K % 64 == 0. */
+CAI_API int cai_gemm_bf16_grouped(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                                  long long ldc, int a_mn_major, int b_mn_major, int epi, const int* seg_counts, int seg_rows,
+                                  int seg_mode, int groups, long long grp_a, long long grp_b, long long grp_c, int grp_seg,
+                                  void* stream);
+
 /* ---- fused compute + collective GEMMs over peer memory, C forms with explicit member arena bases
  * (bases[rank] is the local one; sig_off: arena offset of the signal block, see cai_signal_block_bytes;
  * epoch_base: device word, epoch of the call = *epoch_base + 2 * seq and must grow from call to call).

@@ -61,6 +61,12 @@ struct GemmParams {
     const int* seg_counts;
     int seg_rows;
     int seg_mode;
+    // ---- groups (the local experts of a mixture-of-experts layer in one launch): `groups` independent
+    // products of the same M x N x K; group g reads A / B at row coordinate + g * grp_a / grp_b of their
+    // tensor maps, writes C (and reads R) at row + g * grp_c, and owns grp_seg entries of seg_counts.
+    int groups;
+    long long grp_a, grp_b, grp_c;
+    int grp_seg;
     // ---- kGemmGatherB: B lives in a staging buffer that the leading n_copy CTAs fill from the sharded
     // parameter space (gather.cuh); b_elem_off is the element offset of B inside the staged range.
     GatherJob gat;
@@ -68,14 +74,17 @@ struct GemmParams {
     long long ldb;
 };
 
-__device__ __forceinline__ bool seg_live(const GemmParams& p, int row0) {
+__device__ __forceinline__ bool seg_live(const GemmParams& p, int g, int row0) {
     const int slab = row0 / p.seg_rows;
-    return row0 - slab * p.seg_rows < p.seg_counts[slab];
+    return row0 - slab * p.seg_rows < p.seg_counts[g * p.grp_seg + slab];
 }
 
 constexpr int kGemmPlain = 0, kGemmAllGatherA = 1, kGemmReduceScatter = 2, kGemmGatherB = 3;
 
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile_all, int& tm, int& tn, int& grp) {
+    const int tiles_per_product = p.tiles_m * p.tiles_n;
+    grp = tile_all / tiles_per_product;
+    const int tile = tile_all - grp * tiles_per_product;
     const int per_group = p.group_m * p.tiles_n;
     const int g = tile / per_group;
     const int first_m = g * p.group_m;
@@ -215,7 +224,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_tiles = p.tiles_m * p.tiles_n * p.groups;
     const int num_kb = (p.K + kBK - 1) / kBK;
 
     if (warp == 0) {
@@ -225,10 +234,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             uint32_t ph = 0;
             bool ok = true;
             for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
-                int tm, tn;
-                tile_coords(p, tile, tm, tn);
+                int tm, tn, grp;
+                tile_coords(p, tile, tm, tn, grp);
                 const int m0 = tm * kBM, n0 = tn * BN;
-                if (p.seg_mode == 1 && !seg_live(p, m0)) continue;
+                if (p.seg_mode == 1 && !seg_live(p, grp, m0)) continue;
+                const int ga = static_cast<int>(grp * p.grp_a), gb = static_cast<int>(grp * p.grp_b);
                 if (p.mode == kGemmAllGatherA) {
                     // rows of this tile must have been staged by a copy CTA; they were written through
                     // the generic proxy, the TMA engine reads through the async proxy
@@ -268,7 +278,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     }
                 }
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (p.seg_mode == 2 && !seg_live(p, kb * kBK)) continue;
+                    if (p.seg_mode == 2 && !seg_live(p, grp, kb * kBK)) continue;
                     if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, CAI_DEV_TIMEOUT_TMA_EMPTY)) {
                         ok = false;
                         break;
@@ -278,18 +288,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     uint8_t* b_dst = sB + s * kBStageBytes;
                     const int k0 = kb * kBK;
                     if (!p.a_mn) {
-                        tma_load_2d(a_dst, &tmA, &full[s], k0, m0);
+                        tma_load_2d(a_dst, &tmA, &full[s], k0, m0 + ga);
                     } else {
 #pragma unroll
                         for (int c = 0; c < kBM / 64; ++c)
-                            tma_load_2d(a_dst + c * (kBK * 128), &tmA, &full[s], m0 + c * 64, k0);
+                            tma_load_2d(a_dst + c * (kBK * 128), &tmA, &full[s], m0 + c * 64, k0 + ga);
                     }
                     if (!p.b_mn) {
-                        tma_load_2d(b_dst, &tmB, &full[s], k0, n0);
+                        tma_load_2d(b_dst, &tmB, &full[s], k0, n0 + gb);
                     } else {
 #pragma unroll
                         for (int c = 0; c < BN / 64; ++c)
-                            tma_load_2d(b_dst + c * (kBK * 128), &tmB, &full[s], n0 + c * 64, k0);
+                            tma_load_2d(b_dst + c * (kBK * 128), &tmB, &full[s], n0 + c * 64, k0 + gb);
                     }
                     if (++s == STAGES) {
                         s = 0;
@@ -311,10 +321,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             bool ok = true;
             int t = 0;
             for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
-                if (p.seg_mode == 1) {
+                int grp = 0;
+                if (p.seg_mode) {
                     int tm, tn;
-                    tile_coords(p, tile, tm, tn);
-                    if (!seg_live(p, tm * kBM)) continue;
+                    tile_coords(p, tile, tm, tn, grp);
+                    if (p.seg_mode == 1 && !seg_live(p, grp, tm * kBM)) continue;
                 }
                 const int acc = t & 1;
                 const uint32_t acc_ph = (t >> 1) & 1;
@@ -327,7 +338,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 uint32_t started = 0;  // becomes 1 after the first MMA of the tile (which overwrites the accumulator)
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (p.seg_mode == 2 && !seg_live(p, kb * kBK)) continue;
+                    if (p.seg_mode == 2 && !seg_live(p, grp, kb * kBK)) continue;
                     if (!mbar_wait(&full[s], ph, abort_flag, p.status, CAI_DEV_TIMEOUT_TMA_FULL)) {
                         ok = false;
                         break;
@@ -364,9 +375,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t rs_prev_slot = 0;
         (void)rs_prev_owner; (void)rs_prev_slot;
         for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
-            int tm, tn;
-            tile_coords(p, tile, tm, tn);
-            if (p.seg_mode == 1 && !seg_live(p, tm * kBM)) continue;
+            int tm, tn, grp;
+            tile_coords(p, tile, tm, tn, grp);
+            if (p.seg_mode == 1 && !seg_live(p, grp, tm * kBM)) continue;
             const int acc = t & 1;
             const uint32_t acc_ph = (t >> 1) & 1;
             ++t;
@@ -374,7 +385,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             bool acc_valid = true;
             if (p.seg_mode == 2) {
                 acc_valid = false;
-                for (int kb = 0; kb < num_kb && !acc_valid; ++kb) acc_valid = seg_live(p, kb * kBK);
+                for (int kb = 0; kb < num_kb && !acc_valid; ++kb) acc_valid = seg_live(p, grp, kb * kBK);
             }
             if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag, p.status, CAI_DEV_TIMEOUT_TMEM_FULL)) {
                 ok = false;
@@ -434,8 +445,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 rs_prev_owner = owner;
                 rs_prev_slot = static_cast<uint32_t>((tm - owner * blocks_per_rank) * p.tiles_n + tn);
             } else {
-            const long long row = (long long)tm * kBM + q * 32 + lane;
-            const bool row_ok = row < p.M;
+            const long long row_in = (long long)tm * kBM + q * 32 + lane;   // row inside this group's product
+            const bool row_ok = row_in < p.M;
+            const long long row = row_in + grp * p.grp_c;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t r[32];
@@ -606,7 +618,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
     // gather mode walks every row block of an output column before the next column, so that the columns of B
     // are needed in the order the copy CTAs stage them (A stays L2 resident)
     p.group_m = p.mode == kGemmGatherB ? p.tiles_m : 8;
-    const int tiles = p.tiles_m * p.tiles_n;
+    const int tiles = p.tiles_m * p.tiles_n * p.groups;
     int grid = tiles < sms - p.n_copy ? tiles : sms - p.n_copy;
     if (grid < 1) grid = 1;
     grid += p.n_copy;
@@ -635,7 +647,7 @@ static int gemm_dispatch(const void* A, const void* B, long long lda, long long 
     // Tile width: fewer, wider tiles amortise the A operand better; narrower tiles quantise
     // into waves better when the output is small.
     auto cost = [&](int bn) {
-        const long long tiles = (long long)((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
+        const long long tiles = (long long)((M + kBM - 1) / kBM) * ((N + bn - 1) / bn) * p.groups;
         const long long waves = (tiles + usable - 1) / usable;
         // a 128-wide tile streams 128 B/clk/SM of operands for half the math of a 256-wide one and runs
         // at the L2 limit: measured 27.6 us against 30 us per wave at K = 4096, i.e. 1.84x the cost per FLOP
@@ -644,11 +656,13 @@ static int gemm_dispatch(const void* A, const void* B, long long lda, long long 
     const int BN = cost(256) <= cost(128) ? 256 : 128;
     CUtensorMap tmA, tmB;
     bool ok;
-    if (!p.a_mn) ok = encode_tmap_2d(&tmA, A, M, K, lda, kBK, kBM, 2);
-    else ok = encode_tmap_2d(&tmA, A, K, M, lda, 64, kBK, 2);
+    // the maps of a grouped launch span every group's rows
+    const long long xa = (p.groups - 1) * p.grp_a, xb = (p.groups - 1) * p.grp_b;
+    if (!p.a_mn) ok = encode_tmap_2d(&tmA, A, M + xa, K, lda, kBK, kBM, 2);
+    else ok = encode_tmap_2d(&tmA, A, K + xa, M, lda, 64, kBK, 2);
     if (!ok) return CAI_K_BAD_ARG;
-    if (!p.b_mn) ok = encode_tmap_2d(&tmB, B, N, K, ldb, kBK, BN, 2);
-    else ok = encode_tmap_2d(&tmB, B, K, N, ldb, 64, kBK, 2);
+    if (!p.b_mn) ok = encode_tmap_2d(&tmB, B, N + xb, K, ldb, kBK, BN, 2);
+    else ok = encode_tmap_2d(&tmB, B, K + xb, N, ldb, 64, kBK, 2);
     if (!ok) return CAI_K_BAD_ARG;
     p.status = status_words(dev);
     if (p.mode == kGemmReduceScatter) {
@@ -665,6 +679,7 @@ static void plain_params(GemmParams& p) {
     p.epoch_base = nullptr; p.seq = 0; p.src_off = 0; p.stage_off = 0; p.a_full = nullptr; p.ld_src = 0;
     p.pt = PeerTable{};
     p.seg_counts = nullptr; p.seg_rows = 0; p.seg_mode = 0;
+    p.groups = 1; p.grp_a = p.grp_b = p.grp_c = 0; p.grp_seg = 0;
     p.gat = GatherJob{}; p.b_elem_off = 0; p.ldb = 0;
     p.R = nullptr; p.ldr = 0; p.alpha = 1.f; p.epi = CAI_EPI_BF16; p.a_mn = 0;
 }
@@ -713,6 +728,29 @@ CAI_API int cai_gemm_bf16_seg(const void* A, const void* B, void* C, const void*
     p.ldc = ldc; p.ldr = ldr;
     p.seg_counts = seg_counts; p.seg_rows = seg_rows; p.seg_mode = seg_mode;
     return gemm_dispatch(A, B, lda, ldb, p, sm_limit, reinterpret_cast<cudaStream_t>(stream));
+}
+
+CAI_API int cai_gemm_bf16_grouped(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                                  long long ldc, int a_mn_major, int b_mn_major, int epi, const int* seg_counts, int seg_rows,
+                                  int seg_mode, int groups, long long grp_a, long long grp_b, long long grp_c, int grp_seg,
+                                  void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0 || groups <= 0) return CAI_K_OK;
+    if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 3) || (epi != CAI_EPI_BF16 && (epi != CAI_EPI_F32) && epi != CAI_EPI_F32_ACCUM) ||
+        (epi == CAI_EPI_BF16 && (ldc & 7)) || (seg_mode && (!seg_counts || seg_rows <= 0 || seg_rows % 128 || seg_mode > 2)) ||
+        ((a_mn_major || b_mn_major) && groups > 1 && (K % kBK))) {
+        set_last_error("gemm_grouped: bad arguments (M=%d N=%d K=%d groups=%d)", M, N, K, groups);
+        return CAI_K_BAD_ARG;
+    }
+    GemmParams p;
+    plain_params(p);
+    p.M = M; p.N = N; p.K = K;
+    p.a_mn = a_mn_major ? 1 : 0;
+    p.b_mn = b_mn_major ? 1 : 0;
+    p.epi = epi;
+    p.C = C; p.ldc = ldc;
+    p.seg_counts = seg_counts; p.seg_rows = seg_rows; p.seg_mode = seg_mode;
+    p.groups = groups; p.grp_a = grp_a; p.grp_b = grp_b; p.grp_c = grp_c; p.grp_seg = grp_seg;
+    return gemm_dispatch(A, B, lda, ldb, p, 0, reinterpret_cast<cudaStream_t>(stream));
 }
 
 // y[T,N] = concat_rows(x_local of every member)[T,K] * op(B); also leaves the gathered rows in a_full.

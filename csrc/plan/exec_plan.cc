@@ -221,6 +221,16 @@ struct Builder {
         x.f[0] = 1.0f;
         push(OP_GEMM, ST_COMPUTE_HI, 2.0 * M * N * K, 0, 0, mb, &x);
     }
+    // `groups` products of one shape in a single launch (the local experts): A, B, C are the stacked tensors,
+    // M / N / K the per-group sizes; the runtime derives each group's row offsets from the operand forms.
+    void gemm_grouped(int A, int B, int C, uint32_t M, uint32_t N, uint32_t K, bool ta, bool tb, int epi, int counts,
+                      uint32_t seg_rows, int seg_mode, uint32_t groups, uint16_t mb) {
+        ExecOp x = xop(K_GEMM, static_cast<uint16_t>((ta ? 1 : 0) | (tb ? 2 : 0) | (epi << 4) | 0x100));
+        x.t[0] = A; x.t[1] = B; x.t[2] = C; x.t[4] = counts;
+        x.i[0] = M; x.i[1] = N; x.i[2] = K; x.i[3] = seg_rows; x.i[4] = seg_mode | static_cast<int32_t>(groups << 8);
+        x.f[0] = 1.0f;
+        push(OP_GEMM, ST_COMPUTE_HI, 2.0 * M * N * K * groups, 0, 0, mb, &x);
+    }
     void rmsnorm_fwd(int x, int g, int y, int rstd, uint32_t rows, uint16_t mb) {
         ExecOp e = xop(K_RMSNORM_FWD);
         e.t[0] = x; e.t[1] = g; e.t[2] = y; e.t[3] = rstd;
@@ -310,7 +320,7 @@ void exec_operands(const ExecOp& x, std::vector<int>* reads, std::vector<int>* w
         case K_RMSNORM_FWD: R(0); R(1); W(2); W(3); break;
         case K_RMSNORM_BWD: R(0); R(1); R(2); R(3); if (x.i[2]) R(4); W(4); if (x.i[3]) R(5); W(5); W(6); break;
         case K_GEMM: {
-            const int epi = x.flags >> 4;
+            const int epi = (x.flags >> 4) & 0xF;
             R(0); R(1); if (epi == 2) R(2); R(3); R(4); W(2);
             break;
         }
@@ -651,13 +661,6 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         e.i[0] = m.moe_top_k; e.i[1] = m.num_experts; e.i[2] = moe_cap; e.i[3] = GROUP_EP; e.i[4] = static_cast<int32_t>(b.next_seq++);
         b.push(OP_MOE_GEMM_COMBINE, ST_COMPUTE_HI, 2.0 * T * m.moe_top_k * H, 2.0 * T * m.moe_top_k * H, GROUP_EP, mb, &e);
     };
-    // per local expert: rows [e * ep * cap, (e+1) * ep * cap) of a slab, counts [e * ep, (e+1) * ep)
-    auto expert_rows = [&](int slab, uint32_t e) { return b.view(slab, e * d.ep * moe_cap, d.ep * moe_cap); };
-    auto expert_cnt = [&](const LayerActs& a, uint32_t e) {
-        const TensorDesc& ct = out->tensors[a.cnt_recv];
-        return b.tensor_at(TC_COMM, DT_INT32, ct.offset + static_cast<uint64_t>(e) * d.ep * 4, 1, d.ep, d.ep);
-    };
-
     // ---------------- activations: one set per in-flight microbatch
     const uint32_t slots = std::max<uint32_t>(1, std::min<uint32_t>(d.pp - b.stage, ga));
     out->xhdr.act_slots = slots;
@@ -754,18 +757,14 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
                 b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 10.0 * T * m.num_experts, 0, 0, mb, &e);
             }
             moe_dispatch(a.xn2, -1, a, a.xs, mb);
-            for (uint32_t e = 0; e < E_l; ++e)
-                b.gemm_seg(expert_rows(a.xs, e), b.view(w.wgu.w, e * 2 * F, 2 * F), expert_rows(a.gu, e), seg_m, 2 * F, H, false,
-                           false, 0, expert_cnt(a, e), moe_cap, 1, mb);
+            b.gemm_grouped(a.xs, w.wgu.w, a.gu, seg_m, 2 * F, H, false, false, 0, a.cnt_recv, moe_cap, 1, E_l, mb);
             {
                 ExecOp e = xop(K_SWIGLU_FWD);
                 e.t[0] = a.gu; e.t[1] = a.act;
                 e.i[0] = moe_rows; e.i[1] = F;
                 b.push(OP_SWIGLU, ST_COMPUTE_HI, 4.0 * moe_rows * F, 0, 0, mb, &e);
             }
-            for (uint32_t e = 0; e < E_l; ++e)
-                b.gemm_seg(expert_rows(a.act, e), b.view(w.wd.w, e * H, H), expert_rows(a.ys, e), seg_m, H, F, false, false, 0,
-                           expert_cnt(a, e), moe_cap, 1, mb);
+            b.gemm_grouped(a.act, w.wd.w, a.ys, seg_m, H, F, false, false, 0, a.cnt_recv, moe_cap, 1, E_l, mb);
             moe_combine(a.hmid, x_next, a.rw, a, a.ys, -1, -1, true, mb);
             return;
         }
@@ -910,26 +909,16 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
                 const uint32_t F = m.ffn_hidden, seg_m = d.ep * moe_cap;
                 moe_combine(-1, -1, -1, a, a.ys, dstream, dw_r, false, mb);           // dw[t,s] = <dx_next[t], y(t,s)>
                 moe_dispatch(dstream, a.rw, a, dy_s, mb);                              // dy rows = w[t,s] * dx_next[t]
-                for (uint32_t e = 0; e < E_l; ++e) {
-                    const int cnt = expert_cnt(a, e);
-                    b.gemm_seg(expert_rows(dy_s, e), b.view(w.wd.w, e * H, H), expert_rows(dact_s, e), seg_m, F, H, false, true, 0,
-                               cnt, moe_cap, 1, mb);
-                    b.gemm_seg(expert_rows(dy_s, e), expert_rows(a.act, e), b.view(w.wd.g, e * H, H), H, F, seg_m, true, true, wg_epi,
-                               cnt, moe_cap, 2, mb);
-                }
+                b.gemm_grouped(dy_s, w.wd.w, dact_s, seg_m, F, H, false, true, 0, a.cnt_recv, moe_cap, 1, E_l, mb);
+                b.gemm_grouped(dy_s, a.act, w.wd.g, H, F, seg_m, true, true, wg_epi, a.cnt_recv, moe_cap, 2, E_l, mb);
                 {
                     ExecOp e = xop(K_SWIGLU_BWD);
                     e.t[0] = a.gu; e.t[1] = dact_s; e.t[2] = dgu_s;
                     e.i[0] = moe_rows; e.i[1] = F;
                     b.push(OP_SWIGLU, ST_COMPUTE_HI, 8.0 * moe_rows * F, 0, 0, mb, &e);
                 }
-                for (uint32_t e = 0; e < E_l; ++e) {
-                    const int cnt = expert_cnt(a, e);
-                    b.gemm_seg(expert_rows(dgu_s, e), b.view(w.wgu.w, e * 2 * F, 2 * F), expert_rows(dx_s, e), seg_m, H, 2 * F, false,
-                               true, 0, cnt, moe_cap, 1, mb);
-                    b.gemm_seg(expert_rows(dgu_s, e), expert_rows(a.xs, e), b.view(w.wgu.g, e * 2 * F, 2 * F), 2 * F, H, seg_m, true,
-                               true, wg_epi, cnt, moe_cap, 2, mb);
-                }
+                b.gemm_grouped(dgu_s, w.wgu.w, dx_s, seg_m, H, 2 * F, false, true, 0, a.cnt_recv, moe_cap, 1, E_l, mb);
+                b.gemm_grouped(dgu_s, a.xs, w.wgu.g, 2 * F, H, seg_m, true, true, wg_epi, a.cnt_recv, moe_cap, 2, E_l, mb);
                 moe_combine(-1, dxn, -1, a, dx_s, -1, -1, true, mb);                  // dxn2[t] = sum_s dx(t,s)
                 {
                     ExecOp e = xop(K_MOE_ROUTE, 1);

@@ -58,6 +58,9 @@ CAI_API int cai_exec_step(cai_exec* ex, int step, float lr);
 CAI_API int cai_exec_sync(cai_exec* ex);
 CAI_API int cai_exec_use_graph(cai_exec* ex, int on);
 CAI_API int cai_exec_trace_enable(cai_exec* ex, int on);
+/* One NVTX range per op, named by its kernel, around the launches of a replay (stream replays only; a captured
+ * graph keeps the ranges of the capture). */
+CAI_API int cai_exec_nvtx_enable(cai_exec* ex, int on);
 CAI_API int cai_exec_trace_read(cai_exec* ex, cai_exec_trace_rec* out, int cap);
 
 #endif /* CAI_RUNTIME_H */

@@ -21,6 +21,8 @@
 #include <string>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "../comm/fused.h"
 #include "../comm/gather.cuh"
 #include "../comm/moe.h"
@@ -157,6 +159,7 @@ struct cai_exec {
     cudaGraphExec_t graph = nullptr;
     bool use_graph = false;
     bool trace_on = false;
+    bool nvtx_on = false;   // one NVTX range per op, named by kernel (for timeline tools)
     std::vector<TraceRec> trace;
     cai_fused_hook_t fused_hook = nullptr;
     void* fused_ctx = nullptr;
@@ -187,13 +190,22 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
             return cai_rmsnorm_bwd(P(0), P(1), (const float*)P(2), P(3), P(4), (float*)P(5), (float*)P(6), x.i[0], x.i[1],
                                    x.i[2], x.i[3], st);
         case K_GEMM: {
-            const int ta = x.flags & 1, tb = (x.flags >> 1) & 1, epi = x.flags >> 4;
+            const int ta = x.flags & 1, tb = (x.flags >> 1) & 1, epi = (x.flags >> 4) & 0xF;
             if (ex->has_pending_gather) {
                 // the layer's weights are staged by the copy CTAs of this GEMM (B lies in the staged range)
                 ex->has_pending_gather = false;
                 return cai_fused_gather_gemm(ex->peers[GROUP_DP], ex->pending_gather, P(0), P(1), P(2), P(3), x.i[0], x.i[1], x.i[2],
                                              ex->ld(x.t[0]), ex->ld(x.t[1]), ex->ld(x.t[2]), x.t[3] >= 0 ? ex->ld(x.t[3]) : 0, ta, tb, epi,
                                              x.f[0], reinterpret_cast<const uint32_t*>(ex->hyper_dev) + 7, ex->pending_seq, st);
+            }
+            if (x.flags & 0x100) {
+                // every local expert in one launch: group offsets follow from the operand forms
+                const int M = x.i[0], N = x.i[1], K = x.i[2], seg_rows = x.i[3], seg_mode = x.i[4] & 0xFF, groups = x.i[4] >> 8;
+                const int epi8 = (x.flags >> 4) & 0xF;
+                const long long ga = ta ? K : M, gb = tb ? K : N, gc = M;
+                return cai_gemm_bf16_grouped(P(0), P(1), P(2), M, N, K, ex->ld(x.t[0]), ex->ld(x.t[1]), ex->ld(x.t[2]), ta, tb, epi8,
+                                             (const int*)P(4), seg_rows, seg_mode, groups, ga, gb, gc,
+                                             (seg_mode == 2 ? K : M) / seg_rows, st);
             }
             if (x.t[4] >= 0)  // ragged expert slab: live rows per sub-slab come from a device table
                 return cai_gemm_bf16_seg(P(0), P(1), P(2), P(3), x.i[0], x.i[1], x.i[2], ex->ld(x.t[0]), ex->ld(x.t[1]),
@@ -384,6 +396,16 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
     }
 }
 
+// names of the kernel ids, for NVTX ranges (same order as the enum in plan/formats.h)
+const char* kernel_label(uint16_t k) {
+    static const char* n[K_COUNT] = {"none", "embed_fwd", "embed_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "gemm", "rope", "attn_fwd",
+                                     "attn_bwd", "swiglu_fwd", "swiglu_bwd", "cross_entropy", "adamw", "zero", "nccl_all_reduce",
+                                     "nccl_reduce_scatter", "nccl_all_gather", "nccl_all_to_all", "nccl_send", "nccl_recv",
+                                     "gemm_rs", "ag_gemm", "rs_adamw", "fsdp_ag_gemm", "moe_route", "moe_dispatch", "moe_combine",
+                                     "load_tokens", "add", "cross_entropy_tp", "quant_fp8", "gemm_fp8"};
+    return k < K_COUNT ? n[k] : "?";
+}
+
 int replay(cai_exec* ex) {
     cudaStream_t hi = ex->streams[ST_COMPUTE_HI];
     // fork: every stream starts after everything already queued on compute_hi
@@ -412,7 +434,9 @@ int replay(cai_exec* ex) {
             tr = &ex->trace.back();
             cudaEventRecord(tr->start, st);
         }
+        if (ex->nvtx_on) nvtxRangePushA(kernel_label(ex->exec[op.exec - 1].kernel));
         const int rc = run_op(ex, op, ex->exec[op.exec - 1], st);
+        if (ex->nvtx_on) nvtxRangePop();
         if (rc != 0) return rc;
         {
             // kernels of this library behind the op (memsets and NCCL calls are not ours)
@@ -667,6 +691,10 @@ CAI_API int cai_exec_use_graph(cai_exec* ex, int on) {
 
 CAI_API int cai_exec_trace_enable(cai_exec* ex, int on) {
     ex->trace_on = on != 0;
+    return 0;
+}
+CAI_API int cai_exec_nvtx_enable(cai_exec* ex, int on) {
+    ex->nvtx_on = on != 0;
     return 0;
 }
 

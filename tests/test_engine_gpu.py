@@ -38,6 +38,7 @@ def test_first_step_loss_and_grads_match_fp32_reference():
     ref = _loss_ref(eng, params, tok, tgt)
     ref.backward()
     loss = eng.step(tok, tgt, lr=0.0)  # lr 0: gradients stay inspectable, weights unchanged
+    assert eng.check_canaries()        # nothing wrote outside the arena
     assert abs(loss - ref.item()) < 2e-2 * ref.item(), (loss, ref.item())
     worst = 0.0
     for n in eng.parameter_names():

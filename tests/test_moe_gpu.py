@@ -185,3 +185,40 @@ def test_dispatch_expert_gemm_combine_single_member():
         refd = (y * d.float()).sum(-1) * (pos[:, s] >= 0)
         assert torch.allclose(dw[:, s], refd, atol=0.3, rtol=3e-2)
     assert _lib.device_status(clear=True) == 0
+
+
+def test_grouped_gemm_matches_per_group_products():
+    """All local experts in one launch: forward form (rows segmented), weight-gradient form (K segmented)."""
+    from cai_b200 import ops
+    torch.manual_seed(3)
+    G, cap, nsrc, K, N = 5, 128, 2, 256, 320
+    M = cap * nsrc                                   # rows per expert: one sub-slab per source member
+    counts = torch.tensor([128, 7, 0, 64, 100, 1, 128, 128, 0, 0], device="cuda", dtype=torch.int32)   # [G * nsrc]
+    A = torch.randn(G * M, K, device="cuda").to(torch.bfloat16)
+    W = (torch.randn(G * N, K, device="cuda") * 0.1).to(torch.bfloat16)
+    out = torch.full((G * M, N), 5.0, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_grouped(A, W, out, M, N, K, groups=G, seg_counts=counts, seg_rows=cap, seg_mode=1)
+    for g in range(G):
+        ref = A[g * M:(g + 1) * M].float() @ W[g * N:(g + 1) * N].float().t()
+        for s in range(nsrc):
+            c = int(counts[g * nsrc + s])
+            r0 = g * M + s * cap
+            assert torch.allclose(out[r0:r0 + c].float(), ref[s * cap:s * cap + c], atol=0.3, rtol=2e-2), (g, s)
+            if c == 0:
+                assert torch.all(out[r0:r0 + cap] == 5.0)   # dead sub-slab: tile skipped
+    # weight gradient per expert: dW_g[N, K2] = Y_g^T X_g over the live rows
+    K2 = 192
+    Y = torch.randn(G * M, N, device="cuda").to(torch.bfloat16)
+    X = torch.randn(G * M, K2, device="cuda").to(torch.bfloat16)
+    for g in range(G):
+        for s in range(nsrc):
+            c = int(counts[g * nsrc + s])
+            r0 = g * M + s * cap
+            Y[r0 + c:r0 + cap] = 0
+            X[r0 + c:r0 + cap] = 0
+    dW = torch.zeros(G * N, K2, device="cuda")
+    ops.gemm_grouped(Y, X, dW, N, K2, M, groups=G, trans_a=True, trans_b=True, accumulate=True, seg_counts=counts, seg_rows=cap,
+                     seg_mode=2)
+    for g in range(G):
+        ref = Y[g * M:(g + 1) * M].float().t() @ X[g * M:(g + 1) * M].float()
+        assert torch.allclose(dW[g * N:(g + 1) * N], ref, atol=0.5, rtol=2e-2), g

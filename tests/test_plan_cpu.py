@@ -1,5 +1,6 @@
 """GPU-free tests of the offline compiler, verifier, analytic runtime and tools."""
 import ctypes
+import os
 import subprocess
 from pathlib import Path
 
@@ -201,3 +202,15 @@ def test_plan_variants_compile_and_verify(tmp_path):
         with pytest.raises(plan.PlanError):   # 4 GPUs: dp = 4, or tp = 2 x dp = 2
             plan.compile_plans((ROOT / "configs" / "tiny_mp.cfg").read_text() + "\ngpus_per_rack = 4\ngpus_per_tray = 4\n" + bad,
                                tmp_path / "bad", version=2, text=True)
+
+
+def test_host_code_is_clean_under_address_and_ub_sanitizers():
+    """Plan compiler, verifier (hazard checker), analytic runtime and oracle, built with
+    -fsanitize=address,undefined, run the native self-test without a report."""
+    from cai_b200 import _build
+    exe = _build.build_sanitized_selftest()
+    r = subprocess.run([str(exe)], cwd=ROOT, capture_output=True, text=True, timeout=600,
+                       env=dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=0"))
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-3000:]
+    assert "0 failures" in out and "runtime error" not in out and "AddressSanitizer" not in out, out[-3000:]
