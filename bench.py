@@ -25,6 +25,7 @@ import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import time
 from pathlib import Path
 
@@ -135,9 +136,8 @@ def run_ours(args):
         eng.use_graph(True)
         eng.step(*batches[0])  # capture + first replay
 
-    sampler = ClockSampler(str(ROOT / "gpurun_out" / f"bench_clocks_n{world}.csv")) if rank == 0 else None
+    sampler = ClockSampler(os.path.join(tempfile.gettempdir(), f"cai_bench_clocks_n{world}_{os.getpid()}.csv")) if rank == 0 else None
     if sampler:
-        (ROOT / "gpurun_out").mkdir(exist_ok=True)
         sampler.start()
 
     # ---- device-timed: batch resident on the device
