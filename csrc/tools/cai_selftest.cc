@@ -313,6 +313,38 @@ static void test_exec_plans() {
     VerifyReport rep;
     verify_hazards(p, &rep);
     CHECK(rep.problems > 0, "hazard checker missed a schedule without waits");
+
+    // Column views: two unordered writers on different streams are fine when they cover disjoint columns of
+    // the same rows (dQ beside dK/dV), and a hazard as soon as the column intervals touch.
+    for (int overlap = 0; overlap < 2; ++overlap) {
+        Plan q;
+        q.hdr.version = 2;
+        auto tensor = [&](uint64_t off, uint32_t rows, uint32_t cols, uint32_t ld) {
+            TensorDesc t{};
+            t.offset = off; t.dtype = DT_BF16; t.tclass = TC_WORKSPACE;
+            t.nbytes = (static_cast<uint64_t>(rows - 1) * ld + cols) * 2;
+            q.tensors.push_back(t);
+            q.shapes.insert(q.shapes.end(), {rows, cols, ld, 1u});
+            return static_cast<int>(q.tensors.size()) - 1;
+        };
+        const int left = tensor(1024, 64, 256, 768);                                // columns [0, 256) of a [64, 768] buffer
+        const int right = tensor(1024 + (overlap ? 255 : 256) * 2, 64, 512, 768);   // columns [256, 768) or one column early
+        for (int k = 0; k < 2; ++k) {
+            ExecOp x{};
+            for (int& t : x.t) t = -1;
+            x.kernel = K_ZERO;
+            x.t[0] = k ? right : left;
+            q.exec.push_back(x);
+            Op o{};
+            o.kind = OP_ELEMENTWISE;
+            o.stream_id = k ? ST_COMM_DP : ST_COMPUTE_HI;
+            o.exec = static_cast<uint32_t>(q.exec.size());
+            q.ops.push_back(o);
+        }
+        VerifyReport r2;
+        verify_hazards(q, &r2);
+        CHECK((r2.problems > 0) == (overlap == 1), "column views, overlap=%d: %d problems", overlap, r2.problems);
+    }
 }
 
 static void test_checkpoint_files() {
