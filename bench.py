@@ -168,6 +168,29 @@ def run_ours(args):
     e2e_ms = (time.perf_counter() - t0) * 1e3 / K
     clocks = sampler.stop(gpu_index=local) if sampler else None
 
+    if args.breakdown:
+        # per-op CUDA events over one more step, summed per kernel and GEMM shape (rank 0 prints the table)
+        import collections
+        from cai_b200 import plan as planlib
+        recs = eng.trace_step(*batches[0])
+        agg = collections.defaultdict(lambda: [0.0, 0, 0.0])
+        for r in recs:
+            op = eng.plan.ops[r.op_index]
+            x = eng.plan.exec[op.exec - 1]
+            key = planlib.KERNEL_NAMES[x.kernel]
+            if x.kernel in (planlib.K_GEMM, 20, 21, planlib.K_GEMM_FP8):
+                key += f"_ta{x.flags & 1}tb{(x.flags >> 1) & 1}_M{x.i[0]}N{x.i[1]}K{x.i[2]}"
+            a = agg[key]
+            a[0] += r.end_s - r.start_s
+            a[1] += 1
+            a[2] += op.flops
+        if rank == 0:
+            tot = sum(a[0] for a in agg.values())
+            print(f"# per-op breakdown of one step, {world} GPU(s), {tot * 1e3:.1f} ms traced", file=sys.stderr)
+            for k, a in sorted(agg.items(), key=lambda kv: -kv[1][0])[:30]:
+                print(f"# {k:48s} {a[0] * 1e3:9.2f} ms {100 * a[0] / tot:5.1f}% n={a[1]:5d} {a[2] / max(a[0], 1e-9) / 1e12:8.1f} TFLOP/s",
+                      file=sys.stderr)
+
     t = torch.tensor([dev_ms, e2e_ms], device=eng.device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -226,6 +249,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--comm", default="fused", choices=["fused", "baseline"])
     ap.add_argument("--graph", type=int, default=0)
+    ap.add_argument("--breakdown", action="store_true", help="also print a per-op time table of one step (stderr)")
     ap.add_argument("--config", default="tp8", choices=sorted(CONFIGS), help="which named config (default: the headline one)")
     args = ap.parse_args()
     if args.impl == "reference":
