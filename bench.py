@@ -192,9 +192,13 @@ def run_ours(args):
                       file=sys.stderr)
 
     t = torch.tensor([dev_ms, e2e_ms], device=eng.device, dtype=torch.float64)
+    # the loss lives on the last pipeline stage (the other stages read 0): every rank reports the largest value
+    lv = torch.tensor([loss0 or 0.0, loss_e2e, loss_dev], device=eng.device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(lv, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms = t.tolist()
+    loss0, loss_e2e, loss_dev = lv.tolist()
     tokens = eng.tokens_per_step()
     value = tokens / (dev_ms * 1e-3)
     peaks = {}

@@ -438,10 +438,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 // announce the previous tile: its stores (all but the newest group) have completed
                 asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
                 fence_proxy_async_all();
-                __threadfence_system();
-                bar_sync_epilogue();
-                if (warp == 2 && lane == 0 && rs_prev_owner >= 0)
+                bar_sync_epilogue();   // every lane's stores of the previous tile have completed
+                if (warp == 2 && lane == 0 && rs_prev_owner >= 0) {
+                    // one system-scope fence by the signalling thread (cumulative over what the barrier ordered)
+                    __threadfence_system();
                     st_release_sys(sig_word(p.pt, rs_prev_owner, p.group_kind, kSigTile + p.pt.rank * kSigTileSlots + rs_prev_slot), epoch);
+                }
                 rs_prev_owner = owner;
                 rs_prev_slot = static_cast<uint32_t>((tm - owner * blocks_per_rank) * p.tiles_n + tn);
             } else {
@@ -515,10 +517,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             // the last tile's stores: wait for completion, then announce it
             asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
             fence_proxy_async_all();
-            __threadfence_system();
             bar_sync_epilogue();
-            if (warp == 2 && lane == 0 && rs_prev_owner >= 0)
+            if (warp == 2 && lane == 0 && rs_prev_owner >= 0) {
+                __threadfence_system();
                 st_release_sys(sig_word(p.pt, rs_prev_owner, p.group_kind, kSigTile + p.pt.rank * kSigTileSlots + rs_prev_slot), epoch);
+            }
         }
     }
 
