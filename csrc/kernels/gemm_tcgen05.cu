@@ -154,6 +154,15 @@ __device__ __forceinline__ void allgather_copy_role(const GemmParams& p, uint32_
     }
 }
 
+// Reduce-scatter epilogue staging: 128 columns at a time (32 rows x (256 + 16) bytes per epilogue warp), which
+// leaves room for a fourth operand stage. The kernel has no static shared memory, so the dynamic window starts
+// 1 KB aligned and needs no alignment slack in practice; the reduce-scatter variant budgets 768 bytes.
+constexpr int kRsCols = 128;
+constexpr int kRsPitch = kRsCols * 2 + 16;
+constexpr int kRsStageBytes = 4 * 32 * kRsPitch;
+template <bool RS>
+__host__ __device__ constexpr int gemm_align_slack() { return RS ? 768 : 1024; }
+
 template <int BN, int STAGES, bool RS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -164,6 +173,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    if (static_cast<int>(smem - smem_raw) > gemm_align_slack<RS>()) {
+        // the launch reserved less slack than this base address needs: report instead of running past the end
+        if (threadIdx.x == 0) atomicCAS(p.status, 0, CAI_DEV_BAD_ARG);
+        return;
+    }
     uint8_t* sA = smem;
     uint8_t* sB = smem + STAGES * kAStageBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes);
@@ -398,45 +412,47 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 // the TMA engine as a bulk store over NVLink. The tile's arrival flag is raised one
                 // tile late, once the stores of that tile have completed, so that the wait for remote
                 // completion overlaps the next tile.
-                constexpr int kPitch = BN * 2 + 16;  // padded row pitch: conflict-free 16-byte lanes
-                uint8_t* stg = smem + STAGES * kStageBytes + 256 + q * 32 * kPitch;
+                uint8_t* stg = smem + STAGES * kStageBytes + 256 + q * 32 * kRsPitch;
                 const long long row = (long long)tm * kBM + q * 32 + lane;
                 const int blocks_per_rank = p.rows_per_rank / kBM;
                 const int owner = tm / blocks_per_rank;
-                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staging free again
-                __syncwarp();
+                const long long lrow = row - static_cast<long long>(owner) * p.rows_per_rank;
+                __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.pt.base[owner] + p.stage_off) +
+                                      (static_cast<long long>(p.pt.rank) * p.rows_per_rank + lrow) * p.N + tn * BN;
+                const float alpha = p.alpha;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t r[32];
-                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32;
-                    tmem_ld_32x32(taddr, r);
-                    tmem_ld_wait();
-                    const float alpha = p.alpha;
+                for (int h = 0; h < BN / kRsCols; ++h) {
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staging free again
+                    __syncwarp();
+#pragma unroll 1
+                    for (int c = 0; c < kRsCols / 32; ++c) {
+                        uint32_t r[32];
+                        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + h * kRsCols + c * 32;
+                        tmem_ld_32x32(taddr, r);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint4 o;
-                        o.x = pack_bf16(__uint_as_float(r[j * 8 + 0]) * alpha, __uint_as_float(r[j * 8 + 1]) * alpha);
-                        o.y = pack_bf16(__uint_as_float(r[j * 8 + 2]) * alpha, __uint_as_float(r[j * 8 + 3]) * alpha);
-                        o.z = pack_bf16(__uint_as_float(r[j * 8 + 4]) * alpha, __uint_as_float(r[j * 8 + 5]) * alpha);
-                        o.w = pack_bf16(__uint_as_float(r[j * 8 + 6]) * alpha, __uint_as_float(r[j * 8 + 7]) * alpha);
-                        *reinterpret_cast<uint4*>(stg + lane * kPitch + c * 64 + j * 16) = o;
+                        for (int j = 0; j < 4; ++j) {
+                            uint4 o;
+                            o.x = pack_bf16(__uint_as_float(r[j * 8 + 0]) * alpha, __uint_as_float(r[j * 8 + 1]) * alpha);
+                            o.y = pack_bf16(__uint_as_float(r[j * 8 + 2]) * alpha, __uint_as_float(r[j * 8 + 3]) * alpha);
+                            o.z = pack_bf16(__uint_as_float(r[j * 8 + 4]) * alpha, __uint_as_float(r[j * 8 + 5]) * alpha);
+                            o.w = pack_bf16(__uint_as_float(r[j * 8 + 6]) * alpha, __uint_as_float(r[j * 8 + 7]) * alpha);
+                            *reinterpret_cast<uint4*>(stg + lane * kRsPitch + c * 64 + j * 16) = o;
+                        }
                     }
+                    const bool last_half = h == BN / kRsCols - 1;
+                    if (last_half) tc_fence_before();
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (last_half && lane == 0) mbar_arrive(&tmem_empty[acc]);
+                    const int left = p.N - (tn * BN + h * kRsCols);
+                    const int cols = left < kRsCols ? left : kRsCols;
+                    if (cols > 0) bulk_store(drow + h * kRsCols, stg + lane * kRsPitch, static_cast<uint32_t>(cols) * 2);
+                    tma_store_commit();   // one (possibly empty) group per half
                 }
-                tc_fence_before();
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-                {
-                    const int col0 = tn * BN;
-                    const int cols = p.N - col0 < BN ? p.N - col0 : BN;
-                    const long long lrow = row - static_cast<long long>(owner) * p.rows_per_rank;
-                    __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.pt.base[owner] + p.stage_off) +
-                                          (static_cast<long long>(p.pt.rank) * p.rows_per_rank + lrow) * p.N + col0;
-                    if (cols > 0) bulk_store(drow, stg + lane * kPitch, static_cast<uint32_t>(cols) * 2);
-                    tma_store_commit();
-                }
-                // announce the previous tile: its stores (all but the newest group) have completed
-                asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
+                // announce the previous tile: its stores (all but this tile's groups) have completed
+                if constexpr (BN / kRsCols == 2) asm volatile("cp.async.bulk.wait_group 2;" ::: "memory");
+                else asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
                 fence_proxy_async_all();
                 bar_sync_epilogue();   // every lane's stores of the previous tile have completed
                 if (warp == 2 && lane == 0 && rs_prev_owner >= 0) {
@@ -527,7 +543,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
     if constexpr (RS) {
         // ---------------- reduce phase: sum the partials of all members for tiles of my rows
-        __shared__ int red_ok;
+        volatile int& red_ok = *reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars) + 192);
         __syncthreads();
         const int blocks_per_rank = p.rows_per_rank / kBM;
         const int items = blocks_per_rank * p.tiles_n;
@@ -605,7 +621,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 template <int BN, int STAGES, bool RS>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int sms,
                        cudaStream_t stream) {
-    constexpr int smem_bytes = STAGES * (kAStageBytes + BN * kBK * 2) + 1024 + 256 + (RS ? 4 * 32 * (BN * 2 + 16) : 0);
+    constexpr int smem_bytes = STAGES * (kAStageBytes + BN * kBK * 2) + gemm_align_slack<RS>() + 256 + (RS ? kRsStageBytes : 0);
+    static_assert(smem_bytes <= 232448, "shared memory per CTA");
     static bool configured[64] = {};
     const int dev = current_device();
     if (!configured[dev & 63]) {
@@ -669,8 +686,8 @@ static int gemm_dispatch(const void* A, const void* B, long long lda, long long 
     if (!ok) return CAI_K_BAD_ARG;
     p.status = status_words(dev);
     if (p.mode == kGemmReduceScatter) {
-        if (BN == 256) return launch_gemm<256, 3, true>(tmA, tmB, p, sms, st);
-        return launch_gemm<128, 5, true>(tmA, tmB, p, sms, st);
+        if (BN == 256) return launch_gemm<256, 4, true>(tmA, tmB, p, sms, st);
+        return launch_gemm<128, 6, true>(tmA, tmB, p, sms, st);
     }
     if (BN == 256) return launch_gemm<256, 4, false>(tmA, tmB, p, sms, st);
     return launch_gemm<128, 6, false>(tmA, tmB, p, sms, st);

@@ -214,3 +214,22 @@ def test_host_code_is_clean_under_address_and_ub_sanitizers():
     out = r.stdout + r.stderr
     assert r.returncode == 0, out[-3000:]
     assert "0 failures" in out and "runtime error" not in out and "AddressSanitizer" not in out, out[-3000:]
+
+
+def test_benchmark_configs_compile_for_every_gpu_count(tmp_path):
+    """The configs bench.py runs (headline config at tp = 1, 2, 4, 8 and the other named configs on 8 GPUs)
+    compile into executable plans; the reference arm reports itself unavailable and exits 0."""
+    import json
+    import sys
+    sys.path.insert(0, str(ROOT))
+    import bench
+    from cai_b200 import plan
+    for n in (1, 2, 4, 8):
+        for comm in ("fused", "baseline"):
+            plan.compile_plans(bench.config_text(n, comm, "tp8"), tmp_path / f"tp{n}{comm}", ranks=(0, 1), version=2, text=True)
+    for name in ("moe_ep8", "fsdp8b", "pp2tp4"):
+        plan.compile_plans(bench.config_text(8, "fused", name), tmp_path / name, ranks=(0, 1), version=2, text=True)
+    r = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line
