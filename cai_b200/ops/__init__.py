@@ -184,12 +184,14 @@ def adamw_(master, m, v, grad, param, step, lr, beta1=0.9, beta2=0.999, eps=1e-8
                           float(eps), float(wd), float(grad_scale), int(step), _stream()), "adamw")
 
 
-def flash_attn_fwd(qkv, B, S, nh, nkv, hd, scale=None):
+def flash_attn_fwd(qkv, B, S, nh, nkv, hd, scale=None, variant=0):
+    """Causal GQA flash attention forward over packed ``qkv`` ``[B*S, (nh + 2 nkv) * hd]``. ``variant``: 0 = chosen
+    from the grid size, 1 = one query tile per CTA (score MMA a block ahead), 2 = two tiles per CTA in ping-pong."""
     assert qkv.dtype == torch.bfloat16 and qkv.is_contiguous()
     scale = hd ** -0.5 if scale is None else scale
     out = torch.empty((B * S, nh * hd), device=qkv.device, dtype=torch.bfloat16)
     lse = torch.empty((B, nh, S), device=qkv.device, dtype=torch.float32)
-    check(lib().cai_flash_attn_fwd(_p(qkv), _p(out), _p(lse), B, S, nh, nkv, hd, float(scale), _stream()),
+    check(lib().cai_flash_attn_fwd_variant(_p(qkv), _p(out), _p(lse), B, S, nh, nkv, hd, float(scale), int(variant), _stream()),
           "flash_attn_fwd")
     return out, lse
 

@@ -67,6 +67,7 @@ def _declare(L):
     L.cai_l2_flush.argtypes = [P, LL, P]
     if hasattr(L, "cai_flash_attn_fwd"):
         L.cai_flash_attn_fwd.argtypes = [P, P, P, I, I, I, I, I, F, P]
+        L.cai_flash_attn_fwd_variant.argtypes = [P, P, P, I, I, I, I, I, F, I, P]
     if hasattr(L, "cai_flash_attn_bwd"):
         L.cai_flash_attn_bwd.argtypes = [P, P, P, P, P, P, I, I, I, I, I, F, P]
 

@@ -69,6 +69,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--variant", type=int, default=0, help="attn_fwd: 0 auto, 1 one tile per CTA, 2 two tiles per CTA")
     a = ap.parse_args(argv)
     dev = "cuda"
     bf = torch.bfloat16
@@ -97,7 +98,7 @@ def main(argv=None):
         o, lse = flash_attn_fwd(qkv, a.batch, a.seq, a.heads, a.kv_heads, hd)
         causal_flops = 4.0 * a.batch * a.heads * a.seq * a.seq * hd / 2
         if a.kernel == "attn_fwd":
-            ms = timeit(lambda: flash_attn_fwd(qkv, a.batch, a.seq, a.heads, a.kv_heads, hd), a.iters, a.warmup, flush)
+            ms = timeit(lambda: flash_attn_fwd(qkv, a.batch, a.seq, a.heads, a.kv_heads, hd, variant=a.variant), a.iters, a.warmup, flush)
             flops = causal_flops
         else:
             do = torch.randn_like(o)

@@ -152,6 +152,10 @@ CAI_API int cai_l2_flush(void* scratch, long long bytes, void* stream);
  * lse is f32 [B, nh, S]. */
 CAI_API int cai_flash_attn_fwd(const void* qkv, void* out, float* lse, int B, int S, int nh, int nkv, int hd,
                                float scale, void* stream);
+/* force_variant: 0 = chosen from the grid size, 1 = one query tile per CTA with the score MMA a block ahead,
+ * 2 = two query tiles per CTA in ping-pong. */
+CAI_API int cai_flash_attn_fwd_variant(const void* qkv, void* out, float* lse, int B, int S, int nh, int nkv, int hd,
+                                       float scale, int force_variant, void* stream);
 /* dqkv packed like qkv. delta is scratch f32 [B, nh, S]. */
 CAI_API int cai_flash_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
                                void* dqkv, int B, int S, int nh, int nkv, int hd, float scale, void* stream);

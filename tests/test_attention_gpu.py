@@ -23,12 +23,13 @@ def _ref_attention(qkv, B, S, nh, nkv, hd):
 
 @pytest.mark.parametrize("B,S,nh,nkv", [(1, 128, 2, 2), (2, 256, 4, 2), (1, 384, 4, 1), (1, 1024, 8, 2),
                                         (2, 2048, 4, 4)])
-def test_flash_attn_fwd(B, S, nh, nkv):
+@pytest.mark.parametrize("variant", [1, 2])
+def test_flash_attn_fwd(B, S, nh, nkv, variant):
     from cai_b200 import ops
     torch.manual_seed(0)
     hd = 128
     qkv = torch.randn(B * S, (nh + 2 * nkv) * hd, device="cuda").to(torch.bfloat16)
-    out, lse = ops.flash_attn_fwd(qkv, B, S, nh, nkv, hd)
+    out, lse = ops.flash_attn_fwd(qkv, B, S, nh, nkv, hd, variant=variant)
     ref, lse_ref = _ref_attention(qkv, B, S, nh, nkv, hd)
     rel = ((out.float() - ref).norm() / ref.norm()).item()
     assert rel < 1e-2, rel
