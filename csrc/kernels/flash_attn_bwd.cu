@@ -34,6 +34,10 @@ struct AttnBwdParams {
     const float* delta;
     __nv_bfloat16* dqkv;
     int* status;
+    // dK / dV with one CTA per QUERY head (small grids): the heads of a kv group take turns adding their
+    // contribution to the group's dK / dV rows; chain[b][g][kv tile] counts the heads that are done.
+    int split_heads;
+    unsigned int* chain;
 };
 
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
@@ -78,6 +82,26 @@ __device__ __forceinline__ void store_acc_bf16(uint32_t tacc, __nv_bfloat16* dst
     }
 }
 
+// The same, added to what the rows already hold (bf16 read-modify-write).
+__device__ __forceinline__ void add_acc_bf16(uint32_t tacc, __nv_bfloat16* dst_row) {
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tacc + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+            const uint4 old = *reinterpret_cast<const uint4*>(dst_row + c * 32 + j4 * 8);
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(v[j4 * 8 + 0]) + bf16_lo(old.x), __uint_as_float(v[j4 * 8 + 1]) + bf16_hi(old.x));
+            o.y = pack_bf16(__uint_as_float(v[j4 * 8 + 2]) + bf16_lo(old.y), __uint_as_float(v[j4 * 8 + 3]) + bf16_hi(old.y));
+            o.z = pack_bf16(__uint_as_float(v[j4 * 8 + 4]) + bf16_lo(old.z), __uint_as_float(v[j4 * 8 + 5]) + bf16_hi(old.z));
+            o.w = pack_bf16(__uint_as_float(v[j4 * 8 + 6]) + bf16_lo(old.w), __uint_as_float(v[j4 * 8 + 7]) + bf16_hi(old.w));
+            *reinterpret_cast<uint4*>(dst_row + c * 32 + j4 * 8) = o;
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------- dK / dV
 __global__ void __launch_bounds__(kAttnBwdThreads, 1)
 attn_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
@@ -105,11 +129,15 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
     const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
     const int heads_all = gridDim.y * gridDim.z;
     const int j = lin / heads_all;  // kv tile
-    const int g = (lin % heads_all) % gridDim.y, b = (lin % heads_all) / gridDim.y;
+    const int ysel = (lin % heads_all) % gridDim.y, b = (lin % heads_all) / gridDim.y;
     const int rep = p.nh / p.nkv;
+    // grid.y is kv groups (a CTA sweeps the group's query heads) or, with split_heads, query heads
+    const int g = p.split_heads ? ysel / rep : ysel;
+    const int h_first = p.split_heads ? ysel : g * rep;
+    const int turn = p.split_heads ? ysel - g * rep : 0;   // my place in the group's accumulation chain
     const int nq = p.S / kAttnTile;
     const int per_head = nq - j;          // query tiles at or below the diagonal
-    const int iters = rep * per_head;
+    const int iters = (p.split_heads ? 1 : rep) * per_head;
     const int row_base = b * p.S;
     const int col_k = (p.nh + g) * kAttnHD, col_v = (p.nh + p.nkv + g) * kAttnHD;
 
@@ -149,7 +177,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
             for (int it = 0; it < iters && ok; ++it) {
                 const int slot = it & 1;
                 const uint32_t ph = (it >> 1) & 1;
-                const int h = g * rep + it / per_head;
+                const int h = h_first + it / per_head;
                 const int q_row = row_base + (j + it % per_head) * kAttnTile;
                 if (!mbar_wait(&qdo_empty[slot], ph ^ 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
                 mbar_expect_tx(&qdo_full[slot], 2 * kAttnTileBytes);
@@ -191,7 +219,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
         const uint32_t lane_bits = static_cast<uint32_t>((warp & 3) * 32) << 16;
         bool ok = true;
         for (int it = 0; it < iters; ++it) {
-            const int h = g * rep + it / per_head;
+            const int h = h_first + it / per_head;
             const int i = j + it % per_head;
             const int buf = it & 1;
             const long long vec = (static_cast<long long>(b) * p.nh + h) * p.S + i * kAttnTile + r;
@@ -246,8 +274,34 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
             tc_fence_after();
             const long long grow = static_cast<long long>(row_base) + j * kAttnTile + r;
             const long long ld = static_cast<long long>(p.nh + 2 * p.nkv) * kAttnHD;
-            if (half == 0) store_acc_bf16(tdK + lane_bits, p.dqkv + grow * ld + col_k);
-            else store_acc_bf16(tdV + lane_bits, p.dqkv + grow * ld + col_v);
+            __nv_bfloat16* dst = p.dqkv + grow * ld + (half == 0 ? col_k : col_v);
+            const uint32_t tacc = (half == 0 ? tdK : tdV) + lane_bits;
+            if (!p.split_heads) {
+                store_acc_bf16(tacc, dst);
+            } else {
+                // heads of the group add in turn: wait (bounded) until the heads before me are done
+                unsigned int* cnt = p.chain + (static_cast<long long>(b) * p.nkv + g) * nq + j;
+                bool go = true;
+                if (turn > 0) {
+                    go = false;
+                    for (uint32_t spin = 0; spin < kSpinLimit && !go; ++spin) {
+                        unsigned int v;
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+                        go = v >= static_cast<unsigned int>(turn);
+                        if (!go && spin > 16) __nanosleep(200);
+                    }
+                    if (!go) atomicCAS(p.status, 0, CAI_DEV_TIMEOUT_ATTN);
+                }
+                if (go) {
+                    if (turn == 0) store_acc_bf16(tacc, dst);
+                    else add_acc_bf16(tacc, dst);
+                }
+                __threadfence();
+                bar_sync_compute();
+                if (threadIdx.x == 128) {   // first compute thread: everyone's rows are written and fenced
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(cnt), "r"(static_cast<unsigned int>(turn + 1)) : "memory");
+                }
+            }
         }
     }
 
@@ -464,7 +518,30 @@ CAI_API int cai_flash_attn_bwd_parts(const void* qkv, const void* out, const voi
     p.dqkv = static_cast<__nv_bfloat16*>(dqkv);
     p.status = status_words(dev);
     const int nq = S / kAttnTile;
-    if (parts & 2) attn_dkdv_kernel<<<dim3(nq, nkv, B), kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_do, p);
+    // Few kv groups per GPU (tensor parallelism): one CTA per query head instead of per kv group shortens the
+    // longest CTA by the group size; the heads of a group then add into dK / dV in turn (chain counters).
+    p.split_heads = 0;
+    p.chain = nullptr;
+    if ((parts & 2) && nh > nkv && static_cast<long long>(nq) * nkv * B < sm_count(dev)) {
+        static unsigned int* chain_buf[64] = {};
+        static size_t chain_cap[64] = {};
+        const size_t need = static_cast<size_t>(B) * nkv * nq;
+        if (chain_cap[dev & 63] < need) {
+            if (chain_buf[dev & 63]) cudaFree(chain_buf[dev & 63]);
+            chain_buf[dev & 63] = nullptr;
+            chain_cap[dev & 63] = 0;
+            if (cudaMalloc(&chain_buf[dev & 63], need * sizeof(unsigned int)) != cudaSuccess) {
+                set_last_error("attn_bwd: cannot allocate the chain counters");
+                return CAI_K_CUDA;
+            }
+            chain_cap[dev & 63] = need;
+        }
+        if (cudaMemsetAsync(chain_buf[dev & 63], 0, need * sizeof(unsigned int), st) != cudaSuccess) return CAI_K_CUDA;
+        p.split_heads = 1;
+        p.chain = chain_buf[dev & 63];
+    }
+    if (parts & 2)
+        attn_dkdv_kernel<<<dim3(nq, p.split_heads ? nh : nkv, B), kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_do, p);
     if (parts & 4) attn_dq_kernel<<<dim3(nq, nh, B), kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_do, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
