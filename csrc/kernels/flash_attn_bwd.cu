@@ -40,6 +40,10 @@ struct AttnBwdParams {
     unsigned int* chain;
 };
 
+// chain counters of the head-split dK / dV kernel: one per (batch, kv group, kv tile)
+constexpr size_t kAttnChainSlots = 65536;
+__device__ unsigned int g_attn_chain[kAttnChainSlots];
+
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
                                   float* __restrict__ delta, int B, int S, int nh) {
     const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -522,23 +526,19 @@ CAI_API int cai_flash_attn_bwd_parts(const void* qkv, const void* out, const voi
     // longest CTA by the group size; the heads of a group then add into dK / dV in turn (chain counters).
     p.split_heads = 0;
     p.chain = nullptr;
-    if ((parts & 2) && nh > nkv && static_cast<long long>(nq) * nkv * B < sm_count(dev)) {
-        static unsigned int* chain_buf[64] = {};
-        static size_t chain_cap[64] = {};
-        const size_t need = static_cast<size_t>(B) * nkv * nq;
-        if (chain_cap[dev & 63] < need) {
-            if (chain_buf[dev & 63]) cudaFree(chain_buf[dev & 63]);
-            chain_buf[dev & 63] = nullptr;
-            chain_cap[dev & 63] = 0;
-            if (cudaMalloc(&chain_buf[dev & 63], need * sizeof(unsigned int)) != cudaSuccess) {
-                set_last_error("attn_bwd: cannot allocate the chain counters");
-                return CAI_K_CUDA;
-            }
-            chain_cap[dev & 63] = need;
+    const size_t need = static_cast<size_t>(B) * nkv * nq;
+    if ((parts & 2) && nh > nkv && static_cast<long long>(nq) * nkv * B < sm_count(dev) && need <= kAttnChainSlots) {
+        // the counters live in a device array of the library: nothing is allocated on this path, so the call
+        // can sit inside a stream capture from its first use
+        static unsigned int* chain_ptr[64] = {};
+        if (!chain_ptr[dev & 63] &&
+            cudaGetSymbolAddress(reinterpret_cast<void**>(&chain_ptr[dev & 63]), g_attn_chain) != cudaSuccess) {
+            set_last_error("attn_bwd: cannot resolve the chain counters");
+            return CAI_K_CUDA;
         }
-        if (cudaMemsetAsync(chain_buf[dev & 63], 0, need * sizeof(unsigned int), st) != cudaSuccess) return CAI_K_CUDA;
+        if (cudaMemsetAsync(chain_ptr[dev & 63], 0, need * sizeof(unsigned int), st) != cudaSuccess) return CAI_K_CUDA;
         p.split_heads = 1;
-        p.chain = chain_buf[dev & 63];
+        p.chain = chain_ptr[dev & 63];
     }
     if (parts & 2)
         attn_dkdv_kernel<<<dim3(nq, p.split_heads ? nh : nkv, B), kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_do, p);
