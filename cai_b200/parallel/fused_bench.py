@@ -19,10 +19,9 @@ import ctypes
 import json
 import os
 import statistics
+import sys
 from ctypes import c_int, c_longlong, c_uint32, c_ulonglong, c_void_p
 from pathlib import Path
-
-import sys
 
 import torch
 import torch.distributed as dist
@@ -33,6 +32,7 @@ if str(ROOT) not in sys.path:
 
 from cai_b200.ops import _lib as klib  # noqa: E402
 from cai_b200.ops import gemm  # noqa: E402
+
 GROUP_TP = 0
 NVLINK_GBS = 770.0   # measured peer copy bandwidth per direction per GPU on this pool
 
