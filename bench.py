@@ -235,14 +235,149 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+REF_SPEC = {"vocab": 64, "seq": 32, "hidden": 64, "layers": 2, "heads": 4, "head_dim": 16, "ffn": 128, "batch_per_rank": 16}
+REF_ID_FILES = ("/tmp/cai_nccl_dp_0.id",)   # the reference's NCCL bootstrap file for pure data parallel; it never deletes it
+
+
+def _run_gpu_trainer(exe, steps, timeout_s):
+    """Run the reference's gpu_trainer (its stock main) with stdout on a pseudo-terminal, so that its per-step
+    `step N  loss X` lines arrive when they are printed (each follows the step's device->host loss read), and
+    return [(step, seconds since launch, loss)], the exit code and the tail of its stderr."""
+    import pty
+    import re
+    import select
+    master, slave = pty.openpty()
+    t0 = time.perf_counter()
+    proc = subprocess.Popen([str(exe), "--steps", str(steps), "--batch", str(REF_SPEC["batch_per_rank"])],
+                            stdout=slave, stderr=subprocess.PIPE, stdin=subprocess.DEVNULL)
+    os.close(slave)
+    pat = re.compile(rb"step\s+(\d+)\s+loss\s+(\S+)")
+    lines, buf = [], b""
+    deadline = t0 + timeout_s
+    while True:
+        if time.perf_counter() > deadline:
+            proc.kill()          # our own child, by handle
+            break
+        r, _, _ = select.select([master], [], [], 0.2)
+        if r:
+            try:
+                chunk = os.read(master, 65536)
+            except OSError:
+                chunk = b""
+            now = time.perf_counter() - t0
+            if not chunk:
+                break
+            buf += chunk
+            while b"\n" in buf:
+                line, buf = buf.split(b"\n", 1)
+                m = pat.search(line)
+                if m:
+                    try:
+                        lines.append((int(m.group(1)), now, float(m.group(2))))
+                    except ValueError:
+                        lines.append((int(m.group(1)), now, float("nan")))
+        elif proc.poll() is not None:
+            break
+    rc = proc.wait()
+    err = proc.stderr.read().decode(errors="replace")[-400:] if proc.stderr else ""
+    os.close(master)
+    return lines, rc, err
+
+
 def run_reference(args):
-    # The reference is a C11 project without Python packaging; `pip install` of it fails (no
-    # setup.py / pyproject). Its only GPU executable, gpu_trainer, runs a hard-coded 88k-parameter
-    # toy model in pure data parallel and cannot express this model (no GQA, RoPE, TP, vocab 32000).
-    if int(os.environ.get("RANK", 0)) == 0:
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "reference is a C project with no Python package (pip install fails: no setup.py/pyproject); "
-                          "its only GPU binary runs a hard-coded toy model and cannot run this config"}), flush=True)
+    """The reference arm: the UNMODIFIED reference, built by its own Makefile (`make CUDA=1 NCCL=1`, see
+    cai_b200/_build.py:build_reference), run through its stock GPU entry point tools/gpu_trainer.c. That
+    executable trains a hard-coded 88k-parameter model (vocab 64, seq 32, hidden 64, 2 layers, MHA 4 x 16, ffn
+    128) in pure data parallel with naive fp32 kernels; it has no way to run the headline model (no GQA, RoPE,
+    tensor-parallel split or vocabulary of 32000: tools/gpu_trainer.c:38-46), so the line says
+    `same_config: false`. Its step already copies the batch host->device and the per-row losses device->host
+    (src/cuda/cai_gpu_train.cu:273-293), so the one measurement is end to end."""
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+
+    def say(obj):
+        if rank == 0:
+            obj = {"impl": "reference", **obj}
+            print(json.dumps(obj), flush=True)
+
+    exe = ROOT / "baseline" / "_ref" / "bin" / "gpu_trainer"
+    if not exe.exists() and rank == 0:
+        try:
+            from cai_b200 import _build
+            _build.build_reference()
+        except Exception:
+            pass
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group(backend="gloo", rank=rank, world_size=world)   # host-side barrier of this harness only
+        dist.barrier()
+    if not exe.exists():
+        log = ROOT / "baseline" / "_ref" / "BUILD_LOG.txt"
+        why = log.read_text().strip().splitlines()[-1][:160] if log.exists() else "no build log"
+        say({"unavailable": f"reference gpu_trainer could not be built here (make CUDA=1 NCCL=1): {why}"})
+        return
+    K, W = args.steps, max(args.warmup, 3)
+    if rank == 0:
+        for f in REF_ID_FILES:      # a stale id file makes the other ranks join a communicator that no longer exists
+            try:
+                os.unlink(f)
+            except OSError:
+                pass
+    if dist:
+        dist.barrier()
+    sampler = ClockSampler(os.path.join(tempfile.gettempdir(), f"cai_ref_clocks_n{world}_{os.getpid()}.csv")) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    lines, rc, err = _run_gpu_trainer(exe, W + K, timeout_s=600)
+    clocks = sampler.stop(gpu_index=int(os.environ.get("LOCAL_RANK", 0))) if sampler else None
+    ok = rc == 0 and len(lines) >= 2
+    # steps are printed every max(1, (W+K)//20) steps: the timed span starts at the first line at or past the
+    # warm-up and ends at the last one
+    span = [l for l in lines if l[0] >= W - 1]
+    if ok and len(span) >= 2:
+        n_steps = span[-1][0] - span[0][0]
+        ms = (span[-1][1] - span[0][1]) * 1e3 / n_steps
+    else:
+        ok, n_steps, ms = False, 0, 0.0
+    if dist:
+        import torch
+        t = torch.tensor([ms if ok else -1.0], dtype=torch.float64)
+        lo = t.clone()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        if rank == 0:       # only rank 0 of the reference prints steps; the others report -1 and are ignored
+            ms = float(t.item())
+        dist.barrier()
+        if rank == 0:
+            for f in REF_ID_FILES:
+                try:
+                    os.unlink(f)
+                except OSError:
+                    pass
+        dist.destroy_process_group()
+    if not ok:
+        say({"unavailable": f"reference gpu_trainer exited {rc} after {len(lines)} step lines: {err.strip()[-200:]}"})
+        return
+    bt = REF_SPEC["batch_per_rank"] * REF_SPEC["seq"]
+    tokens = bt * world
+    value = tokens / (ms * 1e-3)
+    say({
+        "metric": "tokens/s (whole job), training step of the reference's gpu_trainer, timed from its own step lines",
+        "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "steps_timed": n_steps,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp32", "data": "synthetic (the reference's own xorshift token stream), its own random init",
+        "same_config": False,
+        "config": {"model": "reference's hard-coded model: 2L h64 4x16 heads ffn128 V64 seq32 (88,384 parameters); it cannot "
+                            "run the headline model", "global_batch": REF_SPEC["batch_per_rank"] * world,
+                   "seq_len": REF_SPEC["seq"], "parallelism": f"dp{world}",
+                   "timing": "wall clock between the executable's step lines (each printed after the step's loss reached the host)"},
+        "loss_first": lines[0][2], "loss_last": lines[-1][2],
+        "clocks": clocks,
+        "e2e": {"value": value, "unit": "tokens/s", "ms_per_step": ms, "h2d_bytes_per_step": 2 * bt * 4, "d2h_bytes_per_step": bt * 4},
+    })
 
 
 def main():

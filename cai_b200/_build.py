@@ -132,9 +132,61 @@ def build_sanitized_selftest(verbose=False) -> Path:
     return out
 
 
+REFERENCE_SRC = Path(os.environ.get("CAI_REFERENCE_SRC", "/root/reference"))
+REFERENCE_OUT = ROOT / "baseline" / "_ref"
+
+
+def build_reference(verbose=False):
+    """Build the UNMODIFIED reference project (its own Makefile, ``make CUDA=1 NCCL=1``) from a scratch copy of its
+    source tree and keep its executables under ``baseline/_ref/bin`` for the reference arm of ``bench.py``.
+
+    Nothing of the reference's source is edited: its Makefile as shipped lacks ``-Isrc/cuda`` for
+    ``tools/gpu_trainer.c`` and a library path for ``-lcudart``, both of which the Makefile lets the environment
+    supply (``CFLAGS ?=``, ``LDLIBS +=``); ``NVCCFLAGS ?=`` gets an sm_100 code object so the box does not have
+    to JIT the default PTX. Returns the path of ``gpu_trainer`` or None (with the reason in
+    ``baseline/_ref/BUILD_LOG.txt``) when the source tree or the toolchain is missing."""
+    out_bin = REFERENCE_OUT / "bin"
+    exe = out_bin / "gpu_trainer"
+    log = REFERENCE_OUT / "BUILD_LOG.txt"
+    if exe.exists():
+        return exe
+    REFERENCE_OUT.mkdir(parents=True, exist_ok=True)
+    if not (REFERENCE_SRC / "Makefile").exists():
+        log.write_text(f"reference source tree not found at {REFERENCE_SRC}\n")
+        return None
+    import tempfile
+    with tempfile.TemporaryDirectory(prefix="cai_ref_build_") as tmp:
+        work = Path(tmp) / "cai"
+        shutil.copytree(REFERENCE_SRC, work)
+        cuda_home = Path(NVCC).resolve().parent.parent
+        env = dict(os.environ)
+        env["PATH"] = f"{cuda_home / 'bin'}:{env.get('PATH', '')}"
+        env["CFLAGS"] = "-std=c11 -O2 -g -Isrc/cuda"
+        env["LDLIBS"] = f"-L{cuda_home / 'lib64'}"
+        env["NVCCFLAGS"] = "-O2 -std=c++14 -Iinclude -Isrc -gencode arch=compute_100,code=sm_100"
+        r = subprocess.run(["make", "-C", str(work), "CUDA=1", "NCCL=1", "bin/gpu_trainer", "bin/trainer",
+                            "bin/plan_compiler"], env=env, capture_output=True, text=True)
+        log.write_text(f"$ make CUDA=1 NCCL=1 (CFLAGS/LDLIBS/NVCCFLAGS from the environment, source untouched)\n"
+                       f"exit {r.returncode}\n{r.stdout[-4000:]}\n{r.stderr[-4000:]}\n")
+        if verbose:
+            print(log.read_text())
+        if r.returncode != 0 or not (work / "bin" / "gpu_trainer").exists():
+            return None
+        out_bin.mkdir(parents=True, exist_ok=True)
+        for name in ("gpu_trainer", "trainer", "plan_compiler"):
+            if (work / "bin" / name).exists():
+                shutil.copy2(work / "bin" / name, out_bin / name)
+    return exe
+
+
 def build_all(verbose=False):
     host = build_host(verbose)
     kern = build_kernels(verbose)
+    try:
+        build_reference(verbose)   # the comparison arm of bench.py; its absence never fails the product build
+    except Exception as e:  # noqa: BLE001
+        REFERENCE_OUT.mkdir(parents=True, exist_ok=True)
+        (REFERENCE_OUT / "BUILD_LOG.txt").write_text(f"reference build raised: {e}\n")
     return host, kern
 
 

@@ -32,7 +32,7 @@ KERNEL_NAMES = ["none", "embed_fwd", "embed_bwd", "rmsnorm_fwd", "rmsnorm_bwd", 
                 "nccl_all_gather", "nccl_all_to_all", "nccl_send", "nccl_recv", "gemm_rs", "ag_gemm", "rs_adamw",
                 "fsdp_ag_gemm", "moe_route", "moe_dispatch_gemm", "moe_gemm_combine", "load_tokens", "add",
                 "cross_entropy_tp", "quant_fp8", "gemm_fp8"]
-K_GEMM, K_FSDP_AG_GEMM, K_QUANT_FP8, K_GEMM_FP8 = 5, 23, 30, 31
+K_GEMM, K_GEMM_RS, K_AG_GEMM, K_RS_ADAMW, K_FSDP_AG_GEMM, K_QUANT_FP8, K_GEMM_FP8 = 5, 20, 21, 22, 23, 30, 31
 OP_EVENT_RECORD, OP_EVENT_WAIT = 13, 14
 
 
@@ -83,7 +83,8 @@ class TrainSpec(Structure):
                 ("weight_decay", c_float), ("rope_theta", c_float), ("norm_eps", c_float), ("init_std", c_float),
                 ("seed", c_uint32), ("tie_embeddings", c_uint32), ("zero_stage", c_uint32), ("fp8_block", c_uint32),
                 ("comm_mode", c_uint32), ("ce_chunk", c_uint32), ("moe_capacity_factor_x100", c_uint32),
-                ("reserved", c_uint32)]
+                ("wgrad_overlap", c_uint32), ("mb_group", c_uint32), ("fuse_swiglu", c_uint32), ("dp_buckets", c_uint32),
+                ("wait_limit_ms", c_uint32), ("reserved", c_uint32 * 4)]
 
 
 class ExecHeader(Structure):
@@ -101,7 +102,7 @@ class NamedTensor(Structure):
 
 
 assert ctypes.sizeof(PlanHeader) == 128 and ctypes.sizeof(Op) == 32 and ctypes.sizeof(TensorDesc) == 24
-assert ctypes.sizeof(Topology) == 64 and ctypes.sizeof(ModelSpec) == 96 and ctypes.sizeof(TrainSpec) == 64
+assert ctypes.sizeof(Topology) == 64 and ctypes.sizeof(ModelSpec) == 96 and ctypes.sizeof(TrainSpec) == 96
 assert ctypes.sizeof(ExecOp) == 64 and ctypes.sizeof(NamedTensor) == 64 and ctypes.sizeof(ExecHeader) == 32
 
 

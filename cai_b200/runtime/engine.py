@@ -142,12 +142,12 @@ class Engine:
         self.step_count = 0
         self.lr = float(self.train.lr)
         self._init_comms()
-        ga, T = self.hdr.num_microbatches, self.model.microbatch * self.model.seq_len
         self.tokens_dev = self.view("@tokens")
         self.targets_dev = self.view("@targets")
         self.loss_dev = self.view("@loss")
         self.loss_host = torch.zeros(8, dtype=torch.float32).pin_memory()
-        self.batch_rows, self.batch_cols = ga, T
+        # one row per launch of the schedule (the compiler may launch several microbatches together)
+        self.batch_rows, self.batch_cols = int(self.tokens_dev.shape[0]), int(self.tokens_dev.shape[1])
         with torch.cuda.stream(self.stream):
             klib.check(L.cai_rope_table(c_void_p(self.view("@rope_table").data_ptr()), self.model.seq_len,
                                         self.model.head_dim, float(self.train.rope_theta),

@@ -53,6 +53,8 @@ const Key kKeys[] = {
     XKEY("seed", seed, F_U32), XKEY("tie_embeddings", tie_embeddings, F_U32), XKEY("zero_stage", zero_stage, F_U32), XKEY("wgrad_overlap", wgrad_overlap, F_U32),
     XKEY("fp8_block", fp8_block, F_U32), XKEY("comm", comm_mode, F_COMM), XKEY("ce_chunk", ce_chunk, F_U32),
     XKEY("moe_capacity_factor", moe_capacity_factor_x100, F_F32),
+    XKEY("mb_group", mb_group, F_U32), XKEY("fuse_swiglu", fuse_swiglu, F_U32), XKEY("dp_buckets", dp_buckets, F_U32),
+    XKEY("wait_limit_ms", wait_limit_ms, F_U32),
 };
 
 std::string trimmed(const std::string& s) {

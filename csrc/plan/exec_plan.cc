@@ -392,6 +392,18 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         return failf(err, ERR_INVALID, "tp=%u must divide heads, kv heads, ffn and vocab", d.tp);
     if ((m.microbatch * m.seq_len) % d.tp || m.seq_len % 128)
         return failf(err, ERR_INVALID, "tokens per microbatch must divide by tp and seq_len by 128");
+    // Microbatches launched together (TrainSpec::mb_group). A pipeline keeps the configured granularity (fewer,
+    // larger microbatches would widen its bubble); the per-tile signal slots of the fused TP kernels bound the rows.
+    uint32_t mb_group = cfg.train.mb_group;
+    if (mb_group == 0) mb_group = (d.tp > 1 && d.pp == 1 && !moe && d.num_microbatches % 2 == 0) ? 2 : 1;
+    if (mb_group > 1) {
+        if (d.pp != 1) return failf(err, ERR_INVALID, "mb_group > 1 needs pp = 1 (got pp=%u)", d.pp);
+        if (d.num_microbatches % mb_group) return failf(err, ERR_INVALID, "mb_group=%u must divide grad_accum=%u", mb_group, d.num_microbatches);
+        const uint64_t rows = static_cast<uint64_t>(mb_group) * m.microbatch * m.seq_len;
+        if (rows / 128 > kSigLocalSlots || (d.tp > 1 && (rows / d.tp / 128) * ((m.hidden_size + 127) / 128) > kSigTileSlots))
+            return failf(err, ERR_INVALID, "mb_group=%u: %llu rows per launch exceed the signal slots of the fused kernels", mb_group,
+                         static_cast<unsigned long long>(rows));
+    }
     if ((m.vocab_size / d.tp) % 8 || m.hidden_size % 8 || (m.ffn_hidden / d.tp) % 8)
         return failf(err, ERR_INVALID, "local hidden / ffn / vocab sizes must be multiples of 8");
 
@@ -409,11 +421,11 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     b.Cqkv = (b.nh_l + 2 * b.nkv_l) * b.hd;
     b.F_l = m.ffn_hidden / d.tp;
     b.V_l = m.vocab_size / d.tp;
-    b.seq = m.seq_len; b.mbsz = m.microbatch;
-    b.T = m.microbatch * m.seq_len;
+    b.seq = m.seq_len; b.mbsz = m.microbatch * mb_group;
+    b.T = b.mbsz * m.seq_len;
     b.Tl = b.T / d.tp;
     b.layers = h.layers_in_stage;
-    const uint32_t H = b.H, T = b.T, Tl = b.Tl, tp = b.tp, ga = d.num_microbatches;
+    const uint32_t H = b.H, T = b.T, Tl = b.Tl, tp = b.tp, ga = d.num_microbatches / mb_group;   // launches per step
     const float istd = cfg.train.init_std;
 
     // ---------------- parameters (flat space)

@@ -155,7 +155,15 @@ struct cai_exec {
     uint32_t epochs_per_step = 2;
     int ag_copy_ctas = 0;   // 0: chosen per launch from the GEMM's tile count
     float* hyper_dev = nullptr;   // 8 floats
-    float* hyper_host = nullptr;  // pinned
+    // Pinned staging of the per-step scalars. A pinned host-to-device copy reads host memory when it executes,
+    // not when it is enqueued, so a caller that enqueues several steps without synchronising must not find
+    // the words of step N overwritten by step N+1: a ring of slots, each reused only after the copy that read
+    // it has completed (its event), keeps every enqueued step's scalars intact.
+    static constexpr int kHyperSlots = 16;
+    float* hyper_host = nullptr;  // pinned, kHyperSlots x 8 floats
+    cudaEvent_t hyper_ev[kHyperSlots] = {};
+    bool hyper_used[kHyperSlots] = {};
+    unsigned hyper_next = 0;
     cudaGraphExec_t graph = nullptr;
     bool use_graph = false;
     bool trace_on = false;
@@ -523,9 +531,22 @@ CAI_API int cai_exec_create(cai_exec** out, const void* plan_bytes, size_t nbyte
     cudaEventCreateWithFlags(&ex->fork_ev, cudaEventDisableTiming);
     ex->events.resize(ex->hdr.num_events);
     for (cudaEvent_t& e : ex->events) cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
-    cudaMalloc(&ex->hyper_dev, 8 * sizeof(float));
-    cudaMalloc(&ex->counters_dev, 256 * sizeof(unsigned int));
-    cudaMemset(ex->counters_dev, 0, 256 * sizeof(unsigned int));
+    bool dev_ok = true;
+    for (int s = 0; s < ST_COUNT; ++s) dev_ok = dev_ok && ex->join_ev[s] != nullptr;
+    dev_ok = dev_ok && ex->fork_ev != nullptr;
+    for (cudaEvent_t e : ex->events) dev_ok = dev_ok && e != nullptr;
+    dev_ok = dev_ok && cudaMalloc(&ex->hyper_dev, 8 * sizeof(float)) == cudaSuccess;
+    dev_ok = dev_ok && cudaMalloc(&ex->counters_dev, 256 * sizeof(unsigned int)) == cudaSuccess;
+    dev_ok = dev_ok && cudaMemset(ex->counters_dev, 0, 256 * sizeof(unsigned int)) == cudaSuccess;
+    dev_ok = dev_ok && cudaMemset(ex->hyper_dev, 0, 8 * sizeof(float)) == cudaSuccess;
+    dev_ok = dev_ok && cudaMallocHost(&ex->hyper_host, cai_exec::kHyperSlots * 8 * sizeof(float)) == cudaSuccess;
+    for (int i = 0; i < cai_exec::kHyperSlots && dev_ok; ++i)
+        dev_ok = cudaEventCreateWithFlags(&ex->hyper_ev[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!dev_ok) {
+        set_last_error("executor set-up failed (event / device / pinned allocation): %s", cudaGetErrorString(cudaGetLastError()));
+        cai_exec_destroy(ex);
+        return CAI_K_CUDA;
+    }
     {
         uint32_t fused = 0;
         for (const ExecOp& x : ex->exec)
@@ -536,7 +557,6 @@ CAI_API int cai_exec_create(cai_exec** out, const void* plan_bytes, size_t nbyte
             if (!strcmp(nt.name, "@flat_split")) ex->n_shard = static_cast<long long>(nt.rows) << 9;
         ex->epochs_per_step = 2 * fused + 2;
     }
-    cudaMallocHost(&ex->hyper_host, 8 * sizeof(float));
     *out = ex;
     return 0;
 }
@@ -556,9 +576,11 @@ CAI_API void cai_exec_destroy(cai_exec* ex) {
         if (c.comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c.comm);
         if (c.comm2 && g_nccl.CommDestroy) g_nccl.CommDestroy(c.comm2);
     }
-    cudaFree(ex->hyper_dev);
-    cudaFree(ex->counters_dev);
-    cudaFreeHost(ex->hyper_host);
+    for (cudaEvent_t e : ex->hyper_ev)
+        if (e) cudaEventDestroy(e);
+    if (ex->hyper_dev) cudaFree(ex->hyper_dev);
+    if (ex->counters_dev) cudaFree(ex->counters_dev);
+    if (ex->hyper_host) cudaFreeHost(ex->hyper_host);
     delete ex;
 }
 
@@ -637,7 +659,9 @@ CAI_API float* cai_exec_hyper(cai_exec* ex) { return ex->hyper_dev; }
 // the loss.
 CAI_API int cai_exec_step(cai_exec* ex, int step, float lr) {
     cudaStream_t hi = ex->streams[ST_COMPUTE_HI];
-    float* h = ex->hyper_host;
+    const unsigned slot = ex->hyper_next++ % cai_exec::kHyperSlots;
+    if (ex->hyper_used[slot] && cudaEventSynchronize(ex->hyper_ev[slot]) != cudaSuccess) return CAI_K_CUDA;
+    float* h = ex->hyper_host + slot * 8;
     const TrainSpec& t = ex->train;
     h[0] = lr; h[1] = t.beta1; h[2] = t.beta2; h[3] = t.adam_eps; h[4] = t.weight_decay;
     h[5] = 1.f - powf(t.beta1, static_cast<float>(step));
@@ -645,6 +669,8 @@ CAI_API int cai_exec_step(cai_exec* ex, int step, float lr) {
     // epoch base of this step's fused kernels: grows by a fixed stride per step, never resets
     reinterpret_cast<uint32_t*>(h)[7] = static_cast<uint32_t>(step) * ex->epochs_per_step;
     if (cudaMemcpyAsync(ex->hyper_dev, h, 8 * sizeof(float), cudaMemcpyHostToDevice, hi) != cudaSuccess) return CAI_K_CUDA;
+    if (cudaEventRecord(ex->hyper_ev[slot], hi) != cudaSuccess) return CAI_K_CUDA;
+    ex->hyper_used[slot] = true;
     if (ex->use_graph) {
         if (!ex->graph) {
             cudaGraph_t g = nullptr;

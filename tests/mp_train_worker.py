@@ -20,6 +20,8 @@ def main():
     ap.add_argument("--comm", default="baseline")
     ap.add_argument("--steps", type=int, default=6)
     ap.add_argument("--graph", type=int, default=0)
+    ap.add_argument("--burst", type=int, default=0,
+                    help="train on one fixed batch; enqueue this many optimizer steps between two synchronisations")
     ap.add_argument("--out", required=True)
     a = ap.parse_args()
     import torch
@@ -34,7 +36,17 @@ def main():
     dp_id = rank // (a.tp * a.pp)
     rows = eng.hdr.num_microbatches * m.microbatch
     losses = []
-    for step in range(a.steps):
+    if a.burst:
+        # every step sees the same batch, so a run that synchronises after each step and a run that enqueues
+        # `burst` steps back to back must read the same loss after the same number of steps
+        tok, tgt = synthetic_batch(m.vocab_size, m.seq_len, rows * dp, step=0, seed=11)
+        tok, tgt = tok[dp_id * rows:(dp_id + 1) * rows].contiguous().pin_memory(), tgt[dp_id * rows:(dp_id + 1) * rows].contiguous().pin_memory()
+        eng.load_batch(tok, tgt)
+        for step in range(0, a.steps, a.burst):
+            for _ in range(a.burst):
+                eng.run_step()
+            losses.append(eng.read_loss())
+    for step in range(a.steps if not a.burst else 0):
         # the global batch is dp * rows sequences; each data-parallel replica takes its slice
         tok, tgt = synthetic_batch(m.vocab_size, m.seq_len, rows * dp, step=step % 2, seed=11)
         tok, tgt = tok[dp_id * rows:(dp_id + 1) * rows].contiguous().pin_memory(), tgt[dp_id * rows:(dp_id + 1) * rows].contiguous().pin_memory()

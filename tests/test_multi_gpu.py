@@ -52,6 +52,17 @@ def test_tensor_parallel_2_matches_single_gpu(tmp_path, single, comm):
     close(r["losses"], single["losses"])
 
 
+def test_steps_enqueued_without_a_sync_match_synced_steps(tmp_path):
+    """Three optimizer steps enqueued back to back (as the device-timed loop of bench.py does) must use each
+    step's own learning-rate / bias-correction / signal-epoch words: the loss after steps 3 and 6 equals the
+    run that synchronises after every step."""
+    if _gpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    a = run_case(tmp_path, 2, tp=2, comm="fused", burst=1)
+    b = run_case(tmp_path, 2, tp=2, comm="fused", burst=3)
+    close(b["losses"], a["losses"][2::3], tol=0.002)
+
+
 def test_data_parallel_2_baseline_and_fused_agree(tmp_path):
     if _gpus() < 2:
         pytest.skip("needs 2 GPUs")

@@ -192,9 +192,17 @@ def test_plan_variants_compile_and_verify(tmp_path):
     fused = [i for i, x in enumerate(z3.exec) if int(x.kernel) == plan.K_FSDP_AG_GEMM and (x.flags & 1)]
     assert fused and all(int(z3.exec[i + 1].kernel) == plan.K_GEMM for i in fused)   # merged into the GEMM that follows
     # tensor parallel: weight gradients leave the critical path (compute_lo), dQ runs beside dK/dV
-    tp = _variant(tmp_path, "tp2", "tp = 2\ncomm = fused\n", world=2)
+    tp = _variant(tmp_path, "tp2", "tp = 2\ncomm = fused\nmb_group = 1\n", world=2)
     lo_gemms = [op for op in tp.ops if op.exec and int(tp.exec[op.exec - 1].kernel) == plan.K_GEMM and op.stream_id == 1]
     assert len(lo_gemms) >= 4 * 4 * 4   # 4 layers x 4 microbatches x 4 weight gradients
+    # microbatches launched in pairs (the default under tensor parallelism): half the launches, twice the rows each
+    pair = _variant(tmp_path, "tp2_pairs", "tp = 2\ncomm = fused\n", world=2)
+    fused_ops = lambda p: [x for x in p.exec if int(x.kernel) in (plan.K_AG_GEMM, plan.K_GEMM_RS)]
+    assert len(fused_ops(pair)) * 2 == len(fused_ops(tp)) and fused_ops(pair)[0].i[0] == 2 * fused_ops(tp)[0].i[0]
+    assert pair.hdr.num_microbatches == tp.hdr.num_microbatches and pair.hdr.plan_hash == tp.hdr.plan_hash
+    with pytest.raises(plan.PlanError):
+        plan.compile_plans((ROOT / "configs" / "tiny_mp.cfg").read_text() + "\ngpus_per_rack = 2\ngpus_per_tray = 2\npp = 2\nmb_group = 2\n",
+                           tmp_path / "bad_group", version=2, text=True)
     off = _variant(tmp_path, "tp2_serial", "tp = 2\ncomm = fused\nwgrad_overlap = 0\n", world=2)
     assert not [op for op in off.ops if op.exec and int(off.exec[op.exec - 1].kernel) == plan.K_GEMM and op.stream_id == 1]
     # refused combinations
