@@ -81,3 +81,13 @@ def check(rc: int, what: str):
 def device_status(clear: bool = True) -> int:
     """Status word of the current device: 0, or the code of the first bounded wait that ran out."""
     return lib().cai_status_read(1 if clear else 0)
+
+
+def set_wait_limit_us(us: int) -> None:
+    """Time limit of every in-kernel wait on another GPU's flag on the current device (0 = the default, ~2 s)."""
+    check(lib().cai_set_wait_limit_us(ctypes.c_uint(int(us))), "set_wait_limit_us")
+
+
+def status_abort() -> None:
+    """Make every kernel of the current device that sits in a bounded wait give up now (status 108)."""
+    check(lib().cai_status_abort(), "status_abort")

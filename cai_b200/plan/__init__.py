@@ -154,6 +154,8 @@ def lib() -> ctypes.CDLL:
         L.cai_current_step.restype = c_uint32
         L.cai_ckpt_write.argtypes = [c_char_p, c_char_p, c_uint32, c_uint32, c_uint64, c_uint32, POINTER(c_char_p),
                                      POINTER(c_void_p), POINTER(c_uint64)]
+        L.cai_ckpt_write2.argtypes = [c_char_p, c_char_p, c_uint32, c_uint32, c_uint64, c_uint32, POINTER(c_char_p),
+                                      POINTER(c_void_p), POINTER(c_uint64), c_int]
         L.cai_ckpt_probe.argtypes = [c_char_p, c_uint32, POINTER(c_uint32), POINTER(c_uint64), POINTER(c_uint32),
                                      c_char_p, c_size_t]
         L.cai_ckpt_section.argtypes = [c_char_p, c_uint32, c_char_p, POINTER(c_uint64), c_void_p, c_uint64]

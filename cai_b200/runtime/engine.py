@@ -81,6 +81,15 @@ def synthetic_batch(vocab, seq, rows, step, seed, rank_offset=0, out_tokens=None
     return out_tokens, out_targets
 
 
+class DeviceStatusError(RuntimeError):
+    """A kernel of the step gave up on a bounded wait (or refused its arguments) and said so in the device
+    status word; the step's results are not to be trusted."""
+
+    def __init__(self, status):
+        super().__init__(f"a kernel gave up on a bounded wait (device status {status})")
+        self.status = status
+
+
 class Engine:
     """Executes one rank's plan. See the module docstring."""
 
@@ -139,7 +148,9 @@ class Engine:
         klib.check(L.cai_exec_create(ctypes.byref(self.ex), self.plan.raw, len(self.plan.raw), c_void_p(base), handles),
                    "exec_create")
         self.stream = self.streams[0]
-        self.step_count = 0
+        self.step_count = 0          # optimizer steps enqueued
+        self.completed_steps = 0     # optimizer steps whose loss was read back without a device error
+        self.device_fault = False    # a kernel reported an error: the arena may be half-updated
         self.lr = float(self.train.lr)
         self._init_comms()
         self.tokens_dev = self.view("@tokens")
@@ -352,7 +363,9 @@ class Engine:
         klib.check(self.L.cai_exec_sync(self.ex), "exec_sync")
         st = klib.device_status(clear=True)
         if st != 0:
-            raise RuntimeError(f"a kernel gave up on a bounded wait (device status {st})")
+            self.device_fault = True
+            raise DeviceStatusError(st)
+        self.completed_steps = self.step_count
         return float(self.loss_host[0])
 
     def step(self, tokens, targets, lr=None) -> float:
@@ -382,38 +395,83 @@ class Engine:
         self.L.cai_exec_trace_enable(self.ex, 0)
         return [buf[i] for i in range(n)]
 
+    @staticmethod
+    def stream_stats(recs):
+        """Measured per-stream occupancy and idle share of the main compute stream from one traced step.
+
+        Returns ``(step_time_s, busy_s[6], bubble)``: busy is the summed duration of the ops of each of the six
+        logical streams (the reference prints the same six columns from its cost model, tools/trainer.c:86-91);
+        bubble is the time compute_hi spent without an op in flight between the first op of the step and the
+        last one on any stream, over the step time (for a pipeline stage: fill, drain and hand-off waits)."""
+        if not recs:
+            return 0.0, [0.0] * 6, 0.0
+        t0 = min(r.start_s for r in recs)
+        t1 = max(r.end_s for r in recs)
+        busy = [0.0] * 6
+        for r in recs:
+            busy[r.stream] += max(0.0, r.end_s - r.start_s)
+        hi = sorted(((r.start_s, r.end_s) for r in recs if r.stream == 0))
+        covered, cur_s, cur_e = 0.0, None, None
+        for s, e in hi:
+            if cur_e is None or s > cur_e:
+                if cur_e is not None:
+                    covered += cur_e - cur_s
+                cur_s, cur_e = s, e
+            else:
+                cur_e = max(cur_e, e)
+        if cur_e is not None:
+            covered += cur_e - cur_s
+        step = t1 - t0
+        return step, busy, (1.0 - covered / step) if step > 0 else 0.0
+
+    def abort_pending_waits(self):
+        """Host-side lever of the watchdog: kernels of this device that sit in a bounded wait give up now."""
+        klib.status_abort()
+
     # ------------------------------------------------------------------ checkpoint / resume
     # File layout (per rank): "<path>.<tag>.rank%06u" plus a rolling "<path>.latest.rank%06u". The
     # first 12 bytes are the reference's (u32 step, u64 plan_hash; src/runtime.c:244-262); a section
     # table follows with this rank's resident state: bf16 parameters, fp32 master / m / v shard,
     # step counter. The snapshot is copied device->host on the io stream into pinned buffers and the
     # file is written (temporary name + rename) by a background thread, so saving overlaps training.
-    def save_checkpoint(self, path, tag="periodic", wait=False):
+    def save_checkpoint(self, path, tag="periodic", wait=False, roll_latest=True, state=True):
+        """Snapshot this rank's parameters and optimizer state. ``roll_latest=False`` leaves the rolling
+        "latest" file alone (a snapshot taken after a failed step must not replace the last good one);
+        ``state=False`` writes the step counter only (nothing on the device is read)."""
         import threading
-        sections = {"param": self.view("@flat_param"), "master": self.view("@flat_master"),
-                    "m": self.view("@flat_m"), "v": self.view("@flat_v")}
-        io = self.streams[5]
-        io.wait_stream(self.stream)
-        host = {}
-        with torch.cuda.stream(io):
-            for k, t in sections.items():
-                buf = self._ckpt_pinned.get(k) if hasattr(self, "_ckpt_pinned") else None
-                if buf is None or buf.numel() != t.numel() or buf.dtype != t.dtype:
-                    buf = torch.empty(t.shape, dtype=t.dtype).pin_memory()
-                buf.copy_(t, non_blocking=True)
-                host[k] = buf
-        self._ckpt_pinned = host
-        done = torch.cuda.Event()
-        done.record(io)
-        self.stream.wait_event(done)  # the next optimizer update must not overtake the snapshot
-        step, ph, rank = self.step_count, int(self.hdr.plan_hash), self.rank
+        # the previous writer may still be streaming the pinned buffers to disk: it has to finish before the
+        # new device-to-host copies land in them
         prev = getattr(self, "_ckpt_thread", None)
         if prev is not None:
             prev.join()
+            self._ckpt_thread = None
+        host = {}
+        done = None
+        if state:
+            sections = {"param": self.view("@flat_param"), "master": self.view("@flat_master"),
+                        "m": self.view("@flat_m"), "v": self.view("@flat_v")}
+            io = self.streams[5]
+            io.wait_stream(self.stream)
+            pinned = getattr(self, "_ckpt_pinned", {})
+            with torch.cuda.stream(io):
+                for k, t in sections.items():
+                    buf = pinned.get(k)
+                    if buf is None or buf.numel() != t.numel() or buf.dtype != t.dtype:
+                        buf = torch.empty(t.shape, dtype=t.dtype).pin_memory()
+                    buf.copy_(t, non_blocking=True)
+                    host[k] = buf
+            self._ckpt_pinned = host
+            done = torch.cuda.Event()
+            done.record(io)
+            self.stream.wait_event(done)  # the next optimizer update must not overtake the snapshot
+        # the step this state belongs to: the last one whose loss was read back without a device error
+        step = self.completed_steps if not state or tag == "emergency" else self.step_count
+        ph, rank = int(self.hdr.plan_hash), self.rank
 
         def write():
-            done.synchronize()
             import numpy as np
+            if done is not None:
+                done.synchronize()
             meta = np.array([step], dtype=np.int64)
             names = list(host) + ["meta"]
             arrs = [host[k].view(torch.uint8).numpy() if host[k].dtype != torch.bfloat16
@@ -422,7 +480,8 @@ class Engine:
             c_names = (ctypes.c_char_p * n)(*[x.encode() for x in names])
             c_data = (c_void_p * n)(*[c_void_p(a.ctypes.data) for a in arrs])
             c_len = (ctypes.c_uint64 * n)(*[a.nbytes for a in arrs])
-            rc = planlib.lib().cai_ckpt_write(str(path).encode(), tag.encode(), rank, step, ph, n, c_names, c_data, c_len)
+            rc = planlib.lib().cai_ckpt_write2(str(path).encode(), tag.encode(), rank, step, ph, n, c_names, c_data, c_len,
+                                               1 if roll_latest else 0)
             self._ckpt_rc = rc
 
         self._ckpt_rc = 0
@@ -433,6 +492,18 @@ class Engine:
             th.join()
             if self._ckpt_rc != 0:
                 raise IOError(f"checkpoint write failed ({self._ckpt_rc}) for {path}")
+
+    def save_emergency_checkpoint(self, path):
+        """What the trainer leaves behind after a failed step (the reference's "emergency" tag,
+        tools/trainer.c:62-67). The rolling "latest" file is never touched. When a kernel reported an
+        error (a bounded wait ran out) the device state may be half-updated, so only the number of the
+        last completed step is recorded; otherwise the state is saved under the emergency tag."""
+        try:
+            clean = klib.device_status(clear=False) == 0 and not self.device_fault
+        except Exception:
+            clean = False
+        self.save_checkpoint(path, "emergency", wait=True, roll_latest=False, state=clean)
+        return clean
 
     def wait_checkpoint(self):
         th = getattr(self, "_ckpt_thread", None)
@@ -469,7 +540,7 @@ class Engine:
                 raise IOError(f"checkpoint section {i} unreadable")
             key = name.value.decode()
             if key == "meta":
-                self.step_count = int(buf.view(np.int64)[0])
+                self.step_count = self.completed_steps = int(buf.view(np.int64)[0])
             elif key in targets:
                 t = targets[key]
                 src = torch.from_numpy(buf)
@@ -478,6 +549,14 @@ class Engine:
                 with torch.cuda.stream(self.stream):
                     t.view(torch.uint8).view(-1).copy_(src.to(self.device))
         self.synchronize()
+        # every rank must resume from the same step: a rank whose newest file is older (or newer) than the
+        # others' would train a model that no longer exists
+        if self.dist is not None and self.dist.is_initialized() and self.world > 1:
+            t = torch.tensor([self.step_count, -self.step_count], device=self.device, dtype=torch.int64)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            hi, lo = int(t[0].item()), -int(t[1].item())
+            if hi != lo:
+                raise planlib.PlanError(f"ranks resume from different steps ({lo}..{hi}): restore a common checkpoint")
         self._peer_barrier()
         return True
 

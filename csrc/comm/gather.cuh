@@ -102,18 +102,17 @@ __device__ __forceinline__ bool gather_wait_range(const PeerTable& pt, const Gat
     if (s1 >= g.nslots) s1 = g.nslots - 1;
     for (int s = s0; s <= s1; ++s) {
         const uint32_t* flag = gather_flag(pt, g, s);
-        bool seen = false;
-        for (uint32_t it = 0; it < kSpinLimit && !seen; ++it) {
+        bool seen = false, timed_out = false;
+        // the copy CTA that raises this flag waits on a peer itself: give it its whole limit and a little more
+        const uint64_t t0 = global_timer_ns(), limit = peer_wait_limit_ns(status) * 5 / 4;
+        for (uint32_t it = 0; !seen; ++it) {
             uint32_t v;
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
             seen = static_cast<int32_t>(v - epoch) >= 0;
-            if (!seen && it > 32) {
-                __nanosleep(100);
-                if ((it & 1023u) == 0 && *reinterpret_cast<volatile int*>(status) != 0) break;
-            }
+            if (!seen && !peer_spin_continue(it, t0, limit, status, &timed_out)) break;
         }
         if (!seen) {
-            atomicCAS(status, 0, CAI_DEV_TIMEOUT_PEER_FLAG);
+            if (timed_out) atomicCAS(status, 0, CAI_DEV_TIMEOUT_PEER_FLAG);
             return false;
         }
     }

@@ -26,6 +26,10 @@ enum {
 };
 
 CAI_API int cai_status_read(int clear);
+/* Time limit (microseconds) of every in-kernel wait on a flag another GPU sets; 0 = default (about 2 s). */
+CAI_API int cai_set_wait_limit_us(unsigned int us);
+/* Host-side abort: kernels of the current device that sit in a bounded wait give up at once (status 108). */
+CAI_API int cai_status_abort(void);
 CAI_API const char* cai_last_error(void);
 CAI_API int cai_sm_count(void);
 

@@ -257,19 +257,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     // rows of this tile must have been staged by a copy CTA; they were written through
                     // the generic proxy, the TMA engine reads through the async proxy
                     const uint32_t* flag = sig_word(p.pt, p.pt.rank, p.group_kind, kSigLocal + tm);
-                    bool seen = false;
-                    for (uint32_t it = 0; it < kSpinLimit && !seen; ++it) {
+                    bool seen = false, timed_out = false;
+                    // the copy CTA that raises this flag waits on a peer itself: its whole limit and a little more
+                    const uint64_t t0 = global_timer_ns(), limit = peer_wait_limit_ns(p.status) * 5 / 4;
+                    for (uint32_t it = 0; !seen; ++it) {
                         uint32_t v;
                         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
                         seen = static_cast<int32_t>(v - epoch) >= 0;
-                        if (!seen && it > 32) {
-                            __nanosleep(100);
-                            if ((it & 1023u) == 0 && *reinterpret_cast<volatile int*>(p.status) != 0) break;
-                        }
+                        if (!seen && !peer_spin_continue(it, t0, limit, p.status, &timed_out)) break;
                     }
                     if (!seen) {
                         *abort_flag = 1;
-                        atomicCAS(p.status, 0, CAI_DEV_TIMEOUT_PEER_FLAG);
+                        if (timed_out) atomicCAS(p.status, 0, CAI_DEV_TIMEOUT_PEER_FLAG);
                         ok = false;
                         break;
                     }

@@ -1,5 +1,6 @@
 // host_common.cu - status words, tensor-map encoding, device properties.
 #include "host_common.h"
+#include "sm100.cuh"
 
 #include <cudaTypedefs.h>
 #include <stdarg.h>
@@ -134,6 +135,27 @@ CAI_API int cai_status_read(int clear) {
     if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return cai::CAI_K_CUDA;
     if (clear && v) cudaMemset(p, 0, sizeof(int));
     return v;
+}
+
+// Time limit, in microseconds, of every wait of a kernel on a flag that another GPU sets (0 restores the
+// default of about two seconds). Takes effect for kernels launched after the call returns.
+CAI_API int cai_set_wait_limit_us(unsigned int us) {
+    int* p = cai::status_words(cai::current_device());
+    if (!p) return cai::CAI_K_CUDA;
+    return cudaMemcpy(p + cai::kStatusWordLimitUs, &us, sizeof us, cudaMemcpyHostToDevice) == cudaSuccess ? 0 : cai::CAI_K_CUDA;
+}
+
+// Makes every kernel of the current device that sits in a bounded wait give up now: the status word is set
+// to CAI_DEV_ABORTED_BY_HOST on a stream of its own, next to whatever is running (a watchdog calls this when a
+// step overruns its deadline, so that the step unwinds instead of running out one wait limit per kernel).
+CAI_API int cai_status_abort() {
+    int* p = cai::status_words(cai::current_device());
+    if (!p) return cai::CAI_K_CUDA;
+    static thread_local cudaStream_t side = nullptr;
+    if (!side && cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking) != cudaSuccess) return cai::CAI_K_CUDA;
+    static const int code = cai::CAI_DEV_ABORTED_BY_HOST;
+    if (cudaMemcpyAsync(p, &code, sizeof code, cudaMemcpyHostToDevice, side) != cudaSuccess) return cai::CAI_K_CUDA;
+    return cudaStreamSynchronize(side) == cudaSuccess ? 0 : cai::CAI_K_CUDA;
 }
 
 CAI_API const char* cai_last_error() { return cai::last_error(); }

@@ -23,8 +23,15 @@ enum : int {
     CAI_DEV_TIMEOUT_TMEM_EMPTY = 104, // MMA warp never got an accumulator back
     CAI_DEV_TIMEOUT_PEER_FLAG = 105,  // a flag another GPU should have set never arrived
     CAI_DEV_TIMEOUT_ATTN = 106,       // attention pipeline barrier
-    CAI_DEV_BAD_ARG = 107
+    CAI_DEV_BAD_ARG = 107,
+    CAI_DEV_ABORTED_BY_HOST = 108     // the host wrote this into the status word: every pending wait gives up at once
 };
+
+// Layout of the per-device status block (64 ints): word 0 is the status proper (0 = clean, otherwise the
+// first code recorded); word 1 is the time limit of a wait on another GPU's flag in microseconds
+// (0 = kPeerWaitDefaultUs), set by the host (cai_set_wait_limit_us).
+constexpr int kStatusWordLimitUs = 1;
+constexpr uint32_t kPeerWaitDefaultUs = 2000000u;
 
 // Iteration caps. mbarrier.try_wait already blocks for a hardware-defined slice, so the
 // caps translate to roughly a second of wall time before a kernel gives up.
@@ -294,17 +301,42 @@ __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
     return v;
 }
 // Wait until *p >= target (epoch counters never reset, so >= tolerates late readers).
-__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target, int* status) {
-    for (uint32_t it = 0; it < kSpinLimit; ++it) {
-        if (static_cast<int32_t>(ld_acquire_sys(p) - target) >= 0) return true;
-        if (it > 64) {
-            __nanosleep(200);
-            // once any kernel on this device has given up, later waits fail fast instead of each
-            // running out its own limit (a dead peer would otherwise cost seconds per launch)
-            if ((it & 1023u) == 0 && status && *reinterpret_cast<volatile int*>(status) != 0) return false;
-        }
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Time limit (ns) of a wait on a peer's flag: the host's setting in the status block, or the default.
+__device__ __forceinline__ uint64_t peer_wait_limit_ns(const int* status) {
+    const uint32_t us = status ? reinterpret_cast<const volatile uint32_t*>(status)[kStatusWordLimitUs] : 0u;
+    return static_cast<uint64_t>(us ? us : kPeerWaitDefaultUs) * 1000ull;
+}
+// One step of a bounded spin on something another GPU (or another CTA that itself waits on a GPU) sets: sleeps,
+// and every so often checks the clock and the status word. Returns false when the wait must be given up: the
+// limit has passed (`*timed_out` set) or some kernel on this device has already recorded an error, in which case
+// later waits fail fast instead of each running out its own limit (a dead peer would otherwise cost seconds
+// per launch).
+__device__ __forceinline__ bool peer_spin_continue(uint32_t it, uint64_t t0, uint64_t limit_ns, const int* status,
+                                                   bool* timed_out) {
+    if (it <= 64) return true;
+    __nanosleep(200);
+    if ((it & 63u) != 0) return true;
+    if (status && *reinterpret_cast<const volatile int*>(status) != 0) return false;
+    if (global_timer_ns() - t0 > limit_ns || it > 0x3FFFFFF0u) {
+        *timed_out = true;
+        return false;
     }
-    if (status) atomicCAS(status, 0, CAI_DEV_TIMEOUT_PEER_FLAG);
+    return true;
+}
+// Wait until *p >= target (epoch counters never reset, so >= tolerates late readers).
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target, int* status) {
+    const uint64_t t0 = global_timer_ns(), limit = peer_wait_limit_ns(status);
+    bool timed_out = false;
+    for (uint32_t it = 0;; ++it) {
+        if (static_cast<int32_t>(ld_acquire_sys(p) - target) >= 0) return true;
+        if (!peer_spin_continue(it, t0, limit, status, &timed_out)) break;
+    }
+    if (timed_out && status) atomicCAS(status, 0, CAI_DEV_TIMEOUT_PEER_FLAG);
     return false;
 }
 

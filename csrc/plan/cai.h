@@ -93,11 +93,16 @@ int cai_group_members(const char* config_text, uint16_t kind, uint32_t rank, uin
 uint64_t cai_fnv1a64(const void* data, size_t len, uint64_t seed);
 
 /* ---- checkpoint files ("<path>.<tag>.rank%06u" + rolling "<path>.latest.rank%06u") ------
- * Layout: u32 step, u64 plan_hash (the reference's 12 bytes), then u32 'CKP2', u32 nsections,
- * then per section {char name[16]; u64 nbytes} followed by the payloads. */
+ * Layout: u32 step, u64 plan_hash (the reference's 12 bytes), then u32 'CKP3', u32 nsections,
+ * then per section {char name[16]; u64 nbytes; u64 hash} followed by the payloads. The hash (FNV-1a over
+ * 64-bit words) is checked when a section is read back; files with the older 'CKP2' table (no hash) load. */
 int cai_ckpt_write(const char* path, const char* tag, uint32_t rank, uint32_t step, uint64_t plan_hash,
                    uint32_t nsections, const char* const* names, const void* const* data,
                    const uint64_t* nbytes);
+/* Same; roll_latest = 0 writes only "<path>.<tag>.rank..." and leaves the rolling "latest" file alone. */
+int cai_ckpt_write2(const char* path, const char* tag, uint32_t rank, uint32_t step, uint64_t plan_hash,
+                    uint32_t nsections, const char* const* names, const void* const* data,
+                    const uint64_t* nbytes, int roll_latest);
 /* Reads the header of the newest checkpoint for `rank` (prefers .latest). Returns 0 and fills
  * step / plan_hash / nsections, 1 if no checkpoint exists, negative on error. */
 int cai_ckpt_probe(const char* path, uint32_t rank, uint32_t* step, uint64_t* plan_hash, uint32_t* nsections,

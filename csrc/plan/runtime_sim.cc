@@ -249,8 +249,25 @@ int cai_finalize(cai_context_t* ctx) {
 
 // ------------------------------------------------------------------ checkpoint files
 namespace {
-constexpr uint32_t kCkptMagic = 0x32504B43u;  // 'CKP2'
-struct SectionHdr { char name[16]; uint64_t nbytes; };
+constexpr uint32_t kCkptMagicV2 = 0x32504B43u;  // 'CKP2': section table without checksums (still readable)
+constexpr uint32_t kCkptMagic = 0x33504B43u;    // 'CKP3': every section carries a hash of its bytes
+struct SectionHdrV2 { char name[16]; uint64_t nbytes; };
+struct SectionHdr { char name[16]; uint64_t nbytes; uint64_t hash; };
+
+// FNV-1a over 64-bit words (the tail byte-wise): a checkpoint of tens of GB is hashed while it is written,
+// so the byte-serial form would dominate the write.
+uint64_t section_hash(const void* data, uint64_t n) {
+    const uint8_t* p = static_cast<const uint8_t*>(data);
+    uint64_t h = kFnvInit;
+    uint64_t i = 0;
+    for (; i + 8 <= n; i += 8) {
+        uint64_t w;
+        std::memcpy(&w, p + i, 8);
+        h = (h ^ w) * 1099511628211ull;
+    }
+    for (; i < n; ++i) h = (h ^ p[i]) * 1099511628211ull;
+    return h;
+}
 
 std::string ckpt_name(const char* path, const char* tag, uint32_t rank) {
     char buf[1200];
@@ -269,6 +286,7 @@ int write_file(const std::string& file, uint32_t step, uint64_t plan_hash, uint3
         SectionHdr sh{};
         std::strncpy(sh.name, names[i], sizeof sh.name - 1);
         sh.nbytes = nbytes[i];
+        sh.hash = section_hash(data[i], nbytes[i]);
         ok = write_all(f, &sh, sizeof sh);
     }
     for (uint32_t i = 0; ok && i < nsec; ++i) ok = write_all(f, data[i], nbytes[i]);
@@ -283,9 +301,15 @@ int write_file(const std::string& file, uint32_t step, uint64_t plan_hash, uint3
 
 int cai_ckpt_write(const char* path, const char* tag, uint32_t rank, uint32_t step, uint64_t plan_hash,
                    uint32_t nsec, const char* const* names, const void* const* data, const uint64_t* nbytes) {
+    return cai_ckpt_write2(path, tag, rank, step, plan_hash, nsec, names, data, nbytes, 1);
+}
+
+int cai_ckpt_write2(const char* path, const char* tag, uint32_t rank, uint32_t step, uint64_t plan_hash,
+                    uint32_t nsec, const char* const* names, const void* const* data, const uint64_t* nbytes, int roll_latest) {
     int rc = write_file(ckpt_name(path, tag, rank), step, plan_hash, nsec, names, data, nbytes);
-    // roll the "latest" pointer so a resume finds the newest state without knowing the tag
-    if (rc == OK) rc = write_file(ckpt_name(path, "latest", rank), step, plan_hash, nsec, names, data, nbytes);
+    // roll the "latest" pointer so a resume finds the newest state without knowing the tag; a snapshot taken
+    // after a failed step (possibly half-updated state) is kept under its own tag only
+    if (rc == OK && roll_latest) rc = write_file(ckpt_name(path, "latest", rank), step, plan_hash, nsec, names, data, nbytes);
     return rc;
 }
 
@@ -303,7 +327,7 @@ int cai_ckpt_probe(const char* path, uint32_t rank, uint32_t* step, uint64_t* pl
     int rc = OK;
     if (!read_all(f, &st, 4)) rc = ERR_IO;
     else if (!read_all(f, &ph, 8)) ph = 0;               // step-only file: tolerated
-    else if (read_all(f, &magic, 4) && magic == kCkptMagic) {
+    else if (read_all(f, &magic, 4) && (magic == kCkptMagic || magic == kCkptMagicV2)) {
         if (!read_all(f, &ns, 4)) rc = ERR_IO;
     }
     std::fclose(f);
@@ -321,11 +345,20 @@ int cai_ckpt_section(const char* file, uint32_t index, char name[16], uint64_t* 
     uint32_t st, magic = 0, ns = 0;
     uint64_t ph;
     int rc = OK;
-    if (!read_all(f, &st, 4) || !read_all(f, &ph, 8) || !read_all(f, &magic, 4) || magic != kCkptMagic ||
-        !read_all(f, &ns, 4) || index >= ns)
+    if (!read_all(f, &st, 4) || !read_all(f, &ph, 8) || !read_all(f, &magic, 4) ||
+        (magic != kCkptMagic && magic != kCkptMagicV2) || !read_all(f, &ns, 4) || index >= ns)
         rc = ERR_INVALID;
-    std::vector<SectionHdr> hdrs(ns);
-    if (rc == OK && !read_all(f, hdrs.data(), ns * sizeof(SectionHdr))) rc = ERR_IO;
+    std::vector<SectionHdr> hdrs(rc == OK ? ns : 0);
+    const bool hashed = magic == kCkptMagic;
+    if (rc == OK && hashed && !read_all(f, hdrs.data(), ns * sizeof(SectionHdr))) rc = ERR_IO;
+    if (rc == OK && !hashed) {
+        std::vector<SectionHdrV2> old(ns);
+        if (!read_all(f, old.data(), ns * sizeof(SectionHdrV2))) rc = ERR_IO;
+        for (uint32_t i = 0; rc == OK && i < ns; ++i) {
+            std::memcpy(hdrs[i].name, old[i].name, 16);
+            hdrs[i].nbytes = old[i].nbytes;
+        }
+    }
     if (rc == OK) {
         uint64_t off = 0;
         for (uint32_t i = 0; i < index; ++i) off += hdrs[i].nbytes;
@@ -335,6 +368,10 @@ int cai_ckpt_section(const char* file, uint32_t index, char name[16], uint64_t* 
             if (cap < hdrs[index].nbytes) rc = ERR_INVALID;
             else if (std::fseek(f, static_cast<long>(off), SEEK_CUR) != 0 || !read_all(f, dst, hdrs[index].nbytes))
                 rc = ERR_IO;
+            else if (hashed && section_hash(dst, hdrs[index].nbytes) != hdrs[index].hash) {
+                logf(LOG_ERROR, "checkpoint '%s': section '%.16s' fails its checksum", file, hdrs[index].name);
+                rc = ERR_IO;
+            }
         }
     }
     std::fclose(f);

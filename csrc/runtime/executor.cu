@@ -512,6 +512,7 @@ CAI_API int cai_exec_create(cai_exec** out, const void* plan_bytes, size_t nbyte
         }
     ex->arena = static_cast<uint8_t*>(arena_base);
     ex->device = current_device();
+    if (ex->train.wait_limit_ms) cai_set_wait_limit_us(ex->train.wait_limit_ms * 1000u);
     int lo_prio = 0, hi_prio = 0;
     cudaDeviceGetStreamPriorityRange(&lo_prio, &hi_prio);
     for (int s = 0; s < ST_COUNT; ++s) {

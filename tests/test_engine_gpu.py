@@ -197,3 +197,37 @@ def test_activation_recompute_gives_the_same_training_run():
     for n in g0:
         rel = ((g0[n] - g1[n]).norm() / (g0[n].norm() + 1e-12)).item()
         assert rel < 1e-3, (n, rel)
+
+
+def test_trainer_prints_measured_stream_stats_and_handles_a_failed_step(tmp_path):
+    """The device trainer's summary carries measured per-stream occupancy and the compute stream's idle share,
+    its JSONL sink the same fields; a failed step ends the run with exit code 1 and an emergency checkpoint
+    that leaves the rolling "latest" file at the last periodic state."""
+    import json
+    import os
+    import subprocess
+    import sys
+    sink, ck = tmp_path / "log.jsonl", tmp_path / "ck"
+    env = dict(os.environ, RANK="0", WORLD_SIZE="1", LOCAL_RANK="0")
+    cmd = [sys.executable, "-m", "cai_b200.trainer", "--config", str(ROOT / "configs" / "tiny.cfg"), "--jsonl", str(sink),
+           "--ckpt", str(ck), "--ckpt-every", "2"]
+    r = subprocess.run(cmd + ["--steps", "5"], capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert r.returncode == 0, (r.stdout[-2000:], r.stderr[-2000:])
+    assert "per-stream occupancy (ms), measured on the last step: compute_hi=" in r.stdout
+    assert "compute stream idle" in r.stdout and "summary: 4 steps" in r.stdout
+    recs = [json.loads(l) for l in sink.read_text().splitlines()]
+    assert [x["step"] for x in recs] == [0, 1, 2, 3, 4]
+    last = recs[-1]
+    assert last["traced"] and set(last["stream_busy_ms"]) == {"compute_hi", "compute_lo", "comm_tp", "comm_pp", "comm_dp", "io"}
+    assert last["stream_busy_ms"]["compute_hi"] > 0 and 0.0 <= last["bubble_measured"] < 1.0
+    assert all(k in recs[0] for k in ("step_time_s", "mfu", "tokens_per_s", "loss", "bubble_formula"))
+    latest = tmp_path / "ck.latest.rank000000"
+    assert int.from_bytes(latest.read_bytes()[:4], "little") == 4
+    # resume at step 4, fail at step 6: exit 1, emergency file with the last completed step, "latest" untouched
+    before = latest.read_bytes()
+    r = subprocess.run(cmd + ["--steps", "9", "--ckpt-every", "100", "--fail-at", "6"], capture_output=True, text=True,
+                       timeout=600, env=env, cwd=ROOT)
+    assert r.returncode == 1 and "step 6 failed" in r.stderr, (r.stdout[-1000:], r.stderr[-2000:])
+    em = tmp_path / "ck.emergency.rank000000"
+    assert em.exists() and int.from_bytes(em.read_bytes()[:4], "little") == 6
+    assert latest.read_bytes() == before

@@ -103,3 +103,43 @@ def test_corrupted_plan_and_missing_files_are_refused(tmp_path):
         plan.Simulator(tmp_path / "trunc.bin", tmp_path / "topology.bin")
     with pytest.raises(plan.PlanError):
         plan.Simulator(tmp_path / "plan.rank000000.bin", tmp_path / "no_such_topology.bin")
+
+
+def test_checkpoint_sections_are_checksummed_and_emergency_files_leave_latest_alone(tmp_path):
+    """A flipped byte in a section is caught when the section is read back; a write with roll_latest = 0
+    (what the trainer does after a failed step) does not replace the rolling "latest" file."""
+    import ctypes
+    import numpy as np
+    from cai_b200 import plan
+    L = plan.lib()
+    path = str(tmp_path / "ck").encode()
+
+    def write(tag, step, payload, roll):
+        arr = np.frombuffer(payload, dtype=np.uint8).copy()
+        names = (ctypes.c_char_p * 1)(b"master")
+        data = (ctypes.c_void_p * 1)(ctypes.c_void_p(arr.ctypes.data))
+        lens = (ctypes.c_uint64 * 1)(arr.nbytes)
+        assert L.cai_ckpt_write2(path, tag, 3, step, 0xABCD, 1, names, data, lens, roll) == 0
+
+    def read(file):
+        name = ctypes.create_string_buffer(16)
+        n = ctypes.c_uint64(0)
+        assert L.cai_ckpt_section(file, 0, name, ctypes.byref(n), None, 0) == 0
+        buf = np.empty(n.value, dtype=np.uint8)
+        rc = L.cai_ckpt_section(file, 0, name, ctypes.byref(n), ctypes.c_void_p(buf.ctypes.data), buf.nbytes)
+        return rc, buf.tobytes()
+
+    good = bytes(range(256)) * 5 + b"tail"            # not a multiple of 8 bytes: the hash covers the tail too
+    write(b"periodic", 5, good, 1)
+    latest = tmp_path / "ck.latest.rank000003"
+    assert read(str(latest).encode()) == (0, good)
+    write(b"emergency", 7, b"half-updated state", 0)
+    assert (tmp_path / "ck.emergency.rank000003").exists()
+    assert read(str(latest).encode()) == (0, good)      # still step 5
+    step = ctypes.c_uint32(0)
+    assert L.cai_ckpt_probe(path, 3, ctypes.byref(step), None, None, None, 0) == 0 and step.value == 5
+    raw = bytearray(latest.read_bytes())
+    raw[-7] ^= 0x01
+    latest.write_bytes(raw)
+    rc, _ = read(str(latest).encode())
+    assert rc != 0
