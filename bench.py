@@ -45,10 +45,10 @@ CONFIGS = {
 }
 
 
-def config_text(n_gpus: int, comm: str, name: str = "tp8") -> str:
+def config_text(n_gpus: int, comm: str, name: str = "tp8", extra: str = "") -> str:
     fname, _, how = CONFIGS[name]
     base = (ROOT / "configs" / fname).read_text()
-    text = base + f"\ngpus_per_rack = {n_gpus}\ntrays_per_rack = 1\ngpus_per_tray = {n_gpus}\ncomm = {comm}\n"
+    text = base + f"\ngpus_per_rack = {n_gpus}\ntrays_per_rack = 1\ngpus_per_tray = {n_gpus}\ncomm = {comm}\n" + extra
     if how == "tp":
         text += f"tp = {n_gpus}\n"
     elif how == "ep":
@@ -116,7 +116,8 @@ def run_ours(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29533")
-    eng = Engine(config_text=config_text(world, args.comm, args.config), rank=rank, world=world, local_rank=local)
+    extra = "".join(f"{kv.replace('=', ' = ')}\n" for kv in args.set)
+    eng = Engine(config_text=config_text(world, args.comm, args.config, extra), rank=rank, world=world, local_rank=local)
     m = eng.model
     rows = eng.hdr.num_microbatches * m.microbatch
     K, W = args.steps, max(args.warmup, 3)
@@ -220,6 +221,7 @@ def run_ours(args):
                        "global_batch": int(eng.hdr.grad_accum * m.microbatch * eng.hdr.dp), "seq_len": int(m.seq_len),
                        "parallelism": f"tp{eng.hdr.tp} pp{eng.hdr.num_stages} dp{eng.hdr.dp} ep{eng.hdr.ep}", "microbatch": int(m.microbatch), "grad_accum": int(eng.hdr.grad_accum),
                        "comm": args.comm, "cuda_graph": bool(args.graph),
+                       "microbatches_per_launch": int(eng.batch_cols // (m.microbatch * m.seq_len)), "overrides": list(args.set),
                        "l2": "working set (>10 GB per step) exceeds the 126 MB L2; no explicit flush"},
             "mfu_vs_2.25PF": eng.mfu(dev_ms * 1e-3, 2.25e15),
             "mfu_vs_measured_sustained": eng.mfu(dev_ms * 1e-3, measured_peak),
@@ -389,6 +391,8 @@ def main():
     ap.add_argument("--comm", default="fused", choices=["fused", "baseline"])
     ap.add_argument("--graph", type=int, default=0)
     ap.add_argument("--breakdown", action="store_true", help="also print a per-op time table of one step (stderr)")
+    ap.add_argument("--set", action="append", default=[], metavar="KEY=VALUE",
+                    help="override a key of the config file (schedule options such as mb_group=1); repeatable")
     ap.add_argument("--config", default="tp8", choices=sorted(CONFIGS), help="which named config (default: the headline one)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -107,7 +107,7 @@ def build_host(verbose=False) -> Path:
         list(ex.map(lambda c: _run(c, verbose), jobs))
     lib = LIBDIR / "libcai_host.so"
     if jobs or _newer(lib, objs):
-        _run([CXX, "-shared", "-o", lib] + objs + ["-lm", "-lpthread"], verbose)
+        _run([CXX, "-shared", "-o", lib] + objs + ["-lm", "-lpthread", "-ldl"], verbose)
     tool_jobs = []
     for t in sorted((CSRC / "tools").glob("*.cc")):
         exe = BINDIR / t.stem
@@ -128,7 +128,7 @@ def build_sanitized_selftest(verbose=False) -> Path:
     headers = list((CSRC / "plan").glob("*.h")) + list((CSRC / "ref").glob("*.h"))
     if _newer(out, srcs + headers):
         _run([CXX, "-std=c++17", "-O1", "-g", "-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-fno-sanitize-recover=undefined",
-              "-I", CSRC, "-I", CSRC / "plan"] + srcs + ["-o", out, "-lm", "-lpthread"], verbose)
+              "-I", CSRC, "-I", CSRC / "plan"] + srcs + ["-o", out, "-lm", "-lpthread", "-ldl"], verbose)
     return out
 
 

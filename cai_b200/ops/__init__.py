@@ -9,7 +9,7 @@ import torch
 
 from ._lib import KernelError, check, device_status, lib
 
-EPI_BF16, EPI_F32, EPI_F32_ACCUM, EPI_BF16_RESIDUAL = 0, 1, 2, 3
+EPI_BF16, EPI_F32, EPI_F32_ACCUM, EPI_BF16_RESIDUAL, EPI_SWIGLU, EPI_SWIGLU_BWD = 0, 1, 2, 3, 4, 5
 
 
 def _stream():
@@ -64,6 +64,33 @@ def gemm(a, b, *, trans_a=False, trans_b=False, out=None, out_dtype=torch.bfloat
                               out.stride(0), ldr, int(trans_a), int(trans_b), epi, float(alpha),
                               int(sm_limit), _stream()), "gemm")
     return out
+
+
+def gemm_swiglu(x, wgu):
+    """Gate/up projection with SwiGLU in the GEMM epilogue: ``gu = x @ wgu^T`` with ``wgu = [gate rows; up rows]``
+    (``[2F, K]``, F a multiple of 128) and ``act = silu(gu[:, :F]) * gu[:, F:]``. Returns ``(gu, act)``."""
+    assert x.dtype == torch.bfloat16 and wgu.dtype == torch.bfloat16 and x.stride(1) == 1 and wgu.stride(1) == 1
+    M, K = x.shape
+    N = wgu.shape[0]
+    assert wgu.shape[1] == K and N % 256 == 0
+    gu = torch.empty((M, N), device=x.device, dtype=torch.bfloat16)
+    act = torch.empty((M, N // 2), device=x.device, dtype=torch.bfloat16)
+    check(lib().cai_gemm_bf16(_p(x), _p(wgu), _p(gu), _p(act), M, N, K, x.stride(0), wgu.stride(0), gu.stride(0), act.stride(0),
+                              0, 0, EPI_SWIGLU, 1.0, 0, _stream()), "gemm_swiglu")
+    return gu, act
+
+
+def gemm_swiglu_bwd(dy, wd, gu):
+    """Input gradient of the down projection with SwiGLU backward in the epilogue: ``dact = dy @ wd`` (``wd`` is
+    ``[H, F]``) never reaches memory, the result is ``dgu = [dgate | dup]`` (``[T, 2F]``) from the saved ``gu``."""
+    assert dy.dtype == torch.bfloat16 and wd.dtype == torch.bfloat16 and gu.dtype == torch.bfloat16
+    M, K = dy.shape
+    Kb, F = wd.shape
+    assert K == Kb and gu.shape == (M, 2 * F) and gu.stride(1) == 1
+    dgu = torch.empty((M, 2 * F), device=dy.device, dtype=torch.bfloat16)
+    check(lib().cai_gemm_bf16(_p(dy), _p(wd), _p(dgu), _p(gu), M, F, K, dy.stride(0), wd.stride(0), dgu.stride(0), gu.stride(0),
+                              0, 1, EPI_SWIGLU_BWD, 1.0, 0, _stream()), "gemm_swiglu_bwd")
+    return dgu
 
 
 def gemm_grouped(a, b, out, M, N, K, *, groups, trans_a=False, trans_b=False, accumulate=False, seg_counts=None, seg_rows=0,

@@ -109,13 +109,14 @@ assert ctypes.sizeof(ExecOp) == 64 and ctypes.sizeof(NamedTensor) == 64 and ctyp
 class StepStats(Structure):
     _fields_ = [("step_time_s", c_double), ("busy_compute_s", c_double), ("bubble_ratio", c_double),
                 ("mfu", c_double), ("tokens_per_s", c_double), ("tokens_per_s_per_gpu", c_double),
-                ("arena_bytes", c_uint64), ("stream_busy", c_double * 6)]
+                ("arena_bytes", c_uint64), ("stream_busy", c_double * 6), ("loss", c_double), ("bubble_measured", c_double),
+                ("measured", c_uint32), ("reserved", c_uint32)]
 
 
 class InitDesc(Structure):
     _fields_ = [("global_rank", c_uint32), ("world_size", c_uint32), ("local_rank", c_uint32),
                 ("plan_path", c_char_p), ("topology_path", c_char_p), ("checkpoint_path", c_char_p),
-                ("checkpoint_every", c_uint32), ("max_steps", c_uint32)]
+                ("checkpoint_every", c_uint32), ("max_steps", c_uint32), ("backend", c_uint32)]
 
 
 class Batch(Structure):

@@ -21,7 +21,8 @@ int cai_fused_rs_adamw(const cai::PeerTable& pt, unsigned long long grad_off, un
 // All-gather of a row-sharded activation fused into the GEMM that consumes it (gemm_tcgen05.cu).
 int cai_fused_ag_gemm(const cai::PeerTable& pt, int group_kind, unsigned long long src_off, long long ld_src, void* a_full,
                       const void* B, void* C, int T, int N, int K, long long ldb, long long ldc, int b_mn,
-                      int rows_per_rank, const uint32_t* epoch_base, uint32_t seq, int n_copy, cudaStream_t st);
+                      int rows_per_rank, const uint32_t* epoch_base, uint32_t seq, int n_copy, cudaStream_t st,
+                      int epi = 0, const void* R = nullptr, long long ldr = 0);   // epi: CAI_EPI_BF16 or a SwiGLU epilogue (R: its second tensor)
 
 // GEMM whose epilogue reduce-scatters the product over the group and adds a residual (gemm_tcgen05.cu).
 int cai_fused_gemm_rs(const cai::PeerTable& pt, int group_kind, const void* A, const void* B, unsigned long long stage_off,

@@ -22,7 +22,15 @@ enum {
     CAI_EPI_BF16 = 0,          /* C(bf16) = alpha*acc */
     CAI_EPI_F32 = 1,           /* C(f32)  = alpha*acc */
     CAI_EPI_F32_ACCUM = 2,     /* C(f32) += alpha*acc */
-    CAI_EPI_BF16_RESIDUAL = 3  /* C(bf16) = alpha*acc + R(bf16); R may alias C */
+    CAI_EPI_BF16_RESIDUAL = 3, /* C(bf16) = alpha*acc + R(bf16); R may alias C */
+    /* SwiGLU inside the gate/up projection. B holds [gate rows (F); up rows (F)], N = 2F. An output tile covers
+     * BN/2 gate columns and the BN/2 up columns of the same features, so the epilogue writes gate and up to
+     * C[:, j] / C[:, F + j] (the layout the backward reads) and act = silu(gate) * up to R[:, j] (bf16, pitch ldr;
+     * R is an OUTPUT here). F must be a multiple of 128; B must be stored [N, K]. */
+    CAI_EPI_SWIGLU = 4,
+    /* SwiGLU backward inside the down projection's input-gradient product (acc = dact, N = F): R is the saved
+     * [gate | up] activation (pitch ldr, 2F columns), C receives [dgate | dup] (pitch ldc, 2F columns). */
+    CAI_EPI_SWIGLU_BWD = 5
 };
 
 CAI_API int cai_status_read(int clear);

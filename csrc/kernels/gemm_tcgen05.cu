@@ -307,7 +307,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         for (int c = 0; c < kBM / 64; ++c)
                             tma_load_2d(a_dst + c * (kBK * 128), &tmA, &full[s], m0 + c * 64, k0 + ga);
                     }
-                    if (!p.b_mn) {
+                    if (p.epi == CAI_EPI_SWIGLU) {
+                        // gate rows and the up rows of the same features, stacked in one stage
+                        const int F = p.N >> 1, j0 = tn * (BN / 2);
+                        tma_load_2d(b_dst, &tmB, &full[s], k0, j0 + gb);
+                        tma_load_2d(b_dst + (BN / 2) * kBK * 2, &tmB, &full[s], k0, F + j0 + gb);
+                    } else if (!p.b_mn) {
                         tma_load_2d(b_dst, &tmB, &full[s], k0, n0 + gb);
                     } else {
 #pragma unroll
@@ -465,6 +470,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const long long row_in = (long long)tm * kBM + q * 32 + lane;   // row inside this group's product
             const bool row_ok = row_in < p.M;
             const long long row = row_in + grp * p.grp_c;
+            if (p.epi == CAI_EPI_SWIGLU) {
+                // accumulator columns [0, BN/2) are gate, [BN/2, BN) up, of features j0 .. j0 + BN/2
+                const int F = p.N >> 1, j0 = tn * (BN / 2);
+                __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc;
+                __nv_bfloat16* arow = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(p.R)) + row * p.ldr;
+#pragma unroll 1
+                for (int c = 0; c < BN / 64; ++c) {
+                    uint32_t rg[32], ru[32];
+                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32;
+                    tmem_ld_32x32(taddr, rg);
+                    tmem_ld_32x32(taddr + BN / 2, ru);
+                    tmem_ld_wait();
+                    const int j = j0 + c * 32;
+                    if (!row_ok || j >= F) continue;
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        if (j + v * 8 >= F) break;
+                        uint4 og, ou, oa;
+                        uint32_t* pg = &og.x; uint32_t* pu = &ou.x; uint32_t* pa = &oa.x;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            // round to bf16 first: the activation is computed from the values the backward will read
+                            pg[e] = pack_bf16(__uint_as_float(rg[v * 8 + 2 * e]) * p.alpha, __uint_as_float(rg[v * 8 + 2 * e + 1]) * p.alpha);
+                            pu[e] = pack_bf16(__uint_as_float(ru[v * 8 + 2 * e]) * p.alpha, __uint_as_float(ru[v * 8 + 2 * e + 1]) * p.alpha);
+                            const float g0 = bf16_lo(pg[e]), g1 = bf16_hi(pg[e]), u0 = bf16_lo(pu[e]), u1 = bf16_hi(pu[e]);
+                            pa[e] = pack_bf16(g0 * (1.f / (1.f + __expf(-g0))) * u0, g1 * (1.f / (1.f + __expf(-g1))) * u1);
+                        }
+                        *reinterpret_cast<uint4*>(crow + j + v * 8) = og;
+                        *reinterpret_cast<uint4*>(crow + F + j + v * 8) = ou;
+                        *reinterpret_cast<uint4*>(arow + j + v * 8) = oa;
+                    }
+                }
+            } else {
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t r[32];
@@ -478,7 +516,33 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const int col0 = tn * BN + c * 32;
                 if (!row_ok || col0 >= p.N) continue;
                 const float alpha = p.alpha;
-                if (p.epi == CAI_EPI_BF16 || p.epi == CAI_EPI_BF16_RESIDUAL) {
+                if (p.epi == CAI_EPI_SWIGLU_BWD) {
+                    // acc = dact[row, col]; R = saved [gate | up]; C = [dgate | dup]
+                    const int F = p.N;
+                    const __nv_bfloat16* grow = reinterpret_cast<const __nv_bfloat16*>(p.R) + row * p.ldr + col0;
+                    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (col0 + j * 8 >= p.N) break;
+                        const uint4 gv = *reinterpret_cast<const uint4*>(grow + j * 8);
+                        const uint4 uv = *reinterpret_cast<const uint4*>(grow + F + j * 8);
+                        const uint32_t* pg = &gv.x; const uint32_t* pu = &uv.x;
+                        uint4 odg, odu;
+                        uint32_t* pdg = &odg.x; uint32_t* pdu = &odu.x;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            // dact goes through bf16 like the tensor it replaces
+                            const uint32_t dd = pack_bf16(__uint_as_float(r[j * 8 + 2 * e]) * alpha, __uint_as_float(r[j * 8 + 2 * e + 1]) * alpha);
+                            const float d0 = bf16_lo(dd), d1 = bf16_hi(dd);
+                            const float g0 = bf16_lo(pg[e]), g1 = bf16_hi(pg[e]), u0 = bf16_lo(pu[e]), u1 = bf16_hi(pu[e]);
+                            const float s0 = 1.f / (1.f + __expf(-g0)), s1 = 1.f / (1.f + __expf(-g1));
+                            pdg[e] = pack_bf16(d0 * u0 * s0 * (1.f + g0 * (1.f - s0)), d1 * u1 * s1 * (1.f + g1 * (1.f - s1)));
+                            pdu[e] = pack_bf16(d0 * (g0 * s0), d1 * (g1 * s1));
+                        }
+                        *reinterpret_cast<uint4*>(orow + j * 8) = odg;
+                        *reinterpret_cast<uint4*>(orow + F + j * 8) = odu;
+                    }
+                } else if (p.epi == CAI_EPI_BF16 || p.epi == CAI_EPI_BF16_RESIDUAL) {
                     __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
                     const __nv_bfloat16* rrow =
                         p.epi == CAI_EPI_BF16_RESIDUAL
@@ -522,6 +586,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         *reinterpret_cast<float4*>(crow + j * 4) = o;
                     }
                 }
+            }
             }
             tc_fence_before();
             __syncwarp();
@@ -680,7 +745,8 @@ static int gemm_dispatch(const void* A, const void* B, long long lda, long long 
     if (!p.a_mn) ok = encode_tmap_2d(&tmA, A, M + xa, K, lda, kBK, kBM, 2);
     else ok = encode_tmap_2d(&tmA, A, K + xa, M, lda, 64, kBK, 2);
     if (!ok) return CAI_K_BAD_ARG;
-    if (!p.b_mn) ok = encode_tmap_2d(&tmB, B, N + xb, K, ldb, kBK, BN, 2);
+    if (p.epi == CAI_EPI_SWIGLU) ok = encode_tmap_2d(&tmB, B, N + xb, K, ldb, kBK, BN / 2, 2);
+    else if (!p.b_mn) ok = encode_tmap_2d(&tmB, B, N + xb, K, ldb, kBK, BN, 2);
     else ok = encode_tmap_2d(&tmB, B, K + xb, N, ldb, 64, kBK, 2);
     if (!ok) return CAI_K_BAD_ARG;
     p.status = status_words(dev);
@@ -723,7 +789,7 @@ CAI_API int cai_gemm_bf16_seg(const void* A, const void* B, void* C, const void*
         set_last_error("gemm: segmented form needs counts and a slab size that is a multiple of 128");
         return CAI_K_BAD_ARG;
     }
-    if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 3) || epi < 0 || epi > CAI_EPI_BF16_RESIDUAL) {
+    if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 3) || epi < 0 || epi > CAI_EPI_SWIGLU_BWD) {
         set_last_error("gemm: N, lda, ldb must be multiples of 8 (N=%d lda=%lld ldb=%lld ldc=%lld epi=%d)", N,
                        lda, ldb, ldc, epi);
         return CAI_K_BAD_ARG;
@@ -734,6 +800,14 @@ CAI_API int cai_gemm_bf16_seg(const void* A, const void* B, void* C, const void*
     }
     if (epi == CAI_EPI_BF16_RESIDUAL && (!R || (ldr & 7))) {
         set_last_error("gemm: residual epilogue needs R with ldr %% 8 == 0");
+        return CAI_K_BAD_ARG;
+    }
+    if ((epi == CAI_EPI_SWIGLU || epi == CAI_EPI_SWIGLU_BWD) && (!R || (ldr & 7) || (ldc & 7) || seg_mode == 2)) {
+        set_last_error("gemm: SwiGLU epilogues need the second tensor R with ldr %% 8 == 0 and ldc %% 8 == 0");
+        return CAI_K_BAD_ARG;
+    }
+    if (epi == CAI_EPI_SWIGLU && (b_mn_major || (N % 256))) {
+        set_last_error("gemm: fused SwiGLU needs B stored [2F, K] with F a multiple of 128 (N=%d)", N);
         return CAI_K_BAD_ARG;
     }
     GemmParams p;
@@ -775,10 +849,16 @@ CAI_API int cai_gemm_bf16_grouped(const void* A, const void* B, void* C, int M, 
 // y[T,N] = concat_rows(x_local of every member)[T,K] * op(B); also leaves the gathered rows in a_full.
 int cai_fused_ag_gemm(const PeerTable& pt, int group_kind, unsigned long long src_off, long long ld_src, void* a_full,
                       const void* B, void* C, int T, int N, int K, long long ldb, long long ldc, int b_mn,
-                      int rows_per_rank, const uint32_t* epoch_base, uint32_t seq, int n_copy, cudaStream_t st) {
+                      int rows_per_rank, const uint32_t* epoch_base, uint32_t seq, int n_copy, cudaStream_t st,
+                      int epi, const void* R, long long ldr) {
     if (rows_per_rank % kBM || rows_per_rank * pt.size != T || (N & 7) || (K & 7) || (ldb & 7) || (ldc & 7) ||
         T / kBM > static_cast<int>(kSigLocalSlots)) {
         set_last_error("ag_gemm: rows per member must be a multiple of 128 (T=%d rows_per_rank=%d)", T, rows_per_rank);
+        return CAI_K_BAD_ARG;
+    }
+    if ((epi != CAI_EPI_BF16 && epi != CAI_EPI_SWIGLU && epi != CAI_EPI_SWIGLU_BWD) ||
+        (epi != CAI_EPI_BF16 && (!R || (ldr & 7))) || (epi == CAI_EPI_SWIGLU && (b_mn || (N % 256)))) {
+        set_last_error("ag_gemm: unsupported epilogue %d for N=%d", epi, N);
         return CAI_K_BAD_ARG;
     }
     GemmParams p;
@@ -786,6 +866,7 @@ int cai_fused_ag_gemm(const PeerTable& pt, int group_kind, unsigned long long sr
     p.M = T; p.N = N; p.K = K;
     p.b_mn = b_mn ? 1 : 0;
     p.C = C; p.ldc = ldc;
+    p.epi = epi; p.R = R; p.ldr = ldr;
     p.mode = kGemmAllGatherA;
     p.group_kind = group_kind;
     if (n_copy <= 0) {
@@ -882,7 +963,7 @@ CAI_API int cai_fused_ag_gemm_c(void* const* bases, int rank, int size, unsigned
                                 void* stream) {
     if (size < 1 || size > kMaxPeers || T % size) return CAI_K_BAD_ARG;
     return cai_fused_ag_gemm(peer_table_of(bases, rank, size, sig_off), group_kind, src_off, ld_src, a_full, B, C, T, N, K, ldb, ldc,
-                             b_mn, T / size, epoch_base, seq, n_copy, static_cast<cudaStream_t>(stream));
+                             b_mn, T / size, epoch_base, seq, n_copy, static_cast<cudaStream_t>(stream), CAI_EPI_BF16, nullptr, 0);
 }
 
 CAI_API int cai_fused_gemm_rs_c(void* const* bases, int rank, int size, unsigned long long sig_off, int group_kind, const void* A,

@@ -29,7 +29,17 @@ typedef struct {
     const char* checkpoint_path; /* NULL: start from scratch */
     uint32_t checkpoint_every;   /* steps; 0 disables */
     uint32_t max_steps;          /* 0: run until the caller stops */
+    uint32_t backend;            /* CAI_BACKEND_*: which backend replays the plan (the CAI_BACKEND environment
+                                  * variable, "analytic" / "device" / "auto", overrides CAI_BACKEND_DEFAULT) */
 } cai_init_desc_t;
+
+enum {
+    CAI_BACKEND_DEFAULT = 0,  /* analytic unless the environment says otherwise */
+    CAI_BACKEND_ANALYTIC = 1, /* cost model, no GPU: predicts step time, bubble, MFU */
+    CAI_BACKEND_DEVICE = 2,   /* execute the plan on the GPU of local_rank (needs a version-2 plan); fail if impossible */
+    CAI_BACKEND_AUTO = 3      /* device when a GPU and the kernel library are there, else analytic (the reference's order,
+                               * src/runtime.c:32-73) */
+};
 
 typedef struct {
     uint32_t step;
@@ -46,6 +56,11 @@ typedef struct {
     double tokens_per_s_per_gpu;
     uint64_t arena_bytes;
     double stream_busy[6];
+    /* filled by an executing backend (0 under the analytic one) */
+    double loss;                 /* mean loss of the step */
+    double bubble_measured;      /* share of the step the main compute stream had no op in flight */
+    uint32_t measured;           /* 1: times above are measurements, 0: predictions of the cost model */
+    uint32_t reserved;
 } cai_step_stats_t;
 
 typedef struct {
@@ -72,6 +87,7 @@ int cai_trace_enable(cai_context_t* ctx, int on);
 int cai_trace_dump_csv(cai_context_t* ctx, const char* path);
 int cai_finalize(cai_context_t* ctx);
 uint32_t cai_current_step(cai_context_t* ctx);
+const char* cai_backend_name(cai_context_t* ctx);   /* "analytic" or "device" */
 
 /* ---- compiler entry points (used by the Python package through ctypes) ---------------- */
 

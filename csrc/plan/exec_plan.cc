@@ -185,10 +185,10 @@ struct Builder {
     }
     // Linear layer product with tp = 1: C[T,N] = a[T,K] * W[N,K]^T (tb: a[T,K] * W[K,N]) (+ residual R).
     // With fp8 weights the activation is quantised per row and 128 columns and the e4m3 tensor-core GEMM runs.
-    void linear(int a, int W, int C, int R, uint32_t N, uint32_t K, bool tb, uint16_t mb) {
+    void linear(int a, int W, int C, int R, uint32_t N, uint32_t K, bool tb, uint16_t mb, int epi = -1) {
         auto it = fp8w.find(W);
-        if (!fp8 || it == fp8w.end() || K % 128) {
-            gemm(ST_COMPUTE_HI, a, W, C, R, T, N, K, false, tb, R >= 0 ? 3 : 0, mb);
+        if (!fp8 || it == fp8w.end() || K % 128 || epi > 3) {
+            gemm(ST_COMPUTE_HI, a, W, C, R, T, N, K, false, tb, epi >= 0 ? epi : (R >= 0 ? 3 : 0), mb);
             return;
         }
         const Fp8Weight& w = it->second;
@@ -258,14 +258,17 @@ struct Builder {
     // y[T, N] = gather_rows(x_local[Tl, K]) * W[N, K]^T  (column-parallel linear, forward), or
     // with tb: y[T, N] = gather_rows(x_local) * W[K, N] (input gradient of a row-parallel linear).
     // x_full receives the gathered rows (kept for the weight gradient).
-    void col_parallel(int x_local, int x_full, int W, int y, uint32_t N, uint32_t K, bool tb, uint16_t mb) {
+    // epi / aux select a fused epilogue of the product (CAI_EPI_SWIGLU: aux receives the activation;
+    // CAI_EPI_SWIGLU_BWD: aux is the saved [gate | up] tensor and y receives [dgate | dup]).
+    void col_parallel(int x_local, int x_full, int W, int y, uint32_t N, uint32_t K, bool tb, uint16_t mb, int epi = 0,
+                      int aux = -1) {
         if (tp == 1) {
-            linear(x_local, W, y, -1, N, K, tb, mb);
+            linear(x_local, W, y, aux, N, K, tb, mb, epi);
             return;
         }
         if (fused) {
-            ExecOp e = xop(K_AG_GEMM, static_cast<uint16_t>(tb ? 2 : 0));
-            e.t[0] = x_local; e.t[1] = W; e.t[2] = y; e.t[3] = x_full;
+            ExecOp e = xop(K_AG_GEMM, static_cast<uint16_t>((tb ? 2 : 0) | (epi << 4)));
+            e.t[0] = x_local; e.t[1] = W; e.t[2] = y; e.t[3] = x_full; e.t[5] = aux;
             e.i[0] = T; e.i[1] = N; e.i[2] = K; e.i[3] = GROUP_TP; e.i[4] = static_cast<int32_t>(next_seq++);
             e.f[0] = 1.0f;
             push(OP_AG_GEMM, ST_COMPUTE_HI, 2.0 * T * N * K, static_cast<double>(T) * K * 2, GROUP_TP, mb, &e);
@@ -275,7 +278,7 @@ struct Builder {
         nccl(K_NCCL_ALL_GATHER, OP_ALL_GATHER, ST_COMM_TP, x_local, x_full, static_cast<uint64_t>(Tl) * K, DT_BF16,
              GROUP_TP, -1, mb);
         sync(ST_COMM_TP, ST_COMPUTE_HI, mb);
-        gemm(ST_COMPUTE_HI, x_full, W, y, -1, T, N, K, false, tb, 0, mb);
+        gemm(ST_COMPUTE_HI, x_full, W, y, aux, T, N, K, false, tb, epi, mb);
     }
     // out_local[Tl, N] = residual + reduce_scatter_rows(a[T, K] * W[N, K]^T) (row-parallel linear,
     // forward), or with tb the input gradient of a column-parallel linear (residual may be -1).
@@ -321,7 +324,8 @@ void exec_operands(const ExecOp& x, std::vector<int>* reads, std::vector<int>* w
         case K_RMSNORM_BWD: R(0); R(1); R(2); R(3); if (x.i[2]) R(4); W(4); if (x.i[3]) R(5); W(5); W(6); break;
         case K_GEMM: {
             const int epi = (x.flags >> 4) & 0xF;
-            R(0); R(1); if (epi == 2) R(2); R(3); R(4); W(2);
+            R(0); R(1); if (epi == 2) R(2); R(4); W(2);
+            if (epi == 4) W(3); else R(3);   // fused SwiGLU writes the activation into its second tensor
             break;
         }
         case K_ROPE: R(0); R(1); W(0); break;
@@ -342,7 +346,10 @@ void exec_operands(const ExecOp& x, std::vector<int>* reads, std::vector<int>* w
         case K_NCCL_REDUCE_SCATTER: case K_NCCL_ALL_GATHER: case K_NCCL_ALL_TO_ALL: R(0); W(1); break;
         case K_NCCL_SEND: R(0); break;
         case K_NCCL_RECV: W(1); break;
-        case K_AG_GEMM: R(0); R(1); W(2); W(3); break;
+        case K_AG_GEMM:
+            R(0); R(1); W(2); W(3);
+            if (((x.flags >> 4) & 0xF) == 4) W(5); else R(5);
+            break;
         case K_GEMM_RS: R(0); R(1); R(3); W(2); W(4); break;
         case K_RS_ADAMW: R(0); R(1); R(2); R(3); W(0); W(1); W(2); W(4); break;
         case K_FSDP_AG_GEMM: R(0); W(1); break;
@@ -385,7 +392,10 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         return failf(err, ERR_INVALID, "zero_stage = 3 needs comm = fused, tp = 1, pp = 1 and a dense model");
     // fp8 parameters: forward and input-gradient GEMMs of the linear layers run in e4m3 with block scales
     // (tp = 1, dense); weight gradients, attention, the LM head and everything else stay bf16.
-    const bool fp8 = m.param_dtype == DT_FP8_E4M3 && d.tp == 1 && !moe;
+    if (m.param_dtype == DT_FP8_E4M3 && (d.tp != 1 || moe))
+        return failf(err, ERR_INVALID, "param_dtype = fp8e4m3 has an executable schedule for dense models with tp = 1 only "
+                                       "(got tp=%u%s); use bf16 there instead of a silent change of precision", d.tp, moe ? ", MoE" : "");
+    const bool fp8 = m.param_dtype == DT_FP8_E4M3;
     if (d.cp != 1) return failf(err, ERR_INVALID, "context parallelism (cp>1) has no executable schedule");
     if (m.head_dim != 128) return failf(err, ERR_INVALID, "executable plans need head_dim = 128 (got %u)", m.head_dim);
     if (m.num_heads % d.tp || m.num_kv_heads % d.tp || m.ffn_hidden % d.tp || m.vocab_size % d.tp)
@@ -630,6 +640,8 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     // weight-gradient GEMMs (nothing downstream in the layer needs them) go to compute_lo and fill idle SMs,
     // most of all under the attention backward. The attention half of a layer then gathers into its own buffer.
     const bool overlap_wgrad = tp > 1 && !moe && cfg.train.wgrad_overlap != 0;
+    // SwiGLU (forward and backward) rides in the epilogues of the gate/up and down-gradient products
+    const bool fuse_swiglu = cfg.train.fuse_swiglu != 0 && !moe && !fp8 && b.F_l % 128 == 0;
     const int dfull_attn = overlap_wgrad ? b.tensor(TC_WORKSPACE, DT_BF16, T, H) : dfull;
     const int dqkv = b.tensor(TC_WORKSPACE, DT_BF16, T, b.Cqkv);
     const int dao = b.tensor(TC_WORKSPACE, DT_BF16, T, b.Hq_l);
@@ -782,8 +794,11 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         }
         // MLP block
         b.rmsnorm_fwd(a.hmid, w.g2.w, tp > 1 ? xn_local : a.xn2, a.rstd2, Tl, mb);
-        b.col_parallel(tp > 1 ? xn_local : a.xn2, a.xn2, w.wgu.w, a.gu, 2 * b.F_l, H, false, mb);
-        {
+        if (fuse_swiglu) {
+            // gate/up product with SwiGLU in its epilogue: gu and act leave the same kernel
+            b.col_parallel(tp > 1 ? xn_local : a.xn2, a.xn2, w.wgu.w, a.gu, 2 * b.F_l, H, false, mb, 4, a.act);
+        } else {
+            b.col_parallel(tp > 1 ? xn_local : a.xn2, a.xn2, w.wgu.w, a.gu, 2 * b.F_l, H, false, mb);
             ExecOp e = xop(K_SWIGLU_FWD);
             e.t[0] = a.gu; e.t[1] = a.act;
             e.i[0] = T; e.i[1] = b.F_l;
@@ -944,9 +959,13 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             } else {
             // ---- MLP block: x_next = hmid + act * Wd^T
             prepare_layer(l, true, mb);                                                           // ZeRO-3 re-gather, top of the range first
-            b.col_parallel(dstream, dfull, w.wd.w, dact, b.F_l, H, true, mb);                     // dact = gather(dx) * Wd
-            wgrad(g_rows, a.act, w.wd.g, H, b.F_l, T);                                            // dWd = dx^T act
-            {
+            if (fuse_swiglu) {
+                // dact = gather(dx) * Wd never reaches memory: the epilogue turns it into [dgate | dup]
+                b.col_parallel(dstream, dfull, w.wd.w, dgu, b.F_l, H, true, mb, 5, a.gu);
+                wgrad(g_rows, a.act, w.wd.g, H, b.F_l, T);                                        // dWd = dx^T act
+            } else {
+                b.col_parallel(dstream, dfull, w.wd.w, dact, b.F_l, H, true, mb);                 // dact = gather(dx) * Wd
+                wgrad(g_rows, a.act, w.wd.g, H, b.F_l, T);                                        // dWd = dx^T act
                 ExecOp e = xop(K_SWIGLU_BWD);
                 e.t[0] = a.gu; e.t[1] = dact; e.t[2] = dgu;
                 e.i[0] = T; e.i[1] = b.F_l;

@@ -11,6 +11,7 @@
 #include <cstring>
 #include <memory>
 
+#include "backend.h"
 #include "cai.h"
 #include "plan.h"
 
@@ -53,11 +54,32 @@ double analytic_op_seconds(const Topology& topo, const Op& op, const CommGroup* 
     return t;
 }
 
+namespace {
+double analytic_vt(Backend*, const Topology& topo, const Op& op, const CommGroup* g) { return analytic_op_seconds(topo, op, g); }
+void analytic_destroy(Backend* be) { delete be; }
+}  // namespace
+
+Backend* backend_analytic_create() {
+    auto be = new Backend();
+    be->name = "analytic";
+    be->impl = nullptr;
+    be->op_seconds = analytic_vt;
+    be->load_plan = nullptr;
+    be->run_step = nullptr;
+    be->snapshot = nullptr;
+    be->restore = nullptr;
+    be->sync = nullptr;
+    be->destroy = analytic_destroy;
+    return be;
+}
+
 }  // namespace cai
 
 using namespace cai;
 
 struct cai_context {
+    Backend* be = nullptr;
+    ~cai_context() { if (be) be->destroy(be); }
     cai_init_desc_t desc{};
     std::string plan_path, topo_path, ckpt_path;
     Topology topo{};
@@ -93,7 +115,24 @@ int cai_init(cai_context_t** out, const cai_init_desc_t* desc) {
         topology_finalize(&ctx->topo, &err);
     }
     if (desc->checkpoint_path) ctx->ckpt_path = desc->checkpoint_path;
-    logf(LOG_INFO, "rank %u/%u backend=analytic", desc->global_rank, ctx->topo.world_size);
+    // backend selection: the descriptor, unless it leaves the choice open and the environment makes one
+    uint32_t want = desc->backend;
+    if (want == CAI_BACKEND_DEFAULT) {
+        const char* env = std::getenv("CAI_BACKEND");
+        want = !env ? CAI_BACKEND_ANALYTIC : !std::strcmp(env, "device") ? CAI_BACKEND_DEVICE
+             : !std::strcmp(env, "auto") ? CAI_BACKEND_AUTO : CAI_BACKEND_ANALYTIC;
+    }
+    if (want == CAI_BACKEND_DEVICE || want == CAI_BACKEND_AUTO) {
+        std::string why;
+        ctx->be = backend_device_create(desc->local_rank, &why);
+        if (!ctx->be && want == CAI_BACKEND_DEVICE) {
+            logf(LOG_ERROR, "device backend unavailable: %s", why.c_str());
+            return ERR_BACKEND;
+        }
+        if (!ctx->be) logf(LOG_INFO, "device backend unavailable (%s): falling back to the analytic backend", why.c_str());
+    }
+    if (!ctx->be) ctx->be = backend_analytic_create();
+    logf(LOG_INFO, "rank %u/%u backend=%s", desc->global_rank, ctx->topo.world_size, ctx->be->name);
     if (desc->plan_path) {
         if (int rc = cai_load_plan(ctx.get(), desc->plan_path); rc != OK) return rc;
     }
@@ -114,6 +153,9 @@ int cai_load_plan(cai_context_t* ctx, const char* path) {
     if (p.hdr.world_size != ctx->topo.world_size) {
         logf(LOG_ERROR, "plan world_size %u != topology world_size %u", p.hdr.world_size, ctx->topo.world_size);
         return ERR_PLAN;
+    }
+    if (ctx->be && ctx->be->load_plan) {
+        if (int rc = ctx->be->load_plan(ctx->be, p, path, ctx->desc.global_rank, ctx->topo.world_size); rc != OK) return rc;
     }
     ctx->plan = std::move(p);
     ctx->plan_path = path;
@@ -137,6 +179,16 @@ int cai_load_checkpoint(cai_context_t* ctx, const char* path) {
              (unsigned long long)ph, (unsigned long long)ctx->plan.hdr.plan_hash);
         return ERR_PLAN;
     }
+    if (ctx->be && ctx->be->restore) {
+        for (uint32_t i = 0; i < nsec; ++i) {
+            char name[17] = {0};
+            uint64_t n = 0;
+            if (cai_ckpt_section(resolved, i, name, &n, nullptr, 0) != OK) return ERR_IO;
+            std::vector<uint8_t> buf(n);
+            if (cai_ckpt_section(resolved, i, name, &n, buf.data(), n) != OK) return ERR_IO;
+            if (int rc2 = ctx->be->restore(ctx->be, name, buf.data(), n); rc2 != OK) return rc2;
+        }
+    }
     ctx->step = step;
     logf(LOG_INFO, "resumed from checkpoint at step %u", ctx->step);
     return OK;
@@ -150,9 +202,33 @@ int cai_next_batch(cai_context_t* ctx, cai_batch_t* batch) {
     return OK;
 }
 
-int cai_train_step(cai_context_t* ctx, const cai_batch_t*) {
+int cai_train_step(cai_context_t* ctx, const cai_batch_t* batch) {
     if (!ctx->plan_loaded) return ERR_PLAN;
     const Plan& p = ctx->plan;
+    if (ctx->be && ctx->be->run_step) {
+        // executing backend: the whole table runs on the device, statistics are measurements
+        StepResult r;
+        const uint64_t seed = batch ? batch->seed : (0x9E3779B97F4A7C15ull ^ ctx->step);
+        if (int rc = ctx->be->run_step(ctx->be, ctx->step + 1, seed, ctx->trace_on, &r); rc != OK) return rc;
+        ctx->trace = std::move(r.trace);
+        const double useful = static_cast<double>(p.hdr.global_tokens_per_step) * static_cast<double>(p.hdr.flops_per_token_useful) /
+                              p.hdr.world_size;
+        cai_step_stats_t& L = ctx->last;
+        L = cai_step_stats_t{};
+        L.step_time_s = r.step_time_s;
+        L.busy_compute_s = std::max(r.stream_busy[ST_COMPUTE_HI], r.stream_busy[ST_COMPUTE_LO]);
+        L.bubble_ratio = pipeline_bubble_interleaved(p.hdr.num_stages, p.hdr.num_microbatches, p.hdr.vpp ? p.hdr.vpp : 1);
+        L.mfu = r.step_time_s > 0 ? useful / (ctx->topo.gpu_flops_bf16 * r.step_time_s) : 0.0;
+        L.tokens_per_s = r.step_time_s > 0 ? p.hdr.global_tokens_per_step / r.step_time_s : 0.0;
+        L.tokens_per_s_per_gpu = L.tokens_per_s / p.hdr.world_size;
+        L.arena_bytes = p.hdr.arena_bytes;
+        for (int s = 0; s < ST_COUNT; ++s) L.stream_busy[s] = r.stream_busy[s];
+        L.loss = r.loss;
+        L.bubble_measured = r.hi_idle_ratio;
+        L.measured = 1;
+        ctx->step++;
+        return OK;
+    }
     double clock[ST_COUNT] = {0}, work[ST_COUNT] = {0};
     std::fill(ctx->event_time.begin(), ctx->event_time.end(), 0.0);
     ctx->trace.clear();
@@ -178,7 +254,7 @@ int cai_train_step(cai_context_t* ctx, const cai_batch_t*) {
                 if (c.group_id == op.aux0) g = &c;
             if (!g && op_is_comm(op.kind)) return ERR_PLAN;
         }
-        const double dur = analytic_op_seconds(ctx->topo, op, g);
+        const double dur = ctx->be->op_seconds(ctx->be, ctx->topo, op, g);
         const double start = clock[st];
         clock[st] = start + dur;
         work[st] += dur;
@@ -193,6 +269,7 @@ int cai_train_step(cai_context_t* ctx, const cai_batch_t*) {
                                   static_cast<double>(p.hdr.flops_per_token_useful) / p.hdr.world_size;
     const double cap = ctx->topo.gpu_flops_bf16 * step_time;
     cai_step_stats_t& L = ctx->last;
+    L = cai_step_stats_t{};
     L.step_time_s = step_time;
     L.busy_compute_s = std::max(clock[ST_COMPUTE_HI], clock[ST_COMPUTE_LO]);
     L.bubble_ratio = bubble;
@@ -230,6 +307,26 @@ int cai_should_checkpoint(cai_context_t* ctx) {
 
 int cai_save_checkpoint(cai_context_t* ctx, const char* tag) {
     if (ctx->ckpt_path.empty()) return OK;
+    const bool emergency = !std::strcmp(tag, "emergency");
+    if (ctx->be && ctx->be->snapshot && !emergency) {
+        // an executing backend has real state: parameters and optimizer moments travel with the step counter
+        std::vector<std::string> names;
+        std::vector<std::vector<uint8_t>> data;
+        if (int rc = ctx->be->snapshot(ctx->be, &names, &data); rc != OK) return rc;
+        std::vector<const char*> n;
+        std::vector<const void*> d;
+        std::vector<uint64_t> len;
+        for (size_t i = 0; i < names.size(); ++i) {
+            n.push_back(names[i].c_str());
+            d.push_back(data[i].data());
+            len.push_back(data[i].size());
+        }
+        return cai_ckpt_write(ctx->ckpt_path.c_str(), tag, ctx->desc.global_rank, ctx->step, ctx->plan.hdr.plan_hash,
+                              static_cast<uint32_t>(n.size()), n.data(), d.data(), len.data());
+    }
+    if (emergency)   // after a failed step only the step number is recorded, and "latest" keeps the last good state
+        return cai_ckpt_write2(ctx->ckpt_path.c_str(), tag, ctx->desc.global_rank, ctx->step, ctx->plan.hdr.plan_hash, 0, nullptr,
+                               nullptr, nullptr, ctx->be && ctx->be->snapshot ? 0 : 1);
     return cai_ckpt_write(ctx->ckpt_path.c_str(), tag, ctx->desc.global_rank, ctx->step, ctx->plan.hdr.plan_hash, 0,
                           nullptr, nullptr, nullptr);
 }
@@ -241,6 +338,7 @@ int cai_last_step_stats(cai_context_t* ctx, cai_step_stats_t* out) {
 }
 
 uint32_t cai_current_step(cai_context_t* ctx) { return ctx->step; }
+const char* cai_backend_name(cai_context_t* ctx) { return ctx->be ? ctx->be->name : "none"; }
 
 int cai_finalize(cai_context_t* ctx) {
     delete ctx;

@@ -384,7 +384,7 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
                 const int T = x.i[0], N = x.i[1], K = x.i[2];
                 return cai_fused_ag_gemm(pt, group, ex->tensors[x.t[0]].offset, ex->ld(x.t[0]), P(3), P(1), P(2), T, N, K,
                                          ex->ld(x.t[1]), ex->ld(x.t[2]), (x.flags >> 1) & 1, T / pt.size, epoch_base, seq,
-                                         ex->ag_copy_ctas, st);
+                                         ex->ag_copy_ctas, st, (x.flags >> 4) & 0xF, P(5), x.t[5] >= 0 ? ex->ld(x.t[5]) : 0);
             }
             if (x.kernel == K_GEMM_RS) {
                 const int T = x.i[0], N = x.i[1], K = x.i[2];

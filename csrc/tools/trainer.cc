@@ -1,9 +1,12 @@
-// trainer <plan.bin> <topology.bin> [--steps N] [--ckpt PATH] [--ckpt-every K] [--trace CSV]
+// trainer <plan.bin> <topology.bin> [--steps N] [--ckpt PATH] [--ckpt-every K] [--trace CSV] [--device | --backend B]
 //
-// Replays a compiled plan with the analytic backend (no GPU): per-step critical path, pipeline
-// bubble, MFU and tokens/s, per-stream occupancy, optional op timeline as CSV, periodic and
-// emergency checkpoints. Same command line and table as the reference (tools/trainer.c). The
-// device trainer that runs the same plan on GPUs is `python -m cai_b200.trainer`.
+// Replays a compiled plan: per-step critical path, pipeline bubble, MFU and tokens/s, per-stream
+// occupancy, optional op timeline as CSV, periodic and emergency checkpoints. Same command line and
+// table as the reference (tools/trainer.c). The backend is chosen at cai_init: the analytic cost model
+// (default, no GPU), or with --device the executor of the kernel library, which runs a single-rank
+// executable plan on the GPU and fills the same table with measurements plus a loss column
+// (--backend auto takes the device when there is one, like the reference's cai_init). Multi-rank
+// jobs run through `python -m cai_b200.trainer`.
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -12,7 +15,7 @@
 
 int main(int argc, char** argv) {
     if (argc < 3) {
-        std::fprintf(stderr, "usage: %s <plan.bin> <topology.bin> [--steps N] [--ckpt PATH] [--ckpt-every K] [--trace CSV] [--fail-at STEP]\n", argv[0]);
+        std::fprintf(stderr, "usage: %s <plan.bin> <topology.bin> [--steps N] [--ckpt PATH] [--ckpt-every K] [--trace CSV] [--fail-at STEP] [--device | --backend analytic|device|auto]\n", argv[0]);
         return 2;
     }
     cai_init_desc_t desc;
@@ -23,12 +26,18 @@ int main(int argc, char** argv) {
     const char* trace = nullptr;
     long fail_at = -1;  // host-side fault injection: report a backend error at this step
     if (const char* r = std::getenv("RANK")) desc.global_rank = std::strtoul(r, nullptr, 10);
+    if (const char* r = std::getenv("LOCAL_RANK")) desc.local_rank = std::strtoul(r, nullptr, 10);
     for (int i = 3; i < argc; ++i) {
         if (!std::strcmp(argv[i], "--steps") && i + 1 < argc) desc.max_steps = std::strtoul(argv[++i], nullptr, 10);
         else if (!std::strcmp(argv[i], "--ckpt") && i + 1 < argc) { desc.checkpoint_path = argv[++i]; if (!desc.checkpoint_every) desc.checkpoint_every = 5; }
         else if (!std::strcmp(argv[i], "--ckpt-every") && i + 1 < argc) desc.checkpoint_every = std::strtoul(argv[++i], nullptr, 10);
         else if (!std::strcmp(argv[i], "--trace") && i + 1 < argc) trace = argv[++i];
         else if (!std::strcmp(argv[i], "--fail-at") && i + 1 < argc) fail_at = std::strtol(argv[++i], nullptr, 10);
+        else if (!std::strcmp(argv[i], "--device")) desc.backend = CAI_BACKEND_DEVICE;
+        else if (!std::strcmp(argv[i], "--backend") && i + 1 < argc) {
+            const char* b = argv[++i];
+            desc.backend = !std::strcmp(b, "device") ? CAI_BACKEND_DEVICE : !std::strcmp(b, "auto") ? CAI_BACKEND_AUTO : CAI_BACKEND_ANALYTIC;
+        }
         else { std::fprintf(stderr, "unknown arg: %s\n", argv[i]); return 2; }
     }
     cai_context_t* ctx = nullptr;
@@ -40,8 +49,9 @@ int main(int argc, char** argv) {
         return 1;
     }
     if (trace) cai_trace_enable(ctx, 1);
-    std::printf("step | step_time | bubble |   MFU  | tokens/s    | tok/s/gpu\n");
-    std::printf("-----+-----------+--------+--------+-------------+----------\n");
+    const bool device = !std::strcmp(cai_backend_name(ctx), "device");
+    std::printf("step | step_time | bubble |   MFU  | tokens/s    | tok/s/gpu%s\n", device ? " |   loss" : "");
+    std::printf("-----+-----------+--------+--------+-------------+----------%s\n", device ? "+--------" : "");
     double sum_mfu = 0, sum_tps = 0;
     unsigned n = 0;
     cai_step_stats_t st;
@@ -56,8 +66,10 @@ int main(int argc, char** argv) {
             return 1;
         }
         cai_last_step_stats(ctx, &st);
-        std::printf("%4u | %7.2f ms| %5.1f%% | %5.1f%% | %9.2e | %8.1f\n", batch.step, st.step_time_s * 1e3,
+        std::printf("%4u | %7.2f ms| %5.1f%% | %5.1f%% | %9.2e | %8.1f", batch.step, st.step_time_s * 1e3,
                     st.bubble_ratio * 100.0, st.mfu * 100.0, st.tokens_per_s, st.tokens_per_s_per_gpu);
+        if (st.measured) std::printf(" | %7.4f", st.loss);
+        std::printf("\n");
         sum_mfu += st.mfu;
         sum_tps += st.tokens_per_s;
         ++n;
@@ -68,9 +80,11 @@ int main(int argc, char** argv) {
         std::printf("\nsummary: %u steps | avg MFU %.1f%% | avg %.3e tokens/s | arena %.2f GiB/gpu\n", n, sum_mfu / n * 100.0,
                     sum_tps / n, st.arena_bytes / (1024.0 * 1024.0 * 1024.0));
         static const char* names[] = {"compute_hi", "compute_lo", "comm_tp", "comm_pp", "comm_dp", "io"};
-        std::printf("per-stream occupancy (ms): ");
+        std::printf("per-stream occupancy (ms)%s: ", st.measured ? ", measured" : "");
         for (int s = 0; s < 6; ++s) std::printf("%s=%.1f ", names[s], st.stream_busy[s] * 1e3);
         std::printf("\n");
+        if (st.measured) std::printf("compute stream idle %.1f%% of the step (measured); pipeline bubble by formula %.1f%%\n",
+                                     st.bubble_measured * 100.0, st.bubble_ratio * 100.0);
     }
     if (trace && cai_trace_dump_csv(ctx, trace) == 0) std::printf("wrote op timeline to %s\n", trace);
     cai_finalize(ctx);

@@ -231,3 +231,28 @@ def test_trainer_prints_measured_stream_stats_and_handles_a_failed_step(tmp_path
     em = tmp_path / "ck.emergency.rank000000"
     assert em.exists() and int.from_bytes(em.read_bytes()[:4], "little") == 6
     assert latest.read_bytes() == before
+
+
+def test_c_trainer_runs_an_executable_plan_on_the_device(tmp_path):
+    """`bin/trainer --device`: the C runtime's device backend (kernel library opened at run time) trains the tiny
+    model from plan files alone: loss column falls, statistics are measurements, a checkpoint with real state is
+    written and resumed."""
+    import subprocess
+    BIN = ROOT / "bin"
+    subprocess.run([BIN / "plan_compiler", ROOT / "configs" / "tiny.cfg", tmp_path, "--quiet", "--rank", "0", "--exec"], check=True,
+                   capture_output=True)
+    pl, tp, ck = tmp_path / "plan.rank000000.bin", tmp_path / "topology.bin", tmp_path / "ck"
+    r = subprocess.run([BIN / "trainer", pl, tp, "--steps", "6", "--device", "--ckpt", ck, "--ckpt-every", "3"], capture_output=True,
+                       text=True, timeout=600)
+    assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-1500:])
+    assert "backend=device" in r.stderr and "per-stream occupancy (ms), measured" in r.stdout
+    rows = [l.split("|") for l in r.stdout.splitlines() if l[:4].strip().isdigit()]
+    losses = [float(x[-1]) for x in rows]
+    assert len(losses) == 6 and losses[-1] < losses[0] and all(l == l for l in losses)
+    latest = tmp_path / "ck.latest.rank000000"
+    assert latest.exists() and latest.stat().st_size > 1_000_000      # parameters + optimizer state, not 12 bytes
+    r2 = subprocess.run([BIN / "trainer", pl, tp, "--steps", "8", "--device", "--ckpt", ck, "--ckpt-every", "100"], capture_output=True,
+                        text=True, timeout=600)
+    assert r2.returncode == 0 and "resumed from checkpoint at step 6" in r2.stderr
+    rows2 = [l.split("|") for l in r2.stdout.splitlines() if l[:4].strip().isdigit()]
+    assert [int(x[0]) for x in rows2] == [6, 7] and float(rows2[0][-1]) < losses[0]

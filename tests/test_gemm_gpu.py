@@ -65,3 +65,32 @@ def test_gemm_many_tiles_persistent():
     assert (c - ref).abs().max().item() < 0.1
     c2 = ops.gemm(a, b, out_dtype=torch.float32, sm_limit=16)
     assert torch.equal(c, c2)
+
+
+@pytest.mark.parametrize("M,F,K", [(256, 128, 128), (1024, 1024, 512), (300, 384, 264), (4096, 4096, 256)])
+def test_gemm_with_swiglu_in_the_epilogue(M, F, K):
+    """gate/up projection + SwiGLU in one kernel, and the down projection's input gradient + SwiGLU backward in
+    one kernel, against the fp32 formulas applied to the same bf16-rounded intermediates."""
+    from cai_b200 import ops
+    torch.manual_seed(3)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    wgu = (torch.randn(2 * F, K, device="cuda") * K ** -0.5).to(torch.bfloat16)
+    gu, act = ops.gemm_swiglu(x, wgu)
+    ref_gu = x.float() @ wgu.float().t()
+    assert ((gu.float() - ref_gu).norm() / ref_gu.norm()).item() < 5e-3
+    g, u = gu[:, :F].float(), gu[:, F:].float()
+    ref_act = torch.nn.functional.silu(g) * u
+    assert (act.float() - ref_act).abs().max().item() <= 1e-2 * ref_act.abs().max().item() + 1e-3
+    assert torch.equal(act, ops.swiglu_fwd(gu))           # same numbers as the stand-alone kernel
+    # backward: dgu = [dact * up * silu'(gate) | dact * silu(gate)] with dact = dy @ wd
+    H = K
+    dy = torch.randn(M, H, device="cuda", dtype=torch.bfloat16)
+    wd = (torch.randn(H, F, device="cuda") * H ** -0.5).to(torch.bfloat16)
+    dgu = ops.gemm_swiglu_bwd(dy, wd, gu)
+    dact = ops.gemm(dy, wd, trans_b=True)
+    want = ops.swiglu_bwd(gu, dact)
+    assert (dgu.float() - want.float()).abs().max().item() <= 2e-2 * want.float().abs().max().item() + 1e-3
+    s = torch.sigmoid(g)
+    d = dy.float() @ wd.float()
+    ref = torch.cat([d * u * s * (1 + g * (1 - s)), d * g * s], dim=1)
+    assert ((dgu.float() - ref).norm() / ref.norm()).item() < 1e-2

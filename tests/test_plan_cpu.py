@@ -206,7 +206,8 @@ def test_plan_variants_compile_and_verify(tmp_path):
     off = _variant(tmp_path, "tp2_serial", "tp = 2\ncomm = fused\nwgrad_overlap = 0\n", world=2)
     assert not [op for op in off.ops if op.exec and int(off.exec[op.exec - 1].kernel) == plan.K_GEMM and op.stream_id == 1]
     # refused combinations
-    for bad in ("zero_stage = 3\ncomm = baseline\n", "zero_stage = 3\ncomm = fused\ntp = 2\n"):
+    for bad in ("zero_stage = 3\ncomm = baseline\n", "zero_stage = 3\ncomm = fused\ntp = 2\n",
+                "param_dtype = fp8e4m3\ntp = 2\n"):      # fp8 under tensor parallelism: an error, not a silent bf16 run
         with pytest.raises(plan.PlanError):   # 4 GPUs: dp = 4, or tp = 2 x dp = 2
             plan.compile_plans((ROOT / "configs" / "tiny_mp.cfg").read_text() + "\ngpus_per_rack = 4\ngpus_per_tray = 4\n" + bad,
                                tmp_path / "bad", version=2, text=True)
@@ -241,3 +242,17 @@ def test_benchmark_configs_compile_for_every_gpu_count(tmp_path):
     assert r.returncode == 0
     line = json.loads(r.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and "unavailable" in line
+
+
+def test_backend_selection_at_cai_init(tmp_path):
+    """One runtime API, two backends: without a GPU `--device` is refused with a reason, `--backend auto` falls
+    back to the analytic backend (the order of the reference's cai_init, src/runtime.c:32-73)."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("checks the fallback on a box without a GPU")
+    run(BIN / "plan_compiler", ROOT / "configs" / "tiny.cfg", tmp_path, "--quiet", "--rank", "0", "--exec")
+    pl, tp = tmp_path / "plan.rank000000.bin", tmp_path / "topology.bin"
+    r = run(BIN / "trainer", pl, tp, "--steps", "2", "--device", ok=False)
+    assert r.returncode == 1 and "device backend unavailable" in r.stderr
+    r = run(BIN / "trainer", pl, tp, "--steps", "2", "--backend", "auto")
+    assert "backend=analytic" in r.stderr and "falling back" in r.stderr and "summary: 2 steps" in r.stdout
