@@ -14,8 +14,11 @@ Two measurements per run, both over EXACTLY K optimizer steps after W warm-up st
 The working set (3 GB of bf16 weights, >7 GB of activations per microbatch) is far larger than the
 126 MB L2, so no explicit L2 flush is needed between iterations.
 
-``--impl reference`` would run the unmodified reference; it has no executable that can run this
-model (see the message it prints), so that arm reports itself unavailable.
+``--impl reference`` runs the unmodified reference, built by its own Makefile into ``baseline/_ref``
+(``cai_b200/_build.py:build_reference``), through its stock GPU entry point ``gpu_trainer``. That
+executable can only train its hard-coded 88k-parameter model, so its line carries
+``same_config: false``; both arms also print ``useful_flops_per_s`` (6 x parameters x tokens/s, plus the
+attention term for this framework's arm) so that the work rates can be compared across the two models.
 """
 from __future__ import annotations
 
@@ -223,6 +226,7 @@ def run_ours(args):
                        "comm": args.comm, "cuda_graph": bool(args.graph),
                        "microbatches_per_launch": int(eng.batch_cols // (m.microbatch * m.seq_len)), "overrides": list(args.set),
                        "l2": "working set (>10 GB per step) exceeds the 126 MB L2; no explicit flush"},
+            "useful_flops_per_s": float(eng.hdr.flops_per_token_useful) * value,
             "mfu_vs_2.25PF": eng.mfu(dev_ms * 1e-3, 2.25e15),
             "mfu_vs_measured_sustained": eng.mfu(dev_ms * 1e-3, measured_peak),
             "loss_first": loss0, "loss_last": loss_e2e, "loss_after_device_timed": loss_dev,
@@ -372,6 +376,7 @@ def run_reference(args):
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp32", "data": "synthetic (the reference's own xorshift token stream), its own random init",
         "same_config": False,
+        "useful_flops_per_s": 6.0 * 88384 * value,
         "config": {"model": "reference's hard-coded model: 2L h64 4x16 heads ffn128 V64 seq32 (88,384 parameters); it cannot "
                             "run the headline model", "global_batch": REF_SPEC["batch_per_rank"] * world,
                    "seq_len": REF_SPEC["seq"], "parallelism": f"dp{world}",

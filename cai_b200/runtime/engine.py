@@ -140,6 +140,10 @@ class Engine:
         self.arena.zero_()
         self.arena[:self._arena_shift].fill_(0xA5)
         self.arena[self._arena_shift + int(self.hdr.arena_bytes):].fill_(0xA5)
+        # guard bytes between the class segments of the arena (the compiler leaves them uncovered)
+        self._inner_guards = self._segment_gaps()
+        for lo, hi in self._inner_guards:
+            self.arena[self._arena_shift + lo:self._arena_shift + hi].fill_(0xA5)
         self.ex = c_void_p()
         # The six streams come from torch's pool: tensors touched on them stay valid for torch's
         # caching allocators after the executor is gone. compute_hi and comm_tp get high priority.
@@ -171,15 +175,36 @@ class Engine:
 
     _GUARD = 4096
 
+    def _segment_gaps(self):
+        """Byte ranges of the arena that lie between the tensors of one class and the first tensor of the next:
+        the guard words the compiler leaves at the end of every class segment."""
+        ext = {}
+        for t in self.plan.tensors:
+            if t.nbytes == 0:
+                continue
+            lo, hi = ext.get(t.tclass, (1 << 62, 0))
+            ext[t.tclass] = (min(lo, t.offset), max(hi, t.offset + t.nbytes))
+        order = sorted(ext.values())
+        gaps = []
+        for (lo_a, hi_a), (lo_b, _) in zip(order, order[1:] + [(int(self.hdr.arena_bytes), 0)]):
+            if lo_b > hi_a:
+                gaps.append((int(hi_a), int(lo_b)))
+        return gaps
+
     def check_canaries(self):
-        """Debug aid: the guard bytes on both sides of the arena must still hold their pattern, i.e. no kernel
-        wrote below the first or past the last tensor of the plan. Synchronises the device."""
+        """Debug aid: the guard bytes on both sides of the arena and between its class segments (parameters,
+        gradients, optimizer state, activations, communication buffers, workspace) must still hold their pattern,
+        i.e. no kernel wrote past the end of the tensors of one class. Synchronises the device."""
         torch.cuda.synchronize(self.device)
         head = self.arena[:self._arena_shift]
         tail = self.arena[self._arena_shift + int(self.hdr.arena_bytes):]
         bad = int((head != 0xA5).sum().item()) + int((tail != 0xA5).sum().item())
         if bad:
             raise RuntimeError(f"{bad} guard bytes around the arena were overwritten")
+        for lo, hi in self._inner_guards:
+            n = int((self.arena[self._arena_shift + lo:self._arena_shift + hi] != 0xA5).sum().item())
+            if n:
+                raise RuntimeError(f"{n} guard bytes between arena segments (offsets {lo}..{hi}) were overwritten")
         return True
 
     # ------------------------------------------------------------------ arena views

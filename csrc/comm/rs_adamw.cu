@@ -3,7 +3,13 @@
 // the all-gather of the updated bf16 parameters.
 //
 // Every rank owns a contiguous 1/dp shard of the flat parameter space (master, m, v live only
-// there). For each element of its shard the owner pulls the fp32 gradient of every replica with
+// there). A launch covers a bucket [lo, hi) of the flat space - the whole space, or one layer's
+// parameters, launched on the data-parallel stream as soon as the last microbatch's weight gradients of
+// that layer exist, so that the reduction and the update overlap the rest of the backward pass (the
+// reference plan places a REDUCE_SCATTER per layer on comm_dp for the same reason,
+// src/model.c:501-503). Each rank handles the part of the bucket that falls into its shard (possibly
+// nothing: it still takes part in the handshakes, which is how the owners learn that its gradients
+// are complete). For each of its elements the owner pulls the fp32 gradient of every replica with
 // peer loads over NVLink, sums in registers, applies AdamW, and pushes the new bf16 value into the
 // parameter buffer of every replica with peer stores. Nothing is staged, nothing goes through
 // NCCL. Cross-GPU ordering: an entry handshake ("my gradients are complete") before the first
@@ -28,6 +34,7 @@ struct RsAdamwParams {
     float* m;
     float* v;
     long long n_flat, n_shard;
+    long long bucket_lo, bucket_hi;          // this launch covers [bucket_lo, bucket_hi) of the flat space
     const float* hyper;  // lr, b1, b2, eps, wd, bc1, bc2, [7] = epoch base (uint32 bits)
     float gscale;
     uint32_t seq;
@@ -48,10 +55,12 @@ __global__ void __launch_bounds__(256) rs_adamw_kernel(const PeerTable pt, const
     if (ok) {
         const float lr = p.hyper[0], b1 = p.hyper[1], b2 = p.hyper[2], eps = p.hyper[3], wd = p.hyper[4],
                     bc1 = p.hyper[5], bc2 = p.hyper[6];
-        const long long lo = static_cast<long long>(pt.rank) * p.n_shard;
-        const long long hi = lo + p.n_shard < p.n_flat ? lo + p.n_shard : p.n_flat;
+        const long long lo = static_cast<long long>(pt.rank) * p.n_shard;   // my shard: [lo, shard_hi)
+        const long long shard_hi = lo + p.n_shard < p.n_flat ? lo + p.n_shard : p.n_flat;
+        const long long first = lo > p.bucket_lo ? lo : p.bucket_lo;         // my part of this bucket
+        const long long hi = shard_hi < p.bucket_hi ? shard_hi : p.bucket_hi;
         const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
-        for (long long i = lo + (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < hi; i += stride) {
+        for (long long i = first + (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < hi; i += stride) {
             float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int mbr = 0; mbr < kMaxPeers; ++mbr) {
@@ -110,21 +119,27 @@ using namespace cai;
 
 int cai_fused_rs_adamw(const PeerTable& pt, unsigned long long grad_off, unsigned long long param_off, float* master,
                        float* m, float* v, long long n_flat, long long n_shard, const float* hyper, float gscale,
-                       uint32_t seq, unsigned int* done_counter, int local_params, cudaStream_t st) {
-    if ((n_shard & 3) || (n_flat & 3)) {
-        set_last_error("rs_adamw: element counts must be multiples of 4");
+                       uint32_t seq, unsigned int* done_counter, int local_params, cudaStream_t st,
+                       long long bucket_lo, long long bucket_hi, int max_ctas) {
+    if (bucket_hi < 0) bucket_hi = n_flat;
+    if ((n_shard & 3) || (n_flat & 3) || (bucket_lo & 3) || (bucket_hi & 3) || bucket_lo < 0 || bucket_lo > bucket_hi || bucket_hi > n_flat) {
+        set_last_error("rs_adamw: element counts and bucket bounds must be multiples of 4 (bucket %lld..%lld of %lld)", bucket_lo,
+                       bucket_hi, n_flat);
         return CAI_K_BAD_ARG;
     }
     RsAdamwParams p;
     p.grad_off = grad_off; p.param_off = param_off;
     p.master = master; p.m = m; p.v = v;
     p.n_flat = n_flat; p.n_shard = n_shard;
+    p.bucket_lo = bucket_lo; p.bucket_hi = bucket_hi;
     p.hyper = hyper; p.gscale = gscale; p.seq = seq;
     p.done_counter = done_counter;
     p.local_params = local_params;
     const int dev = current_device();
     p.status = status_words(dev);
-    const int grid = sm_count(dev) * 4;
+    // a bucket that runs beside the backward pass takes a slice of the GPU (max_ctas), the end-of-step launch all of it
+    int grid = sm_count(dev) * 4;
+    if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
     rs_adamw_kernel<<<grid, 256, 0, st>>>(pt, p);
     if (cudaGetLastError() != cudaSuccess) {
         set_last_error("rs_adamw launch failed");
@@ -146,5 +161,5 @@ extern "C" __attribute__((visibility("default"))) int cai_fused_rs_adamw_c(
     pt.size = size;
     pt.sig_off = sig_off;
     return cai_fused_rs_adamw(pt, grad_off, param_off, master, m, v, n_flat, n_shard, hyper, gscale, seq, scratch, local_params,
-                              static_cast<cudaStream_t>(stream));
+                              static_cast<cudaStream_t>(stream), 0, -1, 0);
 }

@@ -172,7 +172,12 @@ CAI_API int cai_flash_attn_fwd_variant(const void* qkv, void* out, float* lse, i
 CAI_API int cai_flash_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
                                void* dqkv, int B, int S, int nh, int nkv, int hd, float scale, void* stream);
 /* The same in separately launchable parts (bit 0: delta = rowsum(dO * O), bit 1: dK / dV, bit 2: dQ; the last two
- * both need delta and write disjoint columns of dqkv, so they may run on different streams). */
+ * both need delta and write disjoint columns of dqkv, so they may run on different streams).
+ * With few heads (GQA, grid of the dK / dV part no larger than the SM count) the dK / dV part runs one CTA per query
+ * head and chains the heads of a kv group through counters in ONE device array of the library, cleared by each
+ * call: two calls whose dK / dV parts overlap on the GPU race on it, so issue those from one stream (or order
+ * them with events). The first such call on a device resolves the array's address and should precede any stream
+ * capture. */
 CAI_API int cai_flash_attn_bwd_parts(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
                                      void* dqkv, int B, int S, int nh, int nkv, int hd, float scale, int parts, void* stream);
 

@@ -40,7 +40,13 @@ struct AttnBwdParams {
     unsigned int* chain;
 };
 
-// chain counters of the head-split dK / dV kernel: one per (batch, kv group, kv tile)
+// chain counters of the head-split dK / dV kernel: one per (batch, kv group, kv tile).
+// ONE array serves every call on a device: each call clears the slots it uses (stream-ordered memset) before
+// its kernel, so two attention backwards that overlap on one GPU (different streams) would reset each other's
+// counters. Calls that take the head-split path must therefore be ordered against each other; the executor
+// issues them from one stream. A CTA of turn t waits (bounded) for the CTA of turn t - 1 of the same kv tile,
+// which has a lower linear block id: with the grid no larger than the number of SMs every CTA is resident at
+// once and the order of dispatch does not matter; the launcher only takes this path then.
 constexpr size_t kAttnChainSlots = 65536;
 __device__ unsigned int g_attn_chain[kAttnChainSlots];
 
@@ -527,9 +533,11 @@ CAI_API int cai_flash_attn_bwd_parts(const void* qkv, const void* out, const voi
     p.split_heads = 0;
     p.chain = nullptr;
     const size_t need = static_cast<size_t>(B) * nkv * nq;
-    if ((parts & 2) && nh > nkv && static_cast<long long>(nq) * nkv * B < sm_count(dev) && need <= kAttnChainSlots) {
-        // the counters live in a device array of the library: nothing is allocated on this path, so the call
-        // can sit inside a stream capture from its first use
+    if ((parts & 2) && nh > nkv && static_cast<long long>(nq) * nkv * B < sm_count(dev) &&
+        static_cast<long long>(nq) * nh * B <= sm_count(dev) && need <= kAttnChainSlots) {
+        // the counters live in a device array of the library: nothing is allocated on this path. The first call
+        // on a device resolves the array's address (which may load the module), so it should come before any
+        // stream capture; later calls only enqueue work.
         static unsigned int* chain_ptr[64] = {};
         if (!chain_ptr[dev & 63] &&
             cudaGetSymbolAddress(reinterpret_cast<void**>(&chain_ptr[dev & 63]), g_attn_chain) != cudaSuccess) {

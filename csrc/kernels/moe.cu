@@ -85,12 +85,53 @@ moe_route_fwd_kernel(const float* __restrict__ logits, int* __restrict__ idx, fl
         S += best * inv;
     }
     if (lane < k) {
-        int ps = atomicAdd(&counts[sel_e], 1);
-        if (ps >= cap) ps = -1;  // over capacity: the token skips this expert
         idx[t * k + lane] = sel_e;
         w[t * k + lane] = sel_p / S;
-        pos[t * k + lane] = ps;
     }
+}
+
+// Slot of every (token, choice) inside its expert's slab, in token order: pos[i] = how many earlier entries
+// of idx chose the same expert, or -1 past the slab's capacity (the token skips that expert). One CTA per
+// expert scans idx front to back, so which tokens are dropped and the row order inside a slab are the same in
+// every run (an atomic counter per expert would hand out slots in arrival order). counts[e] is the number
+// of entries that chose e, dropped ones included.
+__global__ void __launch_bounds__(256)
+moe_assign_slots_kernel(const int* __restrict__ idx, int* __restrict__ pos, int* __restrict__ counts, int n, int cap) {
+    __shared__ int warp_tot[8];
+    const int e = blockIdx.x, lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
+    int base = 0;
+    for (int i0 = 0; i0 < n; i0 += 256 * 8) {
+        const int i = i0 + threadIdx.x * 8;
+        unsigned mask = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (i + j < n && idx[i + j] == e) mask |= 1u << j;
+        const int mine = __popc(mask);
+        int incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        if (lane == 31) warp_tot[wp] = incl;
+        __syncthreads();
+        int before = 0, total = 0;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            if (q < wp) before += warp_tot[q];
+            total += warp_tot[q];
+        }
+        int slot = base + before + incl - mine;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (mask >> j & 1) {
+                pos[i + j] = slot < cap ? slot : -1;
+                ++slot;
+            }
+        base += total;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) counts[e] = base;
 }
 
 // ------------------------------------------------------------------ router backward
@@ -347,8 +388,8 @@ CAI_API int cai_moe_route_fwd(const float* logits, int* idx, float* w, int* pos,
         return CAI_K_BAD_ARG;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (cudaMemsetAsync(counts, 0, static_cast<size_t>(E) * sizeof(int), st) != cudaSuccess) return CAI_K_CUDA;
     moe_route_fwd_kernel<<<(T * 32 + 255) / 256, 256, 0, st>>>(logits, idx, w, pos, counts, T, E, k, cap);
+    moe_assign_slots_kernel<<<E, 256, 0, st>>>(idx, pos, counts, T * k, cap);
     return cudaGetLastError() == cudaSuccess ? 0 : CAI_K_CUDA;
 }
 

@@ -31,6 +31,7 @@ int fill_plan_header(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t
 namespace {
 
 constexpr uint64_t kTensorAlign = 1024;
+constexpr uint64_t kSegmentGuardBytes = 1024;
 constexpr uint32_t kFlatAlignElems = 512;  // parameters start on multiples of this many elements
 
 int failf(std::string* err, int code, const char* fmt, ...) {
@@ -352,7 +353,7 @@ void exec_operands(const ExecOp& x, std::vector<int>* reads, std::vector<int>* w
             break;
         case K_GEMM_RS: R(0); R(1); R(3); W(2); W(4); break;
         case K_RS_ADAMW: R(0); R(1); R(2); R(3); W(0); W(1); W(2); W(4); break;
-        case K_FSDP_AG_GEMM: R(0); W(1); break;
+        case K_FSDP_AG_GEMM: if (x.t[2] >= 0) R(2); else R(0); W(1); break;   // t[2]: the slice of the local shard that is read
         case K_QUANT_FP8: R(0); W(1); W(2); W(3); W(4); break;
         case K_GEMM_FP8: R(0); R(1); R(3); R(4); R(5); W(2); break;
         case K_MOE_ROUTE:
@@ -479,6 +480,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
                 std::snprintf(nm, sizeof nm, "L%u.%s", base_layer + l, suffix);
                 return nm;
             };
+            layer_range[l].first = align_up(b.flat_elems, kFlatAlignElems);
             L[l].g1 = b.param(name("g1"), 1, H, 0.f);
             L[l].wqkv = b.param(name("wqkv"), b.Cqkv, H, istd);
             L[l].wo = b.param(name("wo"), H, b.Hq_l, istd);
@@ -489,6 +491,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
                 L[l].wgu = b.param(name("wgu"), 2 * b.F_l, H, istd);
                 L[l].wd = b.param(name("wd"), H, b.F_l, istd);
             }
+            layer_range[l].second = align_up(b.flat_elems, kFlatAlignElems);
         }
         if (b.last_stage) {
             gf = b.param("gf", 1, H, 0.f);
@@ -583,6 +586,15 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         }
         ExecOp e = xop(K_FSDP_AG_GEMM, static_cast<uint16_t>((fuse ? 1 : 0) | (reverse ? 2 : 0)));
         e.t[0] = b.flat_param; e.t[1] = dst;
+        {
+            // the part of the local shard the peers (and this rank) read for this group: what the hazard analysis
+            // orders against the optimizer's writes into the shard
+            const uint64_t r = rank / (d.tp * d.pp * d.cp) % std::max(1u, d.dp);
+            const uint64_t a0 = std::max<uint64_t>(lo, r * n_shard), a1 = std::min<uint64_t>(hi, (r + 1) * n_shard);
+            const uint64_t off = a0 < a1 ? a0 - r * n_shard : 0;
+            e.t[2] = b.tensor_at(TC_PARAM, DT_BF16, out->tensors[b.flat_param].offset + off * 2, 1, 0, 0);
+            out->tensors[e.t[2]].nbytes = a0 < a1 ? (a1 - a0) * 2 : 0;
+        }
         e.i[0] = static_cast<int32_t>(lo >> 9); e.i[1] = static_cast<int32_t>(hi >> 9); e.i[2] = 0;
         e.i[3] = GROUP_DP; e.i[4] = static_cast<int32_t>(b.next_seq++);
         b.push(OP_ALL_GATHER, ST_COMPUTE_HI, 0, static_cast<double>(hi - lo) * 2 * (d.dp - 1) / d.dp, GROUP_DP, mb, &e);
@@ -747,6 +759,41 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     const uint32_t pp_prev = b.stage > 0 ? b.stage - 1 : 0, pp_next = b.stage + 1;
 
     const double grad_scale = 1.0 / (static_cast<double>(T) * ga);
+
+    // ---- data-parallel gradient buckets (fused mode): reduce-scatter + AdamW (+ parameter all-gather) of a range of
+    // the flat space as ONE kernel on comm_dp. With dp_buckets every layer is a bucket, launched in the last
+    // microbatch's backward right after the layer's weight gradients, so it overlaps the layers below it.
+    const uint32_t dp_rank = rank / (d.tp * d.pp * d.cp) % std::max(1u, d.dp);
+    const bool dp_buckets = d.dp > 1 && b.fused && cfg.train.dp_buckets != 0 && tp == 1;
+    auto emit_bucket = [&](uint64_t lo, uint64_t hi, int max_ctas, uint16_t mb) {
+        if (hi > hdr_n_rep) hi = hdr_n_rep;
+        if (lo >= hi) return;
+        auto sub = [&](int flat, uint16_t tclass, uint16_t dt, uint64_t elem_off, uint64_t elems) {
+            const int id = b.tensor_at(tclass, dt, out->tensors[flat].offset + elem_off * dtype_size(dt), 1, 0, 0);
+            out->tensors[id].nbytes = elems * dtype_size(dt);
+            return id;
+        };
+        // what this rank's kernel touches: everybody's gradients of the bucket are read by the owners; the owner
+        // updates its part of master / m / v; parameters change in the bucket on every member (replicated) or in
+        // the owner's shard (ZeRO-3)
+        const uint64_t own_lo = std::max<uint64_t>(lo, static_cast<uint64_t>(dp_rank) * hdr_n_shard);
+        const uint64_t own_hi = std::min<uint64_t>(hi, static_cast<uint64_t>(dp_rank + 1) * hdr_n_shard);
+        ExecOp e = xop(K_RS_ADAMW, static_cast<uint16_t>((zero3 ? 1 : 0) | 2));   // flag 2: t[3] is a bucket of the flat gradients
+        e.t[3] = sub(b.flat_grad, TC_GRAD, DT_FP32, lo, hi - lo);
+        if (own_lo < own_hi) {
+            const uint64_t o = own_lo - static_cast<uint64_t>(dp_rank) * hdr_n_shard;
+            e.t[0] = sub(b.flat_master, TC_OPTSTATE, DT_FP32, o, own_hi - own_lo);
+            e.t[1] = sub(b.flat_m, TC_OPTSTATE, DT_FP32, o, own_hi - own_lo);
+            e.t[2] = sub(b.flat_v, TC_OPTSTATE, DT_FP32, o, own_hi - own_lo);
+            if (zero3) e.t[4] = sub(b.flat_param, TC_PARAM, DT_BF16, o, own_hi - own_lo);
+        }
+        if (!zero3) e.t[4] = sub(b.flat_param, TC_PARAM, DT_BF16, lo, hi - lo);
+        e.i[0] = static_cast<int32_t>(hdr_n_rep & 0xFFFFFFFFu); e.i[1] = static_cast<int32_t>(hdr_n_rep >> 32);
+        e.i[2] = static_cast<int32_t>(hdr_n_shard & 0xFFFFFFFFu); e.i[3] = GROUP_DP; e.i[4] = static_cast<int32_t>(b.next_seq++);
+        e.f[0] = 1.0f / d.dp;
+        e.f[1] = static_cast<float>(max_ctas);
+        b.push(OP_RS_ADAMW, ST_COMM_DP, 18.0 * (own_hi > own_lo ? own_hi - own_lo : 0), 4.0 * (hi - lo), GROUP_DP, mb, &e);
+    };
     std::vector<int> send_done(slots, -1);  // event recorded after a slot's activation send
 
     // ================================================================ forward of one layer
@@ -1011,6 +1058,13 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             wgrad(dqkv, a.xn1, w.wqkv.g, b.Cqkv, H, T);
             b.row_parallel(dqkv, w.wqkv.w, -1, dxn, partial, rs_tmp, H, b.Cqkv, true, mb);
             b.rmsnorm_bwd(a.x, w.g1.w, a.rstd1, dxn, dstream, w.g1.g, norm_scratch, Tl, true, !first_mb, mb);
+            if (dp_buckets && mb + 1 == ga) {
+                // the layer's gradients are complete on this rank: its bucket goes to comm_dp and runs under the
+                // backward of the layers below (a slice of the SMs is enough to keep NVLink busy)
+                b.sync(ST_COMPUTE_HI, ST_COMM_DP, mb);
+                if (lo_pending) b.sync(ST_COMPUTE_LO, ST_COMM_DP, mb);
+                emit_bucket(layer_range[l].first, layer_range[l].second, 64, mb);
+            }
         }
         join_lo();
         if (b.first_stage) {
@@ -1074,13 +1128,20 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     }
     if (d.dp > 1) {
         if (b.fused) {
-            ExecOp e = xop(K_RS_ADAMW, zero3 ? 1 : 0);   // flag 1: bf16 parameters are sharded too, write my shard only
-            e.t[0] = b.flat_master; e.t[1] = b.flat_m; e.t[2] = b.flat_v; e.t[3] = b.flat_grad; e.t[4] = b.flat_param;
-            e.i[0] = static_cast<int32_t>(n_rep & 0xFFFFFFFFu); e.i[1] = static_cast<int32_t>(n_rep >> 32);
-            e.i[2] = static_cast<int32_t>(n_shard & 0xFFFFFFFFu); e.i[3] = GROUP_DP; e.i[4] = static_cast<int32_t>(b.next_seq++);
-            e.f[0] = 1.0f / d.dp;
             b.sync(ST_COMPUTE_HI, ST_COMM_DP, 0);
-            b.push(OP_RS_ADAMW, ST_COMM_DP, 18.0 * n_shard, 4.0 * n_rep, GROUP_DP, 0, &e);
+            if (dp_buckets && b.layers > 0) {
+                // the layers went out during the backward pass; what is left are the parameters around them
+                // (embedding, final gain, head)
+                emit_bucket(0, layer_range.front().first, 0, 0);
+                emit_bucket(layer_range.back().second, n_rep, 0, 0);
+            } else {
+                ExecOp e = xop(K_RS_ADAMW, zero3 ? 1 : 0);   // flag 1: bf16 parameters are sharded too, write my shard only
+                e.t[0] = b.flat_master; e.t[1] = b.flat_m; e.t[2] = b.flat_v; e.t[3] = b.flat_grad; e.t[4] = b.flat_param;
+                e.i[0] = static_cast<int32_t>(n_rep & 0xFFFFFFFFu); e.i[1] = static_cast<int32_t>(n_rep >> 32);
+                e.i[2] = static_cast<int32_t>(n_shard & 0xFFFFFFFFu); e.i[3] = GROUP_DP; e.i[4] = static_cast<int32_t>(b.next_seq++);
+                e.f[0] = 1.0f / d.dp;
+                b.push(OP_RS_ADAMW, ST_COMM_DP, 18.0 * n_shard, 4.0 * n_rep, GROUP_DP, 0, &e);
+            }
             b.sync(ST_COMM_DP, ST_COMPUTE_HI, 0);
             if (n_exp) {
                 // the experts this rank owns: plain AdamW on the tail of the flat space
@@ -1122,7 +1183,9 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
 
     // ---------------- arena
     uint64_t want[TC_COUNT];
-    for (int c = 0; c < TC_COUNT; ++c) want[c] = align_up(b.cursor[c], kTensorAlign);
+    // every class segment ends with guard bytes that no tensor covers: the runtime fills them with a pattern and
+    // checks them in debug runs, so a kernel that runs past the last tensor of one class into the next is caught
+    for (int c = 0; c < TC_COUNT; ++c) want[c] = align_up(b.cursor[c], kTensorAlign) + (b.cursor[c] ? kSegmentGuardBytes : 0);
     Arena arena;
     arena_layout(&arena, want);
     arena_relocate(arena, out->tensors.data(), static_cast<uint32_t>(out->tensors.size()));

@@ -178,6 +178,7 @@ struct cai_exec {
     uint32_t pending_seq = 0;
     bool has_pending_gather = false;
     long long n_shard = 0;  // elements of the flat parameter space each data-parallel member owns
+    int flat_ids[5] = {-1, -1, -1, -1, -1};  // tensor ids of @flat_grad, @flat_param, @flat_master, @flat_m, @flat_v
 
     void* ptr(int t) const { return t >= 0 ? arena + tensors[t].offset : nullptr; }
     long long ld(int t) const { return shapes[static_cast<size_t>(t) * 4 + 2]; }
@@ -394,6 +395,20 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
             }
             const long long n_flat = (static_cast<long long>(static_cast<uint32_t>(x.i[1])) << 32) | static_cast<uint32_t>(x.i[0]);
             const long long n_shard = static_cast<uint32_t>(x.i[2]);
+            if (x.flags & 2) {
+                // a bucket of the flat space: the record's tensors are the slices it touches (for the hazard proof);
+                // the kernel indexes from the bases of the flat buffers
+                const int fg = ex->flat_ids[0], fp = ex->flat_ids[1], fm = ex->flat_ids[2], f1 = ex->flat_ids[3], f2 = ex->flat_ids[4];
+                if (fg < 0 || fp < 0 || fm < 0 || f1 < 0 || f2 < 0) {
+                    set_last_error("rs_adamw bucket: plan lacks the flat buffers");
+                    return CAI_K_BAD_ARG;
+                }
+                const long long lo = static_cast<long long>(ex->tensors[x.t[3]].offset - ex->tensors[fg].offset) / 4;
+                const long long hi = lo + static_cast<long long>(ex->tensors[x.t[3]].nbytes / 4);
+                return cai_fused_rs_adamw(pt, ex->tensors[fg].offset, ex->tensors[fp].offset, (float*)ex->ptr(fm), (float*)ex->ptr(f1),
+                                          (float*)ex->ptr(f2), n_flat, n_shard, ex->hyper_dev, x.f[0], seq, ex->counters_dev,
+                                          x.flags & 1, st, lo, hi, static_cast<int>(x.f[1]));
+            }
             return cai_fused_rs_adamw(pt, ex->tensors[x.t[3]].offset, ex->tensors[x.t[4]].offset, (float*)P(0), (float*)P(1),
                                       (float*)P(2), n_flat, n_shard, ex->hyper_dev, x.f[0], seq, ex->counters_dev, x.flags & 1, st);
         }
@@ -449,7 +464,7 @@ int replay(cai_exec* ex) {
         {
             // kernels of this library behind the op (memsets and NCCL calls are not ours)
             const uint16_t k = ex->exec[op.exec - 1].kernel;
-            ex->launches += (k == K_ATTN_BWD && ex->exec[op.exec - 1].flags) ? __builtin_popcount(ex->exec[op.exec - 1].flags) : (k == K_ATTN_BWD || k == K_CROSS_ENTROPY_TP || k == K_RMSNORM_BWD) ? 3 : (k == K_ZERO || (k >= K_NCCL_ALL_REDUCE && k <= K_NCCL_RECV) || (k == K_FSDP_AG_GEMM && (ex->exec[op.exec - 1].flags & 1))) ? 0 : 1;
+            ex->launches += (k == K_ATTN_BWD && ex->exec[op.exec - 1].flags) ? __builtin_popcount(ex->exec[op.exec - 1].flags) : (k == K_ATTN_BWD || k == K_CROSS_ENTROPY_TP || k == K_RMSNORM_BWD) ? 3 : (k == K_MOE_ROUTE && !(ex->exec[op.exec - 1].flags & 1)) ? 2 : (k == K_ZERO || (k >= K_NCCL_ALL_REDUCE && k <= K_NCCL_RECV) || (k == K_FSDP_AG_GEMM && (ex->exec[op.exec - 1].flags & 1))) ? 0 : 1;
         }
         if (tr) cudaEventRecord(tr->stop, st);
     }
@@ -554,8 +569,12 @@ CAI_API int cai_exec_create(cai_exec** out, const void* plan_bytes, size_t nbyte
             if (x.kernel == K_AG_GEMM || x.kernel == K_GEMM_RS || x.kernel == K_RS_ADAMW || x.kernel == K_MOE_DISPATCH_GEMM ||
                 x.kernel == K_MOE_GEMM_COMBINE || x.kernel == K_FSDP_AG_GEMM)
                 ++fused;
-        for (const NamedTensor& nt : ex->named)
+        static const char* const flat_names[5] = {"@flat_grad", "@flat_param", "@flat_master", "@flat_m", "@flat_v"};
+        for (const NamedTensor& nt : ex->named) {
             if (!strcmp(nt.name, "@flat_split")) ex->n_shard = static_cast<long long>(nt.rows) << 9;
+            for (int k = 0; k < 5; ++k)
+                if (!strcmp(nt.name, flat_names[k])) ex->flat_ids[k] = nt.tensor;
+        }
         ex->epochs_per_step = 2 * fused + 2;
     }
     *out = ex;

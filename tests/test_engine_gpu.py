@@ -256,3 +256,21 @@ def test_c_trainer_runs_an_executable_plan_on_the_device(tmp_path):
     assert r2.returncode == 0 and "resumed from checkpoint at step 6" in r2.stderr
     rows2 = [l.split("|") for l in r2.stdout.splitlines() if l[:4].strip().isdigit()]
     assert [int(x[0]) for x in rows2] == [6, 7] and float(rows2[0][-1]) < losses[0]
+
+
+def test_guard_bytes_between_arena_segments_catch_an_overrun():
+    """The compiler leaves guard bytes behind the tensors of every class; after a step they are intact, and a
+    write just past the last tensor of a class (what an overrunning kernel would do) is reported."""
+    from cai_b200.runtime.engine import synthetic_batch
+    eng = _engine()
+    m = eng.model
+    rows = eng.hdr.num_microbatches * m.microbatch
+    tok, tgt = synthetic_batch(m.vocab_size, m.seq_len, rows, step=0, seed=0)
+    eng.step(tok, tgt)
+    assert len(eng._inner_guards) >= 4 and all(hi - lo >= 1024 for lo, hi in eng._inner_guards[:-1])
+    assert eng.check_canaries()
+    lo, hi = eng._inner_guards[1]
+    eng.arena[eng._arena_shift + lo] = 0
+    with pytest.raises(RuntimeError, match="between arena segments"):
+        eng.check_canaries()
+    eng.close()

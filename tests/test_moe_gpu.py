@@ -52,6 +52,12 @@ def test_router_capacity_drops():
     first = pos[idx == 3]
     assert (first >= 0).sum().item() == 128 and (first < 0).sum().item() == 512 - 128
     assert counts[3].item() == 512
+    # slots go out in token order: the first 128 tokens keep the expert, token t sits in row t, and a second
+    # run gives the same assignment
+    tok_slot = pos[:, 0] if bool((idx[:, 0] == 3).all()) else pos[idx == 3]
+    assert torch.equal(tok_slot[:128].long(), torch.arange(128, device="cuda")) and bool((tok_slot[128:] < 0).all())
+    idx2, w2, pos2, counts2 = ops.moe_route_fwd(logits, 2, cap=128)
+    assert torch.equal(pos, pos2) and torch.equal(idx, idx2) and torch.equal(counts, counts2)
 
 
 def test_first_step_loss_and_grads_match_fp32_reference():
