@@ -120,9 +120,92 @@ def _time(fn, iters, warmup, flush):
     return t.item()
 
 
+STAMP_WORDS = ("entry", "first_ready", "first_acc", "last_epilogue", "reduce_start", "reduce_flags", "end", "copy_done")
+
+
+def _phase_summary(buf):
+    """Per-CTA stamp records (globaltimer ns, 8 words per CTA) -> microseconds since the first CTA entered."""
+    t = buf.view(-1, 8).cpu().numpy().astype("float64")
+    live = t[t[:, 0] > 0]
+    if not len(live):
+        return {}
+    t0 = live[:, 0].min()
+    out = {"ctas": int(len(live))}
+    for i, name in enumerate(STAMP_WORDS):
+        col = live[:, i][live[:, i] > 0]
+        if len(col):
+            out[name] = {"min": (col.min() - t0) / 1e3, "median": (statistics.median(col.tolist()) - t0) / 1e3,
+                         "max": (col.max() - t0) / 1e3}
+    return out
+
+
+def tp_chain(a, pb, L, rank, world, dev, st, flush, gemm_peak, res):
+    """The pattern of a tensor-parallel MLP in steady state: x_local[T/n, H] -> all-gather -> GEMM (W1[F, H]) ->
+    GEMM (W2[H, F]) -> reduce-scatter -> x_local, `--chain` times back to back without a host synchronisation, as
+    the executor enqueues it. Reports the time per pair against the same chain through NCCL and, from the last
+    pair, where the CTAs of each kernel spent their time (per-CTA globaltimer stamps)."""
+    bf = torch.bfloat16
+    T, F, H = a.tokens, a.out_features, a.in_features
+    Tl = T // world
+    x_local, x_off = pb.alloc((Tl, H), bf)
+    a_full, _ = pb.alloc((T, H), bf)
+    _, stage_off = pb.alloc((world, Tl, H), bf)
+    x_local.copy_(torch.randn(Tl, H, device=dev))
+    W1 = (torch.randn(F, H, device=dev) * H ** -0.5).to(bf)
+    W2 = (torch.randn(H, F, device=dev) * (F * world) ** -0.5).to(bf)
+    y = torch.empty(T, F, device=dev, dtype=bf)
+    L.cai_fused_debug_stamps.argtypes = [c_void_p]
+    stamps = [torch.zeros(256 * 8, dtype=torch.int64, device=dev) for _ in range(2)]
+    dist.barrier()
+
+    def pair(with_stamps=False):
+        if with_stamps:
+            L.cai_fused_debug_stamps(c_void_p(stamps[0].data_ptr()))
+        klib.check(L.cai_fused_ag_gemm_c(pb.bases, rank, world, 0, GROUP_TP, x_off, H, a_full.data_ptr(), W1.data_ptr(), y.data_ptr(),
+                                         T, F, H, H, F, 0, pb.epoch.data_ptr(), pb.next_seq(), a.copy_ctas, st), "ag_gemm")
+        if with_stamps:
+            L.cai_fused_debug_stamps(c_void_p(stamps[1].data_ptr()))
+        klib.check(L.cai_fused_gemm_rs_c(pb.bases, rank, world, 0, GROUP_TP, y.data_ptr(), W2.data_ptr(), stage_off, x_local.data_ptr(),
+                                         None, T, H, F, F, F, H, 0, 0, pb.epoch.data_ptr(), pb.next_seq(), st), "gemm_rs")
+        if with_stamps:
+            L.cai_fused_debug_stamps(None)
+
+    def fused():
+        for i in range(a.chain):
+            pair(with_stamps=(i == a.chain - 1))
+
+    gathered = torch.empty(T, H, device=dev, dtype=bf)
+    partial = torch.empty(T, H, device=dev, dtype=bf)
+    xb = x_local.clone()
+
+    def baseline():
+        for _ in range(a.chain):
+            dist.all_gather_into_tensor(gathered, xb)
+            gemm(gathered, W1, out=y)
+            gemm(y, W2, out=partial)
+            dist.reduce_scatter_tensor(xb, partial)
+
+    ms_f = _time(fused, a.iters, a.warmup, flush) / a.chain
+    ms_b = _time(baseline, a.iters, a.warmup, flush) / a.chain
+    flops = 2.0 * 2.0 * T * F * H
+    link = 2 * (world - 1) * Tl * H * 2          # rows pulled by the gather + partial rows pushed by the reduce-scatter
+    roof = max(flops / (gemm_peak * 1e12), link / (NVLINK_GBS * 1e9))
+    phases = {"ag_gemm": _phase_summary(stamps[0]), "gemm_rs": _phase_summary(stamps[1])}
+    allp = [None] * world
+    dist.all_gather_object(allp, phases)
+    res.update(T=T, N=F, K=H, chain=a.chain, fused_us_per_pair=ms_f * 1e3, nccl_path_us_per_pair=ms_b * 1e3,
+               speedup_vs_nccl_path=ms_b / ms_f, roofline_us_per_pair=roof * 1e6, frac_of_roofline=roof / (ms_f * 1e-3),
+               link_bytes_per_pair=link, status=klib.device_status(clear=True), fused_us=ms_f * 1e3, phases_us_by_rank=allp)
+    if rank == 0:
+        print(json.dumps(res), flush=True)
+    pb.close()
+    dist.destroy_process_group()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", choices=["ag_gemm", "gemm_rs", "rs_adamw", "gather_gemm", "moe_exchange"], required=True)
+    ap.add_argument("--op", choices=["ag_gemm", "gemm_rs", "rs_adamw", "gather_gemm", "moe_exchange", "tp_chain"], required=True)
+    ap.add_argument("--chain", type=int, default=24, help="tp_chain: all-gather -> GEMM / GEMM -> reduce-scatter pairs enqueued back to back")
     ap.add_argument("--params", type=int, default=256 << 20, help="rs_adamw: elements of the flat parameter space")
     ap.add_argument("--experts", type=int, default=64)
     ap.add_argument("--top-k", type=int, default=8)
@@ -161,6 +244,8 @@ def main(argv=None):
     peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
     gemm_peak = peaks.get("bf16_tflops", 1590.0)
     res = {"op": a.op, "world": world, "T": T, "N": N, "K": K}
+    if a.op == "tp_chain":
+        return tp_chain(a, pb, L, rank, world, dev, st, flush, gemm_peak, res)
     if a.op == "ag_gemm":
         # C[T,N] = gather(x_local[Tl,K]) @ W[N,K]^T
         x_local, x_off = pb.alloc((Tl, K), bf)

@@ -72,7 +72,23 @@ struct GemmParams {
     GatherJob gat;
     long long b_elem_off;
     long long ldb;
+    // ---- optional per-CTA time stamps (globaltimer, ns) for the phase tables of the fused modes: 8 words per CTA,
+    // see kStamp*; null in production launches.
+    unsigned long long* stamps;
 };
+
+// words of a CTA's stamp record
+constexpr int kStampEntry = 0;        // kernel entry
+constexpr int kStampFirstReady = 1;   // first tile's operands may be loaded (all-gather: its rows are staged)
+constexpr int kStampFirstAcc = 2;     // first accumulator complete
+constexpr int kStampLastEpi = 3;      // last tile's epilogue (and pushes) done
+constexpr int kStampReduceStart = 4;  // reduce-scatter: reduce phase entered
+constexpr int kStampReduceFlags = 5;  // reduce-scatter: every member's partial of the first item has arrived
+constexpr int kStampEnd = 6;          // CTA done
+constexpr int kStampCopyDone = 7;     // all-gather copy CTA: last unit staged
+__device__ __forceinline__ void stamp(const GemmParams& p, int word) {
+    if (p.stamps) p.stamps[static_cast<size_t>(blockIdx.x) * 8 + word] = global_timer_ns();
+}
 
 __device__ __forceinline__ bool seg_live(const GemmParams& p, int g, int row0) {
     const int slab = row0 / p.seg_rows;
@@ -197,12 +213,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // that owns those rows (peer stores) and raises a per-tile flag there; when a CTA has no GEMM
     // tiles left it sums, for output tiles of its own rows, the partials of all members (+ residual).
     uint32_t epoch = 0;
+    if (threadIdx.x == 0) stamp(p, kStampEntry);
     if (p.mode != kGemmPlain) {
         epoch = *p.epoch_base + 2 * p.seq;
         if (p.mode == kGemmAllGatherA) {
             if (blockIdx.x == 0 && threadIdx.x == 0) signal_all(p.pt, p.group_kind, kSigEntry + p.pt.rank, epoch);
             if (static_cast<int>(blockIdx.x) < p.n_copy) {
                 allgather_copy_role(p, epoch, smem, bars);
+                if (threadIdx.x == 0) stamp(p, kStampCopyDone);
                 return;
             }
         }
@@ -290,6 +308,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         break;
                     }
                 }
+                if (tile == cta) stamp(p, kStampFirstReady);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (p.seg_mode == 2 && !seg_live(p, grp, kb * kBK)) continue;
                     if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, CAI_DEV_TIMEOUT_TMA_EMPTY)) {
@@ -410,6 +429,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 break;
             }
             tc_fence_after();
+            if (t == 1 && warp == 2 && lane == 0) stamp(p, kStampFirstAcc);
             if constexpr (RS) {
                 // Reduce-scatter epilogue: the warp's 32 rows x BN bf16 are staged in shared memory
                 // and every lane hands its row (one contiguous run in the owner's staging buffer) to
@@ -593,6 +613,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (lane == 0) mbar_arrive(&tmem_empty[acc]);
             }
         }
+        if constexpr (!RS) {
+            if (warp == 2 && lane == 0) stamp(p, kStampLastEpi);
+        }
         if constexpr (RS) {
             // the last tile's stores: wait for completion, then announce it
             asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -602,6 +625,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 __threadfence_system();
                 st_release_sys(sig_word(p.pt, rs_prev_owner, p.group_kind, kSigTile + p.pt.rank * kSigTileSlots + rs_prev_slot), epoch);
             }
+            if (warp == 2 && lane == 0) stamp(p, kStampLastEpi);
         }
     }
 
@@ -612,6 +636,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int blocks_per_rank = p.rows_per_rank / kBM;
         const int items = blocks_per_rank * p.tiles_n;
         const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.pt.base[p.pt.rank] + p.stage_off);
+        if (threadIdx.x == 0) stamp(p, kStampReduceStart);
         for (int item = cta; item < items; item += ncta) {
             if (threadIdx.x == 0) {
                 int good = 1;
@@ -619,6 +644,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     good = wait_flag_ge(sig_word(p.pt, p.pt.rank, p.group_kind, kSigTile + src * kSigTileSlots + item), epoch,
                                         p.status) ? 1 : 0;
                 red_ok = good;
+                if (item == cta) stamp(p, kStampReduceFlags);
             }
             __syncthreads();
             if (!red_ok) break;
@@ -676,6 +702,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) stamp(p, kStampEnd);
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
@@ -719,6 +746,9 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
     return CAI_K_OK;
 }
 
+// Debug aid of the micro-benchmarks: when set, the next launches of the fused modes record per-CTA time stamps.
+static unsigned long long* g_stamp_buf[64] = {};
+
 // Picks the tile width, encodes the tensor maps and launches. `p` carries everything but the
 // tile bookkeeping.
 static int gemm_dispatch(const void* A, const void* B, long long lda, long long ldb, GemmParams& p, int sm_limit,
@@ -750,6 +780,7 @@ static int gemm_dispatch(const void* A, const void* B, long long lda, long long 
     else ok = encode_tmap_2d(&tmB, B, K + xb, N, ldb, 64, kBK, 2);
     if (!ok) return CAI_K_BAD_ARG;
     p.status = status_words(dev);
+    p.stamps = p.mode != kGemmPlain ? g_stamp_buf[dev & 63] : nullptr;
     if (p.mode == kGemmReduceScatter) {
         if (BN == 256) return launch_gemm<256, 4, true>(tmA, tmB, p, sms, st);
         return launch_gemm<128, 6, true>(tmA, tmB, p, sms, st);
@@ -765,7 +796,7 @@ static void plain_params(GemmParams& p) {
     p.pt = PeerTable{};
     p.seg_counts = nullptr; p.seg_rows = 0; p.seg_mode = 0;
     p.groups = 1; p.grp_a = p.grp_b = p.grp_c = 0; p.grp_seg = 0;
-    p.gat = GatherJob{}; p.b_elem_off = 0; p.ldb = 0;
+    p.gat = GatherJob{}; p.b_elem_off = 0; p.ldb = 0; p.stamps = nullptr;
     p.R = nullptr; p.ldr = 0; p.alpha = 1.f; p.epi = CAI_EPI_BF16; p.a_mn = 0;
 }
 
@@ -944,6 +975,14 @@ int cai_fused_gather_gemm(const PeerTable& pt, const cai::GatherJob& job_in, con
     p.b_elem_off = b_off;
     p.ldb = ldb;
     return gemm_dispatch(A, B, lda, ldb, p, 0, st);
+}
+
+// Per-CTA phase stamps of the fused GEMM modes: `buf` holds 8 x 256 uint64 (device memory, zeroed by the caller) or is
+// null to switch the stamps off. Word layout: kernel entry, first tile ready, first accumulator, last epilogue,
+// reduce start, reduce flags seen, CTA end, copy CTA done (globaltimer ns). Used by cai_b200/parallel/fused_bench.py.
+CAI_API int cai_fused_debug_stamps(void* buf) {
+    g_stamp_buf[current_device() & 63] = static_cast<unsigned long long*>(buf);
+    return 0;
 }
 
 // ---- C forms of the fused GEMMs with explicit member bases (tests, micro-benchmarks, other runtimes).

@@ -199,11 +199,112 @@ reduce_parts_kernel(const float* __restrict__ parts, float* __restrict__ out, in
     }
 }
 
+// Backward in ONE sweep for H <= 2048: a warp keeps a row of x and dy in registers, writes dx and adds the row's
+// dy * x * rstd into per-lane column sums that it carries across all the rows it handles; at the end the warps of
+// a CTA combine their sums in shared memory and the CTA writes one partial row of the gain gradient. x and dy are
+// read once (the two-kernel form above reads them twice).
+static __global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g,
+                         const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dy,
+                         __nv_bfloat16* __restrict__ dx, float* __restrict__ dg_partial, int rows, int H, int dx_acc) {
+    __shared__ float sdg[kNormWarpCols];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int c = threadIdx.x; c < kNormWarpCols; c += kNormThreads) sdg[c] = 0.f;
+    __syncthreads();
+    uint4 gv[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const int col = (c * 32 + lane) * 8;
+        gv[c] = col < H ? reinterpret_cast<const uint4*>(g)[col >> 3] : make_uint4(0u, 0u, 0u, 0u);
+    }
+    float acc[8][8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[c][e] = 0.f;
+    const long long nwarps = static_cast<long long>(gridDim.x) * (kNormThreads / 32);
+    for (long long row = static_cast<long long>(blockIdx.x) * (kNormThreads / 32) + warp; row < rows; row += nwarps) {
+        const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+        const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * H);
+        uint4* dxr = reinterpret_cast<uint4*>(dx + row * H);
+        uint4 xv[8], dv[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const int col = (c * 32 + lane) * 8;
+            if (col < H) {
+                xv[c] = xr[col >> 3];
+                dv[c] = dyr[col >> 3];
+            }
+        }
+        float S = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const int col = (c * 32 + lane) * 8;
+            if (col < H) {
+                float xf[8], df[8], gf[8];
+                unpack8(xv[c], xf);
+                unpack8(dv[c], df);
+                unpack8(gv[c], gf);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) S += df[e] * gf[e] * xf[e];
+            }
+        }
+        S = warp_sum(S);
+        const float rr = rstd[row];
+        const float k3 = rr * rr * rr * S / H;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const int col = (c * 32 + lane) * 8;
+            if (col < H) {
+                float xf[8], df[8], gf[8], o[8];
+                unpack8(xv[c], xf);
+                unpack8(dv[c], df);
+                unpack8(gv[c], gf);
+                if (dx_acc) unpack8(dxr[col >> 3], o);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float v = rr * df[e] * gf[e] - k3 * xf[e];
+                    o[e] = dx_acc ? o[e] + v : v;
+                    acc[c][e] += df[e] * xf[e] * rr;
+                }
+                dxr[col >> 3] = pack8(o);
+            }
+        }
+    }
+    // warps take turns adding into the CTA's row (a fixed order, so the result does not depend on timing)
+    for (int w = 0; w < kNormThreads / 32; ++w) {
+        if (w == warp) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int col = (c * 32 + lane) * 8;
+                if (col < H) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) sdg[col + e] += acc[c][e];
+                }
+            }
+        }
+        __syncthreads();
+    }
+    for (int c = threadIdx.x; c < H; c += kNormThreads) dg_partial[static_cast<long long>(blockIdx.x) * H + c] = sdg[c];
+}
+
 // Host side of RMSNorm backward, shared by the entry points: `scratch` holds at most `parts_cap`
 // rows of H floats. Returns a cudaError_t-style 0 / non-zero.
 static inline int launch_rmsnorm_bwd(const void* x, const void* g, const float* rstd, const void* dy, void* dx, float* dg,
                                      float* scratch, int parts_cap, int sms, int rows, int H, int dx_accumulate,
                                      int dg_accumulate, cudaStream_t st) {
+    if (H <= kNormWarpCols && (H & 7) == 0 && parts_cap >= 1) {
+        // one sweep: dx and the partial gain gradients from the same read of x and dy
+        long long want = (static_cast<long long>(rows) + 7) / 8;
+        int grid = static_cast<int>(want < 2LL * sms ? want : 2LL * sms);
+        if (grid > parts_cap) grid = parts_cap;
+        if (grid < 1) grid = 1;
+        rmsnorm_bwd_fused_kernel<<<grid, kNormThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(g),
+                                                               rstd, static_cast<const __nv_bfloat16*>(dy),
+                                                               static_cast<__nv_bfloat16*>(dx), scratch, rows, H, dx_accumulate);
+        reduce_parts_kernel<<<(H + 31) / 32, 256, 0, st>>>(scratch, dg, grid, H, dg_accumulate);
+        return cudaGetLastError() == cudaSuccess ? 0 : 1;
+    }
     const int R = (H + kNormWarpCols - 1) / kNormWarpCols;
     const int groups = 8 / R;
     const long long want = (static_cast<long long>(rows) + groups - 1) / groups;

@@ -406,14 +406,24 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     // Microbatches launched together (TrainSpec::mb_group). A pipeline keeps the configured granularity (fewer,
     // larger microbatches would widen its bubble); the per-tile signal slots of the fused TP kernels bound the rows.
     uint32_t mb_group = cfg.train.mb_group;
-    if (mb_group == 0) mb_group = (d.tp > 1 && d.pp == 1 && !moe && d.num_microbatches % 2 == 0) ? 2 : 1;
+    auto rows_fit = [&](uint32_t g) {
+        const uint64_t rows = static_cast<uint64_t>(g) * m.microbatch * m.seq_len;
+        return rows / 128 <= kSigLocalSlots && !(d.tp > 1 && (rows / d.tp / 128) * ((m.hidden_size + 127) / 128) > kSigTileSlots);
+    };
+    if (mb_group == 0) {
+        // as many as divide grad_accum and keep a launch at or under 16384 tokens (a launch that size fills the GPU
+        // and amortises the hand-shakes of the fused kernels; activation memory grows with it)
+        mb_group = 1;
+        if (d.pp == 1 && !moe && cfg.train.zero_stage < 3)
+            for (uint32_t g = 2; g <= d.num_microbatches; g *= 2)
+                if (d.num_microbatches % g == 0 && static_cast<uint64_t>(g) * m.microbatch * m.seq_len <= 16384 && rows_fit(g)) mb_group = g;
+    }
     if (mb_group > 1) {
         if (d.pp != 1) return failf(err, ERR_INVALID, "mb_group > 1 needs pp = 1 (got pp=%u)", d.pp);
         if (d.num_microbatches % mb_group) return failf(err, ERR_INVALID, "mb_group=%u must divide grad_accum=%u", mb_group, d.num_microbatches);
-        const uint64_t rows = static_cast<uint64_t>(mb_group) * m.microbatch * m.seq_len;
-        if (rows / 128 > kSigLocalSlots || (d.tp > 1 && (rows / d.tp / 128) * ((m.hidden_size + 127) / 128) > kSigTileSlots))
+        if (!rows_fit(mb_group))
             return failf(err, ERR_INVALID, "mb_group=%u: %llu rows per launch exceed the signal slots of the fused kernels", mb_group,
-                         static_cast<unsigned long long>(rows));
+                         static_cast<unsigned long long>(mb_group) * m.microbatch * m.seq_len);
     }
     if ((m.vocab_size / d.tp) % 8 || m.hidden_size % 8 || (m.ffn_hidden / d.tp) % 8)
         return failf(err, ERR_INVALID, "local hidden / ffn / vocab sizes must be multiples of 8");
@@ -654,6 +664,9 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     const bool overlap_wgrad = tp > 1 && !moe && cfg.train.wgrad_overlap != 0;
     // SwiGLU (forward and backward) rides in the epilogues of the gate/up and down-gradient products
     const bool fuse_swiglu = cfg.train.fuse_swiglu != 0 && !moe && !fp8 && b.F_l % 128 == 0;
+    // The backward form is opt-in (fuse_swiglu = 2): its epilogue reads gate / up row by row next to the stores and
+    // is slower than the product it rides on (measured 53 ms against 23 + 11 ms per step for the two kernels)
+    const bool fuse_swiglu_bwd = fuse_swiglu && cfg.train.fuse_swiglu >= 2;
     const int dfull_attn = overlap_wgrad ? b.tensor(TC_WORKSPACE, DT_BF16, T, H) : dfull;
     const int dqkv = b.tensor(TC_WORKSPACE, DT_BF16, T, b.Cqkv);
     const int dao = b.tensor(TC_WORKSPACE, DT_BF16, T, b.Hq_l);
@@ -792,7 +805,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         e.i[2] = static_cast<int32_t>(hdr_n_shard & 0xFFFFFFFFu); e.i[3] = GROUP_DP; e.i[4] = static_cast<int32_t>(b.next_seq++);
         e.f[0] = 1.0f / d.dp;
         e.f[1] = static_cast<float>(max_ctas);
-        b.push(OP_RS_ADAMW, ST_COMM_DP, 18.0 * (own_hi > own_lo ? own_hi - own_lo : 0), 4.0 * (hi - lo), GROUP_DP, mb, &e);
+        b.push(OP_RS_ADAMW, ST_COMM_DP, 18.0 * (hi - lo) / d.dp, 4.0 * (hi - lo), GROUP_DP, mb, &e);   // cost: rank-independent
     };
     std::vector<int> send_done(slots, -1);  // event recorded after a slot's activation send
 
@@ -1006,7 +1019,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             } else {
             // ---- MLP block: x_next = hmid + act * Wd^T
             prepare_layer(l, true, mb);                                                           // ZeRO-3 re-gather, top of the range first
-            if (fuse_swiglu) {
+            if (fuse_swiglu_bwd) {
                 // dact = gather(dx) * Wd never reaches memory: the epilogue turns it into [dgate | dup]
                 b.col_parallel(dstream, dfull, w.wd.w, dgu, b.F_l, H, true, mb, 5, a.gu);
                 wgrad(g_rows, a.act, w.wd.g, H, b.F_l, T);                                        // dWd = dx^T act

@@ -163,15 +163,16 @@ struct TrainSpec {
     uint32_t zero_stage = 1;      // 1 = optimizer state sharded over dp (fused path), 3 = bf16 parameters sharded too
     uint32_t fp8_block = 128;
     uint32_t comm_mode = 1;       // 0 = NCCL-only baseline ops, 1 = fused compute+collective kernels
-    uint32_t ce_chunk = 1024;     // rows of logits materialised at a time
+    uint32_t ce_chunk = 4096;     // rows of logits materialised at a time (the head's weight gradient is read-modify-written once per chunk)
     uint32_t moe_capacity_factor_x100 = 200;
     uint32_t wgrad_overlap = 1;   // tp > 1: weight-gradient GEMMs run on compute_lo next to the backward's critical path
     // Microbatches of a step are independent until the optimizer. With pp = 1 the schedule may launch `mb_group`
     // of them together (their sequences side by side in one activation set): the same tokens, loss and gradients
-    // with 1/mb_group as many kernel launches and collective hand-shakes. 0 = chosen by the compiler (2 under
-    // tensor parallelism when grad_accum is even, otherwise 1).
+    // with 1/mb_group as many kernel launches and collective hand-shakes. 0 = chosen by the compiler (dense models
+    // without a pipeline or parameter sharding: the largest power of two that divides grad_accum and keeps a launch
+    // at or under 16384 tokens; otherwise 1).
     uint32_t mb_group = 0;
-    uint32_t fuse_swiglu = 1;     // SwiGLU forward inside the gate/up GEMM epilogue (gate/up weight rows interleaved)
+    uint32_t fuse_swiglu = 1;     // 1: SwiGLU forward inside the gate/up GEMM epilogue; 2: also its backward inside the down-gradient GEMM
     uint32_t dp_buckets = 1;      // dp > 1, fused: gradient reduce-scatter + AdamW per layer bucket, overlapped with backward
     uint32_t wait_limit_ms = 0;   // bounded device-side waits: 0 = the library default (about a second)
     uint32_t reserved[4] = {0, 0, 0, 0};

@@ -419,6 +419,18 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
     }
 }
 
+// How many kernels of this library one exec record launches (memsets and NCCL calls are not ours).
+int own_kernels_of(const ExecOp& x) {
+    const uint16_t k = x.kernel;
+    if (k == K_ZERO || (k >= K_NCCL_ALL_REDUCE && k <= K_NCCL_RECV)) return 0;
+    if (k == K_FSDP_AG_GEMM && (x.flags & 1)) return 0;            // rides in the GEMM that follows
+    if (k == K_ATTN_BWD) return x.flags ? __builtin_popcount(x.flags) : 3;
+    if (k == K_CROSS_ENTROPY_TP) return 3;
+    if (k == K_RMSNORM_BWD) return x.i[1] <= 2048 ? 2 : 3;         // one sweep + reduce, or dg / reduce / dx
+    if (k == K_MOE_ROUTE && !(x.flags & 1)) return 2;              // top-k, then slots in token order
+    return 1;
+}
+
 // names of the kernel ids, for NVTX ranges (same order as the enum in plan/formats.h)
 const char* kernel_label(uint16_t k) {
     static const char* n[K_COUNT] = {"none", "embed_fwd", "embed_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "gemm", "rope", "attn_fwd",
@@ -462,9 +474,7 @@ int replay(cai_exec* ex) {
         if (ex->nvtx_on) nvtxRangePop();
         if (rc != 0) return rc;
         {
-            // kernels of this library behind the op (memsets and NCCL calls are not ours)
-            const uint16_t k = ex->exec[op.exec - 1].kernel;
-            ex->launches += (k == K_ATTN_BWD && ex->exec[op.exec - 1].flags) ? __builtin_popcount(ex->exec[op.exec - 1].flags) : (k == K_ATTN_BWD || k == K_CROSS_ENTROPY_TP || k == K_RMSNORM_BWD) ? 3 : (k == K_MOE_ROUTE && !(ex->exec[op.exec - 1].flags & 1)) ? 2 : (k == K_ZERO || (k >= K_NCCL_ALL_REDUCE && k <= K_NCCL_RECV) || (k == K_FSDP_AG_GEMM && (ex->exec[op.exec - 1].flags & 1))) ? 0 : 1;
+            ex->launches += own_kernels_of(ex->exec[op.exec - 1]);
         }
         if (tr) cudaEventRecord(tr->stop, st);
     }

@@ -22,7 +22,7 @@ def _ref_attention(qkv, B, S, nh, nkv, hd):
 
 
 @pytest.mark.parametrize("B,S,nh,nkv", [(1, 128, 2, 2), (2, 256, 4, 2), (1, 384, 4, 1), (1, 1024, 8, 2),
-                                        (2, 2048, 4, 4)])
+                                        (2, 2048, 4, 4), (1, 4096, 16, 8)])
 @pytest.mark.parametrize("variant", [1, 2])
 def test_flash_attn_fwd(B, S, nh, nkv, variant):
     from cai_b200 import ops
@@ -37,7 +37,12 @@ def test_flash_attn_fwd(B, S, nh, nkv, variant):
     assert torch.allclose(lse, lse_ref, atol=2e-2, rtol=1e-3)
 
 
-@pytest.mark.parametrize("B,S,nh,nkv", [(1, 128, 2, 2), (2, 256, 4, 2), (1, 384, 4, 1), (1, 1024, 8, 2)])
+# The dK / dV kernel has two forms: one CTA per kv group looping over the group's query heads (grids that fill
+# the GPU: B * kv groups * key tiles >= SM count) and one CTA per query head with chained adds (small grids).
+# (1, 4096, 16, 8) is the shape of the headline model on one GPU and takes the first form with two heads per
+# group; (1, 512, 8, 1) chains eight heads; (2, 4096, 2, 1) is the tp = 8 shape with two microbatches per launch.
+@pytest.mark.parametrize("B,S,nh,nkv", [(1, 128, 2, 2), (2, 256, 4, 2), (1, 384, 4, 1), (1, 1024, 8, 2),
+                                        (1, 4096, 16, 8), (1, 512, 8, 1), (2, 4096, 2, 1)])
 def test_flash_attn_bwd(B, S, nh, nkv):
     from cai_b200 import ops
     if not hasattr(ops.lib(), "cai_flash_attn_bwd"):

@@ -111,7 +111,7 @@ def test_trace_has_measured_times():
     tok, tgt = synthetic_batch(m.vocab_size, m.seq_len, rows, step=0, seed=0)
     eng.step(tok, tgt)
     recs = eng.trace_step(tok, tgt)
-    assert len(recs) >= 100
+    assert len(recs) >= 40
     assert all(r.end_s >= r.start_s for r in recs)
     assert sum(r.end_s - r.start_s for r in recs) > 0
     eng.close()
@@ -274,3 +274,24 @@ def test_guard_bytes_between_arena_segments_catch_an_overrun():
     with pytest.raises(RuntimeError, match="between arena segments"):
         eng.check_canaries()
     eng.close()
+
+
+def test_swiglu_fused_into_the_gemms_trains_like_the_standalone_kernels():
+    """fuse_swiglu = 0 (stand-alone SwiGLU kernels), 1 (forward in the gate/up GEMM epilogue, the default) and 2 (also
+    the backward in the down-gradient GEMM epilogue) are the same arithmetic on the same bf16 intermediates."""
+    from cai_b200.runtime.engine import Engine, synthetic_batch
+    base = (ROOT / "configs" / "tiny.cfg").read_text()
+    curves, grads = [], []
+    for mode in (0, 1, 2):
+        eng = Engine(config_text=base + f"\nfuse_swiglu = {mode}\n", rank=0, world=1, local_rank=0)
+        m = eng.model
+        rows = eng.hdr.num_microbatches * m.microbatch
+        tok, tgt = synthetic_batch(m.vocab_size, m.seq_len, rows, step=0, seed=0)
+        first = eng.step(tok, tgt, lr=0.0)
+        grads.append(eng.grad("L0.wgu").float().clone())
+        curves.append([first] + [eng.step(tok, tgt) for _ in range(3)])
+        eng.close()
+    for c in curves[1:]:
+        assert all(abs(a - b) <= 2e-3 * max(1.0, abs(a)) for a, b in zip(curves[0], c)), curves
+    for g in grads[1:]:
+        assert ((g - grads[0]).norm() / grads[0].norm()).item() < 1e-2

@@ -114,3 +114,38 @@ def test_tp2_pp2_cuda_graph(tmp_path, single):
         pytest.skip("needs 4 GPUs")
     r = run_case(tmp_path, 4, tp=2, pp=2, comm="baseline", graph=1)
     close(r["losses"], single["losses"])
+
+
+def test_tp2_pp2_fused(tmp_path, single):
+    """Pipeline stages whose layers run the fused all-gather -> GEMM / GEMM -> reduce-scatter kernels."""
+    if _gpus() < 4:
+        pytest.skip("needs 4 GPUs")
+    r = run_case(tmp_path, 4, tp=2, pp=2, comm="fused")
+    close(r["losses"], single["losses"])
+
+
+def test_tensor_parallel_8_fused(tmp_path):
+    if _gpus() < 8:
+        pytest.skip("needs 8 GPUs")
+    one = run_case(tmp_path, 1, config="tiny_tp8")
+    r = run_case(tmp_path, 8, config="tiny_tp8", tp=8, comm="fused")
+    close(r["losses"], one["losses"])
+
+
+def test_expert_parallel_8_matches_replicated_experts(tmp_path):
+    """The MoE model on 8 GPUs: experts sharded over all of them (ep = 8) against experts replicated (ep = 1),
+    same global batch; the curves agree within 2 % and fall."""
+    if _gpus() < 8:
+        pytest.skip("needs 8 GPUs")
+    a = run_case(tmp_path, 8, config="tiny_moe", comm="fused", ep=1, steps=8)
+    b = run_case(tmp_path, 8, config="tiny_moe", comm="fused", ep=8, steps=8)
+    close(a["losses"], b["losses"])
+    assert b["losses"][-1] < b["losses"][0]
+
+
+def test_data_parallel_4_zero3_matches_replicated(tmp_path):
+    if _gpus() < 4:
+        pytest.skip("needs 4 GPUs")
+    a = run_case(tmp_path, 4, comm="baseline")
+    b = run_case(tmp_path, 4, comm="fused", zero=3)
+    close(a["losses"], b["losses"], tol=0.01)

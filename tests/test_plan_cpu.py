@@ -195,11 +195,14 @@ def test_plan_variants_compile_and_verify(tmp_path):
     tp = _variant(tmp_path, "tp2", "tp = 2\ncomm = fused\nmb_group = 1\n", world=2)
     lo_gemms = [op for op in tp.ops if op.exec and int(tp.exec[op.exec - 1].kernel) == plan.K_GEMM and op.stream_id == 1]
     assert len(lo_gemms) >= 4 * 4 * 4   # 4 layers x 4 microbatches x 4 weight gradients
-    # microbatches launched in pairs (the default under tensor parallelism): half the launches, twice the rows each
-    pair = _variant(tmp_path, "tp2_pairs", "tp = 2\ncomm = fused\n", world=2)
+    # microbatches launched in pairs: half the launches, twice the rows each; left to the compiler, as many as divide
+    # grad_accum and keep a launch under 16384 tokens (all four here)
+    pair = _variant(tmp_path, "tp2_pairs", "tp = 2\ncomm = fused\nmb_group = 2\n", world=2)
+    auto = _variant(tmp_path, "tp2_auto", "tp = 2\ncomm = fused\n", world=2)
     fused_ops = lambda p: [x for x in p.exec if int(x.kernel) in (plan.K_AG_GEMM, plan.K_GEMM_RS)]
     assert len(fused_ops(pair)) * 2 == len(fused_ops(tp)) and fused_ops(pair)[0].i[0] == 2 * fused_ops(tp)[0].i[0]
     assert pair.hdr.num_microbatches == tp.hdr.num_microbatches and pair.hdr.plan_hash == tp.hdr.plan_hash
+    assert len(fused_ops(auto)) * 4 == len(fused_ops(tp))
     with pytest.raises(plan.PlanError):
         plan.compile_plans((ROOT / "configs" / "tiny_mp.cfg").read_text() + "\ngpus_per_rack = 2\ngpus_per_tray = 2\npp = 2\nmb_group = 2\n",
                            tmp_path / "bad_group", version=2, text=True)

@@ -11,7 +11,7 @@ def _bf(x):
     return x.to(torch.bfloat16)
 
 
-@pytest.mark.parametrize("rows,H", [(37, 256), (512, 2048), (100, 4096)])
+@pytest.mark.parametrize("rows,H", [(37, 256), (512, 2048), (100, 4096), (8192, 2048), (3000, 1024), (64, 6144)])
 def test_rmsnorm_fwd_bwd(rows, H):
     from cai_b200 import ops
     torch.manual_seed(0)
