@@ -7,6 +7,7 @@ iterations). Also the small fixed-size workloads that profiler captures are take
     python -m cai_b200.ops.microbench rmsnorm_bwd --rows 4096 --hidden 2048
     python -m cai_b200.ops.microbench swiglu --rows 4096 --ffn 8192
     python -m cai_b200.ops.microbench gemm_fp8 --m 8192 --n 8192 --k 8192
+    python -m cai_b200.ops.microbench gemm_swiglu --m 8192 --n 16384 --k 2048     (n = 2 x ffn: gate and up)
 
 Prints one JSON line per run: milliseconds (median of ``--iters`` after ``--warmup``), achieved
 TFLOP/s or GB/s, and the fraction of the measured peaks in ``MEASURED_PEAKS.json`` when present.
@@ -52,7 +53,7 @@ def timeit(fn, iters, warmup, flush):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "attn_fwd", "attn_bwd", "rmsnorm_bwd", "swiglu"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_fp8", "gemm_swiglu", "attn_fwd", "attn_bwd", "rmsnorm_bwd", "swiglu"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -84,6 +85,17 @@ def main(argv=None):
         tf = 2.0 * a.m * a.n * a.k / ms / 1e9
         out.update(m=a.m, n=a.n, k=a.k, ta=a.ta, tb=a.tb, f32_accumulate=a.f32, ms=ms, tflops=tf,
                    frac_of_peak=tf / tf_peak, peak_source=src)
+    elif a.kernel == "gemm_swiglu":
+        # gate/up projection with SwiGLU in the epilogue against the plain product followed by the stand-alone kernel
+        from . import gemm_swiglu
+        X = torch.randn(a.m, a.k, device=dev, dtype=bf)
+        W = torch.randn(a.n, a.k, device=dev, dtype=bf) * a.k ** -0.5
+        C = torch.empty(a.m, a.n, device=dev, dtype=bf)
+        ms = timeit(lambda: gemm_swiglu(X, W), a.iters, a.warmup, flush)
+        ms_two = timeit(lambda: swiglu_fwd(gemm(X, W, out=C)), a.iters, a.warmup, flush)
+        tf = 2.0 * a.m * a.n * a.k / ms / 1e9
+        out.update(m=a.m, n=a.n, k=a.k, ms=ms, tflops=tf, frac_of_peak=tf / tf_peak, gemm_plus_swiglu_kernel_ms=ms_two,
+                   peak_source=src)
     elif a.kernel == "gemm_fp8":
         from . import gemm_fp8, quant_blocks_128x128, quant_rows_1x128
         xq, sx = quant_rows_1x128(torch.randn(a.m, a.k, device=dev).to(bf))

@@ -218,6 +218,13 @@ def verify(config_path, check_exec=True):
     return rc, buf.value.decode()
 
 
+def lint(config_path):
+    """Pre-compile checks of a configuration (what ``bin/topology_linter`` prints). Returns ``(failed, report_text)``."""
+    buf = ctypes.create_string_buffer(1 << 16)
+    rc = lib().cai_lint(str(config_path).encode(), buf, len(buf))
+    return rc, buf.value.decode()
+
+
 class PlanFile:
     """A plan file parsed into ctypes arrays (version 1 or 2)."""
 

@@ -406,6 +406,12 @@ class Engine:
         return int(self.L.cai_exec_launches(self.ex))
 
     # ------------------------------------------------------------------ trace
+    def debug_bounds(self, on=True):
+        """Check every operand's extent against the plan's tensor table before each launch (slow path for debugging;
+        ``CAI_DEBUG_BOUNDS=1`` in the environment switches it on from the start)."""
+        self.L.cai_exec_set_debug.argtypes = [c_void_p, c_int]
+        self.L.cai_exec_set_debug(self.ex, int(on))
+
     def nvtx(self, on=True):
         """One NVTX range per op of a replay, named by kernel, for timeline tools."""
         self.L.cai_exec_nvtx_enable(self.ex, int(on))

@@ -17,7 +17,8 @@ void gather_job_finish(GatherJob& job);
 int cai_fused_rs_adamw(const cai::PeerTable& pt, unsigned long long grad_off, unsigned long long param_off, float* master,
                        float* m, float* v, long long n_flat, long long n_shard, const float* hyper, float gscale,
                        uint32_t seq, unsigned int* done_counter, int local_params, cudaStream_t st,
-                       long long bucket_lo = 0, long long bucket_hi = -1, int max_ctas = 0);   // bucket: the part of the flat space this launch covers
+                       long long bucket_lo = 0, long long bucket_hi = -1, int max_ctas = 0,   // bucket: the part of the flat space this launch covers
+                       int staged = 0, float* gacc = nullptr, int acc_only = 0, int acc_first = 0);   // sharded gradients, see rs_adamw.cu
 
 // All-gather of a row-sharded activation fused into the GEMM that consumes it (gemm_tcgen05.cu).
 int cai_fused_ag_gemm(const cai::PeerTable& pt, int group_kind, unsigned long long src_off, long long ld_src, void* a_full,

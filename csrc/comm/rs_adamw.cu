@@ -40,6 +40,13 @@ struct RsAdamwParams {
     uint32_t seq;
     unsigned int* done_counter;
     int local_params;  // bf16 parameters sharded like the optimizer state: write my shard only
+    // Sharded gradients (ZeRO-3 with per-layer buckets): the members' gradients of the bucket sit in a staging buffer
+    // (element i of the flat space at grad_off + (i - bucket_lo) * 4) and hold ONE microbatch; the owner keeps the
+    // running sum of its elements in `gacc` (indexed like master). acc_only: reduce into gacc and stop (not the last
+    // microbatch); acc_first: gacc holds nothing yet.
+    int staged;
+    float* gacc;
+    int acc_only, acc_first;
     int* status;
 };
 
@@ -62,14 +69,25 @@ __global__ void __launch_bounds__(256) rs_adamw_kernel(const PeerTable pt, const
         const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
         for (long long i = first + (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < hi; i += stride) {
             float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+            const long long gi = p.staged ? i - p.bucket_lo : i;
 #pragma unroll
             for (int mbr = 0; mbr < kMaxPeers; ++mbr) {
                 if (mbr < pt.size) {
-                    const float4 t = *reinterpret_cast<const float4*>(pt.base[mbr] + p.grad_off + i * 4);
+                    const float4 t = *reinterpret_cast<const float4*>(pt.base[mbr] + p.grad_off + gi * 4);
                     g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
                 }
             }
             const long long j = i - lo;
+            if (p.gacc) {
+                if (!p.acc_first) {
+                    const float4 a = *reinterpret_cast<const float4*>(p.gacc + j);
+                    g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+                }
+                if (p.acc_only) {
+                    *reinterpret_cast<float4*>(p.gacc + j) = g;
+                    continue;
+                }
+            }
             const float4 p4 = *reinterpret_cast<const float4*>(p.master + j);
             const float4 m4 = *reinterpret_cast<const float4*>(p.m + j);
             const float4 v4 = *reinterpret_cast<const float4*>(p.v + j);
@@ -120,7 +138,7 @@ using namespace cai;
 int cai_fused_rs_adamw(const PeerTable& pt, unsigned long long grad_off, unsigned long long param_off, float* master,
                        float* m, float* v, long long n_flat, long long n_shard, const float* hyper, float gscale,
                        uint32_t seq, unsigned int* done_counter, int local_params, cudaStream_t st,
-                       long long bucket_lo, long long bucket_hi, int max_ctas) {
+                       long long bucket_lo, long long bucket_hi, int max_ctas, int staged, float* gacc, int acc_only, int acc_first) {
     if (bucket_hi < 0) bucket_hi = n_flat;
     if ((n_shard & 3) || (n_flat & 3) || (bucket_lo & 3) || (bucket_hi & 3) || bucket_lo < 0 || bucket_lo > bucket_hi || bucket_hi > n_flat) {
         set_last_error("rs_adamw: element counts and bucket bounds must be multiples of 4 (bucket %lld..%lld of %lld)", bucket_lo,
@@ -135,6 +153,7 @@ int cai_fused_rs_adamw(const PeerTable& pt, unsigned long long grad_off, unsigne
     p.hyper = hyper; p.gscale = gscale; p.seq = seq;
     p.done_counter = done_counter;
     p.local_params = local_params;
+    p.staged = staged; p.gacc = gacc; p.acc_only = acc_only; p.acc_first = acc_first;
     const int dev = current_device();
     p.status = status_words(dev);
     // a bucket that runs beside the backward pass takes a slice of the GPU (max_ctas), the end-of-step launch all of it
@@ -161,5 +180,5 @@ extern "C" __attribute__((visibility("default"))) int cai_fused_rs_adamw_c(
     pt.size = size;
     pt.sig_off = sig_off;
     return cai_fused_rs_adamw(pt, grad_off, param_off, master, m, v, n_flat, n_shard, hyper, gscale, seq, scratch, local_params,
-                              static_cast<cudaStream_t>(stream), 0, -1, 0);
+                              static_cast<cudaStream_t>(stream), 0, -1, 0, 0, nullptr, 0, 0);
 }

@@ -102,6 +102,10 @@ int cai_compile_text(const char* config_text, const char* outdir, uint32_t rank_
 /* Whole-cluster verification; returns the number of problems (0 = pass), negative on error.
  * The report text is written into `report`. */
 int cai_verify(const char* config_path, int check_exec, char* report, size_t report_len);
+/* Pre-compile checks of a configuration (memory budget, tensor-parallel placement, rank <-> location round trips,
+ * pipeline bubble): "[ok]" / "[warn]" / "[FAIL]" lines in `report`; returns the number of failed checks,
+ * negative when the configuration cannot be read. */
+int cai_lint(const char* config_path, char* report, size_t report_len);
 /* Decomposition summary as "key=value\n" lines. */
 int cai_describe(const char* config_text, char* out, size_t out_len, char* err, size_t errlen);
 /* Members of a communicator, for building process groups. Returns the count. */

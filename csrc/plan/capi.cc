@@ -105,6 +105,25 @@ int cai_group_members(const char* text, uint16_t kind, uint32_t rank, uint32_t* 
     return static_cast<int>(m.size());
 }
 
+int cai_lint(const char* config_path, char* report, size_t report_len) {
+    Config cfg;
+    std::string e;
+    Decomp d;
+    std::ostringstream o;
+    int rc = 0;
+    if (config_load(config_path, &cfg, &e) != OK) { o << "config error: " << e << "\n"; rc = ERR_INVALID; }
+    else if (topology_finalize(&cfg.topo, &e) != OK) { o << "topology: " << e << "\n"; rc = ERR_TOPOLOGY; }
+    else if (decompose(cfg, &d, &e) != OK) { o << "decompose: " << e << "\n"; rc = ERR_INVALID; }
+    else {
+        VerifyReport rep;
+        lint_config(cfg, d, d.mem_total <= mem_budget(cfg), &rep);
+        for (const std::string& l : rep.lines) o << l << "\n";
+        rc = rep.problems;
+    }
+    if (report && report_len) std::snprintf(report, report_len, "%s", o.str().c_str());
+    return rc;
+}
+
 int cai_verify(const char* config_path, int check_exec, char* report, size_t report_len) {
     Config cfg;
     std::string e;

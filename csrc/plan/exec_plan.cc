@@ -352,7 +352,7 @@ void exec_operands(const ExecOp& x, std::vector<int>* reads, std::vector<int>* w
             if (((x.flags >> 4) & 0xF) == 4) W(5); else R(5);
             break;
         case K_GEMM_RS: R(0); R(1); R(3); W(2); W(4); break;
-        case K_RS_ADAMW: R(0); R(1); R(2); R(3); W(0); W(1); W(2); W(4); break;
+        case K_RS_ADAMW: R(0); R(1); R(2); R(3); R(5); W(0); W(1); W(2); W(4); W(5); break;   // t[5]: gradient accumulator of the shard
         case K_FSDP_AG_GEMM: if (x.t[2] >= 0) R(2); else R(0); W(1); break;   // t[2]: the slice of the local shard that is read
         case K_QUANT_FP8: R(0); W(1); W(2); W(3); W(4); break;
         case K_GEMM_FP8: R(0); R(1); R(3); R(4); R(5); W(2); break;
@@ -581,6 +581,33 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         relocate(gf);
         for (LayerParams& w : L) for (const Param* q : {&w.g1, &w.wqkv, &w.wo, &w.g2, &w.wgu, &w.wd}) relocate(*q);
     }
+    // ZeRO-3 with per-layer buckets: gradients are sharded too. A layer's weight gradients of ONE microbatch land in
+    // one of two alternating layer-sized fp32 buffers; the layer's bucket kernel (every microbatch) sums the
+    // members' buffers for the elements this rank owns into a shard-sized accumulator, and on the last microbatch
+    // goes on to AdamW. Only the small resident group (embedding, gains, head) keeps full-size gradients.
+    const bool shard_grads = zero3 && cfg.train.dp_buckets != 0 && b.layers > 0;
+    int grad_stage[2] = {-1, -1}, grad_acc = -1;
+    if (shard_grads) {
+        uint64_t max_layer = 0;
+        for (const auto& r : layer_range) max_layer = std::max(max_layer, r.second - r.first);
+        out->tensors[b.flat_grad].nbytes = misc_hi * 4;
+        b.cursor[TC_GRAD] = misc_hi * 4;
+        auto gbuf = [&](uint64_t elems) {
+            b.cursor[TC_GRAD] = align_up(b.cursor[TC_GRAD], kTensorAlign);
+            const int id = b.tensor_at(TC_GRAD, DT_FP32, b.cursor[TC_GRAD], 1, 0, 0);
+            out->tensors[id].nbytes = elems * 4;
+            b.cursor[TC_GRAD] += elems * 4;
+            return id;
+        };
+        grad_stage[0] = gbuf(max_layer);
+        grad_stage[1] = b.layers > 1 ? gbuf(max_layer) : grad_stage[0];
+        grad_acc = gbuf(n_shard);
+        for (uint32_t l = 0; l < b.layers; ++l)
+            for (const Param* q : {&L[l].wqkv, &L[l].wo, &L[l].wgu, &L[l].wd}) {
+                const uint64_t flat_off = out->tensors[q->g].offset / 4;
+                out->tensors[q->g].offset = out->tensors[grad_stage[l & 1]].offset + (flat_off - layer_range[l].first) * 4;
+            }
+    }
     // Emits the gather of one parameter group. `fuse` marks a record that the runtime merges into the
     // GEMM that follows it (the gather runs in that kernel's copy CTAs); otherwise it is a kernel of its own.
     int resident[2] = {-1, -1};
@@ -778,7 +805,9 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     // microbatch's backward right after the layer's weight gradients, so it overlaps the layers below it.
     const uint32_t dp_rank = rank / (d.tp * d.pp * d.cp) % std::max(1u, d.dp);
     const bool dp_buckets = d.dp > 1 && b.fused && cfg.train.dp_buckets != 0 && tp == 1;
-    auto emit_bucket = [&](uint64_t lo, uint64_t hi, int max_ctas, uint16_t mb) {
+    // layer >= 0 with sharded gradients: the bucket reads the layer's staging buffers; `last` = the step's last
+    // microbatch (the update follows the reduction), `first` = its first (the accumulator is overwritten)
+    auto emit_bucket = [&](uint64_t lo, uint64_t hi, int max_ctas, uint16_t mb, int layer = -1, bool first = true, bool last = true) {
         if (hi > hdr_n_rep) hi = hdr_n_rep;
         if (lo >= hi) return;
         auto sub = [&](int flat, uint16_t tclass, uint16_t dt, uint64_t elem_off, uint64_t elems) {
@@ -789,24 +818,31 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         // what this rank's kernel touches: everybody's gradients of the bucket are read by the owners; the owner
         // updates its part of master / m / v; parameters change in the bucket on every member (replicated) or in
         // the owner's shard (ZeRO-3)
+        const bool staged = shard_grads && layer >= 0;
         const uint64_t own_lo = std::max<uint64_t>(lo, static_cast<uint64_t>(dp_rank) * hdr_n_shard);
         const uint64_t own_hi = std::min<uint64_t>(hi, static_cast<uint64_t>(dp_rank + 1) * hdr_n_shard);
-        ExecOp e = xop(K_RS_ADAMW, static_cast<uint16_t>((zero3 ? 1 : 0) | 2));   // flag 2: t[3] is a bucket of the flat gradients
-        e.t[3] = sub(b.flat_grad, TC_GRAD, DT_FP32, lo, hi - lo);
+        // flags: 1 parameters sharded (write my shard only), 2 a bucket (bounds in i[0..1]), 4 gradients staged per layer,
+        // 8 reduce into the accumulator only (not the last microbatch), 16 overwrite the accumulator (first microbatch)
+        ExecOp e = xop(K_RS_ADAMW, static_cast<uint16_t>((zero3 ? 1 : 0) | 2 | (staged ? 4 : 0) | (staged && !last ? 8 : 0) |
+                                                         (staged && first ? 16 : 0)));
+        e.t[3] = staged ? sub(grad_stage[layer & 1], TC_GRAD, DT_FP32, 0, hi - lo) : sub(b.flat_grad, TC_GRAD, DT_FP32, lo, hi - lo);
         if (own_lo < own_hi) {
             const uint64_t o = own_lo - static_cast<uint64_t>(dp_rank) * hdr_n_shard;
-            e.t[0] = sub(b.flat_master, TC_OPTSTATE, DT_FP32, o, own_hi - own_lo);
-            e.t[1] = sub(b.flat_m, TC_OPTSTATE, DT_FP32, o, own_hi - own_lo);
-            e.t[2] = sub(b.flat_v, TC_OPTSTATE, DT_FP32, o, own_hi - own_lo);
-            if (zero3) e.t[4] = sub(b.flat_param, TC_PARAM, DT_BF16, o, own_hi - own_lo);
+            if (!staged || last) {
+                e.t[0] = sub(b.flat_master, TC_OPTSTATE, DT_FP32, o, own_hi - own_lo);
+                e.t[1] = sub(b.flat_m, TC_OPTSTATE, DT_FP32, o, own_hi - own_lo);
+                e.t[2] = sub(b.flat_v, TC_OPTSTATE, DT_FP32, o, own_hi - own_lo);
+                if (zero3) e.t[4] = sub(b.flat_param, TC_PARAM, DT_BF16, o, own_hi - own_lo);
+            }
+            if (staged) e.t[5] = sub(grad_acc, TC_GRAD, DT_FP32, o, own_hi - own_lo);
         }
         if (!zero3) e.t[4] = sub(b.flat_param, TC_PARAM, DT_BF16, lo, hi - lo);
-        e.i[0] = static_cast<int32_t>(hdr_n_rep & 0xFFFFFFFFu); e.i[1] = static_cast<int32_t>(hdr_n_rep >> 32);
-        e.i[2] = static_cast<int32_t>(hdr_n_shard & 0xFFFFFFFFu); e.i[3] = GROUP_DP; e.i[4] = static_cast<int32_t>(b.next_seq++);
+        e.i[0] = static_cast<int32_t>(lo >> 9); e.i[1] = static_cast<int32_t>(hi >> 9); e.i[2] = max_ctas;
+        e.i[3] = GROUP_DP; e.i[4] = static_cast<int32_t>(b.next_seq++);
         e.f[0] = 1.0f / d.dp;
-        e.f[1] = static_cast<float>(max_ctas);
         b.push(OP_RS_ADAMW, ST_COMM_DP, 18.0 * (hi - lo) / d.dp, 4.0 * (hi - lo), GROUP_DP, mb, &e);   // cost: rank-independent
     };
+    int stage_free_ev[2] = {-1, -1};   // sharded gradients: recorded on comm_dp after the bucket that last read a staging buffer
     std::vector<int> send_done(slots, -1);  // event recorded after a slot's activation send
 
     // ================================================================ forward of one layer
@@ -926,7 +962,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     auto backward = [&](uint16_t mb) {
         const uint32_t s = mb % slots;
         const bool first_mb = mb == 0;                 // first gradient contribution overwrites
-        const int wg_epi = first_mb ? 1 : 2;           // CAI_EPI_F32 / CAI_EPI_F32_ACCUM
+        const int wg_epi = (first_mb || shard_grads) ? 1 : 2;   // CAI_EPI_F32 / CAI_EPI_F32_ACCUM (staged gradients hold one microbatch)
         bool lo_pending = false;
         // G[M,N] (+)= A[K,M]^T * B[K,N]: a weight gradient; its operands are complete on compute_hi
         auto wgrad = [&](int A, int B, int G, uint32_t M, uint32_t N, uint32_t K) {
@@ -991,6 +1027,11 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             const int g_rows = tp > 1 ? dfull : dstream;  // all T rows of the incoming gradient
             const int g_rows_attn = tp > 1 ? dfull_attn : dstream;
             join_lo();
+            if (shard_grads && stage_free_ev[l & 1] >= 0) {
+                // this layer's weight gradients overwrite a staging buffer the members may still be reading
+                b.wait(ST_COMPUTE_HI, static_cast<uint32_t>(stage_free_ev[l & 1]), mb);
+                stage_free_ev[l & 1] = -1;
+            }
             if (recompute) layer_forward(mb, a, w, x_scratch);
             if (moe) {
                 const uint32_t F = m.ffn_hidden, seg_m = d.ep * moe_cap;
@@ -1071,12 +1112,14 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             wgrad(dqkv, a.xn1, w.wqkv.g, b.Cqkv, H, T);
             b.row_parallel(dqkv, w.wqkv.w, -1, dxn, partial, rs_tmp, H, b.Cqkv, true, mb);
             b.rmsnorm_bwd(a.x, w.g1.w, a.rstd1, dxn, dstream, w.g1.g, norm_scratch, Tl, true, !first_mb, mb);
-            if (dp_buckets && mb + 1 == ga) {
+            if (dp_buckets && (shard_grads || mb + 1 == ga)) {
                 // the layer's gradients are complete on this rank: its bucket goes to comm_dp and runs under the
-                // backward of the layers below (a slice of the SMs is enough to keep NVLink busy)
+                // backward of the layers below (a slice of the SMs is enough to keep NVLink busy). With sharded
+                // gradients every microbatch's contribution is reduced into the owners' accumulators.
                 b.sync(ST_COMPUTE_HI, ST_COMM_DP, mb);
                 if (lo_pending) b.sync(ST_COMPUTE_LO, ST_COMM_DP, mb);
-                emit_bucket(layer_range[l].first, layer_range[l].second, 64, mb);
+                emit_bucket(layer_range[l].first, layer_range[l].second, 64, mb, l, mb == 0, mb + 1 == ga);
+                if (shard_grads) stage_free_ev[l & 1] = static_cast<int>(b.record(ST_COMM_DP, mb));
             }
         }
         join_lo();

@@ -126,6 +126,9 @@ void verify_hazards(const Plan& p, VerifyReport* rep);
 // Pairwise send/recv order between adjacent pipeline stages (not just counts).
 void verify_pipeline_pairing(const std::vector<Plan>& stage_plans, VerifyReport* rep);
 
+// Pre-compile sanity checks of a configuration; `memory_fits` is what report_decomp returned.
+void lint_config(const Config& cfg, const Decomp& d, bool memory_fits, VerifyReport* rep);
+
 // Which tensors an exec record reads / writes (ids into Plan::tensors).
 void exec_operands(const ExecOp& x, std::vector<int>* reads, std::vector<int>* writes);
 

@@ -293,4 +293,51 @@ void verify_pipeline_pairing(const std::vector<Plan>& stages, VerifyReport* rep)
         add(rep, true, "pipeline sends and receives pair up in issue order across %zu stages", stages.size());
 }
 
+// Pre-compile sanity checks of a configuration (what `topology_linter` prints): memory against the budget,
+// tensor-parallel groups inside one NVLink domain, rank <-> physical location round trips on the edge ranks,
+// pipeline bubble. Findings go to the report as "[ok]" / "[warn]" / "[FAIL]" lines; only failures count as
+// problems. The checks and their wording follow the reference tool (tools/topology_linter.c:70-99).
+void lint_config(const Config& cfg, const Decomp& d, bool memory_fits, VerifyReport* rep) {
+    const Topology& t = cfg.topo;
+    char line[256];
+    auto say = [&](const char* tag, bool is_problem) {
+        rep->lines.push_back(std::string("  ") + tag + " " + line);
+        if (is_problem) ++rep->problems;
+    };
+    if (!memory_fits) {
+        std::snprintf(line, sizeof line, "per-GPU memory over budget");
+        say("[FAIL]", true);
+    }
+    if (d.tp > t.gpus_per_rack) {
+        std::snprintf(line, sizeof line, "TP=%u exceeds gpus_per_rack=%u (spans NVLink domains)", d.tp, t.gpus_per_rack);
+        say("[FAIL]", true);
+    } else if (t.gpus_per_rack % d.tp) {
+        std::snprintf(line, sizeof line, "TP=%u does not divide gpus_per_rack=%u; some TP groups cross racks", d.tp, t.gpus_per_rack);
+        say("[warn]", false);
+    } else {
+        std::snprintf(line, sizeof line, "TP=%u fits intra-rack (%u groups/rack)", d.tp, t.gpus_per_rack / d.tp);
+        say("[ok]  ", false);
+    }
+    std::vector<uint32_t> probes;   // first / last GPU of the first rack, first GPU of the second, last rank
+    for (uint32_t r : {0u, t.gpus_per_rack - 1, t.gpus_per_rack, t.world_size - 1})
+        if (r < t.world_size && std::find(probes.begin(), probes.end(), r) == probes.end()) probes.push_back(r);
+    for (uint32_t r : probes) {
+        const PhysId p = phys_of_rank(t, r);
+        const uint32_t back = rank_of(t, p.rack_id, p.tray_id, p.gpu_in_tray);
+        if (back != r) {
+            std::snprintf(line, sizeof line, "rank %u maps to (rack %u,tray %u,gpu %u) but back to %u", r, p.rack_id, p.tray_id,
+                          p.gpu_in_tray, back);
+            say("[FAIL]", true);
+        } else {
+            std::snprintf(line, sizeof line, "rank %u -> rack %u tray %u gpu %u (nic %u rail %u)", r, p.rack_id, p.tray_id,
+                          p.gpu_in_tray, p.nic_id, p.rail_id);
+            say("[ok]  ", false);
+        }
+    }
+    if (d.bubble_ratio > 0.25) {
+        std::snprintf(line, sizeof line, "pipeline bubble %.1f%% is high; raise grad_accum or lower PP", d.bubble_ratio * 100.0);
+        say("[warn]", false);
+    }
+}
+
 }  // namespace cai

@@ -62,5 +62,9 @@ CAI_API int cai_exec_trace_enable(cai_exec* ex, int on);
  * graph keeps the ranges of the capture). */
 CAI_API int cai_exec_nvtx_enable(cai_exec* ex, int on);
 CAI_API int cai_exec_trace_read(cai_exec* ex, cai_exec_trace_rec* out, int cap);
+/* Debug mode (also CAI_DEBUG_BOUNDS=1 in the environment): before each launch of a replay, the extent every operand
+ * needs (from the record's rows / columns / pitch) is checked against the plan's tensor table; a mismatch fails the
+ * step with the op's index instead of letting a kernel write past its tensor. */
+CAI_API int cai_exec_set_debug(cai_exec* ex, int on);
 
 #endif /* CAI_RUNTIME_H */

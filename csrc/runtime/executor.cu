@@ -16,6 +16,7 @@
 #include <dlfcn.h>
 #include <math.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <string>
@@ -168,6 +169,7 @@ struct cai_exec {
     bool use_graph = false;
     bool trace_on = false;
     bool nvtx_on = false;   // one NVTX range per op, named by kernel (for timeline tools)
+    bool debug_bounds = false;   // check every operand's extent against the plan's tensor table before each launch
     std::vector<TraceRec> trace;
     cai_fused_hook_t fused_hook = nullptr;
     void* fused_ctx = nullptr;
@@ -178,6 +180,7 @@ struct cai_exec {
     uint32_t pending_seq = 0;
     bool has_pending_gather = false;
     long long n_shard = 0;  // elements of the flat parameter space each data-parallel member owns
+    long long n_rep = 0;    // elements of the flat space that are replicated over the data-parallel group
     int flat_ids[5] = {-1, -1, -1, -1, -1};  // tensor ids of @flat_grad, @flat_param, @flat_master, @flat_m, @flat_v
 
     void* ptr(int t) const { return t >= 0 ? arena + tensors[t].offset : nullptr; }
@@ -396,18 +399,27 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
             const long long n_flat = (static_cast<long long>(static_cast<uint32_t>(x.i[1])) << 32) | static_cast<uint32_t>(x.i[0]);
             const long long n_shard = static_cast<uint32_t>(x.i[2]);
             if (x.flags & 2) {
-                // a bucket of the flat space: the record's tensors are the slices it touches (for the hazard proof);
-                // the kernel indexes from the bases of the flat buffers
+                // a bucket [i0, i1) x 512 of the flat space: the record's tensors are the slices it touches (for the
+                // hazard proof); the kernel indexes from the bases of the flat buffers
                 const int fg = ex->flat_ids[0], fp = ex->flat_ids[1], fm = ex->flat_ids[2], f1 = ex->flat_ids[3], f2 = ex->flat_ids[4];
-                if (fg < 0 || fp < 0 || fm < 0 || f1 < 0 || f2 < 0) {
+                if (fg < 0 || fp < 0 || fm < 0 || f1 < 0 || f2 < 0 || ex->n_rep <= 0) {
                     set_last_error("rs_adamw bucket: plan lacks the flat buffers");
                     return CAI_K_BAD_ARG;
                 }
-                const long long lo = static_cast<long long>(ex->tensors[x.t[3]].offset - ex->tensors[fg].offset) / 4;
-                const long long hi = lo + static_cast<long long>(ex->tensors[x.t[3]].nbytes / 4);
-                return cai_fused_rs_adamw(pt, ex->tensors[fg].offset, ex->tensors[fp].offset, (float*)ex->ptr(fm), (float*)ex->ptr(f1),
-                                          (float*)ex->ptr(f2), n_flat, n_shard, ex->hyper_dev, x.f[0], seq, ex->counters_dev,
-                                          x.flags & 1, st, lo, hi, static_cast<int>(x.f[1]));
+                const long long lo = static_cast<long long>(static_cast<uint32_t>(x.i[0])) << 9;
+                const long long hi = static_cast<long long>(static_cast<uint32_t>(x.i[1])) << 9;
+                const bool staged = (x.flags & 4) != 0;
+                // sharded gradients: the members' staging buffer of the layer, and my slice of the accumulator moved
+                // back to the start of the shard (the kernel indexes it like master)
+                float* gacc = nullptr;
+                if (staged && x.t[5] >= 0) {
+                    const long long own_lo = lo > ex->peers[group].rank * ex->n_shard ? lo : ex->peers[group].rank * ex->n_shard;
+                    gacc = static_cast<float*>(P(5)) - (own_lo - ex->peers[group].rank * ex->n_shard);
+                }
+                return cai_fused_rs_adamw(pt, staged ? ex->tensors[x.t[3]].offset : ex->tensors[fg].offset, ex->tensors[fp].offset,
+                                          (float*)ex->ptr(fm), (float*)ex->ptr(f1), (float*)ex->ptr(f2), ex->n_rep, ex->n_shard,
+                                          ex->hyper_dev, x.f[0], seq, ex->counters_dev, x.flags & 1, st, lo, hi, x.i[2], staged ? 1 : 0,
+                                          gacc, (x.flags & 8) ? 1 : 0, (x.flags & 16) ? 1 : 0);
             }
             return cai_fused_rs_adamw(pt, ex->tensors[x.t[3]].offset, ex->tensors[x.t[4]].offset, (float*)P(0), (float*)P(1),
                                       (float*)P(2), n_flat, n_shard, ex->hyper_dev, x.f[0], seq, ex->counters_dev, x.flags & 1, st);
@@ -417,6 +429,106 @@ int run_op(cai_exec* ex, const Op& op, const ExecOp& x, cudaStream_t st) {
             set_last_error("no launcher for kernel id %d", (int)x.kernel);
             return CAI_K_BAD_ARG;
     }
+}
+
+// Debug mode (cai_exec_set_debug / CAI_DEBUG_BOUNDS=1): before a record is launched, the extent every operand needs,
+// worked out from the record's own dimensions (rows, columns, pitch, element size), is checked against the bytes
+// the plan gives that tensor. A plan whose dimensions and tensor table disagree is refused with the op's index
+// instead of letting a kernel run past a tensor into its neighbour in the arena.
+struct Need { int t; long long rows, cols, ld, esize; };
+
+bool operand_fits(const cai_exec* ex, const Need& n, const char** why) {
+    if (n.t < 0 || n.rows <= 0 || n.cols <= 0) return true;
+    const TensorDesc& td = ex->tensors[n.t];
+    const long long ld = n.ld > 0 ? n.ld : n.cols;
+    const unsigned long long need = (static_cast<unsigned long long>(n.rows - 1) * ld + n.cols) * n.esize;
+    if (need > td.nbytes) {
+        *why = "operand smaller than the extent the kernel addresses";
+        return false;
+    }
+    if (td.offset + td.nbytes > ex->hdr.arena_bytes) {
+        *why = "operand outside the arena";
+        return false;
+    }
+    return true;
+}
+
+int check_operands(const cai_exec* ex, const ExecOp& x, size_t op_index) {
+    std::vector<Need> needs;
+    auto need = [&](int slot, long long rows, long long cols, long long esize, bool pitched = true) {
+        Need n;
+        n.t = x.t[slot];
+        n.rows = rows; n.cols = cols; n.esize = esize;
+        n.ld = (pitched && x.t[slot] >= 0) ? ex->ld(x.t[slot]) : 0;
+        needs.push_back(n);
+    };
+    const long long i0 = x.i[0], i1 = x.i[1], i2 = x.i[2];
+    switch (x.kernel) {
+        case K_RMSNORM_FWD:
+            need(0, i0, i1, 2); need(1, 1, i1, 2, false); need(2, i0, i1, 2); need(3, 1, i0, 4, false);
+            break;
+        case K_RMSNORM_BWD:
+            need(0, i0, i1, 2); need(1, 1, i1, 2, false); need(2, 1, i0, 4, false); need(3, i0, i1, 2); need(4, i0, i1, 2);
+            need(5, 1, i1, 4, false);
+            break;
+        case K_GEMM: {
+            if ((x.flags & 0x100) || x.t[4] >= 0) break;   // grouped / ragged forms: not covered
+            const int ta = x.flags & 1, tb = (x.flags >> 1) & 1, epi = (x.flags >> 4) & 0xF;
+            const long long M = i0, N = i1, K = i2;
+            if (ta) need(0, K, M, 2); else need(0, M, K, 2);
+            if (tb) need(1, K, N, 2); else need(1, N, K, 2);
+            if (epi == 4) { need(2, M, N, 2); need(3, M, N / 2, 2); }
+            else if (epi == 5) { need(2, M, 2 * N, 2); need(3, M, 2 * N, 2); }
+            else {
+                need(2, M, N, (epi == 1 || epi == 2) ? 4 : 2);
+                if (epi == 3) need(3, M, N, 2);
+            }
+            break;
+        }
+        case K_AG_GEMM: {
+            const long long T = i0, N = i1, K = i2;
+            const int tb = (x.flags >> 1) & 1, epi = (x.flags >> 4) & 0xF;
+            need(3, T, K, 2);
+            if (tb) need(1, K, N, 2); else need(1, N, K, 2);
+            need(2, T, epi == 5 ? 2 * N : N, 2);
+            if (epi == 4) need(5, T, N / 2, 2);
+            if (epi == 5) need(5, T, 2 * N, 2);
+            break;
+        }
+        case K_GEMM_RS: {
+            const long long T = i0, N = i1, K = i2;
+            const int tb = (x.flags >> 1) & 1;
+            need(0, T, K, 2);
+            if (tb) need(1, K, N, 2); else need(1, N, K, 2);
+            need(4, T, N, 2);
+            break;
+        }
+        case K_ROPE: need(0, i0, (static_cast<long long>(x.i[2]) + x.i[3]) * x.i[4], 2); break;
+        case K_ATTN_FWD: case K_ATTN_BWD: {
+            const long long rows = i0 * i1, nh = i2, nkv = x.i[3], hd = x.i[4];
+            need(0, rows, (nh + 2 * nkv) * hd, 2);
+            need(1, rows, nh * hd, 2);
+            if (x.kernel == K_ATTN_FWD) need(2, nh * i0, i1, 4, false);
+            else { need(2, rows, nh * hd, 2); need(5, rows, (nh + 2 * nkv) * hd, 2); }
+            break;
+        }
+        case K_SWIGLU_FWD: need(0, i0, 2 * i1, 2); need(1, i0, i1, 2); break;
+        case K_SWIGLU_BWD: need(0, i0, 2 * i1, 2); need(1, i0, i1, 2); need(2, i0, 2 * i1, 2); break;
+        case K_CROSS_ENTROPY: case K_CROSS_ENTROPY_TP: need(0, i0, i1, 2); need(1, 1, i0, 4, false); break;
+        case K_EMBED_FWD: need(0, 1, i0, 4, false); need(2, i0, i1, 2); break;
+        case K_EMBED_BWD: need(0, 1, i0, 4, false); need(1, i0, i1, 2); break;
+        default: break;
+    }
+    for (const Need& n : needs) {
+        const char* why = nullptr;
+        if (!operand_fits(ex, n, &why)) {
+            set_last_error("debug bounds: op %zu (kernel %d): tensor %d (%llu bytes) %s (%lld x %lld, pitch %lld, %lld-byte elements)",
+                           op_index, (int)x.kernel, n.t, (unsigned long long)ex->tensors[n.t].nbytes, why, n.rows, n.cols,
+                           n.ld > 0 ? n.ld : n.cols, n.esize);
+            return CAI_K_BAD_ARG;
+        }
+    }
+    return 0;
 }
 
 // How many kernels of this library one exec record launches (memsets and NCCL calls are not ours).
@@ -468,6 +580,10 @@ int replay(cai_exec* ex) {
             ex->trace.push_back(r);
             tr = &ex->trace.back();
             cudaEventRecord(tr->start, st);
+        }
+        if (ex->debug_bounds) {
+            const int brc = check_operands(ex, ex->exec[op.exec - 1], i);
+            if (brc != 0) return brc;
         }
         if (ex->nvtx_on) nvtxRangePushA(kernel_label(ex->exec[op.exec - 1].kernel));
         const int rc = run_op(ex, op, ex->exec[op.exec - 1], st);
@@ -537,6 +653,7 @@ CAI_API int cai_exec_create(cai_exec** out, const void* plan_bytes, size_t nbyte
         }
     ex->arena = static_cast<uint8_t*>(arena_base);
     ex->device = current_device();
+    if (const char* dbg = getenv("CAI_DEBUG_BOUNDS")) ex->debug_bounds = *dbg && *dbg != '0';
     if (ex->train.wait_limit_ms) cai_set_wait_limit_us(ex->train.wait_limit_ms * 1000u);
     int lo_prio = 0, hi_prio = 0;
     cudaDeviceGetStreamPriorityRange(&lo_prio, &hi_prio);
@@ -581,7 +698,10 @@ CAI_API int cai_exec_create(cai_exec** out, const void* plan_bytes, size_t nbyte
                 ++fused;
         static const char* const flat_names[5] = {"@flat_grad", "@flat_param", "@flat_master", "@flat_m", "@flat_v"};
         for (const NamedTensor& nt : ex->named) {
-            if (!strcmp(nt.name, "@flat_split")) ex->n_shard = static_cast<long long>(nt.rows) << 9;
+            if (!strcmp(nt.name, "@flat_split")) {
+                ex->n_shard = static_cast<long long>(nt.rows) << 9;
+                ex->n_rep = static_cast<long long>(nt.master) << 9;
+            }
             for (int k = 0; k < 5; ++k)
                 if (!strcmp(nt.name, flat_names[k])) ex->flat_ids[k] = nt.tensor;
         }
@@ -747,6 +867,10 @@ CAI_API int cai_exec_use_graph(cai_exec* ex, int on) {
 
 CAI_API int cai_exec_trace_enable(cai_exec* ex, int on) {
     ex->trace_on = on != 0;
+    return 0;
+}
+CAI_API int cai_exec_set_debug(cai_exec* ex, int on) {
+    ex->debug_bounds = on != 0;
     return 0;
 }
 CAI_API int cai_exec_nvtx_enable(cai_exec* ex, int on) {

@@ -27,7 +27,8 @@ def run_case(tmp_path, nproc, **kw):
            "--out", str(out)]
     for k, v in kw.items():
         cmd += [f"--{k}", str(v)]
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    # every multi-GPU case also runs the executor's operand-extent checks (debug mode)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", CAI_DEBUG_BOUNDS="1")
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert r.returncode == 0, (r.stdout[-3000:], r.stderr[-3000:])
     return json.loads(out.read_text())

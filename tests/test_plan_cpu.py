@@ -90,6 +90,14 @@ def test_topology_mismatch_is_refused(tmp_path):
 def test_linter_verify_recover_tools(tmp_path):
     r = run(BIN / "topology_linter", ROOT / "configs" / "small.cfg")
     assert "RESULT: all checks passed" in r.stdout
+    from cai_b200 import plan
+    failed, rep = plan.lint(ROOT / "configs" / "small.cfg")             # the same checks through the library
+    assert failed == 0 and "TP=4 fits intra-rack" in rep
+    bad = tmp_path / "tp_across.cfg"
+    bad.write_text((ROOT / "configs" / "b200_tp8.cfg").read_text() + "\ngpus_per_rack = 4\ntrays_per_rack = 1\ngpus_per_tray = 4\nnum_racks = 2\n")
+    failed, rep = plan.lint(bad)
+    assert failed == 1 and "exceeds gpus_per_rack" in rep
+    assert run(BIN / "topology_linter", bad, ok=False).returncode == 1
     r = run(BIN / "plan_verify", ROOT / "configs" / "full220k.cfg")
     assert "tile all 220032 ranks" in r.stdout and "RESULT: all checks passed" in r.stdout
     r = run(BIN / "plan_verify", ROOT / "configs" / "b200_pp2tp4.cfg", "--exec")
