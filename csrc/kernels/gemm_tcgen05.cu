@@ -75,6 +75,39 @@ struct GemmParams {
     // ---- optional per-CTA time stamps (globaltimer, ns) for the phase tables of the fused modes: 8 words per CTA,
     // see kStamp*; null in production launches.
     unsigned long long* stamps;
+    // all-gather mode: tiles [tail_start, tiles) are shared by ALL CTAs, the copy CTAs included: once a copy CTA has
+    // staged its units it joins the GEMM for the tail instead of leaving its SM idle. tail_start == tiles: no tail.
+    int tail_start;
+};
+
+// The tiles one CTA works on, in order; producer, MMA issuer and epilogue warps walk the same sequence.
+// Head: tiles [0, tail_start) striped over the compute CTAs. Tail: tiles [tail_start, tiles) striped over the grid.
+struct TileWalk {
+    int next_head, head_end, head_stride, next_tail, tail_end, tail_stride;
+    __device__ __forceinline__ TileWalk(const GemmParams& p, int num_tiles) {
+        const int tail0 = p.tail_start < num_tiles ? p.tail_start : num_tiles;
+        const int cta = static_cast<int>(blockIdx.x) - p.n_copy;
+        head_stride = static_cast<int>(gridDim.x) - p.n_copy;
+        head_end = tail0;
+        next_head = cta >= 0 ? cta : tail0;          // a copy CTA has no head tiles
+        tail_end = num_tiles;
+        tail_stride = static_cast<int>(gridDim.x);
+        // in the tail the compute CTAs come first, so that they continue with consecutive tiles
+        next_tail = tail0 + (cta >= 0 ? cta : head_stride + static_cast<int>(blockIdx.x));
+    }
+    __device__ __forceinline__ int next() {
+        if (next_head < head_end) {
+            const int t = next_head;
+            next_head += head_stride;
+            return t;
+        }
+        if (next_tail < tail_end) {
+            const int t = next_tail;
+            next_tail += tail_stride;
+            return t;
+        }
+        return -1;
+    }
 };
 
 // words of a CTA's stamp record
@@ -124,8 +157,7 @@ __device__ __forceinline__ void bar_sync_epilogue() { asm volatile("bar.sync 2, 
 constexpr int kAgSlots = 6;
 constexpr uint32_t kAgPiece = 32768;
 
-__device__ __forceinline__ void allgather_copy_role(const GemmParams& p, uint32_t epoch, uint8_t* ring, uint64_t* bars) {
-    if (threadIdx.x != 0) return;
+__device__ __forceinline__ bool allgather_copy_role(const GemmParams& p, uint32_t epoch, uint8_t* ring, uint64_t* bars) {
     volatile int no_abort = 0;
     for (int i = 0; i < kAgSlots; ++i) mbar_init(&bars[i], 1);
     mbar_fence_init();
@@ -138,10 +170,11 @@ __device__ __forceinline__ void allgather_copy_role(const GemmParams& p, uint32_
     const uint32_t pieces = static_cast<uint32_t>(contiguous ? (kBM * row_bytes) / kAgPiece : kBM);
     uint32_t n = 0;  // pieces issued by this CTA so far (slot = n % kAgSlots, phase = (n / kAgSlots) & 1)
     for (int u = blockIdx.x; u < units; u += p.n_copy) {
-        // own rows first, then the peers in ring order, so early tiles never wait on NVLink
-        const int s = (p.pt.rank + u / blocks_per_rank) % p.pt.size;
+        // the peers in ring order, own rows last: the compute CTAs read the own rows from their source, the staged
+        // copy only serves later readers of the gathered buffer
+        const int s = (p.pt.rank + 1 + u / blocks_per_rank) % p.pt.size;
         const int j = u % blocks_per_rank;
-        if (!wait_flag_ge(sig_word(p.pt, p.pt.rank, p.group_kind, kSigEntry + s), epoch, p.status)) return;
+        if (!wait_flag_ge(sig_word(p.pt, p.pt.rank, p.group_kind, kSigEntry + s), epoch, p.status)) return false;
         const uint8_t* src = p.pt.base[s] + p.src_off + static_cast<size_t>(j) * kBM * p.ld_src * 2;
         uint8_t* dst = reinterpret_cast<uint8_t*>(p.a_full) + (static_cast<size_t>(s) * p.rows_per_rank + j * kBM) * row_bytes;
         const size_t src_step = contiguous ? piece : static_cast<size_t>(p.ld_src) * 2;
@@ -157,7 +190,7 @@ __device__ __forceinline__ void allgather_copy_role(const GemmParams& p, uint32_
             if (i >= kLag) {
                 const uint32_t m = n - (i < pieces ? kLag + 1 : pieces + kLag - i);  // global index of the piece to store
                 const uint32_t slot = m % kAgSlots;
-                if (!mbar_wait(&bars[slot], (m / kAgSlots) & 1, &no_abort, p.status, CAI_DEV_TIMEOUT_TMA_FULL)) return;
+                if (!mbar_wait(&bars[slot], (m / kAgSlots) & 1, &no_abort, p.status, CAI_DEV_TIMEOUT_TMA_FULL)) return false;
                 bulk_store(dst + static_cast<size_t>(i - kLag) * piece, ring + slot * kAgPiece, piece);
                 tma_store_commit();
             }
@@ -168,6 +201,7 @@ __device__ __forceinline__ void allgather_copy_role(const GemmParams& p, uint32_
         uint32_t* flag = sig_word(p.pt, p.pt.rank, p.group_kind, kSigLocal + s * blocks_per_rank + j);
         asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
     }
+    return true;
 }
 
 // Reduce-scatter epilogue staging: 128 columns at a time (32 rows x (256 + 16) bytes per epilogue warp), which
@@ -182,7 +216,8 @@ __host__ __device__ constexpr int gemm_align_slack() { return RS ? 768 : 1024; }
 template <int BN, int STAGES, bool RS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmA2, const GemmParams p) {
+    // tmA2: all-gather mode only, this member's own rows where they were produced (no staging, no wait)
     constexpr int kBStageBytes = BN * kBK * 2;
     constexpr int kStageBytes = kAStageBytes + kBStageBytes;
     constexpr uint32_t kTmemCols = 2 * BN;
@@ -219,9 +254,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (p.mode == kGemmAllGatherA) {
             if (blockIdx.x == 0 && threadIdx.x == 0) signal_all(p.pt, p.group_kind, kSigEntry + p.pt.rank, epoch);
             if (static_cast<int>(blockIdx.x) < p.n_copy) {
-                allgather_copy_role(p, epoch, smem, bars);
-                if (threadIdx.x == 0) stamp(p, kStampCopyDone);
-                return;
+                // the ring's barriers sit behind the GEMM pipeline's (which this CTA initialises afterwards if it joins)
+                volatile int* copy_ok = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars) + 196);
+                if (threadIdx.x == 0) {
+                    *copy_ok = allgather_copy_role(p, epoch, smem, reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(bars) + 200)) ? 1 : 0;
+                    stamp(p, kStampCopyDone);
+                }
+                __syncthreads();
+                if (!*copy_ok || p.tail_start >= p.tiles_m * p.tiles_n * p.groups) return;
             }
         }
         if (p.mode == kGemmGatherB && static_cast<int>(blockIdx.x) < p.n_copy) {
@@ -230,9 +270,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             return;
         }
     }
-    const int cta = static_cast<int>(blockIdx.x) - p.n_copy;
-    const int ncta = static_cast<int>(gridDim.x) - p.n_copy;
-
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
@@ -265,13 +302,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
+            TileWalk walk(p, num_tiles);
+            bool first_tile = true;
+            for (int tile = walk.next(); tile >= 0 && ok; tile = walk.next()) {
                 int tm, tn, grp;
                 tile_coords(p, tile, tm, tn, grp);
                 const int m0 = tm * kBM, n0 = tn * BN;
                 if (p.seg_mode == 1 && !seg_live(p, grp, m0)) continue;
                 const int ga = static_cast<int>(grp * p.grp_a), gb = static_cast<int>(grp * p.grp_b);
-                if (p.mode == kGemmAllGatherA) {
+                const int own_blk0 = p.mode == kGemmAllGatherA ? p.pt.rank * (p.rows_per_rank / kBM) : 0;
+                const bool local_rows = p.mode == kGemmAllGatherA && tm >= own_blk0 && tm < own_blk0 + p.rows_per_rank / kBM;
+                if (p.mode == kGemmAllGatherA && !local_rows) {
                     // rows of this tile must have been staged by a copy CTA; they were written through
                     // the generic proxy, the TMA engine reads through the async proxy
                     const uint32_t* flag = sig_word(p.pt, p.pt.rank, p.group_kind, kSigLocal + tm);
@@ -308,7 +349,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         break;
                     }
                 }
-                if (tile == cta) stamp(p, kStampFirstReady);
+                if (first_tile) stamp(p, kStampFirstReady);
+                first_tile = false;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (p.seg_mode == 2 && !seg_live(p, grp, kb * kBK)) continue;
                     if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, CAI_DEV_TIMEOUT_TMA_EMPTY)) {
@@ -319,7 +361,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     uint8_t* a_dst = sA + s * kAStageBytes;
                     uint8_t* b_dst = sB + s * kBStageBytes;
                     const int k0 = kb * kBK;
-                    if (!p.a_mn) {
+                    if (local_rows) {
+                        tma_load_2d(a_dst, &tmA2, &full[s], k0, m0 - own_blk0 * kBM);   // my rows, straight from their source
+                    } else if (!p.a_mn) {
                         tma_load_2d(a_dst, &tmA, &full[s], k0, m0 + ga);
                     } else {
 #pragma unroll
@@ -357,7 +401,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             uint32_t ph = 0;
             bool ok = true;
             int t = 0;
-            for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
+            TileWalk walk(p, num_tiles);
+            for (int tile = walk.next(); tile >= 0 && ok; tile = walk.next()) {
                 int grp = 0;
                 if (p.seg_mode) {
                     int tm, tn;
@@ -410,8 +455,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         bool ok = true;
         int rs_prev_owner = -1;
         uint32_t rs_prev_slot = 0;
-        (void)rs_prev_owner; (void)rs_prev_slot;
-        for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
+        bool rs_reduce_seen = false;
+        (void)rs_prev_owner; (void)rs_prev_slot; (void)rs_reduce_seen;
+        TileWalk walk(p, num_tiles);
+        for (int tile = walk.next(); tile >= 0 && ok; tile = walk.next()) {
             int tm, tn, grp;
             tile_coords(p, tile, tm, tn, grp);
             if (p.seg_mode == 1 && !seg_live(p, grp, tm * kBM)) continue;
@@ -444,6 +491,92 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.pt.base[owner] + p.stage_off) +
                                       (static_cast<long long>(p.pt.rank) * p.rows_per_rank + lrow) * p.N + tn * BN;
                 const float alpha = p.alpha;
+                if (owner == p.pt.rank) {
+                    // A tile of MY rows (they come last in the walk): nothing is pushed. The other members sent their
+                    // partials of these rows early (each walks its own rows last too), so the reduction happens right
+                    // here: accumulator (still fp32) + every member's partial from my staging buffer + residual ->
+                    // the final rows. No separate reduce pass trails the GEMM.
+                    volatile int* rs_ok = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars) + 192);
+                    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // pushes of the tile before this one
+                    fence_proxy_async_all();
+                    bar_sync_epilogue();
+                    if (warp == 2 && lane == 0) {
+                        if (rs_prev_owner >= 0) {
+                            __threadfence_system();
+                            st_release_sys(sig_word(p.pt, rs_prev_owner, p.group_kind, kSigTile + p.pt.rank * kSigTileSlots + rs_prev_slot), epoch);
+                        }
+                        if (!rs_reduce_seen) stamp(p, kStampReduceStart);
+                        const uint32_t item = static_cast<uint32_t>((tm - owner * blocks_per_rank) * p.tiles_n + tn);
+                        int good = 1;
+                        for (int src = 0; src < p.pt.size && good; ++src)
+                            if (src != p.pt.rank)
+                                good = wait_flag_ge(sig_word(p.pt, p.pt.rank, p.group_kind, kSigTile + src * kSigTileSlots + item), epoch,
+                                                    p.status) ? 1 : 0;
+                        *rs_ok = good;
+                        if (!rs_reduce_seen) stamp(p, kStampReduceFlags);
+                    }
+                    rs_reduce_seen = true;
+                    rs_prev_owner = -1;
+                    bar_sync_epilogue();
+                    if (!*rs_ok) {
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.pt.base[p.pt.rank] + p.stage_off);
+                    const bool row_ok = lrow < p.rows_per_rank;
+#pragma unroll 1
+                    for (int c = 0; c < BN / 32; ++c) {
+                        uint32_t r[32];
+                        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32;
+                        tmem_ld_32x32(taddr, r);
+                        tmem_ld_wait();
+                        const int col0 = tn * BN + c * 32;
+                        if (!row_ok || col0 >= p.N) continue;
+                        float v[32];
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]) * alpha;
+                        const int nv = (p.N - col0) >= 32 ? 4 : (p.N - col0) / 8;   // 16-byte vectors of this chunk inside N
+#pragma unroll 1
+                        for (int src = 0; src < p.pt.size; ++src) {
+                            if (src == p.pt.rank) continue;
+                            const uint4* prow = reinterpret_cast<const uint4*>(stage + (static_cast<long long>(src) * p.rows_per_rank + lrow) * p.N + col0);
+                            uint4 pv[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                if (j < nv) pv[j] = prow[j];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                if (j < nv) {
+                                    v[j * 8 + 0] += bf16_lo(pv[j].x); v[j * 8 + 1] += bf16_hi(pv[j].x);
+                                    v[j * 8 + 2] += bf16_lo(pv[j].y); v[j * 8 + 3] += bf16_hi(pv[j].y);
+                                    v[j * 8 + 4] += bf16_lo(pv[j].z); v[j * 8 + 5] += bf16_hi(pv[j].z);
+                                    v[j * 8 + 6] += bf16_lo(pv[j].w); v[j * 8 + 7] += bf16_hi(pv[j].w);
+                                }
+                        }
+                        __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + lrow * p.ldc + col0;
+                        const uint4* rrow = p.R ? reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.R) + lrow * p.ldr + col0) : nullptr;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (j >= nv) break;
+                            if (rrow) {
+                                const uint4 rv = rrow[j];
+                                v[j * 8 + 0] += bf16_lo(rv.x); v[j * 8 + 1] += bf16_hi(rv.x);
+                                v[j * 8 + 2] += bf16_lo(rv.y); v[j * 8 + 3] += bf16_hi(rv.y);
+                                v[j * 8 + 4] += bf16_lo(rv.z); v[j * 8 + 5] += bf16_hi(rv.z);
+                                v[j * 8 + 6] += bf16_lo(rv.w); v[j * 8 + 7] += bf16_hi(rv.w);
+                            }
+                            uint4 o;
+                            o.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]); o.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
+                            o.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]); o.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
+                            *reinterpret_cast<uint4*>(crow + j * 8) = o;
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+                    continue;
+                }
 #pragma unroll 1
                 for (int h = 0; h < BN / kRsCols; ++h) {
                     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staging free again
@@ -629,77 +762,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
     }
 
-    if constexpr (RS) {
-        // ---------------- reduce phase: sum the partials of all members for tiles of my rows
-        volatile int& red_ok = *reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars) + 192);
-        __syncthreads();
-        const int blocks_per_rank = p.rows_per_rank / kBM;
-        const int items = blocks_per_rank * p.tiles_n;
-        const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.pt.base[p.pt.rank] + p.stage_off);
-        if (threadIdx.x == 0) stamp(p, kStampReduceStart);
-        for (int item = cta; item < items; item += ncta) {
-            if (threadIdx.x == 0) {
-                int good = 1;
-                for (int src = 0; src < p.pt.size && good; ++src)
-                    good = wait_flag_ge(sig_word(p.pt, p.pt.rank, p.group_kind, kSigTile + src * kSigTileSlots + item), epoch,
-                                        p.status) ? 1 : 0;
-                red_ok = good;
-                if (item == cta) stamp(p, kStampReduceFlags);
-            }
-            __syncthreads();
-            if (!red_ok) break;
-            const int mb = item / p.tiles_n, tn = item - mb * p.tiles_n;
-            constexpr int vec_cols = BN / 8;
-            constexpr int kUnits = kBM * vec_cols;
-            // four independent units per thread and iteration keep enough loads in flight
-            for (int u0 = threadIdx.x; u0 < kUnits; u0 += kGemmThreads * 4) {
-                uint4 part[4][kMaxPeers];
-                uint4 res[4];
-                bool live[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int u = u0 + k * kGemmThreads;
-                    const int rr = u / vec_cols, cc = (u - rr * vec_cols) * 8;
-                    const long long lrow = static_cast<long long>(mb) * kBM + rr;
-                    const int col = tn * BN + cc;
-                    live[k] = u < kUnits && lrow < p.rows_per_rank && col < p.N;
-                    if (!live[k]) continue;
-#pragma unroll
-                    for (int src = 0; src < kMaxPeers; ++src)
-                        if (src < p.pt.size)
-                            part[k][src] = *reinterpret_cast<const uint4*>(stage + (static_cast<long long>(src) * p.rows_per_rank + lrow) * p.N + col);
-                    if (p.R) res[k] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.R) + lrow * p.ldr + col);
-                }
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    if (!live[k]) continue;
-                    const int u = u0 + k * kGemmThreads;
-                    const int rr = u / vec_cols, cc = (u - rr * vec_cols) * 8;
-                    const long long lrow = static_cast<long long>(mb) * kBM + rr;
-                    const int col = tn * BN + cc;
-                    float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                    for (int src = 0; src < kMaxPeers; ++src)
-                        if (src < p.pt.size) {
-                            const uint4 v = part[k][src];
-                            acc8[0] += bf16_lo(v.x); acc8[1] += bf16_hi(v.x); acc8[2] += bf16_lo(v.y); acc8[3] += bf16_hi(v.y);
-                            acc8[4] += bf16_lo(v.z); acc8[5] += bf16_hi(v.z); acc8[6] += bf16_lo(v.w); acc8[7] += bf16_hi(v.w);
-                        }
-                    if (p.R) {
-                        const uint4 v = res[k];
-                        acc8[0] += bf16_lo(v.x); acc8[1] += bf16_hi(v.x); acc8[2] += bf16_lo(v.y); acc8[3] += bf16_hi(v.y);
-                        acc8[4] += bf16_lo(v.z); acc8[5] += bf16_hi(v.z); acc8[6] += bf16_lo(v.w); acc8[7] += bf16_hi(v.w);
-                    }
-                    uint4 o;
-                    o.x = pack_bf16(acc8[0], acc8[1]); o.y = pack_bf16(acc8[2], acc8[3]);
-                    o.z = pack_bf16(acc8[4], acc8[5]); o.w = pack_bf16(acc8[6], acc8[7]);
-                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + lrow * p.ldc + col) = o;
-                }
-            }
-            __syncthreads();
-        }
-    }
-
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0) stamp(p, kStampEnd);
@@ -710,7 +772,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 template <int BN, int STAGES, bool RS>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int sms,
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmA2, GemmParams& p, int sms,
                        cudaStream_t stream) {
     constexpr int smem_bytes = STAGES * (kAStageBytes + BN * kBK * 2) + gemm_align_slack<RS>() + 256 + (RS ? kRsStageBytes : 0);
     static_assert(smem_bytes <= 232448, "shared memory per CTA");
@@ -737,7 +799,17 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
         set_last_error("gemm_rs: too many tiles per member for the signal block");
         return CAI_K_BAD_ARG;
     }
-    gemm_bf16_kernel<BN, STAGES, RS><<<grid, kGemmThreads, smem_bytes, stream>>>(tmA, tmB, p);
+    if (p.mode == kGemmAllGatherA && p.n_copy > 0) {
+        // the last quarter of the tiles is shared with the copy CTAs, which have staged their units by then
+        // The head lasts about as long as the copy: one copy CTA moves ~45 GB/s through its shared-memory ring, one
+        // compute CTA finishes a 128 x BN x K tile at ~8.4 TFLOP/s. What is left after that many waves is the tail.
+        const int ncomp = grid - p.n_copy;
+        const double copy_us = static_cast<double>(p.M) * p.K * 2.0 / p.n_copy / 45e3;
+        const double tile_us = 2.0 * kBM * BN * static_cast<double>(p.K) / 8.4e6;
+        const long long head = static_cast<long long>(copy_us / tile_us + 1.0) * ncomp;
+        p.tail_start = head < tiles ? static_cast<int>(head) : tiles;
+    }
+    gemm_bf16_kernel<BN, STAGES, RS><<<grid, kGemmThreads, smem_bytes, stream>>>(tmA, tmB, tmA2, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         set_last_error("gemm launch failed: %s", cudaGetErrorString(e));
@@ -781,12 +853,16 @@ static int gemm_dispatch(const void* A, const void* B, long long lda, long long 
     if (!ok) return CAI_K_BAD_ARG;
     p.status = status_words(dev);
     p.stamps = p.mode != kGemmPlain ? g_stamp_buf[dev & 63] : nullptr;
+    CUtensorMap tmA2 = tmA;
+    if (p.mode == kGemmAllGatherA &&
+        !encode_tmap_2d(&tmA2, p.pt.base[p.pt.rank] + p.src_off, p.rows_per_rank, K, p.ld_src, kBK, kBM, 2))
+        return CAI_K_BAD_ARG;
     if (p.mode == kGemmReduceScatter) {
-        if (BN == 256) return launch_gemm<256, 4, true>(tmA, tmB, p, sms, st);
-        return launch_gemm<128, 6, true>(tmA, tmB, p, sms, st);
+        if (BN == 256) return launch_gemm<256, 4, true>(tmA, tmB, tmA2, p, sms, st);
+        return launch_gemm<128, 6, true>(tmA, tmB, tmA2, p, sms, st);
     }
-    if (BN == 256) return launch_gemm<256, 4, false>(tmA, tmB, p, sms, st);
-    return launch_gemm<128, 6, false>(tmA, tmB, p, sms, st);
+    if (BN == 256) return launch_gemm<256, 4, false>(tmA, tmB, tmA2, p, sms, st);
+    return launch_gemm<128, 6, false>(tmA, tmB, tmA2, p, sms, st);
 }
 
 static void plain_params(GemmParams& p) {
@@ -796,7 +872,7 @@ static void plain_params(GemmParams& p) {
     p.pt = PeerTable{};
     p.seg_counts = nullptr; p.seg_rows = 0; p.seg_mode = 0;
     p.groups = 1; p.grp_a = p.grp_b = p.grp_c = 0; p.grp_seg = 0;
-    p.gat = GatherJob{}; p.b_elem_off = 0; p.ldb = 0; p.stamps = nullptr;
+    p.gat = GatherJob{}; p.b_elem_off = 0; p.ldb = 0; p.stamps = nullptr; p.tail_start = 0x7fffffff;
     p.R = nullptr; p.ldr = 0; p.alpha = 1.f; p.epi = CAI_EPI_BF16; p.a_mn = 0;
 }
 
