@@ -977,12 +977,17 @@ int cai_fused_ag_gemm(const PeerTable& pt, int group_kind, unsigned long long sr
     p.mode = kGemmAllGatherA;
     p.group_kind = group_kind;
     if (n_copy <= 0) {
-        // As many copy CTAs as the GEMM leaves idle, within [16, 48]: one CTA keeps about 128 KB in flight,
-        // and it takes a few MB in flight to fill an NVLink.
+        // Enough copy CTAs to finish the gather in about 0.6 of the GEMM's time, or at NVLink rate when the GEMM is
+        // shorter than the transfer. One copy CTA sustains ~35 GB/s through its shared-memory ring (measured with the
+        // per-CTA stamps: 16 CTAs moved 67 MB in 120 us), a compute CTA a 128 x 256 x K tile at ~8.4 TFLOP/s.
         const int sms = sm_count(current_device());
-        const int tiles = ((T + kBM - 1) / kBM) * ((N + 255) / 256);
-        n_copy = sms - tiles;
-        n_copy = n_copy < 16 ? 16 : n_copy > 48 ? 48 : n_copy;
+        const double tiles = static_cast<double>((T + kBM - 1) / kBM) * ((N + 255) / 256);
+        const double gemm_us = tiles * (2.0 * kBM * 256 * static_cast<double>(K) / 8.4e6) / sms;
+        const double bytes = static_cast<double>(T) * K * 2.0;
+        const double link_us = bytes * (pt.size - 1) / pt.size / 650e3;
+        const double target_us = 0.6 * gemm_us > link_us ? 0.6 * gemm_us : link_us;
+        n_copy = static_cast<int>(bytes / 35e3 / (target_us > 1.0 ? target_us : 1.0) + 0.999);
+        n_copy = n_copy < 16 ? 16 : n_copy > 40 ? 40 : n_copy;
         const int units = T / kBM;
         if (n_copy > units) n_copy = units;
     }

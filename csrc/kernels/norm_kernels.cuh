@@ -203,13 +203,16 @@ reduce_parts_kernel(const float* __restrict__ parts, float* __restrict__ out, in
 // dy * x * rstd into per-lane column sums that it carries across all the rows it handles; at the end the warps of
 // a CTA combine their sums in shared memory and the CTA writes one partial row of the gain gradient. x and dy are
 // read once (the two-kernel form above reads them twice).
-static __global__ void __launch_bounds__(kNormThreads)
+// 128 threads: the kernel holds a row of x, dy and 64 column sums per lane (about 250 registers), and with four warps
+// a CTA takes half an SM's register file, so it still fits beside a resident GEMM CTA of another stream.
+constexpr int kNormFusedThreads = 128;
+static __global__ void __launch_bounds__(kNormFusedThreads)
 rmsnorm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g,
                          const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dy,
                          __nv_bfloat16* __restrict__ dx, float* __restrict__ dg_partial, int rows, int H, int dx_acc) {
     __shared__ float sdg[kNormWarpCols];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int c = threadIdx.x; c < kNormWarpCols; c += kNormThreads) sdg[c] = 0.f;
+    for (int c = threadIdx.x; c < kNormWarpCols; c += kNormFusedThreads) sdg[c] = 0.f;
     __syncthreads();
     uint4 gv[8];
 #pragma unroll
@@ -222,8 +225,8 @@ rmsnorm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
     for (int c = 0; c < 8; ++c)
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[c][e] = 0.f;
-    const long long nwarps = static_cast<long long>(gridDim.x) * (kNormThreads / 32);
-    for (long long row = static_cast<long long>(blockIdx.x) * (kNormThreads / 32) + warp; row < rows; row += nwarps) {
+    const long long nwarps = static_cast<long long>(gridDim.x) * (kNormFusedThreads / 32);
+    for (long long row = static_cast<long long>(blockIdx.x) * (kNormFusedThreads / 32) + warp; row < rows; row += nwarps) {
         const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
         const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * H);
         uint4* dxr = reinterpret_cast<uint4*>(dx + row * H);
@@ -272,7 +275,7 @@ rmsnorm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
         }
     }
     // warps take turns adding into the CTA's row (a fixed order, so the result does not depend on timing)
-    for (int w = 0; w < kNormThreads / 32; ++w) {
+    for (int w = 0; w < kNormFusedThreads / 32; ++w) {
         if (w == warp) {
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
@@ -285,7 +288,7 @@ rmsnorm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
         }
         __syncthreads();
     }
-    for (int c = threadIdx.x; c < H; c += kNormThreads) dg_partial[static_cast<long long>(blockIdx.x) * H + c] = sdg[c];
+    for (int c = threadIdx.x; c < H; c += kNormFusedThreads) dg_partial[static_cast<long long>(blockIdx.x) * H + c] = sdg[c];
 }
 
 // Host side of RMSNorm backward, shared by the entry points: `scratch` holds at most `parts_cap`
@@ -295,11 +298,12 @@ static inline int launch_rmsnorm_bwd(const void* x, const void* g, const float* 
                                      int dg_accumulate, cudaStream_t st) {
     if (H <= kNormWarpCols && (H & 7) == 0 && parts_cap >= 1) {
         // one sweep: dx and the partial gain gradients from the same read of x and dy
-        long long want = (static_cast<long long>(rows) + 7) / 8;
+        const int wpc = kNormFusedThreads / 32;
+        long long want = (static_cast<long long>(rows) + wpc - 1) / wpc;
         int grid = static_cast<int>(want < 2LL * sms ? want : 2LL * sms);
         if (grid > parts_cap) grid = parts_cap;
         if (grid < 1) grid = 1;
-        rmsnorm_bwd_fused_kernel<<<grid, kNormThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(g),
+        rmsnorm_bwd_fused_kernel<<<grid, kNormFusedThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(g),
                                                                rstd, static_cast<const __nv_bfloat16*>(dy),
                                                                static_cast<__nv_bfloat16*>(dx), scratch, rows, H, dx_accumulate);
         reduce_parts_kernel<<<(H + 31) / 32, 256, 0, st>>>(scratch, dg, grid, H, dg_accumulate);
