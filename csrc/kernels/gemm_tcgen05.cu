@@ -537,22 +537,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                         for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]) * alpha;
                         const int nv = (p.N - col0) >= 32 ? 4 : (p.N - col0) / 8;   // 16-byte vectors of this chunk inside N
-#pragma unroll 1
-                        for (int src = 0; src < p.pt.size; ++src) {
-                            if (src == p.pt.rank) continue;
-                            const uint4* prow = reinterpret_cast<const uint4*>(stage + (static_cast<long long>(src) * p.rows_per_rank + lrow) * p.N + col0);
-                            uint4 pv[4];
+                        // every member's partial of 16 columns is requested before the first one is consumed: the loop
+                        // is bound by the latency of these loads, so as many as the registers allow are in flight
 #pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                if (j < nv) pv[j] = prow[j];
+                        for (int hv = 0; hv < 2; ++hv) {
+                            uint4 pv[kMaxPeers][2];
 #pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                if (j < nv) {
-                                    v[j * 8 + 0] += bf16_lo(pv[j].x); v[j * 8 + 1] += bf16_hi(pv[j].x);
-                                    v[j * 8 + 2] += bf16_lo(pv[j].y); v[j * 8 + 3] += bf16_hi(pv[j].y);
-                                    v[j * 8 + 4] += bf16_lo(pv[j].z); v[j * 8 + 5] += bf16_hi(pv[j].z);
-                                    v[j * 8 + 6] += bf16_lo(pv[j].w); v[j * 8 + 7] += bf16_hi(pv[j].w);
+                            for (int src = 0; src < kMaxPeers; ++src) {
+                                if (src < p.pt.size && src != p.pt.rank) {
+                                    const uint4* prow = reinterpret_cast<const uint4*>(
+                                        stage + (static_cast<long long>(src) * p.rows_per_rank + lrow) * p.N + col0);
+                                    if (hv * 2 < nv) pv[src][0] = prow[hv * 2];
+                                    if (hv * 2 + 1 < nv) pv[src][1] = prow[hv * 2 + 1];
                                 }
+                            }
+#pragma unroll
+                            for (int src = 0; src < kMaxPeers; ++src) {
+                                if (src < p.pt.size && src != p.pt.rank) {
+#pragma unroll
+                                    for (int k = 0; k < 2; ++k) {
+                                        const int j = hv * 2 + k;
+                                        if (j < nv) {
+                                            v[j * 8 + 0] += bf16_lo(pv[src][k].x); v[j * 8 + 1] += bf16_hi(pv[src][k].x);
+                                            v[j * 8 + 2] += bf16_lo(pv[src][k].y); v[j * 8 + 3] += bf16_hi(pv[src][k].y);
+                                            v[j * 8 + 4] += bf16_lo(pv[src][k].z); v[j * 8 + 5] += bf16_hi(pv[src][k].z);
+                                            v[j * 8 + 6] += bf16_lo(pv[src][k].w); v[j * 8 + 7] += bf16_hi(pv[src][k].w);
+                                        }
+                                    }
+                                }
+                            }
                         }
                         __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + lrow * p.ldc + col0;
                         const uint4* rrow = p.R ? reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.R) + lrow * p.ldr + col0) : nullptr;
@@ -977,17 +990,13 @@ int cai_fused_ag_gemm(const PeerTable& pt, int group_kind, unsigned long long sr
     p.mode = kGemmAllGatherA;
     p.group_kind = group_kind;
     if (n_copy <= 0) {
-        // Enough copy CTAs to finish the gather in about 0.6 of the GEMM's time, or at NVLink rate when the GEMM is
-        // shorter than the transfer. One copy CTA sustains ~35 GB/s through its shared-memory ring (measured with the
-        // per-CTA stamps: 16 CTAs moved 67 MB in 120 us), a compute CTA a 128 x 256 x K tile at ~8.4 TFLOP/s.
+        // Sixteen copy CTAs already move what the fabric gives when every member pulls at once (measured with the
+        // per-CTA stamps on 4 GPUs: 50 MB of remote rows in ~110 us with 16 CTAs and with 25); more only take SMs from
+        // the GEMM. When the GEMM has fewer tiles than SMs the idle SMs copy too (up to 32).
         const int sms = sm_count(current_device());
-        const double tiles = static_cast<double>((T + kBM - 1) / kBM) * ((N + 255) / 256);
-        const double gemm_us = tiles * (2.0 * kBM * 256 * static_cast<double>(K) / 8.4e6) / sms;
-        const double bytes = static_cast<double>(T) * K * 2.0;
-        const double link_us = bytes * (pt.size - 1) / pt.size / 650e3;
-        const double target_us = 0.6 * gemm_us > link_us ? 0.6 * gemm_us : link_us;
-        n_copy = static_cast<int>(bytes / 35e3 / (target_us > 1.0 ? target_us : 1.0) + 0.999);
-        n_copy = n_copy < 16 ? 16 : n_copy > 40 ? 40 : n_copy;
+        const int tiles = ((T + kBM - 1) / kBM) * ((N + 255) / 256);
+        n_copy = sms - tiles;
+        n_copy = n_copy < 16 ? 16 : n_copy > 32 ? 32 : n_copy;
         const int units = T / kBM;
         if (n_copy > units) n_copy = units;
     }
