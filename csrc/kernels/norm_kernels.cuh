@@ -199,87 +199,103 @@ reduce_parts_kernel(const float* __restrict__ parts, float* __restrict__ out, in
     }
 }
 
-// Backward in ONE sweep for H <= 2048: a warp keeps a row of x and dy in registers, writes dx and adds the row's
-// dy * x * rstd into per-lane column sums that it carries across all the rows it handles; at the end the warps of
-// a CTA combine their sums in shared memory and the CTA writes one partial row of the gain gradient. x and dy are
-// read once (the two-kernel form above reads them twice).
-// 128 threads: the kernel holds a row of x, dy and 64 column sums per lane (about 250 registers), and with four warps
-// a CTA takes half an SM's register file, so it still fits beside a resident GEMM CTA of another stream.
-constexpr int kNormFusedThreads = 128;
-static __global__ void __launch_bounds__(kNormFusedThreads)
+// Backward in ONE sweep for H <= 8192: a row is handled by R = ceil(H / 1024) warps that keep their slice of x and
+// dy in registers (32 elements per lane), write dx and add the row's dy * x * rstd into per-lane column sums that
+// they carry across all the rows they handle; at the end the warps of a CTA combine their sums in shared memory
+// (in a fixed order) and the CTA writes one partial row of the gain gradient. x and dy are read once (the
+// two-kernel form above reads them twice). About 100 registers per thread, so two CTAs of eight warps share an SM
+// and a CTA still fits beside a resident GEMM CTA of another stream.
+constexpr int kNormFusedThreads = 256;
+constexpr int kNormFusedCols = 1024;   // columns one warp covers: 32 lanes x 4 chunks x 8 elements
+constexpr int kNormFusedMaxH = 8192;
+static __global__ void __launch_bounds__(kNormFusedThreads, 2)
 rmsnorm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g,
                          const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dy,
-                         __nv_bfloat16* __restrict__ dx, float* __restrict__ dg_partial, int rows, int H, int dx_acc) {
-    __shared__ float sdg[kNormWarpCols];
+                         __nv_bfloat16* __restrict__ dx, float* __restrict__ dg_partial, int rows, int H, int dx_acc, int R) {
+    extern __shared__ float sdg[];   // H floats, then 8 partial row sums
+    float* part = sdg + H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int c = threadIdx.x; c < kNormWarpCols; c += kNormFusedThreads) sdg[c] = 0.f;
-    __syncthreads();
-    uint4 gv[8];
+    const int groups = 8 / R;                 // rows a CTA works on at a time
+    const int grp = warp / R, sub = warp - grp * R;
+    const bool active = grp < groups;
+    const int col0 = sub * kNormFusedCols;
+    const uint4* gr = reinterpret_cast<const uint4*>(g);
+    for (int c = threadIdx.x; c < H; c += kNormFusedThreads) sdg[c] = 0.f;
+    float acc[4][8];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        const int col = (c * 32 + lane) * 8;
-        gv[c] = col < H ? reinterpret_cast<const uint4*>(g)[col >> 3] : make_uint4(0u, 0u, 0u, 0u);
-    }
-    float acc[8][8];
-#pragma unroll
-    for (int c = 0; c < 8; ++c)
+    for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[c][e] = 0.f;
-    const long long nwarps = static_cast<long long>(gridDim.x) * (kNormFusedThreads / 32);
-    for (long long row = static_cast<long long>(blockIdx.x) * (kNormFusedThreads / 32) + warp; row < rows; row += nwarps) {
-        const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
-        const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * H);
-        uint4* dxr = reinterpret_cast<uint4*>(dx + row * H);
-        uint4 xv[8], dv[8];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            const int col = (c * 32 + lane) * 8;
-            if (col < H) {
-                xv[c] = xr[col >> 3];
-                dv[c] = dyr[col >> 3];
-            }
-        }
+    for (long long base = static_cast<long long>(blockIdx.x) * groups; base < rows; base += static_cast<long long>(gridDim.x) * groups) {
+        const long long row = base + grp;
+        const bool live = active && row < rows;
+        uint4 xv[4], dv[4];
         float S = 0.f;
+        if (live) {
+            const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+            const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * H);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            const int col = (c * 32 + lane) * 8;
-            if (col < H) {
-                float xf[8], df[8], gf[8];
-                unpack8(xv[c], xf);
-                unpack8(dv[c], df);
-                unpack8(gv[c], gf);
+            for (int c = 0; c < 4; ++c) {
+                const int col = col0 + (c * 32 + lane) * 8;
+                if (col < H) {
+                    xv[c] = xr[col >> 3];
+                    dv[c] = dyr[col >> 3];
+                }
+            }
 #pragma unroll
-                for (int e = 0; e < 8; ++e) S += df[e] * gf[e] * xf[e];
+            for (int c = 0; c < 4; ++c) {
+                const int col = col0 + (c * 32 + lane) * 8;
+                if (col < H) {
+                    float xf[8], df[8], gf[8];
+                    unpack8(xv[c], xf);
+                    unpack8(dv[c], df);
+                    unpack8(gr[col >> 3], gf);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) S += df[e] * gf[e] * xf[e];
+                }
             }
         }
         S = warp_sum(S);
-        const float rr = rstd[row];
-        const float k3 = rr * rr * rr * S / H;
+        if (R > 1) {
+            if (lane == 0) part[warp] = S;
+            __syncthreads();
+            if (active) {
+                S = 0.f;
+                for (int k = 0; k < R; ++k) S += part[grp * R + k];
+            }
+            __syncthreads();
+        }
+        if (live) {
+            const float rr = rstd[row];
+            const float k3 = rr * rr * rr * S / H;
+            uint4* dxr = reinterpret_cast<uint4*>(dx + row * H);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            const int col = (c * 32 + lane) * 8;
-            if (col < H) {
-                float xf[8], df[8], gf[8], o[8];
-                unpack8(xv[c], xf);
-                unpack8(dv[c], df);
-                unpack8(gv[c], gf);
-                if (dx_acc) unpack8(dxr[col >> 3], o);
+            for (int c = 0; c < 4; ++c) {
+                const int col = col0 + (c * 32 + lane) * 8;
+                if (col < H) {
+                    float xf[8], df[8], gf[8], o[8];
+                    unpack8(xv[c], xf);
+                    unpack8(dv[c], df);
+                    unpack8(gr[col >> 3], gf);
+                    if (dx_acc) unpack8(dxr[col >> 3], o);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float v = rr * df[e] * gf[e] - k3 * xf[e];
-                    o[e] = dx_acc ? o[e] + v : v;
-                    acc[c][e] += df[e] * xf[e] * rr;
+                    for (int e = 0; e < 8; ++e) {
+                        const float v = rr * df[e] * gf[e] - k3 * xf[e];
+                        o[e] = dx_acc ? o[e] + v : v;
+                        acc[c][e] += df[e] * xf[e] * rr;
+                    }
+                    dxr[col >> 3] = pack8(o);
                 }
-                dxr[col >> 3] = pack8(o);
             }
         }
     }
-    // warps take turns adding into the CTA's row (a fixed order, so the result does not depend on timing)
-    for (int w = 0; w < kNormFusedThreads / 32; ++w) {
-        if (w == warp) {
+    // row groups take turns adding into the CTA's row (a fixed order, so the result does not depend on timing)
+    __syncthreads();
+    for (int w = 0; w < groups; ++w) {
+        if (active && grp == w) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const int col = (c * 32 + lane) * 8;
+            for (int c = 0; c < 4; ++c) {
+                const int col = col0 + (c * 32 + lane) * 8;
                 if (col < H) {
 #pragma unroll
                     for (int e = 0; e < 8; ++e) sdg[col + e] += acc[c][e];
@@ -296,16 +312,19 @@ rmsnorm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
 static inline int launch_rmsnorm_bwd(const void* x, const void* g, const float* rstd, const void* dy, void* dx, float* dg,
                                      float* scratch, int parts_cap, int sms, int rows, int H, int dx_accumulate,
                                      int dg_accumulate, cudaStream_t st) {
-    if (H <= kNormWarpCols && (H & 7) == 0 && parts_cap >= 1) {
+    if (H <= kNormFusedMaxH && (H & 7) == 0 && parts_cap >= 1) {
         // one sweep: dx and the partial gain gradients from the same read of x and dy
-        const int wpc = kNormFusedThreads / 32;
-        long long want = (static_cast<long long>(rows) + wpc - 1) / wpc;
+        int Rf = (H + kNormFusedCols - 1) / kNormFusedCols;
+        Rf = Rf <= 1 ? 1 : Rf <= 2 ? 2 : Rf <= 4 ? 4 : 8;        // a divisor of the CTA's eight warps
+        const int gpc = 8 / Rf;
+        long long want = (static_cast<long long>(rows) + gpc - 1) / gpc;
         int grid = static_cast<int>(want < 2LL * sms ? want : 2LL * sms);
         if (grid > parts_cap) grid = parts_cap;
         if (grid < 1) grid = 1;
-        rmsnorm_bwd_fused_kernel<<<grid, kNormFusedThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(g),
-                                                               rstd, static_cast<const __nv_bfloat16*>(dy),
-                                                               static_cast<__nv_bfloat16*>(dx), scratch, rows, H, dx_accumulate);
+        const size_t smem = (static_cast<size_t>(H) + 8) * sizeof(float);
+        rmsnorm_bwd_fused_kernel<<<grid, kNormFusedThreads, smem, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(g),
+                                                                      rstd, static_cast<const __nv_bfloat16*>(dy),
+                                                                      static_cast<__nv_bfloat16*>(dx), scratch, rows, H, dx_accumulate, Rf);
         reduce_parts_kernel<<<(H + 31) / 32, 256, 0, st>>>(scratch, dg, grid, H, dg_accumulate);
         return cudaGetLastError() == cudaSuccess ? 0 : 1;
     }

@@ -190,14 +190,39 @@ __global__ void embed_fwd_kernel(const int* __restrict__ tokens, const __nv_bflo
     for (int i = threadIdx.x; i < nv; i += blockDim.x) o[i] = e[i];
 }
 
-__global__ void embed_bwd_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ dout,
-                                 float* __restrict__ dE, int H, int lo, int hi) {
-    const long long t = blockIdx.x;
-    const int tok = tokens[t];
-    if (tok < lo || tok >= hi) return;
-    float* row = dE + (long long)(tok - lo) * H;
-    const __nv_bfloat16* d = dout + t * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) atomicAdd(row + i, __bfloat162float(d[i]));
+// Embedding backward without atomics: a CTA owns kEmbRows consecutive vocabulary rows, scans the token list front to
+// back and adds the gradient row of every token that falls into its range, in token order. Each row of dE has one
+// writer and a fixed order of additions, so the result is the same in every run (the reference scatters with
+// atomicAdd, src/cuda/cai_kernels.cu:26-34).
+constexpr int kEmbRows = 32;
+__global__ void __launch_bounds__(256)
+embed_bwd_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ dout, float* __restrict__ dE, int T, int H,
+                 int lo, int hi) {
+    __shared__ unsigned match[8];
+    __shared__ int toks[256];
+    const int v0 = lo + static_cast<int>(blockIdx.x) * kEmbRows;
+    const int v1 = v0 + kEmbRows < hi ? v0 + kEmbRows : hi;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int t0 = 0; t0 < T; t0 += 256) {
+        const int t = t0 + threadIdx.x;
+        const int tok = t < T ? tokens[t] : -1;
+        const unsigned m = __ballot_sync(0xffffffffu, tok >= v0 && tok < v1);
+        toks[threadIdx.x] = tok;
+        if (lane == 0) match[warp] = m;
+        __syncthreads();
+        for (int w = 0; w < 8; ++w) {
+            unsigned bits = match[w];
+            while (bits) {
+                const int b = __ffs(bits) - 1;
+                bits &= bits - 1;
+                const int tt = t0 + w * 32 + b;
+                float* row = dE + static_cast<long long>(toks[w * 32 + b] - lo) * H;
+                const __nv_bfloat16* d = dout + static_cast<long long>(tt) * H;
+                for (int i = threadIdx.x; i < H; i += 256) row[i] += __bfloat162float(d[i]);
+            }
+        }
+        __syncthreads();
+    }
 }
 
 // ------------------------------------------------------------------ cross entropy
@@ -503,8 +528,9 @@ CAI_API int cai_embed_fwd(const int* tokens, const void* E, void* out, int T, in
 CAI_API int cai_embed_bwd(const int* tokens, const void* dout, float* dE, int T, int H, int vocab_lo,
                           int vocab_hi, void* stream) {
     if (T <= 0) return CAI_K_OK;
-    embed_bwd_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(tokens, (const __nv_bfloat16*)dout, dE, H, vocab_lo,
-                                                          vocab_hi);
+    if (vocab_hi <= vocab_lo) return CAI_K_OK;
+    embed_bwd_kernel<<<(vocab_hi - vocab_lo + kEmbRows - 1) / kEmbRows, 256, 0, (cudaStream_t)stream>>>(
+        tokens, (const __nv_bfloat16*)dout, dE, T, H, vocab_lo, vocab_hi);
     CAI_LAUNCH_CHECK("embed_bwd");
     return CAI_K_OK;
 }

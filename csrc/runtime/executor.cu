@@ -538,7 +538,7 @@ int own_kernels_of(const ExecOp& x) {
     if (k == K_FSDP_AG_GEMM && (x.flags & 1)) return 0;            // rides in the GEMM that follows
     if (k == K_ATTN_BWD) return x.flags ? __builtin_popcount(x.flags) : 3;
     if (k == K_CROSS_ENTROPY_TP) return 3;
-    if (k == K_RMSNORM_BWD) return x.i[1] <= 2048 ? 2 : 3;         // one sweep + reduce, or dg / reduce / dx
+    if (k == K_RMSNORM_BWD) return x.i[1] <= 8192 ? 2 : 3;         // one sweep + reduce, or dg / reduce / dx
     if (k == K_MOE_ROUTE && !(x.flags & 1)) return 2;              // top-k, then slots in token order
     return 1;
 }

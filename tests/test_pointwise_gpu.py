@@ -97,6 +97,17 @@ def test_embedding():
     ops.embed_bwd_(tok, dout, dE)
     ref = torch.zeros(V, H, device="cuda").index_add_(0, tok.long(), dout.float())
     assert torch.allclose(dE, ref, atol=1e-4)
+    # many tokens per row, a vocabulary that is not a multiple of the rows a CTA owns, a slice, and the same bits twice
+    V2, T2 = 77, 5000
+    tok2 = torch.randint(0, V2, (T2,), device="cuda", dtype=torch.int32)
+    d2 = _bf(torch.randn(T2, H, device="cuda"))
+    a = ops.embed_bwd_(tok2, d2, torch.zeros(V2, H, device="cuda"))
+    b = ops.embed_bwd_(tok2, d2, torch.zeros(V2, H, device="cuda"))
+    assert torch.equal(a, b)
+    ref2 = torch.zeros(V2, H, device="cuda").index_add_(0, tok2.long(), d2.float())
+    assert torch.allclose(a, ref2, atol=2e-3, rtol=1e-4)
+    part = ops.embed_bwd_(tok2, d2, torch.zeros(30, H, device="cuda"), vocab_lo=20, vocab_hi=50)
+    assert torch.allclose(part, ref2[20:50], atol=2e-3, rtol=1e-4)
     # vocabulary slice [250, 500)
     out2 = ops.embed_fwd(tok, E[250:500].contiguous(), vocab_lo=250, vocab_hi=500)
     mask = ((tok >= 250) & (tok < 500))
