@@ -232,6 +232,7 @@ int cai_verify(const char* config_path, int check_exec, char* report, size_t rep
             for (const Plan& p : plans) {
                 verify_event_order(p, &rep);
                 verify_hazards(p, &rep);
+                verify_peer_reuse(p, &rep);
             }
             verify_pipeline_pairing(plans, &rep);
         }

@@ -123,6 +123,9 @@ void verify_event_order(const Plan& p, VerifyReport* rep);
 // Happens-before analysis over streams + events: no two ops that touch overlapping arena bytes
 // (at least one writing) may be unordered. Needs a version-2 plan.
 void verify_hazards(const Plan& p, VerifyReport* rep);
+// Cross-rank reuse of the buffers the fused tensor-parallel kernels share between GPUs: every reuse is separated
+// from the peers' accesses by an op that orders the whole group. Needs a version-2 plan.
+void verify_peer_reuse(const Plan& p, VerifyReport* rep);
 // Pairwise send/recv order between adjacent pipeline stages (not just counts).
 void verify_pipeline_pairing(const std::vector<Plan>& stage_plans, VerifyReport* rep);
 

@@ -293,6 +293,76 @@ void verify_pipeline_pairing(const std::vector<Plan>& stages, VerifyReport* rep)
         add(rep, true, "pipeline sends and receives pair up in issue order across %zu stages", stages.size());
 }
 
+// Cross-rank reuse of the buffers the fused tensor-parallel kernels share between GPUs. Every member of the group
+// replays the same op sequence, so one rank's plan stands for all of them. Two facts about the kernels make a
+// group-wide ordering: an all-gather -> GEMM returns only after every member has entered the same op (it needs their
+// entry signals), and a GEMM -> reduce-scatter returns only after every member has reached the epilogue of the same
+// op (it needs their partial tiles); an NCCL collective on the group orders the same way. So "op B of this rank runs
+// after every member has finished op A" holds whenever one of those group-ordering ops lies strictly between A and B
+// on the compute stream. Checked here:
+//   * the rows peers pull in an all-gather -> GEMM (its local source tensor) are next overwritten only after a
+//     group-ordering op that follows the gather;
+//   * a staging buffer that peers push partial tiles into (GEMM -> reduce-scatter) receives the pushes of the NEXT
+//     reduce-scatter only after a group-ordering op that follows the first (a member may still be reading the
+//     partials of the first one until then). Local kernels that reuse the buffer after the op are ordered against it
+//     by the in-rank hazard analysis: when the op has returned, every push into this rank's buffer has been consumed.
+// The step is treated as cyclic (its last ops are followed by the next step's first).
+void verify_peer_reuse(const Plan& p, VerifyReport* rep) {
+    if (p.hdr.version < 2 || p.exec.empty()) return;
+    struct Item { uint32_t op; const ExecOp* x; bool barrier; };
+    std::vector<Item> seq;   // the ops of compute_hi and comm_tp in issue order (everything that can touch these buffers)
+    for (uint32_t i = 0; i < p.ops.size(); ++i) {
+        const Op& op = p.ops[i];
+        if (!op.exec || op.exec > p.exec.size()) continue;
+        const ExecOp& x = p.exec[op.exec - 1];
+        const bool tp_nccl = (x.kernel == K_NCCL_ALL_REDUCE || x.kernel == K_NCCL_REDUCE_SCATTER || x.kernel == K_NCCL_ALL_GATHER) &&
+                             x.i[3] == GROUP_TP;
+        const bool fused = (x.kernel == K_AG_GEMM || x.kernel == K_GEMM_RS) && x.i[3] == GROUP_TP;
+        seq.push_back({i, &x, tp_nccl || fused});
+    }
+    auto overlap = [&](int a, int b) {
+        if (a < 0 || b < 0) return false;
+        const TensorDesc& ta = p.tensors[a];
+        const TensorDesc& tb = p.tensors[b];
+        return ta.offset < tb.offset + tb.nbytes && tb.offset < ta.offset + ta.nbytes;
+    };
+    const size_t n = seq.size();
+    size_t checks = 0;
+    int problems = 0;
+    std::vector<int> reads, writes;
+    for (size_t a = 0; a < n; ++a) {
+        const ExecOp& xa = *seq[a].x;
+        if (!seq[a].barrier || (xa.kernel != K_AG_GEMM && xa.kernel != K_GEMM_RS)) continue;
+        const int shared = xa.kernel == K_AG_GEMM ? xa.t[0] : xa.t[4];   // pulled by peers / pushed into by peers
+        if (shared < 0) continue;
+        bool ordered = false;
+        for (size_t k = 1; k <= n; ++k) {   // walk forward, wrapping into the next step
+            const Item& it = seq[(a + k) % n];
+            const ExecOp& xb = *it.x;
+            bool touches = false;
+            if (xb.kernel == K_GEMM_RS && xa.kernel == K_GEMM_RS && it.barrier && overlap(xb.t[4], shared)) touches = true;   // next remote pushes
+            if (!touches && xa.kernel == K_AG_GEMM) {
+                exec_operands(xb, &reads, &writes);
+                for (int w : writes)
+                    if (overlap(w, shared)) touches = true;
+            }
+            if (touches) {
+                ++checks;
+                if (!ordered) {
+                    ++problems;
+                    add(rep, false, "rank %u: op %u touches a buffer shared with the peers of op %u without a group-ordering op in between",
+                        p.hdr.global_rank, it.op, seq[a].op);
+                }
+                break;
+            }
+            if (it.barrier) ordered = true;
+        }
+    }
+    if (!problems && checks)
+        add(rep, true, "rank %u: peer-visible buffers of the fused TP kernels are reused only across a group-ordering op (%zu checks)",
+            p.hdr.global_rank, checks);
+}
+
 // Pre-compile sanity checks of a configuration (what `topology_linter` prints): memory against the budget,
 // tensor-parallel groups inside one NVLink domain, rank <-> physical location round trips on the edge ranks,
 // pipeline bubble. Findings go to the report as "[ok]" / "[warn]" / "[FAIL]" lines; only failures count as

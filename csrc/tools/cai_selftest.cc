@@ -314,6 +314,27 @@ static void test_exec_plans() {
     verify_hazards(p, &rep);
     CHECK(rep.problems > 0, "hazard checker missed a schedule without waits");
 
+    // Cross-rank reuse: the fused tp = 8 plan passes; turn every all-gather -> GEMM into a plain GEMM (so that two
+    // reduce-scatters follow each other with nothing that orders the group in between) and the proof must fail.
+    {
+        Config cf;
+        config_load("configs/b200_tp8.cfg", &cf, &err);
+        cf.train.comm_mode = 1;
+        topology_finalize(&cf.topo, &err);
+        Decomp df;
+        decompose(cf, &df, &err);
+        Plan pf;
+        CHECK(build_plan_v2(cf, df, 0, plan_hash(cf, df), topology_hash(cf.topo), &pf, &err) == OK, "fused tp8 plan: %s", err.c_str());
+        VerifyReport good;
+        verify_peer_reuse(pf, &good);
+        CHECK(good.problems == 0 && !good.lines.empty(), "peer reuse of the fused tp8 plan: %d problems", good.problems);
+        for (ExecOp& x : pf.exec)
+            if (x.kernel == K_AG_GEMM) x.kernel = K_GEMM;
+        VerifyReport bad;
+        verify_peer_reuse(pf, &bad);
+        CHECK(bad.problems > 0, "peer-reuse proof missed reduce-scatters that share a staging buffer without a group-ordering op");
+    }
+
     // Column views: two unordered writers on different streams are fine when they cover disjoint columns of
     // the same rows (dQ beside dK/dV), and a hazard as soon as the column intervals touch.
     for (int overlap = 0; overlap < 2; ++overlap) {
