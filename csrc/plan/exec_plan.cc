@@ -380,7 +380,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
 
     const bool moe = m.is_moe != 0;
     if (moe) {
-        if (d.tp != 1 || d.pp != 1) return failf(err, ERR_INVALID, "MoE plans need tp = 1 and pp = 1 (got tp=%u pp=%u)", d.tp, d.pp);
+        if (d.tp != 1) return failf(err, ERR_INVALID, "MoE plans need tp = 1 (got tp=%u): the expert GEMMs are not split over a tensor-parallel group", d.tp);
         if (d.ep != 1 && d.ep != d.dp) return failf(err, ERR_INVALID, "MoE plans need ep = 1 or ep = dp (got ep=%u dp=%u)", d.ep, d.dp);
         if (m.num_experts % 32 || m.num_experts > 256 || m.moe_top_k < 1 || m.moe_top_k > 8 || m.num_experts % d.ep)
             return failf(err, ERR_INVALID, "MoE plans need experts %% 32 == 0 (<= 256), top_k <= 8, experts %% ep == 0");
