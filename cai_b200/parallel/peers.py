@@ -66,11 +66,24 @@ class PeerArenas:
         self.opened.clear()
 
 
+def expert_group_members(hdr, rank):
+    """Members of the expert group of a mixture-of-experts plan under tensor parallelism: the tp ranks of each of
+    the ep data-parallel replicas of this rank's block (member index = replica * tp + tp rank). The experts are spread
+    over all of them; every member routes the rows of the sequence it owns."""
+    tp, ep = int(hdr.tp), max(1, int(hdr.ep))
+    replica = tp * int(hdr.num_stages) * int(hdr.cp)
+    tp_id, within, dp_id = rank % tp, rank % replica, rank // replica
+    first_dp = (dp_id // ep) * ep
+    return [within - tp_id + t + (first_dp + i) * replica for i in range(ep) for t in range(tp)]
+
+
 def attach(engine, groups, store):
-    """Exchange arenas for every communicator the plan runs fused kernels on (TP and DP)."""
+    """Exchange arenas for every communicator the plan runs fused kernels on (TP, DP and the expert group)."""
     pa = PeerArenas(engine, store)
     for g in groups:
         if g.kind in (planlib.GROUP_TP, planlib.GROUP_DP) and g.size > 1:
             members = planlib.group_members(engine.config_text, g.kind, engine.rank)
             pa.attach_group(g.kind, members)
+    if engine.model.is_moe and engine.hdr.tp > 1:
+        pa.attach_group(planlib.GROUP_EP, expert_group_members(engine.hdr, engine.rank))
     return pa

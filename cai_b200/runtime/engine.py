@@ -280,9 +280,11 @@ class Engine:
         base = name.split(".")[-1]
         if ".experts." in name:
             # local experts are a contiguous block of rows of the all-experts tensor
+            # (under tensor parallelism the experts are spread over the tp x ep ranks of the expert group)
             ep = max(1, self.hdr.ep)
             ep_id = (self.rank // (self.hdr.tp * self.hdr.num_stages * self.hdr.cp)) % ep
-            return (rows * ep, cols), (slice(ep_id * rows, (ep_id + 1) * rows), slice(None))
+            members, me = ep * tp, ep_id * tp + tp_id
+            return (rows * members, cols), (slice(me * rows, (me + 1) * rows), slice(None))
         if base in ("embed", "lm_head"):
             return (m.vocab_size, H), (slice(tp_id * rows, (tp_id + 1) * rows), slice(None))
         if base == "wqkv":

@@ -380,7 +380,10 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
 
     const bool moe = m.is_moe != 0;
     if (moe) {
-        if (d.tp != 1) return failf(err, ERR_INVALID, "MoE plans need tp = 1 (got tp=%u): the expert GEMMs are not split over a tensor-parallel group", d.tp);
+        // Under tensor parallelism the experts are spread over the tp x ep ranks of a replica block (every rank routes
+        // the rows of the sequence it owns), so that group must fit one peer table.
+        if (d.tp * std::max(1u, d.ep) > static_cast<uint32_t>(kMaxPeers) || m.num_experts % (d.tp * std::max(1u, d.ep)))
+            return failf(err, ERR_INVALID, "MoE plans need tp x ep <= %d and experts %% (tp x ep) == 0 (got tp=%u ep=%u)", kMaxPeers, d.tp, d.ep);
         if (d.ep != 1 && d.ep != d.dp) return failf(err, ERR_INVALID, "MoE plans need ep = 1 or ep = dp (got ep=%u dp=%u)", d.ep, d.dp);
         if (m.num_experts % 32 || m.num_experts > 256 || m.moe_top_k < 1 || m.moe_top_k > 8 || m.num_experts % d.ep)
             return failf(err, ERR_INVALID, "MoE plans need experts %% 32 == 0 (<= 256), top_k <= 8, experts %% ep == 0");
@@ -511,7 +514,8 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     }
     // Expert weights come last in the flat space: everything before them is replicated over the
     // data-parallel group (gradients are reduced), the experts of an expert-parallel group are not.
-    const uint32_t E_l = moe ? m.num_experts / d.ep : 0;
+    const uint32_t xg = moe ? d.tp * std::max(1u, d.ep) : 1;   // members of the expert group: tp x ep
+    const uint32_t E_l = moe ? m.num_experts / xg : 0;
     const uint64_t n_replicated = moe && d.ep > 1 ? align_up(b.flat_elems, kFlatAlignElems) : 0;
     if (moe)
         for (uint32_t l = 0; l < b.layers; ++l) {
@@ -712,22 +716,22 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     // Mixture of experts: every member keeps, per local expert and per source member, a slab of
     // `moe_cap` rows (capacity factor x the even share); tokens beyond a slab's capacity skip that expert.
     const uint32_t moe_cap = moe ? static_cast<uint32_t>(align_up(
-        static_cast<uint64_t>(std::max(1.0, cfg.train.moe_capacity_factor_x100 / 100.0) * T * m.moe_top_k / m.num_experts + 0.999), 128)) : 0;
-    const uint32_t moe_rows = moe ? E_l * d.ep * moe_cap : 0;
+        static_cast<uint64_t>(std::max(1.0, cfg.train.moe_capacity_factor_x100 / 100.0) * Tl * m.moe_top_k / m.num_experts + 0.999), 128)) : 0;
+    const uint32_t moe_rows = moe ? E_l * xg * moe_cap : 0;   // every member routes its own Tl rows of the sequence
     int dy_s = -1, dact_s = -1, dgu_s = -1, dx_s = -1, dw_r = -1, dlogits = -1;
     if (moe) {
         dy_s = b.tensor(TC_COMM, DT_BF16, moe_rows, H);        // gradient rows pushed by the token owners
         dx_s = b.tensor(TC_COMM, DT_BF16, moe_rows, H);        // input gradients pulled back by the token owners
         dact_s = b.tensor(TC_WORKSPACE, DT_BF16, moe_rows, m.ffn_hidden);
         dgu_s = b.tensor(TC_WORKSPACE, DT_BF16, moe_rows, 2 * m.ffn_hidden);
-        dw_r = b.tensor(TC_WORKSPACE, DT_FP32, T, m.moe_top_k);
-        dlogits = b.tensor(TC_WORKSPACE, DT_BF16, T, m.num_experts);
+        dw_r = b.tensor(TC_WORKSPACE, DT_FP32, Tl, m.moe_top_k);
+        dlogits = b.tensor(TC_WORKSPACE, DT_BF16, Tl, m.num_experts);
     }
     auto moe_dispatch = [&](int rows, int scale, const LayerActs& a, int slab, uint16_t mb) {
         ExecOp e = xop(K_MOE_DISPATCH_GEMM);
         e.t[0] = rows; e.t[1] = a.ridx; e.t[2] = a.rpos; e.t[3] = scale; e.t[4] = a.counts; e.t[5] = slab; e.t[6] = a.cnt_recv;
         e.i[0] = m.moe_top_k; e.i[1] = m.num_experts; e.i[2] = moe_cap; e.i[3] = GROUP_EP; e.i[4] = static_cast<int32_t>(b.next_seq++);
-        b.push(OP_MOE_DISPATCH_GEMM, ST_COMPUTE_HI, 0, 2.0 * T * m.moe_top_k * H, GROUP_EP, mb, &e);
+        b.push(OP_MOE_DISPATCH_GEMM, ST_COMPUTE_HI, 0, 2.0 * Tl * m.moe_top_k * H, GROUP_EP, mb, &e);
     };
     // mode 0: out = base + sum_s w_s * slab row ; mode 1: plain sum ; mode 2: dw[t, s] = <dot_with[t], slab row>
     auto moe_combine = [&](int base, int outt, int weights, const LayerActs& a, int slab, int dot_with, int dw, bool announce,
@@ -735,7 +739,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         ExecOp e = xop(K_MOE_GEMM_COMBINE, announce ? 1 : 0);
         e.t[0] = base; e.t[1] = outt; e.t[2] = a.ridx; e.t[3] = a.rpos; e.t[4] = weights; e.t[5] = slab; e.t[6] = dot_with; e.t[7] = dw;
         e.i[0] = m.moe_top_k; e.i[1] = m.num_experts; e.i[2] = moe_cap; e.i[3] = GROUP_EP; e.i[4] = static_cast<int32_t>(b.next_seq++);
-        b.push(OP_MOE_GEMM_COMBINE, ST_COMPUTE_HI, 2.0 * T * m.moe_top_k * H, 2.0 * T * m.moe_top_k * H, GROUP_EP, mb, &e);
+        b.push(OP_MOE_GEMM_COMBINE, ST_COMPUTE_HI, 2.0 * Tl * m.moe_top_k * H, 2.0 * Tl * m.moe_top_k * H, GROUP_EP, mb, &e);
     };
     // ---------------- activations: one set per in-flight microbatch
     const uint32_t slots = std::max<uint32_t>(1, std::min<uint32_t>(d.pp - b.stage, ga));
@@ -754,17 +758,17 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         a.lse = b.tensor(TC_ACTIVATION, DT_FP32, b.nh_l, T);
         a.hmid = b.tensor(TC_ACTIVATION, DT_BF16, Tl, H);
         a.rstd2 = b.tensor(TC_ACTIVATION, DT_FP32, 1, Tl);
-        a.xn2 = b.tensor(TC_ACTIVATION, DT_BF16, T, H);
+        a.xn2 = b.tensor(TC_ACTIVATION, DT_BF16, moe ? Tl : T, H);   // MoE: the router and the dispatch work on the local rows
         if (!moe) {
             a.gu = b.tensor(TC_ACTIVATION, DT_BF16, T, 2 * b.F_l);
             a.act = b.tensor(TC_ACTIVATION, DT_BF16, T, b.F_l);
         } else {
-            a.logits = b.tensor(TC_ACTIVATION, DT_FP32, T, m.num_experts);
-            a.ridx = b.tensor(TC_ACTIVATION, DT_INT32, T, m.moe_top_k);
-            a.rw = b.tensor(TC_ACTIVATION, DT_FP32, T, m.moe_top_k);
-            a.rpos = b.tensor(TC_ACTIVATION, DT_INT32, T, m.moe_top_k);
+            a.logits = b.tensor(TC_ACTIVATION, DT_FP32, Tl, m.num_experts);
+            a.ridx = b.tensor(TC_ACTIVATION, DT_INT32, Tl, m.moe_top_k);
+            a.rw = b.tensor(TC_ACTIVATION, DT_FP32, Tl, m.moe_top_k);
+            a.rpos = b.tensor(TC_ACTIVATION, DT_INT32, Tl, m.moe_top_k);
             a.counts = b.tensor(TC_ACTIVATION, DT_INT32, 1, m.num_experts);
-            a.cnt_recv = b.tensor(TC_COMM, DT_INT32, 1, E_l * d.ep);     // written by the sending members
+            a.cnt_recv = b.tensor(TC_COMM, DT_INT32, 1, E_l * xg);       // written by the sending members
             a.xs = b.tensor(TC_COMM, DT_BF16, moe_rows, H);              // expert inputs, written by the senders
             a.gu = b.tensor(TC_ACTIVATION, DT_BF16, moe_rows, 2 * m.ffn_hidden);
             a.act = b.tensor(TC_ACTIVATION, DT_BF16, moe_rows, m.ffn_hidden);
@@ -867,14 +871,14 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         b.row_parallel(a.ao, w.wo.w, a.x, a.hmid, partial, rs_tmp, H, b.Hq_l, false, mb);
         if (moe) {
             // router -> dispatch (permute + peer stores) -> expert FFN over the slabs -> combine (peer loads)
-            const uint32_t F = m.ffn_hidden, seg_m = d.ep * moe_cap;
-            b.rmsnorm_fwd(a.hmid, w.g2.w, a.xn2, a.rstd2, T, mb);
-            b.gemm(ST_COMPUTE_HI, a.xn2, w.wr.w, a.logits, -1, T, m.num_experts, H, false, false, 1, mb);
+            const uint32_t F = m.ffn_hidden, seg_m = xg * moe_cap;
+            b.rmsnorm_fwd(a.hmid, w.g2.w, a.xn2, a.rstd2, Tl, mb);
+            b.gemm(ST_COMPUTE_HI, a.xn2, w.wr.w, a.logits, -1, Tl, m.num_experts, H, false, false, 1, mb);
             {
                 ExecOp e = xop(K_MOE_ROUTE);
                 e.t[0] = a.logits; e.t[1] = a.ridx; e.t[2] = a.rw; e.t[3] = a.rpos; e.t[4] = a.counts;
-                e.i[0] = T; e.i[1] = m.num_experts; e.i[2] = m.moe_top_k; e.i[3] = moe_cap;
-                b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 10.0 * T * m.num_experts, 0, 0, mb, &e);
+                e.i[0] = Tl; e.i[1] = m.num_experts; e.i[2] = m.moe_top_k; e.i[3] = moe_cap;
+                b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 10.0 * Tl * m.num_experts, 0, 0, mb, &e);
             }
             moe_dispatch(a.xn2, -1, a, a.xs, mb);
             b.gemm_grouped(a.xs, w.wgu.w, a.gu, seg_m, 2 * F, H, false, false, 0, a.cnt_recv, moe_cap, 1, E_l, mb);
@@ -1034,7 +1038,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             }
             if (recompute) layer_forward(mb, a, w, x_scratch);
             if (moe) {
-                const uint32_t F = m.ffn_hidden, seg_m = d.ep * moe_cap;
+                const uint32_t F = m.ffn_hidden, seg_m = xg * moe_cap;
                 moe_combine(-1, -1, -1, a, a.ys, dstream, dw_r, false, mb);           // dw[t,s] = <dx_next[t], y(t,s)>
                 moe_dispatch(dstream, a.rw, a, dy_s, mb);                              // dy rows = w[t,s] * dx_next[t]
                 b.gemm_grouped(dy_s, w.wd.w, dact_s, seg_m, F, H, false, true, 0, a.cnt_recv, moe_cap, 1, E_l, mb);
@@ -1051,12 +1055,12 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
                 {
                     ExecOp e = xop(K_MOE_ROUTE, 1);
                     e.t[0] = a.logits; e.t[1] = a.ridx; e.t[2] = dw_r; e.t[3] = a.rpos; e.t[4] = dlogits;
-                    e.i[0] = T; e.i[1] = m.num_experts; e.i[2] = m.moe_top_k;
-                    b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 20.0 * T * m.num_experts, 0, 0, mb, &e);
+                    e.i[0] = Tl; e.i[1] = m.num_experts; e.i[2] = m.moe_top_k;
+                    b.push(OP_ELEMENTWISE, ST_COMPUTE_HI, 20.0 * Tl * m.num_experts, 0, 0, mb, &e);
                 }
-                b.gemm(ST_COMPUTE_HI, dlogits, w.wr.w, dxn, dxn, T, H, m.num_experts, false, true, 3, mb);   // dxn2 += dlogits * Wr
-                b.gemm(ST_COMPUTE_HI, dlogits, a.xn2, w.wr.g, -1, m.num_experts, H, T, true, true, wg_epi, mb);
-                b.rmsnorm_bwd(a.hmid, w.g2.w, a.rstd2, dxn, dstream, w.g2.g, norm_scratch, T, true, !first_mb, mb);
+                b.gemm(ST_COMPUTE_HI, dlogits, w.wr.w, dxn, dxn, Tl, H, m.num_experts, false, true, 3, mb);   // dxn2 += dlogits * Wr
+                b.gemm(ST_COMPUTE_HI, dlogits, a.xn2, w.wr.g, -1, m.num_experts, H, Tl, true, true, wg_epi, mb);
+                b.rmsnorm_bwd(a.hmid, w.g2.w, a.rstd2, dxn, dstream, w.g2.g, norm_scratch, Tl, true, !first_mb, mb);
             } else {
             // ---- MLP block: x_next = hmid + act * Wd^T
             prepare_layer(l, true, mb);                                                           // ZeRO-3 re-gather, top of the range first
@@ -1168,7 +1172,10 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     if (tp > 1) {
         b.sync(ST_COMPUTE_HI, ST_COMM_TP, 0);
         for (const NamedTensor& nt : out->named) {
-            if (nt.init_std != 0.f) continue;
+            const size_t nlen = std::strlen(nt.name);
+            const bool router = moe && nlen > 3 && !std::strcmp(nt.name + nlen - 3, ".wr");   // replicated over tp like the gains
+            if (nt.init_std != 0.f && !router) continue;
+            if (nt.init_std < 0.f) continue;
             b.nccl(K_NCCL_ALL_REDUCE, OP_ALL_REDUCE, ST_COMM_TP, nt.grad, nt.grad, static_cast<uint64_t>(nt.rows) * nt.cols,
                    DT_FP32, GROUP_TP, -1, 0);
         }

@@ -170,3 +170,31 @@ def test_moe_pipeline_2_x_expert_parallel_2(tmp_path):
     b = run_case(tmp_path, 4, config="tiny_moe", comm="fused", pp=2, ep=2)
     close(a["losses"], b["losses"])
     assert b["losses"][-1] < b["losses"][0]
+
+
+def test_moe_tensor_parallel_2_matches_single_gpu(tmp_path):
+    """Mixture of experts under tensor parallelism: attention is split over the two GPUs, the experts are spread
+    over them (each GPU routes the rows of the sequence it owns); same curve as one GPU."""
+    if _gpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    one = run_case(tmp_path, 1, config="tiny_moe_tp", comm="fused")
+    two = run_case(tmp_path, 2, config="tiny_moe_tp", comm="fused", tp=2)
+    close(two["losses"], one["losses"])
+
+
+def test_moe_tp2_x_ep2(tmp_path):
+    """tp 2 x ep 2 on four GPUs (experts over all four) against ep 2 on two GPUs: same global batch, same curve."""
+    if _gpus() < 4:
+        pytest.skip("needs 4 GPUs")
+    a = run_case(tmp_path, 2, config="tiny_moe_tp", comm="fused", ep=2)
+    b = run_case(tmp_path, 4, config="tiny_moe_tp", comm="fused", tp=2, ep=2)
+    close(a["losses"], b["losses"])
+
+
+def test_moe_tp2_pp2_ep2(tmp_path):
+    """All three at once, as in the reference's full220k_moe config: tp 2 x pp 2 x ep 2 on eight GPUs."""
+    if _gpus() < 8:
+        pytest.skip("needs 8 GPUs")
+    a = run_case(tmp_path, 2, config="tiny_moe_tp", comm="fused", ep=2)
+    b = run_case(tmp_path, 8, config="tiny_moe_tp", comm="fused", tp=2, pp=2, ep=2)
+    close(a["losses"], b["losses"])
