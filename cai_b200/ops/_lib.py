@@ -70,6 +70,8 @@ def _declare(L):
         L.cai_flash_attn_fwd_variant.argtypes = [P, P, P, I, I, I, I, I, F, I, P]
     if hasattr(L, "cai_flash_attn_bwd"):
         L.cai_flash_attn_bwd.argtypes = [P, P, P, P, P, P, I, I, I, I, I, F, P]
+    if hasattr(L, "cai_flash_attn_bwd_ex"):
+        L.cai_flash_attn_bwd_ex.argtypes = [P, P, P, P, P, P, I, I, I, I, I, F, I, I, P]
 
 
 def check(rc: int, what: str):

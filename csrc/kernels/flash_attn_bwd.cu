@@ -482,17 +482,413 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
     }
 }
 
+
+// ---------------------------------------------------------------------------- pipelined forms
+// The kernels above keep one 128 x 128 score tile in flight: the MMAs of a step wait for the exponentials of the
+// same step and the tensor pipe idles two thirds of the time. The forms below split every step into two 64-column
+// half steps with their own S / dP accumulators (64 TMEM columns each, the same 512 columns in total) and stream
+// the swept operand in 64-row half tiles through four shared-memory stages. The MMA thread runs the score products
+// of half step u + 2 right behind the gradient products of half step u, so the tensor pipe works on one half while
+// the compute warps work on the other. A warp group writes its bf16 results over the first half of the 32 fp32
+// columns it has just read (no other warp reads those), so a half step needs no barrier between the groups; the
+// A operand of the gradient products is addressed in two 16-column pieces.
+constexpr int kAttnPipeStages = 4;
+constexpr int kAttnPipeStageBytes = 2 * kAttnHalfBytes;  // two 64-row operands per stage (Q + dO, or K + V)
+
+struct AttnPipeSmem {
+    uint8_t* fixed0;   // dK/dV: K     dQ: Q
+    uint8_t* fixed1;   // dK/dV: V     dQ: dO
+    uint8_t* stages;   // 4 x (64-row operand pair)
+    float* sL;
+    float* sD;
+    uint64_t* fixed_full;
+    uint64_t* st_full;
+    uint64_t* st_empty;
+    uint64_t* sdp_full;
+    uint64_t* out_ready;
+    uint64_t* final_bar;
+    uint32_t* tmem_slot;
+    volatile int* abort_flag;
+};
+
+__device__ __forceinline__ AttnPipeSmem attn_pipe_carve(uint8_t* smem_raw) {
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    AttnPipeSmem m;
+    m.fixed0 = smem;
+    m.fixed1 = smem + kAttnTileBytes;
+    m.stages = smem + 2 * kAttnTileBytes;
+    m.sL = reinterpret_cast<float*>(smem + 2 * kAttnTileBytes + kAttnPipeStages * kAttnPipeStageBytes);
+    m.sD = m.sL + 256;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(m.sD + 256);
+    m.fixed_full = bars;
+    m.st_full = bars + 1;
+    m.st_empty = bars + 5;
+    m.sdp_full = bars + 9;
+    m.out_ready = bars + 11;
+    m.final_bar = bars + 13;
+    m.tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    m.abort_flag = reinterpret_cast<volatile int*>(m.tmem_slot + 1);
+    return m;
+}
+
+__device__ __forceinline__ void attn_pipe_init(const AttnPipeSmem& m) {
+    mbar_init(m.fixed_full, 1);
+    for (int i = 0; i < kAttnPipeStages; ++i) {
+        mbar_init(&m.st_full[i], 1);
+        mbar_init(&m.st_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+        mbar_init(&m.sdp_full[i], 1);
+        mbar_init(&m.out_ready[i], 256);
+    }
+    mbar_init(m.final_bar, 1);
+    *m.abort_flag = 0;
+    mbar_fence_init();
+}
+
+__global__ void __launch_bounds__(kAttnBwdThreads, 1)
+attn_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_qkv64,
+                      const __grid_constant__ CUtensorMap tm_do64, const AttnBwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const AttnPipeSmem m = attn_pipe_carve(smem_raw);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    const int heads_all = gridDim.y * gridDim.z;
+    const int j = lin / heads_all;  // kv tile, heaviest first
+    const int ysel = (lin % heads_all) % gridDim.y, b = (lin % heads_all) / gridDim.y;
+    const int rep = p.nh / p.nkv;
+    const int g = p.split_heads ? ysel / rep : ysel;
+    const int h_first = p.split_heads ? ysel : g * rep;
+    const int turn = p.split_heads ? ysel - g * rep : 0;
+    const int nq = p.S / kAttnTile;
+    const int per_head = nq - j;
+    const int iters = (p.split_heads ? 1 : rep) * per_head;
+    const int total = 2 * iters;  // half steps
+    const int row_base = b * p.S;
+    const int col_k = (p.nh + g) * kAttnHD, col_v = (p.nh + p.nkv + g) * kAttnHD;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tm_qkv);
+        tma_prefetch_desc(&tm_qkv64);
+        tma_prefetch_desc(&tm_do64);
+        attn_pipe_init(m);
+    }
+    if (warp == 1) {
+        tmem_alloc(m.tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *m.tmem_slot;
+    // half step s: S^T at tmem_base + s * 128, dP^T 64 columns behind it
+    const uint32_t tdV = tmem_base + 256, tdK = tmem_base + 384;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int kv_row = row_base + j * kAttnTile;
+            mbar_expect_tx(m.fixed_full, 2 * kAttnTileBytes);
+            tma_load_2d(m.fixed0, &tm_qkv, m.fixed_full, col_k, kv_row);
+            tma_load_2d(m.fixed0 + kAttnSub, &tm_qkv, m.fixed_full, col_k + 64, kv_row);
+            tma_load_2d(m.fixed1, &tm_qkv, m.fixed_full, col_v, kv_row);
+            tma_load_2d(m.fixed1 + kAttnSub, &tm_qkv, m.fixed_full, col_v + 64, kv_row);
+            bool ok = true;
+            for (int u = 0; u < total && ok; ++u) {
+                const int st = u & 3, it = u >> 1;
+                const uint32_t ph = (u >> 2) & 1;
+                const int h = h_first + it / per_head;
+                const int q_row = row_base + (j + it % per_head) * kAttnTile + (u & 1) * 64;
+                if (!mbar_wait(&m.st_empty[st], ph ^ 1, m.abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+                mbar_expect_tx(&m.st_full[st], kAttnPipeStageBytes);
+                uint8_t* q = m.stages + st * kAttnPipeStageBytes;
+                uint8_t* d = q + kAttnHalfBytes;
+                tma_load_2d(q, &tm_qkv64, &m.st_full[st], h * kAttnHD, q_row);
+                tma_load_2d(q + kAttnHalfSub, &tm_qkv64, &m.st_full[st], h * kAttnHD + 64, q_row);
+                tma_load_2d(d, &tm_do64, &m.st_full[st], h * kAttnHD, q_row);
+                tma_load_2d(d + kAttnHalfSub, &tm_do64, &m.st_full[st], h * kAttnHD + 64, q_row);
+            }
+            if (!ok)
+                for (int i = 0; i < 32; ++i) __nanosleep(50000);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_n64 = umma_idesc_bf16(128, 64, 0, 0);
+            const uint32_t idesc_mn = umma_idesc_bf16(128, 128, 0, 1);
+            const uint32_t aK = smem_u32(m.fixed0), aV = smem_u32(m.fixed1), aSt = smem_u32(m.stages);
+            bool ok = mbar_wait(m.fixed_full, 0, m.abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN);
+            // score products of half step u: S^T = K Q_u^T, dP^T = V dO_u^T
+            auto scores = [&](int u) -> bool {
+                const int st = u & 3, s = u & 1;
+                if (!mbar_wait(&m.st_full[st], (u >> 2) & 1, m.abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) return false;
+                tc_fence_after();
+                const uint32_t q = aSt + st * kAttnPipeStageBytes, d = q + kAttnHalfBytes;
+                issue_qk_n64(tmem_base + s * 128, aK, q, idesc_n64);
+                issue_qk_n64(tmem_base + s * 128 + 64, aV, d, idesc_n64);
+                umma_commit(&m.sdp_full[s]);
+                return true;
+            };
+            if (ok) ok = scores(0);
+            if (ok) ok = scores(1);
+            for (int u = 0; u < total && ok; ++u) {
+                const int st = u & 3, s = u & 1;
+                if (!mbar_wait(&m.out_ready[s], (u >> 1) & 1, m.abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t q = aSt + st * kAttnPipeStageBytes, d = q + kAttnHalfBytes;
+                issue_pv_k64(tdV, tmem_base + s * 128, d, idesc_mn, u > 0);       // dV += P^T dO
+                issue_pv_k64(tdK, tmem_base + s * 128 + 64, q, idesc_mn, u > 0);  // dK += dS^T Q
+                umma_commit(&m.st_empty[st]);
+                if (u + 2 < total) ok = scores(u + 2);
+            }
+            if (ok) umma_commit(m.final_bar);
+        }
+    } else if (warp >= 4) {
+        const int r = (warp & 3) * 32 + lane;  // kv row inside the tile == TMEM lane
+        const int half = warp >= 8 ? 1 : 0;    // which 32 of a half step's 64 query columns
+        const uint32_t lane_bits = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        bool ok = true;
+        for (int it = 0; it < iters && ok; ++it) {
+            const int h = h_first + it / per_head;
+            const int i = j + it % per_head;
+            const int buf = it & 1;
+            const long long vec = (static_cast<long long>(b) * p.nh + h) * p.S + i * kAttnTile + r;
+            if (half == 0) m.sL[buf * 128 + r] = p.lse[vec] * 1.4426950408889634f;
+            else m.sD[buf * 128 + r] = p.delta[vec];
+            bar_sync_compute();
+            const bool diag = (i == j);
+#pragma unroll 1
+            for (int s = 0; s < 2; ++s) {
+                if (!mbar_wait(&m.sdp_full[s], it & 1, m.abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+                tc_fence_after();
+                const int qb = s * 64 + half * 32;  // first query column of this thread's chunk
+                const uint32_t tS = tmem_base + lane_bits + s * 128 + half * 32;
+                const uint32_t tdP = tS + 64;
+                const float4* L4 = reinterpret_cast<const float4*>(m.sL + buf * 128 + qb);
+                const float4* D4 = reinterpret_cast<const float4*>(m.sD + buf * 128 + qb);
+                uint32_t sv[32], dp[32], pk[16], dk[16];
+                tmem_ld_32x32(tS, sv);
+                tmem_ld_32x32(tdP, dp);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e4 = 0; e4 < 8; ++e4) {
+                    const float4 l = L4[e4], dl = D4[e4];
+                    const float ls[4] = {l.x, l.y, l.z, l.w}, ds[4] = {dl.x, dl.y, dl.z, dl.w};
+                    float pr[4], dsv[4];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const int e = e4 * 4 + t;
+                        float pv = fast_exp2(__uint_as_float(sv[e]) * p.scale_log2 - ls[t]);
+                        if (diag && r > qb + e) pv = 0.f;  // key (row r) may not lie after the query (column)
+                        pr[t] = pv;
+                        dsv[t] = pv * (__uint_as_float(dp[e]) - ds[t]) * p.scale;
+                    }
+                    pk[e4 * 2] = pack_bf16(pr[0], pr[1]);
+                    pk[e4 * 2 + 1] = pack_bf16(pr[2], pr[3]);
+                    dk[e4 * 2] = pack_bf16(dsv[0], dsv[1]);
+                    dk[e4 * 2 + 1] = pack_bf16(dsv[2], dsv[3]);
+                }
+                tmem_st_32x16(tS, pk);
+                tmem_st_32x16(tdP, dk);
+                tmem_st_wait();
+                tc_fence_before();
+                mbar_arrive(&m.out_ready[s]);
+            }
+        }
+        if (ok && mbar_wait(m.final_bar, 0, m.abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) {
+            tc_fence_after();
+            const long long grow = static_cast<long long>(row_base) + j * kAttnTile + r;
+            const long long ld = static_cast<long long>(p.nh + 2 * p.nkv) * kAttnHD;
+            __nv_bfloat16* dst = p.dqkv + grow * ld + (half == 0 ? col_k : col_v);
+            const uint32_t tacc = (half == 0 ? tdK : tdV) + lane_bits;
+            if (!p.split_heads) {
+                store_acc_bf16(tacc, dst);
+            } else {
+                unsigned int* cnt = p.chain + (static_cast<long long>(b) * p.nkv + g) * nq + j;
+                bool go = true;
+                if (turn > 0) {
+                    go = false;
+                    for (uint32_t spin = 0; spin < kSpinLimit && !go; ++spin) {
+                        unsigned int v;
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+                        go = v >= static_cast<unsigned int>(turn);
+                        if (!go && spin > 16) __nanosleep(200);
+                    }
+                    if (!go) atomicCAS(p.status, 0, CAI_DEV_TIMEOUT_ATTN);
+                }
+                if (go) {
+                    if (turn == 0) store_acc_bf16(tacc, dst);
+                    else add_acc_bf16(tacc, dst);
+                }
+                __threadfence();
+                bar_sync_compute();
+                if (threadIdx.x == 128) {
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(cnt), "r"(static_cast<unsigned int>(turn + 1)) : "memory");
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+__global__ void __launch_bounds__(kAttnBwdThreads, 1)
+attn_dq_pipe_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
+                    const __grid_constant__ CUtensorMap tm_qkv64, const AttnBwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const AttnPipeSmem m = attn_pipe_carve(smem_raw);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    const int heads_all = gridDim.y * gridDim.z;
+    const int i = gridDim.x - 1 - lin / heads_all;  // q tile, heaviest first across all heads
+    const int h = (lin % heads_all) % gridDim.y, b = (lin % heads_all) / gridDim.y;
+    const int g = h / (p.nh / p.nkv);
+    const int total = 2 * (i + 1);  // half steps: 64 keys each
+    const int row_base = b * p.S;
+    const int col_q = h * kAttnHD, col_k = (p.nh + g) * kAttnHD, col_v = (p.nh + p.nkv + g) * kAttnHD;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tm_qkv);
+        tma_prefetch_desc(&tm_do);
+        tma_prefetch_desc(&tm_qkv64);
+        attn_pipe_init(m);
+    }
+    if (warp == 1) {
+        tmem_alloc(m.tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *m.tmem_slot;
+    const uint32_t tdQ = tmem_base + 256;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int q_row = row_base + i * kAttnTile;
+            mbar_expect_tx(m.fixed_full, 2 * kAttnTileBytes);
+            tma_load_2d(m.fixed0, &tm_qkv, m.fixed_full, col_q, q_row);
+            tma_load_2d(m.fixed0 + kAttnSub, &tm_qkv, m.fixed_full, col_q + 64, q_row);
+            tma_load_2d(m.fixed1, &tm_do, m.fixed_full, col_q, q_row);
+            tma_load_2d(m.fixed1 + kAttnSub, &tm_do, m.fixed_full, col_q + 64, q_row);
+            bool ok = true;
+            for (int u = 0; u < total && ok; ++u) {
+                const int st = u & 3;
+                const uint32_t ph = (u >> 2) & 1;
+                const int kv_row = row_base + u * 64;
+                if (!mbar_wait(&m.st_empty[st], ph ^ 1, m.abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+                mbar_expect_tx(&m.st_full[st], kAttnPipeStageBytes);
+                uint8_t* k = m.stages + st * kAttnPipeStageBytes;
+                uint8_t* v = k + kAttnHalfBytes;
+                tma_load_2d(k, &tm_qkv64, &m.st_full[st], col_k, kv_row);
+                tma_load_2d(k + kAttnHalfSub, &tm_qkv64, &m.st_full[st], col_k + 64, kv_row);
+                tma_load_2d(v, &tm_qkv64, &m.st_full[st], col_v, kv_row);
+                tma_load_2d(v + kAttnHalfSub, &tm_qkv64, &m.st_full[st], col_v + 64, kv_row);
+            }
+            if (!ok)
+                for (int k = 0; k < 32; ++k) __nanosleep(50000);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_n64 = umma_idesc_bf16(128, 64, 0, 0);
+            const uint32_t idesc_mn = umma_idesc_bf16(128, 128, 0, 1);
+            const uint32_t aQ = smem_u32(m.fixed0), aD = smem_u32(m.fixed1), aSt = smem_u32(m.stages);
+            bool ok = mbar_wait(m.fixed_full, 0, m.abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN);
+            auto scores = [&](int u) -> bool {   // S = Q K_u^T, dP = dO V_u^T
+                const int st = u & 3, s = u & 1;
+                if (!mbar_wait(&m.st_full[st], (u >> 2) & 1, m.abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) return false;
+                tc_fence_after();
+                const uint32_t k = aSt + st * kAttnPipeStageBytes, v = k + kAttnHalfBytes;
+                issue_qk_n64(tmem_base + s * 128, aQ, k, idesc_n64);
+                issue_qk_n64(tmem_base + s * 128 + 64, aD, v, idesc_n64);
+                umma_commit(&m.sdp_full[s]);
+                return true;
+            };
+            if (ok) ok = scores(0);
+            if (ok) ok = scores(1);
+            for (int u = 0; u < total && ok; ++u) {
+                const int st = u & 3, s = u & 1;
+                if (!mbar_wait(&m.out_ready[s], (u >> 1) & 1, m.abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+                tc_fence_after();
+                issue_pv_k64(tdQ, tmem_base + s * 128 + 64, aSt + st * kAttnPipeStageBytes, idesc_mn, u > 0);  // dQ += dS K
+                umma_commit(&m.st_empty[st]);
+                if (u + 2 < total) ok = scores(u + 2);
+            }
+            if (ok) umma_commit(m.final_bar);
+        }
+    } else if (warp >= 4) {
+        const int r = (warp & 3) * 32 + lane;  // q row inside the tile
+        const int half = warp >= 8 ? 1 : 0;    // which 32 of a half step's 64 key columns
+        const uint32_t lane_bits = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const long long vec = (static_cast<long long>(b) * p.nh + h) * p.S + i * kAttnTile + r;
+        const float lse2 = p.lse[vec] * 1.4426950408889634f;
+        const float dl = p.delta[vec];
+        bool ok = true;
+#pragma unroll 1
+        for (int u = 0; u < total; ++u) {
+            const int s = u & 1;
+            if (!mbar_wait(&m.sdp_full[s], (u >> 1) & 1, m.abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+            tc_fence_after();
+            const bool diag = (u >> 1) == i;
+            const int kb = s * 64 + half * 32;  // first key column (inside the 128-key tile) of this thread's chunk
+            const uint32_t tS = tmem_base + lane_bits + s * 128 + half * 32;
+            const uint32_t tdP = tS + 64;
+            uint32_t sv[32], dp[32], dk[16];
+            tmem_ld_32x32(tS, sv);
+            tmem_ld_32x32(tdP, dp);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+                float p0 = fast_exp2(__uint_as_float(sv[e]) * p.scale_log2 - lse2);
+                float p1 = fast_exp2(__uint_as_float(sv[e + 1]) * p.scale_log2 - lse2);
+                if (diag) {
+                    if (kb + e > r) p0 = 0.f;
+                    if (kb + e + 1 > r) p1 = 0.f;
+                }
+                dk[e >> 1] = pack_bf16(p0 * (__uint_as_float(dp[e]) - dl) * p.scale,
+                                       p1 * (__uint_as_float(dp[e + 1]) - dl) * p.scale);
+            }
+            tmem_st_32x16(tdP, dk);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&m.out_ready[s]);
+        }
+        if (ok && mbar_wait(m.final_bar, 0, m.abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) {
+            tc_fence_after();
+            const long long grow = static_cast<long long>(row_base) + i * kAttnTile + r;
+            const long long ld = static_cast<long long>(p.nh + 2 * p.nkv) * kAttnHD;
+            store_acc_bf16(tdQ + lane_bits, p.dqkv + grow * ld + col_q, half * 2, half * 2 + 2);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
 }  // namespace cai
 
 using namespace cai;
 
 CAI_API int cai_flash_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
                                void* dqkv, int B, int S, int nh, int nkv, int hd, float scale, void* stream) {
-    return cai_flash_attn_bwd_parts(qkv, out, dout, lse, delta, dqkv, B, S, nh, nkv, hd, scale, 7, stream);
+    return cai_flash_attn_bwd_ex(qkv, out, dout, lse, delta, dqkv, B, S, nh, nkv, hd, scale, 7, 0, stream);
 }
 
 CAI_API int cai_flash_attn_bwd_parts(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
                                      void* dqkv, int B, int S, int nh, int nkv, int hd, float scale, int parts, void* stream) {
+    return cai_flash_attn_bwd_ex(qkv, out, dout, lse, delta, dqkv, B, S, nh, nkv, hd, scale, parts, 0, stream);
+}
+
+CAI_API int cai_flash_attn_bwd_ex(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
+                                  void* dqkv, int B, int S, int nh, int nkv, int hd, float scale, int parts, int variant,
+                                  void* stream) {
     if (hd != kAttnHD || S % kAttnTile || nkv <= 0 || nh % nkv) {
         set_last_error("flash_attn_bwd: needs head_dim 128, seq %% 128 == 0, heads %% kv_heads == 0");
         return CAI_K_BAD_ARG;
@@ -504,12 +900,19 @@ CAI_API int cai_flash_attn_bwd_parts(const void* qkv, const void* out, const voi
     CUtensorMap tm_qkv, tm_do;
     if (!encode_tmap_2d(&tm_qkv, qkv, static_cast<uint64_t>(B) * S, ld, ld, 64, kAttnTile, 2)) return CAI_K_BAD_ARG;
     if (!encode_tmap_2d(&tm_do, dout, static_cast<uint64_t>(B) * S, ldo, ldo, 64, kAttnTile, 2)) return CAI_K_BAD_ARG;
+    const bool pipelined = variant != 1;
+    CUtensorMap tm_qkv64, tm_do64;  // 64-row boxes: the half tiles the pipelined kernels stream
+    if (pipelined && (!encode_tmap_2d(&tm_qkv64, qkv, static_cast<uint64_t>(B) * S, ld, ld, 64, 64, 2) ||
+                      !encode_tmap_2d(&tm_do64, dout, static_cast<uint64_t>(B) * S, ldo, ldo, 64, 64, 2)))
+        return CAI_K_BAD_ARG;
     constexpr int smem_bytes = 6 * kAttnTileBytes + 2048 + 1024 + 256;
     static bool configured[64] = {};
     const int dev = current_device();
     if (!configured[dev & 63]) {
         if (cudaFuncSetAttribute(attn_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess ||
-            cudaFuncSetAttribute(attn_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
+            cudaFuncSetAttribute(attn_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_dkdv_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_dq_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
             set_last_error("cudaFuncSetAttribute(attn_bwd) failed");
             return CAI_K_CUDA;
         }
@@ -548,9 +951,14 @@ CAI_API int cai_flash_attn_bwd_parts(const void* qkv, const void* out, const voi
         p.split_heads = 1;
         p.chain = chain_ptr[dev & 63];
     }
-    if (parts & 2)
-        attn_dkdv_kernel<<<dim3(nq, p.split_heads ? nh : nkv, B), kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_do, p);
-    if (parts & 4) attn_dq_kernel<<<dim3(nq, nh, B), kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_do, p);
+    const dim3 grid_kv(nq, p.split_heads ? nh : nkv, B), grid_q(nq, nh, B);
+    if (pipelined) {
+        if (parts & 2) attn_dkdv_pipe_kernel<<<grid_kv, kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_qkv64, tm_do64, p);
+        if (parts & 4) attn_dq_pipe_kernel<<<grid_q, kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_do, tm_qkv64, p);
+    } else {
+        if (parts & 2) attn_dkdv_kernel<<<grid_kv, kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_do, p);
+        if (parts & 4) attn_dq_kernel<<<grid_q, kAttnBwdThreads, smem_bytes, st>>>(tm_qkv, tm_do, p);
+    }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         set_last_error("attn_bwd launch failed: %s", cudaGetErrorString(e));
