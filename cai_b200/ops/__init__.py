@@ -223,16 +223,15 @@ def flash_attn_fwd(qkv, B, S, nh, nkv, hd, scale=None, variant=0):
     return out, lse
 
 
-def flash_attn_bwd(qkv, out, dout, lse, B, S, nh, nkv, hd, scale=None, dqkv=None, delta=None, variant=0, parts=7):
-    """Causal GQA flash attention backward. ``variant``: 0 = default (pipelined half steps), 1 = one score tile in
-    flight per CTA; ``parts``: bit 0 delta, bit 1 dK / dV, bit 2 dQ."""
+def flash_attn_bwd(qkv, out, dout, lse, B, S, nh, nkv, hd, scale=None, dqkv=None, delta=None, parts=7):
+    """Causal GQA flash attention backward. ``parts``: bit 0 delta, bit 1 dK / dV, bit 2 dQ."""
     scale = hd ** -0.5 if scale is None else scale
     if dqkv is None:
         dqkv = torch.empty_like(qkv)
     if delta is None:
         delta = torch.empty((B, nh, S), device=qkv.device, dtype=torch.float32)
-    check(lib().cai_flash_attn_bwd_ex(_p(qkv), _p(out), _p(dout), _p(lse), _p(delta), _p(dqkv), B, S, nh, nkv, hd,
-                                      float(scale), int(parts), int(variant), _stream()), "flash_attn_bwd")
+    check(lib().cai_flash_attn_bwd_parts(_p(qkv), _p(out), _p(dout), _p(lse), _p(delta), _p(dqkv), B, S, nh, nkv, hd,
+                                         float(scale), int(parts), _stream()), "flash_attn_bwd")
     return dqkv
 
 

@@ -70,8 +70,7 @@ def _declare(L):
         L.cai_flash_attn_fwd_variant.argtypes = [P, P, P, I, I, I, I, I, F, I, P]
     if hasattr(L, "cai_flash_attn_bwd"):
         L.cai_flash_attn_bwd.argtypes = [P, P, P, P, P, P, I, I, I, I, I, F, P]
-    if hasattr(L, "cai_flash_attn_bwd_ex"):
-        L.cai_flash_attn_bwd_ex.argtypes = [P, P, P, P, P, P, I, I, I, I, I, F, I, I, P]
+        L.cai_flash_attn_bwd_parts.argtypes = [P, P, P, P, P, P, I, I, I, I, I, F, I, P]
 
 
 def check(rc: int, what: str):

@@ -70,8 +70,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
-    ap.add_argument("--variant", type=int, default=0, help="attn_fwd: 0 auto, 1 one tile per CTA, 2 two tiles per CTA; "
-                    "attn_bwd: 0 pipelined half steps, 1 one score tile in flight")
+    ap.add_argument("--variant", type=int, default=0, help="attn_fwd: 0 auto, 1 one tile per CTA, 2 two tiles per CTA")
     ap.add_argument("--parts", type=int, default=7, help="attn_bwd: bit 0 delta, bit 1 dK/dV, bit 2 dQ")
     a = ap.parse_args(argv)
     dev = "cuda"
@@ -119,7 +118,7 @@ def main(argv=None):
             dqkv = torch.empty_like(qkv)
             delta = torch.empty_like(lse)
             ms = timeit(lambda: flash_attn_bwd(qkv, o, do, lse, a.batch, a.seq, a.heads, a.kv_heads, hd, dqkv=dqkv,
-                                               delta=delta, variant=a.variant, parts=a.parts), a.iters, a.warmup, flush)
+                                               delta=delta, parts=a.parts), a.iters, a.warmup, flush)
             flops = 2.5 * causal_flops
         tf = flops / ms / 1e9
         out.update(batch=a.batch, seq=a.seq, heads=a.heads, kv_heads=a.kv_heads, ms=ms, tflops_useful=tf,

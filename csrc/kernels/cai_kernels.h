@@ -180,10 +180,4 @@ CAI_API int cai_flash_attn_bwd(const void* qkv, const void* out, const void* dou
  * capture. */
 CAI_API int cai_flash_attn_bwd_parts(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
                                      void* dqkv, int B, int S, int nh, int nkv, int hd, float scale, int parts, void* stream);
-/* variant: 0 / 2 = pipelined kernels (two 64-column half steps in flight per CTA, the swept operand streamed in
- * 64-row half tiles), 1 = one 128 x 128 score tile in flight per CTA. */
-CAI_API int cai_flash_attn_bwd_ex(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
-                                  void* dqkv, int B, int S, int nh, int nkv, int hd, float scale, int parts, int variant,
-                                  void* stream);
-
 #endif /* CAI_KERNELS_H */

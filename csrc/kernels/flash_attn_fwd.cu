@@ -78,7 +78,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
             mbar_init(&v_full[i], 1);
             mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], 128);
+            mbar_init(&p_full[i], 4);
             mbar_init(&o_final[i], 1);
         }
         *abort_flag = 0;
@@ -180,7 +180,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
             float m_used = -INFINITY, l = 0.f;
             bool ok = true;
             for (int j = 0; j < nx; ++j) {
-                if (!mbar_wait(&s_full[X], j & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+                if (!mbar_wait_warp(&s_full[X], j & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
                 tc_fence_after();
                 const bool diag = (j == nx - 1);
                 // the whole score row (128 fp32) comes into registers with one wait and is used for both the
@@ -246,9 +246,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
                 }
                 tmem_st_wait();
                 tc_fence_before();
-                mbar_arrive(&p_full[X]);
+                mbar_arrive_warp(&p_full[X]);
             }
-            if (ok && mbar_wait(&o_final[X], 0, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) {
+            if (ok && mbar_wait_warp(&o_final[X], 0, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) {
                 tc_fence_after();
                 const float inv = 1.f / l;
                 const long long grow = static_cast<long long>(row_base) + q0 + r;
@@ -334,7 +334,7 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) 
             mbar_init(&v_full[i], 1);
             mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], 128);
+            mbar_init(&p_full[i], 4);
         }
         mbar_init(pv_done, 1);
         *abort_flag = 0;
@@ -414,7 +414,7 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) 
         bool ok = true;
         for (int j = 0; j < n; ++j) {
             const uint32_t tS = tmem_base + (j & 1) * 128 + lane_bits;
-            if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+            if (!mbar_wait_warp(&s_full[j & 1], (j >> 1) & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
             tc_fence_after();
             const bool diag = (j == n - 1);
             uint32_t sc[4][32];
@@ -446,7 +446,7 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) 
                 l *= alpha;
                 if (j > 0) {
                     // O is complete up to block j-1 only when that block's P V has finished
-                    if (!mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+                    if (!mbar_wait_warp(pv_done, (j - 1) & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
                     waited_pv = true;
                     tc_fence_after();
 #pragma unroll 1
@@ -483,12 +483,12 @@ attn_fwd1_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) 
             }
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(&p_full[j & 1]);
+            mbar_arrive_warp(&p_full[j & 1]);
             // every phase of pv_done is consumed exactly once per step, so its parity never runs ahead
             if (j > 0 && !waited_pv &&
-                !mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
+                !mbar_wait_warp(pv_done, (j - 1) & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) { ok = false; break; }
         }
-        if (ok && mbar_wait(pv_done, (n - 1) & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) {
+        if (ok && mbar_wait_warp(pv_done, (n - 1) & 1, abort_flag, p.status, CAI_DEV_TIMEOUT_ATTN)) {
             tc_fence_after();
             const float inv = 1.f / l;
             const long long grow = static_cast<long long>(row_base) + q0 + r;

@@ -99,6 +99,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     return false;
 }
 
+// The same for a whole converged warp: every lane leaves with the same answer, so the warp stays converged on
+// the failure path as well.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int code) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, code));
+}
+// One arrival for a converged warp whose lanes have all finished (and fenced) their part. Thirty-two separate
+// arrivals on one barrier word are serialised; with several warps they sit on the critical path of every step.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
