@@ -86,6 +86,12 @@ def build_kernels(verbose=False, ptxas_info=False) -> Path:
     lib = LIBDIR / "libcai_kernels.so"
     if jobs or _newer(lib, objs):
         _run([NVCC, "-shared", "-o", lib] + objs + ["-cudart", "static", "-ldl", "-lpthread"], verbose)
+    # stand-alone CUDA tools (measurement programs that need no Python): bin/<name>
+    BINDIR.mkdir(parents=True, exist_ok=True)
+    for t in sorted((CSRC / "tools").glob("*.cu")):
+        exe = BINDIR / t.stem
+        if _newer(exe, [t] + headers):
+            _run([NVCC] + NVCC_FLAGS + [t, "-o", exe, "-cudart", "static", "-lcuda"], verbose)
     return lib
 
 
