@@ -225,8 +225,23 @@ def lint(config_path):
     return rc, buf.value.decode()
 
 
+TENSOR_CLASSES = ("param", "grad", "optstate", "activation", "comm", "workspace")
+
+
 class PlanFile:
     """A plan file parsed into ctypes arrays (version 1 or 2)."""
+
+    def class_bytes(self) -> dict:
+        """Bytes every tensor class occupies in the arena (extent of the class's tensors; same rule as the C++
+        ``plan_class_bytes``): what a device allocates, as opposed to the memory model of the decomposition report."""
+        lo = [None] * len(TENSOR_CLASSES)
+        hi = [0] * len(TENSOR_CLASSES)
+        for t in self.tensors:
+            if t.tclass >= len(TENSOR_CLASSES) or t.nbytes == 0:
+                continue
+            lo[t.tclass] = t.offset if lo[t.tclass] is None else min(lo[t.tclass], t.offset)
+            hi[t.tclass] = max(hi[t.tclass], t.offset + t.nbytes)
+        return {n: (hi[i] - lo[i] if lo[i] is not None else 0) for i, n in enumerate(TENSOR_CLASSES)}
 
     def __init__(self, path):
         self.path = str(path)

@@ -323,6 +323,20 @@ int build_plan_v1(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
 }
 
 // ------------------------------------------------------------------ plan files
+void plan_class_bytes(const Plan& p, uint64_t out[TC_COUNT]) {
+    uint64_t lo[TC_COUNT], hi[TC_COUNT];
+    for (int c = 0; c < TC_COUNT; ++c) {
+        lo[c] = ~0ull;
+        hi[c] = 0;
+    }
+    for (const TensorDesc& t : p.tensors) {
+        if (t.tclass >= TC_COUNT || t.nbytes == 0) continue;
+        lo[t.tclass] = std::min(lo[t.tclass], t.offset);
+        hi[t.tclass] = std::max(hi[t.tclass], t.offset + t.nbytes);
+    }
+    for (int c = 0; c < TC_COUNT; ++c) out[c] = hi[c] > lo[c] ? hi[c] - lo[c] : 0;
+}
+
 int plan_write(const std::string& path, const Plan& p) {
     if (p.hdr.magic != kPlanMagic) return ERR_INVALID;
     const std::string tmp = path + ".tmp";

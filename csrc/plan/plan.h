@@ -107,6 +107,10 @@ int build_plan_v1(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
 // Version-2 plan: an executable schedule with real tensors and kernel records.
 int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph, uint64_t th, Plan* out,
                   std::string* err);
+// Bytes every tensor class occupies in a plan's arena (extent from the lowest offset to the highest end of the class's
+// tensors, so views and reused workspace count once): what a device really allocates, next to the model the
+// decomposition report prints (the reference's formula, which e.g. counts gradients at the parameter width).
+void plan_class_bytes(const Plan& p, uint64_t out[TC_COUNT]);
 int plan_write(const std::string& path, const Plan& p);
 int plan_read(const std::string& path, Plan* p);
 void plan_arena_breakdown(const Plan& p, uint64_t out_bytes[TC_COUNT]);

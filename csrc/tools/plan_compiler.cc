@@ -113,6 +113,14 @@ int main(int argc, char** argv) {
         }
         std::printf("  wrote %s  (stage %u, ops=%u, arena=%.2f GiB)\n", path.c_str(), p.hdr.pipeline_stage, p.hdr.num_ops,
                     p.hdr.arena_bytes / (1024.0 * 1024.0 * 1024.0));
+        if (exec) {
+            // what this rank's device allocates, class by class (the report above is the reference's memory model)
+            uint64_t cb[TC_COUNT];
+            plan_class_bytes(p, cb);
+            std::printf("    arena by class:");
+            for (int c = 0; c < TC_COUNT; ++c) std::printf(" %s=%.2f GiB", tclass_name(static_cast<uint16_t>(c)), cb[c] / (1024.0 * 1024.0 * 1024.0));
+            std::printf("\n");
+        }
     }
     return failed ? 1 : 0;
 }

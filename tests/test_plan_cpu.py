@@ -267,3 +267,19 @@ def test_backend_selection_at_cai_init(tmp_path):
     assert r.returncode == 1 and "device backend unavailable" in r.stderr
     r = run(BIN / "trainer", pl, tp, "--steps", "2", "--backend", "auto")
     assert "backend=analytic" in r.stderr and "falling back" in r.stderr and "summary: 2 steps" in r.stdout
+
+
+def test_arena_by_class_describes_what_a_device_allocates(tmp_path):
+    """The executable plan's per-class extents add up to its arena, and under ZeRO-3 the gradient class is the owned
+    shard plus two layer-sized stages, not the whole flat space (reference memory model: src/model.c:247-267)."""
+    from cai_b200 import plan
+    r = run(BIN / "plan_compiler", ROOT / "configs" / "b200_fsdp8b.cfg", tmp_path, "--exec", "--rank", "0")
+    assert "arena by class:" in r.stdout
+    pf = plan.PlanFile(tmp_path / "plan.rank000000.bin")
+    cb = pf.class_bytes()
+    total = sum(cb.values())
+    assert 0.98 * pf.hdr.arena_bytes <= total <= pf.hdr.arena_bytes
+    d = plan.describe((ROOT / "configs" / "b200_fsdp8b.cfg").read_text())
+    flat_grad_bytes = 4 * d["total_params"]
+    assert cb["grad"] < 0.3 * flat_grad_bytes          # dp = 8: a shard, two layer stages, the resident group
+    assert abs(cb["optstate"] - d["mem_opt"]) <= 0.02 * d["mem_opt"]   # master + m + v of the shard, as modelled
