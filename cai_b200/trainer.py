@@ -155,8 +155,14 @@ def main(argv=None):
     stream_line = None
     try:
         for step in range(first, a.steps):
+            straggler = None
             if hb is not None:
-                hb.check(step, timeout=a.peer_timeout)      # raises RankFailure naming the silent ranks
+                # raises RankFailure naming the silent ranks; a peer that keeps everyone waiting for a large share
+                # of a step is reported as a straggler
+                waited, last_rank = hb.check(step, timeout=a.peer_timeout)
+                if n and waited > max(0.25 * (h.global_tokens_per_step * n / sum_tps), 0.05):
+                    straggler = {"rank": last_rank, "waited_s": waited}
+                    print(f"rank {rank}: waited {waited * 1e3:.0f} ms for rank {last_rank} before step {step}", file=sys.stderr)
             tok, tgt = synthetic_batch(m.vocab_size, m.seq_len, rows * h.dp, step=step, seed=eng.train.seed)
             tok = tok[dp_id * rows:(dp_id + 1) * rows].contiguous().pin_memory()
             tgt = tgt[dp_id * rows:(dp_id + 1) * rows].contiguous().pin_memory()
@@ -202,6 +208,8 @@ def main(argv=None):
                            "bubble_formula": bubble}
                     if peak_measured:
                         rec["mfu_vs_measured_peak"] = eng.mfu(dt, peak_measured)
+                    if straggler:
+                        rec["straggler"] = straggler
                     if traced:
                         rec["stream_busy_ms"] = {planlib.STREAMS[i]: busy[i] * 1e3 for i in range(6)}
                         rec["bubble_measured"] = idle

@@ -36,13 +36,22 @@ class Heartbeat:
             return -1
 
     def check(self, step: int, timeout: float = 5.0, poll: float = 0.02):
-        """Block until every rank has published ``>= step`` or raise RankFailure after ``timeout``."""
-        deadline = time.monotonic() + timeout
+        """Block until every rank has published ``>= step`` or raise RankFailure after ``timeout``.
+
+        Returns ``(waited_s, last_rank)``: how long this rank stood at the check and which peer arrived last (a
+        straggler shows up here as a repeated ``last_rank`` with a wait that is a large share of the step time)."""
+        t0 = time.monotonic()
+        deadline = t0 + timeout
         missing = set(range(self.world))
+        last_rank = self.rank
         while True:
-            missing = {r for r in missing if self.progress(r) < step}
+            still = {r for r in missing if self.progress(r) < step}
+            others = (missing - still) - {self.rank}
+            if others:
+                last_rank = max(others)     # later batches of arrivals overwrite earlier ones
+            missing = still
             if not missing:
-                return
+                return time.monotonic() - t0, last_rank
             if time.monotonic() > deadline:
                 raise RankFailure(missing, step)
             time.sleep(poll)

@@ -52,6 +52,72 @@ def test_heartbeat_names_the_rank_that_left():
         assert by_rank[r][1] == "failure" and by_rank[r][2] == [1] and by_rank[r][3] == 3
 
 
+def _straggler_main(rank, world, port, q):
+    from torch.distributed import TCPStore
+    from cai_b200.utils.health import Heartbeat
+    store = TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=timedelta(seconds=20))
+    hb = Heartbeat(store, rank, world)
+    worst = (0.0, -1)
+    for step in range(1, 5):
+        if rank == 2 and step == 3:
+            time.sleep(0.5)                 # a slow rank: late, but inside the deadline
+        hb.beat(step)
+        waited, last = hb.check(step, timeout=5.0)
+        if step > 1 and waited > worst[0]:  # step 1 absorbs the processes' different start-up times
+            worst = (waited, last)
+    q.put((rank, worst))
+    time.sleep(0.5)
+
+
+def test_heartbeat_reports_the_rank_everyone_waited_for():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_straggler_main, args=(r, 3, 29873, q)) for r in range(3)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=60)
+    got = dict(q.get(timeout=5) for _ in range(3))
+    for r in (0, 1):
+        waited, last = got[r]
+        assert waited > 0.3 and last == 2, got
+    assert got[2][0] < 0.3
+
+
+def _collective_main(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=timedelta(seconds=3))
+    x = torch.ones(4)
+    dist.all_reduce(x)                      # step 1: everyone takes part
+    if rank == 1:
+        q.put((rank, "left"))               # leaves between steps, nothing of its own in flight
+        time.sleep(6.0)
+        return
+    t0 = time.monotonic()
+    try:
+        dist.all_reduce(x)                  # step 2: rank 1 never joins
+        q.put((rank, "completed", time.monotonic() - t0))
+    except Exception as e:                  # the short process-group timeout ends the wait with an error
+        q.put((rank, "error", time.monotonic() - t0, type(e).__name__))
+
+
+def test_collective_with_a_missing_rank_ends_with_an_error_not_a_hang():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_collective_main, args=(r, 2, 29875, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict((g[0], g) for g in (q.get(timeout=60) for _ in range(2)))
+    for p in procs:
+        p.join(timeout=30)
+        if p.is_alive():
+            p.kill()
+    assert got[1][1] == "left"
+    assert got[0][1] == "error" and got[0][2] < 20.0, got
+
+
 def test_watchdog_fires_on_an_overrunning_step_only():
     from cai_b200.utils.health import Watchdog
     hits = []
