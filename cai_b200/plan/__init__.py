@@ -7,6 +7,7 @@ reference project (include/cai_plan.h, include/cai_topology.h).
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import (POINTER, Structure, c_char, c_char_p, c_double, c_float, c_int, c_int32, c_size_t, c_uint16,
                     c_uint32, c_uint64, c_void_p)
 from pathlib import Path
@@ -289,13 +290,24 @@ def read_topology(path) -> Topology:
     return Topology.from_buffer_copy(raw, 4)
 
 
-class Simulator:
-    """Analytic replay of a plan (the reference's ``trainer`` behaviour) through the C API."""
+BACKENDS = {"default": 0, "analytic": 1, "device": 2, "auto": 3, "calibrated": 4}
 
-    def __init__(self, plan_path, topology_path, rank=0, checkpoint_path=None, checkpoint_every=0, max_steps=0):
+
+class Simulator:
+    """Replay of a plan through the C API (the reference's ``trainer`` behaviour). ``backend``: "analytic" prices ops
+    from FLOPs and bytes over the datasheet figures (the reference's model), "calibrated" prices version-2 plans with
+    costs fitted to this repository's kernels as measured on B200s (``calibration``: optional key = value file that
+    overrides constants), "device" / "auto" execute on a GPU."""
+
+    def __init__(self, plan_path, topology_path, rank=0, checkpoint_path=None, checkpoint_every=0, max_steps=0,
+                 backend="default", calibration=None):
         self._keep = [str(plan_path).encode(), str(topology_path).encode(),
                       str(checkpoint_path).encode() if checkpoint_path else None]
-        d = InitDesc(rank, 0, 0, self._keep[0], self._keep[1], self._keep[2], checkpoint_every, max_steps)
+        if calibration is not None:
+            os.environ["CAI_CALIBRATION"] = str(calibration)
+        elif backend == "calibrated":
+            os.environ.pop("CAI_CALIBRATION", None)
+        d = InitDesc(rank, 0, 0, self._keep[0], self._keep[1], self._keep[2], checkpoint_every, max_steps, BACKENDS[backend])
         self.ctx = c_void_p()
         rc = lib().cai_init(ctypes.byref(self.ctx), ctypes.byref(d))
         if rc != 0:

@@ -1,9 +1,10 @@
 // backend.h - what the runtime asks of a backend.
 //
 // The runtime (runtime_sim.cc) owns the plan, the step counter, statistics, tracing and checkpoint
-// files; a backend turns one step of the op table into times. Two exist:
+// files; a backend turns one step of the op table into times. Three exist:
 //   * analytic: prices every op from its FLOPs / bytes and the topology's datasheet figures; the
 //     runtime walks the op table over six stream clocks (no GPU);
+//   * calibrated: prices every op with costs fitted to this repository's kernels as measured on B200s (no GPU);
 //   * device: hands the whole table to the executor in libcai_kernels.so, which launches the real
 //     kernels on six CUDA streams, and reports measured times and the loss.
 // Same role as the reference's `struct cai_backend {name, impl, op_seconds, sync, destroy}`
@@ -33,6 +34,9 @@ struct Backend {
     void* impl;
     // Pricing backends: modelled seconds `op` occupies its stream (`g` = its communicator or null).
     double (*op_seconds)(Backend* be, const Topology& topo, const Op& op, const CommGroup* g);
+    // Optional for pricing backends: the share of the GPU's SMs the op keeps busy while it runs (0..1). When given,
+    // the replayer does not let a step be shorter than the sum of duration x share over all streams.
+    double (*op_sm_share)(Backend* be, const Topology& topo, const Op& op, const CommGroup* g) = nullptr;
     // Executing backends: bind a plan (file bytes; the plan is parsed again by the executor) ...
     int (*load_plan)(Backend* be, const Plan& plan, const std::string& path, uint32_t rank, uint32_t world);
     // ... and run one optimizer step of it on a synthetic batch drawn from `seed`.
@@ -45,6 +49,9 @@ struct Backend {
 };
 
 Backend* backend_analytic_create();
+// Costs fitted to measurements on B200s (backend_calibrated.cc); `calibration_path` (may be null) overrides constants
+// from a key = value file. nullptr (with the reason in *why) when that file cannot be read or names an unknown key.
+Backend* backend_calibrated_create(const char* calibration_path, std::string* why);
 // nullptr (with the reason in *why) when the kernel library or a CUDA device is missing.
 Backend* backend_device_create(uint32_t local_rank, std::string* why);
 

@@ -30,15 +30,17 @@ typedef struct {
     uint32_t checkpoint_every;   /* steps; 0 disables */
     uint32_t max_steps;          /* 0: run until the caller stops */
     uint32_t backend;            /* CAI_BACKEND_*: which backend replays the plan (the CAI_BACKEND environment
-                                  * variable, "analytic" / "device" / "auto", overrides CAI_BACKEND_DEFAULT) */
+                                  * variable, "analytic" / "calibrated" / "device" / "auto", overrides CAI_BACKEND_DEFAULT) */
 } cai_init_desc_t;
 
 enum {
     CAI_BACKEND_DEFAULT = 0,  /* analytic unless the environment says otherwise */
     CAI_BACKEND_ANALYTIC = 1, /* cost model, no GPU: predicts step time, bubble, MFU */
     CAI_BACKEND_DEVICE = 2,   /* execute the plan on the GPU of local_rank (needs a version-2 plan); fail if impossible */
-    CAI_BACKEND_AUTO = 3      /* device when a GPU and the kernel library are there, else analytic (the reference's order,
+    CAI_BACKEND_AUTO = 3,     /* device when a GPU and the kernel library are there, else analytic (the reference's order,
                                * src/runtime.c:32-73) */
+    CAI_BACKEND_CALIBRATED = 4 /* cost model fitted to this repository's kernels as measured on B200s, no GPU (needs a
+                                * version-2 plan; constants can be overridden from the file named by CAI_CALIBRATION) */
 };
 
 typedef struct {

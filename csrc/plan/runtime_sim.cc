@@ -120,7 +120,16 @@ int cai_init(cai_context_t** out, const cai_init_desc_t* desc) {
     if (want == CAI_BACKEND_DEFAULT) {
         const char* env = std::getenv("CAI_BACKEND");
         want = !env ? CAI_BACKEND_ANALYTIC : !std::strcmp(env, "device") ? CAI_BACKEND_DEVICE
-             : !std::strcmp(env, "auto") ? CAI_BACKEND_AUTO : CAI_BACKEND_ANALYTIC;
+             : !std::strcmp(env, "auto") ? CAI_BACKEND_AUTO : !std::strcmp(env, "calibrated") ? CAI_BACKEND_CALIBRATED
+             : CAI_BACKEND_ANALYTIC;
+    }
+    if (want == CAI_BACKEND_CALIBRATED) {
+        std::string why;
+        ctx->be = backend_calibrated_create(std::getenv("CAI_CALIBRATION"), &why);
+        if (!ctx->be) {
+            logf(LOG_ERROR, "calibrated backend: %s", why.c_str());
+            return ERR_BACKEND;
+        }
     }
     if (want == CAI_BACKEND_DEVICE || want == CAI_BACKEND_AUTO) {
         std::string why;
@@ -230,6 +239,7 @@ int cai_train_step(cai_context_t* ctx, const cai_batch_t* batch) {
         return OK;
     }
     double clock[ST_COUNT] = {0}, work[ST_COUNT] = {0};
+    double sm_work = 0.0;  // sum of duration x share of the SMs, over all streams (backends that know the share)
     std::fill(ctx->event_time.begin(), ctx->event_time.end(), 0.0);
     ctx->trace.clear();
     if (ctx->trace_on) ctx->trace.reserve(p.ops.size());
@@ -255,6 +265,7 @@ int cai_train_step(cai_context_t* ctx, const cai_batch_t* batch) {
             if (!g && op_is_comm(op.kind)) return ERR_PLAN;
         }
         const double dur = ctx->be->op_seconds(ctx->be, ctx->topo, op, g);
+        if (ctx->be->op_sm_share) sm_work += dur * ctx->be->op_sm_share(ctx->be, ctx->topo, op, g);
         const double start = clock[st];
         clock[st] = start + dur;
         work[st] += dur;
@@ -263,6 +274,7 @@ int cai_train_step(cai_context_t* ctx, const cai_batch_t* batch) {
 
     double busy = 0.0;
     for (double c : clock) busy = std::max(busy, c);
+    busy = std::max(busy, sm_work);  // streams overlap only as far as their kernels leave SMs to each other
     const double bubble = pipeline_bubble_interleaved(p.hdr.num_stages, p.hdr.num_microbatches, p.hdr.vpp ? p.hdr.vpp : 1);
     const double step_time = bubble < 1.0 ? busy / (1.0 - bubble) : busy;
     const double useful_per_gpu = static_cast<double>(p.hdr.global_tokens_per_step) *

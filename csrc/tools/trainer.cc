@@ -15,7 +15,7 @@
 
 int main(int argc, char** argv) {
     if (argc < 3) {
-        std::fprintf(stderr, "usage: %s <plan.bin> <topology.bin> [--steps N] [--ckpt PATH] [--ckpt-every K] [--trace CSV] [--fail-at STEP] [--device | --backend analytic|device|auto]\n", argv[0]);
+        std::fprintf(stderr, "usage: %s <plan.bin> <topology.bin> [--steps N] [--ckpt PATH] [--ckpt-every K] [--trace CSV] [--fail-at STEP] [--device | --backend analytic|calibrated|device|auto] [--calibration FILE]\n", argv[0]);
         return 2;
     }
     cai_init_desc_t desc;
@@ -36,7 +36,12 @@ int main(int argc, char** argv) {
         else if (!std::strcmp(argv[i], "--device")) desc.backend = CAI_BACKEND_DEVICE;
         else if (!std::strcmp(argv[i], "--backend") && i + 1 < argc) {
             const char* b = argv[++i];
-            desc.backend = !std::strcmp(b, "device") ? CAI_BACKEND_DEVICE : !std::strcmp(b, "auto") ? CAI_BACKEND_AUTO : CAI_BACKEND_ANALYTIC;
+            desc.backend = !std::strcmp(b, "device") ? CAI_BACKEND_DEVICE : !std::strcmp(b, "auto") ? CAI_BACKEND_AUTO
+                         : !std::strcmp(b, "calibrated") ? CAI_BACKEND_CALIBRATED : CAI_BACKEND_ANALYTIC;
+        }
+        else if (!std::strcmp(argv[i], "--calibration") && i + 1 < argc) {
+            setenv("CAI_CALIBRATION", argv[++i], 1);   // constants of the calibrated backend, key = value
+            if (desc.backend == CAI_BACKEND_DEFAULT) desc.backend = CAI_BACKEND_CALIBRATED;
         }
         else { std::fprintf(stderr, "unknown arg: %s\n", argv[i]); return 2; }
     }
