@@ -88,12 +88,6 @@ constexpr int kAttnBwdThreads = 128 + kAttnComputeThreads;  // warp 0 TMA, warp 
 
 __device__ __forceinline__ void bar_sync_compute() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 
-__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)[8]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
-                 "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                 : "memory");
-}
-
 // One 32-column chunk of a finished fp32 accumulator, times `mul`, to bf16 rows (stored, or added to what is there).
 template <bool kAdd>
 __device__ __forceinline__ void put_acc_chunk(uint32_t tacc, __nv_bfloat16* dst_row, int c, float mul) {
@@ -123,7 +117,7 @@ __device__ __forceinline__ void put_acc_chunk(uint32_t tacc, __nv_bfloat16* dst_
 // dK / dV work of one thread on 16 query columns: S^T / dP^T (dP^T `dp_off` columns behind S^T) -> P^T, dS^T
 // (unscaled) as bf16 over the first 8 of the 16 columns read.
 template <bool kDiag>
-__device__ __forceinline__ void dkdv_half_step(uint32_t tS, uint32_t dp_off, const float* L, const float* D,
+__device__ __forceinline__ void dkdv_pass16(uint32_t tS, uint32_t dp_off, const float* L, const float* D,
                                                float scale_log2, int r, int qb) {
     const uint32_t tdP = tS + dp_off;
     uint32_t sv[16], dp[16], pk[8], dk[8];
@@ -165,7 +159,7 @@ __device__ __forceinline__ void dkdv_half_step(uint32_t tS, uint32_t dp_off, con
 // dQ work of one thread on 16 key columns: S / dP (dP `dp_off` columns behind S) -> dS (unscaled) as bf16 over the
 // first 8 of the 16 dP columns read.
 template <bool kDiag>
-__device__ __forceinline__ void dq_half_step(uint32_t tS, uint32_t dp_off, float lse2, float dl, float scale_log2, int r,
+__device__ __forceinline__ void dq_pass16(uint32_t tS, uint32_t dp_off, float lse2, float dl, float scale_log2, int r,
                                              int kb) {
     const uint32_t tdP = tS + dp_off;
     uint32_t sv[16], dp[16], dk[8];
@@ -334,8 +328,8 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
             for (int cc = 0; cc < 2; ++cc) {
                 const int qb = grp * 32 + cc * 16;  // first query column of this pass
                 const uint32_t t = tS + lane_bits + qb;
-                if (i == j) dkdv_half_step<true>(t, 128, sL + buf * 128 + qb, sD + buf * 128 + qb, p.scale_log2, r, qb);
-                else dkdv_half_step<false>(t, 128, sL + buf * 128 + qb, sD + buf * 128 + qb, p.scale_log2, r, qb);
+                if (i == j) dkdv_pass16<true>(t, 128, sL + buf * 128 + qb, sD + buf * 128 + qb, p.scale_log2, r, qb);
+                else dkdv_pass16<false>(t, 128, sL + buf * 128 + qb, sD + buf * 128 + qb, p.scale_log2, r, qb);
             }
             tc_fence_before();
             mbar_arrive_warp(pds_ready);
@@ -509,8 +503,8 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
             for (int cc = 0; cc < 2; ++cc) {
                 const int kb = grp * 32 + cc * 16;  // first key column of this pass
                 const uint32_t t = tS + lane_bits + kb;
-                if (j == i) dq_half_step<true>(t, 128, lse2, dl, p.scale_log2, r, kb);
-                else dq_half_step<false>(t, 128, lse2, dl, p.scale_log2, r, kb);
+                if (j == i) dq_pass16<true>(t, 128, lse2, dl, p.scale_log2, r, kb);
+                else dq_pass16<false>(t, 128, lse2, dl, p.scale_log2, r, kb);
             }
             tc_fence_before();
             mbar_arrive_warp(ds_ready);
