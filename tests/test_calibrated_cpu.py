@@ -87,3 +87,20 @@ def test_version_1_plans_fall_back_to_the_analytic_cost(tmp_path):
         out.append(sim.step().step_time_s)
         sim.close()
     assert out[1] >= out[0] * 0.999   # never below the analytic figure (the SM-work bound can only add)
+
+
+def test_layout_advisor_ranks_executable_layouts(tmp_path):
+    """`python -m cai_b200.plan.advise`: every layout of the headline model on 8 GPUs that keeps the global batch is
+    priced; the benchmark's own layout (tp = 8) is among them with the step time the backend predicts for it."""
+    from cai_b200.plan import advise
+    ok, refused = advise.advise(ROOT / "configs" / "b200_tp8.cfg", gpus=8)
+    assert not refused
+    layouts = {(r["tp"], r["pp"], r["dp"], r["zero_stage"]) for r in ok}
+    assert {(8, 1, 1, 1), (1, 1, 8, 1), (1, 1, 8, 3), (4, 2, 1, 1), (2, 2, 2, 1)} <= layouts
+    assert all(r["grad_accum"] * r["dp"] == 8 for r in ok)            # global batch kept
+    assert [r["step_ms"] for r in ok] == sorted(r["step_ms"] for r in ok) and all(r["fits"] for r in ok)
+    tp8 = next(r for r in ok if (r["tp"], r["pp"]) == (8, 1))
+    assert abs(tp8["step_ms"] - MEASURED_MS[8]) <= 0.10 * MEASURED_MS[8]
+    r = subprocess.run([sys.executable, "-m", "cai_b200.plan.advise", str(ROOT / "configs" / "b200_moe_ep8.cfg"), "--gpus", "8"],
+                       capture_output=True, text=True, cwd=ROOT)
+    assert r.returncode == 0 and "tokens/s" in r.stdout
