@@ -9,10 +9,9 @@ parameter initialisation, batches and checkpoints.
 from __future__ import annotations
 
 import ctypes
-import math
 import os
 import tempfile
-from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_ulonglong, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_size_t, c_ulonglong, c_void_p
 from pathlib import Path
 
 import torch

@@ -5,7 +5,6 @@ device status word, and the context must stay usable for ordinary kernels.
 
 The "second member" is just a second buffer on the same GPU: the kernel's peer stores land there and
 nothing ever raises the flags it waits for. No kernel spins without a limit, nothing traps."""
-import ctypes
 import time
 from ctypes import c_int, c_longlong, c_uint32, c_ulonglong, c_void_p
 

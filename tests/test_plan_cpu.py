@@ -1,5 +1,4 @@
 """GPU-free tests of the offline compiler, verifier, analytic runtime and tools."""
-import ctypes
 import os
 import subprocess
 from pathlib import Path

@@ -1,5 +1,4 @@
 """Bandwidth-bound kernels against plain PyTorch fp32 references."""
-import math
 
 import pytest
 import torch

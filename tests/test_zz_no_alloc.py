@@ -8,7 +8,6 @@ between calls and keeps old contents, so the second call must not be disturbed b
 checks that sizes beyond the fixed maximum are refused. It sits last in collection order so that
 a failure here cannot hide other results in a run that stops at the first failure.
 """
-import ctypes
 from ctypes import c_int, c_void_p
 
 import pytest
