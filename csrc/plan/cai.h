@@ -89,7 +89,7 @@ int cai_trace_enable(cai_context_t* ctx, int on);
 int cai_trace_dump_csv(cai_context_t* ctx, const char* path);
 int cai_finalize(cai_context_t* ctx);
 uint32_t cai_current_step(cai_context_t* ctx);
-const char* cai_backend_name(cai_context_t* ctx);   /* "analytic" or "device" */
+const char* cai_backend_name(cai_context_t* ctx);   /* "analytic", "calibrated" or "device" */
 
 /* ---- compiler entry points (used by the Python package through ctypes) ---------------- */
 

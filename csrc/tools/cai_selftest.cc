@@ -6,6 +6,7 @@
 // pairing, checkpoint files, golden hashes of the bundled configs).
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <set>
 
@@ -394,6 +395,54 @@ static void test_checkpoint_files() {
     if (f) std::fclose(f);
 }
 
+// The calibrated pricing backend through the public C API: a version-2 plan replayed with measured kernel costs takes
+// longer than with the datasheet model, streams overlap only as far as the SMs allow, and a calibration file with an
+// unknown key is refused at cai_init.
+static void test_calibrated_backend() {
+    Config c;
+    std::string err;
+    if (config_load("configs/b200_tp8.cfg", &c, &err) != OK) { CHECK(false, "%s", err.c_str()); return; }
+    topology_finalize(&c.topo, &err);
+    Decomp d;
+    CHECK(decompose(c, &d, &err) == OK, "%s", err.c_str());
+    Plan p;
+    CHECK(build_plan_v2(c, d, 0, plan_hash(c, d), topology_hash(c.topo), &p, &err) == OK, "%s", err.c_str());
+    CHECK(plan_write("/tmp/cai_selftest_cal.bin", p) == OK && topology_write("/tmp/cai_selftest_cal_topo.bin", c.topo) == OK, "write");
+    double t[2] = {0, 0};
+    for (int k = 0; k < 2; ++k) {
+        cai_init_desc_t desc{};
+        desc.plan_path = "/tmp/cai_selftest_cal.bin";
+        desc.topology_path = "/tmp/cai_selftest_cal_topo.bin";
+        desc.backend = k ? CAI_BACKEND_CALIBRATED : CAI_BACKEND_ANALYTIC;
+        unsetenv("CAI_CALIBRATION");
+        cai_context_t* ctx = nullptr;
+        CHECK(cai_init(&ctx, &desc) == 0, "cai_init backend %d", k);
+        if (!ctx) return;
+        CHECK(!std::strcmp(cai_backend_name(ctx), k ? "calibrated" : "analytic"), "backend name");
+        CHECK(cai_train_step(ctx, nullptr) == 0, "step");
+        cai_step_stats_t st;
+        cai_last_step_stats(ctx, &st);
+        t[k] = st.step_time_s;
+        if (k) CHECK(st.step_time_s >= st.stream_busy[ST_COMPUTE_HI] * 0.9999 &&
+                     st.step_time_s <= (st.stream_busy[ST_COMPUTE_HI] + st.stream_busy[ST_COMPUTE_LO]) * 1.0001, "SM-work bound");
+        cai_finalize(ctx);
+    }
+    CHECK(t[1] > 2.0 * t[0] && t[1] > 0.08 && t[1] < 0.13, "calibrated %.4f s against analytic %.4f s (measured: 0.108 s)", t[1], t[0]);
+    FILE* f = std::fopen("/tmp/cai_selftest_cal_bad.cfg", "w");
+    if (f) {
+        std::fputs("no_such_constant = 1\n", f);
+        std::fclose(f);
+    }
+    setenv("CAI_CALIBRATION", "/tmp/cai_selftest_cal_bad.cfg", 1);
+    cai_init_desc_t desc{};
+    desc.plan_path = "/tmp/cai_selftest_cal.bin";
+    desc.topology_path = "/tmp/cai_selftest_cal_topo.bin";
+    desc.backend = CAI_BACKEND_CALIBRATED;
+    cai_context_t* ctx = nullptr;
+    CHECK(cai_init(&ctx, &desc) != 0, "unknown calibration key accepted");
+    unsetenv("CAI_CALIBRATION");
+}
+
 int main() {
     log_set_level(LOG_ERROR);
     test_topology();
@@ -407,6 +456,7 @@ int main() {
     test_config_parser();
     test_exec_plans();
     test_checkpoint_files();
+    test_calibrated_backend();
     std::printf("%d checks, %d failures\n", g_checks, g_fail);
     return g_fail ? 1 : 0;
 }
