@@ -34,6 +34,7 @@ KERNEL_NAMES = ["none", "embed_fwd", "embed_bwd", "rmsnorm_fwd", "rmsnorm_bwd", 
                 "fsdp_ag_gemm", "moe_route", "moe_dispatch_gemm", "moe_gemm_combine", "load_tokens", "add",
                 "cross_entropy_tp", "quant_fp8", "gemm_fp8"]
 K_GEMM, K_GEMM_RS, K_AG_GEMM, K_RS_ADAMW, K_FSDP_AG_GEMM, K_QUANT_FP8, K_GEMM_FP8 = 5, 20, 21, 22, 23, 30, 31
+K_MOE_ROUTE, K_MOE_DISPATCH_GEMM, K_MOE_GEMM_COMBINE = 24, 25, 26
 OP_EVENT_RECORD, OP_EVENT_WAIT = 13, 14
 
 

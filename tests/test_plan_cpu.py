@@ -282,3 +282,25 @@ def test_arena_by_class_describes_what_a_device_allocates(tmp_path):
     flat_grad_bytes = 4 * d["total_params"]
     assert cb["grad"] < 0.3 * flat_grad_bytes          # dp = 8: a shard, two layer stages, the resident group
     assert abs(cb["optstate"] - d["mem_opt"]) <= 0.02 * d["mem_opt"]   # master + m + v of the shard, as modelled
+
+
+@pytest.mark.parametrize("world,keys", [(2, "tp = 2"), (2, "pp = 2"), (4, "tp = 2\nep = 2"), (4, "pp = 2\nep = 2"),
+                                        (8, "tp = 2\npp = 2\nep = 2"), (8, "ep = 8")])
+def test_moe_layouts_compile_and_verify(tmp_path, world, keys):
+    """Mixture-of-experts plans beside tensor and pipeline parallelism (what configs/full220k_moe.cfg mixes; reference
+    emission: src/model.c:463-475,584-591): every rank compiles, the cluster verifier finds no unordered access, and
+    the experts are spread over the tp x ep ranks of a stage."""
+    from cai_b200 import plan
+    text = (ROOT / "configs" / "tiny_moe_tp.cfg").read_text()
+    text += f"\ngpus_per_rack = {world}\ngpus_per_tray = {world}\ncomm = fused\n{keys}\n"
+    cfg = tmp_path / "moe.cfg"
+    cfg.write_text(text)
+    plan.compile_plans(cfg, tmp_path / "out", version=2)
+    problems, report = plan.verify(cfg)
+    assert problems == 0, report[-2000:]
+    d = plan.describe(text)
+    pf = plan.PlanFile(tmp_path / "out" / "plan.rank000000.bin")
+    kinds = {int(x.kernel) for x in pf.exec}
+    assert {plan.K_MOE_ROUTE, plan.K_MOE_DISPATCH_GEMM, plan.K_MOE_GEMM_COMBINE} <= kinds
+    if d["tp"] > 1:
+        assert {plan.K_AG_GEMM, plan.K_GEMM_RS} <= kinds     # attention stays tensor parallel around the experts
