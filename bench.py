@@ -337,7 +337,7 @@ def run_reference(args):
     sampler = ClockSampler(os.path.join(tempfile.gettempdir(), f"cai_ref_clocks_n{world}_{os.getpid()}.csv")) if rank == 0 else None
     if sampler:
         sampler.start()
-    lines, rc, err = _run_gpu_trainer(exe, W + K, timeout_s=600)
+    lines, rc, err = _run_gpu_trainer(exe, W + K, timeout_s=180)   # a run takes seconds; a hung NCCL bootstrap must not hold the job
     clocks = sampler.stop(gpu_index=int(os.environ.get("LOCAL_RANK", 0))) if sampler else None
     ok = rc == 0 and len(lines) >= 2
     # steps are printed every max(1, (W+K)//20) steps: the timed span starts at the first line at or past the
