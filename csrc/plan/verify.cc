@@ -293,6 +293,108 @@ void verify_pipeline_pairing(const std::vector<Plan>& stages, VerifyReport* rep)
         add(rep, true, "pipeline sends and receives pair up in issue order across %zu stages", stages.size());
 }
 
+// Cross-rank reuse of the slabs of the expert exchange. The dispatch kernel stores rows into the slabs of the other
+// members from its first instruction on and returns only after every member has issued all of its stores (exit
+// hand-shake); the combine kernel with the announce flag starts only after every member has reached it (entry
+// hand-shake) and then loads rows out of the other members' slabs. Both therefore order the expert group: "every
+// member has finished what precedes the op on its stream" holds for everything after it. Every member replays the same
+// sequence, so one rank's plan stands for the group. Checked here (the step is cyclic):
+//   * a slab peers push into (dispatch) is not touched locally between the last group-ordering op and that dispatch:
+//     a member that is ahead may already be storing into it;
+//   * a slab peers pull from (combine) is next overwritten locally only after a group-ordering op that follows the
+//     combine: a member that is behind may still be loading from it;
+//   * a combine without the announce flag reads slabs whose last local write lies before a group-ordering op.
+static void verify_expert_exchange_reuse(const Plan& p, VerifyReport* rep) {
+    struct Item { uint32_t op; const ExecOp* x; bool orders; };
+    std::vector<Item> seq;
+    bool any = false;
+    for (uint32_t i = 0; i < p.ops.size(); ++i) {
+        const Op& op = p.ops[i];
+        if (!op.exec || op.exec > p.exec.size()) continue;
+        const ExecOp& x = p.exec[op.exec - 1];
+        const bool dispatch = x.kernel == K_MOE_DISPATCH_GEMM, combine = x.kernel == K_MOE_GEMM_COMBINE;
+        any = any || dispatch || combine;
+        seq.push_back({i, &x, dispatch || (combine && (x.flags & 1))});
+    }
+    if (!any) return;
+    auto overlap = [&](int a, int b) {
+        if (a < 0 || b < 0) return false;
+        const TensorDesc& ta = p.tensors[a];
+        const TensorDesc& tb = p.tensors[b];
+        return ta.nbytes && tb.nbytes && ta.offset < tb.offset + tb.nbytes && tb.offset < ta.offset + ta.nbytes;
+    };
+    const size_t n = seq.size();
+    size_t checks = 0;
+    int problems = 0;
+    std::vector<int> reads, writes;
+    auto touches = [&](const ExecOp& x, int buf, bool writes_only) {
+        exec_operands(x, &reads, &writes);
+        for (int w : writes)
+            if (overlap(w, buf)) return true;
+        if (!writes_only)
+            for (int r : reads)
+                if (overlap(r, buf)) return true;
+        return false;
+    };
+    for (size_t a = 0; a < n; ++a) {
+        const ExecOp& xa = *seq[a].x;
+        if (xa.kernel == K_MOE_DISPATCH_GEMM) {
+            // backwards from the dispatch: local accesses of the slab must lie before an ordering op
+            for (int buf : {xa.t[5], xa.t[6]}) {
+                if (buf < 0) continue;
+                for (size_t k = 1; k < n; ++k) {
+                    const Item& it = seq[(a + n - k) % n];
+                    if (it.orders) break;
+                    if (touches(*it.x, buf, false)) {
+                        ++problems;
+                        add(rep, false, "rank %u: op %u touches a slab that the peers of dispatch op %u may already be storing into",
+                            p.hdr.global_rank, it.op, seq[a].op);
+                        break;
+                    }
+                }
+                ++checks;
+            }
+        } else if (xa.kernel == K_MOE_GEMM_COMBINE && xa.t[5] >= 0) {
+            const int buf = xa.t[5];
+            // forwards: the next local write of the slab comes after an ordering op
+            bool ordered = false;
+            for (size_t k = 1; k < n; ++k) {
+                const Item& it = seq[(a + k) % n];
+                if (it.x->kernel != K_MOE_GEMM_COMBINE && it.x->kernel != K_MOE_DISPATCH_GEMM && touches(*it.x, buf, true)) {
+                    if (!ordered) {
+                        ++problems;
+                        add(rep, false, "rank %u: op %u overwrites a slab that the peers of combine op %u may still be loading from",
+                            p.hdr.global_rank, it.op, seq[a].op);
+                    }
+                    break;
+                }
+                if (it.orders) ordered = true;
+            }
+            ++checks;
+            // backwards, for a combine that does not announce: the slab's last local write lies before an ordering op
+            if (!(xa.flags & 1)) {
+                bool ord = false;
+                for (size_t k = 1; k < n; ++k) {
+                    const Item& it = seq[(a + n - k) % n];
+                    if (it.x->kernel != K_MOE_GEMM_COMBINE && it.x->kernel != K_MOE_DISPATCH_GEMM && touches(*it.x, buf, true)) {
+                        if (!ord) {
+                            ++problems;
+                            add(rep, false, "rank %u: combine op %u loads from the peers' slabs without a hand-shake after their last write (op %u here)",
+                                p.hdr.global_rank, seq[a].op, it.op);
+                        }
+                        break;
+                    }
+                    if (it.orders) ord = true;
+                }
+                ++checks;
+            }
+        }
+    }
+    if (!problems && checks)
+        add(rep, true, "rank %u: slabs of the expert exchange are reused only across a group-ordering op (%zu checks)",
+            p.hdr.global_rank, checks);
+}
+
 // Cross-rank reuse of the buffers the fused tensor-parallel kernels share between GPUs. Every member of the group
 // replays the same op sequence, so one rank's plan stands for all of them. Two facts about the kernels make a
 // group-wide ordering: an all-gather -> GEMM returns only after every member has entered the same op (it needs their
@@ -361,6 +463,7 @@ void verify_peer_reuse(const Plan& p, VerifyReport* rep) {
     if (!problems && checks)
         add(rep, true, "rank %u: peer-visible buffers of the fused TP kernels are reused only across a group-ordering op (%zu checks)",
             p.hdr.global_rank, checks);
+    verify_expert_exchange_reuse(p, rep);
 }
 
 // Pre-compile sanity checks of a configuration (what `topology_linter` prints): memory against the budget,

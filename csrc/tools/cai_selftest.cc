@@ -336,6 +336,29 @@ static void test_exec_plans() {
         CHECK(bad.problems > 0, "peer-reuse proof missed reduce-scatters that share a staging buffer without a group-ordering op");
     }
 
+    // Expert exchange: the ep = 8 plan passes; without the combine's entry hand-shake (announce flag cleared) a member
+    // would load expert outputs its peers may not have written yet, and the proof must say so.
+    {
+        Config cf;
+        config_load("configs/b200_moe_ep8.cfg", &cf, &err);
+        cf.train.comm_mode = 1;
+        topology_finalize(&cf.topo, &err);
+        Decomp df;
+        decompose(cf, &df, &err);
+        Plan pf;
+        CHECK(build_plan_v2(cf, df, 0, plan_hash(cf, df), topology_hash(cf.topo), &pf, &err) == OK, "moe ep8 plan: %s", err.c_str());
+        VerifyReport good;
+        verify_peer_reuse(pf, &good);
+        bool said = false;
+        for (const std::string& l : good.lines) said = said || l.find("slabs of the expert exchange") != std::string::npos;
+        CHECK(good.problems == 0 && said, "expert-exchange reuse of the ep8 plan: %d problems", good.problems);
+        for (ExecOp& x : pf.exec)
+            if (x.kernel == K_MOE_GEMM_COMBINE) x.flags &= static_cast<uint16_t>(~1u);
+        VerifyReport bad;
+        verify_peer_reuse(pf, &bad);
+        CHECK(bad.problems > 0, "expert-exchange proof missed combines that load from peers without a hand-shake");
+    }
+
     // Column views: two unordered writers on different streams are fine when they cover disjoint columns of
     // the same rows (dQ beside dK/dV), and a hazard as soon as the column intervals touch.
     for (int overlap = 0; overlap < 2; ++overlap) {
