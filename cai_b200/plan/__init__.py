@@ -145,7 +145,7 @@ def lib() -> ctypes.CDLL:
         L.cai_fnv1a64.argtypes = [c_void_p, c_size_t, c_uint64]
         L.cai_fnv1a64.restype = c_uint64
         L.cai_init.argtypes = [POINTER(c_void_p), POINTER(InitDesc)]
-        for fn in ("cai_load_plan", "cai_load_checkpoint", "cai_save_checkpoint", "cai_trace_dump_csv"):
+        for fn in ("cai_load_plan", "cai_load_checkpoint", "cai_save_checkpoint", "cai_trace_dump_csv", "cai_trace_dump_json"):
             getattr(L, fn).argtypes = [c_void_p, c_char_p]
         L.cai_next_batch.argtypes = [c_void_p, POINTER(Batch)]
         L.cai_train_step.argtypes = [c_void_p, POINTER(Batch)]
@@ -342,7 +342,9 @@ class Simulator:
         lib().cai_trace_enable(self.ctx, int(on))
 
     def dump_trace(self, path):
-        return lib().cai_trace_dump_csv(self.ctx, str(path).encode())
+        """CSV in the reference's schema, or (path ending in .json) the Trace Event format of chrome://tracing / Perfetto."""
+        fn = lib().cai_trace_dump_json if str(path).endswith(".json") else lib().cai_trace_dump_csv
+        return fn(self.ctx, str(path).encode())
 
     def close(self):
         if self.ctx:

@@ -50,7 +50,18 @@ def measured_peak_flops():
         return None
 
 
+def write_trace_json(path, recs, rank=0):
+    """The measured timeline in the Trace Event format (chrome://tracing, Perfetto): one track per logical stream."""
+    ev = [{"ph": "M", "pid": rank, "tid": s, "name": "thread_name", "args": {"name": planlib.STREAMS[s]}} for s in range(6)]
+    ev += [{"ph": "X", "pid": rank, "tid": r.stream, "name": planlib.OP_NAMES[r.kind], "ts": r.start_s * 1e6,
+            "dur": (r.end_s - r.start_s) * 1e6, "args": {"op": r.op_index, "bytes": r.bytes, "flops": r.flops}} for r in recs]
+    with open(path, "w") as f:
+        json.dump({"displayTimeUnit": "ms", "traceEvents": ev}, f)
+
+
 def write_trace_csv(path, recs):
+    if str(path).endswith(".json"):
+        return write_trace_json(path, recs)
     with open(path, "w") as f:
         f.write("op_index,kind,stream,start_us,end_us,dur_us,bytes,flops\n")
         for r in recs:
@@ -66,7 +77,7 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--ckpt")
     ap.add_argument("--ckpt-every", type=int, default=0)
-    ap.add_argument("--trace")
+    ap.add_argument("--trace", help="write the last step's measured op timeline: CSV (reference schema), or Trace Event JSON for chrome://tracing / Perfetto when the path ends in .json")
     ap.add_argument("--graph", action="store_true")
     ap.add_argument("--nvtx", action="store_true", help="NVTX range per op, named by kernel (for timeline tools)")
     ap.add_argument("--jsonl")

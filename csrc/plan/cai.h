@@ -87,6 +87,7 @@ int cai_save_checkpoint(cai_context_t* ctx, const char* tag);
 int cai_last_step_stats(cai_context_t* ctx, cai_step_stats_t* out);
 int cai_trace_enable(cai_context_t* ctx, int on);
 int cai_trace_dump_csv(cai_context_t* ctx, const char* path);
+int cai_trace_dump_json(cai_context_t* ctx, const char* path);   /* Trace Event format (chrome://tracing, Perfetto) */
 int cai_finalize(cai_context_t* ctx);
 uint32_t cai_current_step(cai_context_t* ctx);
 const char* cai_backend_name(cai_context_t* ctx);   /* "analytic", "calibrated" or "device" */

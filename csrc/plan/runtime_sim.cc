@@ -313,6 +313,28 @@ int cai_trace_dump_csv(cai_context_t* ctx, const char* path) {
     return OK;
 }
 
+// The same timeline in the Trace Event format (chrome://tracing, Perfetto): one complete event per op, one track per
+// logical stream. The reference's header promises a "Chrome-trace style" dump (include/cai.h:62) and only has the CSV.
+int cai_trace_dump_json(cai_context_t* ctx, const char* path) {
+    if (ctx->trace.empty()) return ERR_INVALID;
+    FILE* f = std::fopen(path, "w");
+    if (!f) return ERR_IO;
+    std::fprintf(f, "{\"displayTimeUnit\": \"ms\", \"traceEvents\": [\n");
+    for (int s = 0; s < ST_COUNT; ++s)
+        std::fprintf(f, "{\"ph\": \"M\", \"pid\": %u, \"tid\": %d, \"name\": \"thread_name\", \"args\": {\"name\": \"%s\"}},\n",
+                     ctx->desc.global_rank, s, stream_name(static_cast<uint16_t>(s)));
+    for (size_t i = 0; i < ctx->trace.size(); ++i) {
+        const cai_trace_rec_t& r = ctx->trace[i];
+        std::fprintf(f, "{\"ph\": \"X\", \"pid\": %u, \"tid\": %u, \"name\": \"%s\", \"ts\": %.4f, \"dur\": %.4f, "
+                        "\"args\": {\"op\": %u, \"bytes\": %llu, \"flops\": %llu}}%s\n",
+                     ctx->desc.global_rank, r.stream, op_name(r.kind), r.start_s * 1e6, (r.end_s - r.start_s) * 1e6, r.op_index,
+                     (unsigned long long)r.bytes, (unsigned long long)r.flops, i + 1 < ctx->trace.size() ? "," : "");
+    }
+    std::fprintf(f, "]}\n");
+    std::fclose(f);
+    return OK;
+}
+
 int cai_should_checkpoint(cai_context_t* ctx) {
     return ctx->desc.checkpoint_every && ctx->step % ctx->desc.checkpoint_every == 0;
 }

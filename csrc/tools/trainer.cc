@@ -91,7 +91,11 @@ int main(int argc, char** argv) {
         if (st.measured) std::printf("compute stream idle %.1f%% of the step (measured); pipeline bubble by formula %.1f%%\n",
                                      st.bubble_measured * 100.0, st.bubble_ratio * 100.0);
     }
-    if (trace && cai_trace_dump_csv(ctx, trace) == 0) std::printf("wrote op timeline to %s\n", trace);
+    if (trace) {   // *.json: Trace Event format for chrome://tracing / Perfetto; anything else: the reference's CSV
+        const size_t n = std::strlen(trace);
+        const bool json = n > 5 && !std::strcmp(trace + n - 5, ".json");
+        if ((json ? cai_trace_dump_json(ctx, trace) : cai_trace_dump_csv(ctx, trace)) == 0) std::printf("wrote op timeline to %s\n", trace);
+    }
     cai_finalize(ctx);
     return 0;
 }

@@ -304,3 +304,20 @@ def test_moe_layouts_compile_and_verify(tmp_path, world, keys):
     assert {plan.K_MOE_ROUTE, plan.K_MOE_DISPATCH_GEMM, plan.K_MOE_GEMM_COMBINE} <= kinds
     if d["tp"] > 1:
         assert {plan.K_AG_GEMM, plan.K_GEMM_RS} <= kinds     # attention stays tensor parallel around the experts
+
+
+def test_trace_in_the_trace_event_format(tmp_path):
+    """`trainer --trace x.json` writes the op timeline as Trace Event JSON (chrome://tracing, Perfetto): one track per
+    logical stream, one complete event per op with the times of the CSV."""
+    import csv
+    import json
+    run(BIN / "plan_compiler", ROOT / "configs" / "small.cfg", tmp_path, "--quiet", "--rank", "0")
+    pl, tp = tmp_path / "plan.rank000000.bin", tmp_path / "topology.bin"
+    run(BIN / "trainer", pl, tp, "--steps", "1", "--trace", tmp_path / "t.json")
+    run(BIN / "trainer", pl, tp, "--steps", "1", "--trace", tmp_path / "t.csv")
+    ev = json.loads((tmp_path / "t.json").read_text())["traceEvents"]
+    rows = list(csv.DictReader(open(tmp_path / "t.csv")))
+    spans = [e for e in ev if e["ph"] == "X"]
+    assert len(spans) == len(rows) and {e["args"]["name"] for e in ev if e["ph"] == "M"} >= {"compute_hi", "comm_tp", "io"}
+    for e, r in zip(spans[:50], rows[:50]):
+        assert e["name"] == r["kind"] and abs(e["ts"] - float(r["start_us"])) < 1e-3 and abs(e["dur"] - float(r["dur_us"])) < 1e-3
