@@ -104,3 +104,22 @@ def test_layout_advisor_ranks_executable_layouts(tmp_path):
     r = subprocess.run([sys.executable, "-m", "cai_b200.plan.advise", str(ROOT / "configs" / "b200_moe_ep8.cfg"), "--gpus", "8"],
                        capture_output=True, text=True, cwd=ROOT)
     assert r.returncode == 0 and "tokens/s" in r.stdout
+
+
+def test_timelines_of_two_backends_compare_kind_by_kind(tmp_path):
+    """`python -m cai_b200.plan.compare`: the predicted timeline (CSV) against the reference model's (Trace Event JSON) for
+    the same plan: ops match by index, every kind shows up once per stream, the calibrated sums are the larger ones."""
+    from cai_b200.plan import compare
+    pl, tp = _plans(tmp_path, 8)
+    for backend, out in (("calibrated", "pred.csv"), ("analytic", "ana.json")):
+        r = subprocess.run([str(BIN / "trainer"), str(pl), str(tp), "--steps", "1", "--backend", backend, "--trace", str(tmp_path / out)],
+                           capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+    table, odd = compare.compare(tmp_path / "pred.csv", tmp_path / "ana.json")
+    assert not any(odd.values())
+    kinds = {(r["kind"], r["stream"]) for r in table}
+    assert {("gemm_rs", "compute_hi"), ("ag_gemm", "compute_hi"), ("gemm", "compute_lo"), ("attn_bwd", "comm_dp")} <= kinds
+    assert all(r["a_ms"] >= r["b_ms"] for r in table if r["kind"] in ("gemm", "gemm_rs", "ag_gemm", "attn_fwd", "attn_bwd"))
+    r = subprocess.run([sys.executable, "-m", "cai_b200.plan.compare", str(tmp_path / "pred.csv"), str(tmp_path / "ana.json")],
+                       capture_output=True, text=True, cwd=ROOT)
+    assert r.returncode == 0 and "sum of op durations" in r.stdout
