@@ -321,3 +321,30 @@ def test_trace_in_the_trace_event_format(tmp_path):
     assert len(spans) == len(rows) and {e["args"]["name"] for e in ev if e["ph"] == "M"} >= {"compute_hi", "comm_tp", "io"}
     for e, r in zip(spans[:50], rows[:50]):
         assert e["name"] == r["kind"] and abs(e["ts"] - float(r["start_us"])) < 1e-3 and abs(e["dur"] - float(r["dur_us"])) < 1e-3
+
+
+# Executable plans of the benchmark configurations, rank 0 and the last rank, as they were when BASELINE.md's numbers
+# were measured on B200s (sha256, first 16 hex digits). A change of the plan compiler that alters one of them is either
+# deliberate (then the step has to be measured again and the digest updated) or a bug.
+MEASURED_PLANS = {
+    ("tp8", 1, "fused"): ("691edde438fa009a", "691edde438fa009a"),
+    ("tp8", 2, "fused"): ("af14005d59482e38", "67362f9f01015e1e"),
+    ("tp8", 4, "fused"): ("f074173f27db902b", "91fbd995d635d5cf"),
+    ("tp8", 8, "fused"): ("3230a613780c1809", "cab1a76a3f6e89f2"),
+    ("tp8", 8, "baseline"): ("37e665126f1978e3", "f43d11d7210b076f"),
+    ("moe_ep8", 8, "fused"): ("7ce712fd5b4cd7d5", "fec1ef0e689e7b60"),
+    ("fsdp8b", 8, "fused"): ("c6017d080ddc6ceb", "4fba568e1e74895c"),
+    ("pp2tp4", 8, "fused"): ("a26a5476ec8825f0", "836a06f629acb32b"),
+}
+
+
+@pytest.mark.parametrize("key", sorted(MEASURED_PLANS))
+def test_executable_plans_of_the_measured_configurations_are_unchanged(tmp_path, key):
+    import sys
+    sys.path.insert(0, str(ROOT))
+    import bench
+    from cai_b200 import plan
+    name, n, comm = key
+    plan.compile_plans(bench.config_text(n, comm, name), tmp_path, ranks=(0, n), version=2, text=True)
+    got = tuple(hashlib.sha256((tmp_path / f"plan.rank{r:06d}.bin").read_bytes()).hexdigest()[:16] for r in (0, n - 1))
+    assert got == MEASURED_PLANS[key]
