@@ -1,4 +1,5 @@
 """GPU-free tests of the offline compiler, verifier, analytic runtime and tools."""
+import hashlib
 import os
 import subprocess
 from pathlib import Path
