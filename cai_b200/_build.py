@@ -138,7 +138,8 @@ def build_sanitized_selftest(verbose=False) -> Path:
     return out
 
 
-REFERENCE_SRC = Path(os.environ.get("CAI_REFERENCE_SRC", "/root/reference"))
+# the reference's source tree: next to this repository unless CAI_REFERENCE_SRC says otherwise
+REFERENCE_SRC = Path(os.environ.get("CAI_REFERENCE_SRC", ROOT.parent / "reference"))
 REFERENCE_OUT = ROOT / "baseline" / "_ref"
 
 

@@ -324,8 +324,8 @@ def test_trace_in_the_trace_event_format(tmp_path):
         assert e["name"] == r["kind"] and abs(e["ts"] - float(r["start_us"])) < 1e-3 and abs(e["dur"] - float(r["dur_us"])) < 1e-3
 
 
-# Executable plans of the benchmark configurations, rank 0 and the last rank, as they were when BASELINE.md's numbers
-# were measured on B200s (sha256, first 16 hex digits). A change of the plan compiler that alters one of them is either
+# Executable plans of the benchmark configurations, rank 0 and the last rank, as they were when the repository's
+# published step times were measured on B200s (sha256, first 16 hex digits). A change of the plan compiler that alters one of them is either
 # deliberate (then the step has to be measured again and the digest updated) or a bug.
 MEASURED_PLANS = {
     ("tp8", 1, "fused"): ("691edde438fa009a", "691edde438fa009a"),
