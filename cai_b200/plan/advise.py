@@ -22,9 +22,10 @@ def _divisors(n, limit):
     return [d for d in range(1, min(n, limit) + 1) if n % d == 0]
 
 
-def candidates(base: dict, world: int):
+def candidates(base: dict, world: int, mb_groups=(0,)):
     """Layouts worth pricing: tp divides the kv heads (<= 8, one NVLink domain), pp divides the layers, the rest is data
-    (and, for MoE, expert) parallel; ZeRO-3 where the compiler has an executable schedule for it."""
+    (and, for MoE, expert) parallel; ZeRO-3 where the compiler has an executable schedule for it. ``mb_groups``:
+    microbatches per launch to try (0 = the compiler's choice)."""
     global_batch = base["global_batch"]
     for tp in _divisors(base["num_kv_heads"], 8):
         for pp in _divisors(base["num_layers"], 8):
@@ -38,14 +39,17 @@ def candidates(base: dict, world: int):
             if pp > 1 and grad_accum < pp:
                 continue
             for zero in ((1, 3) if (tp == 1 and pp == 1 and dp > 1 and not base["is_moe"]) else (1,)):
-                yield {"tp": tp, "pp": pp, "dp": dp, "ep": dp if base["is_moe"] else 1, "zero_stage": zero,
-                       "grad_accum": grad_accum}
+                for g in mb_groups:
+                    if g and (grad_accum % g or pp > 1 or zero == 3 or base["is_moe"]):
+                        continue        # grouping exists for dense, unpipelined, ZeRO-1 schedules only
+                    yield {"tp": tp, "pp": pp, "dp": dp, "ep": dp if base["is_moe"] else 1, "zero_stage": zero,
+                           "grad_accum": grad_accum, "mb_group": g}
 
 
 def evaluate(config_text: str, cand: dict, world: int, backend: str = "calibrated", workdir=None) -> dict:
     text = (config_text + f"\ngpus_per_rack = {world}\ntrays_per_rack = 1\ngpus_per_tray = {world}\nnum_racks = 1\n"
             f"tp = {cand['tp']}\npp = {cand['pp']}\nep = {cand['ep']}\nzero_stage = {cand['zero_stage']}\n"
-            f"grad_accum = {cand['grad_accum']}\ncomm = fused\n")
+            f"grad_accum = {cand['grad_accum']}\ncomm = fused\nmb_group = {cand.get('mb_group', 0)}\n")
     out = dict(cand)
     with tempfile.TemporaryDirectory(dir=workdir) as tmp:
         try:
@@ -70,11 +74,11 @@ def evaluate(config_text: str, cand: dict, world: int, backend: str = "calibrate
     return out
 
 
-def advise(config_path, gpus=None, backend="calibrated"):
+def advise(config_path, gpus=None, backend="calibrated", mb_groups=(0,)):
     text = Path(config_path).read_text()
     base = describe(text)
     world = gpus or base["world_size"]
-    rows = [evaluate(text, c, world, backend) for c in candidates(base, world)]
+    rows = [evaluate(text, c, world, backend) for c in candidates(base, world, mb_groups)]
     ok = sorted((r for r in rows if "step_ms" in r), key=lambda r: (not r["fits"], r["step_ms"]))
     return ok, [r for r in rows if "step_ms" not in r]
 
@@ -85,14 +89,15 @@ def main(argv=None):
     ap.add_argument("--gpus", type=int, default=None, help="GPUs of one NVLink domain (default: the configuration's)")
     ap.add_argument("--backend", default="calibrated", choices=("calibrated", "analytic"))
     ap.add_argument("--top", type=int, default=12)
+    ap.add_argument("--mb-groups", default="0", help="microbatches per launch to try, comma separated (0 = the compiler's choice)")
     a = ap.parse_args(argv)
-    ok, refused = advise(a.config, a.gpus, a.backend)
-    print(f"{'tp':>3} {'pp':>3} {'dp':>3} {'ep':>3} {'zero':>4} {'accum':>5} | {'step ms':>9} | {'tokens/s':>10} | {'arena GiB':>9} | fits")
+    ok, refused = advise(a.config, a.gpus, a.backend, tuple(int(x) for x in a.mb_groups.split(",")))
+    print(f"{'tp':>3} {'pp':>3} {'dp':>3} {'ep':>3} {'zero':>4} {'accum':>5} {'group':>5} | {'step ms':>9} | {'tokens/s':>10} | {'arena GiB':>9} | fits")
     for r in ok[:a.top]:
-        print(f"{r['tp']:3d} {r['pp']:3d} {r['dp']:3d} {r['ep']:3d} {r['zero_stage']:4d} {r['grad_accum']:5d} | {r['step_ms']:9.1f} | "
+        print(f"{r['tp']:3d} {r['pp']:3d} {r['dp']:3d} {r['ep']:3d} {r['zero_stage']:4d} {r['grad_accum']:5d} {r['mb_group']:5d} | {r['step_ms']:9.1f} | "
               f"{r['tokens_per_s']:10.3e} | {r['arena_gib']:9.2f} | {'yes' if r['fits'] else 'NO'}")
     for r in refused:
-        print(f"{r['tp']:3d} {r['pp']:3d} {r['dp']:3d} {r['ep']:3d} {r['zero_stage']:4d} {r['grad_accum']:5d} | not executable: {r['note']}")
+        print(f"{r['tp']:3d} {r['pp']:3d} {r['dp']:3d} {r['ep']:3d} {r['zero_stage']:4d} {r['grad_accum']:5d} {r['mb_group']:5d} | not executable: {r['note']}")
     return 0
 
 
