@@ -86,6 +86,7 @@ struct CalibratedImpl {
     Calibration c;
     std::vector<ExecOp> exec;
     std::vector<TensorDesc> tensors;
+    uint32_t capacity_x100 = 200;
 };
 
 double gemm_seconds(const Calibration& c, double M, double N, double K, bool ta, int sms, double* share) {
@@ -118,8 +119,20 @@ double price(const CalibratedImpl& im, const Topology& topo, const Op& op, const
     const uint32_t n = g ? g->size : 1;
     auto point = [&](const PointCost& pc) { return (pc.fixed_us + operand_mb(im, x) * pc.us_per_mb) * 1e-6; };
     switch (x.kernel) {
-    case K_GEMM:
-        return gemm_seconds(c, x.i[0], x.i[1], x.i[2], x.flags & 1, c.sms, share);
+    case K_GEMM: {
+        double M = x.i[0], N = x.i[1], K = x.i[2];
+        if (x.flags & 0x100) {
+            // grouped expert GEMM: one launch over all local experts' slabs (op.flops counts every slab row); tiles past a
+            // slab's token count are skipped, and with balanced routing a slab is filled to 1 / capacity factor
+            const double experts = std::max(1.0, std::round(static_cast<double>(op.flops) / (2.0 * M * N * K)));
+            const double live = std::min(1.0, 100.0 / std::max(100u, im.capacity_x100));
+            if (x.i[4] == 2050) K *= live;   // weight-gradient form: the ragged dimension is K
+            else M *= live;
+            if (x.i[4] == 2050) return experts * gemm_seconds(c, M, N, K, x.flags & 1, c.sms, share);
+            M *= experts;
+        }
+        return gemm_seconds(c, M, N, K, x.flags & 1, c.sms, share);
+    }
     case K_GEMM_FP8:
         return gemm_seconds(c, x.i[0], x.i[1], x.i[2], false, c.sms, share) / c.fp8_speedup;
     case K_AG_GEMM: case K_GEMM_RS: {
@@ -212,6 +225,7 @@ int calibrated_load_plan(Backend* be, const Plan& plan, const std::string&, uint
     auto* im = static_cast<CalibratedImpl*>(be->impl);
     im->exec = plan.exec;
     im->tensors = plan.tensors;
+    im->capacity_x100 = plan.train.moe_capacity_factor_x100 ? plan.train.moe_capacity_factor_x100 : 200;
     return OK;
 }
 
