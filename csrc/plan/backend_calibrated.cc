@@ -77,6 +77,15 @@ bool set_key(Calibration* c, const std::string& k, double v) {
             *e.dst = v;
             return true;
         }
+    struct PEntry { const char* name; PointCost* dst; };
+    PEntry points[] = {{"pointwise", &c->point_default}, {"rmsnorm_fwd", &c->rmsnorm_fwd}, {"rmsnorm_bwd", &c->rmsnorm_bwd},
+                       {"rope", &c->rope}, {"swiglu", &c->swiglu}, {"adamw", &c->adamw}, {"cross_entropy", &c->cross_entropy},
+                       {"embed", &c->embed}};
+    for (const PEntry& e : points) {   // <kernel>_fixed_us, <kernel>_us_per_mb
+        const std::string n = e.name;
+        if (k == n + "_fixed_us") { e.dst->fixed_us = v; return true; }
+        if (k == n + "_us_per_mb") { e.dst->us_per_mb = v; return true; }
+    }
     if (k == "sms") { c->sms = static_cast<int>(v); return true; }
     if (k == "ag_copy_ctas") { c->ag_copy_ctas = static_cast<int>(v); return true; }
     return false;

@@ -134,3 +134,15 @@ def test_timelines_of_two_backends_compare_kind_by_kind(tmp_path):
     r = subprocess.run([sys.executable, "-m", "cai_b200.plan.compare", str(tmp_path / "pred.csv"), str(tmp_path / "ana.json")],
                        capture_output=True, text=True, cwd=ROOT)
     assert r.returncode == 0 and "sum of op durations" in r.stdout
+
+
+def test_bundled_calibration_file_spells_out_the_built_in_constants(tmp_path):
+    """configs/b200_calibration.cfg documents every constant with its built-in value: loading it changes nothing."""
+    pl, tp = _plans(tmp_path, 4)
+    outs = []
+    for extra in ([], ["--calibration", str(ROOT / "configs" / "b200_calibration.cfg")]):
+        r = subprocess.run([str(BIN / "trainer"), str(pl), str(tp), "--steps", "1", "--backend", "calibrated"] + extra,
+                           capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+        outs.append([l for l in r.stdout.splitlines() if l.strip().startswith("0 |")][0])
+    assert outs[0] == outs[1]
