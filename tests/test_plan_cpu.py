@@ -256,7 +256,7 @@ def test_benchmark_configs_compile_for_every_gpu_count(tmp_path):
 
 
 def test_backend_selection_at_cai_init(tmp_path):
-    """One runtime API, two backends: without a GPU `--device` is refused with a reason, `--backend auto` falls
+    """One runtime API for every backend: without a GPU `--device` is refused with a reason, `--backend auto` falls
     back to the analytic backend (the order of the reference's cai_init, src/runtime.c:32-73)."""
     import torch
     if torch.cuda.is_available():
