@@ -138,3 +138,22 @@ def test_tied_head_is_copied_when_the_destination_unties_it_and_never_dropped_si
     _write(lp, got, 10, tmp_path / "p2")
     with pytest.raises(plan.PlanError):
         reshard.reshard(piped, tmp_path / "p2", tied, tmp_path / "t3")
+
+
+def test_checkpoint_inspector_lists_sections_and_notices_damage(tmp_path):
+    import subprocess
+    import sys
+    from cai_b200.utils import ckpt_info, reshard
+    cfg = _cfg(tmp_path, "one", "tiny_mp.cfg", 1, "")
+    layout = reshard.layout_of(cfg)
+    _write(layout, _random_state([layout], seed=5), 17, tmp_path / "ck")
+    info = ckpt_info.inspect(tmp_path / "ck", 0)
+    assert info["step"] == 17 and info["plan_hash"] == layout[0].plan_hash
+    assert [s[0] for s in info["sections"]] == ["param", "master", "m", "v", "meta"] and all(s[2] for s in info["sections"])
+    assert dict((s[0], s[1]) for s in info["sections"])["master"] == 4 * layout[0].n_opt
+    f = Path(info["file"])
+    raw = bytearray(f.read_bytes())
+    raw[len(raw) // 2] ^= 0x40                      # one flipped bit in the middle of the file
+    f.write_bytes(bytes(raw))
+    r = subprocess.run([sys.executable, "-m", "cai_b200.utils.ckpt_info", str(tmp_path / "ck")], capture_output=True, text=True, cwd=ROOT)
+    assert r.returncode == 1 and "CHECKSUM MISMATCH" in r.stdout
