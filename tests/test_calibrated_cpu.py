@@ -146,3 +146,39 @@ def test_bundled_calibration_file_spells_out_the_built_in_constants(tmp_path):
         assert r.returncode == 0, r.stderr
         outs.append([l for l in r.stdout.splitlines() if l.strip().startswith("0 |")][0])
     assert outs[0] == outs[1]
+
+
+def test_fit_recovers_the_constants_a_timeline_was_made_with(tmp_path):
+    """`python -m cai_b200.plan.fit`: timelines priced with altered constants (a slower GEMM, another launch cost, other
+    attention step times, a slower RoPE) stand in for measured ones; the least-squares fit over three layouts of the
+    headline model gives those constants back, and a file written from it reproduces the timelines."""
+    from cai_b200.plan import fit
+    truth = {"gemm_launch_us": 20.0, "gemm_tile_us": 1.5, "gemm_sm_flops": 5.0e12, "gemm_tile_us_ta": 6.0, "gemm_sm_flops_ta": 4.0e12,
+             "attn_fwd_step_us": 2.2, "attn_fwd_fixed_us": 31.0, "attn_dkdv_step_us": 4.4, "attn_dq_step_us": 3.3,
+             "attn_bwd_fixed_us": 12.0, "rope_fixed_us": 11.0, "rope_us_per_mb": 0.5, "rmsnorm_bwd_us_per_mb": 0.4}
+    cal = tmp_path / "truth.cfg"
+    cal.write_text("".join(f"{k} = {v}\n" for k, v in truth.items()))
+    pairs = []
+    for n in (1, 2, 8):
+        pl, tp = _plans(tmp_path, n)
+        out = tmp_path / f"measured{n}.csv"
+        r = subprocess.run([str(BIN / "trainer"), str(pl), str(tp), "--steps", "1", "--calibration", str(cal), "--trace", str(out)],
+                           capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+        pairs.append((pl, out))
+    consts, report = fit.fit(pairs)
+    for k, v in truth.items():
+        assert k in consts and abs(consts[k] - v) <= 0.02 * v, (k, consts.get(k), v, report)
+    # the command-line form writes a calibration file that the backend accepts and that reproduces the step time
+    flat = [str(x) for pair in pairs for x in pair]
+    r = subprocess.run([sys.executable, "-m", "cai_b200.plan.fit"] + flat, capture_output=True, text=True, cwd=ROOT)
+    assert r.returncode == 0, r.stderr
+    fitted = tmp_path / "fitted.cfg"
+    fitted.write_text(r.stdout)
+    pl, tp = pairs[2][0], pairs[2][0].parent / "topology.bin"
+
+    def ms(calfile):
+        rr = subprocess.run([str(BIN / "trainer"), str(pl), str(tp), "--steps", "1", "--calibration", str(calfile)], capture_output=True, text=True)
+        assert rr.returncode == 0, rr.stderr
+        return float([l for l in rr.stdout.splitlines() if l.strip().startswith("0 |")][0].split("|")[1].split()[0])
+    assert abs(ms(fitted) - ms(cal)) <= 0.01 * ms(cal)
