@@ -46,7 +46,7 @@ def candidates(base: dict, world: int, mb_groups=(0,)):
                            "grad_accum": grad_accum, "mb_group": g}
 
 
-def evaluate(config_text: str, cand: dict, world: int, backend: str = "calibrated", workdir=None) -> dict:
+def evaluate(config_text: str, cand: dict, world: int, backend: str = "calibrated", workdir=None, calibration=None) -> dict:
     text = (config_text + f"\ngpus_per_rack = {world}\ntrays_per_rack = 1\ngpus_per_tray = {world}\nnum_racks = 1\n"
             f"tp = {cand['tp']}\npp = {cand['pp']}\nep = {cand['ep']}\nzero_stage = {cand['zero_stage']}\n"
             f"grad_accum = {cand['grad_accum']}\ncomm = fused\nmb_group = {cand.get('mb_group', 0)}\n")
@@ -63,7 +63,8 @@ def evaluate(config_text: str, cand: dict, world: int, backend: str = "calibrate
             stage_rank.setdefault(pf.hdr.pipeline_stage, (r, pf.hdr.arena_bytes))
         step = 0.0
         for r, _ in stage_rank.values():
-            sim = Simulator(Path(tmp) / f"plan.rank{r:06d}.bin", Path(tmp) / "topology.bin", rank=r, backend=backend)
+            sim = Simulator(Path(tmp) / f"plan.rank{r:06d}.bin", Path(tmp) / "topology.bin", rank=r, backend=backend,
+                            calibration=calibration)
             st = sim.step()
             sim.close()
             step = max(step, st.step_time_s)
@@ -74,11 +75,11 @@ def evaluate(config_text: str, cand: dict, world: int, backend: str = "calibrate
     return out
 
 
-def advise(config_path, gpus=None, backend="calibrated", mb_groups=(0,)):
+def advise(config_path, gpus=None, backend="calibrated", mb_groups=(0,), calibration=None):
     text = Path(config_path).read_text()
     base = describe(text)
     world = gpus or base["world_size"]
-    rows = [evaluate(text, c, world, backend) for c in candidates(base, world, mb_groups)]
+    rows = [evaluate(text, c, world, backend, calibration=calibration) for c in candidates(base, world, mb_groups)]
     ok = sorted((r for r in rows if "step_ms" in r), key=lambda r: (not r["fits"], r["step_ms"]))
     return ok, [r for r in rows if "step_ms" not in r]
 
@@ -90,8 +91,9 @@ def main(argv=None):
     ap.add_argument("--backend", default="calibrated", choices=("calibrated", "analytic"))
     ap.add_argument("--top", type=int, default=12)
     ap.add_argument("--mb-groups", default="0", help="microbatches per launch to try, comma separated (0 = the compiler's choice)")
+    ap.add_argument("--calibration", help="key = value file overriding constants of the calibrated backend (see configs/b200_calibration.cfg)")
     a = ap.parse_args(argv)
-    ok, refused = advise(a.config, a.gpus, a.backend, tuple(int(x) for x in a.mb_groups.split(",")))
+    ok, refused = advise(a.config, a.gpus, a.backend, tuple(int(x) for x in a.mb_groups.split(",")), a.calibration)
     print(f"{'tp':>3} {'pp':>3} {'dp':>3} {'ep':>3} {'zero':>4} {'accum':>5} {'group':>5} | {'step ms':>9} | {'tokens/s':>10} | {'arena GiB':>9} | fits")
     for r in ok[:a.top]:
         print(f"{r['tp']:3d} {r['pp']:3d} {r['dp']:3d} {r['ep']:3d} {r['zero_stage']:4d} {r['grad_accum']:5d} {r['mb_group']:5d} | {r['step_ms']:9.1f} | "
