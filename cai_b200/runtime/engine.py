@@ -118,6 +118,7 @@ class Engine:
         if self.plan.hdr.version != 2:
             raise planlib.PlanError(f"{plan_path} is a cost-only (version 1) plan; compile with --exec")
         self.topology = planlib.read_topology(topology_path)
+        self.topology_path = str(topology_path)
         th = planlib.fnv1a(bytes(self.topology))
         if th != self.plan.hdr.topology_hash:
             raise planlib.PlanError("plan was compiled for a different topology (hash mismatch)")

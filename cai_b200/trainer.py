@@ -252,6 +252,17 @@ def main(argv=None):
             line += (f" | avg {sum_tps / n:.3e} tokens/s | arena {h.arena_bytes / 2**30:.2f} GiB/gpu | "
                      f"{eng.launches_per_step} kernel launches/step")
             print(line)
+        if n:
+            # what the calibrated pricing backend predicts for this rank's plan, next to what was measured
+            try:
+                sim = planlib.Simulator(eng.plan.path, eng.topology_path, rank=rank, backend="calibrated")
+                predicted = sim.step().step_time_s
+                sim.close()
+                measured = h.global_tokens_per_step / (sum_tps / n)
+                print(f"calibrated model: {predicted * 1e3:.2f} ms/step predicted, {measured * 1e3:.2f} measured "
+                      f"(measured / predicted = {measured / predicted:.2f})")
+            except Exception as e:  # the prediction is a courtesy; a run never fails over it
+                print(f"calibrated model: no prediction ({e})", file=sys.stderr)
         if stream_line:
             busy, idle = stream_line
             print("per-stream occupancy (ms), measured on the last step: " +
