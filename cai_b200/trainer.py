@@ -37,6 +37,7 @@ import torch
 from . import plan as planlib
 from .runtime.engine import Engine, synthetic_batch
 from .utils.health import Heartbeat, RankFailure, Watchdog
+from .utils.schedule import lr_at
 
 ROOT = Path(__file__).resolve().parent.parent
 
@@ -82,6 +83,10 @@ def main(argv=None):
     ap.add_argument("--nvtx", action="store_true", help="NVTX range per op, named by kernel (for timeline tools)")
     ap.add_argument("--jsonl")
     ap.add_argument("--comm", choices=["fused", "baseline"])
+    ap.add_argument("--lr-warmup", type=int, default=0, help="steps of linear learning-rate warm-up")
+    ap.add_argument("--lr-decay", choices=["none", "cosine", "linear"], default="none", help="decay after the warm-up")
+    ap.add_argument("--lr-total", type=int, default=0, help="step at which the decay ends (default: --steps)")
+    ap.add_argument("--lr-min-ratio", type=float, default=0.1, help="final rate as a share of the configured one")
     ap.add_argument("--step-timeout", type=float, default=600.0, help="watchdog deadline of one step in seconds (0 = off)")
     ap.add_argument("--peer-timeout", type=float, default=120.0, help="how long to wait for the other ranks between steps (0 = off)")
     ap.add_argument("--fail-at", type=int, default=-1, help="raise in the step callback at this step (host-side fault injection)")
@@ -162,6 +167,8 @@ def main(argv=None):
         sys.stderr.flush()
         os._exit(1)
 
+    base_lr = float(eng.lr)
+    scheduled = a.lr_warmup > 0 or a.lr_decay != "none"
     dog = Watchdog(a.step_timeout, on_overrun) if a.step_timeout > 0 else None
     stream_line = None
     try:
@@ -181,6 +188,8 @@ def main(argv=None):
                 eng.use_graph(True)
             if step == a.fail_at:
                 raise RuntimeError("injected failure (--fail-at)")
+            if scheduled:
+                eng.lr = lr_at(step, base_lr, a.lr_warmup, a.lr_total or a.steps, a.lr_decay, a.lr_min_ratio)
             last = step == a.steps - 1
             traced = last and (a.trace or not a.no_stream_stats)
             if dog:
@@ -221,6 +230,8 @@ def main(argv=None):
                         rec["mfu_vs_measured_peak"] = eng.mfu(dt, peak_measured)
                     if straggler:
                         rec["straggler"] = straggler
+                    if scheduled:
+                        rec["lr"] = eng.lr
                     if traced:
                         rec["stream_busy_ms"] = {planlib.STREAMS[i]: busy[i] * 1e3 for i in range(6)}
                         rec["bubble_measured"] = idle
