@@ -36,6 +36,7 @@ import torch
 
 from . import plan as planlib
 from .runtime.engine import Engine, synthetic_batch
+from .utils.data import TokenBatches
 from .utils.health import Heartbeat, RankFailure, Watchdog
 from .utils.schedule import lr_at
 
@@ -83,6 +84,8 @@ def main(argv=None):
     ap.add_argument("--nvtx", action="store_true", help="NVTX range per op, named by kernel (for timeline tools)")
     ap.add_argument("--jsonl")
     ap.add_argument("--comm", choices=["fused", "baseline"])
+    ap.add_argument("--data", help="token file (raw uint16 / uint32 ids, or .npy) to train on; default: synthetic tokens")
+    ap.add_argument("--data-dtype", choices=["uint16", "uint32"], default=None, help="id width of a raw --data file (default uint16)")
     ap.add_argument("--lr-warmup", type=int, default=0, help="steps of linear learning-rate warm-up")
     ap.add_argument("--lr-decay", choices=["none", "cosine", "linear"], default="none", help="decay after the warm-up")
     ap.add_argument("--lr-total", type=int, default=0, help="step at which the decay ends (default: --steps)")
@@ -167,6 +170,11 @@ def main(argv=None):
         sys.stderr.flush()
         os._exit(1)
 
+    data = None
+    if a.data:
+        data = TokenBatches(a.data, m.vocab_size, m.seq_len, rows * h.dp, eng.train.seed, dp=h.dp, dp_id=dp_id, dtype=a.data_dtype)
+        if is_printer:
+            print(f"data: {len(data.tokens):,} tokens from {a.data}, {rows * h.dp} windows of {m.seq_len} per step")
     base_lr = float(eng.lr)
     scheduled = a.lr_warmup > 0 or a.lr_decay != "none"
     dog = Watchdog(a.step_timeout, on_overrun) if a.step_timeout > 0 else None
@@ -181,9 +189,12 @@ def main(argv=None):
                 if n and waited > max(0.25 * (h.global_tokens_per_step * n / sum_tps), 0.05):
                     straggler = {"rank": last_rank, "waited_s": waited}
                     print(f"rank {rank}: waited {waited * 1e3:.0f} ms for rank {last_rank} before step {step}", file=sys.stderr)
-            tok, tgt = synthetic_batch(m.vocab_size, m.seq_len, rows * h.dp, step=step, seed=eng.train.seed)
-            tok = tok[dp_id * rows:(dp_id + 1) * rows].contiguous().pin_memory()
-            tgt = tgt[dp_id * rows:(dp_id + 1) * rows].contiguous().pin_memory()
+            if data is not None:
+                tok, tgt = data.get(step)       # prefetched into pinned memory; a function of (seed, step) only
+            else:
+                tok, tgt = synthetic_batch(m.vocab_size, m.seq_len, rows * h.dp, step=step, seed=eng.train.seed)
+                tok = tok[dp_id * rows:(dp_id + 1) * rows].contiguous().pin_memory()
+                tgt = tgt[dp_id * rows:(dp_id + 1) * rows].contiguous().pin_memory()
             if a.graph and step == first + 1:
                 eng.use_graph(True)
             if step == a.fail_at:
@@ -253,6 +264,8 @@ def main(argv=None):
     finally:
         if dog:
             dog.close()
+        if data is not None:
+            data.close()
     if eng.wait_checkpoint() != 0:
         print("warning: a checkpoint write failed", file=sys.stderr)
     if is_printer and (n or stream_line):
