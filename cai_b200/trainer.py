@@ -2,6 +2,7 @@
 
     python -m cai_b200.trainer <plan.bin> <topology.bin> [--steps N] [--ckpt PATH] [--ckpt-every K]
                                [--trace CSV] [--graph] [--nvtx] [--jsonl FILE]
+                               [--data TOKENS] [--lr-warmup N] [--lr-decay cosine|linear]
                                [--step-timeout S] [--peer-timeout S] [--fail-at STEP]
     python -m cai_b200.trainer --config configs/x.cfg [...]        (compiles this rank's plan first)
 
@@ -21,7 +22,7 @@ of the last completed step; the rolling "latest" checkpoint is never replaced by
 
 Rank and world size come from RANK / WORLD_SIZE / LOCAL_RANK (``launch.sh`` or
 ``torch.distributed.run`` set them). Data is a synthetic uniform-random token stream, a different
-slice per data-parallel replica.
+slice per data-parallel replica, or with ``--data`` windows of a token file (``cai_b200/utils/data.py``).
 """
 from __future__ import annotations
 
