@@ -1116,13 +1116,13 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             wgrad(dqkv, a.xn1, w.wqkv.g, b.Cqkv, H, T);
             b.row_parallel(dqkv, w.wqkv.w, -1, dxn, partial, rs_tmp, H, b.Cqkv, true, mb);
             b.rmsnorm_bwd(a.x, w.g1.w, a.rstd1, dxn, dstream, w.g1.g, norm_scratch, Tl, true, !first_mb, mb);
-            if (dp_buckets && (shard_grads || mb + 1 == ga)) {
+            if (dp_buckets && (shard_grads || mb + 1u == ga)) {
                 // the layer's gradients are complete on this rank: its bucket goes to comm_dp and runs under the
                 // backward of the layers below (a slice of the SMs is enough to keep NVLink busy). With sharded
                 // gradients every microbatch's contribution is reduced into the owners' accumulators.
                 b.sync(ST_COMPUTE_HI, ST_COMM_DP, mb);
                 if (lo_pending) b.sync(ST_COMPUTE_LO, ST_COMM_DP, mb);
-                emit_bucket(layer_range[l].first, layer_range[l].second, 64, mb, l, mb == 0, mb + 1 == ga);
+                emit_bucket(layer_range[l].first, layer_range[l].second, 64, mb, l, mb == 0, mb + 1u == ga);
                 if (shard_grads) stage_free_ev[l & 1] = static_cast<int>(b.record(ST_COMM_DP, mb));
             }
         }

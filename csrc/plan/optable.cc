@@ -18,30 +18,58 @@ uint32_t rank_stage(const Decomp& d, uint32_t rank) {
     return static_cast<uint32_t>((rank / (static_cast<uint64_t>(d.tp) * d.cp)) % d.pp);
 }
 
+// One communicator of one rank, computed without touching the heap: whole-world checks call this once per rank and kind
+// (hundreds of thousands of ranks), so it does only the arithmetic its kind needs.
+bool rank_group(const Decomp& d, const Topology& topo, bool is_moe, uint16_t kind, uint32_t rank, CommGroup* out) {
+    const uint32_t replica = d.tp * d.pp * d.cp;
+    CommGroup c{};
+    c.kind = kind;
+    switch (kind) {
+        case GROUP_TP: {
+            const uint32_t tp_first = rank - rank % d.tp;
+            c.group_id = 0;
+            c.size = d.tp;
+            c.color = tp_first;
+            c.intra_rack = same_rack(topo, tp_first, tp_first + d.tp - 1) ? 1 : 0;
+            break;
+        }
+        case GROUP_DP: {
+            const uint32_t within = rank % replica;
+            c.group_id = 1;
+            c.size = d.dp;
+            c.color = within;
+            c.intra_rack = d.dp > 1 && same_rack(topo, within, within + (d.dp - 1) * replica) ? 1 : 0;
+            break;
+        }
+        case GROUP_PP: {
+            // The reference always prices pipeline and expert groups at the inter-rack rate
+            // (src/model.c:581,589); kept so version-1 plans stay byte-identical.
+            const uint32_t tp_id = rank % d.tp, cp_id = (rank / d.tp) % d.cp, dp_id = rank / replica;
+            c.group_id = 2;
+            c.size = d.pp;
+            c.color = dp_id * (d.tp * d.cp) + cp_id * d.tp + tp_id;
+            break;
+        }
+        case GROUP_EP: {
+            if (!(is_moe && d.ep > 1)) return false;
+            const uint32_t within = rank % replica, dp_id = rank / replica;
+            c.group_id = 3;
+            c.size = d.ep;
+            c.color = within + (dp_id / d.ep) * d.ep * replica;
+            break;
+        }
+        default: return false;
+    }
+    *out = c;
+    return true;
+}
+
 std::vector<CommGroup> rank_groups(const Decomp& d, const Topology& topo, bool is_moe, uint32_t rank) {
-    const uint64_t replica = static_cast<uint64_t>(d.tp) * d.pp * d.cp;
-    const uint32_t tp_id = rank % d.tp;
-    const uint32_t cp_id = (rank / d.tp) % d.cp;
-    const uint32_t dp_id = static_cast<uint32_t>(rank / replica);
-    const uint32_t within = static_cast<uint32_t>(rank % replica);
     std::vector<CommGroup> g;
-    auto add = [&](uint16_t kind, uint32_t size, uint32_t color, bool intra) {
-        CommGroup c{};
-        c.group_id = static_cast<uint32_t>(g.size());
-        c.kind = kind;
-        c.size = size;
-        c.color = color;
-        c.intra_rack = intra ? 1 : 0;
-        g.push_back(c);
-    };
-    const uint32_t tp_first = rank - tp_id;
-    add(GROUP_TP, d.tp, tp_first, same_rack(topo, tp_first, tp_first + d.tp - 1));
-    add(GROUP_DP, d.dp, within,
-        d.dp > 1 && same_rack(topo, within, within + (d.dp - 1) * static_cast<uint32_t>(replica)));
-    // The reference always prices pipeline and expert groups at the inter-rack rate
-    // (src/model.c:581,589); kept so version-1 plans stay byte-identical.
-    add(GROUP_PP, d.pp, dp_id * (d.tp * d.cp) + cp_id * d.tp + tp_id, false);
-    if (is_moe && d.ep > 1) add(GROUP_EP, d.ep, within + (dp_id / d.ep) * d.ep * static_cast<uint32_t>(replica), false);
+    g.reserve(4);
+    CommGroup c;
+    for (uint16_t kind : {GROUP_TP, GROUP_DP, GROUP_PP, GROUP_EP})
+        if (rank_group(d, topo, is_moe, kind, rank, &c)) g.push_back(c);
     return g;
 }
 
@@ -290,11 +318,25 @@ int build_plan_v1(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     c.layer_w = static_cast<double>(layer_params_total(m)) / tpf / (c.moe ? d.ep : 1) * pb;
     c.a2a = c.moe ? T * m.moe_top_k * m.hidden_size * pb / tpf : 0.0;
 
-    Emitter e;
-    e.ops.reserve(1024);
-    for (const Tick& t : schedule_1f1b(c.stage, d.pp, d.num_microbatches)) {
-        if (t.kind == 0) microbatch_forward(e, c, t.microbatch);
-        else microbatch_backward(e, c, t.microbatch);
+    // The forward (and the backward) op sequence of a stage is the same for every microbatch but for the microbatch id
+    // and the numbers of its events, which count up in emission order: each is emitted once and stamped per tick.
+    Emitter fwd, bwd, e;
+    microbatch_forward(fwd, c, 0);
+    microbatch_backward(bwd, c, 0);
+    const std::vector<Tick> ticks = schedule_1f1b(c.stage, d.pp, d.num_microbatches);
+    size_t total = 8;
+    for (const Tick& t : ticks) total += t.kind == 0 ? fwd.ops.size() : bwd.ops.size();
+    e.ops.reserve(total);
+    for (const Tick& t : ticks) {
+        const Emitter& src = t.kind == 0 ? fwd : bwd;
+        const size_t at = e.ops.size();
+        e.ops.insert(e.ops.end(), src.ops.begin(), src.ops.end());
+        for (size_t i = at; i < e.ops.size(); ++i) {
+            Op& o = e.ops[i];
+            o.aux1 = t.microbatch;
+            if (o.kind == OP_EVENT_RECORD || o.kind == OP_EVENT_WAIT) o.aux0 += e.next_event;
+        }
+        e.next_event += src.next_event;
     }
     if (d.dp > 1) e.sync(ST_COMM_DP, {ST_COMPUTE_LO}, 0);
     e.compute(OP_OPTIMIZER, ST_COMPUTE_LO, c.opt, 0);

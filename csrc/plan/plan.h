@@ -98,6 +98,7 @@ struct Plan {
 };
 uint32_t rank_stage(const Decomp& d, uint32_t rank);
 std::vector<CommGroup> rank_groups(const Decomp& d, const Topology& topo, bool is_moe, uint32_t rank);
+bool rank_group(const Decomp& d, const Topology& topo, bool is_moe, uint16_t kind, uint32_t rank, CommGroup* out);  // false: the rank has no group of this kind
 // Members of the communicator of `kind` that `rank` belongs to, in group-rank order.
 std::vector<uint32_t> group_members(const Decomp& d, bool is_moe, uint16_t kind, uint32_t rank);
 

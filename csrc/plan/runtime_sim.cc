@@ -88,9 +88,54 @@ struct cai_context {
     uint32_t step = 0;
     cai_step_stats_t last{};
     std::vector<double> event_time;
+    // The op table with every price looked up. A pricing backend is a function of the op, its communicator and the
+    // topology alone, so the table is priced when the first step of a plan runs; every later step only advances the
+    // six stream clocks over these entries (one per op, same order).
+    struct ReplayEntry {
+        double dur;       // modelled seconds (work entries)
+        double sm;        // dur x share of the SMs the op keeps busy (0 when the backend does not say)
+        uint32_t event;   // record / wait entries
+        uint8_t what;     // 0 work, 1 record, 2 wait
+        uint8_t stream;
+    };
+    std::vector<ReplayEntry> replay;
+    int replay_status = OK;
     bool trace_on = false;
     std::vector<cai_trace_rec_t> trace;
 };
+
+// Prices the loaded plan's op table once. Returns the status the first malformed op would give a step.
+static int price_table(cai_context* ctx) {
+    const Plan& p = ctx->plan;
+    ctx->replay.clear();
+    ctx->replay.reserve(p.ops.size());
+    const CommGroup* by_id[16] = {};
+    for (const CommGroup& c : p.groups)
+        if (c.group_id < 16) by_id[c.group_id] = &c;      // later entries win, as a linear search for the last match does
+    for (const Op& op : p.ops) {
+        cai_context::ReplayEntry r{};
+        if (op.stream_id >= ST_COUNT) return ERR_PLAN;
+        r.stream = static_cast<uint8_t>(op.stream_id);
+        if (op.kind == OP_EVENT_RECORD || op.kind == OP_EVENT_WAIT) {
+            if (op.aux0 >= p.hdr.num_events) return op.kind == OP_EVENT_RECORD ? ERR_PLAN : ERR_DEPENDENCY;
+            r.what = op.kind == OP_EVENT_RECORD ? 1 : 2;
+            r.event = op.aux0;
+        } else {
+            const CommGroup* g = nullptr;
+            if (op_is_comm(op.kind) || op.kind >= OP_COUNT_V1) {
+                if (op.aux0 < 16) g = by_id[op.aux0];
+                else
+                    for (const CommGroup& c : p.groups)
+                        if (c.group_id == op.aux0) g = &c;
+                if (!g && op_is_comm(op.kind)) return ERR_PLAN;
+            }
+            r.dur = ctx->be->op_seconds(ctx->be, ctx->topo, op, g);
+            if (ctx->be->op_sm_share) r.sm = r.dur * ctx->be->op_sm_share(ctx->be, ctx->topo, op, g);
+        }
+        ctx->replay.push_back(r);
+    }
+    return OK;
+}
 
 extern "C" {
 
@@ -169,6 +214,7 @@ int cai_load_plan(cai_context_t* ctx, const char* path) {
     ctx->plan = std::move(p);
     ctx->plan_path = path;
     ctx->event_time.assign(ctx->plan.hdr.num_events ? ctx->plan.hdr.num_events : 1, 0.0);
+    ctx->replay.clear();
     ctx->plan_loaded = true;
     logf(LOG_INFO, "plan loaded: stage %u/%u ops=%u groups=%u arena=%.2f GiB", ctx->plan.hdr.pipeline_stage,
          ctx->plan.hdr.num_stages, ctx->plan.hdr.num_ops, ctx->plan.hdr.num_groups,
@@ -238,38 +284,31 @@ int cai_train_step(cai_context_t* ctx, const cai_batch_t* batch) {
         ctx->step++;
         return OK;
     }
+    if (ctx->replay.empty() && !p.ops.empty()) ctx->replay_status = price_table(ctx);
+    if (ctx->replay_status != OK) return ctx->replay_status;
     double clock[ST_COUNT] = {0}, work[ST_COUNT] = {0};
     double sm_work = 0.0;  // sum of duration x share of the SMs, over all streams (backends that know the share)
+    double* const event_time = ctx->event_time.data();
     std::fill(ctx->event_time.begin(), ctx->event_time.end(), 0.0);
     ctx->trace.clear();
     if (ctx->trace_on) ctx->trace.reserve(p.ops.size());
-
-    for (uint32_t i = 0; i < p.ops.size(); ++i) {
-        const Op& op = p.ops[i];
-        const uint16_t st = op.stream_id;
-        if (st >= ST_COUNT) return ERR_PLAN;
-        if (op.kind == OP_EVENT_RECORD) {
-            if (op.aux0 >= p.hdr.num_events) return ERR_PLAN;
-            ctx->event_time[op.aux0] = clock[st];
-            continue;
+    const bool tracing = ctx->trace_on;
+    const cai_context::ReplayEntry* const prog = ctx->replay.data();
+    const uint32_t n_ops = static_cast<uint32_t>(ctx->replay.size());
+    for (uint32_t i = 0; i < n_ops; ++i) {
+        const cai_context::ReplayEntry& r = prog[i];
+        double& c = clock[r.stream];
+        if (r.what == 1) {
+            event_time[r.event] = c;
+        } else if (r.what == 2) {
+            c = std::max(c, event_time[r.event]);
+        } else {
+            const double start = c;
+            c = start + r.dur;
+            work[r.stream] += r.dur;
+            sm_work += r.sm;
+            if (tracing) ctx->trace.push_back({i, p.ops[i].kind, r.stream, start, start + r.dur, p.ops[i].bytes, p.ops[i].flops});
         }
-        if (op.kind == OP_EVENT_WAIT) {
-            if (op.aux0 >= p.hdr.num_events) return ERR_DEPENDENCY;
-            clock[st] = std::max(clock[st], ctx->event_time[op.aux0]);
-            continue;
-        }
-        const CommGroup* g = nullptr;
-        if (op_is_comm(op.kind) || op.kind >= OP_COUNT_V1) {
-            for (const CommGroup& c : p.groups)
-                if (c.group_id == op.aux0) g = &c;
-            if (!g && op_is_comm(op.kind)) return ERR_PLAN;
-        }
-        const double dur = ctx->be->op_seconds(ctx->be, ctx->topo, op, g);
-        if (ctx->be->op_sm_share) sm_work += dur * ctx->be->op_sm_share(ctx->be, ctx->topo, op, g);
-        const double start = clock[st];
-        clock[st] = start + dur;
-        work[st] += dur;
-        if (ctx->trace_on) ctx->trace.push_back({i, op.kind, st, start, start + dur, op.bytes, op.flops});
     }
 
     double busy = 0.0;

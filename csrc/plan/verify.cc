@@ -32,21 +32,18 @@ void verify_tiling(const Decomp& d, const Topology& topo, bool is_moe, uint16_t 
     uint32_t want = 0;
     bool uniform = true, in_range = true;
     for (uint32_t r = 0; r < W; ++r) {
-        const CommGroup* g = nullptr;
-        const std::vector<CommGroup> gs = rank_groups(d, topo, is_moe, r);
-        for (const CommGroup& c : gs)
-            if (c.kind == kind) g = &c;
-        if (!g) {
+        CommGroup g;
+        if (!rank_group(d, topo, is_moe, kind, r, &g)) {
             add(rep, false, "%s: rank %u has no group", name, r);
             return;
         }
-        if (r == 0) want = g->size;
-        else if (g->size != want) uniform = false;
-        if (g->color >= W) {
+        if (r == 0) want = g.size;
+        else if (g.size != want) uniform = false;
+        if (g.color >= W) {
             in_range = false;
             continue;
         }
-        count[g->color]++;
+        count[g.color]++;
     }
     uint32_t buckets = 0, bad = 0;
     uint64_t total = 0;
@@ -66,13 +63,11 @@ void verify_tiling(const Decomp& d, const Topology& topo, bool is_moe, uint16_t 
     // group_members() must agree with the colouring the plans carry
     for (uint32_t r : {0u, W / 2, W - 1}) {
         const std::vector<uint32_t> mem = group_members(d, is_moe, kind, r);
-        uint32_t color = 0;
-        for (const CommGroup& c : rank_groups(d, topo, is_moe, r))
-            if (c.kind == kind) color = c.color;
+        CommGroup mine{}, theirs{};
+        rank_group(d, topo, is_moe, kind, r, &mine);
+        const uint32_t color = mine.color;
         for (uint32_t peer : mem) {
-            uint32_t pc = ~0u;
-            for (const CommGroup& c : rank_groups(d, topo, is_moe, peer))
-                if (c.kind == kind) pc = c.color;
+            const uint32_t pc = rank_group(d, topo, is_moe, kind, peer, &theirs) ? theirs.color : ~0u;
             if (pc != color) {
                 add(rep, false, "%s: rank %u lists peer %u of another colour", name, r, peer);
                 return;
