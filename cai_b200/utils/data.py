@@ -50,6 +50,8 @@ class TokenBatches:
         if self.windows <= 0:
             raise ValueError(f"{path}: {len(self.tokens)} tokens are fewer than one window of {seq + 1}")
         self.pin = torch.cuda.is_available() if pin is None else pin
+        # the prefetch thread pins its buffers in the CUDA context of the rank's own device, not of device 0
+        self._device = torch.cuda.current_device() if (self.pin and torch.cuda.is_available()) else None
         self._q, self._next, self._thread, self._stop = None, None, None, False
         self._depth = max(0, int(prefetch))
 
@@ -72,6 +74,8 @@ class TokenBatches:
 
     # ---- prefetching -------------------------------------------------------------------------------------------
     def _run(self, first):
+        if self._device is not None:
+            torch.cuda.set_device(self._device)
         step = first
         while not self._stop:
             try:
