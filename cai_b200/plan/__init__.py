@@ -136,6 +136,8 @@ def lib() -> ctypes.CDLL:
             raise PlanError(f"{_LIB_PATH} is missing: run `python -m cai_b200._build` first")
         L = ctypes.CDLL(str(_LIB_PATH))
         L.cai_status_str.restype = c_char_p
+        L.cai_log_set_level.argtypes = [c_int]
+        L.cai_log_set_level.restype = None
         L.cai_compile.argtypes = [c_char_p, c_char_p, c_uint32, c_uint32, c_uint32, POINTER(c_uint64),
                                   POINTER(c_uint64), c_char_p, c_size_t]
         L.cai_compile_text.argtypes = L.cai_compile.argtypes
@@ -168,6 +170,15 @@ def lib() -> ctypes.CDLL:
 
 def fnv1a(data: bytes, seed: int = 0) -> int:
     return lib().cai_fnv1a64(data, len(data), seed)
+
+
+LOG_LEVELS = {"error": 0, "warn": 1, "info": 2, "debug": 3}
+
+
+def set_log_level(level) -> None:
+    """Level of the native library's stderr log (``"error" | "warn" | "info" | "debug"`` or 0..3); the environment
+    variable CAI_LOG_LEVEL sets the starting level of a process (default info, as in the reference, src/common.c:9-22)."""
+    lib().cai_log_set_level(LOG_LEVELS[level] if isinstance(level, str) else int(level))
 
 
 def compile_plans(config, outdir, ranks=None, version=2, text=False):

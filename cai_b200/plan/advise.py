@@ -12,10 +12,11 @@ tools/topology_linter.c suggests tensor-parallel sizes by rule); here the answer
 from __future__ import annotations
 
 import argparse
+import os
 import tempfile
 from pathlib import Path
 
-from . import PlanError, PlanFile, Simulator, compile_plans, describe
+from . import PlanError, PlanFile, Simulator, compile_plans, describe, set_log_level
 
 
 def _divisors(n, limit):
@@ -93,6 +94,8 @@ def main(argv=None):
     ap.add_argument("--mb-groups", default="0", help="microbatches per launch to try, comma separated (0 = the compiler's choice)")
     ap.add_argument("--calibration", help="key = value file overriding constants of the calibrated backend (see configs/b200_calibration.cfg)")
     a = ap.parse_args(argv)
+    if "CAI_LOG_LEVEL" not in os.environ:
+        set_log_level("warn")       # one table on stdout; the per-plan INFO lines of dozens of replays are noise here
     ok, refused = advise(a.config, a.gpus, a.backend, tuple(int(x) for x in a.mb_groups.split(",")), a.calibration)
     print(f"{'tp':>3} {'pp':>3} {'dp':>3} {'ep':>3} {'zero':>4} {'accum':>5} {'group':>5} | {'step ms':>9} | {'tokens/s':>10} | {'arena GiB':>9} | fits")
     for r in ok[:a.top]:

@@ -3,16 +3,31 @@
 // stay interchangeable.
 #include <sys/stat.h>
 
+#include <strings.h>
+
 #include <cstdarg>
+#include <cstdlib>
 #include <cstring>
 
 #include "plan.h"
 
 namespace cai {
 
-static LogLevel g_level = LOG_INFO;
+// Default INFO, as in the reference (src/common.c:9-22). CAI_LOG_LEVEL (error | warn | info | debug, or 0..3) sets the
+// starting level of a process; log_set_level() / cai_log_set_level() override it.
+static int g_level = -1;
+static int level_from_env() {
+    const char* e = std::getenv("CAI_LOG_LEVEL");
+    if (!e || !*e) return LOG_INFO;
+    static const char* names[] = {"error", "warn", "info", "debug"};
+    for (int i = 0; i < 4; ++i)
+        if (!strcasecmp(e, names[i])) return i;
+    if (e[0] >= '0' && e[0] <= '3' && !e[1]) return e[0] - '0';
+    return LOG_INFO;
+}
 void log_set_level(LogLevel lv) { g_level = lv; }
 void logf(LogLevel lv, const char* fmt, ...) {
+    if (g_level < 0) g_level = level_from_env();
     if (lv > g_level) return;
     static const char* tags[] = {"ERROR", "WARN", "INFO", "DEBUG"};
     std::fprintf(stderr, "[cai %s] ", tags[lv]);

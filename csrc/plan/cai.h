@@ -76,6 +76,7 @@ typedef struct {
 } cai_trace_rec_t;
 
 const char* cai_status_str(int status);
+void cai_log_set_level(int level);   /* 0 error, 1 warn, 2 info (default), 3 debug; CAI_LOG_LEVEL sets the starting level */
 
 int cai_init(cai_context_t** ctx, const cai_init_desc_t* desc);
 int cai_load_plan(cai_context_t* ctx, const char* path);

@@ -140,6 +140,7 @@ static int price_table(cai_context* ctx) {
 extern "C" {
 
 const char* cai_status_str(int status) { return status_str(status); }
+void cai_log_set_level(int level) { log_set_level(static_cast<LogLevel>(level < 0 ? 0 : level > 3 ? 3 : level)); }
 
 int cai_init(cai_context_t** out, const cai_init_desc_t* desc) {
     auto ctx = std::make_unique<cai_context>();

@@ -24,3 +24,26 @@ def test_unknown_attribute_is_an_attribute_error():
     with pytest.raises(AttributeError):
         cai_b200.no_such_thing
     assert not hasattr(cai_b200, "__wrapped__")
+
+
+def test_log_level_from_the_environment_and_the_api(tmp_path):
+    """CAI_LOG_LEVEL sets the native library's starting level; set_log_level overrides it."""
+    import os
+    code = ("from cai_b200 import plan\n"
+            "import sys\n"
+            "if len(sys.argv) > 1: plan.set_log_level(sys.argv[1])\n"
+            f"plan.compile_plans(open('{ROOT}/configs/tiny.cfg').read(), '{tmp_path}', ranks=(0, 1), version=2, text=True)\n"
+            f"s = plan.Simulator('{tmp_path}/plan.rank000000.bin', '{tmp_path}/topology.bin', rank=0)\n"
+            "s.step(); s.close()\n")
+    def run(env_level=None, arg=None):
+        env = {k: v for k, v in os.environ.items() if k != "CAI_LOG_LEVEL"}
+        if env_level:
+            env["CAI_LOG_LEVEL"] = env_level
+        r = subprocess.run([sys.executable, "-c", code] + ([arg] if arg else []), capture_output=True, text=True, cwd=ROOT, env=env, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        return r.stderr
+    assert "[cai INFO] plan loaded" in run()
+    assert "[cai INFO]" not in run(env_level="warn")
+    assert "[cai INFO]" not in run(env_level="0")
+    assert "[cai INFO] plan loaded" in run(env_level="warn", arg="info")
+    assert "[cai INFO]" not in run(arg="error")
