@@ -172,6 +172,35 @@ def fnv1a(data: bytes, seed: int = 0) -> int:
     return lib().cai_fnv1a64(data, len(data), seed)
 
 
+class PipelineStats(ctypes.Structure):
+    _fields_ = [("n_stages", c_uint32), ("reserved", c_uint32), ("step_time_s", c_double), ("bubble_formula", c_double),
+                ("bubble_replayed", c_double), ("tokens_per_s", c_double), ("mfu", c_double),
+                ("stage_finish_s", c_double * 64), ("stage_busy_hi_s", c_double * 64), ("stage_idle_hi", c_double * 64)]
+
+
+def pipeline_replay(plan_paths, topology_path, backend="calibrated", calibration=None, trace=None) -> dict:
+    """Replay the plans of all stages of one pipeline together (``plan_paths[s]``: one rank of stage ``s``): sends meet
+    their receives, so fill, drain, uneven stages and transfer times are in the step time without the closed bubble
+    formula the single-plan replay (and the reference, src/runtime.c:191-194) applies. ``trace``: path of a Trace
+    Event JSON timeline with one process per stage. Raises ``PlanError`` when the stages' sends and receives deadlock."""
+    paths = [str(p).encode() for p in plan_paths]
+    arr = (c_char_p * len(paths))(*paths)
+    st = PipelineStats()
+    err = ctypes.create_string_buffer(512)
+    L = lib()
+    L.cai_pipeline_replay.argtypes = [POINTER(c_char_p), c_uint32, c_char_p, c_uint32, c_char_p, c_char_p, POINTER(PipelineStats),
+                                      c_char_p, c_size_t]
+    rc = L.cai_pipeline_replay(arr, len(paths), str(topology_path).encode(), BACKENDS[backend],
+                               str(calibration).encode() if calibration else None, str(trace).encode() if trace else None,
+                               ctypes.byref(st), err, len(err))
+    if rc != 0:
+        raise PlanError(f"pipeline replay failed ({L.cai_status_str(rc).decode()}): {err.value.decode()}")
+    n = st.n_stages
+    return {"step_time_s": st.step_time_s, "bubble_formula": st.bubble_formula, "bubble_replayed": st.bubble_replayed,
+            "tokens_per_s": st.tokens_per_s, "mfu": st.mfu, "stage_finish_s": list(st.stage_finish_s[:n]),
+            "stage_busy_hi_s": list(st.stage_busy_hi_s[:n]), "stage_idle_hi": list(st.stage_idle_hi[:n])}
+
+
 LOG_LEVELS = {"error": 0, "warn": 1, "info": 2, "debug": 3}
 
 

@@ -2,7 +2,8 @@
 
 For every layout the executable-plan compiler accepts (tensor x pipeline x data / expert parallel, optimizer-state or
 full ZeRO-3 sharding), the plans of one rank per pipeline stage are compiled and replayed by the calibrated pricing
-backend (costs fitted to this repository's kernels as measured on B200s); the table gives the predicted step time,
+backend (costs fitted to this repository's kernels as measured on B200s; the stages of a pipeline are replayed together,
+their sends meeting their receives); the table gives the predicted step time,
 tokens/s and the arena a rank allocates. The global batch of the input configuration is kept (``grad_accum`` follows the
 data-parallel degree). This is the offline question the reference's simulator is for ("which decomposition?",
 tools/topology_linter.c suggests tensor-parallel sizes by rule); here the answer comes from measured kernel costs.
@@ -16,7 +17,7 @@ import os
 import tempfile
 from pathlib import Path
 
-from . import PlanError, PlanFile, Simulator, compile_plans, describe, set_log_level
+from . import PlanError, PlanFile, Simulator, compile_plans, describe, pipeline_replay, set_log_level
 
 
 def _divisors(n, limit):
@@ -62,13 +63,16 @@ def evaluate(config_text: str, cand: dict, world: int, backend: str = "calibrate
         for r in range(world):
             pf = PlanFile(Path(tmp) / f"plan.rank{r:06d}.bin")
             stage_rank.setdefault(pf.hdr.pipeline_stage, (r, pf.hdr.arena_bytes))
-        step = 0.0
-        for r, _ in stage_rank.values():
+        if cand["pp"] > 1:
+            # all stages replayed together: sends meet their receives, no closed bubble formula
+            paths = [Path(tmp) / f"plan.rank{stage_rank[s][0]:06d}.bin" for s in sorted(stage_rank)]
+            step = pipeline_replay(paths, Path(tmp) / "topology.bin", backend=backend, calibration=calibration)["step_time_s"]
+        else:
+            r = stage_rank[0][0]
             sim = Simulator(Path(tmp) / f"plan.rank{r:06d}.bin", Path(tmp) / "topology.bin", rank=r, backend=backend,
                             calibration=calibration)
-            st = sim.step()
+            step = sim.step().step_time_s
             sim.close()
-            step = max(step, st.step_time_s)
         d = describe(text)
         out.update(step_ms=step * 1e3, tokens_per_s=d["global_tokens"] / step,
                    arena_gib=max(a for _, a in stage_rank.values()) / 2**30,

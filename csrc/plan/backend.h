@@ -48,6 +48,24 @@ struct Backend {
     void (*destroy)(Backend* be);
 };
 
+// Joint replay of all stages of one pipeline under a pricing backend (pipeline_sim.cc).
+struct PipelineResult {
+    struct Stage {
+        double finish_s = 0.0;               // when the stage's last op ends
+        double stream_busy[ST_COUNT] = {};   // summed op durations per logical stream
+        double sm_work_s = 0.0;              // sum of duration x share of the SMs (backends that know the share)
+        double idle_hi = 0.0;                // share of the step compute_hi has no op in flight
+    };
+    struct Rec { uint32_t stage; cai_trace_rec_t rec; };
+    double step_time_s = 0.0, bubble_formula = 0.0, tokens_per_s = 0.0, mfu = 0.0;
+    std::vector<Stage> stages;
+    bool want_trace = false;
+    std::vector<Rec> trace;
+};
+// `stages[s]` is the plan of one rank of stage s (same tensor / data coordinates). ERR_DEPENDENCY (with the op named in
+// *err) when the sends and receives of neighbouring stages can never all meet.
+int replay_pipeline(const std::vector<const Plan*>& stages, const Topology& topo, Backend* be, PipelineResult* out, std::string* err);
+
 Backend* backend_analytic_create();
 // Costs fitted to measurements on B200s (backend_calibrated.cc); `calibration_path` (may be null) overrides constants
 // from a key = value file. nullptr (with the reason in *why) when that file cannot be read or names an unknown key.

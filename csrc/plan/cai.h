@@ -75,6 +75,22 @@ typedef struct {
     uint64_t flops;
 } cai_trace_rec_t;
 
+/* Result of cai_pipeline_replay: all stages of one pipeline replayed together (sends meet their receives), so fill,
+ * drain, uneven stages and transfer times are in step_time_s without the closed bubble formula. */
+#define CAI_MAX_PIPELINE_STAGES 64
+typedef struct {
+    uint32_t n_stages;
+    uint32_t reserved;
+    double step_time_s;
+    double bubble_formula;       /* (pp-1)/(m+pp-1), for comparison */
+    double bubble_replayed;      /* share of the step the busiest stage's main compute stream stands still */
+    double tokens_per_s;
+    double mfu;
+    double stage_finish_s[CAI_MAX_PIPELINE_STAGES];
+    double stage_busy_hi_s[CAI_MAX_PIPELINE_STAGES];
+    double stage_idle_hi[CAI_MAX_PIPELINE_STAGES];
+} cai_pipeline_stats_t;
+
 const char* cai_status_str(int status);
 void cai_log_set_level(int level);   /* 0 error, 1 warn, 2 info (default), 3 debug; CAI_LOG_LEVEL sets the starting level */
 
@@ -90,6 +106,12 @@ int cai_trace_enable(cai_context_t* ctx, int on);
 int cai_trace_dump_csv(cai_context_t* ctx, const char* path);
 int cai_trace_dump_json(cai_context_t* ctx, const char* path);   /* Trace Event format (chrome://tracing, Perfetto) */
 int cai_finalize(cai_context_t* ctx);
+/* plan_paths[s]: the plan file of one rank of stage s. backend: CAI_BACKEND_ANALYTIC or CAI_BACKEND_CALIBRATED
+ * (calibration_path may be NULL). trace_json_path (may be NULL): Trace Event timeline, one process per stage.
+ * CAI_ERR_DEPENDENCY with the op named in err when the stages' sends and receives deadlock. */
+int cai_pipeline_replay(const char* const* plan_paths, uint32_t n_stages, const char* topology_path, uint32_t backend,
+                        const char* calibration_path, const char* trace_json_path, cai_pipeline_stats_t* out, char* err,
+                        size_t errlen);
 uint32_t cai_current_step(cai_context_t* ctx);
 const char* cai_backend_name(cai_context_t* ctx);   /* "analytic", "calibrated" or "device" */
 

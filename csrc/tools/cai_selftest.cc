@@ -11,6 +11,7 @@
 #include <set>
 
 #include "cai.h"
+#include "backend.h"
 #include "plan.h"
 
 using namespace cai;
@@ -466,6 +467,52 @@ static void test_calibrated_backend() {
     unsetenv("CAI_CALIBRATION");
 }
 
+// Joint replay of the stages of a pipeline: a healthy schedule replays, a missing receive is counted, and a schedule in
+// which two stages wait for each other (a gradient receive moved in front of the first activation send on the same
+// in-order stream) is reported as a deadlock instead of producing a time.
+static void test_pipeline_replay() {
+    Config c;
+    std::string err;
+    if (config_load("configs/b200_pp2tp4.cfg", &c, &err) != OK) { CHECK(false, "%s", err.c_str()); return; }
+    topology_finalize(&c.topo, &err);
+    Decomp d;
+    CHECK(decompose(c, &d, &err) == OK, "%s", err.c_str());
+    const uint64_t ph = plan_hash(c, d), th = topology_hash(c.topo);
+    Plan st0, st1;
+    CHECK(build_plan_v2(c, d, 0, ph, th, &st0, &err) == OK, "%s", err.c_str());
+    CHECK(build_plan_v2(c, d, d.tp * d.cp, ph, th, &st1, &err) == OK, "%s", err.c_str());
+    Backend* be = backend_analytic_create();
+    PipelineResult r;
+    CHECK(replay_pipeline({&st0, &st1}, c.topo, be, &r, &err) == OK, "healthy pipeline: %s", err.c_str());
+    CHECK(r.stages.size() == 2 && r.step_time_s > 0 && r.step_time_s >= r.stages[0].stream_busy[ST_COMPUTE_HI], "step %.4f", r.step_time_s);
+    CHECK(replay_pipeline({&st1, &st0}, c.topo, be, &r, &err) == ERR_PLAN, "stages in the wrong order accepted");
+    {   // one receive fewer on the upper stage
+        Plan broken = st1;
+        for (size_t i = 0; i < broken.ops.size(); ++i)
+            if (broken.ops[i].kind == OP_PIPE_RECV) { broken.ops.erase(broken.ops.begin() + static_cast<long>(i)); break; }
+        CHECK(replay_pipeline({&st0, &broken}, c.topo, be, &r, &err) == ERR_DEPENDENCY && err.find("receives") != std::string::npos,
+              "missing receive: %s", err.c_str());
+    }
+    {   // stage 0 posts its first gradient receive in front of its first activation send, on the same stream
+        Plan broken = st0;
+        size_t first_send = broken.ops.size(), first_recv = broken.ops.size();
+        for (size_t i = 0; i < broken.ops.size(); ++i) {
+            if (broken.ops[i].kind == OP_PIPE_SEND && first_send == broken.ops.size()) first_send = i;
+            if (broken.ops[i].kind == OP_PIPE_RECV && first_recv == broken.ops.size()) first_recv = i;
+        }
+        CHECK(first_send < first_recv && first_recv < broken.ops.size(), "stage 0 sends before it receives");
+        if (first_send < first_recv && first_recv < broken.ops.size()) {
+            Op moved = broken.ops[first_recv];
+            moved.stream_id = broken.ops[first_send].stream_id;
+            broken.ops.erase(broken.ops.begin() + static_cast<long>(first_recv));
+            broken.ops.insert(broken.ops.begin() + static_cast<long>(first_send), moved);
+            CHECK(replay_pipeline({&broken, &st1}, c.topo, be, &r, &err) == ERR_DEPENDENCY && err.find("deadlock") != std::string::npos,
+                  "deadlock not reported: %s", err.c_str());
+        }
+    }
+    be->destroy(be);
+}
+
 int main() {
     log_set_level(LOG_ERROR);
     test_topology();
@@ -480,6 +527,7 @@ int main() {
     test_exec_plans();
     test_checkpoint_files();
     test_calibrated_backend();
+    test_pipeline_replay();
     std::printf("%d checks, %d failures\n", g_checks, g_fail);
     return g_fail ? 1 : 0;
 }

@@ -1,4 +1,5 @@
 // trainer <plan.bin> <topology.bin> [--steps N] [--ckpt PATH] [--ckpt-every K] [--trace CSV] [--device | --backend B]
+// trainer <plan.bin> <topology.bin> --pipeline [--backend analytic|calibrated] [--calibration FILE] [--trace x.json]
 //
 // Replays a compiled plan: per-step critical path, pipeline bubble, MFU and tokens/s, per-stream
 // occupancy, optional op timeline as CSV, periodic and emergency checkpoints. Same command line and
@@ -7,15 +8,62 @@
 // executable plan on the GPU and fills the same table with measurements plus a loss column
 // (--backend auto takes the device when there is one, like the reference's cai_init). Multi-rank
 // jobs run through `python -m cai_b200.trainer`.
+//
+// --pipeline replays the plans of ALL stages of the pipeline the given plan belongs to (its siblings are looked up in
+// the same directory) as one graph in which sends meet their receives, instead of correcting one stage's busy time
+// with the closed bubble formula: per-stage finish times and idle shares, step time, and a deadlock report when the
+// stages' sends and receives cannot all meet.
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
+#include <string>
+#include <vector>
+
 #include "cai.h"
+#include "plan.h"
+
+// The plans of all stages of the pipeline `plan_path` belongs to, replayed together.
+static int run_pipeline(const char* plan_path, const char* topology_path, uint32_t backend, const char* trace) {
+    cai::Plan p;
+    if (cai::plan_read(plan_path, &p) != cai::OK) { std::fprintf(stderr, "cannot read plan '%s'\n", plan_path); return 1; }
+    const cai::PlanHeader& h = p.hdr;
+    const uint32_t stride = h.tp * (h.cp ? h.cp : 1), base = h.global_rank - h.pipeline_stage * stride;
+    std::string dir = plan_path;
+    const size_t slash = dir.find_last_of('/');
+    dir = slash == std::string::npos ? "." : dir.substr(0, slash);
+    std::vector<std::string> paths;
+    std::vector<const char*> cpaths;
+    for (uint32_t s = 0; s < h.num_stages; ++s) {
+        char name[64];
+        std::snprintf(name, sizeof name, "/plan.rank%06u.bin", base + s * stride);
+        paths.push_back(dir + name);
+        if (FILE* f = std::fopen(paths.back().c_str(), "rb")) std::fclose(f);
+        else {
+            std::fprintf(stderr, "stage %u of the pipeline needs %s: compile the plans of all stages (plan_compiler --all, or --rank %u)\n", s,
+                         paths.back().c_str(), base + s * stride);
+            return 1;
+        }
+    }
+    for (const std::string& q : paths) cpaths.push_back(q.c_str());
+    cai_pipeline_stats_t st;
+    char err[512] = "";
+    const int rc = cai_pipeline_replay(cpaths.data(), h.num_stages, topology_path, backend, std::getenv("CAI_CALIBRATION"), trace, &st, err, sizeof err);
+    if (rc != 0) { std::fprintf(stderr, "pipeline replay failed (%s): %s\n", cai_status_str(rc), err); return 1; }
+    std::printf("stage |   rank | finish      | compute_hi busy | idle\n");
+    std::printf("------+--------+-------------+-----------------+-------\n");
+    for (uint32_t s = 0; s < st.n_stages; ++s)
+        std::printf("%5u | %6u | %8.2f ms | %12.2f ms | %4.1f%%\n", s, base + s * stride, st.stage_finish_s[s] * 1e3, st.stage_busy_hi_s[s] * 1e3,
+                    st.stage_idle_hi[s] * 100.0);
+    std::printf("\nstep %.2f ms | %.3e tokens/s | MFU %.1f%% | busiest stage idle %.1f%% of the step; pipeline bubble by formula %.1f%%\n",
+                st.step_time_s * 1e3, st.tokens_per_s, st.mfu * 100.0, st.bubble_replayed * 100.0, st.bubble_formula * 100.0);
+    if (trace) std::printf("wrote the timeline of all stages to %s\n", trace);
+    return 0;
+}
 
 int main(int argc, char** argv) {
     if (argc < 3) {
-        std::fprintf(stderr, "usage: %s <plan.bin> <topology.bin> [--steps N] [--ckpt PATH] [--ckpt-every K] [--trace CSV] [--fail-at STEP] [--device | --backend analytic|calibrated|device|auto] [--calibration FILE]\n", argv[0]);
+        std::fprintf(stderr, "usage: %s <plan.bin> <topology.bin> [--steps N] [--ckpt PATH] [--ckpt-every K] [--trace CSV] [--fail-at STEP] [--device | --backend analytic|calibrated|device|auto] [--calibration FILE] [--pipeline]\n", argv[0]);
         return 2;
     }
     cai_init_desc_t desc;
@@ -25,6 +73,7 @@ int main(int argc, char** argv) {
     desc.max_steps = 10;
     const char* trace = nullptr;
     long fail_at = -1;  // host-side fault injection: report a backend error at this step
+    bool pipeline = false;
     if (const char* r = std::getenv("RANK")) desc.global_rank = std::strtoul(r, nullptr, 10);
     if (const char* r = std::getenv("LOCAL_RANK")) desc.local_rank = std::strtoul(r, nullptr, 10);
     for (int i = 3; i < argc; ++i) {
@@ -34,6 +83,7 @@ int main(int argc, char** argv) {
         else if (!std::strcmp(argv[i], "--trace") && i + 1 < argc) trace = argv[++i];
         else if (!std::strcmp(argv[i], "--fail-at") && i + 1 < argc) fail_at = std::strtol(argv[++i], nullptr, 10);
         else if (!std::strcmp(argv[i], "--device")) desc.backend = CAI_BACKEND_DEVICE;
+        else if (!std::strcmp(argv[i], "--pipeline")) pipeline = true;
         else if (!std::strcmp(argv[i], "--backend") && i + 1 < argc) {
             const char* b = argv[++i];
             desc.backend = !std::strcmp(b, "device") ? CAI_BACKEND_DEVICE : !std::strcmp(b, "auto") ? CAI_BACKEND_AUTO
@@ -45,6 +95,7 @@ int main(int argc, char** argv) {
         }
         else { std::fprintf(stderr, "unknown arg: %s\n", argv[i]); return 2; }
     }
+    if (pipeline) return run_pipeline(argv[1], argv[2], desc.backend, trace);
     cai_context_t* ctx = nullptr;
     int rc = cai_init(&ctx, &desc);
     if (rc != 0) { std::fprintf(stderr, "init failed: %s\n", cai_status_str(rc)); return 1; }
