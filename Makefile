@@ -29,6 +29,9 @@ demo: host
 	./bin/plan_compiler configs/full220k.cfg out/full
 	@echo "== replay stage 0 of the 220k plan (analytic backend) =="
 	./bin/trainer out/full/plan.rank000000.bin out/full/topology.bin --steps 5
+	@echo "== all three stages of small.cfg replayed together (no bubble formula) =="
+	./bin/plan_compiler configs/small.cfg out/small --all --quiet > /dev/null
+	./bin/trainer out/small/plan.rank000000.bin out/small/topology.bin --pipeline
 	@echo "== train the fp64 oracle on CPU =="
 	./bin/reftrain --steps 400
 	@echo "== executable plan for 8 B200s: compile, verify, predict =="

@@ -3,6 +3,7 @@
 #include <sstream>
 
 #include "cai.h"
+#include "backend.h"
 #include "plan.h"
 
 using namespace cai;
@@ -235,6 +236,24 @@ int cai_verify(const char* config_path, int check_exec, char* report, size_t rep
                 verify_peer_reuse(p, &rep);
             }
             verify_pipeline_pairing(plans, &rep);
+            if (plans.size() > 1) {
+                // every send must be able to meet its receive once streams, events and the rendezvous of NCCL
+                // point-to-point calls are taken together: replay all stages as one graph and look for a cycle
+                std::vector<const Plan*> ptrs;
+                for (const Plan& p : plans) ptrs.push_back(&p);
+                Backend* be = backend_analytic_create();
+                PipelineResult pr;
+                std::string why;
+                const int rc = replay_pipeline(ptrs, cfg.topo, be, &pr, &why);
+                be->destroy(be);
+                if (rc == OK) {
+                    std::snprintf(line, sizeof line, "  [ok]   the %zu stages replay together without a deadlock", plans.size());
+                    rep.lines.push_back(line);
+                } else {
+                    rep.lines.push_back("  [FAIL] joint replay of the stages: " + why);
+                    rep.problems++;
+                }
+            }
         }
         dump();
     }
