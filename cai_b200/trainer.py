@@ -72,6 +72,27 @@ def write_trace_csv(path, recs):
                     f"{r.end_s * 1e6:.4f},{(r.end_s - r.start_s) * 1e6:.4f},{r.bytes},{r.flops}\n")
 
 
+def predicted_step_time(eng, rank):
+    """Step time the calibrated pricing backend predicts for the running plan. A pipelined job is replayed with all
+    of its stages together (the sibling stages' plans are compiled from the configuration when it is known); otherwise,
+    and for a single stage, this rank's plan alone."""
+    h = eng.hdr
+    if h.num_stages > 1 and eng.config_text:
+        import tempfile
+        stride = h.tp * max(1, h.cp)
+        base = rank - h.pipeline_stage * stride
+        with tempfile.TemporaryDirectory(prefix="cai_predict_") as tmp:
+            for s in range(h.num_stages):
+                planlib.compile_plans(eng.config_text, tmp, ranks=(base + s * stride, base + s * stride + 1), version=2, text=True)
+            paths = [Path(tmp) / f"plan.rank{base + s * stride:06d}.bin" for s in range(h.num_stages)]
+            return planlib.pipeline_replay(paths, Path(tmp) / "topology.bin", backend="calibrated")["step_time_s"]
+    sim = planlib.Simulator(eng.plan.path, eng.topology_path, rank=rank, backend="calibrated")
+    try:
+        return sim.step().step_time_s
+    finally:
+        sim.close()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="cai_b200.trainer")
     ap.add_argument("plan", nargs="?")
@@ -280,9 +301,7 @@ def main(argv=None):
         if n:
             # what the calibrated pricing backend predicts for this rank's plan, next to what was measured
             try:
-                sim = planlib.Simulator(eng.plan.path, eng.topology_path, rank=rank, backend="calibrated")
-                predicted = sim.step().step_time_s
-                sim.close()
+                predicted = predicted_step_time(eng, rank)
                 measured = h.global_tokens_per_step / (sum_tps / n)
                 print(f"calibrated model: {predicted * 1e3:.2f} ms/step predicted, {measured * 1e3:.2f} measured "
                       f"(measured / predicted = {measured / predicted:.2f})")

@@ -99,3 +99,18 @@ def test_trainer_tool_finds_the_sibling_stages_and_writes_one_timeline(tmp_path)
     paths[0].unlink()
     r = subprocess.run([BIN / "trainer", paths[1], topo, "--pipeline"], capture_output=True, text=True, timeout=120)
     assert r.returncode == 1 and "plan.rank000000.bin" in r.stderr
+
+
+def test_device_trainer_predicts_a_pipelined_job_with_all_stages(tmp_path):
+    """The prediction the device trainer prints beside its measurement: joint replay when the job is pipelined and
+    the configuration is known, this rank's plan alone otherwise."""
+    import types
+    from cai_b200 import plan, trainer
+    text = (ROOT / "configs" / "tiny_mp.cfg").read_text() + "\ntp = 2\npp = 2\ngpus_per_rack = 4\ngpus_per_tray = 4\n"
+    plan.compile_plans(text, tmp_path, ranks=(3, 4), version=2, text=True)      # rank 3: stage 1, tp rank 1
+    pf = plan.PlanFile(tmp_path / "plan.rank000003.bin")
+    eng = types.SimpleNamespace(hdr=pf.hdr, config_text=text, plan=pf, topology_path=str(tmp_path / "topology.bin"))
+    joint = trainer.predicted_step_time(eng, 3)
+    eng.config_text = None
+    alone = trainer.predicted_step_time(eng, 3)
+    assert 0 < joint < alone * 1.2 and joint != alone
