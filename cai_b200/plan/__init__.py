@@ -175,7 +175,8 @@ def fnv1a(data: bytes, seed: int = 0) -> int:
 class PipelineStats(ctypes.Structure):
     _fields_ = [("n_stages", c_uint32), ("reserved", c_uint32), ("step_time_s", c_double), ("bubble_formula", c_double),
                 ("bubble_replayed", c_double), ("tokens_per_s", c_double), ("mfu", c_double),
-                ("stage_finish_s", c_double * 64), ("stage_busy_hi_s", c_double * 64), ("stage_idle_hi", c_double * 64)]
+                ("stage_finish_s", c_double * 64), ("stage_busy_hi_s", c_double * 64), ("stage_idle_hi", c_double * 64),
+                ("stage_sm_busy_s", c_double * 64)]
 
 
 def pipeline_replay(plan_paths, topology_path, backend="calibrated", calibration=None, trace=None) -> dict:
@@ -198,7 +199,8 @@ def pipeline_replay(plan_paths, topology_path, backend="calibrated", calibration
     n = st.n_stages
     return {"step_time_s": st.step_time_s, "bubble_formula": st.bubble_formula, "bubble_replayed": st.bubble_replayed,
             "tokens_per_s": st.tokens_per_s, "mfu": st.mfu, "stage_finish_s": list(st.stage_finish_s[:n]),
-            "stage_busy_hi_s": list(st.stage_busy_hi_s[:n]), "stage_idle_hi": list(st.stage_idle_hi[:n])}
+            "stage_busy_hi_s": list(st.stage_busy_hi_s[:n]), "stage_idle_hi": list(st.stage_idle_hi[:n]),
+            "stage_sm_busy_s": list(st.stage_sm_busy_s[:n])}
 
 
 LOG_LEVELS = {"error": 0, "warn": 1, "info": 2, "debug": 3}

@@ -51,7 +51,7 @@ struct Backend {
 // Joint replay of all stages of one pipeline under a pricing backend (pipeline_sim.cc).
 struct PipelineResult {
     struct Stage {
-        double finish_s = 0.0;               // when the stage's last op ends
+        double finish_s = 0.0;               // when the stage's last op ends on the longest path (streams overlapping freely)
         double stream_busy[ST_COUNT] = {};   // summed op durations per logical stream
         double sm_work_s = 0.0;              // sum of duration x share of the SMs (backends that know the share)
         double idle_hi = 0.0;                // share of the step compute_hi has no op in flight

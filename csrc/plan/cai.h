@@ -86,9 +86,10 @@ typedef struct {
     double bubble_replayed;      /* share of the step the busiest stage's main compute stream stands still */
     double tokens_per_s;
     double mfu;
-    double stage_finish_s[CAI_MAX_PIPELINE_STAGES];
+    double stage_finish_s[CAI_MAX_PIPELINE_STAGES];  /* end of the stage's longest path, streams overlapping freely */
     double stage_busy_hi_s[CAI_MAX_PIPELINE_STAGES];
     double stage_idle_hi[CAI_MAX_PIPELINE_STAGES];
+    double stage_sm_busy_s[CAI_MAX_PIPELINE_STAGES]; /* sum of duration x share of the SMs over all streams (0: the backend does not say) */
 } cai_pipeline_stats_t;
 
 const char* cai_status_str(int status);

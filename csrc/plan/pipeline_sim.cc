@@ -228,8 +228,9 @@ int replay_pipeline(const std::vector<const Plan*>& stages, const Topology& topo
         PipelineResult::Stage& st = out->stages[s];
         for (int q = 0; q < ST_COUNT; ++q)
             if (tails[s][q] >= 0) st.finish_s = std::max(st.finish_s, g.nodes[tails[s][q]].start + g.nodes[tails[s][q]].dur);
-        st.finish_s = std::max(st.finish_s, st.sm_work_s);   // streams share the SMs (backends that know the share)
-        out->step_time_s = std::max(out->step_time_s, st.finish_s);
+        // streams overlap only as far as their kernels leave SMs to each other (backends that know the share): a stage
+        // cannot finish before the SM time of all its kernels has been served
+        out->step_time_s = std::max(out->step_time_s, std::max(st.finish_s, st.sm_work_s));
     }
     for (PipelineResult::Stage& st : out->stages)
         st.idle_hi = out->step_time_s > 0 ? 1.0 - std::min(1.0, st.stream_busy[ST_COMPUTE_HI] / out->step_time_s) : 0.0;
@@ -295,6 +296,7 @@ extern "C" int cai_pipeline_replay(const char* const* plan_paths, uint32_t n_sta
         out->stage_finish_s[s] = r.stages[s].finish_s;
         out->stage_busy_hi_s[s] = r.stages[s].stream_busy[ST_COMPUTE_HI];
         out->stage_idle_hi[s] = r.stages[s].idle_hi;
+        out->stage_sm_busy_s[s] = r.stages[s].sm_work_s;
         busiest = std::max(busiest, r.stages[s].stream_busy[ST_COMPUTE_HI]);
     }
     // share of the step the busiest stage's main compute stream stands still: what fill, drain and transfers cost

@@ -50,11 +50,15 @@ static int run_pipeline(const char* plan_path, const char* topology_path, uint32
     char err[512] = "";
     const int rc = cai_pipeline_replay(cpaths.data(), h.num_stages, topology_path, backend, std::getenv("CAI_CALIBRATION"), trace, &st, err, sizeof err);
     if (rc != 0) { std::fprintf(stderr, "pipeline replay failed (%s): %s\n", cai_status_str(rc), err); return 1; }
-    std::printf("stage |   rank | finish      | compute_hi busy | idle\n");
-    std::printf("------+--------+-------------+-----------------+-------\n");
-    for (uint32_t s = 0; s < st.n_stages; ++s)
-        std::printf("%5u | %6u | %8.2f ms | %12.2f ms | %4.1f%%\n", s, base + s * stride, st.stage_finish_s[s] * 1e3, st.stage_busy_hi_s[s] * 1e3,
+    const bool sm = st.stage_sm_busy_s[0] > 0;   // the calibrated backend knows what share of the SMs a kernel keeps busy
+    std::printf("stage |   rank | finish      | compute_hi busy | idle %s\n", sm ? " | SMs busy" : "");
+    std::printf("------+--------+-------------+-----------------+-------%s\n", sm ? "+---------" : "");
+    for (uint32_t s = 0; s < st.n_stages; ++s) {
+        std::printf("%5u | %6u | %8.2f ms | %12.2f ms | %4.1f%%", s, base + s * stride, st.stage_finish_s[s] * 1e3, st.stage_busy_hi_s[s] * 1e3,
                     st.stage_idle_hi[s] * 100.0);
+        if (sm) std::printf(" | %6.1f%%", st.step_time_s > 0 ? st.stage_sm_busy_s[s] / st.step_time_s * 100.0 : 0.0);
+        std::printf("\n");
+    }
     std::printf("\nstep %.2f ms | %.3e tokens/s | MFU %.1f%% | busiest stage idle %.1f%% of the step; pipeline bubble by formula %.1f%%\n",
                 st.step_time_s * 1e3, st.tokens_per_s, st.mfu * 100.0, st.bubble_replayed * 100.0, st.bubble_formula * 100.0);
     if (trace) std::printf("wrote the timeline of all stages to %s\n", trace);

@@ -34,7 +34,10 @@ def test_config_5_is_predicted_within_five_percent_of_the_measured_step(tmp_path
     paths, topo, d = _stage_plans(tmp_path, bench.config_text(8, "fused", "pp2tp4"), 2)
     r = plan.pipeline_replay(paths, topo, backend="calibrated")
     assert abs(r["step_time_s"] * 1e3 - 2446.0) <= 0.05 * 2446.0, r
-    assert len(r["stage_finish_s"]) == 2 and max(r["stage_finish_s"]) == pytest.approx(r["step_time_s"])
+    # the step is the longer of the longest dependency path and the SM time of the busiest stage; here the stages are
+    # SM-bound (weight-gradient GEMMs on the second compute stream fill the gaps of fill and drain)
+    assert len(r["stage_finish_s"]) == 2 and max(r["stage_finish_s"]) < r["step_time_s"]
+    assert max(r["stage_sm_busy_s"]) == pytest.approx(r["step_time_s"])
     assert all(0.0 <= x < 0.5 for x in r["stage_idle_hi"])
     assert r["bubble_formula"] == pytest.approx(1.0 / 17.0)
 
