@@ -401,6 +401,9 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
                                        "(got tp=%u%s); use bf16 there instead of a silent change of precision", d.tp, moe ? ", MoE" : "");
     const bool fp8 = m.param_dtype == DT_FP8_E4M3;
     if (d.cp != 1) return failf(err, ERR_INVALID, "context parallelism (cp>1) has no executable schedule");
+    if (d.vpp > 1)
+        return failf(err, ERR_INVALID, "vpp = %u: there is no interleaved executable schedule (the key changes the bubble formula of "
+                     "cost-only plans only, as in the reference); use vpp = 1", d.vpp);
     if (m.head_dim != 128) return failf(err, ERR_INVALID, "executable plans need head_dim = 128 (got %u)", m.head_dim);
     if (m.num_heads % d.tp || m.num_kv_heads % d.tp || m.ffn_hidden % d.tp || m.vocab_size % d.tp)
         return failf(err, ERR_INVALID, "tp=%u must divide heads, kv heads, ffn and vocab", d.tp);

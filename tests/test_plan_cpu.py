@@ -218,7 +218,8 @@ def test_plan_variants_compile_and_verify(tmp_path):
     assert not [op for op in off.ops if op.exec and int(off.exec[op.exec - 1].kernel) == plan.K_GEMM and op.stream_id == 1]
     # refused combinations
     for bad in ("zero_stage = 3\ncomm = baseline\n", "zero_stage = 3\ncomm = fused\ntp = 2\n",
-                "param_dtype = fp8e4m3\ntp = 2\n"):      # fp8 under tensor parallelism: an error, not a silent bf16 run
+                "param_dtype = fp8e4m3\ntp = 2\n",       # fp8 under tensor parallelism: an error, not a silent bf16 run
+                "pp = 2\nvpp = 2\n"):                    # interleaving: an error, not a silent plain 1F1B schedule
         with pytest.raises(plan.PlanError):   # 4 GPUs: dp = 4, or tp = 2 x dp = 2
             plan.compile_plans((ROOT / "configs" / "tiny_mp.cfg").read_text() + "\ngpus_per_rack = 4\ngpus_per_tray = 4\n" + bad,
                                tmp_path / "bad", version=2, text=True)
