@@ -70,7 +70,7 @@ int cai_describe(const char* text, char* out, size_t out_len, char* err, size_t 
     if (int rc = decompose(cfg, &d, &e); rc != OK) { put_err(err, errlen, e); return rc; }
     std::ostringstream o;
     const ModelSpec& m = cfg.model;
-    o << "world_size=" << cfg.topo.world_size << "\ntp=" << d.tp << "\npp=" << d.pp << "\ndp=" << d.dp << "\nep=" << d.ep
+    o << "world_size=" << cfg.topo.world_size << "\nspare_gpus=" << cfg.topo.spare_gpus << "\ntp=" << d.tp << "\npp=" << d.pp << "\ndp=" << d.dp << "\nep=" << d.ep
       << "\ncp=" << d.cp << "\nvpp=" << d.vpp << "\nreplica=" << d.model_replica_gpus << "\nglobal_batch=" << d.global_batch
       << "\nglobal_tokens=" << d.global_tokens << "\nnum_microbatches=" << d.num_microbatches
       << "\nlayers_per_stage=" << d.layers_per_stage << "\nbubble_ratio=" << d.bubble_ratio
