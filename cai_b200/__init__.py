@@ -4,6 +4,7 @@ The public names are loaded on first use, so ``import cai_b200`` stays cheap and
 
     Engine, synthetic_batch          device executor of a compiled plan (needs a GPU)
     PlanFile, Simulator              plan files and their GPU-free replay under a pricing backend
+    pipeline_replay                  all stages of a pipeline replayed together (no closed bubble formula)
     compile_plans, describe          the offline compiler and the decomposition report as a dict
     TokenBatches, lr_at, reshard     data, learning-rate schedule, checkpoint re-layout
 """
@@ -12,7 +13,7 @@ __version__ = "0.2.0"
 _PUBLIC = {
     "Engine": "cai_b200.runtime.engine", "synthetic_batch": "cai_b200.runtime.engine",
     "PlanFile": "cai_b200.plan", "Simulator": "cai_b200.plan", "compile_plans": "cai_b200.plan", "describe": "cai_b200.plan",
-    "PlanError": "cai_b200.plan",
+    "PlanError": "cai_b200.plan", "pipeline_replay": "cai_b200.plan",
     "TokenBatches": "cai_b200.utils.data", "lr_at": "cai_b200.utils.schedule", "reshard": "cai_b200.utils.reshard",
 }
 __all__ = sorted(_PUBLIC) + ["__version__"]
