@@ -1,0 +1,567 @@
+"""A reference interpreter of executable plans on the CPU: a test oracle for the schedule, not a backend.
+
+The plan compiler turns a configuration into one op table per rank: kernel records over tensors of a static arena, in
+issue order over six streams, with the collectives and the pipeline hand-offs of the layout. The GPU executor runs those
+tables with the sm_100a kernels; this module runs the same tables with plain PyTorch arithmetic on the host, every rank
+of the job inside one process, so that what a layout computes can be checked without a GPU: a job of tp x pp x dp ranks
+must train exactly like the one-device model (``reference_torch.forward_loss`` + AdamW), because every collective,
+every hand-off and every shard boundary in the tables is executed for real.
+
+What is interpreted: the dense decoder under tensor (fused or NCCL-only plans), pipeline and data parallelism with
+sharded optimizer state (the fused reduce-scatter + AdamW kernel in its whole-space and its per-layer bucket form) or
+with parameters and gradients sharded too (ZeRO-3: parameter gathers, staged gradients, owners' accumulators). Each record does what the kernel it names is specified to do (``csrc/kernels/cai_kernels.h``,
+``csrc/comm/fused.h``): tensors keep their storage types (bf16 activations and weights, fp32 gradients and optimizer
+state), arithmetic inside a record is fp32. Mixture-of-experts records and the e4m3 path are not interpreted and raise
+``NotImplementedError``.
+
+Ranks run as coroutines in program order. That order is a legal serialisation of a rank's streams (a wait never
+precedes its record in a table); a collective runs when every member of its group has reached it (members of a group
+issue identical sequences); a pipeline send deposits its message and continues, a receive blocks until the message
+is there. A job whose ranks cannot all finish raises instead of hanging.
+"""
+from __future__ import annotations
+
+import math
+import tempfile
+from collections import defaultdict, deque
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from .. import plan as planlib
+from ..utils import reshard
+
+K = {name: i for i, name in enumerate(planlib.KERNEL_NAMES)}
+_TORCH = {0: torch.float32, 1: torch.bfloat16, 2: torch.float16, 5: torch.int32, 6: torch.uint8}
+ST_IO = 5
+
+
+class _Rank:
+    def __init__(self, pf: planlib.PlanFile, rank: int):
+        self.pf, self.rank = pf, rank
+        self.rl = reshard.RankLayout(pf, rank)
+        self.arena = torch.zeros(int(pf.hdr.arena_bytes) + 16, dtype=torch.uint8)
+        self.named = pf.named_dict()
+        self._typed = {}
+
+    def _base(self, dtype):
+        if dtype not in self._typed:
+            n = self.arena.numel() // torch.empty(0, dtype=dtype).element_size() * torch.empty(0, dtype=dtype).element_size()
+            self._typed[dtype] = self.arena[:n].view(dtype)
+        return self._typed[dtype]
+
+    def mat(self, tid, rows=None, cols=None):
+        """Pitched 2-D view of a tensor; ``rows`` / ``cols`` override the table's extent (a record names its own)."""
+        t = self.pf.tensors[tid]
+        r, c, ld = self.pf.shape(tid)
+        dt = _TORCH[t.dtype]
+        es = planlib.DTYPE_SIZE[t.dtype]
+        rows, cols = r if rows is None else rows, c if cols is None else cols
+        ld = ld or cols
+        need = ((rows - 1) * ld + cols) * es if rows and cols else 0
+        if need > t.nbytes:
+            raise ValueError(f"tensor {tid}: a record addresses {need} bytes of {t.nbytes}")
+        return torch.as_strided(self._base(dt), (rows, cols), (ld, 1), t.offset // es)
+
+    def flat(self, tid, count=None):
+        t = self.pf.tensors[tid]
+        es = planlib.DTYPE_SIZE[t.dtype]
+        n = t.nbytes // es if count is None else count
+        if n * es > t.nbytes:
+            raise ValueError(f"tensor {tid}: a record addresses {n * es} bytes of {t.nbytes}")
+        return self._base(_TORCH[t.dtype])[t.offset // es:t.offset // es + n]
+
+    def at(self, byte_offset, dtype, count):
+        es = torch.empty(0, dtype=dtype).element_size()
+        return self._base(dtype)[byte_offset // es:byte_offset // es + count]
+
+    def offset(self, tid):
+        return int(self.pf.tensors[tid].offset)
+
+    def named_flat(self, name):
+        return self.flat(self.named[name].tensor)
+
+
+def _rope(x, seq, theta, inverse):
+    """x [T, heads, hd] fp32, position of row t is t % seq; rotate-half convention (``reference_torch.rope``)."""
+    T, _, hd = x.shape
+    half = hd // 2
+    pos = (torch.arange(T) % seq).to(torch.float32)
+    inv = theta ** (-torch.arange(half, dtype=torch.float32) / half)
+    ang = pos[:, None] * inv[None, :]
+    c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    if inverse:
+        s = -s
+    x1, x2 = x[..., :half], x[..., half:]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1)
+
+
+def _attention(q, k, v, B, S, scale):
+    """q [B*S, nh, hd], k / v [B*S, nkv, hd] fp32 -> out [B*S, nh*hd], causal, grouped-query."""
+    nh, nkv, hd = q.shape[1], k.shape[1], q.shape[2]
+    qh = q.view(B, S, nh, hd).transpose(1, 2)
+    kh = k.view(B, S, nkv, hd).transpose(1, 2).repeat_interleave(nh // nkv, 1)
+    vh = v.view(B, S, nkv, hd).transpose(1, 2).repeat_interleave(nh // nkv, 1)
+    s = (qh @ kh.transpose(-1, -2)) * scale
+    s = s.masked_fill(~torch.ones(S, S, dtype=torch.bool).tril(), float("-inf"))
+    lse = torch.logsumexp(s, -1)                                   # [B, nh, S]
+    out = torch.softmax(s, -1) @ vh
+    return out.transpose(1, 2).reshape(B * S, nh * hd), lse
+
+
+class PlanInterpreter:
+    """All ranks of one job, interpreted on the host. ``config_text``: the job's configuration (executable layout)."""
+
+    def __init__(self, config_text: str):
+        self.config_text = config_text
+        d = planlib.describe(config_text)
+        self.world = int(d["world_size"])
+        with tempfile.TemporaryDirectory(prefix="cai_interp_") as tmp:
+            planlib.compile_plans(config_text, tmp, ranks=(0, self.world), version=2, text=True)
+            self.ranks = [_Rank(planlib.PlanFile(Path(tmp) / f"plan.rank{r:06d}.bin"), r) for r in range(self.world)]
+        pf = self.ranks[0].pf
+        self.train, self.model, self.hdr = pf.train, pf.model, pf.hdr
+        if self.model.is_moe or self.model.param_dtype != 1:
+            raise NotImplementedError("mixture-of-experts and e4m3 plans are not interpreted")
+        self.step_count = 0
+        self.lr = float(self.train.lr)
+        self._members = {}
+        self.rows_per_replica = int(self.hdr.num_microbatches * self.hdr.microbatch)
+
+    # ------------------------------------------------------------------ state in, state out
+    def layouts(self):
+        return [r.rl for r in self.ranks]
+
+    def load_state(self, state, step=0):
+        """``state[name][key]``: global fp32 ``master`` / ``m`` / ``v`` tensor of every parameter (the form
+        ``cai_b200.utils.reshard`` works on). Every rank receives what a checkpoint of its layout would hold."""
+        for r in self.ranks:
+            sec = reshard.rank_sections(r.rl, state, step)
+            for key, name in (("master", "@flat_master"), ("m", "@flat_m"), ("v", "@flat_v")):
+                dst = r.named_flat(name)
+                dst[:len(sec[key])].copy_(torch.from_numpy(sec[key]))
+            p = r.named_flat("@flat_param")
+            p[:len(sec["param"])].copy_(torch.from_numpy(sec["param"]).view(torch.bfloat16))
+        self.step_count = step
+
+    def state(self):
+        """The global state back out of the ranks' buffers (same form as ``load_state`` takes)."""
+        def read(rank):
+            r = self.ranks[rank]
+            out = {"plan_hash": r.rl.plan_hash, "step": self.step_count}
+            for key, name in (("master", "@flat_master"), ("m", "@flat_m"), ("v", "@flat_v")):
+                out[key] = r.named_flat(name).numpy().copy()
+            return out
+        return reshard.gather_global(self.layouts(), read)[0]
+
+    def parameter(self, rank, name):
+        """One rank's bf16 shard of a parameter as fp32 (what its kernels read)."""
+        r = self.ranks[rank]
+        nt = r.named[name]
+        return r.mat(nt.tensor).float()
+
+    # ------------------------------------------------------------------ one optimizer step
+    def step(self, tokens, targets, lr=None) -> float:
+        """``tokens`` / ``targets``: int tensors ``[global sequences, seq]``; data-parallel replica ``d`` takes rows
+        ``[d * rows, (d + 1) * rows)``. Returns the mean loss over the global batch."""
+        self.step_count += 1
+        t = self.step_count
+        b1, b2 = float(self.train.beta1), float(self.train.beta2)
+        self.hyper = (float(self.lr if lr is None else lr), b1, b2, float(self.train.adam_eps), float(self.train.weight_decay),
+                      1.0 - b1 ** t, 1.0 - b2 ** t)
+        rows = self.rows_per_replica
+        for r in self.ranks:
+            d = r.rl.dp_id
+            for name, src in (("@tokens", tokens), ("@targets", targets)):
+                dst = r.named_flat(name)
+                part = src[d * rows:(d + 1) * rows].reshape(-1).to(torch.int32)
+                dst[:part.numel()].copy_(part)
+        self._run()
+        # the last stage accumulates the loss; the plan all-reduces it over the tensor- and data-parallel groups
+        last = next(r for r in self.ranks if r.rl.stage == r.rl.pp - 1)
+        return float(last.named_flat("@loss")[0].item())
+
+    # ------------------------------------------------------------------ scheduler
+    def members(self, kind, rank):
+        key = (kind, rank)
+        if key not in self._members:
+            self._members[key] = planlib.group_members(self.config_text, kind, rank)
+        return self._members[key]
+
+    def _run(self):
+        self.mail = defaultdict(deque)          # (src rank, dst rank, channel) -> messages
+        self.pending = {}                       # (group members, call index) -> {rank: request}
+        self.calls = defaultdict(int)           # (rank, group members) -> collectives issued
+        gens = {r.rank: self._program(r) for r in self.ranks}
+        blocked = {}
+        while gens:
+            progress = False
+            for rank in list(gens):
+                want = blocked.get(rank)
+                if want is not None and not self._ready(want):
+                    continue
+                try:
+                    blocked[rank] = gens[rank].send(None) if want is None else gens[rank].send(True)
+                    progress = True
+                except StopIteration:
+                    del gens[rank]
+                    blocked.pop(rank, None)
+                    progress = True
+            if not progress:
+                waiting = {rk: w[:2] for rk, w in blocked.items()}
+                raise RuntimeError(f"the ranks wait for each other and none can continue: {waiting}")
+
+    def _ready(self, want):
+        what = want[0]
+        if what == "recv":
+            return bool(self.mail[want[1]])
+        if what == "coll":
+            return want[1] not in self.pending      # the last member to arrive ran it and removed the entry
+        return True
+
+    def _collective(self, r, kind, fn, payload):
+        """Generator helper: join call number n of the rank's group; the last member to arrive runs ``fn``."""
+        mem = tuple(self.members(kind, r.rank))
+        n = self.calls[(r.rank, mem)]
+        self.calls[(r.rank, mem)] += 1
+        key = (mem, n)
+        slot = self.pending.setdefault(key, {})
+        slot[r.rank] = payload
+        if len(slot) == len(mem):
+            fn([self.ranks[m] for m in mem], [slot[m] for m in mem])
+            del self.pending[key]
+            return None
+        return ("coll", key)
+
+    # ------------------------------------------------------------------ a rank's program
+    def _program(self, r: _Rank):
+        pf = r.pf
+        for op in pf.ops:
+            if op.kind in (planlib.OP_EVENT_RECORD, planlib.OP_EVENT_WAIT) or not op.exec:
+                continue
+            x = pf.exec[op.exec - 1]
+            k = int(x.kernel)
+            handler = self._local.get(k)
+            if handler is not None:
+                handler(self, r, x)
+                continue
+            if k == K["nccl_send"]:
+                peer = self.members(planlib.GROUP_PP, r.rank)[x.i[4]]
+                n = (int(x.i[1]) & 0xFFFFFFFF) << 32 | (int(x.i[0]) & 0xFFFFFFFF)
+                self.mail[(r.rank, peer, int(op.stream_id == ST_IO))].append(r.flat(x.t[0], n).clone())
+                continue
+            if k == K["nccl_recv"]:
+                peer = self.members(planlib.GROUP_PP, r.rank)[x.i[4]]
+                key = (peer, r.rank, int(op.stream_id == ST_IO))
+                if not self.mail[key]:
+                    yield ("recv", key)
+                n = (int(x.i[1]) & 0xFFFFFFFF) << 32 | (int(x.i[0]) & 0xFFFFFFFF)
+                r.flat(x.t[1], n).copy_(self.mail[key].popleft())
+                continue
+            coll = self._group_ops.get(k)
+            if coll is None:
+                raise NotImplementedError(f"kernel '{planlib.KERNEL_NAMES[k]}' is not interpreted")
+            kind = (planlib.GROUP_TP if k == K["cross_entropy_tp"] else planlib.GROUP_DP if k == K["fsdp_ag_gemm"] else int(x.i[3]))
+            wait = self._collective(r, kind, coll.__get__(self), x)
+            if wait is not None:
+                yield wait
+
+    # ------------------------------------------------------------------ records of one rank
+    def _gemm_core(self, r, A, B, M, N, Kd, ta, tb):
+        a = r.mat(A, Kd if ta else M, M if ta else Kd).float()
+        b = r.mat(B, Kd if tb else N, N if tb else Kd).float()
+        return (a.t() if ta else a) @ (b if tb else b.t())
+
+    def _epilogue(self, r, acc, x, C, R, epi, alpha=1.0):
+        M, N = acc.shape
+        acc = acc * alpha
+        if epi == 0:
+            r.mat(C, M, N).copy_(acc)
+        elif epi == 1:
+            r.mat(C, M, N).copy_(acc)
+        elif epi == 2:
+            c = r.mat(C, M, N)
+            c.copy_(c + acc)
+        elif epi == 3:
+            r.mat(C, M, N).copy_(acc + r.mat(R, M, N).float())
+        elif epi == 4:      # SwiGLU forward: C = [gate | up], R (an output) = silu(gate) * up
+            F = N // 2
+            r.mat(C, M, N).copy_(acc)
+            g, u = acc[:, :F], acc[:, F:]
+            r.mat(R, M, F).copy_(g * torch.sigmoid(g) * u)
+        elif epi == 5:      # SwiGLU backward: acc = dact [M, F]; R = saved [gate | up]; C = [dgate | dup]
+            F = N
+            gu = r.mat(R, M, 2 * F).float()
+            g, u = gu[:, :F], gu[:, F:]
+            sg = torch.sigmoid(g)
+            r.mat(C, M, 2 * F).copy_(torch.cat([acc * u * sg * (1 + g * (1 - sg)), acc * g * sg], 1))
+        else:
+            raise NotImplementedError(f"GEMM epilogue {epi}")
+
+    def _k_gemm(self, r, x):
+        if x.flags & 0x100 or x.t[4] >= 0:
+            raise NotImplementedError("segmented / grouped expert GEMMs are not interpreted")
+        ta, tb, epi = x.flags & 1, (x.flags >> 1) & 1, (x.flags >> 4) & 0xF
+        acc = self._gemm_core(r, x.t[0], x.t[1], x.i[0], x.i[1], x.i[2], ta, tb)
+        self._epilogue(r, acc, x, x.t[2], x.t[3], epi, float(x.f[0]))
+
+    def _k_embed_fwd(self, r, x):
+        T, H, lo, hi = x.i[0], x.i[1], x.i[2], x.i[3]
+        tok = r.flat(x.t[0], T).long()
+        E = r.mat(x.t[1], hi - lo, H)
+        own = (tok >= lo) & (tok < hi)
+        out = torch.zeros(T, H)
+        out[own] = E[tok[own] - lo].float()
+        r.mat(x.t[2], T, H).copy_(out)
+
+    def _k_embed_bwd(self, r, x):
+        T, H, lo, hi = x.i[0], x.i[1], x.i[2], x.i[3]
+        tok = r.flat(x.t[0], T).long()
+        own = (tok >= lo) & (tok < hi)
+        dE = r.mat(x.t[2], hi - lo, H)
+        dE.index_add_(0, tok[own] - lo, r.mat(x.t[1], T, H).float()[own])
+
+    def _k_rmsnorm_fwd(self, r, x):
+        rows, H = x.i[0], x.i[1]
+        v = r.mat(x.t[0], rows, H).float()
+        rstd = torch.rsqrt(v.pow(2).mean(-1) + float(x.f[0]))
+        r.mat(x.t[2], rows, H).copy_(v * rstd[:, None] * r.flat(x.t[1], H).float())
+        r.flat(x.t[3], rows).copy_(rstd)
+
+    def _k_rmsnorm_bwd(self, r, x):
+        rows, H, dx_acc, dg_acc = x.i[0], x.i[1], x.i[2], x.i[3]
+        v, g = r.mat(x.t[0], rows, H).float(), r.flat(x.t[1], H).float()
+        rstd, dy = r.flat(x.t[2], rows).float(), r.mat(x.t[3], rows, H).float()
+        xhat = v * rstd[:, None]
+        dyg = dy * g
+        dx = rstd[:, None] * (dyg - xhat * (dyg * xhat).mean(-1, keepdim=True))
+        dst = r.mat(x.t[4], rows, H)
+        dst.copy_(dst.float() + dx if dx_acc else dx)
+        dg = r.flat(x.t[5], H)
+        part = (dy * xhat).sum(0)
+        dg.copy_(dg + part if dg_acc else part)
+
+    def _k_rope(self, r, x):
+        T, seq, nh, nkv, hd = x.i[0], x.i[1], x.i[2], x.i[3], x.i[4]
+        qkv = r.mat(x.t[0], T, (nh + 2 * nkv) * hd)
+        qk = qkv[:, :(nh + nkv) * hd].float().view(T, nh + nkv, hd)
+        qkv[:, :(nh + nkv) * hd].copy_(_rope(qk, seq, float(self.train.rope_theta), bool(x.flags & 1)).reshape(T, -1))
+
+    def _split_qkv(self, r, tid, T, nh, nkv, hd):
+        qkv = r.mat(tid, T, (nh + 2 * nkv) * hd).float()
+        q, kk, v = qkv.split([nh * hd, nkv * hd, nkv * hd], 1)
+        return q.reshape(T, nh, hd), kk.reshape(T, nkv, hd), v.reshape(T, nkv, hd)
+
+    def _k_attn_fwd(self, r, x):
+        B, S, nh, nkv, hd = x.i[0], x.i[1], x.i[2], x.i[3], x.i[4]
+        q, kk, v = self._split_qkv(r, x.t[0], B * S, nh, nkv, hd)
+        out, lse = _attention(q, kk, v, B, S, float(x.f[0]))
+        r.mat(x.t[1], B * S, nh * hd).copy_(out)
+        r.flat(x.t[2], B * nh * S).copy_(lse.reshape(-1))
+
+    def _k_attn_bwd(self, r, x):
+        parts = int(x.flags) or 7
+        if not parts & 6:
+            return              # the row sums alone: an intermediate of the kernels, not needed here
+        B, S, nh, nkv, hd = x.i[0], x.i[1], x.i[2], x.i[3], x.i[4]
+        T = B * S
+        q, kk, v = (t.clone().requires_grad_(True) for t in self._split_qkv(r, x.t[0], T, nh, nkv, hd))
+        out, _ = _attention(q, kk, v, B, S, float(x.f[0]))
+        out.backward(r.mat(x.t[2], T, nh * hd).float())
+        dqkv = r.mat(x.t[5], T, (nh + 2 * nkv) * hd)
+        if parts & 4:
+            dqkv[:, :nh * hd].copy_(q.grad.reshape(T, -1))
+        if parts & 2:
+            dqkv[:, nh * hd:].copy_(torch.cat([kk.grad.reshape(T, -1), v.grad.reshape(T, -1)], 1))
+
+    def _k_swiglu_fwd(self, r, x):
+        T, F = x.i[0], x.i[1]
+        gu = r.mat(x.t[0], T, 2 * F).float()
+        g, u = gu[:, :F], gu[:, F:]
+        r.mat(x.t[1], T, F).copy_(g * torch.sigmoid(g) * u)
+
+    def _k_swiglu_bwd(self, r, x):
+        T, F = x.i[0], x.i[1]
+        gu, da = r.mat(x.t[0], T, 2 * F).float(), r.mat(x.t[1], T, F).float()
+        g, u = gu[:, :F], gu[:, F:]
+        sg = torch.sigmoid(g)
+        r.mat(x.t[2], T, 2 * F).copy_(torch.cat([da * u * sg * (1 + g * (1 - sg)), da * g * sg], 1))
+
+    def _k_cross_entropy(self, r, x):
+        rows, V = x.i[0], x.i[1]
+        lg = r.mat(x.t[0], rows, V)
+        tgt = r.flat(x.t[1], rows).long()
+        z = lg.float()
+        lse = torch.logsumexp(z, -1)
+        live = tgt >= 0
+        safe = tgt.clamp(min=0)
+        loss = (lse - z.gather(1, safe[:, None])[:, 0])[live].sum()
+        d = torch.softmax(z, -1)
+        d[torch.arange(rows), safe] -= 1.0
+        d[~live] = 0.0
+        lg.copy_(d * float(x.f[0]))
+        acc = r.flat(x.t[2], 1)
+        acc.copy_(acc + loss * float(x.f[1]))
+
+    def _k_adamw(self, r, x):
+        n = (int(x.i[1]) & 0xFFFFFFFF) << 32 | (int(x.i[0]) & 0xFFFFFFFF)
+        self._adamw(r.flat(x.t[0], n), r.flat(x.t[1], n), r.flat(x.t[2], n), r.flat(x.t[3], n).float() * float(x.f[0]),
+                    [r.flat(x.t[4], n)])
+
+    def _adamw(self, master, m, v, g, params):
+        lr, b1, b2, eps, wd, bc1, bc2 = self.hyper
+        m.copy_(b1 * m + (1 - b1) * g)
+        v.copy_(b2 * v + (1 - b2) * g * g)
+        master.copy_(master - lr * ((m / bc1) / ((v / bc2).sqrt() + eps) + wd * master))
+        for p in params:
+            p.copy_(master)
+
+    def _k_zero(self, r, x):
+        t = r.pf.tensors[x.t[0]]
+        r.arena[t.offset:t.offset + t.nbytes].zero_()
+
+    def _k_add(self, r, x):
+        n = x.i[0]
+        r.flat(x.t[2], n).copy_(r.flat(x.t[0], n).float() + r.flat(x.t[1], n).float())
+
+    # ------------------------------------------------------------------ records of a whole group
+    @staticmethod
+    def _count(x):
+        return (int(x.i[1]) & 0xFFFFFFFF) << 32 | (int(x.i[0]) & 0xFFFFFFFF)
+
+    def _g_all_reduce(self, ranks, xs):
+        n = self._count(xs[0])
+        total = sum(r.flat(x.t[0], n).float() for r, x in zip(ranks, xs))
+        for r, x in zip(ranks, xs):
+            r.flat(x.t[1], n).copy_(total)
+
+    def _g_reduce_scatter(self, ranks, xs):
+        n = self._count(xs[0])                          # elements every member receives
+        srcs = [r.flat(x.t[0], n * len(ranks)).float() for r, x in zip(ranks, xs)]
+        for i, (r, x) in enumerate(zip(ranks, xs)):
+            r.flat(x.t[1], n).copy_(sum(s[i * n:(i + 1) * n] for s in srcs))
+
+    def _g_all_gather(self, ranks, xs):
+        n = self._count(xs[0])                          # elements every member contributes
+        parts = [r.flat(x.t[0], n).clone() for r, x in zip(ranks, xs)]
+        for r, x in zip(ranks, xs):
+            dst = r.flat(x.t[1], n * len(ranks))
+            for i, p in enumerate(parts):
+                dst[i * n:(i + 1) * n].copy_(p)
+
+    def _g_cross_entropy_tp(self, ranks, xs):
+        rows, Vl = xs[0].i[0], xs[0].i[1]
+        z = [r.mat(x.t[0], rows, Vl).float() for r, x in zip(ranks, xs)]
+        full = torch.cat(z, 1)
+        lse = torch.logsumexp(full, -1)
+        for (r, x), zl in zip(zip(ranks, xs), z):
+            lo = x.i[2]
+            tgt = r.flat(x.t[1], rows).long()
+            live = tgt >= 0
+            mine = live & (tgt >= lo) & (tgt < lo + Vl)
+            d = torch.exp(zl - lse[:, None])
+            idx = torch.nonzero(mine)[:, 0]
+            d[idx, tgt[idx] - lo] -= 1.0
+            d[~live] = 0.0
+            loss = -zl[idx, tgt[idx] - lo].sum()
+            if x.i[4]:
+                loss = loss + lse[live].sum()
+            r.mat(x.t[0], rows, Vl).copy_(d * float(x.f[0]))
+            acc = r.flat(x.t[2], 1)
+            acc.copy_(acc + loss * float(x.f[1]))
+
+    def _g_ag_gemm(self, ranks, xs):
+        x0 = xs[0]
+        T, N, Kd = x0.i[0], x0.i[1], x0.i[2]
+        Tl = T // len(ranks)
+        blocks = [r.mat(x.t[0], Tl, Kd).clone() for r, x in zip(ranks, xs)]
+        for r, x in zip(ranks, xs):
+            full = r.mat(x.t[3], T, Kd)
+            for i, b in enumerate(blocks):
+                full[i * Tl:(i + 1) * Tl].copy_(b)
+            tb, epi = (x.flags >> 1) & 1, (x.flags >> 4) & 0xF
+            acc = self._gemm_core(r, x.t[3], x.t[1], T, N, Kd, 0, tb)
+            self._epilogue(r, acc, x, x.t[2], x.t[5], epi)
+
+    def _g_gemm_rs(self, ranks, xs):
+        x0 = xs[0]
+        T, N, Kd = x0.i[0], x0.i[1], x0.i[2]
+        Tl = T // len(ranks)
+        # partial products travel as bf16 (the staging buffers of the kernel), the owner sums them in fp32
+        partial = [self._gemm_core(r, x.t[0], x.t[1], T, N, Kd, 0, (x.flags >> 1) & 1).to(torch.bfloat16).float()
+                   for r, x in zip(ranks, xs)]
+        for i, (r, x) in enumerate(zip(ranks, xs)):
+            total = sum(p[i * Tl:(i + 1) * Tl] for p in partial)
+            if x.t[3] >= 0:
+                total = total + r.mat(x.t[3], Tl, N).float()
+            r.mat(x.t[2], Tl, N).copy_(total)
+
+    def _g_fsdp_gather(self, ranks, xs):
+        """ZeRO-3: the flat range [lo, hi) of the parameter space, whose member r keeps [r * n_shard, (r + 1) * n_shard),
+        lands in every member's staging buffer (fused into the GEMM that follows it on the device, or a kernel of its own)."""
+        x0 = xs[0]
+        lo, hi = (int(x0.i[0]) & 0xFFFFFFFF) << 9, (int(x0.i[1]) & 0xFFFFFFFF) << 9
+        n_shard = ranks[0].rl.n_shard
+        whole = torch.cat([r.flat(x.t[0])[:n_shard] for r, x in zip(ranks, xs)])
+        for r, x in zip(ranks, xs):
+            r.flat(x.t[1], hi - lo).copy_(whole[lo:hi])
+
+    def _g_rs_adamw(self, ranks, xs):
+        x0 = xs[0]
+        gscale = float(x0.f[0])
+        own_params, staged = bool(x0.flags & 1), bool(x0.flags & 4)      # ZeRO-3: parameters / gradients sharded too
+        acc_only, acc_first = bool(x0.flags & 8), bool(x0.flags & 16)
+        if x0.flags & 2:        # a bucket [lo, hi) of the flat space; the kernel indexes from the flat buffers
+            lo, hi = (int(x0.i[0]) & 0xFFFFFFFF) << 9, (int(x0.i[1]) & 0xFFFFFFFF) << 9
+            n_flat, n_shard = ranks[0].rl.n_rep, ranks[0].rl.n_shard
+            names = ("@flat_master", "@flat_m", "@flat_v", "@flat_grad", "@flat_param")
+            buf = [[r.named_flat(n) for n in names] for r in ranks]
+            if staged:          # one microbatch's gradients of the bucket, element i of the flat space at i - lo
+                for b, (r, x) in zip(buf, zip(ranks, xs)):
+                    b[3] = r.flat(x.t[3])
+        else:
+            n_flat = (int(x0.i[1]) & 0xFFFFFFFF) << 32 | (int(x0.i[0]) & 0xFFFFFFFF)
+            n_shard = int(x0.i[2]) & 0xFFFFFFFF
+            lo, hi = 0, n_flat
+            buf = [[r.flat(x.t[j]) for j in range(5)] for r, x in zip(ranks, xs)]
+        for i, (r, x) in enumerate(zip(ranks, xs)):
+            s_lo = i * n_shard
+            first, last = max(s_lo, lo), min(min(s_lo + n_shard, n_flat), hi)
+            if first >= last:
+                continue
+            g0 = lo if staged else 0
+            g = sum(b[3][first - g0:last - g0].float() for b in buf)
+            if staged and x.t[5] >= 0:      # running sum over the microbatches, kept by the owner
+                gacc = r.flat(x.t[5])[:last - first]
+                if not acc_first:
+                    g = g + gacc
+                if acc_only:
+                    gacc.copy_(g)
+                    continue
+            master, m, v = (buf[i][j][first - s_lo:last - s_lo] for j in range(3))
+            params = [buf[i][4][first - s_lo:last - s_lo]] if own_params else [b[4][first:last] for b in buf]
+            self._adamw(master, m, v, g * gscale, params)
+
+    _local = {K["gemm"]: _k_gemm, K["embed_fwd"]: _k_embed_fwd, K["embed_bwd"]: _k_embed_bwd, K["rmsnorm_fwd"]: _k_rmsnorm_fwd,
+              K["rmsnorm_bwd"]: _k_rmsnorm_bwd, K["rope"]: _k_rope, K["attn_fwd"]: _k_attn_fwd, K["attn_bwd"]: _k_attn_bwd,
+              K["swiglu_fwd"]: _k_swiglu_fwd, K["swiglu_bwd"]: _k_swiglu_bwd, K["cross_entropy"]: _k_cross_entropy,
+              K["adamw"]: _k_adamw, K["zero"]: _k_zero, K["add"]: _k_add}
+    _group_ops = {K["nccl_all_reduce"]: _g_all_reduce, K["nccl_reduce_scatter"]: _g_reduce_scatter,
+                  K["nccl_all_gather"]: _g_all_gather, K["cross_entropy_tp"]: _g_cross_entropy_tp, K["ag_gemm"]: _g_ag_gemm,
+                  K["gemm_rs"]: _g_gemm_rs, K["rs_adamw"]: _g_rs_adamw, K["fsdp_ag_gemm"]: _g_fsdp_gather}
+
+
+def random_state(interp: PlanInterpreter, seed=0, std=0.02):
+    """A global parameter state (master drawn N(0, std), gains 1, moments 0) shaped after the job's own tables."""
+    g = np.random.default_rng(seed)
+    state = {}
+    for rl in interp.layouts():
+        for name, _, rows, cols in rl.params:
+            if name in state:
+                continue
+            gshape, _ = rl.slice_of(name, rows, cols)
+            gain = name.split(".")[-1] in ("g1", "g2", "gf")
+            master = np.ones(gshape, dtype=np.float32) if gain else (g.standard_normal(gshape) * std).astype(np.float32)
+            state[name] = {"master": master, "m": np.zeros(gshape, dtype=np.float32), "v": np.zeros(gshape, dtype=np.float32)}
+    return state

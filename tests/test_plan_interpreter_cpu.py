@@ -1,0 +1,110 @@
+"""Executable plans interpreted on the host, every rank of a job in one process: whatever the layout, the job must
+train like the one-device fp32 model (same losses, same parameters after AdamW), because every collective, every
+pipeline hand-off and every shard boundary of the op tables is executed for real. No GPU involved."""
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _built():
+    from cai_b200 import _build, plan
+    _build.build_host()
+    plan.set_log_level("warn")
+
+
+def _train_both(text, steps=3, seed=1):
+    """Losses of the interpreted job and of the reference model over the same batches, and how far their fp32 master
+    parameters are apart at the end relative to how far they moved."""
+    from cai_b200 import plan
+    from cai_b200.models import reference_torch as ref
+    from cai_b200.models.plan_interpreter import PlanInterpreter, random_state
+    it = PlanInterpreter(text)
+    st = random_state(it, seed=seed)
+    it.load_state(st)
+    m, tr = it.model, it.train
+    master = {k: torch.tensor(v["master"]).clone() for k, v in st.items()}
+    start = {k: v.clone() for k, v in master.items()}
+    mom = {k: torch.zeros_like(v) for k, v in master.items()}
+    var = {k: torch.zeros_like(v) for k, v in master.items()}
+    G, S = int(plan.describe(text)["global_batch"]), int(m.seq_len)
+    gen = torch.Generator().manual_seed(5)
+    losses = []
+    for step in range(1, steps + 1):
+        tok = torch.randint(0, m.vocab_size, (G, S), generator=gen)
+        tgt = torch.randint(0, m.vocab_size, (G, S), generator=gen)
+        got = it.step(tok, tgt)
+        # the reference reads bf16 weights like the kernels do and keeps the fp32 master / moments
+        p = {k: v.to(torch.bfloat16).float().requires_grad_(True) for k, v in master.items()}
+        loss = ref.forward_loss(p, tok, tgt, layers=m.num_layers, heads=m.num_heads, kv_heads=m.num_kv_heads,
+                                head_dim=m.head_dim, seq=S, eps=tr.norm_eps, theta=tr.rope_theta)
+        loss.backward()
+        b1, b2 = tr.beta1, tr.beta2
+        for k in master:
+            g = p[k].grad
+            mom[k] = b1 * mom[k] + (1 - b1) * g
+            var[k] = b2 * var[k] + (1 - b2) * g * g
+            master[k] = master[k] - tr.lr * ((mom[k] / (1 - b1 ** step)) / ((var[k] / (1 - b2 ** step)).sqrt() + tr.adam_eps)
+                                             + tr.weight_decay * master[k])
+        losses.append((got, float(loss.detach())))
+    end = it.state()
+    drift = max(float((torch.tensor(end[k]["master"]) - master[k]).abs().mean() / ((master[k] - start[k]).abs().mean() + 1e-12))
+                for k in master)
+    return losses, drift
+
+
+def _cfg(base, world, keys):
+    return ((ROOT / "configs" / base).read_text() +
+            f"\ngpus_per_rack = {world}\ngpus_per_tray = {world}\ntrays_per_rack = 1\nnum_racks = 1\n{keys}\n")
+
+
+LAYOUTS = {
+    "one rank": (1, ""),
+    "one rank, recompute": (1, "recompute = 1"),
+    "one rank, SwiGLU kernels": (1, "fuse_swiglu = 0"),
+    "one rank, SwiGLU in both GEMMs": (1, "fuse_swiglu = 2"),
+    "tp2 fused": (2, "tp = 2\ncomm = fused"),
+    "tp2 fused, one microbatch per launch, serial wgrad": (2, "tp = 2\ncomm = fused\nmb_group = 1\nwgrad_overlap = 0"),
+    "tp2 NCCL-only": (2, "tp = 2\ncomm = baseline"),
+    "pp2": (2, "pp = 2"),
+    "dp2 fused": (2, "comm = fused"),
+    "dp2 fused, one bucket": (2, "comm = fused\ndp_buckets = 0"),
+    "dp2 NCCL-only": (2, "comm = baseline"),
+    "dp2 ZeRO-3": (2, "comm = fused\nzero_stage = 3"),
+    "dp2 ZeRO-3, full gradients": (2, "comm = fused\nzero_stage = 3\ndp_buckets = 0"),
+    "tp4 fused": (4, "tp = 4\ncomm = fused"),
+    "tp2 x pp2 fused": (4, "tp = 2\npp = 2\ncomm = fused"),
+    "tp2 x dp2 fused": (4, "tp = 2\ncomm = fused"),
+    "pp2 x dp2 fused": (4, "pp = 2\ncomm = fused"),
+    "dp4 ZeRO-3": (4, "comm = fused\nzero_stage = 3"),
+    "tp2 x pp2 x dp2 fused": (8, "tp = 2\npp = 2\ncomm = fused"),
+    "pp4 x dp2 NCCL-only": (8, "pp = 4\ncomm = baseline"),
+}
+
+
+@pytest.mark.parametrize("name", sorted(LAYOUTS))
+def test_every_layout_trains_like_the_one_device_model(name):
+    world, keys = LAYOUTS[name]
+    losses, drift = _train_both(_cfg("tiny_mp.cfg", world, keys))
+    for got, want in losses:
+        assert got == pytest.approx(want, abs=1.5e-3), (name, losses)
+    # parameters after three AdamW steps: apart by a few percent of the distance they moved (bf16 storage of
+    # activations and weights turns a few near-zero gradients around; a wrong shard or a lost contribution moves whole tensors)
+    assert drift < 0.05, (name, drift)
+
+
+def test_the_reference_config_with_grouped_query_attention_and_an_untied_head():
+    """tiny.cfg has 4 query heads on 2 kv heads; an untied LM head adds a parameter the pipeline's last stage owns."""
+    losses, drift = _train_both(_cfg("tiny.cfg", 2, "pp = 2\ntie_embeddings = 0"))
+    assert all(got == pytest.approx(want, abs=1.5e-3) for got, want in losses) and drift < 0.05
+
+
+def test_layouts_without_an_interpretation_say_so():
+    from cai_b200.models.plan_interpreter import PlanInterpreter
+    with pytest.raises(NotImplementedError):
+        PlanInterpreter(_cfg("tiny_moe.cfg", 1, ""))
+    with pytest.raises(NotImplementedError):
+        PlanInterpreter(_cfg("tiny_mp.cfg", 1, "param_dtype = fp8e4m3"))
