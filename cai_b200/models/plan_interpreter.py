@@ -21,7 +21,6 @@ is there. A job whose ranks cannot all finish raises instead of hanging.
 """
 from __future__ import annotations
 
-import math
 import tempfile
 from collections import defaultdict, deque
 from pathlib import Path
@@ -71,13 +70,6 @@ class _Rank:
         if n * es > t.nbytes:
             raise ValueError(f"tensor {tid}: a record addresses {n * es} bytes of {t.nbytes}")
         return self._base(_TORCH[t.dtype])[t.offset // es:t.offset // es + n]
-
-    def at(self, byte_offset, dtype, count):
-        es = torch.empty(0, dtype=dtype).element_size()
-        return self._base(dtype)[byte_offset // es:byte_offset // es + count]
-
-    def offset(self, tid):
-        return int(self.pf.tensors[tid].offset)
 
     def named_flat(self, name):
         return self.flat(self.named[name].tensor)

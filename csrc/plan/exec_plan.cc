@@ -390,10 +390,13 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         if (!cfg.train.comm_mode) return failf(err, ERR_INVALID, "MoE plans exist only for comm = fused (in-kernel dispatch/combine)");
     }
     // ZeRO-3: the bf16 parameters are sharded over the data-parallel group like the optimizer state and
-    // gathered layer by layer (the gather is fused into the first GEMM that reads the layer's weights).
-    const bool zero3 = cfg.train.zero_stage >= 3 && d.dp > 1 && cfg.train.comm_mode != 0 && !moe && d.tp == 1 && d.pp == 1;
+    // gathered layer by layer (the gather is fused into the first GEMM that reads the layer's weights). Beside tensor
+    // parallelism every rank shards ITS slice of the weights over the ranks that hold the same slice; the gathers are
+    // then kernels of their own (the first consumer is an all-gather + GEMM kernel, which has no copy role for weights)
+    // and gradients stay whole (the per-layer buckets that shard them exist for tp = 1).
+    const bool zero3 = cfg.train.zero_stage >= 3 && d.dp > 1 && cfg.train.comm_mode != 0 && !moe && d.pp == 1;
     if (cfg.train.zero_stage >= 3 && d.dp > 1 && !zero3)
-        return failf(err, ERR_INVALID, "zero_stage = 3 needs comm = fused, tp = 1, pp = 1 and a dense model");
+        return failf(err, ERR_INVALID, "zero_stage = 3 needs comm = fused, pp = 1 and a dense model");
     // fp8 parameters: forward and input-gradient GEMMs of the linear layers run in e4m3 with block scales
     // (tp = 1, dense); weight gradients, attention, the LM head and everything else stay bf16.
     if (m.param_dtype == DT_FP8_E4M3 && (d.tp != 1 || moe))
@@ -592,7 +595,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     // one of two alternating layer-sized fp32 buffers; the layer's bucket kernel (every microbatch) sums the
     // members' buffers for the elements this rank owns into a shard-sized accumulator, and on the last microbatch
     // goes on to AdamW. Only the small resident group (embedding, gains, head) keeps full-size gradients.
-    const bool shard_grads = zero3 && cfg.train.dp_buckets != 0 && b.layers > 0;
+    const bool shard_grads = zero3 && cfg.train.dp_buckets != 0 && b.layers > 0 && d.tp == 1;
     int grad_stage[2] = {-1, -1}, grad_acc = -1;
     if (shard_grads) {
         uint64_t max_layer = 0;
@@ -674,7 +677,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     };
     // makes layer l's weights usable: ZeRO-3 gather (fused into the next GEMM unless fp8 needs them quantised first)
     auto prepare_layer = [&](int l, bool reverse, uint16_t mb) {
-        gather_group(l, reverse, !fp8, mb);
+        gather_group(l, reverse, !fp8 && d.tp == 1, mb);
         if (fp8 && zero3 && fp8_resident != l) {
             quant_layer(static_cast<uint32_t>(l), mb);
             fp8_resident = l;

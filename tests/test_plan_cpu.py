@@ -217,7 +217,13 @@ def test_plan_variants_compile_and_verify(tmp_path):
     off = _variant(tmp_path, "tp2_serial", "tp = 2\ncomm = fused\nwgrad_overlap = 0\n", world=2)
     assert not [op for op in off.ops if op.exec and int(off.exec[op.exec - 1].kernel) == plan.K_GEMM and op.stream_id == 1]
     # refused combinations
-    for bad in ("zero_stage = 3\ncomm = baseline\n", "zero_stage = 3\ncomm = fused\ntp = 2\n",
+    # ZeRO-3 beside tensor parallelism: every rank shards its slice of the weights over its data-parallel group; the
+    # gathers are kernels of their own (none rides in a GEMM) and the gradients stay whole
+    z3tp = _variant(tmp_path, "zero3_tp2", "comm = fused\nzero_stage = 3\ntp = 2\n", world=4)
+    gathers = [x for x in z3tp.exec if int(x.kernel) == plan.K_FSDP_AG_GEMM]
+    assert gathers and not any(x.flags & 1 for x in gathers) and plan.K_AG_GEMM in kernels(z3tp)
+    assert not [x for x in z3tp.exec if int(x.kernel) == plan.K_RS_ADAMW and (x.flags & 4)]
+    for bad in ("zero_stage = 3\ncomm = baseline\n", "zero_stage = 3\ncomm = fused\npp = 2\n",
                 "param_dtype = fp8e4m3\ntp = 2\n",       # fp8 under tensor parallelism: an error, not a silent bf16 run
                 "pp = 2\nvpp = 2\n"):                    # interleaving: an error, not a silent plain 1F1B schedule
         with pytest.raises(plan.PlanError):   # 4 GPUs: dp = 4, or tp = 2 x dp = 2
