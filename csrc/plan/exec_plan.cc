@@ -394,9 +394,9 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     // parallelism every rank shards ITS slice of the weights over the ranks that hold the same slice; the gathers are
     // then kernels of their own (the first consumer is an all-gather + GEMM kernel, which has no copy role for weights)
     // and gradients stay whole (the per-layer buckets that shard them exist for tp = 1).
-    const bool zero3 = cfg.train.zero_stage >= 3 && d.dp > 1 && cfg.train.comm_mode != 0 && !moe && d.pp == 1;
+    const bool zero3 = cfg.train.zero_stage >= 3 && d.dp > 1 && cfg.train.comm_mode != 0 && !moe;
     if (cfg.train.zero_stage >= 3 && d.dp > 1 && !zero3)
-        return failf(err, ERR_INVALID, "zero_stage = 3 needs comm = fused, pp = 1 and a dense model");
+        return failf(err, ERR_INVALID, "zero_stage = 3 needs comm = fused and a dense model");
     // fp8 parameters: forward and input-gradient GEMMs of the linear layers run in e4m3 with block scales
     // (tp = 1, dense); weight gradients, attention, the LM head and everything else stay bf16.
     if (m.param_dtype == DT_FP8_E4M3 && (d.tp != 1 || moe))
@@ -480,9 +480,11 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             L[l].g1 = b.param(lname(nm, l, "g1"), 1, H, 0.f);
             L[l].g2 = b.param(lname(nm, l, "g2"), 1, H, 0.f);
         }
-        gf = b.param("gf", 1, H, 0.f);
-        if (!b.tied) head = b.param("lm_head", b.V_l, H, istd);
-        else head = embed;
+        if (b.last_stage) {
+            gf = b.param("gf", 1, H, 0.f);
+            if (!b.tied) head = b.param("lm_head", b.V_l, H, istd);
+            else head = embed;
+        }
         misc_hi = align_up(b.flat_elems, kFlatAlignElems);
         for (uint32_t l = 0; l < b.layers; ++l) {
             layer_range[l].first = align_up(b.flat_elems, kFlatAlignElems);

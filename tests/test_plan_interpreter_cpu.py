@@ -81,7 +81,9 @@ LAYOUTS = {
     "pp2 x dp2 fused": (4, "pp = 2\ncomm = fused"),
     "dp4 ZeRO-3": (4, "comm = fused\nzero_stage = 3"),
     "tp2 x dp2 ZeRO-3": (4, "tp = 2\ncomm = fused\nzero_stage = 3"),
+    "pp2 x dp2 ZeRO-3": (4, "pp = 2\ncomm = fused\nzero_stage = 3"),
     "tp2 x pp2 x dp2 fused": (8, "tp = 2\npp = 2\ncomm = fused"),
+    "tp2 x pp2 x dp2 ZeRO-3": (8, "tp = 2\npp = 2\ncomm = fused\nzero_stage = 3"),
     "tp4 x dp2 ZeRO-3": (8, "tp = 4\ncomm = fused\nzero_stage = 3"),
     "pp4 x dp2 NCCL-only": (8, "pp = 4\ncomm = baseline"),
 }
