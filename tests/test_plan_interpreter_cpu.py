@@ -100,6 +100,25 @@ def test_every_layout_trains_like_the_one_device_model(name):
     assert drift < 0.05, (name, drift)
 
 
+ODD = {
+    "three stages over four layers": (3, "pp = 3"),
+    "two stages over five layers": (2, "pp = 2\nnum_layers = 5\ncomm = fused"),
+    "three replicas": (3, "comm = fused"),
+    "three replicas, ZeRO-3": (3, "comm = fused\nzero_stage = 3"),
+    "tp2 x dp3": (6, "tp = 2\ncomm = fused"),
+    "one microbatch per step under a pipeline": (2, "pp = 2\ngrad_accum = 1"),
+    "three microbatches of one sequence": (2, "comm = fused\nmicrobatch = 1\ngrad_accum = 3"),
+    "untied head under tensor parallelism": (2, "tp = 2\ncomm = fused\ntie_embeddings = 0"),
+}
+
+
+@pytest.mark.parametrize("name", sorted(ODD))
+def test_shapes_that_do_not_divide_evenly(name):
+    world, keys = ODD[name]
+    losses, drift = _train_both(_cfg("tiny_mp.cfg", world, keys), steps=2)
+    assert all(got == pytest.approx(want, abs=1.5e-3) for got, want in losses) and drift < 0.05, (name, losses, drift)
+
+
 def test_the_reference_config_with_grouped_query_attention_and_an_untied_head():
     """tiny.cfg has 4 query heads on 2 kv heads; an untied LM head adds a parameter the pipeline's last stage owns."""
     losses, drift = _train_both(_cfg("tiny.cfg", 2, "pp = 2\ntie_embeddings = 0"))
