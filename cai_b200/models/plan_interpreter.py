@@ -11,8 +11,8 @@ What is interpreted: the dense decoder under tensor (fused or NCCL-only plans), 
 sharded optimizer state (the fused reduce-scatter + AdamW kernel in its whole-space and its per-layer bucket form) or
 with parameters and gradients sharded too (ZeRO-3: parameter gathers, staged gradients, owners' accumulators). Each record does what the kernel it names is specified to do (``csrc/kernels/cai_kernels.h``,
 ``csrc/comm/fused.h``): tensors keep their storage types (bf16 activations and weights, fp32 gradients and optimizer
-state), arithmetic inside a record is fp32. Mixture-of-experts records and the e4m3 path are not interpreted and raise
-``NotImplementedError``.
+state, e4m3 operands with their block scales under ``param_dtype = fp8e4m3``), arithmetic inside a record is fp32.
+Mixture-of-experts records are not interpreted and raise ``NotImplementedError``.
 
 Ranks run as coroutines in program order. That order is a legal serialisation of a rank's streams (a wait never
 precedes its record in a table); a collective runs when every member of its group has reached it (members of a group
@@ -32,7 +32,7 @@ from .. import plan as planlib
 from ..utils import reshard
 
 K = {name: i for i, name in enumerate(planlib.KERNEL_NAMES)}
-_TORCH = {0: torch.float32, 1: torch.bfloat16, 2: torch.float16, 5: torch.int32, 6: torch.uint8}
+_TORCH = {0: torch.float32, 1: torch.bfloat16, 2: torch.float16, 3: torch.float8_e4m3fn, 5: torch.int32, 6: torch.uint8}
 ST_IO = 5
 
 
@@ -114,8 +114,8 @@ class PlanInterpreter:
             self.ranks = [_Rank(planlib.PlanFile(Path(tmp) / f"plan.rank{r:06d}.bin"), r) for r in range(self.world)]
         pf = self.ranks[0].pf
         self.train, self.model, self.hdr = pf.train, pf.model, pf.hdr
-        if self.model.is_moe or self.model.param_dtype != 1:
-            raise NotImplementedError("mixture-of-experts and e4m3 plans are not interpreted")
+        if self.model.is_moe:
+            raise NotImplementedError("mixture-of-experts plans are not interpreted")
         self.step_count = 0
         self.lr = float(self.train.lr)
         self._members = {}
@@ -297,6 +297,42 @@ class PlanInterpreter:
         ta, tb, epi = x.flags & 1, (x.flags >> 1) & 1, (x.flags >> 4) & 0xF
         acc = self._gemm_core(r, x.t[0], x.t[1], x.i[0], x.i[1], x.i[2], ta, tb)
         self._epilogue(r, acc, x, x.t[2], x.t[3], epi, float(x.f[0]))
+
+    @staticmethod
+    def _quant(v, rows_per_scale, cols_per_scale=128):
+        """e4m3 with one scale (amax / 448) per ``rows_per_scale x cols_per_scale`` block; returns (q as fp32 values, scale)."""
+        R, C = v.shape
+        br, bc = -(-R // rows_per_scale), -(-C // cols_per_scale)
+        pad = torch.zeros(br * rows_per_scale, bc * cols_per_scale)
+        pad[:R, :C] = v
+        blocks = pad.view(br, rows_per_scale, bc, cols_per_scale)
+        scale = blocks.abs().amax((1, 3)) / 448.0
+        safe = torch.where(scale > 0, scale, torch.ones_like(scale))
+        q = (blocks / safe[:, None, :, None]).to(torch.float8_e4m3fn).float().view(br * rows_per_scale, bc * cols_per_scale)[:R, :C]
+        return q, scale
+
+    def _k_quant_fp8(self, r, x):
+        rows, cols = x.i[0], x.i[1]
+        v = r.mat(x.t[0], rows, cols).float()
+        if x.flags & 1:     # a weight: 128 x 128 blocks, and the transposed copy with its own scale table
+            q, sc = self._quant(v, 128)
+            r.mat(x.t[1], rows, cols).copy_(q)
+            r.mat(x.t[2], -(-rows // 128), -(-cols // 128)).copy_(sc)
+            if x.t[3] >= 0:
+                r.mat(x.t[3], cols, rows).copy_(q.t())
+                r.mat(x.t[4], -(-cols // 128), -(-rows // 128)).copy_(sc.t())
+        else:               # an activation: one scale per row and 128 columns
+            q, sc = self._quant(v, 1)
+            r.mat(x.t[1], rows, cols).copy_(q)
+            r.mat(x.t[2], rows, cols // 128).copy_(sc)
+
+    def _k_gemm_fp8(self, r, x):
+        """C[M,N] = sum over 128-wide k blocks of sa[m,kb] * sb[n/128,kb] * (Aq[m,kb] . Bq[n,kb])."""
+        M, N, Kd = x.i[0], x.i[1], x.i[2]
+        a = r.mat(x.t[0], M, Kd).float() * r.mat(x.t[4], M, Kd // 128).float().repeat_interleave(128, 1)
+        sb = r.mat(x.t[5], -(-N // 128), Kd // 128).float().repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)
+        b = r.mat(x.t[1], N, Kd).float() * sb
+        self._epilogue(r, a @ b.t(), x, x.t[2], x.t[3], (x.flags >> 4) & 0xF)
 
     def _k_embed_fwd(self, r, x):
         T, H, lo, hi = x.i[0], x.i[1], x.i[2], x.i[3]
@@ -538,7 +574,7 @@ class PlanInterpreter:
     _local = {K["gemm"]: _k_gemm, K["embed_fwd"]: _k_embed_fwd, K["embed_bwd"]: _k_embed_bwd, K["rmsnorm_fwd"]: _k_rmsnorm_fwd,
               K["rmsnorm_bwd"]: _k_rmsnorm_bwd, K["rope"]: _k_rope, K["attn_fwd"]: _k_attn_fwd, K["attn_bwd"]: _k_attn_bwd,
               K["swiglu_fwd"]: _k_swiglu_fwd, K["swiglu_bwd"]: _k_swiglu_bwd, K["cross_entropy"]: _k_cross_entropy,
-              K["adamw"]: _k_adamw, K["zero"]: _k_zero, K["add"]: _k_add}
+              K["adamw"]: _k_adamw, K["zero"]: _k_zero, K["add"]: _k_add, K["quant_fp8"]: _k_quant_fp8, K["gemm_fp8"]: _k_gemm_fp8}
     _group_ops = {K["nccl_all_reduce"]: _g_all_reduce, K["nccl_reduce_scatter"]: _g_reduce_scatter,
                   K["nccl_all_gather"]: _g_all_gather, K["cross_entropy_tp"]: _g_cross_entropy_tp, K["ag_gemm"]: _g_ag_gemm,
                   K["gemm_rs"]: _g_gemm_rs, K["rs_adamw"]: _g_rs_adamw, K["fsdp_ag_gemm"]: _g_fsdp_gather}
