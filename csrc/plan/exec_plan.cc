@@ -267,7 +267,7 @@ struct Builder {
             linear(x_local, W, y, aux, N, K, tb, mb, epi);
             return;
         }
-        if (fused) {
+        if (fused && !fp8) {
             ExecOp e = xop(K_AG_GEMM, static_cast<uint16_t>((tb ? 2 : 0) | (epi << 4)));
             e.t[0] = x_local; e.t[1] = W; e.t[2] = y; e.t[3] = x_full; e.t[5] = aux;
             e.i[0] = T; e.i[1] = N; e.i[2] = K; e.i[3] = GROUP_TP; e.i[4] = static_cast<int32_t>(next_seq++);
@@ -279,7 +279,10 @@ struct Builder {
         nccl(K_NCCL_ALL_GATHER, OP_ALL_GATHER, ST_COMM_TP, x_local, x_full, static_cast<uint64_t>(Tl) * K, DT_BF16,
              GROUP_TP, -1, mb);
         sync(ST_COMM_TP, ST_COMPUTE_HI, mb);
-        gemm(ST_COMPUTE_HI, x_full, W, y, aux, T, N, K, false, tb, epi, mb);
+        // e4m3 weights: the gathered rows are quantised and the block-scaled product runs (there is no e4m3 form of
+        // the all-gather + GEMM kernel, so the collective stays a call of its own beside it)
+        if (fp8) linear(x_full, W, y, aux, N, K, tb, mb, epi);
+        else gemm(ST_COMPUTE_HI, x_full, W, y, aux, T, N, K, false, tb, epi, mb);
     }
     // out_local[Tl, N] = residual + reduce_scatter_rows(a[T, K] * W[N, K]^T) (row-parallel linear,
     // forward), or with tb the input gradient of a column-parallel linear (residual may be -1).
@@ -289,7 +292,7 @@ struct Builder {
             linear(a, W, out_local, residual, N, K, tb, mb);
             return;
         }
-        if (fused) {
+        if (fused && !fp8) {
             ExecOp e = xop(K_GEMM_RS, static_cast<uint16_t>(tb ? 2 : 0));
             e.t[0] = a; e.t[1] = W; e.t[2] = out_local; e.t[3] = residual; e.t[4] = partial;
             e.i[0] = T; e.i[1] = N; e.i[2] = K; e.i[3] = GROUP_TP; e.i[4] = static_cast<int32_t>(next_seq++);
@@ -297,7 +300,8 @@ struct Builder {
             push(OP_GEMM_RS, ST_COMPUTE_HI, 2.0 * T * N * K, static_cast<double>(T) * N * 2, GROUP_TP, mb, &e);
             return;
         }
-        gemm(ST_COMPUTE_HI, a, W, partial, -1, T, N, K, false, tb, 0, mb);
+        if (fp8) linear(a, W, partial, -1, N, K, tb, mb);
+        else gemm(ST_COMPUTE_HI, a, W, partial, -1, T, N, K, false, tb, 0, mb);
         sync(ST_COMPUTE_HI, ST_COMM_TP, mb);
         nccl(K_NCCL_REDUCE_SCATTER, OP_REDUCE_SCATTER, ST_COMM_TP, partial, residual >= 0 ? rs_tmp : out_local,
              static_cast<uint64_t>(Tl) * N, DT_BF16, GROUP_TP, -1, mb);
@@ -399,9 +403,9 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         return failf(err, ERR_INVALID, "zero_stage = 3 needs comm = fused and a dense model");
     // fp8 parameters: forward and input-gradient GEMMs of the linear layers run in e4m3 with block scales
     // (tp = 1, dense); weight gradients, attention, the LM head and everything else stay bf16.
-    if (m.param_dtype == DT_FP8_E4M3 && (d.tp != 1 || moe))
-        return failf(err, ERR_INVALID, "param_dtype = fp8e4m3 has an executable schedule for dense models with tp = 1 only "
-                                       "(got tp=%u%s); use bf16 there instead of a silent change of precision", d.tp, moe ? ", MoE" : "");
+    if (m.param_dtype == DT_FP8_E4M3 && moe)
+        return failf(err, ERR_INVALID, "param_dtype = fp8e4m3 has an executable schedule for dense models only; "
+                                       "use bf16 for mixture-of-experts models instead of a silent change of precision");
     const bool fp8 = m.param_dtype == DT_FP8_E4M3;
     if (d.cp != 1) return failf(err, ERR_INVALID, "context parallelism (cp>1) has no executable schedule");
     if (d.vpp > 1)

@@ -223,11 +223,16 @@ def test_plan_variants_compile_and_verify(tmp_path):
     gathers = [x for x in z3tp.exec if int(x.kernel) == plan.K_FSDP_AG_GEMM]
     assert gathers and not any(x.flags & 1 for x in gathers) and plan.K_AG_GEMM in kernels(z3tp)
     assert not [x for x in z3tp.exec if int(x.kernel) == plan.K_RS_ADAMW and (x.flags & 4)]
+    # e4m3 linear layers under tensor parallelism: the collectives stay calls of their own beside the block-scaled GEMMs
+    # (the fused all-gather / reduce-scatter GEMM kernels are bf16 only)
+    f8tp = _variant(tmp_path, "fp8_tp2", "param_dtype = fp8e4m3\ntp = 2\ncomm = fused\n", world=2)
+    assert plan.K_GEMM_FP8 in kernels(f8tp) and not ({plan.K_AG_GEMM, plan.K_GEMM_RS} & kernels(f8tp))
+    with pytest.raises(plan.PlanError):      # experts in e4m3: an error, not a silent bf16 run
+        plan.compile_plans((ROOT / "configs" / "tiny_moe.cfg").read_text() + "\nparam_dtype = fp8e4m3\n", tmp_path / "bad_moe", version=2, text=True)
     # ... and beside a pipeline: every stage shards its own parameters
     z3pp = _variant(tmp_path, "zero3_pp2", "comm = fused\nzero_stage = 3\npp = 2\n", world=4)
     assert plan.K_FSDP_AG_GEMM in kernels(z3pp) and z3pp.hdr.num_stages == 2
     for bad in ("zero_stage = 3\ncomm = baseline\n",
-                "param_dtype = fp8e4m3\ntp = 2\n",       # fp8 under tensor parallelism: an error, not a silent bf16 run
                 "pp = 2\nvpp = 2\n"):                    # interleaving: an error, not a silent plain 1F1B schedule
         with pytest.raises(plan.PlanError):   # 4 GPUs: dp = 4, or tp = 2 x dp = 2
             plan.compile_plans((ROOT / "configs" / "tiny_mp.cfg").read_text() + "\ngpus_per_rack = 4\ngpus_per_tray = 4\n" + bad,

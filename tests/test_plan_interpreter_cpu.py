@@ -125,7 +125,8 @@ def test_the_reference_config_with_grouped_query_attention_and_an_untied_head():
     assert all(got == pytest.approx(want, abs=1.5e-3) for got, want in losses) and drift < 0.05
 
 
-@pytest.mark.parametrize("world,keys", [(1, ""), (2, "comm = fused\nzero_stage = 3"), (2, "pp = 2")])
+@pytest.mark.parametrize("world,keys", [(1, ""), (2, "comm = fused\nzero_stage = 3"), (2, "pp = 2"), (2, "tp = 2\ncomm = fused"),
+                                        (4, "tp = 2\ncomm = fused\nzero_stage = 3")])
 def test_block_scaled_e4m3_linear_layers_stay_close_to_the_fp32_model(world, keys):
     """param_dtype = fp8e4m3: activations quantised per row and 128 columns, weights per 128 x 128 block (again after
     every ZeRO-3 gather), forward and input-gradient products in e4m3. The losses stay within a few 1e-3 of the fp32
