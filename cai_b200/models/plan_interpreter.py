@@ -163,6 +163,9 @@ class PlanInterpreter:
         self.hyper = (float(self.lr if lr is None else lr), b1, b2, float(self.train.adam_eps), float(self.train.weight_decay),
                       1.0 - b1 ** t, 1.0 - b2 ** t)
         rows = self.rows_per_replica
+        if tokens.shape[0] != rows * int(self.hdr.dp) or tokens.shape != targets.shape or tokens.shape[1] != int(self.model.seq_len):
+            raise ValueError(f"a step of this job takes {rows * int(self.hdr.dp)} sequences of {int(self.model.seq_len)} tokens, "
+                             f"got {tuple(tokens.shape)}")
         for r in self.ranks:
             d = r.rl.dp_id
             for name, src in (("@tokens", tokens), ("@targets", targets)):

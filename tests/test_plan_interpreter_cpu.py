@@ -141,3 +141,30 @@ def test_layouts_without_an_interpretation_say_so():
     from cai_b200.models.plan_interpreter import PlanInterpreter
     with pytest.raises(NotImplementedError):
         PlanInterpreter(_cfg("tiny_moe.cfg", 1, ""))
+
+
+def test_a_run_continues_on_another_layout_from_the_state_of_the_first():
+    """Two steps on tp 2 x pp 2, the global state (master, moments, step) moved to dp 2 with ZeRO-3, two more steps: the
+    losses of the second half equal those of an uninterrupted one-rank run, so nothing of the optimizer state is lost or
+    misplaced when the layout changes (the path a re-sharded checkpoint takes)."""
+    from cai_b200 import plan
+    from cai_b200.models.plan_interpreter import PlanInterpreter, random_state
+    first = PlanInterpreter(_cfg("tiny_mp.cfg", 4, "tp = 2\npp = 2\ncomm = fused\ntie_embeddings = 0"))
+    # two replicas with half the accumulation steps: the global batch stays what it was
+    second = PlanInterpreter(_cfg("tiny_mp.cfg", 2, "comm = fused\nzero_stage = 3\ntie_embeddings = 0\ngrad_accum = 2"))
+    single = PlanInterpreter(_cfg("tiny_mp.cfg", 1, "tie_embeddings = 0"))
+    st = random_state(first, seed=4)
+    first.load_state(st)
+    single.load_state(st)
+    m = first.model
+    G, S = int(plan.describe(first.config_text)["global_batch"]), int(m.seq_len)
+    gen = torch.Generator().manual_seed(9)
+    batches = [(torch.randint(0, m.vocab_size, (G, S), generator=gen), torch.randint(0, m.vocab_size, (G, S), generator=gen))
+               for _ in range(4)]
+    want = [single.step(*b) for b in batches]
+    got = [first.step(*b) for b in batches[:2]]
+    second.load_state(first.state(), step=first.step_count)
+    got += [second.step(*b) for b in batches[2:]]
+    assert got == pytest.approx(want, abs=1.5e-3), (got, want)
+    with pytest.raises(ValueError, match="sequences"):
+        second.step(batches[0][0][:3], batches[0][1][:3])
