@@ -7,12 +7,14 @@ of the job inside one process, so that what a layout computes can be checked wit
 must train exactly like the one-device model (``reference_torch.forward_loss`` + AdamW), because every collective,
 every hand-off and every shard boundary in the tables is executed for real.
 
-What is interpreted: the dense decoder under tensor (fused or NCCL-only plans), pipeline and data parallelism with
+What is interpreted: the decoder under tensor (fused or NCCL-only plans), pipeline and data parallelism with
 sharded optimizer state (the fused reduce-scatter + AdamW kernel in its whole-space and its per-layer bucket form) or
 with parameters and gradients sharded too (ZeRO-3: parameter gathers, staged gradients, owners' accumulators). Each record does what the kernel it names is specified to do (``csrc/kernels/cai_kernels.h``,
 ``csrc/comm/fused.h``): tensors keep their storage types (bf16 activations and weights, fp32 gradients and optimizer
 state, e4m3 operands with their block scales under ``param_dtype = fp8e4m3``), arithmetic inside a record is fp32.
-Mixture-of-experts records are not interpreted and raise ``NotImplementedError``.
+Mixture-of-experts plans are interpreted too: router, slot assignment in token order, dispatch into the owners' slabs,
+the experts' products over the live rows of the slabs, combine, and the backward of all of it. A record without an
+interpretation raises ``NotImplementedError``.
 
 Ranks run as coroutines in program order. That order is a legal serialisation of a rank's streams (a wait never
 precedes its record in a table); a collective runs when every member of its group has reached it (members of a group
@@ -114,8 +116,6 @@ class PlanInterpreter:
             self.ranks = [_Rank(planlib.PlanFile(Path(tmp) / f"plan.rank{r:06d}.bin"), r) for r in range(self.world)]
         pf = self.ranks[0].pf
         self.train, self.model, self.hdr = pf.train, pf.model, pf.hdr
-        if self.model.is_moe:
-            raise NotImplementedError("mixture-of-experts plans are not interpreted")
         self.step_count = 0
         self.lr = float(self.train.lr)
         self._members = {}
@@ -184,6 +184,16 @@ class PlanInterpreter:
             self._members[key] = planlib.group_members(self.config_text, kind, rank)
         return self._members[key]
 
+    def expert_group(self, r):
+        """Members of the group the experts are spread over, in member order: the tp ranks of each of the ep replicas
+        of the rank's block (member = replica * tp + tp rank), as ``cai_b200.parallel.peers`` maps them on the device."""
+        h = self.hdr
+        tp, ep = int(h.tp), max(1, int(h.ep))
+        replica = tp * int(h.num_stages) * max(1, int(h.cp))
+        tp_id, within, dp_id = r.rank % tp, r.rank % replica, r.rank // replica
+        first_dp = (dp_id // ep) * ep
+        return [within - tp_id + t + (first_dp + i) * replica for i in range(ep) for t in range(tp)]
+
     def _run(self):
         self.mail = defaultdict(deque)          # (src rank, dst rank, channel) -> messages
         self.pending = {}                       # (group members, call index) -> {rank: request}
@@ -215,9 +225,9 @@ class PlanInterpreter:
             return want[1] not in self.pending      # the last member to arrive ran it and removed the entry
         return True
 
-    def _collective(self, r, kind, fn, payload):
+    def _collective(self, r, kind, fn, payload, members=None):
         """Generator helper: join call number n of the rank's group; the last member to arrive runs ``fn``."""
-        mem = tuple(self.members(kind, r.rank))
+        mem = tuple(members if members is not None else self.members(kind, r.rank))
         n = self.calls[(r.rank, mem)]
         self.calls[(r.rank, mem)] += 1
         key = (mem, n)
@@ -258,7 +268,8 @@ class PlanInterpreter:
             if coll is None:
                 raise NotImplementedError(f"kernel '{planlib.KERNEL_NAMES[k]}' is not interpreted")
             kind = (planlib.GROUP_TP if k == K["cross_entropy_tp"] else planlib.GROUP_DP if k == K["fsdp_ag_gemm"] else int(x.i[3]))
-            wait = self._collective(r, kind, coll.__get__(self), x)
+            members = self.expert_group(r) if k in (K["moe_dispatch_gemm"], K["moe_gemm_combine"]) else None
+            wait = self._collective(r, kind, coll.__get__(self), x, members)
             if wait is not None:
                 yield wait
 
@@ -294,9 +305,37 @@ class PlanInterpreter:
         else:
             raise NotImplementedError(f"GEMM epilogue {epi}")
 
+    def _k_gemm_slabs(self, r, x):
+        """The products of the local experts over their ragged slabs. Group g reads A, B at row g * (rows of one group)
+        and writes C likewise; the segmented dimension is cut into sub-slabs of ``seg_rows`` rows of which only the first
+        ``counts[...]`` hold data: mode 1 segments M (rows past a count are not written), mode 2 segments K (rows past a
+        count do not contribute: the weight gradient)."""
+        ta, tb, epi = x.flags & 1, (x.flags >> 1) & 1, (x.flags >> 4) & 0xF
+        M, N, Kd, seg_rows = x.i[0], x.i[1], x.i[2], x.i[3]
+        seg_mode, groups = x.i[4] & 0xFF, (x.i[4] >> 8) if x.flags & 0x100 else 1
+        ga, gb = (Kd if ta else M), (Kd if tb else N)
+        a_all = r.mat(x.t[0], groups * ga, M if ta else Kd).float()
+        b_all = r.mat(x.t[1], groups * gb, N if tb else Kd).float()
+        c_all = r.mat(x.t[2], groups * M, N)
+        per = (Kd if seg_mode == 2 else M) // seg_rows
+        counts = r.flat(x.t[4], groups * per).long()
+        for g in range(groups):
+            a, b = a_all[g * ga:(g + 1) * ga], b_all[g * gb:(g + 1) * gb]
+            a, b = (a.t() if ta else a), (b if tb else b.t())            # [M, K], [K, N]
+            live = torch.zeros(per * seg_rows, dtype=torch.bool)
+            for j in range(per):
+                live[j * seg_rows:j * seg_rows + int(counts[g * per + j])] = True
+            c = c_all[g * M:(g + 1) * M]
+            if seg_mode == 2:
+                acc = (a[:, live] @ b[live]) * float(x.f[0])
+                c.copy_(c + acc if epi == 2 else acc)
+            else:
+                acc = (a[live] @ b) * float(x.f[0])
+                c[live] = (c[live].float() + acc if epi == 2 else acc).to(c.dtype)
+
     def _k_gemm(self, r, x):
         if x.flags & 0x100 or x.t[4] >= 0:
-            raise NotImplementedError("segmented / grouped expert GEMMs are not interpreted")
+            return self._k_gemm_slabs(r, x)
         ta, tb, epi = x.flags & 1, (x.flags >> 1) & 1, (x.flags >> 4) & 0xF
         acc = self._gemm_core(r, x.t[0], x.t[1], x.i[0], x.i[1], x.i[2], ta, tb)
         self._epilogue(r, acc, x, x.t[2], x.t[3], epi, float(x.f[0]))
@@ -456,7 +495,91 @@ class PlanInterpreter:
         n = x.i[0]
         r.flat(x.t[2], n).copy_(r.flat(x.t[0], n).float() + r.flat(x.t[1], n).float())
 
+    def _k_moe_route(self, r, x):
+        T, E, k = x.i[0], x.i[1], x.i[2]
+        logits = r.mat(x.t[0], T, E).float()
+        if x.flags & 1:     # backward: dlogits from the gradient of the renormalised top-k weights
+            idx, pos = r.mat(x.t[1], T, k).long(), r.mat(x.t[3], T, k)
+            z = logits.clone().requires_grad_(True)
+            p = torch.softmax(z, -1).gather(1, idx)
+            w = p / p.sum(-1, keepdim=True)
+            dw = torch.where(pos >= 0, r.mat(x.t[2], T, k).float(), torch.zeros(()))     # dropped choices carry no gradient
+            w.backward(dw)
+            r.mat(x.t[4], T, E).copy_(z.grad)
+            return
+        cap = x.i[3]
+        p = torch.softmax(logits, -1)
+        # top-k, ties to the lower index (a stable descending sort does that)
+        order = torch.sort(p, dim=-1, descending=True, stable=True)
+        idx, top = order.indices[:, :k], order.values[:, :k]
+        r.mat(x.t[1], T, k).copy_(idx)
+        r.mat(x.t[2], T, k).copy_(top / top.sum(-1, keepdim=True))
+        # slot of every (token, choice) in its expert's slab, in token order; -1 past the capacity
+        flat = idx.reshape(-1)
+        counts = torch.bincount(flat, minlength=E)
+        order = torch.argsort(flat, stable=True)                     # entries grouped by expert, token order kept
+        first = torch.cumsum(counts, 0) - counts                      # where each expert's group starts
+        slot = torch.empty_like(flat)
+        slot[order] = torch.arange(flat.numel()) - first[flat[order]]
+        pos = torch.where(slot < cap, slot, torch.full_like(slot, -1))
+        r.mat(x.t[3], T, k).copy_(pos.view(T, k))
+        r.flat(x.t[4], E).copy_(counts)
+
     # ------------------------------------------------------------------ records of a whole group
+    def _g_moe_dispatch(self, ranks, xs):
+        """Every member permutes its rows by expert straight into the owners' slabs: slab (local expert, source member),
+        row = the slot the router gave; the owners also learn how many rows each source sent."""
+        x0 = xs[0]
+        k, E, cap = x0.i[0], x0.i[1], x0.i[2]
+        n = len(ranks)
+        E_l = E // n
+        for src, (r, x) in enumerate(zip(ranks, xs)):
+            T, H, _ = r.pf.shape(x.t[0])
+            rows = r.mat(x.t[0], T, H).float()
+            idx, pos = r.mat(x.t[1], T, k).long(), r.mat(x.t[2], T, k).long()
+            scale = r.mat(x.t[3], T, k).float() if x.t[3] >= 0 else None
+            counts = r.flat(x.t[4], E).long()
+            for e in range(E):
+                owner, el = e // E_l, e % E_l
+                o, ox = ranks[owner], xs[owner]
+                sub = el * n + src
+                cnt = min(int(counts[e]), cap)
+                o.flat(ox.t[6], E_l * n)[sub] = cnt
+                slab = o.mat(ox.t[5], E_l * n * cap, H)
+                slab[sub * cap + cnt:(sub + 1) * cap].zero_()          # the device zeroes up to the next 128; rows past a count are never read
+                sel = (idx == e) & (pos >= 0)
+                t_i, s_i = torch.nonzero(sel, as_tuple=True)
+                if t_i.numel():
+                    v = rows[t_i] * (scale[t_i, s_i][:, None] if scale is not None else 1.0)
+                    slab[sub * cap + pos[t_i, s_i]] = v.to(slab.dtype)
+
+    def _g_moe_combine(self, ranks, xs):
+        """Every member pulls the rows of its tokens back out of the owners' slabs: weighted sum onto a base, plain sum,
+        or (dw mode) the dot product of each row with the token's incoming gradient."""
+        x0 = xs[0]
+        k, E, cap = x0.i[0], x0.i[1], x0.i[2]
+        n = len(ranks)
+        E_l = E // n
+        for me, (r, x) in enumerate(zip(ranks, xs)):
+            T = r.pf.shape(x.t[2])[0]
+            H = r.pf.shape(x.t[5])[1]
+            idx, pos = r.mat(x.t[2], T, k).long(), r.mat(x.t[3], T, k).long()
+            w = r.mat(x.t[4], T, k).float() if x.t[4] >= 0 else torch.ones(T, k)
+            got = torch.zeros(T, k, H)
+            for owner in range(n):
+                slab = ranks[owner].mat(xs[owner].t[5], E_l * n * cap, H).float()
+                sel = (idx // E_l == owner) & (pos >= 0)
+                t_i, s_i = torch.nonzero(sel, as_tuple=True)
+                if t_i.numel():
+                    got[t_i, s_i] = slab[((idx[t_i, s_i] % E_l) * n + me) * cap + pos[t_i, s_i]]
+            if x.t[7] >= 0:
+                r.mat(x.t[7], T, k).copy_((got * r.mat(x.t[6], T, H).float()[:, None, :]).sum(-1))
+                continue
+            out = (got * w[:, :, None]).sum(1)
+            if x.t[0] >= 0:
+                out = out + r.mat(x.t[0], T, H).float()
+            r.mat(x.t[1], T, H).copy_(out)
+
     @staticmethod
     def _count(x):
         return (int(x.i[1]) & 0xFFFFFFFF) << 32 | (int(x.i[0]) & 0xFFFFFFFF)
@@ -577,10 +700,12 @@ class PlanInterpreter:
     _local = {K["gemm"]: _k_gemm, K["embed_fwd"]: _k_embed_fwd, K["embed_bwd"]: _k_embed_bwd, K["rmsnorm_fwd"]: _k_rmsnorm_fwd,
               K["rmsnorm_bwd"]: _k_rmsnorm_bwd, K["rope"]: _k_rope, K["attn_fwd"]: _k_attn_fwd, K["attn_bwd"]: _k_attn_bwd,
               K["swiglu_fwd"]: _k_swiglu_fwd, K["swiglu_bwd"]: _k_swiglu_bwd, K["cross_entropy"]: _k_cross_entropy,
-              K["adamw"]: _k_adamw, K["zero"]: _k_zero, K["add"]: _k_add, K["quant_fp8"]: _k_quant_fp8, K["gemm_fp8"]: _k_gemm_fp8}
+              K["adamw"]: _k_adamw, K["zero"]: _k_zero, K["add"]: _k_add, K["quant_fp8"]: _k_quant_fp8, K["gemm_fp8"]: _k_gemm_fp8,
+              K["moe_route"]: _k_moe_route}
     _group_ops = {K["nccl_all_reduce"]: _g_all_reduce, K["nccl_reduce_scatter"]: _g_reduce_scatter,
                   K["nccl_all_gather"]: _g_all_gather, K["cross_entropy_tp"]: _g_cross_entropy_tp, K["ag_gemm"]: _g_ag_gemm,
-                  K["gemm_rs"]: _g_gemm_rs, K["rs_adamw"]: _g_rs_adamw, K["fsdp_ag_gemm"]: _g_fsdp_gather}
+                  K["gemm_rs"]: _g_gemm_rs, K["rs_adamw"]: _g_rs_adamw, K["fsdp_ag_gemm"]: _g_fsdp_gather,
+                  K["moe_dispatch_gemm"]: _g_moe_dispatch, K["moe_gemm_combine"]: _g_moe_combine}
 
 
 def random_state(interp: PlanInterpreter, seed=0, std=0.02):

@@ -40,7 +40,7 @@ def _train_both(text, steps=3, seed=1):
         # the reference reads bf16 weights like the kernels do and keeps the fp32 master / moments
         p = {k: v.to(torch.bfloat16).float().requires_grad_(True) for k, v in master.items()}
         loss = ref.forward_loss(p, tok, tgt, layers=m.num_layers, heads=m.num_heads, kv_heads=m.num_kv_heads,
-                                head_dim=m.head_dim, seq=S, eps=tr.norm_eps, theta=tr.rope_theta)
+                                head_dim=m.head_dim, seq=S, eps=tr.norm_eps, theta=tr.rope_theta, top_k=int(m.moe_top_k) if m.is_moe else 0)
         loss.backward()
         b1, b2 = tr.beta1, tr.beta2
         for k in master:
@@ -137,10 +137,6 @@ def test_block_scaled_e4m3_linear_layers_stay_close_to_the_fp32_model(world, key
     assert 0.05 < drift < 0.4, drift
 
 
-def test_layouts_without_an_interpretation_say_so():
-    from cai_b200.models.plan_interpreter import PlanInterpreter
-    with pytest.raises(NotImplementedError):
-        PlanInterpreter(_cfg("tiny_moe.cfg", 1, ""))
 
 
 def test_a_run_continues_on_another_layout_from_the_state_of_the_first():
@@ -168,3 +164,55 @@ def test_a_run_continues_on_another_layout_from_the_state_of_the_first():
     assert got == pytest.approx(want, abs=1.5e-3), (got, want)
     with pytest.raises(ValueError, match="sequences"):
         second.step(batches[0][0][:3], batches[0][1][:3])
+
+
+MOE = {
+    "two replicas, experts replicated": ("tiny_moe.cfg", 2, "comm = fused", 2),
+    "ep2": ("tiny_moe.cfg", 2, "ep = 2\ncomm = fused", 2),
+    "pp2": ("tiny_moe.cfg", 2, "pp = 2\ncomm = fused", 1),
+    "pp2 x ep2": ("tiny_moe.cfg", 4, "pp = 2\nep = 2\ncomm = fused", 2),
+    "tp2": ("tiny_moe_tp.cfg", 2, "tp = 2\ncomm = fused", 1),
+    "tp2 x ep2": ("tiny_moe_tp.cfg", 4, "tp = 2\nep = 2\ncomm = fused", 2),
+    "tp2 x pp2 x ep2": ("tiny_moe_tp.cfg", 8, "tp = 2\npp = 2\nep = 2\ncomm = fused", 2),
+}
+
+
+def test_mixture_of_experts_on_one_rank_follows_the_fp32_model():
+    """Router (softmax, top-k, renormalised weights), dispatch into the expert slabs, the experts' products over the live
+    rows, combine, and all of it backwards. bf16 activations move a few near-tied routing decisions, so the agreement
+    with the fp32 model is looser than for the dense decoder."""
+    losses, drift = _train_both(_cfg("tiny_moe.cfg", 1, ""))
+    # 512 tokens per step and router gradients that pass through bf16 logit gradients: AdamW's normalised steps turn
+    # more small gradients around than in the dense tests (the gradients themselves agree with autograd to a cosine
+    # of 0.99 and above)
+    assert all(got == pytest.approx(want, abs=5e-3) for got, want in losses) and drift < 0.3, (losses, drift)
+
+
+@pytest.mark.parametrize("name", sorted(MOE))
+def test_mixture_of_experts_layouts_train_like_the_one_rank_job(name):
+    """Experts spread over an expert-parallel group, beside tensor parallelism (the tp x ep ranks form the group, every
+    rank routes its own rows) and inside pipeline stages: same losses as the interpreted one-rank job on the same batches."""
+    from cai_b200.models.plan_interpreter import PlanInterpreter, random_state
+    base, world, keys, dp = MOE[name]
+    job = PlanInterpreter(_cfg(base, world, keys + "\ntie_embeddings = 0"))     # a pipeline unties the head: untie it everywhere
+    one = PlanInterpreter(_cfg(base, 1, f"grad_accum = {2 * dp}\ntie_embeddings = 0"))       # the same global batch on one rank
+    st = random_state(one, seed=2)
+    for k in st:
+        if k.endswith(".wr"):
+            st[k]["master"] *= 10.0      # a decisive router: fewer near-tied choices for bf16 rounding to turn around
+    job.load_state(st)
+    one.load_state(st)
+    m = one.model
+    gen = torch.Generator().manual_seed(6)
+    G = one.rows_per_replica
+    for step in range(3):
+        tok = torch.randint(0, m.vocab_size, (G, int(m.seq_len)), generator=gen)
+        tgt = torch.randint(0, m.vocab_size, (G, int(m.seq_len)), generator=gen)
+        # the first step sees identical weights. Later the summation orders of the layouts differ in the last bits, a few
+        # near-tied routing decisions flip, and the curves part by a few 1e-3
+        assert job.step(tok, tgt) == pytest.approx(one.step(tok, tgt), abs=5e-4 if step == 0 else 5e-3), (name, step)
+    import numpy as np
+    a, b = job.state(), one.state()
+    drift = max(float(np.abs(a[k]["master"] - b[k]["master"]).mean() / (np.abs(b[k]["master"] - st[k]["master"]).mean() + 1e-12))
+                for k in st)
+    assert drift < 0.4, (name, drift)        # a misplaced slab or a lost contribution moves whole tensors (drift near 1 and above)
