@@ -216,3 +216,20 @@ def test_mixture_of_experts_layouts_train_like_the_one_rank_job(name):
     drift = max(float(np.abs(a[k]["master"] - b[k]["master"]).mean() / (np.abs(b[k]["master"] - st[k]["master"]).mean() + 1e-12))
                 for k in st)
     assert drift < 0.4, (name, drift)        # a misplaced slab or a lost contribution moves whole tensors (drift near 1 and above)
+
+
+def test_every_layout_the_advisor_lists_for_four_gpus_computes_the_same_model(tmp_path):
+    """The layouts ``cai_b200.plan.advise`` enumerates (tp x pp x dp, ZeRO-1 and ZeRO-3) are not only priced: each one
+    compiles, and its interpreted job follows the fp32 model on the same global batch."""
+    from cai_b200 import plan
+    from cai_b200.plan.advise import candidates
+    text = _cfg("tiny_mp.cfg", 1, "grad_accum = 4")          # global batch: 8 sequences
+    base = plan.describe(text)
+    seen = []
+    for cand in candidates(base, 4):
+        keys = (f"tp = {cand['tp']}\npp = {cand['pp']}\nzero_stage = {cand['zero_stage']}\ngrad_accum = {cand['grad_accum']}\n"
+                "comm = fused")
+        losses, drift = _train_both(_cfg("tiny_mp.cfg", 4, keys), steps=2)
+        assert all(got == pytest.approx(want, abs=1.5e-3) for got, want in losses) and drift < 0.05, (cand, losses, drift)
+        seen.append((cand["tp"], cand["pp"], cand["dp"], cand["zero_stage"]))
+    assert {(4, 1, 1, 1), (1, 1, 4, 3), (2, 2, 1, 1), (2, 1, 2, 3), (1, 2, 2, 3), (1, 4, 1, 1)} <= set(seen), seen
