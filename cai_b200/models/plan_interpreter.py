@@ -16,13 +16,16 @@ Mixture-of-experts plans are interpreted too: router, slot assignment in token o
 the experts' products over the live rows of the slabs, combine, and the backward of all of it. A record without an
 interpretation raises ``NotImplementedError``.
 
-Ranks run as coroutines in program order. That order is a legal serialisation of a rank's streams (a wait never
-precedes its record in a table); a collective runs when every member of its group has reached it (members of a group
-issue identical sequences); a pipeline send deposits its message and continues, a receive blocks until the message
-is there. A job whose ranks cannot all finish raises instead of hanging.
+By default every rank issues its table in program order. That order is a legal serialisation of a rank's streams (a
+wait never precedes its record in a table); a collective runs when every member of its group has reached it; a
+pipeline send deposits its message and continues, a receive blocks until the message is there. A job whose ranks
+cannot all finish raises instead of hanging. With ``order = "random"`` the six streams of every rank advance
+independently, held back only by the plan's own record / wait events, and the next op is drawn at random among all that
+may start: a dynamic check that the events order every dependence (the static proof is ``verify_hazards``).
 """
 from __future__ import annotations
 
+import random
 import tempfile
 from collections import defaultdict, deque
 from pathlib import Path
@@ -107,7 +110,10 @@ def _attention(q, k, v, B, S, scale):
 class PlanInterpreter:
     """All ranks of one job, interpreted on the host. ``config_text``: the job's configuration (executable layout)."""
 
-    def __init__(self, config_text: str):
+    def __init__(self, config_text: str, order: str = "program", seed: int = 0):
+        if order not in ("program", "random"):
+            raise ValueError("order is 'program' or 'random'")
+        self.order, self.seed = order, seed
         self.config_text = config_text
         d = planlib.describe(config_text)
         self.world = int(d["world_size"])
@@ -195,27 +201,69 @@ class PlanInterpreter:
         return [within - tp_id + t + (first_dp + i) * replica for i in range(ep) for t in range(tp)]
 
     def _run(self):
+        """One optimizer step of every rank. ``order = "program"``: each rank issues its table in program order (one
+        legal serialisation of its streams). ``order = "random"``: every rank keeps one queue per stream, a record marks
+        its event when the stream reaches it, a wait holds its stream until the event is marked, and among all ops that
+        could start the next one is drawn at random: any interleaving the events of the plan allow. A plan whose events
+        order every dependence gives the same result under every such interleaving; a missing edge shows as a result
+        that depends on the draw."""
         self.mail = defaultdict(deque)          # (src rank, dst rank, channel) -> messages
-        self.pending = {}                       # (group members, call index) -> {rank: request}
-        self.calls = defaultdict(int)           # (rank, group members) -> collectives issued
-        gens = {r.rank: self._program(r) for r in self.ranks}
-        blocked = {}
-        while gens:
-            progress = False
-            for rank in list(gens):
-                want = blocked.get(rank)
-                if want is not None and not self._ready(want):
+        self.pending = {}                       # collective key -> {rank: request}
+        self.calls = defaultdict(int)           # per rank and channel: collectives issued so far
+        rng = random.Random(self.seed * 1000003 + self.step_count)
+        queues, recorded_before, marked = {}, {}, {}
+        for r in self.ranks:
+            ops = r.pf.ops
+            marked[r.rank] = set()
+            if self.order == "program":
+                queues[(r.rank, 0)] = deque(i for i, op in enumerate(ops)
+                                            if op.exec and op.kind not in (planlib.OP_EVENT_RECORD, planlib.OP_EVENT_WAIT))
+                continue
+            seen = set()
+            for i, op in enumerate(ops):
+                if op.kind == planlib.OP_EVENT_WAIT:
+                    recorded_before[(r.rank, i)] = op.aux0 in seen      # a wait on an event nothing recorded yet passes at once
+                elif op.kind == planlib.OP_EVENT_RECORD:
+                    seen.add(op.aux0)
+                elif not op.exec:
                     continue
-                try:
-                    blocked[rank] = gens[rank].send(None) if want is None else gens[rank].send(True)
-                    progress = True
-                except StopIteration:
-                    del gens[rank]
-                    blocked.pop(rank, None)
-                    progress = True
-            if not progress:
-                waiting = {rk: w[:2] for rk, w in blocked.items()}
-                raise RuntimeError(f"the ranks wait for each other and none can continue: {waiting}")
+                queues.setdefault((r.rank, int(op.stream_id)), deque()).append(i)
+        waiting = {}                            # queue -> what its head op waits for
+        while True:
+            live = [key for key, dq in queues.items() if dq]
+            if not live:
+                return
+            runnable = []
+            for key in live:
+                rank, i = key[0], queues[key][0]
+                if key in waiting:
+                    if self._ready(waiting[key]):
+                        runnable.append(key)
+                    continue
+                op = self.ranks[rank].pf.ops[i]
+                if op.kind == planlib.OP_EVENT_WAIT and recorded_before[(rank, i)] and op.aux0 not in marked[rank]:
+                    continue
+                runnable.append(key)
+            if not runnable:
+                stuck = {key: waiting.get(key, "an event") for key in live}
+                raise RuntimeError(f"the ranks wait for each other and none can continue: {stuck}")
+            # program order: stay with the lowest rank until it blocks (deterministic); random: any op that may start
+            key = runnable[0] if self.order == "program" else rng.choice(runnable)
+            r = self.ranks[key[0]]
+            i = queues[key][0]
+            op = r.pf.ops[i]
+            if op.kind == planlib.OP_EVENT_RECORD:
+                marked[r.rank].add(op.aux0)
+                queues[key].popleft()
+                continue
+            if op.kind == planlib.OP_EVENT_WAIT:
+                queues[key].popleft()
+                continue
+            token = self._issue(r, op, resumed=waiting.pop(key, None))
+            if token is None:
+                queues[key].popleft()
+            else:
+                waiting[key] = token
 
     def _ready(self, want):
         what = want[0]
@@ -225,53 +273,57 @@ class PlanInterpreter:
             return want[1] not in self.pending      # the last member to arrive ran it and removed the entry
         return True
 
-    def _collective(self, r, kind, fn, payload, members=None):
-        """Generator helper: join call number n of the rank's group; the last member to arrive runs ``fn``."""
-        mem = tuple(members if members is not None else self.members(kind, r.rank))
-        n = self.calls[(r.rank, mem)]
-        self.calls[(r.rank, mem)] += 1
-        key = (mem, n)
+    def _collective(self, r, key, members, fn, payload):
+        """Join one collective call; the last member to arrive runs ``fn`` for the whole group."""
         slot = self.pending.setdefault(key, {})
         slot[r.rank] = payload
-        if len(slot) == len(mem):
-            fn([self.ranks[m] for m in mem], [slot[m] for m in mem])
+        if len(slot) == len(members):
+            fn([self.ranks[m] for m in members], [slot[m] for m in members])
             del self.pending[key]
             return None
         return ("coll", key)
 
-    # ------------------------------------------------------------------ a rank's program
-    def _program(self, r: _Rank):
-        pf = r.pf
-        for op in pf.ops:
-            if op.kind in (planlib.OP_EVENT_RECORD, planlib.OP_EVENT_WAIT) or not op.exec:
-                continue
-            x = pf.exec[op.exec - 1]
-            k = int(x.kernel)
-            handler = self._local.get(k)
-            if handler is not None:
-                handler(self, r, x)
-                continue
-            if k == K["nccl_send"]:
-                peer = self.members(planlib.GROUP_PP, r.rank)[x.i[4]]
-                n = (int(x.i[1]) & 0xFFFFFFFF) << 32 | (int(x.i[0]) & 0xFFFFFFFF)
-                self.mail[(r.rank, peer, int(op.stream_id == ST_IO))].append(r.flat(x.t[0], n).clone())
-                continue
-            if k == K["nccl_recv"]:
-                peer = self.members(planlib.GROUP_PP, r.rank)[x.i[4]]
-                key = (peer, r.rank, int(op.stream_id == ST_IO))
-                if not self.mail[key]:
-                    yield ("recv", key)
-                n = (int(x.i[1]) & 0xFFFFFFFF) << 32 | (int(x.i[0]) & 0xFFFFFFFF)
-                r.flat(x.t[1], n).copy_(self.mail[key].popleft())
-                continue
-            coll = self._group_ops.get(k)
-            if coll is None:
-                raise NotImplementedError(f"kernel '{planlib.KERNEL_NAMES[k]}' is not interpreted")
+    # ------------------------------------------------------------------ one op of a rank
+    def _issue(self, r: _Rank, op, resumed=None):
+        """Runs the op, or returns what it has to wait for (``resumed``: the wait it came back from)."""
+        x = r.pf.exec[op.exec - 1]
+        k = int(x.kernel)
+        if resumed is not None and resumed[0] == "coll":
+            return None                                         # the last member to arrive ran it for everyone
+        handler = self._local.get(k)
+        if handler is not None:
+            handler(self, r, x)
+            return None
+        if k == K["nccl_send"]:
+            peer = self.members(planlib.GROUP_PP, r.rank)[x.i[4]]
+            self.mail[(r.rank, peer, int(op.stream_id == ST_IO))].append(r.flat(x.t[0], self._count(x)).clone())
+            return None
+        if k == K["nccl_recv"]:
+            peer = self.members(planlib.GROUP_PP, r.rank)[x.i[4]]
+            key = (peer, r.rank, int(op.stream_id == ST_IO))
+            if not self.mail[key]:
+                return ("recv", key)
+            r.flat(x.t[1], self._count(x)).copy_(self.mail[key].popleft())
+            return None
+        coll = self._group_ops.get(k)
+        if coll is None:
+            raise NotImplementedError(f"kernel '{planlib.KERNEL_NAMES[k]}' is not interpreted")
+        if k in (K["moe_dispatch_gemm"], K["moe_gemm_combine"]):
+            members = tuple(self.expert_group(r))
+        else:
             kind = (planlib.GROUP_TP if k == K["cross_entropy_tp"] else planlib.GROUP_DP if k == K["fsdp_ag_gemm"] else int(x.i[3]))
-            members = self.expert_group(r) if k in (K["moe_dispatch_gemm"], K["moe_gemm_combine"]) else None
-            wait = self._collective(r, kind, coll.__get__(self), x, members)
-            if wait is not None:
-                yield wait
+            members = tuple(self.members(kind, r.rank))
+        # which call of the group this is: the fused kernels carry a sequence number (their signal epoch); NCCL calls of
+        # one communicator match in issue order, and a communicator belongs to one stream (the vocabulary-parallel
+        # cross-entropy has the tensor-parallel group's second one)
+        if k in (K["nccl_all_reduce"], K["nccl_reduce_scatter"], K["nccl_all_gather"], K["cross_entropy_tp"]):
+            lane = ("ce",) if k == K["cross_entropy_tp"] else ("nccl", int(op.stream_id))
+            n = self.calls[(r.rank, members, lane)]
+            self.calls[(r.rank, members, lane)] += 1
+            key = (members, lane, n)
+        else:
+            key = (members, "seq", int(x.i[4]), self.step_count)
+        return self._collective(r, key, members, coll.__get__(self), x)
 
     # ------------------------------------------------------------------ records of one rank
     def _gemm_core(self, r, A, B, M, N, Kd, ta, tb):

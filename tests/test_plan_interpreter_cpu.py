@@ -233,3 +233,71 @@ def test_every_layout_the_advisor_lists_for_four_gpus_computes_the_same_model(tm
         assert all(got == pytest.approx(want, abs=1.5e-3) for got, want in losses) and drift < 0.05, (cand, losses, drift)
         seen.append((cand["tp"], cand["pp"], cand["dp"], cand["zero_stage"]))
     assert {(4, 1, 1, 1), (1, 1, 4, 3), (2, 2, 1, 1), (2, 1, 2, 3), (1, 2, 2, 3), (1, 4, 1, 1)} <= set(seen), seen
+
+
+RANDOM_ORDER = {
+    "tp2 x pp2 fused": ("tiny_mp.cfg", 4, "tp = 2\npp = 2\ncomm = fused"),
+    "tp2 x dp2 ZeRO-3": ("tiny_mp.cfg", 4, "tp = 2\ncomm = fused\nzero_stage = 3"),
+    "dp2 ZeRO-3, per-layer buckets": ("tiny_mp.cfg", 2, "comm = fused\nzero_stage = 3"),
+    "tp2 NCCL-only": ("tiny_mp.cfg", 2, "tp = 2\ncomm = baseline"),
+    "MoE tp2 x ep2": ("tiny_moe_tp.cfg", 4, "tp = 2\nep = 2\ncomm = fused"),
+}
+
+
+def _one_step(job, st, seed=1):
+    job.load_state(st)
+    m = job.model
+    gen = torch.Generator().manual_seed(seed)
+    G = job.rows_per_replica * int(job.hdr.dp)
+    tok = torch.randint(0, m.vocab_size, (G, int(m.seq_len)), generator=gen)
+    tgt = torch.randint(0, m.vocab_size, (G, int(m.seq_len)), generator=gen)
+    return job.step(tok, tgt), job.state()
+
+
+@pytest.mark.parametrize("name", sorted(RANDOM_ORDER))
+def test_any_interleaving_the_events_allow_gives_the_same_bits(name):
+    """The streams of every rank advance independently, held back only by the plan's record / wait events, and the
+    next op is drawn at random: loss and parameters must equal the program-order run bit for bit, or some dependence
+    between streams is not ordered by an event (the dynamic counterpart of the static hazard proof)."""
+    import numpy as np
+    from cai_b200.models.plan_interpreter import PlanInterpreter, random_state
+    base, world, keys = RANDOM_ORDER[name]
+    text = _cfg(base, world, keys)
+    ref = PlanInterpreter(text)
+    st = random_state(ref, seed=3)
+    want_loss, want = _one_step(ref, st)
+    for seed in (1, 2):
+        loss, got = _one_step(PlanInterpreter(text, order="random", seed=seed), st)
+        assert loss == want_loss, (name, seed)
+        assert all(np.array_equal(got[k][key], want[k][key]) for k in want for key in ("master", "m", "v")), (name, seed)
+
+
+def test_a_missing_wait_shows_up_under_random_interleaving():
+    """Control: the weight-gradient GEMMs of a tensor-parallel plan run on the second compute stream behind waits on
+    their operands. With those waits disarmed the random interleaving runs some of them early and the step's result
+    changes; in program order the same broken plan still looks fine, which is why the check draws."""
+    import numpy as np
+    from cai_b200 import plan
+    from cai_b200.models.plan_interpreter import PlanInterpreter, random_state
+    text = _cfg("tiny_mp.cfg", 2, "tp = 2\ncomm = fused")
+    ref = PlanInterpreter(text)
+    st = random_state(ref, seed=3)
+    _, want = _one_step(ref, st)
+
+    def disarm(job):
+        n = 0
+        for r in job.ranks:
+            for op in r.pf.ops:
+                if op.kind == plan.OP_EVENT_WAIT and op.stream_id == 1:
+                    op.aux0 = 0x7FFFFFFF            # an event nothing records: the wait passes at once
+                    n += 1
+        return n
+
+    ordered = PlanInterpreter(text)
+    assert disarm(ordered) > 0
+    _, got = _one_step(ordered, st)
+    assert all(np.array_equal(got[k]["master"], want[k]["master"]) for k in want)
+    drawn = PlanInterpreter(text, order="random", seed=1)
+    disarm(drawn)
+    _, got = _one_step(drawn, st)
+    assert any(not np.array_equal(got[k]["master"], want[k]["master"]) for k in want)
