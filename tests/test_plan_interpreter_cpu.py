@@ -92,10 +92,10 @@ LAYOUTS = {
 @pytest.mark.parametrize("name", sorted(LAYOUTS))
 def test_every_layout_trains_like_the_one_device_model(name):
     world, keys = LAYOUTS[name]
-    losses, drift = _train_both(_cfg("tiny_mp.cfg", world, keys))
+    losses, drift = _train_both(_cfg("tiny_mp.cfg", world, keys), steps=2)
     for got, want in losses:
         assert got == pytest.approx(want, abs=1.5e-3), (name, losses)
-    # parameters after three AdamW steps: apart by a few percent of the distance they moved (bf16 storage of
+    # parameters after two AdamW steps: apart by a few percent of the distance they moved (bf16 storage of
     # activations and weights turns a few near-zero gradients around; a wrong shard or a lost contribution moves whole tensors)
     assert drift < 0.05, (name, drift)
 
