@@ -773,3 +773,72 @@ def random_state(interp: PlanInterpreter, seed=0, std=0.02):
             master = np.ones(gshape, dtype=np.float32) if gain else (g.standard_normal(gshape) * std).astype(np.float32)
             state[name] = {"master": master, "m": np.zeros(gshape, dtype=np.float32), "v": np.zeros(gshape, dtype=np.float32)}
     return state
+
+
+def check_against_reference(config_text: str, steps: int = 3, seed: int = 1, order: str = "program"):
+    """Trains the interpreted job and the one-device fp32 model (``reference_torch.forward_loss`` + AdamW on fp32 master
+    weights read as bf16, like the kernels read them) on the same random batches from the same random parameters.
+    Returns ``(losses, drift)``: per step ``(interpreted, reference)``, and the largest mean distance between the two
+    runs' master parameters relative to how far the parameter moved (a few percent for a correct layout: bf16 storage
+    turns some near-zero gradients around; a wrong shard or a lost contribution moves whole tensors)."""
+    from . import reference_torch as ref
+    it = PlanInterpreter(config_text, order=order, seed=seed)
+    st = random_state(it, seed=seed)
+    it.load_state(st)
+    m, tr = it.model, it.train
+    master = {k: torch.tensor(v["master"]).clone() for k, v in st.items()}
+    start = {k: v.clone() for k, v in master.items()}
+    mom = {k: torch.zeros_like(v) for k, v in master.items()}
+    var = {k: torch.zeros_like(v) for k, v in master.items()}
+    G, S = it.rows_per_replica * int(it.hdr.dp), int(m.seq_len)
+    gen = torch.Generator().manual_seed(5)
+    losses = []
+    for step in range(1, steps + 1):
+        tok = torch.randint(0, m.vocab_size, (G, S), generator=gen)
+        tgt = torch.randint(0, m.vocab_size, (G, S), generator=gen)
+        got = it.step(tok, tgt)
+        p = {k: v.to(torch.bfloat16).float().requires_grad_(True) for k, v in master.items()}
+        loss = ref.forward_loss(p, tok, tgt, layers=m.num_layers, heads=m.num_heads, kv_heads=m.num_kv_heads,
+                                head_dim=m.head_dim, seq=S, eps=tr.norm_eps, theta=tr.rope_theta,
+                                top_k=int(m.moe_top_k) if m.is_moe else 0)
+        loss.backward()
+        b1, b2 = tr.beta1, tr.beta2
+        for k in master:
+            g = p[k].grad
+            mom[k] = b1 * mom[k] + (1 - b1) * g
+            var[k] = b2 * var[k] + (1 - b2) * g * g
+            master[k] = master[k] - tr.lr * ((mom[k] / (1 - b1 ** step)) / ((var[k] / (1 - b2 ** step)).sqrt() + tr.adam_eps)
+                                             + tr.weight_decay * master[k])
+        losses.append((got, float(loss.detach())))
+    end = it.state()
+    drift = max(float((torch.tensor(end[k]["master"]) - master[k]).abs().mean() / ((master[k] - start[k]).abs().mean() + 1e-12))
+                for k in master)
+    return losses, drift
+
+
+def main(argv=None):
+    """``python -m cai_b200.models.plan_interpreter CONFIG [--steps N] [--order random]``: before a layout goes to the
+    GPUs, run its executable plans on the host, every rank in this process, next to the one-device fp32 model. Meant
+    for small stand-ins of the real model (same layout keys, small sizes): the arenas of all ranks live in host memory."""
+    import argparse
+    ap = argparse.ArgumentParser(description="interpret a configuration's executable plans on the host and compare with the fp32 model")
+    ap.add_argument("config")
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--order", choices=("program", "random"), default="program",
+                    help="random: any interleaving of a rank's streams that the plan's events allow")
+    ap.add_argument("--seed", type=int, default=1)
+    ap.add_argument("--tolerance", type=float, default=5e-3, help="largest accepted |interpreted - reference| loss")
+    a = ap.parse_args(argv)
+    planlib.set_log_level("warn")
+    losses, drift = check_against_reference(Path(a.config).read_text(), a.steps, a.seed, a.order)
+    worst = 0.0
+    for i, (got, want) in enumerate(losses, 1):
+        print(f"step {i}: interpreted {got:.5f}   fp32 model {want:.5f}   difference {got - want:+.5f}")
+        worst = max(worst, abs(got - want))
+    ok = worst <= a.tolerance and drift < 0.5
+    print(f"parameters apart by {drift * 100:.1f}% of the distance they moved; " + ("PASS" if ok else "FAIL"))
+    return 0 if ok else 1
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

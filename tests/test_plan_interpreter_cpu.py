@@ -19,41 +19,8 @@ def _built():
 def _train_both(text, steps=3, seed=1):
     """Losses of the interpreted job and of the reference model over the same batches, and how far their fp32 master
     parameters are apart at the end relative to how far they moved."""
-    from cai_b200 import plan
-    from cai_b200.models import reference_torch as ref
-    from cai_b200.models.plan_interpreter import PlanInterpreter, random_state
-    it = PlanInterpreter(text)
-    st = random_state(it, seed=seed)
-    it.load_state(st)
-    m, tr = it.model, it.train
-    master = {k: torch.tensor(v["master"]).clone() for k, v in st.items()}
-    start = {k: v.clone() for k, v in master.items()}
-    mom = {k: torch.zeros_like(v) for k, v in master.items()}
-    var = {k: torch.zeros_like(v) for k, v in master.items()}
-    G, S = int(plan.describe(text)["global_batch"]), int(m.seq_len)
-    gen = torch.Generator().manual_seed(5)
-    losses = []
-    for step in range(1, steps + 1):
-        tok = torch.randint(0, m.vocab_size, (G, S), generator=gen)
-        tgt = torch.randint(0, m.vocab_size, (G, S), generator=gen)
-        got = it.step(tok, tgt)
-        # the reference reads bf16 weights like the kernels do and keeps the fp32 master / moments
-        p = {k: v.to(torch.bfloat16).float().requires_grad_(True) for k, v in master.items()}
-        loss = ref.forward_loss(p, tok, tgt, layers=m.num_layers, heads=m.num_heads, kv_heads=m.num_kv_heads,
-                                head_dim=m.head_dim, seq=S, eps=tr.norm_eps, theta=tr.rope_theta, top_k=int(m.moe_top_k) if m.is_moe else 0)
-        loss.backward()
-        b1, b2 = tr.beta1, tr.beta2
-        for k in master:
-            g = p[k].grad
-            mom[k] = b1 * mom[k] + (1 - b1) * g
-            var[k] = b2 * var[k] + (1 - b2) * g * g
-            master[k] = master[k] - tr.lr * ((mom[k] / (1 - b1 ** step)) / ((var[k] / (1 - b2 ** step)).sqrt() + tr.adam_eps)
-                                             + tr.weight_decay * master[k])
-        losses.append((got, float(loss.detach())))
-    end = it.state()
-    drift = max(float((torch.tensor(end[k]["master"]) - master[k]).abs().mean() / ((master[k] - start[k]).abs().mean() + 1e-12))
-                for k in master)
-    return losses, drift
+    from cai_b200.models.plan_interpreter import check_against_reference
+    return check_against_reference(text, steps, seed)
 
 
 def _cfg(base, world, keys):
@@ -301,3 +268,13 @@ def test_a_missing_wait_shows_up_under_random_interleaving():
     disarm(drawn)
     _, got = _one_step(drawn, st)
     assert any(not np.array_equal(got[k]["master"], want[k]["master"]) for k in want)
+
+
+def test_command_line_check_of_a_configuration(tmp_path, capsys):
+    from cai_b200.models import plan_interpreter
+    cfg = tmp_path / "job.cfg"
+    cfg.write_text(_cfg("tiny_mp.cfg", 2, "pp = 2"))
+    assert plan_interpreter.main([str(cfg), "--steps", "2", "--order", "random"]) == 0
+    out = capsys.readouterr().out
+    assert "step 2: interpreted" in out and out.strip().endswith("PASS")
+    assert plan_interpreter.main([str(cfg), "--steps", "1", "--tolerance", "0"]) == 1      # nothing matches to the last bit
