@@ -2,7 +2,7 @@
 # compiles the sm_100a kernel library, the GPU-free host library and the tools in-tree with nvcc / g++.
 PYTHON ?= python
 
-.PHONY: all host test gputest demo predict clean
+.PHONY: all host test gputest demo predict interpret clean
 
 all:            ## kernels (sm_100a), host library, tools
 	$(PYTHON) -m cai_b200._build
@@ -41,6 +41,9 @@ demo: host
 
 predict: host   ## rank the executable layouts of CONFIG on GPUS B200s by predicted step time
 	$(PYTHON) -m cai_b200.plan.advise $(or $(CONFIG),configs/b200_tp8.cfg) --gpus $(or $(GPUS),8)
+
+interpret: host ## run CONFIG's executable plans on the host, every rank in one process, next to the fp32 model (small models)
+	$(PYTHON) -m cai_b200.models.plan_interpreter $(or $(CONFIG),configs/tiny_mp.cfg) $(if $(ORDER),--order $(ORDER))
 
 clean:
 	rm -rf build bin out cai_b200/lib
