@@ -40,7 +40,8 @@ def candidates(base: dict, world: int, mb_groups=(0,)):
             grad_accum = global_batch // per_replica
             if pp > 1 and grad_accum < pp:
                 continue
-            for zero in ((1, 3) if (dp > 1 and not base["is_moe"]) else (1,)):
+            stages = (1,) if dp == 1 or base["is_moe"] else (1, 2, 3) if tp == 1 else (1, 3)      # ZeRO-2 shards gradients through the tp = 1 buckets
+            for zero in stages:
                 for g in mb_groups:
                     if g and (grad_accum % g or pp > 1 or zero == 3 or base["is_moe"]):
                         continue        # grouping exists for dense, unpipelined, ZeRO-1 schedules only

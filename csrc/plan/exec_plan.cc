@@ -401,6 +401,13 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     const bool zero3 = cfg.train.zero_stage >= 3 && d.dp > 1 && cfg.train.comm_mode != 0 && !moe;
     if (cfg.train.zero_stage >= 3 && d.dp > 1 && !zero3)
         return failf(err, ERR_INVALID, "zero_stage = 3 needs comm = fused and a dense model");
+    // ZeRO-2: parameters stay whole on every rank (as with zero_stage = 1), but the fp32 gradients are sharded like under
+    // ZeRO-3: a layer's weight gradients of one microbatch land in one of two alternating layer-sized buffers and the
+    // layer's bucket kernel sums the members' buffers into the owners' shard-sized accumulators. Needs the per-layer
+    // buckets, which exist for tp = 1.
+    const bool zero2 = cfg.train.zero_stage == 2 && d.dp > 1 && !moe && cfg.train.comm_mode != 0 && d.tp == 1 && cfg.train.dp_buckets != 0;
+    if (cfg.train.zero_stage == 2 && d.dp > 1 && !zero2)
+        return failf(err, ERR_INVALID, "zero_stage = 2 needs comm = fused, tp = 1, per-layer buckets (dp_buckets = 1) and a dense model");
     // fp8 parameters: forward and input-gradient GEMMs of the linear layers run in e4m3 with block scales
     // (tp = 1, dense); weight gradients, attention, the LM head and everything else stay bf16.
     if (m.param_dtype == DT_FP8_E4M3 && moe)
@@ -478,7 +485,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
         std::snprintf(nm, 40, "L%u.%s", base_layer + l, suffix);
         return nm;
     };
-    if (zero3) {
+    if (zero3 || zero2) {      // the small tensors first, then every layer's matrices as one contiguous group
         char nm[40];
         for (uint32_t l = 0; l < b.layers; ++l) {
             L[l].g1 = b.param(lname(nm, l, "g1"), 1, H, 0.f);
@@ -601,7 +608,7 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
     // one of two alternating layer-sized fp32 buffers; the layer's bucket kernel (every microbatch) sums the
     // members' buffers for the elements this rank owns into a shard-sized accumulator, and on the last microbatch
     // goes on to AdamW. Only the small resident group (embedding, gains, head) keeps full-size gradients.
-    const bool shard_grads = zero3 && cfg.train.dp_buckets != 0 && b.layers > 0 && d.tp == 1;
+    const bool shard_grads = (zero3 || zero2) && cfg.train.dp_buckets != 0 && b.layers > 0 && d.tp == 1;
     int grad_stage[2] = {-1, -1}, grad_acc = -1;
     if (shard_grads) {
         uint64_t max_layer = 0;
@@ -852,7 +859,9 @@ int build_plan_v2(const Config& cfg, const Decomp& d, uint32_t rank, uint64_t ph
             }
             if (staged) e.t[5] = sub(grad_acc, TC_GRAD, DT_FP32, o, own_hi - own_lo);
         }
-        if (!zero3) e.t[4] = sub(b.flat_param, TC_PARAM, DT_BF16, lo, hi - lo);
+        // replicated parameters: the owners push the bucket's new values to every member, in the launch that updates
+        // (a launch that only reduces into the accumulators touches no parameter)
+        if (!zero3 && (!staged || last)) e.t[4] = sub(b.flat_param, TC_PARAM, DT_BF16, lo, hi - lo);
         e.i[0] = static_cast<int32_t>(lo >> 9); e.i[1] = static_cast<int32_t>(hi >> 9); e.i[2] = max_ctas;
         e.i[3] = GROUP_DP; e.i[4] = static_cast<int32_t>(b.next_seq++);
         e.f[0] = 1.0f / d.dp;

@@ -160,7 +160,7 @@ struct TrainSpec {
     float rope_theta = 10000.f, norm_eps = 1e-6f, init_std = 0.02f;
     uint32_t seed = 0;
     uint32_t tie_embeddings = 1;
-    uint32_t zero_stage = 1;      // 1 = optimizer state sharded over dp (fused path), 3 = bf16 parameters sharded too
+    uint32_t zero_stage = 1;      // 1 = optimizer state sharded over dp (fused path), 2 = fp32 gradients sharded too, 3 = bf16 parameters sharded too
     uint32_t fp8_block = 128;
     uint32_t comm_mode = 1;       // 0 = NCCL-only baseline ops, 1 = fused compute+collective kernels
     uint32_t ce_chunk = 4096;     // rows of logits materialised at a time (the head's weight gradient is read-modify-written once per chunk)

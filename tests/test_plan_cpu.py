@@ -217,6 +217,19 @@ def test_plan_variants_compile_and_verify(tmp_path):
     off = _variant(tmp_path, "tp2_serial", "tp = 2\ncomm = fused\nwgrad_overlap = 0\n", world=2)
     assert not [op for op in off.ops if op.exec and int(off.exec[op.exec - 1].kernel) == plan.K_GEMM and op.stream_id == 1]
     # refused combinations
+    # ZeRO-2: parameters whole as under ZeRO-1, gradients staged per layer and reduced into the owners' accumulators
+    z2 = _variant(tmp_path, "zero2", "comm = fused\nzero_stage = 2\nmb_group = 1\n", world=2)
+    assert plan.K_FSDP_AG_GEMM not in kernels(z2)
+    assert [x for x in z2.exec if int(x.kernel) == plan.K_RS_ADAMW and (x.flags & 4) and not (x.flags & 1)]
+    n2 = z2.named_dict()
+    assert z2.tensors[n2["@flat_param"].tensor].nbytes == z1.tensors[n1["@flat_param"].tensor].nbytes
+    # what it saves grows with the depth: per-layer buffers for two layers and a shard-sized accumulator instead of all gradients
+    deep1 = _variant(tmp_path, "zero1_deep", "comm = fused\nnum_layers = 12\n", world=2)
+    deep2 = _variant(tmp_path, "zero2_deep", "comm = fused\nzero_stage = 2\nnum_layers = 12\n", world=2)
+    assert deep2.class_bytes()["grad"] < 0.8 * deep1.class_bytes()["grad"]
+    with pytest.raises(plan.PlanError):      # the staged buckets exist for tp = 1
+        plan.compile_plans((ROOT / "configs" / "tiny_mp.cfg").read_text() + "\ngpus_per_rack = 4\ngpus_per_tray = 4\ncomm = fused\nzero_stage = 2\ntp = 2\n",
+                           tmp_path / "bad_z2", version=2, text=True)
     # ZeRO-3 beside tensor parallelism: every rank shards its slice of the weights over its data-parallel group; the
     # gathers are kernels of their own (none rides in a GEMM) and the gradients stay whole
     z3tp = _variant(tmp_path, "zero3_tp2", "comm = fused\nzero_stage = 3\ntp = 2\n", world=4)

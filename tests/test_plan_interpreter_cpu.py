@@ -40,6 +40,8 @@ LAYOUTS = {
     "dp2 fused": (2, "comm = fused"),
     "dp2 fused, one bucket": (2, "comm = fused\ndp_buckets = 0"),
     "dp2 NCCL-only": (2, "comm = baseline"),
+    "dp2 ZeRO-2": (2, "comm = fused\nzero_stage = 2\nmb_group = 1"),
+    "pp2 x dp2 ZeRO-2": (4, "pp = 2\ncomm = fused\nzero_stage = 2"),
     "dp2 ZeRO-3": (2, "comm = fused\nzero_stage = 3"),
     "dp2 ZeRO-3, full gradients": (2, "comm = fused\nzero_stage = 3\ndp_buckets = 0"),
     "tp4 fused": (4, "tp = 4\ncomm = fused"),
@@ -206,6 +208,7 @@ RANDOM_ORDER = {
     "tp2 x pp2 fused": ("tiny_mp.cfg", 4, "tp = 2\npp = 2\ncomm = fused"),
     "tp2 x dp2 ZeRO-3": ("tiny_mp.cfg", 4, "tp = 2\ncomm = fused\nzero_stage = 3"),
     "dp2 ZeRO-3, per-layer buckets": ("tiny_mp.cfg", 2, "comm = fused\nzero_stage = 3"),
+    "dp2 ZeRO-2": ("tiny_mp.cfg", 2, "comm = fused\nzero_stage = 2\nmb_group = 1"),
     "tp2 NCCL-only": ("tiny_mp.cfg", 2, "tp = 2\ncomm = baseline"),
     "MoE tp2 x ep2": ("tiny_moe_tp.cfg", 4, "tp = 2\nep = 2\ncomm = fused"),
 }

@@ -50,7 +50,7 @@ def _files(path, world):
 
 LAYOUTS = {
     "dense": ("tiny_mp.cfg", [(4, "tp = 2\npp = 2"), (2, "tp = 1\npp = 1"), (2, "zero_stage = 3"), (4, "tp = 4"),
-                              (4, "tp = 2\nzero_stage = 3"), (4, "pp = 2\nzero_stage = 3"), (1, "")]),
+                              (4, "tp = 2\nzero_stage = 3"), (4, "pp = 2\nzero_stage = 3"), (2, "zero_stage = 2"), (1, "")]),
     "moe": ("tiny_moe_tp.cfg", [(4, "tp = 2\nep = 2"), (2, "ep = 2"), (2, "tp = 2"), (4, "pp = 2\nep = 2"), (1, "")]),
 }
 
