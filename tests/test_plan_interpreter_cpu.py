@@ -281,3 +281,28 @@ def test_command_line_check_of_a_configuration(tmp_path, capsys):
     out = capsys.readouterr().out
     assert "step 2: interpreted" in out and out.strip().endswith("PASS")
     assert plan_interpreter.main([str(cfg), "--steps", "1", "--tolerance", "0"]) == 1      # nothing matches to the last bit
+
+
+SMALL = "\nhidden_size = 256\nffn_hidden = 1024\nnum_layers = 4\nnum_heads = 8\nnum_kv_heads = 8\nvocab_size = 2048\nseq_len = 256\n"
+BENCH_LAYOUTS = {
+    "tp8": ("tp8", SMALL),                                              # tp 8 fused, microbatches launched together
+    "pp2tp4": ("pp2tp4", SMALL + "num_kv_heads = 4\n"),                 # pp 2 x tp 4, full recompute, sixteen microbatches
+    "fsdp8b": ("fsdp8b", SMALL),                                        # dp 8, ZeRO-3, e4m3 linear layers
+    "moe_ep8": ("moe_ep8", SMALL + "ffn_hidden = 256\n"),               # 64 experts, top-8, ep 8
+}
+
+
+@pytest.mark.parametrize("name", sorted(BENCH_LAYOUTS))
+def test_the_benchmark_layouts_scaled_down_on_eight_ranks(name):
+    """The layouts ``bench.py`` measures on eight GPUs, with the model shrunk to fit a host: same parallel keys, same
+    schedule options, every rank interpreted."""
+    import sys
+    sys.path.insert(0, str(ROOT))
+    import bench
+    from cai_b200.models.plan_interpreter import check_against_reference
+    config, extra = BENCH_LAYOUTS[name]
+    losses, drift = check_against_reference(bench.config_text(8, "fused", config) + extra, steps=2)
+    assert all(got == pytest.approx(want, abs=5e-3 if name in ("fsdp8b", "moe_ep8") else 1.5e-3) for got, want in losses), (name, losses)
+    # 64 experts share 4096 tokens: most expert rows see a handful of tokens, and AdamW's normalised steps turn their
+    # tiny gradients around freely; the dense layouts stay within a few percent, e4m3 within its quantisation noise
+    assert drift < {"tp8": 0.05, "pp2tp4": 0.05, "fsdp8b": 0.4, "moe_ep8": 0.9}[name], (name, drift)
